@@ -1,0 +1,30 @@
+// Host-side helpers shared by every translation unit of the library: status codes,
+// per-device facts (queried once per device, never assumed from device 0) and the few
+// launch knobs that benchmarks may override.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "../../include/fpt_b200.h"
+
+namespace fpt {
+
+struct DeviceInfo {
+    int device;
+    int sm_count;
+    int64_t l2_bytes;
+    int cc_major, cc_minor;
+};
+
+struct Tuning {
+    int blocks_per_sm;  // persistent-grid cap: blocks per SM (0 = one block per tile, no cap)
+    int streaming;      // -1 decide from footprint vs L2, 0 never, 1 always
+};
+
+int current_device_info(DeviceInfo* out);
+Tuning tuning();
+
+inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? FPT_OK : int(e); }
+
+}  // namespace fpt

@@ -1,0 +1,132 @@
+// Process-wide host state: per-device facts, launch knobs, the program table and status strings.
+#include <atomic>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "fpt_programs.h"
+
+namespace fpt {
+
+namespace {
+constexpr int kMaxDevices = 64;
+struct DeviceSlot {
+    std::atomic<int> ready{0};
+    DeviceInfo info{};
+};
+DeviceSlot g_devices[kMaxDevices];
+std::mutex g_device_mutex;
+std::atomic<int> g_blocks_per_sm{0};
+std::atomic<int> g_streaming{-1};
+
+enum { DT_FP16 = kFp16, DT_BF16 = kBf16 };
+enum { SRC_CURRENT = FPT_SRC_CURRENT, SRC_SOLLYA = FPT_SRC_SOLLYA };
+enum { SH_ODD_HALF = kOddHalf, SH_ODD = kOdd, SH_ODD_SAT = kOddSat, SH_SWISH = kSwish, SH_XMUL_HALF = kXmulHalf,
+       SH_EVEN = kEven, SH_ALG_SIG = kAlgSig, SH_ALG_TANH = kAlgTanh };
+#define FPT_PROGRAM(NAME, DT, SRC, SHAPE, DEG, CLAMP, C0, C1, C2, C3, C4, C5, C6) \
+    { #NAME, DT_##DT, SRC_##SRC, SH_##SHAPE, DEG, CLAMP, { C0, C1, C2, C3, C4, C5, C6 } },
+const ProgramRow k_rows[] = {
+#include "fpt_program_table.inc"
+};
+#undef FPT_PROGRAM
+constexpr int k_row_count = int(sizeof(k_rows) / sizeof(k_rows[0]));
+}  // namespace
+
+int current_device_info(DeviceInfo* out) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? FPT_ERR_NO_DEVICE : int(e);
+    if (device < 0 || device >= kMaxDevices) return FPT_ERR_NO_DEVICE;
+    DeviceSlot& slot = g_devices[device];
+    if (!slot.ready.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_device_mutex);
+        if (!slot.ready.load(std::memory_order_relaxed)) {
+            DeviceInfo info{};
+            info.device = device;
+            int l2 = 0;
+            if ((e = cudaDeviceGetAttribute(&info.sm_count, cudaDevAttrMultiProcessorCount, device)) != cudaSuccess) return int(e);
+            if ((e = cudaDeviceGetAttribute(&l2, cudaDevAttrL2CacheSize, device)) != cudaSuccess) return int(e);
+            if ((e = cudaDeviceGetAttribute(&info.cc_major, cudaDevAttrComputeCapabilityMajor, device)) != cudaSuccess) return int(e);
+            if ((e = cudaDeviceGetAttribute(&info.cc_minor, cudaDevAttrComputeCapabilityMinor, device)) != cudaSuccess) return int(e);
+            info.l2_bytes = l2;
+            slot.info = info;
+            slot.ready.store(1, std::memory_order_release);
+        }
+    }
+    *out = slot.info;
+    if (out->cc_major != 10) return FPT_ERR_NO_DEVICE;
+    return FPT_OK;
+}
+
+Tuning tuning() { return Tuning{g_blocks_per_sm.load(), g_streaming.load()}; }
+
+const ProgramRow* program_table(int* count) {
+    if (count) *count = k_row_count;
+    return k_rows;
+}
+
+const ProgramRow* find_program(int function, int direction, int degree, int dtype, int source) {
+    static const char* const fn_names[] = {"SIGMOID", "TANH", "SWISH", "ERF", "GELU"};
+    if (function < 0 || function > FPT_FN_GELU || (direction != FPT_FWD && direction != FPT_BWD)) return nullptr;
+    char name[32];
+    std::snprintf(name, sizeof(name), "%s_%s_D%d", fn_names[function], direction == FPT_FWD ? "FWD" : "BWD", degree);
+    for (int i = 0; i < k_row_count; ++i)
+        if (k_rows[i].dtype == dtype && k_rows[i].source == source && !std::strcmp(k_rows[i].name, name)) return &k_rows[i];
+    return nullptr;
+}
+
+}  // namespace fpt
+
+extern "C" {
+
+const char* fpt_status_string(int status) {
+    switch (status) {
+    case FPT_OK: return "ok";
+    case FPT_ERR_NULL_POINTER: return "null pointer argument";
+    case FPT_ERR_BAD_SIZE: return "size argument out of range";
+    case FPT_ERR_MISALIGNED: return "pointer is not aligned as required";
+    case FPT_ERR_UNKNOWN_PROGRAM: return "no polynomial program for this function/direction/degree/dtype/source";
+    case FPT_ERR_BAD_ENUM: return "enumeration argument out of range";
+    case FPT_ERR_UNSUPPORTED_SHAPE: return "operation not defined for this program shape";
+    case FPT_ERR_NO_DEVICE: return "no usable CUDA device of compute capability 10.x is current";
+    case FPT_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    default: return status > 0 ? cudaGetErrorString(cudaError_t(status)) : "unknown status";
+    }
+}
+
+const char* fpt_version(void) { return "fpt_b200 0.1 sm_100a"; }
+
+int fpt_program_count(void) { return fpt::k_row_count; }
+
+int fpt_program_info(int index, char* name_out, int name_capacity, int* dtype, int* source, int* shape, int* degree,
+                     uint16_t* clamp, uint16_t* coeffs7) {
+    if (index < 0 || index >= fpt::k_row_count) return FPT_ERR_BAD_SIZE;
+    const fpt::ProgramRow& r = fpt::k_rows[index];
+    if (name_out && name_capacity > 0) {
+        std::strncpy(name_out, r.name, size_t(name_capacity) - 1);
+        name_out[name_capacity - 1] = 0;
+    }
+    if (dtype) *dtype = r.dtype;
+    if (source) *source = r.source;
+    if (shape) *shape = r.shape;
+    if (degree) *degree = r.degree;
+    if (clamp) *clamp = r.clamp;
+    if (coeffs7) std::memcpy(coeffs7, r.c, sizeof(r.c));
+    return FPT_OK;
+}
+
+int fpt_set_tuning(const char* key, int value) {
+    if (!key) return FPT_ERR_NULL_POINTER;
+    if (!std::strcmp(key, "blocks_per_sm")) { if (value < 0 || value > 64) return FPT_ERR_BAD_SIZE; fpt::g_blocks_per_sm = value; return FPT_OK; }
+    if (!std::strcmp(key, "streaming")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_streaming = value; return FPT_OK; }
+    return FPT_ERR_BAD_ENUM;
+}
+
+int fpt_get_tuning(const char* key, int* value) {
+    if (!key || !value) return FPT_ERR_NULL_POINTER;
+    if (!std::strcmp(key, "blocks_per_sm")) { *value = fpt::g_blocks_per_sm; return FPT_OK; }
+    if (!std::strcmp(key, "streaming")) { *value = fpt::g_streaming; return FPT_OK; }
+    return FPT_ERR_BAD_ENUM;
+}
+
+}  // extern "C"

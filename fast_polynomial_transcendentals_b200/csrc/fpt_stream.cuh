@@ -1,0 +1,210 @@
+// HBM-streaming element-wise kernel skeleton for sm_100a.
+//
+// One skeleton moves the bytes for every flat 16-bit element-wise operator of the
+// library (unary activations, gradient products, SwiGLU, B3 sigmoid, fractional
+// exp2): NIN input arrays and NOUT output arrays of the same length, processed in
+// per-thread vectors of 128 or 256 bits.  Each thread issues UNROLL independent
+// vector loads per input before it computes, so that a persistent grid of
+// (SM count x resident blocks) keeps enough bytes in flight to cover HBM latency.
+// Above the L2 size the loads and stores carry streaming (evict-first) hints;
+// below it they use the read-only path and plain stores so that back-to-back
+// launches stay L2 resident.  A ragged tail (length not a multiple of the vector
+// width) is finished by the last block with 16-bit accesses inside the same
+// launch; misaligned pointers take the all-scalar kernel.
+#pragma once
+
+#include <cstdint>
+#include <cuda_runtime.h>
+
+#include "fpt_common.h"
+
+namespace fpt {
+
+constexpr int kBlock = 256;
+
+template <int WORDS>
+struct alignas(WORDS * 4) Vec {
+    uint32_t w[WORDS];
+};
+
+template <int WORDS, bool STREAM>
+__device__ __forceinline__ Vec<WORDS> load_vec(const void* p) {
+    Vec<WORDS> v;
+    if constexpr (WORDS == 4) {
+        if constexpr (STREAM)
+            asm volatile("ld.global.cs.v4.b32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+        else
+            asm volatile("ld.global.nc.v4.b32 {%0,%1,%2,%3}, [%4];"
+                         : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]) : "l"(p));
+    } else {
+        if constexpr (STREAM)
+            asm volatile("ld.global.L1::no_allocate.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                           "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+        else
+            asm volatile("ld.global.nc.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
+                         : "=r"(v.w[0]), "=r"(v.w[1]), "=r"(v.w[2]), "=r"(v.w[3]), "=r"(v.w[4]), "=r"(v.w[5]),
+                           "=r"(v.w[6]), "=r"(v.w[7]) : "l"(p));
+    }
+    return v;
+}
+
+template <int WORDS, bool STREAM>
+__device__ __forceinline__ void store_vec(void* p, const Vec<WORDS>& v) {
+    if constexpr (WORDS == 4) {
+        if constexpr (STREAM)
+            asm volatile("st.global.cs.v4.b32 [%0], {%1,%2,%3,%4};"
+                         :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+        else
+            asm volatile("st.global.v4.b32 [%0], {%1,%2,%3,%4};"
+                         :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]) : "memory");
+    } else {
+        asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};"
+                     :: "l"(p), "r"(v.w[0]), "r"(v.w[1]), "r"(v.w[2]), "r"(v.w[3]), "r"(v.w[4]), "r"(v.w[5]),
+                        "r"(v.w[6]), "r"(v.w[7]) : "memory");
+    }
+}
+
+template <int NIN, int NOUT>
+struct StreamArgs {
+    const uint16_t* in[NIN];
+    uint16_t* out[NOUT];
+    int64_t n_vec;   // whole vectors
+    int64_t n_elem;  // all elements (tail = n_elem - n_vec * elements per vector)
+};
+
+// Op contract:  static constexpr int NIN, NOUT;
+//               __device__ void apply(const uint32_t (&in)[NIN], uint32_t (&out)[NOUT]) const;   (two lanes per word)
+template <class Op, int WORDS, int UNROLL, bool STREAM>
+__global__ void __launch_bounds__(kBlock) stream_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
+    constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+    constexpr int64_t kTile = int64_t(kBlock) * UNROLL;
+    const int64_t stride = int64_t(gridDim.x) * kTile;
+    for (int64_t tile = int64_t(blockIdx.x) * kTile; tile < a.n_vec; tile += stride) {
+        const int64_t first = tile + threadIdx.x;
+        Vec<WORDS> v[NIN][UNROLL];
+        const bool full = tile + kTile <= a.n_vec;
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t idx = first + int64_t(u) * kBlock;
+            if (full || idx < a.n_vec) {
+#pragma unroll
+                for (int i = 0; i < NIN; ++i)
+                    v[i][u] = load_vec<WORDS, STREAM>(reinterpret_cast<const Vec<WORDS>*>(a.in[i]) + idx);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < UNROLL; ++u) {
+            const int64_t idx = first + int64_t(u) * kBlock;
+            if (full || idx < a.n_vec) {
+                Vec<WORDS> r[NOUT];
+#pragma unroll
+                for (int w = 0; w < WORDS; ++w) {
+                    uint32_t xi[NIN], yo[NOUT];
+#pragma unroll
+                    for (int i = 0; i < NIN; ++i) xi[i] = v[i][u].w[w];
+                    op.apply(xi, yo);
+#pragma unroll
+                    for (int o = 0; o < NOUT; ++o) r[o].w[w] = yo[o];
+                }
+#pragma unroll
+                for (int o = 0; o < NOUT; ++o)
+                    store_vec<WORDS, STREAM>(reinterpret_cast<Vec<WORDS>*>(a.out[o]) + idx, r[o]);
+            }
+        }
+    }
+    if (blockIdx.x == gridDim.x - 1) {  // ragged tail, one element per thread step
+        for (int64_t e = a.n_vec * (WORDS * 2) + threadIdx.x; e < a.n_elem; e += kBlock) {
+            uint32_t xi[NIN], yo[NOUT];
+#pragma unroll
+            for (int i = 0; i < NIN; ++i) xi[i] = uint32_t(a.in[i][e]) * 0x00010001u;
+            op.apply(xi, yo);
+#pragma unroll
+            for (int o = 0; o < NOUT; ++o) a.out[o][e] = uint16_t(yo[o]);
+        }
+    }
+}
+
+// All-scalar variant for pointers that are not 16-byte aligned.
+template <class Op>
+__global__ void __launch_bounds__(kBlock) element_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
+    constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+    for (int64_t e = int64_t(blockIdx.x) * kBlock + threadIdx.x; e < a.n_elem; e += int64_t(gridDim.x) * kBlock) {
+        uint32_t xi[NIN], yo[NOUT];
+#pragma unroll
+        for (int i = 0; i < NIN; ++i) xi[i] = uint32_t(a.in[i][e]) * 0x00010001u;
+        op.apply(xi, yo);
+#pragma unroll
+        for (int o = 0; o < NOUT; ++o) a.out[o][e] = uint16_t(yo[o]);
+    }
+}
+
+template <class Op, int WORDS, int UNROLL, bool STREAM>
+static int launch_stream_config(const Op& op, const StreamArgs<Op::NIN, Op::NOUT>& a, const DeviceInfo& dev,
+                                const Tuning& t, cudaStream_t stream) {
+    auto kernel = stream_kernel<Op, WORDS, UNROLL, STREAM>;
+    const int64_t tiles = (a.n_vec + int64_t(kBlock) * UNROLL - 1) / (int64_t(kBlock) * UNROLL);
+    int64_t grid = tiles > 0 ? tiles : 1;
+    if (t.blocks_per_sm > 0) {
+        const int64_t cap = int64_t(dev.sm_count) * t.blocks_per_sm;
+        if (grid > cap) grid = cap;
+    }
+    if (grid > 0x7fffffff) grid = 0x7fffffff;
+    kernel<<<unsigned(grid), kBlock, 0, stream>>>(op, a);
+    return cuda_status(cudaGetLastError());
+}
+
+// Launch configuration per regime (chosen by measurement on B200, see the sweep numbers in
+// the design notes): vector width in 32-bit words, independent loads per thread.
+#ifndef FPT_STREAM_WORDS
+#define FPT_STREAM_WORDS 4
+#endif
+#ifndef FPT_STREAM_UNROLL
+#define FPT_STREAM_UNROLL 4
+#endif
+#ifndef FPT_RESIDENT_WORDS
+#define FPT_RESIDENT_WORDS 4
+#endif
+#ifndef FPT_RESIDENT_UNROLL
+#define FPT_RESIDENT_UNROLL 2
+#endif
+
+// `bytes touched > L2` selects the streaming regime (evict-first hints, deeper unroll).
+template <class Op>
+static int launch_stream(const Op& op, StreamArgs<Op::NIN, Op::NOUT> a, int64_t n_elem, cudaStream_t stream) {
+    if (n_elem <= 0) return FPT_OK;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+    const Tuning t = tuning();
+    a.n_elem = n_elem;
+    uintptr_t align = 0;
+    for (int i = 0; i < Op::NIN; ++i) align |= reinterpret_cast<uintptr_t>(a.in[i]);
+    for (int o = 0; o < Op::NOUT; ++o) align |= reinterpret_cast<uintptr_t>(a.out[o]);
+    if (align & 1u) return FPT_ERR_MISALIGNED;
+    const int64_t bytes = n_elem * 2 * (Op::NIN + Op::NOUT);
+    const bool streaming = t.streaming < 0 ? bytes > dev.l2_bytes : t.streaming != 0;
+    constexpr uintptr_t kStreamAlign = FPT_STREAM_WORDS * 4 - 1, kResidentAlign = FPT_RESIDENT_WORDS * 4 - 1;
+    if (align & (streaming ? kStreamAlign : kResidentAlign)) {
+        if constexpr (FPT_STREAM_WORDS == 8 || FPT_RESIDENT_WORDS == 8) {
+            if (!(align & 15u)) {  // 16-byte aligned but not 32: narrow vectors
+                a.n_vec = n_elem / 8;
+                return launch_stream_config<Op, 4, 2, false>(op, a, dev, t, stream);
+            }
+        }
+        a.n_vec = 0;
+        int64_t grid = (n_elem + kBlock - 1) / kBlock;
+        const int64_t cap = int64_t(dev.sm_count) * 32;
+        if (grid > cap) grid = cap;
+        element_kernel<Op><<<unsigned(grid), kBlock, 0, stream>>>(op, a);
+        return cuda_status(cudaGetLastError());
+    }
+    if (streaming) {
+        a.n_vec = n_elem / (FPT_STREAM_WORDS * 2);
+        return launch_stream_config<Op, FPT_STREAM_WORDS, FPT_STREAM_UNROLL, true>(op, a, dev, t, stream);
+    }
+    a.n_vec = n_elem / (FPT_RESIDENT_WORDS * 2);
+    return launch_stream_config<Op, FPT_RESIDENT_WORDS, FPT_RESIDENT_UNROLL, false>(op, a, dev, t, stream);
+}
+
+}  // namespace fpt

@@ -1,0 +1,274 @@
+"""The reference's ``spline_ops`` operator surface on top of the C ABI.
+
+Same op names, argument order, defaults, output allocation and error behaviour
+as the reference's pybind module (reference:
+autonumerics_zero/spline_ops/spline_ops.cpp:2285-2452; argument checks
+:293-298, :1647-1649, :1671-1686), implemented as thin Python functions that
+validate torch CUDA tensors, allocate the output and call
+``libfpt_b200.so`` on the current stream of the tensor's device.
+
+Differences kept on purpose:
+  * the call runs under a device guard for the input tensor's device (the
+    reference assumes the current device already matches);
+  * element counts are 64-bit all the way down (the reference narrows
+    ``numel()`` to ``int`` for the flat ops).
+Errors are ``RuntimeError`` like ``TORCH_CHECK``.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from ._lib import BF16, BWD, FN_GELU, FN_SIGMOID, FN_SWISH, FN_TANH, FP16, FWD
+
+_FUNCTIONS = {"sigmoid": FN_SIGMOID, "tanh": FN_TANH, "swish": FN_SWISH, "gelu": FN_GELU}
+_DEFAULT_DEGREE = {("sigmoid", "fwd"): 3, ("sigmoid", "bwd"): 4, ("tanh", "fwd"): 3, ("tanh", "bwd"): 4,
+                   ("swish", "fwd"): 3, ("swish", "bwd"): 4, ("gelu", "fwd"): 5, ("gelu", "bwd"): 5}
+
+
+def _check_input(x: torch.Tensor, name: str) -> None:
+    if not isinstance(x, torch.Tensor) or not x.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not x.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if x.dtype not in (torch.float16, torch.bfloat16):
+        raise RuntimeError(f"{name} must be float16 or bfloat16")
+
+
+def _check_fp16(x: torch.Tensor, name: str) -> None:
+    _check_input(x, name)
+    if x.dtype != torch.float16:
+        raise RuntimeError(f"{name} must be float16")
+
+
+def _dtype_id(x: torch.Tensor) -> int:
+    return BF16 if x.dtype == torch.bfloat16 else FP16
+
+
+def _source(coeff_source_id: int, x: torch.Tensor) -> int:
+    if coeff_source_id not in (0, 1):
+        raise RuntimeError("coeff_source_id must be 0 (current) or 1 (sollya)")
+    if coeff_source_id == 1 and x.dtype != torch.bfloat16:
+        raise RuntimeError("FP16 spline kernels only support coeff_source=current")
+    return int(coeff_source_id)
+
+
+def _same(a: torch.Tensor, b: torch.Tensor, an: str, bn: str) -> None:
+    if a.dtype != b.dtype:
+        raise RuntimeError(f"{an} and {bn} must have the same dtype")
+    if a.numel() != b.numel():
+        raise RuntimeError(f"{an} and {bn} must have the same number of elements")
+
+
+class _Guard:
+    """Make the tensor's device current for the duration of one launch."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, x: torch.Tensor):
+        self.index = x.device.index
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+        return torch.cuda.current_stream(self.index).cuda_stream
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
+def _call(name: str, x: torch.Tensor, *args) -> None:
+    fn = getattr(_lib.load(), name)
+    with _Guard(x) as stream:
+        status = fn(*args, stream)
+    if status != 0:
+        _lib.check(name, status)
+
+
+# ---- unary / gradient products -------------------------------------------------------------
+
+def _unary(x, function: str, direction: int, degree: int, source: int = 0):
+    _check_input(x, "x")
+    out = torch.empty_like(x)
+    try:
+        _call("fpt_unary", x, out.data_ptr(), x.data_ptr(), x.numel(), _FUNCTIONS[function], direction, degree,
+              _dtype_id(x), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            which = "forward" if direction == FWD else "backward"
+            raise RuntimeError(f"Unsupported {function} {which} degree: {degree}") from None
+        raise
+    return out
+
+
+def _binary(grad_out, x, function: str, degree: int, source: int = 0):
+    _check_input(grad_out, "grad_out")
+    _check_input(x, "x")
+    _same(grad_out, x, "grad_out", "x")
+    grad_in = torch.empty_like(x)
+    try:
+        _call("fpt_binary_bwd", x, grad_in.data_ptr(), grad_out.data_ptr(), x.data_ptr(), x.numel(),
+              _FUNCTIONS[function], degree, _dtype_id(x), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            raise RuntimeError(f"Unsupported {function} backward degree: {degree}") from None
+        raise
+    return grad_in
+
+
+def _make_fixed(function: str, direction: str, degree: int):
+    if direction == "fwd":
+        def op(x):
+            return _unary(x, function, FWD, degree)
+    else:
+        def op(grad_out, x):
+            return _binary(grad_out, x, function, degree)
+    return op
+
+
+for _fn in ("sigmoid", "tanh", "swish", "gelu"):
+    for _dir in ("fwd", "bwd"):
+        globals()[f"{_fn}_{_dir}"] = _make_fixed(_fn, _dir, _DEFAULT_DEGREE[(_fn, _dir)])
+        globals()[f"{_fn}_{_dir}"].__doc__ = f"{_fn} {_dir}, default degree {_DEFAULT_DEGREE[(_fn, _dir)]}"
+        for _deg in (3, 4, 5, 6):
+            globals()[f"{_fn}_{_dir}_d{_deg}"] = _make_fixed(_fn, _dir, _deg)
+
+
+def sigmoid_fwd_variant(x, degree: int, coeff_source_id: int):
+    return _unary(x, "sigmoid", FWD, int(degree), _source(coeff_source_id, x))
+
+
+def sigmoid_bwd_variant(grad_out, x, degree: int, coeff_source_id: int):
+    return _binary(grad_out, x, "sigmoid", int(degree), _source(coeff_source_id, x))
+
+
+def swish_fwd_variant(x, degree: int, coeff_source_id: int):
+    """degree 0 selects the native special-function-unit kernel."""
+    return _unary(x, "swish", FWD, int(degree), _source(coeff_source_id, x))
+
+
+def swish_bwd_variant(grad_out, x, degree: int, coeff_source_id: int):
+    return _binary(grad_out, x, "swish", int(degree), _source(coeff_source_id, x))
+
+
+def gelu_fwd_variant(x, degree: int, coeff_source_id: int):
+    return _unary(x, "gelu", FWD, int(degree), _source(coeff_source_id, x))
+
+
+def gelu_bwd_variant(grad_out, x, degree: int, coeff_source_id: int):
+    return _binary(grad_out, x, "gelu", int(degree), _source(coeff_source_id, x))
+
+
+def _alg(grad_out, y, function: str):
+    _check_input(grad_out, "grad_out")
+    _check_input(y, "x")
+    grad_in = torch.empty_like(y)
+    _call("fpt_bwd_algebraic", y, grad_in.data_ptr(), grad_out.data_ptr(), y.data_ptr(), y.numel(),
+          _FUNCTIONS[function], _dtype_id(y))
+    return grad_in
+
+
+def sigmoid_bwd_alg(grad_out, y):
+    """grad_in = grad_out * y * (1 - y) from the saved forward output."""
+    return _alg(grad_out, y, "sigmoid")
+
+
+def tanh_bwd_alg(grad_out, y):
+    """grad_in = grad_out * (1 - y^2) from the saved forward output."""
+    return _alg(grad_out, y, "tanh")
+
+
+# ---- SwiGLU --------------------------------------------------------------------------------
+
+def swish_mul_fwd_variant(gate, up, degree: int, coeff_source_id: int):
+    _check_input(gate, "gate")
+    _check_input(up, "up")
+    _same(gate, up, "gate", "up")
+    source = _source(coeff_source_id, gate)
+    out = torch.empty_like(up)
+    try:
+        _call("fpt_swish_mul", gate, out.data_ptr(), gate.data_ptr(), up.data_ptr(), gate.numel(), int(degree),
+              _dtype_id(gate), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            raise RuntimeError(f"Unsupported swish_mul forward degree: {degree}") from None
+        raise
+    return out
+
+
+def swish_mul_bwd_variant(grad_out, gate, up, degree: int, coeff_source_id: int):
+    for t, n in ((grad_out, "grad_out"), (gate, "gate"), (up, "up")):
+        _check_input(t, n)
+    if not (grad_out.dtype == gate.dtype == up.dtype):
+        raise RuntimeError("grad_out, gate, and up must have the same dtype")
+    if not (grad_out.numel() == gate.numel() == up.numel()):
+        raise RuntimeError("grad_out, gate, and up must have the same number of elements")
+    source = _source(coeff_source_id, gate)
+    grad_gate, grad_up = torch.empty_like(gate), torch.empty_like(up)
+    try:
+        _call("fpt_swish_mul_bwd", gate, grad_gate.data_ptr(), grad_up.data_ptr(), grad_out.data_ptr(),
+              gate.data_ptr(), up.data_ptr(), gate.numel(), int(degree), _dtype_id(gate), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            raise RuntimeError(f"Unsupported swish_mul backward degree: {degree}") from None
+        raise
+    return [grad_gate, grad_up]
+
+
+def _packed_dims(packed):
+    if packed.dim() < 1:
+        raise RuntimeError("packed gate/up tensor must have at least one dimension")
+    width = packed.size(-1)
+    if width % 2:
+        raise RuntimeError("packed gate/up last dimension must be even")
+    hidden = width // 2
+    if hidden % 2:
+        raise RuntimeError("packed SwiGLU hidden size must be even")
+    return width, hidden
+
+
+def swish_mul_packed_fwd_variant(packed, degree: int, coeff_source_id: int):
+    """packed [..., 2H] = [gate | up]  ->  [..., H]."""
+    _check_input(packed, "packed")
+    width, hidden = _packed_dims(packed)
+    source = _source(coeff_source_id, packed)
+    out = torch.empty(*packed.shape[:-1], hidden, dtype=packed.dtype, device=packed.device)
+    if packed.numel() == 0:
+        return out
+    rows = packed.numel() // width
+    try:
+        _call("fpt_swish_mul_packed", packed, out.data_ptr(), packed.data_ptr(), rows, hidden, int(degree),
+              _dtype_id(packed), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            raise RuntimeError(f"Unsupported packed swish_mul forward degree: {degree}") from None
+        raise
+    return out
+
+
+def swish_mul_packed_bwd_variant(grad_out, packed, degree: int, coeff_source_id: int):
+    _check_input(grad_out, "grad_out")
+    _check_input(packed, "packed")
+    if grad_out.dtype != packed.dtype:
+        raise RuntimeError("grad_out and packed must have the same dtype")
+    width, hidden = _packed_dims(packed)
+    if grad_out.numel() * 2 != packed.numel() or (grad_out.dim() and grad_out.size(-1) != hidden):
+        raise RuntimeError("grad_out must match the packed tensor with its last dimension halved")
+    source = _source(coeff_source_id, packed)
+    grad_packed = torch.empty_like(packed)
+    if packed.numel() == 0:
+        return grad_packed
+    rows = packed.numel() // width
+    try:
+        _call("fpt_swish_mul_packed_bwd", packed, grad_packed.data_ptr(), grad_out.data_ptr(), packed.data_ptr(),
+              rows, hidden, int(degree), _dtype_id(packed), source)
+    except _lib.FptError as err:
+        if err.status == -4:
+            raise RuntimeError(f"Unsupported packed swish_mul backward degree: {degree}") from None
+        raise
+    return grad_packed

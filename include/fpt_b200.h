@@ -1,0 +1,113 @@
+/*
+ * fpt_b200 -- C ABI of the B200 (sm_100a) packed polynomial transcendental library.
+ *
+ * Drop-in boundary: the reference separates its torch-facing C++ (spline_ops.cpp)
+ * from its CUDA kernels by `extern "C" void launch_*(void* out, const void* in, ...,
+ * int size, cudaStream_t)` launchers (reference: autonumerics_zero/spline_ops/
+ * spline_ops.cpp:14-288).  This library offers that boundary twice:
+ *
+ *   1. the `fpt_*` entry points below: one entry point per operator family, the
+ *      program selected by (function, direction, degree, dtype, coefficient
+ *      source) instead of by symbol name; 64-bit sizes; an `int` status return
+ *      (0 ok, negative = rejected argument, positive = cudaError_t);
+ *   2. the reference's own `launch_*` symbols with the reference's exact
+ *      signatures (declared in fpt_b200_compat.h), thin shims over (1), so the
+ *      reference's spline_ops.cpp links against this library unchanged.
+ *
+ * Conventions: every pointer is a device pointer owned by the caller; 16-bit data
+ * are fp16 or bf16 bit patterns according to `dtype`; work is enqueued on `stream`
+ * of the CURRENT device and the call returns without synchronising; no entry
+ * point allocates device memory.  All entry points may be called concurrently
+ * from several host threads and for several devices.
+ */
+#ifndef FPT_B200_H
+#define FPT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* fpt_stream_t; /* == cudaStream_t */
+
+/* status codes (positive values are cudaError_t) */
+#define FPT_OK 0
+#define FPT_ERR_NULL_POINTER (-1)
+#define FPT_ERR_BAD_SIZE (-2)
+#define FPT_ERR_MISALIGNED (-3)      /* pointer not aligned to the element size / required vector width */
+#define FPT_ERR_UNKNOWN_PROGRAM (-4) /* no program for (function, direction, degree, dtype, source) */
+#define FPT_ERR_BAD_ENUM (-5)
+#define FPT_ERR_UNSUPPORTED_SHAPE (-6)
+#define FPT_ERR_NO_DEVICE (-7)       /* no CUDA device, or not compute capability 10.x */
+#define FPT_ERR_DEVICE_TIMEOUT (-8)  /* a bounded device-side wait ran out (attention kernel status word) */
+
+enum { FPT_FP16 = 0, FPT_BF16 = 1 };
+enum { FPT_SRC_CURRENT = 0, FPT_SRC_SOLLYA = 1 };
+enum { FPT_FN_SIGMOID = 0, FPT_FN_TANH = 1, FPT_FN_SWISH = 2, FPT_FN_ERF = 3, FPT_FN_GELU = 4 };
+enum { FPT_FWD = 0, FPT_BWD = 1 };
+/* degree: 3..6 selects the polynomial of that degree; 0 selects the native special-function-unit
+ * (MUFU) control that shares the same memory code. */
+
+const char* fpt_status_string(int status);
+/* library / build identification, e.g. "fpt_b200 sm_100a" */
+const char* fpt_version(void);
+
+/* ---- program table (reference: spline_structs_odd.cuh:14-1047, spline_structs_odd_bf16.cuh:11-1006,
+ *      spline_structs_sollya_bf16.cuh:14-852) ------------------------------------------------------ */
+int fpt_program_count(void);
+/* name_out receives e.g. "SIGMOID_FWD_D3"; coeffs7 receives the seven 16-bit coefficient slots. */
+int fpt_program_info(int index, char* name_out, int name_capacity, int* dtype, int* source, int* shape,
+                     int* degree, uint16_t* clamp, uint16_t* coeffs7);
+
+/* ---- unary activations: out = F(in)
+ *      replaces launch_{sigmoid,tanh,swish,gelu}_fwd_d{3..6}_kernel[_bf16[_sollya]] and
+ *      launch_swish_fwd_native_kernel[_bf16] (reference: spline_kernels.cu:49-64,544-571,1177-1250;
+ *      spline_kernels_bf16.cu:57-72,636-668).  direction FPT_BWD evaluates the derivative program F'(in). */
+int fpt_unary(void* out, const void* in, int64_t n, int function, int direction, int degree, int dtype,
+              int source, fpt_stream_t stream);
+/* `repeats` evaluations per loaded element, each fed back as the next input (val <- F(val)); the
+ * ALU-bound probe of the reference's repeated-evaluation benchmarks (benchmark_bfloat16_sollya.cu:70-82). */
+int fpt_unary_repeat(void* out, const void* in, int64_t n, int function, int direction, int degree, int dtype,
+                     int source, int repeats, fpt_stream_t stream);
+
+/* ---- gradient products: grad_in = grad_out * F'(x)
+ *      replaces launch_{sigmoid,tanh,swish,gelu}_bwd_d{3..6}_kernel[_bf16[_sollya]],
+ *      launch_swish_bwd_native_kernel[_bf16] (reference: spline_kernels.cu:66-90,573-607). */
+int fpt_binary_bwd(void* grad_in, const void* grad_out, const void* x, int64_t n, int function, int degree,
+                   int dtype, int source, fpt_stream_t stream);
+/* grad_in = grad_out * g(y) with y the saved forward output: sigmoid y(1-y), tanh 1-y^2
+ *      replaces launch_{sigmoid,tanh}_bwd_alg_kernel[_bf16] (reference: spline_structs_odd.cuh:668-682). */
+int fpt_bwd_algebraic(void* grad_in, const void* grad_out, const void* y, int64_t n, int function, int dtype,
+                      fpt_stream_t stream);
+
+/* ---- SwiGLU: out = swish(gate) * up over flat arrays (B4 routed experts, B1 unpacked)
+ *      replaces launch_swish_mul_fwd_{native,d3..d6}_kernel[_bf16[_sollya]]
+ *      (reference: spline_kernels.cu:137-158,609-642; spline_kernels_bf16.cu:143-164,705-739). */
+int fpt_swish_mul(void* out, const void* gate, const void* up, int64_t n, int degree, int dtype, int source,
+                  fpt_stream_t stream);
+/* grad_gate = (grad_out*up)*swish'(gate), grad_up = grad_out*swish(gate)
+ *      replaces launch_swish_mul_bwd_* (reference: spline_kernels.cu:183-245; bf16 D3/current uses the
+ *      shared-sigmoid form of spline_kernels_bf16.cu:255-341). */
+int fpt_swish_mul_bwd(void* grad_gate, void* grad_up, const void* grad_out, const void* gate, const void* up,
+                      int64_t n, int degree, int dtype, int source, fpt_stream_t stream);
+
+/* ---- packed SwiGLU (B1 dense FFN): packed [rows, 2*hidden] = [gate | up] -> out [rows, hidden]
+ *      replaces launch_swish_mul_packed_fwd_{native,d3..d6}_kernel[_bf16[_sollya]]
+ *      (reference: spline_kernels.cu:247-351,700-733; spline_kernels_bf16.cu:421-503,838-883). */
+int fpt_swish_mul_packed(void* out, const void* packed, int64_t rows, int64_t hidden, int degree, int dtype,
+                         int source, fpt_stream_t stream);
+/* grad_packed [rows, 2*hidden] from grad_out [rows, hidden] and packed
+ *      replaces launch_swish_mul_packed_bwd_* (reference: spline_kernels.cu:418-494,735-769). */
+int fpt_swish_mul_packed_bwd(void* grad_packed, const void* grad_out, const void* packed, int64_t rows,
+                             int64_t hidden, int degree, int dtype, int source, fpt_stream_t stream);
+
+/* ---- launch knobs for benchmarks (process-wide; defaults are the measured-best values) -------- */
+/* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1. */
+int fpt_set_tuning(const char* key, int value);
+int fpt_get_tuning(const char* key, int* value);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FPT_B200_H */

@@ -1,0 +1,142 @@
+"""GPU parity of fused SwiGLU (flat B4 form and packed B1 form), forward and backward."""
+import numpy as np
+import pytest
+
+from util import assert_bits_equal, normal_bits, ref_call, to_bits, to_device
+
+pytestmark = pytest.mark.gpu
+
+CASES = [("fp16", 0, 0, ""), ("bf16", 1, 0, "_bf16"), ("bf16", 1, 1, "_bf16_sollya")]
+
+
+def stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def swiglu(fpt, cuda, gb, ub, degree, dtype, dt, source):
+    import torch
+    g, u = to_device(gb, dtype, cuda), to_device(ub, dtype, cuda)
+    out = torch.empty_like(g)
+    fpt.call("fpt_swish_mul", out.data_ptr(), g.data_ptr(), u.data_ptr(), g.numel(), degree, dt, source, stream())
+    torch.cuda.synchronize()
+    return to_bits(out)
+
+
+@pytest.mark.parametrize("n", [5, 8 * 4096 + 3, 1408 * 777])
+def test_flat_forward_bit_exact(fpt, cuda, oracle, n):
+    for dtype, dt, source, _ in CASES:
+        for degree in (3, 4, 5, 6):
+            gb, ub = normal_bits(n, 1.5, dtype, seed=degree), normal_bits(n, 1.5, dtype, seed=degree + 9)
+            idx = oracle.find_program(f"SWISH_FWD_D{degree}", dt, source)
+            assert_bits_equal(swiglu(fpt, cuda, gb, ub, degree, dtype, dt, source), oracle.swiglu(idx, gb, ub),
+                              f"swiglu d{degree} {dtype} src{source} n={n}", gb)
+
+
+def test_flat_equals_unary_times_up_and_reference_tails(fpt, cuda, oracle):
+    """Fused swish_mul == swish_fwd * up exactly; bf16 tails [-100,-20,20,100] * 1 -> [0,0,20,100]."""
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_ops
+    g = torch.randn(1 << 16, device=cuda).mul_(3).to(torch.bfloat16)
+    u = torch.randn(1 << 16, device=cuda).to(torch.bfloat16)
+    for degree in (3, 4, 5, 6):
+        fused = spline_ops.swish_mul_fwd_variant(g, u, degree, 0)
+        split = spline_ops.swish_fwd_variant(g, degree, 0) * u
+        assert torch.equal(fused, split)
+        tails = torch.tensor([-100.0, -20.0, 20.0, 100.0], device=cuda, dtype=torch.bfloat16)
+        out = spline_ops.swish_mul_fwd_variant(tails, torch.ones_like(tails), degree, 0)
+        assert out.float().tolist() == [0.0, 0.0, 20.0, 100.0]
+
+
+@pytest.mark.parametrize("rows,hidden", [(3, 8), (37, 512), (33, 1408), (64, 14336), (5, 6), (7, 10), (1024, 768)])
+def test_packed_forward_bit_exact_and_equals_unpacked(fpt, cuda, oracle, rows, hidden):
+    import torch
+    for dtype, dt, source, _ in CASES:
+        for degree in (3, 5):
+            pb = normal_bits(rows * 2 * hidden, 1.5, dtype, seed=rows + degree).reshape(rows, 2 * hidden)
+            idx = oracle.find_program(f"SWISH_FWD_D{degree}", dt, source)
+            packed = to_device(pb, dtype, cuda)
+            out = torch.empty(rows, hidden, dtype=packed.dtype, device=cuda)
+            fpt.call("fpt_swish_mul_packed", out.data_ptr(), packed.data_ptr(), rows, hidden, degree, dt, source, stream())
+            torch.cuda.synchronize()
+            want = oracle.swiglu_packed(idx, pb)
+            assert_bits_equal(to_bits(out), want, f"packed {rows}x{hidden} d{degree} {dtype}")
+            flat = swiglu(fpt, cuda, np.ascontiguousarray(pb[:, :hidden]), np.ascontiguousarray(pb[:, hidden:]),
+                          degree, dtype, dt, source)
+            assert_bits_equal(to_bits(out), flat, "packed == unpacked")
+
+
+def test_backward_flat_and_packed_bit_exact(fpt, cuda, oracle):
+    import torch
+    rows, hidden = 129, 264
+    n = rows * hidden
+    for dtype, dt, source, _ in CASES:
+        for degree in (3, 4, 5, 6):
+            gb, ub, gob = (normal_bits(n, 1.5, dtype, seed=s + degree) for s in (1, 2, 3))
+            if degree == 3 and dt == 1 and source == 0:
+                sig = oracle.find_program("SIGMOID_FWD_D3", 1, 0)
+                want_gg, want_gu = oracle.swiglu_bwd_shared_sigmoid(sig, gob, gb, ub)
+            else:
+                f = oracle.find_program(f"SWISH_FWD_D{degree}", dt, source)
+                b = oracle.find_program(f"SWISH_BWD_D{degree}", dt, source)
+                want_gg, want_gu = oracle.swiglu_bwd(f, b, gob, gb, ub)
+            g, u, go = (to_device(x, dtype, cuda) for x in (gb, ub, gob))
+            gg, gu = torch.empty_like(g), torch.empty_like(g)
+            fpt.call("fpt_swish_mul_bwd", gg.data_ptr(), gu.data_ptr(), go.data_ptr(), g.data_ptr(), u.data_ptr(), n,
+                     degree, dt, source, stream())
+            torch.cuda.synchronize()
+            assert_bits_equal(to_bits(gg), want_gg, f"grad_gate d{degree} {dtype} src{source}", gb)
+            assert_bits_equal(to_bits(gu), want_gu, f"grad_up d{degree} {dtype} src{source}", gb)
+            packed = torch.cat([g.view(rows, hidden), u.view(rows, hidden)], dim=1).contiguous()
+            gp = torch.empty_like(packed)
+            fpt.call("fpt_swish_mul_packed_bwd", gp.data_ptr(), go.data_ptr(), packed.data_ptr(), rows, hidden, degree,
+                     dt, source, stream())
+            torch.cuda.synchronize()
+            assert_bits_equal(to_bits(gp[:, :hidden].contiguous()), want_gg, "packed grad_gate")
+            assert_bits_equal(to_bits(gp[:, hidden:].contiguous()), want_gu, "packed grad_up")
+
+
+def test_native_swiglu_close_to_torch(fpt, cuda):
+    import torch
+    g = torch.randn(1 << 18, device=cuda).mul_(1.5).to(torch.bfloat16)
+    u = torch.randn(1 << 18, device=cuda).mul_(1.5).to(torch.bfloat16)
+    out = torch.empty_like(g)
+    fpt.call("fpt_swish_mul", out.data_ptr(), g.data_ptr(), u.data_ptr(), g.numel(), 0, 1, 0, stream())
+    torch.cuda.synchronize()
+    want = (torch.nn.functional.silu(g.float()).to(torch.bfloat16) * u)
+    assert float((out.float() - want.float()).abs().max()) <= 0.07
+
+
+def test_reference_kernels_agree_bit_for_bit(fpt, cuda, ref_kernels):
+    """Same inputs through the reference's launch_swish_mul_* kernels and ours: identical bits."""
+    import torch
+    rows, hidden = 256, 1408
+    n = rows * hidden
+    for dtype, dt, source, suffix in CASES:
+        for degree in (3, 4, 5, 6):
+            gb, ub, gob = (normal_bits(n, 1.5, dtype, seed=s * 7 + degree) for s in (1, 2, 3))
+            g, u, go = (to_device(x, dtype, cuda) for x in (gb, ub, gob))
+            ours, ref = torch.empty_like(g), torch.empty_like(g)
+            fpt.call("fpt_swish_mul", ours.data_ptr(), g.data_ptr(), u.data_ptr(), n, degree, dt, source, stream())
+            torch.cuda.synchronize()
+            ref_call(ref_kernels, f"launch_swish_mul_fwd_d{degree}_kernel{suffix}", ref, g, u, n)
+            torch.cuda.synchronize()
+            assert_bits_equal(to_bits(ours), to_bits(ref), f"swish_mul_fwd d{degree}{suffix}", gb)
+
+            packed = torch.cat([g.view(rows, hidden), u.view(rows, hidden)], dim=1).contiguous()
+            ours_p = torch.empty(rows, hidden, dtype=g.dtype, device=cuda)
+            ref_p = torch.empty_like(ours_p)
+            fpt.call("fpt_swish_mul_packed", ours_p.data_ptr(), packed.data_ptr(), rows, hidden, degree, dt, source, stream())
+            torch.cuda.synchronize()
+            ref_call(ref_kernels, f"launch_swish_mul_packed_fwd_d{degree}_kernel{suffix}", ref_p, packed, rows, hidden)
+            torch.cuda.synchronize()
+            assert_bits_equal(to_bits(ours_p), to_bits(ref_p), f"swish_mul_packed_fwd d{degree}{suffix}")
+
+            gg, gu, rgg, rgu = (torch.empty_like(g) for _ in range(4))
+            fpt.call("fpt_swish_mul_bwd", gg.data_ptr(), gu.data_ptr(), go.data_ptr(), g.data_ptr(), u.data_ptr(), n,
+                     degree, dt, source, stream())
+            torch.cuda.synchronize()
+            ref_call(ref_kernels, f"launch_swish_mul_bwd_d{degree}_kernel{suffix}", rgg, rgu, go, g, u, n)
+            torch.cuda.synchronize()
+            assert_bits_equal(to_bits(gg), to_bits(rgg), f"swish_mul_bwd gate d{degree}{suffix}", gb)
+            assert_bits_equal(to_bits(gu), to_bits(rgu), f"swish_mul_bwd up d{degree}{suffix}", gb)
