@@ -1,0 +1,421 @@
+#!/usr/bin/env python3
+"""Benchmark of the packed polynomial transcendental hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (one "step"): the isolated FP16 function sweep at the HBM endpoint, N = 2^28 elements per function
+and per GPU -- polynomial sigmoid D3, tanh D4, SiLU D3, fractional exp2 (hinge) and paired sin/cos (D5/D6
+half turn) -- on seeded synthetic inputs already resident in HBM.  `value` is elements/s over the whole job
+(all functions, all GPUs).  Every function is also run in its native special-function-unit form and, at the
+L2-resident endpoint N = 2^20, in both forms; those numbers, the SwiGLU and B3 lines ride along in
+`functions` / `extras`.  `e2e` is the same sweep through the public `spline_ops` API from pinned HOST buffers
+with both PCIe copies inside the timed region.  Prints ONE JSON line on rank 0.
+
+`--impl reference` times the CPU path instead: this repository's exact packed-arithmetic emulator (the port of
+the reference's programs used as the parity oracle) with all host threads on a bounded sample of the sweep.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+N_HBM = 1 << 28
+N_L2 = 1 << 20
+SEED = 1234
+NOMINAL_HBM_GBS = 8000.0
+
+
+def measured_peaks():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        d = json.loads(path.read_text())
+        return float(d["hbm_gbs"]), float(d.get("bf16_tflops", 1590.0)), "measured"
+    return 6650.0, 1590.0, "fallback"
+
+
+# ------------------------------------------------------------------------------------ CPU arm
+
+def cpu_sample_inputs(n):
+    import numpy as np
+    rng = np.random.default_rng(SEED)
+    u8 = rng.uniform(-8, 8, n).astype(np.float16).view(np.uint16)
+    frac = rng.uniform(0, 1, n).astype(np.float16).view(np.uint16)
+    ang = rng.uniform(-math.pi, math.pi, n).astype(np.float32)
+    return u8, frac, ang
+
+
+def cpu_sweep(oracle, inputs):
+    """One pass of the sweep on the CPU emulator; returns elements processed."""
+    u8, frac, ang = inputs
+    oracle.unary(oracle.find_program("SIGMOID_FWD_D3", 0), u8)
+    oracle.unary(oracle.find_program("TANH_FWD_D4", 0), u8)
+    oracle.unary(oracle.find_program("SWISH_FWD_D3", 0), u8)
+    oracle.exp2_hinge(frac, 0)
+    oracle.sincos_packed("d5_d6_half_turn_fp16", ang)
+    return 5 * u8.size
+
+
+def cpu_baseline(sample_elems=1 << 22, budget_s=12.0):
+    from oracle import oracle
+    oracle.build()
+    inputs = cpu_sample_inputs(sample_elems)
+    cpu_sweep(oracle, inputs)
+    t0 = time.perf_counter()
+    done, passes = 0, 0
+    while time.perf_counter() - t0 < budget_s and passes < 8:
+        done += cpu_sweep(oracle, inputs)
+        passes += 1
+    dt = time.perf_counter() - t0
+    return {"value": done / dt, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+            "sample": f"{passes} passes of the 5-function sweep at 2^{int(math.log2(sample_elems))} elements per "
+                      f"function, exact packed-FMA emulator (OpenMP, all host threads)"}
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from oracle import oracle
+    oracle.build()
+    n = 1 << 21
+    inputs = cpu_sample_inputs(n)
+    for _ in range(max(1, min(args.warmup, 2))):
+        cpu_sweep(oracle, inputs)
+    t0 = time.perf_counter()
+    done = 0
+    for _ in range(args.steps):
+        done += cpu_sweep(oracle, inputs)
+    dt = time.perf_counter() - t0
+    value = done / dt
+    line = {
+        "impl": "reference", "metric": "elements_per_s_fp16_function_sweep", "value": value, "unit": "elements/s",
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+                         "sample": f"each step = the 5-function sweep at 2^21 elements per function (bounded "
+                                   f"sample of the 2^28 workload), exact packed-FMA emulator, all host threads"},
+        "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def workload_config(n_gpus):
+    return {"workload": "BASELINE config[1]: isolated FP16 function sweep, HBM endpoint N=2^28 per function "
+                        "(sigmoid D3, tanh D4, SiLU D3, exp2 hinge, sin/cos D5/D6), polynomial vs native SFU",
+            "elements_per_function_per_gpu": N_HBM, "functions": 5, "sharding": f"{n_gpus} x independent element ranges",
+            "l2": "inputs of 512 MiB..1 GiB per function exceed the 126 MB L2; no flush needed"}
+
+
+# ------------------------------------------------------------------------------------ GPU arm
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+        return False
+
+    def summary(self):
+        sm, reasons, sm_max = [], set(), None
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                sm_max = float(r[2])
+            except (ValueError, IndexError):
+                continue
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            for name, flag in zip(names, r[5:9]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": sm_max, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def make_inputs(torch, device, n, rank):
+    """Seeded per-rank inputs: the global stream of rank r starts at element r*n of the same generator."""
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED + 7919 * rank)
+    u8 = (torch.rand(n, device=device, generator=g) * 16 - 8).to(torch.float16)
+    frac = torch.rand(n, device=device, generator=g).to(torch.float16)
+    ang = (torch.rand(n, device=device, generator=g) * (2 * math.pi) - math.pi).contiguous()
+    return u8, frac, ang
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+    from fast_polynomial_transcendentals_b200 import _lib, spline_ops
+    from fast_polynomial_transcendentals_b200.pipeline import HostPipeline
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    hbm_peak, _, peak_kind = measured_peaks()
+
+    u8, frac, ang = make_inputs(torch, device, N_HBM, rank)
+    out16 = torch.empty(N_HBM, dtype=torch.float16, device=device)
+    out_sc = torch.empty(2, N_HBM, dtype=torch.float16, device=device)
+
+    def k_unary(fn, degree, x, out, n):
+        return lambda: _lib.check("fpt_unary", lib.fpt_unary(out.data_ptr(), x.data_ptr(), n, fn, 0, degree, 0, 0, stream))
+
+    def k_exp2(variant, x, out, n):
+        return lambda: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(out.data_ptr(), x.data_ptr(), n, variant, 1, stream))
+
+    def k_sincos(variant, x, out, n):
+        return lambda: _lib.check("fpt_sincos", lib.fpt_sincos(out.data_ptr(), x.data_ptr(), n, variant, 0, stream))
+
+    def sweep(n, poly):
+        o16, osc = out16[:n], out_sc.view(-1)[: 2 * n]
+        return [
+            ("sigmoid", 4, k_unary(0, 3 if poly else 0, u8[:n], o16, n)),
+            ("tanh", 4, k_unary(1, 4 if poly else 0, u8[:n], o16, n)),
+            ("silu", 4, k_unary(2, 3 if poly else 0, u8[:n], o16, n)),
+            ("exp2", 4, k_exp2(1 if poly else 0, frac[:n], o16, n)),
+            ("sincos", 8, k_sincos(3 if poly else 10, ang[:n], osc, n)),
+        ]
+
+    def barrier(collective):
+        if collective and world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def time_sweep(kernels, steps, warmup, collective=False):
+        """Per-kernel CUDA-event durations inside a back-to-back loop; returns (total ms, {name: avg ms})."""
+        for _ in range(warmup):
+            for _, _, k in kernels:
+                k()
+        barrier(collective)
+        marks = [[torch.cuda.Event(enable_timing=True) for _ in range(len(kernels) + 1)] for _ in range(steps)]
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for s in range(steps):
+            marks[s][0].record()
+            for i, (_, _, k) in enumerate(kernels):
+                k()
+                marks[s][i + 1].record()
+        stop.record()
+        barrier(collective)
+        total = start.elapsed_time(stop)
+        per = {}
+        for i, (name, _, _) in enumerate(kernels):
+            per[name] = sum(marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(steps)) / steps
+        return total, per
+
+    # ---- headline: polynomial sweep at the HBM endpoint, with clock sampling
+    poly_hbm = sweep(N_HBM, True)
+    with ClockSampler(local) as clocks:
+        total_ms, per_poly = time_sweep(poly_hbm, args.steps, args.warmup, collective=True)
+    if world > 1:
+        t = torch.tensor([total_ms], device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    elements_per_step = 5 * N_HBM * world
+    value = elements_per_step * args.steps / (total_ms * 1e-3)
+    gpu_launches = len(poly_hbm) * args.steps
+
+    if rank != 0:
+        if world > 1:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    # ---- rank 0 only: native twins, L2 endpoint, SwiGLU / B3 lines, e2e, CPU baseline
+    _, per_native = time_sweep(sweep(N_HBM, False), max(3, args.steps // 2), 3)
+    functions = {}
+    for name, bytes_per, _ in poly_hbm:
+        gbs = bytes_per * N_HBM / (per_poly[name] * 1e-3) / 1e9
+        functions[name] = {
+            "poly_elements_per_s": N_HBM / (per_poly[name] * 1e-3), "native_elements_per_s": N_HBM / (per_native[name] * 1e-3),
+            "poly_ms": per_poly[name], "native_ms": per_native[name], "poly_gbs": gbs,
+            "frac_of_measured_hbm": gbs / hbm_peak, "frac_of_nominal_8tbs": gbs / NOMINAL_HBM_GBS,
+            "algorithmic_bytes_per_element": bytes_per,
+        }
+    l2 = {}
+    reps = 200
+    _, l2_poly = time_sweep(sweep(N_L2, True), reps, 50)
+    _, l2_native = time_sweep(sweep(N_L2, False), reps, 50)
+    for name in l2_poly:
+        l2[name] = {"poly_us": l2_poly[name] * 1e3, "native_us": l2_native[name] * 1e3,
+                    "speedup_vs_native": l2_native[name] / l2_poly[name]}
+    # ALU-bound probe: 16 evaluations per load at the L2 endpoint
+    alu = {}
+    for name, fn, deg in (("sigmoid", 0, 3), ("tanh", 1, 4), ("silu", 2, 3)):
+        ks = [(kind, 4, (lambda d=d: _lib.check("fpt_unary_repeat", lib.fpt_unary_repeat(
+            out16.data_ptr(), u8.data_ptr(), N_L2, fn, 0, d, 0, 0, 16, stream)))) for kind, d in (("poly", deg), ("native", 0))]
+        _, t = time_sweep(ks, 100, 20)
+        alu[name] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
+    ks = [(kind, 4, (lambda v=v: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(
+        out16.data_ptr(), frac.data_ptr(), N_L2, v, 16, stream)))) for kind, v in (("poly", 1), ("native", 0))]
+    _, t = time_sweep(ks, 100, 20)
+    alu["exp2"] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
+    ks = [(kind, 8, (lambda v=v: _lib.check("fpt_sincos", lib.fpt_sincos(
+        out_sc.data_ptr(), ang.data_ptr(), N_L2, v, 16, stream)))) for kind, v in (("poly", 3), ("native", 10))]
+    _, t = time_sweep(ks, 100, 20)
+    alu["sincos"] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
+
+    extras = {"l2_resident_2^20": l2, "alu_bound_16_evals_per_load_2^20": alu}
+    del u8, frac, ang, out16, out_sc
+    torch.cuda.empty_cache()
+    extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep)
+    extras["b3_config1"] = bench_b3(torch, lib, _lib, device, stream, time_sweep)
+
+    # ---- e2e through the public API with host buffers
+    e2e = bench_e2e(torch, spline_ops, HostPipeline, device)
+
+    cpu = cpu_baseline()
+    dominant = functions["sigmoid"]
+    line = {
+        "metric": "elements_per_s_fp16_function_sweep", "value": value, "unit": "elements/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
+        "roofline": {"bound": "hbm", "achieved": dominant["poly_gbs"], "peak": hbm_peak, "unit": "GB/s",
+                     "frac": dominant["poly_gbs"] / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "kernel": "stream_kernel<UnaryOp<fp16, ODD_HALF, 3>> (sigmoid D3), 4 algorithmic bytes per element "
+                               "x 2^28 elements per launch", "frac_of_nominal_8tbs": dominant["poly_gbs"] / NOMINAL_HBM_GBS},
+        "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks.summary(),
+        "functions": functions, "extras": extras,
+    }
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep):
+    out = {}
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    for name, rows, hidden in (("B1_dense_16384x14336", 16384, 14336), ("B4_routed_131072x1408", 131072, 1408)):
+        packed = (torch.randn(rows, 2 * hidden, device=device, generator=g) * 1.5).to(torch.bfloat16)
+        gate, up = packed[:, :hidden].contiguous(), packed[:, hidden:].contiguous()
+        o = torch.empty_like(gate)
+        n = rows * hidden
+        ks = [
+            ("flat_poly", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 3, 1, 0, stream))),
+            ("flat_native", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 0, 1, 0, stream))),
+            ("packed_poly", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, stream))),
+            ("packed_native", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 0, 1, 0, stream))),
+        ]
+        _, t = time_sweep(ks, 10, 3)
+        out[name] = {k: {"ms": v, "elements_per_s": n / (v * 1e-3), "gbs": 6 * n / (v * 1e-3) / 1e9,
+                         "frac_of_measured_hbm": 6 * n / (v * 1e-3) / 1e9 / hbm_peak} for k, v in t.items()}
+        del packed, gate, up, o
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_b3(torch, lib, _lib, device, stream, time_sweep):
+    n = 1 << 24
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    x = (torch.rand(n, device=device, generator=g) * 32 - 16).to(torch.bfloat16)
+    o = torch.empty_like(x)
+    ks = [("b3_direct_poly", 4, lambda: _lib.check("fpt_b3_sigmoid_direct", lib.fpt_b3_sigmoid_direct(o.data_ptr(), None, x.data_ptr(), n, 0, 12, stream))),
+          ("sigmoid_native", 4, lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, 0, 0, 0, 1, 0, stream)))]
+    _, t = time_sweep(ks, 50, 10)
+    return {k: {"us": v * 1e3, "elements_per_s": n / (v * 1e-3)} for k, v in t.items()} | {"n": n, "regime": "64 MiB touched: L2 resident"}
+
+
+def bench_e2e(torch, spline_ops, HostPipeline, device):
+    """The sweep from pinned host memory through spline_ops: chunked H2D -> kernel -> D2H on three streams."""
+    n = 1 << 26          # per function; bounded so that the default run stays within minutes
+    chunk = 1 << 23
+    g = torch.Generator()
+    g.manual_seed(SEED)
+    host_u8 = (torch.rand(n, generator=g) * 16 - 8).to(torch.float16).pin_memory()
+    host_frac = torch.rand(n, generator=g).to(torch.float16).pin_memory()
+    host_ang = (torch.rand(n, generator=g) * (2 * math.pi) - math.pi).pin_memory()
+    host_out = torch.empty(n, dtype=torch.float16).pin_memory()
+    host_sc = torch.empty(2 * n, dtype=torch.float16).pin_memory()
+    unary_pipe = HostPipeline(device, [(torch.float16, 1)], [(torch.float16, 1)], chunk)
+    # sin/cos keeps the two planes of a chunk adjacent in the device buffer; the host copy de-interleaves per chunk
+    sincos_pipe = HostPipeline(device, [(torch.float32, 1)], [(torch.float16, 2)], chunk)
+
+    def run_once():
+        launches = 0
+        for op, src in ((spline_ops.sigmoid_fwd_d3, host_u8), (spline_ops.tanh_fwd_d4, host_u8),
+                        (spline_ops.swish_fwd_d3, host_u8), (spline_ops.exp2_fraction, host_frac)):
+            def fn(ins, outs, m, op=op):
+                outs[0].copy_(op(ins[0]))
+            launches += 2 * unary_pipe.run(fn, [src], [host_out], n)
+        def fn_sc(ins, outs, m):
+            outs[0].copy_(spline_ops.sincos_d5_d6_half_turn_fp16(ins[0]).view(-1))
+        launches += 2 * sincos_pipe.run(fn_sc, [host_ang], [host_sc], n)
+        unary_pipe.synchronize()
+        sincos_pipe.synchronize()
+        return launches
+
+    run_once()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    reps = 2
+    for _ in range(reps):
+        run_once()
+    torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / reps
+    h2d = 4 * n * 2 + n * 4
+    d2h = 4 * n * 2 + 2 * n * 2
+    return {"value": 5 * n / dt, "unit": "elements/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+            "elements_per_function": n, "ms_per_step": dt * 1e3,
+            "path": "spline_ops.* on pinned host buffers, 2^23-element chunks, H2D / kernel / D2H on three streams; "
+                    "sin/cos results are returned chunk by chunk as [cos | sin] blocks"}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,11 @@ SIGNATURES: dict[str, list] = {
     "fpt_swish_mul_bwd": [_vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed": [_vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed_bwd": [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp],
+    "fpt_b3_sigmoid_direct": [_vp, _vp, _vp, _i64, _int, _int, _vp],
+    "fpt_exp2_fraction": [_vp, _vp, _i64, _int, _int, _vp],
+    "fpt_sincos": [_vp, _vp, _i64, _int, _int, _vp],
+    "fpt_rope_table": [_vp, _vp, _i64, _i64, _int, _int, _vp],
+    "fpt_rope_apply": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_set_tuning": [ctypes.c_char_p, _int],
     "fpt_get_tuning": [ctypes.c_char_p, ctypes.POINTER(_int)],
 }

@@ -1,0 +1,118 @@
+// Isolated score-mod evaluators: the direct piecewise-cubic sigmoid of sigmoid attention (B3) and the
+// fractional exp2 hinge, as flat element-wise kernels.
+#include "fpt_programs.h"
+#include "fpt_scoremod.cuh"
+#include "fpt_stream.cuh"
+
+namespace fpt {
+namespace {
+
+template <bool WITH_GRAD>
+struct B3Op {
+    static constexpr int NIN = 1, NOUT = WITH_GRAD ? 2 : 1;
+    B3Words k;
+    __device__ __forceinline__ void apply(const uint32_t (&in)[1], uint32_t (&out)[NOUT]) const {
+        if constexpr (WITH_GRAD) {
+            out[0] = b3_direct_with_grad(in[0], k, out[1]);
+        } else {
+            out[0] = b3_direct(in[0], k);
+        }
+    }
+};
+
+// fp32 scores -> bf16 probabilities (the form in which the attention kernel meets the evaluator)
+template <bool WITH_GRAD>
+__global__ void __launch_bounds__(kBlock) b3_from_f32_kernel(const B3Words k, const float* __restrict__ scores,
+                                                            uint16_t* __restrict__ prob, uint16_t* __restrict__ grad,
+                                                            int64_t n) {
+    const int64_t pairs = n / 2;
+    for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < pairs; i += int64_t(gridDim.x) * kBlock) {
+        const float2 s = reinterpret_cast<const float2*>(scores)[i];
+        const uint32_t x = Sfu<kBf16>::pack(s.x, s.y);
+        if constexpr (WITH_GRAD) {
+            uint32_t g;
+            reinterpret_cast<uint32_t*>(prob)[i] = b3_direct_with_grad(x, k, g);
+            reinterpret_cast<uint32_t*>(grad)[i] = g;
+        } else {
+            reinterpret_cast<uint32_t*>(prob)[i] = b3_direct(x, k);
+        }
+    }
+    if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
+        const uint32_t x = Sfu<kBf16>::pack(scores[n - 1], scores[n - 1]);
+        uint32_t g = 0;
+        const uint32_t p = WITH_GRAD ? b3_direct_with_grad(x, k, g) : b3_direct(x, k);
+        prob[n - 1] = uint16_t(p);
+        if constexpr (WITH_GRAD) grad[n - 1] = uint16_t(g);
+    }
+}
+
+template <int VARIANT>  // 0 native MUFU ex2, 1 hinge
+struct Exp2Op {
+    static constexpr int NIN = 1, NOUT = 1;
+    Exp2Words k;
+    int repeats;
+    __device__ __forceinline__ void apply(const uint32_t (&in)[1], uint32_t (&out)[1]) const {
+        uint32_t x = in[0], v = 0;
+#pragma unroll 1
+        for (int r = 0; r < repeats; ++r) {
+            if constexpr (VARIANT == 0) v = Sfu<kFp16>::ex2(x);
+            else v = exp2_hinge(x, k);
+            x = Pk<kFp16>::fma(v, 0x38003800u, 0xb800b800u);  // back into [0, 1): v/2 - 1/2
+        }
+        out[0] = v;
+    }
+};
+
+}  // namespace
+}  // namespace fpt
+
+using namespace fpt;
+
+extern "C" int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
+                                     int log2_n, fpt_stream_t stream) {
+    if (n < 0) return FPT_ERR_BAD_SIZE;
+    if (n > 0 && (!prob || !scores)) return FPT_ERR_NULL_POINTER;
+    if (log2_n < 1 || log2_n > 24) return FPT_ERR_BAD_SIZE;
+    const B3Words k = b3_words(log2_n);
+    if (n == 0) return FPT_OK;
+    if (scores_are_f32) {
+        DeviceInfo dev;
+        if (int rc = current_device_info(&dev)) return rc;
+        if ((reinterpret_cast<uintptr_t>(scores) & 7u) || (reinterpret_cast<uintptr_t>(prob) & 3u) ||
+            (reinterpret_cast<uintptr_t>(grad) & 3u))
+            return FPT_ERR_MISALIGNED;
+        int64_t grid = (n / 2 + kBlock - 1) / kBlock;
+        if (grid < 1) grid = 1;
+        const int64_t cap = int64_t(dev.sm_count) * 64;
+        if (grid > cap) grid = cap;
+        if (grad)
+            b3_from_f32_kernel<true><<<unsigned(grid), kBlock, 0, stream>>>(
+                k, static_cast<const float*>(scores), static_cast<uint16_t*>(prob), static_cast<uint16_t*>(grad), n);
+        else
+            b3_from_f32_kernel<false><<<unsigned(grid), kBlock, 0, stream>>>(
+                k, static_cast<const float*>(scores), static_cast<uint16_t*>(prob), nullptr, n);
+        return cuda_status(cudaGetLastError());
+    }
+    if (grad) {
+        StreamArgs<1, 2> a{};
+        a.in[0] = static_cast<const uint16_t*>(scores);
+        a.out[0] = static_cast<uint16_t*>(prob);
+        a.out[1] = static_cast<uint16_t*>(grad);
+        return launch_stream(B3Op<true>{k}, a, n, stream);
+    }
+    StreamArgs<1, 1> a{};
+    a.in[0] = static_cast<const uint16_t*>(scores);
+    a.out[0] = static_cast<uint16_t*>(prob);
+    return launch_stream(B3Op<false>{k}, a, n, stream);
+}
+
+extern "C" int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int repeats, fpt_stream_t stream) {
+    if (n < 0 || repeats < 1) return FPT_ERR_BAD_SIZE;
+    if (n > 0 && (!out || !in)) return FPT_ERR_NULL_POINTER;
+    if (variant < FPT_EXP2_NATIVE || variant > FPT_EXP2_HINGE_ENDPOINT) return FPT_ERR_BAD_ENUM;
+    StreamArgs<1, 1> a{};
+    a.in[0] = static_cast<const uint16_t*>(in);
+    a.out[0] = static_cast<uint16_t*>(out);
+    if (variant == FPT_EXP2_NATIVE) return launch_stream(Exp2Op<0>{Exp2Words{}, repeats}, a, n, stream);
+    return launch_stream(Exp2Op<1>{exp2_words(variant == FPT_EXP2_HINGE_ENDPOINT), repeats}, a, n, stream);
+}

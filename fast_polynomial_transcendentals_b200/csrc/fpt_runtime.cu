@@ -65,14 +65,33 @@ const ProgramRow* program_table(int* count) {
     return k_rows;
 }
 
+namespace {
+// [function][direction][degree-3][dtype][source] -> row index + 1 (0 = none), filled once.
+struct ProgramIndex {
+    unsigned char slot[5][2][4][2][2];
+    ProgramIndex() {
+        static const char* const fn_names[] = {"SIGMOID", "TANH", "SWISH", "ERF", "GELU"};
+        std::memset(slot, 0, sizeof(slot));
+        for (int i = 0; i < k_row_count; ++i) {
+            const ProgramRow& r = k_rows[i];
+            for (int f = 0; f < 5; ++f)
+                for (int d = 0; d < 2; ++d) {
+                    char name[32];
+                    std::snprintf(name, sizeof(name), "%s_%s_D%d", fn_names[f], d == 0 ? "FWD" : "BWD", r.degree);
+                    if (r.degree >= 3 && r.degree <= 6 && !std::strcmp(r.name, name))
+                        slot[f][d][r.degree - 3][r.dtype][r.source] = (unsigned char)(i + 1);
+                }
+        }
+    }
+};
+}  // namespace
+
 const ProgramRow* find_program(int function, int direction, int degree, int dtype, int source) {
-    static const char* const fn_names[] = {"SIGMOID", "TANH", "SWISH", "ERF", "GELU"};
+    static const ProgramIndex index;
     if (function < 0 || function > FPT_FN_GELU || (direction != FPT_FWD && direction != FPT_BWD)) return nullptr;
-    char name[32];
-    std::snprintf(name, sizeof(name), "%s_%s_D%d", fn_names[function], direction == FPT_FWD ? "FWD" : "BWD", degree);
-    for (int i = 0; i < k_row_count; ++i)
-        if (k_rows[i].dtype == dtype && k_rows[i].source == source && !std::strcmp(k_rows[i].name, name)) return &k_rows[i];
-    return nullptr;
+    if (degree < 3 || degree > 6 || dtype < 0 || dtype > 1 || source < 0 || source > 1) return nullptr;
+    const int s = index.slot[function][direction][degree - 3][dtype][source];
+    return s ? &k_rows[s - 1] : nullptr;
 }
 
 }  // namespace fpt

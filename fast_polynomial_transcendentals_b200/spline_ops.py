@@ -272,3 +272,197 @@ def swish_mul_packed_bwd_variant(grad_out, packed, degree: int, coeff_source_id:
             raise RuntimeError(f"Unsupported packed swish_mul backward degree: {degree}") from None
         raise
     return grad_packed
+
+
+# ---- paired sin/cos (reference: spline_ops.cpp:325-560) ---------------------------------------
+
+_SINCOS_VARIANTS = {
+    "d3_d4_quarter_turn_fp16": 0, "d3_d4_half_turn_fp16": 1, "d5_d4_half_turn_fp16": 2, "d5_d6_half_turn_fp16": 3,
+    "d7_d6_half_turn_fp16": 4, "d3_d4_bf16": 5, "d3_d4_quarter_turn_bf16": 6, "d3_d4_half_turn_bf16": 7,
+    "d5_d6_half_turn_bf16": 8, "d5_d4_half_turn_fp16_bf16": 9, "native_fp16": 10, "native_bf16": 11,
+}
+
+
+def _sincos(angles, variant: int, out_dtype, iterations: int = 0):
+    if not isinstance(angles, torch.Tensor) or not angles.is_cuda:
+        raise RuntimeError("angles must be a CUDA tensor")
+    if not angles.is_contiguous():
+        raise RuntimeError("angles must be contiguous")
+    if angles.dtype != torch.float32:
+        raise RuntimeError("angles must be float32")
+    out = torch.empty((2, *angles.shape), dtype=out_dtype, device=angles.device)
+    _call("fpt_sincos", angles, out.data_ptr(), angles.data_ptr(), angles.numel(), variant, iterations)
+    return out
+
+
+def _make_sincos(variant: int, out_dtype, compute: bool):
+    if compute:
+        def op(angles, iterations):
+            if int(iterations) <= 0:
+                raise RuntimeError("iterations must be positive")
+            return _sincos(angles, variant, out_dtype, int(iterations))
+    else:
+        def op(angles):
+            return _sincos(angles, variant, out_dtype)
+    op.__doc__ = "angles fp32 [...] -> [2, ...] (cos first)"
+    return op
+
+
+for _name, _variant in _SINCOS_VARIANTS.items():
+    _dtype = torch.bfloat16 if _name.endswith("bf16") else torch.float16
+    globals()[f"sincos_{_name}"] = _make_sincos(_variant, _dtype, False)
+    globals()[f"sincos_{_name}_compute"] = _make_sincos(_variant, _dtype, True)
+
+
+# ---- RoPE (reference: spline_ops.cpp:562-1140) -------------------------------------------------
+
+ROPE_HALF_TURN_D5_D6, ROPE_QUARTER_TURN_D3_D4, ROPE_NATIVE, ROPE_CACHED = 0, 1, 2, 3
+
+
+def _rope_table(parameters, sequence_length: int, kind: int, dtype, name: str, iterations: int = 0):
+    if not isinstance(parameters, torch.Tensor) or not parameters.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not parameters.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if parameters.dim() != 1:
+        raise RuntimeError(f"{name} must be one-dimensional")
+    if parameters.dtype != dtype:
+        raise RuntimeError(f"{name} has the wrong dtype")
+    if int(sequence_length) <= 0:
+        raise RuntimeError("sequence_length must be positive")
+    if parameters.numel() == 0 or parameters.numel() % 2:
+        raise RuntimeError(f"{name} must contain a positive even number of elements")
+    out = torch.empty((2, int(sequence_length), parameters.numel()), dtype=torch.float16, device=parameters.device)
+    _call("fpt_rope_table", parameters, out.data_ptr(), parameters.data_ptr(), int(sequence_length),
+          parameters.numel(), kind, iterations)
+    return out
+
+
+def rope_sincos_native_fp16(frequencies, sequence_length):
+    return _rope_table(frequencies, sequence_length, ROPE_NATIVE, torch.float32, "frequencies")
+
+
+def rope_sincos_fixed_d3_d4_fp16(phase_increments, sequence_length):
+    return _rope_table(phase_increments, sequence_length, ROPE_QUARTER_TURN_D3_D4, torch.int32, "phase_increments")
+
+
+def rope_sincos_fixed_half_turn_d5_d6_fp16(phase_increments, sequence_length):
+    if phase_increments.numel() % 4:
+        raise RuntimeError("phase_increments must contain a multiple of four elements")
+    return _rope_table(phase_increments, sequence_length, ROPE_HALF_TURN_D5_D6, torch.int32, "phase_increments")
+
+
+def rope_sincos_native_fp16_compute(frequencies, sequence_length, iterations):
+    return _rope_table(frequencies, sequence_length, ROPE_NATIVE, torch.float32, "frequencies", int(iterations))
+
+
+def rope_sincos_fixed_d3_d4_fp16_compute(phase_increments, sequence_length, iterations):
+    return _rope_table(phase_increments, sequence_length, ROPE_QUARTER_TURN_D3_D4, torch.int32, "phase_increments",
+                       int(iterations))
+
+
+def rope_sincos_fixed_half_turn_d5_d6_fp16_compute(phase_increments, sequence_length, iterations):
+    return _rope_table(phase_increments, sequence_length, ROPE_HALF_TURN_D5_D6, torch.int32, "phase_increments",
+                       int(iterations))
+
+
+def _check_rope_qk(q, k, dtype, dtype_name):
+    for t, n in ((q, "q"), (k, "k")):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError(f"{n} must be a CUDA tensor")
+        if not t.is_contiguous():
+            raise RuntimeError(f"{n} must be contiguous")
+        if t.dtype != dtype:
+            raise RuntimeError(f"{n} must be {dtype_name}")
+        if t.dim() != 4:
+            raise RuntimeError(f"{n} must have shape [batch, sequence, heads, head_dim]")
+    if q.device != k.device:
+        raise RuntimeError("q and k must be on the same CUDA device")
+    if q.size(0) != k.size(0):
+        raise RuntimeError("q and k batch sizes must match")
+    if q.size(1) != k.size(1):
+        raise RuntimeError("q and k sequence lengths must match")
+    if q.size(3) != k.size(3):
+        raise RuntimeError("q and k head dimensions must match")
+    if q.size(2) <= 0 or k.size(2) <= 0:
+        raise RuntimeError("q and k must contain at least one head")
+    if q.size(3) <= 0 or q.size(3) % 8:
+        raise RuntimeError("head_dim must be a positive multiple of eight")
+    if q.size(0) > 65535:
+        raise RuntimeError("batch size is too large for the CUDA grid")
+
+
+def _rope_apply(q, k, parameters, kind: int, param_dtype, name: str, io_dtype=torch.float16):
+    _check_rope_qk(q, k, io_dtype, "float16" if io_dtype == torch.float16 else "bfloat16")
+    if not isinstance(parameters, torch.Tensor) or not parameters.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not parameters.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    B, S, Hq, D = q.shape
+    Hk = k.size(2)
+    if kind == ROPE_CACHED:
+        if parameters.dtype != torch.float16:
+            raise RuntimeError("rope_table must be float16")
+        if parameters.dim() != 3 or tuple(parameters.shape) != (2, S, D // 2):
+            raise RuntimeError("rope_table must have shape [2, sequence, head_dim / 2]")
+    else:
+        if parameters.dim() != 1:
+            raise RuntimeError(f"{name} must be one-dimensional")
+        if parameters.dtype != param_dtype:
+            raise RuntimeError(f"{name} has the wrong dtype")
+        if parameters.numel() != D // 2:
+            raise RuntimeError(f"{name} must contain head_dim / 2 elements")
+    if parameters.device != q.device:
+        raise RuntimeError(f"{name} must be on the same CUDA device as q and k")
+    q_out = torch.empty((B, Hq, S, D), dtype=q.dtype, device=q.device)
+    k_out = torch.empty((B, Hk, S, D), dtype=k.dtype, device=k.device)
+    _call("fpt_rope_apply", q, q_out.data_ptr(), k_out.data_ptr(), q.data_ptr(), k.data_ptr(), parameters.data_ptr(),
+          B, S, Hq, Hk, D, kind, BF16 if io_dtype == torch.bfloat16 else FP16)
+    return [q_out, k_out]
+
+
+def rope_apply_fixed_half_turn_d5_d6_fp16(q, k, phase_increments):
+    """Fused polynomial RoPE + transpose: [B,S,H,D] fp16 -> [B,H,S,D]."""
+    return _rope_apply(q, k, phase_increments, ROPE_HALF_TURN_D5_D6, torch.int32, "phase_increments")
+
+
+def rope_apply_native_fp16(q, k, frequencies):
+    return _rope_apply(q, k, frequencies, ROPE_NATIVE, torch.float32, "frequencies")
+
+
+def rope_apply_cached_fp16(q, k, rope_table):
+    return _rope_apply(q, k, rope_table, ROPE_CACHED, torch.float16, "rope_table")
+
+
+def rope_apply_fixed_half_turn_d5_d6_bf16(q, k, phase_increments):
+    """Not in the reference: the same fp16 polynomial rotation around bf16 inputs and outputs, the form a
+    bf16 attention consumes."""
+    return _rope_apply(q, k, phase_increments, ROPE_HALF_TURN_D5_D6, torch.int32, "phase_increments", torch.bfloat16)
+
+
+# ---- score-mod evaluators as stand-alone ops (not in the reference's module) --------------------
+
+EXP2_NATIVE, EXP2_HINGE_LEAST_SQUARES, EXP2_HINGE_ENDPOINT = 0, 1, 2
+
+
+def exp2_fraction(x, variant: int = EXP2_HINGE_LEAST_SQUARES, repeats: int = 1):
+    """2^x for fp16 x in [0, 1): native MUFU, or the two-segment hinge with either constant set."""
+    _check_fp16(x, "x")
+    out = torch.empty_like(x)
+    _call("fpt_exp2_fraction", x, out.data_ptr(), x.data_ptr(), x.numel(), int(variant), int(repeats))
+    return out
+
+
+def b3_sigmoid_direct(scores, log2_n: int = 12, with_grad: bool = False):
+    """Direct piecewise-cubic sigmoid(score - log n) of sigmoid attention; scores bf16 or fp32 -> bf16."""
+    if not isinstance(scores, torch.Tensor) or not scores.is_cuda:
+        raise RuntimeError("scores must be a CUDA tensor")
+    if not scores.is_contiguous():
+        raise RuntimeError("scores must be contiguous")
+    if scores.dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError("scores must be bfloat16 or float32")
+    prob = torch.empty(scores.shape, dtype=torch.bfloat16, device=scores.device)
+    grad = torch.empty_like(prob) if with_grad else None
+    _call("fpt_b3_sigmoid_direct", scores, prob.data_ptr(), grad.data_ptr() if with_grad else None, scores.data_ptr(),
+          scores.numel(), int(scores.dtype == torch.float32), int(log2_n))
+    return (prob, grad) if with_grad else prob

@@ -102,6 +102,62 @@ int fpt_swish_mul_packed(void* out, const void* packed, int64_t rows, int64_t hi
 int fpt_swish_mul_packed_bwd(void* grad_packed, const void* grad_out, const void* packed, int64_t rows,
                              int64_t hidden, int degree, int dtype, int source, fpt_stream_t stream);
 
+/* ---- B3 sigmoid attention score-mod, isolated: prob = p(score) ~ sigmoid(score - log n), bf16 out
+ *      Direct piecewise cubic on the raw score with the deployed n = 4096 constants shifted to
+ *      n = 2^log2_n (reference: scripts/audit_b3_deployed_fit.py:341-366 for the arithmetic,
+ *      extras/paper/manuscript/main.tex:1042-1117 for the instruction sequence and immediates).
+ *      `scores` is bf16, or fp32 when scores_are_f32 != 0 (rounded to bf16 first, as in the attention kernel).
+ *      `grad` may be NULL; otherwise it receives prob * (intercept + slope*clamp(score)), the coupled
+ *      derivative of the deployed pair. */
+int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
+                          int log2_n, fpt_stream_t stream);
+
+/* ---- fractional exp2 on packed fp16, x in [0, 1)
+ *      replaces FractionalNative / FractionalPwl2Hinge of the reference's stand-alone benchmark
+ *      (reference: autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:53-99, 200-259).
+ *      `repeats` >= 1 evaluations per element, fed back through x <- v/2 - 1/2. */
+enum { FPT_EXP2_NATIVE = 0, FPT_EXP2_HINGE_LEAST_SQUARES = 1, FPT_EXP2_HINGE_ENDPOINT = 2 };
+int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int repeats, fpt_stream_t stream);
+
+/* ---- paired sin/cos: fp32 angles [n] -> out [2, n] 16-bit, cos plane first
+ *      replaces launch_sincos_*_{fp16,bf16}[_compute] (reference: sincos_kernels.cu:527-975 evaluators,
+ *      1084-1240 kernels).  iterations == 0: one evaluation; iterations > 0: the repeated-evaluation probe
+ *      (sums of `iterations` evaluations, angle <- fma(angle, 1 - 2^-24, 2^-13) between them). */
+enum {
+    FPT_SINCOS_D3_D4_QUARTER_TURN_FP16 = 0,
+    FPT_SINCOS_D3_D4_HALF_TURN_FP16 = 1,
+    FPT_SINCOS_D5_D4_HALF_TURN_FP16 = 2,
+    FPT_SINCOS_D5_D6_HALF_TURN_FP16 = 3,
+    FPT_SINCOS_D7_D6_HALF_TURN_FP16 = 4,
+    FPT_SINCOS_D3_D4_BF16 = 5,
+    FPT_SINCOS_D3_D4_QUARTER_TURN_BF16 = 6,
+    FPT_SINCOS_D3_D4_HALF_TURN_BF16 = 7,
+    FPT_SINCOS_D5_D6_HALF_TURN_BF16 = 8,
+    FPT_SINCOS_D5_D4_HALF_TURN_FP16_BF16 = 9,
+    FPT_SINCOS_VARIANT_COUNT = 10,
+    FPT_SINCOS_NATIVE_FP16 = 10,
+    FPT_SINCOS_NATIVE_BF16 = 11
+};
+int fpt_sincos(void* out, const void* angles, int64_t n, int variant, int iterations, fpt_stream_t stream);
+
+/* ---- RoPE tables: table [2, seq, freq_count] fp16 (cos plane, then sin plane)
+ *      replaces launch_rope_sincos_{native,fixed_d3_d4,fixed_half_turn_d5_d6}_fp16[_compute]
+ *      (reference: sincos_kernels.cu:1242-1348, 1387-1480).  params: int32 Q0.32 phase increments
+ *      [freq_count] (round(freq * 2^32 / 2pi)), or fp32 frequencies for FPT_ROPE_NATIVE. */
+enum { FPT_ROPE_HALF_TURN_D5_D6 = 0, FPT_ROPE_QUARTER_TURN_D3_D4 = 1, FPT_ROPE_NATIVE = 2, FPT_ROPE_CACHED = 3 };
+int fpt_rope_table(void* table, const void* params, int64_t seq, int64_t freq_count, int kind, int iterations,
+                   fpt_stream_t stream);
+
+/* ---- fused RoPE rotation + transpose: q [B,S,Hq,D], k [B,S,Hk,D] -> q_out [B,Hq,S,D], k_out [B,Hk,S,D]
+ *      replaces launch_rope_apply_{fixed_half_turn_d5_d6,native,cached}_fp16
+ *      (reference: sincos_kernels.cu:1504-1754).  Interleaved (even, odd) pairs; one parameter per pair:
+ *      params [D/2] increments or frequencies, or for FPT_ROPE_CACHED a table [2, S, D/2] fp16.
+ *      dtype FPT_FP16 is the reference's form.  FPT_BF16 reads and writes bf16 around the same fp16
+ *      rotation (input widened exactly and rounded to fp16, result rounded once to bf16). */
+int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const void* params, int64_t batch,
+                   int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int kind, int dtype,
+                   fpt_stream_t stream);
+
 /* ---- launch knobs for benchmarks (process-wide; defaults are the measured-best values) -------- */
 /* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1. */
 int fpt_set_tuning(const char* key, int value);
