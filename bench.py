@@ -130,7 +130,7 @@ class ClockSampler:
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
-                                          "-lms", "100", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+                                          "-lms", "50", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except OSError:
@@ -190,7 +190,8 @@ def run_gpu_arm(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     lib = _lib.load()
-    stream = torch.cuda.current_stream().cuda_stream
+    ctx = {"stream": torch.cuda.current_stream().cuda_stream}
+    S = lambda: ctx["stream"]  # kernels read the launch stream at call time (graph capture swaps it)
     hbm_peak, _, peak_kind = measured_peaks()
 
     u8, frac, ang = make_inputs(torch, device, N_HBM, rank)
@@ -198,13 +199,13 @@ def run_gpu_arm(args):
     out_sc = torch.empty(2, N_HBM, dtype=torch.float16, device=device)
 
     def k_unary(fn, degree, x, out, n):
-        return lambda: _lib.check("fpt_unary", lib.fpt_unary(out.data_ptr(), x.data_ptr(), n, fn, 0, degree, 0, 0, stream))
+        return lambda: _lib.check("fpt_unary", lib.fpt_unary(out.data_ptr(), x.data_ptr(), n, fn, 0, degree, 0, 0, S()))
 
     def k_exp2(variant, x, out, n):
-        return lambda: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(out.data_ptr(), x.data_ptr(), n, variant, 1, stream))
+        return lambda: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(out.data_ptr(), x.data_ptr(), n, variant, 1, S()))
 
     def k_sincos(variant, x, out, n):
-        return lambda: _lib.check("fpt_sincos", lib.fpt_sincos(out.data_ptr(), x.data_ptr(), n, variant, 0, stream))
+        return lambda: _lib.check("fpt_sincos", lib.fpt_sincos(out.data_ptr(), x.data_ptr(), n, variant, 0, S()))
 
     def sweep(n, poly):
         o16, osc = out16[:n], out_sc.view(-1)[: 2 * n]
@@ -243,6 +244,40 @@ def run_gpu_arm(args):
             per[name] = sum(marks[s][i].elapsed_time(marks[s][i + 1]) for s in range(steps)) / steps
         return total, per
 
+    def time_graph(kernels, launches=20, rounds=15):
+        """Kernel-side time of small launches: every kernel is captured `launches` times into its own CUDA graph and
+        the replay is timed, so that host launch cost stays outside the measurement.  Returns {name: avg ms}."""
+        side = torch.cuda.Stream(device)
+        per = {}
+        for name, _, k in kernels:
+            saved = ctx["stream"]
+            ctx["stream"] = side.cuda_stream
+            try:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    for _ in range(3):
+                        k()
+                    graph = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(graph, stream=side):
+                        for _ in range(launches):
+                            k()
+                torch.cuda.current_stream().wait_stream(side)
+            finally:
+                ctx["stream"] = saved
+            graph.replay()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(rounds):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                graph.replay()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b) / launches)
+            times.sort()
+            per[name] = times[len(times) // 2]
+        return per
+
     # ---- headline: polynomial sweep at the HBM endpoint, with clock sampling
     poly_hbm = sweep(N_HBM, True)
     with ClockSampler(local) as clocks:
@@ -273,9 +308,8 @@ def run_gpu_arm(args):
             "algorithmic_bytes_per_element": bytes_per,
         }
     l2 = {}
-    reps = 200
-    _, l2_poly = time_sweep(sweep(N_L2, True), reps, 50)
-    _, l2_native = time_sweep(sweep(N_L2, False), reps, 50)
+    l2_poly = time_graph(sweep(N_L2, True))
+    l2_native = time_graph(sweep(N_L2, False))
     for name in l2_poly:
         l2[name] = {"poly_us": l2_poly[name] * 1e3, "native_us": l2_native[name] * 1e3,
                     "speedup_vs_native": l2_native[name] / l2_poly[name]}
@@ -283,23 +317,24 @@ def run_gpu_arm(args):
     alu = {}
     for name, fn, deg in (("sigmoid", 0, 3), ("tanh", 1, 4), ("silu", 2, 3)):
         ks = [(kind, 4, (lambda d=d: _lib.check("fpt_unary_repeat", lib.fpt_unary_repeat(
-            out16.data_ptr(), u8.data_ptr(), N_L2, fn, 0, d, 0, 0, 16, stream)))) for kind, d in (("poly", deg), ("native", 0))]
-        _, t = time_sweep(ks, 100, 20)
+            out16.data_ptr(), u8.data_ptr(), N_L2, fn, 0, d, 0, 0, 16, S())))) for kind, d in (("poly", deg), ("native", 0))]
+        t = time_graph(ks)
         alu[name] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
     ks = [(kind, 4, (lambda v=v: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(
-        out16.data_ptr(), frac.data_ptr(), N_L2, v, 16, stream)))) for kind, v in (("poly", 1), ("native", 0))]
-    _, t = time_sweep(ks, 100, 20)
+        out16.data_ptr(), frac.data_ptr(), N_L2, v, 16, S())))) for kind, v in (("poly", 1), ("native", 0))]
+    t = time_graph(ks)
     alu["exp2"] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
     ks = [(kind, 8, (lambda v=v: _lib.check("fpt_sincos", lib.fpt_sincos(
-        out_sc.data_ptr(), ang.data_ptr(), N_L2, v, 16, stream)))) for kind, v in (("poly", 3), ("native", 10))]
-    _, t = time_sweep(ks, 100, 20)
+        out_sc.data_ptr(), ang.data_ptr(), N_L2, v, 16, S())))) for kind, v in (("poly", 3), ("native", 10))]
+    t = time_graph(ks)
     alu["sincos"] = {"poly_us": t["poly"] * 1e3, "native_us": t["native"] * 1e3, "speedup_vs_native": t["native"] / t["poly"]}
 
-    extras = {"l2_resident_2^20": l2, "alu_bound_16_evals_per_load_2^20": alu}
+    extras = {"l2_resident_2^20": l2, "alu_bound_16_evals_per_load_2^20": alu,
+              "l2_timing": "CUDA-graph replay of 20 launches per kernel, median of 15 replays (no host launch cost)"}
     del u8, frac, ang, out16, out_sc
     torch.cuda.empty_cache()
-    extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep)
-    extras["b3_config1"] = bench_b3(torch, lib, _lib, device, stream, time_sweep)
+    extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep)
+    extras["b3_config1"] = bench_b3(torch, lib, _lib, device, S, time_graph)
 
     # ---- e2e through the public API with host buffers
     e2e = bench_e2e(torch, spline_ops, HostPipeline, device)
@@ -323,7 +358,7 @@ def run_gpu_arm(args):
         dist.destroy_process_group()
 
 
-def bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep):
+def bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep):
     out = {}
     g = torch.Generator(device=device)
     g.manual_seed(SEED)
@@ -333,10 +368,10 @@ def bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep):
         o = torch.empty_like(gate)
         n = rows * hidden
         ks = [
-            ("flat_poly", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 3, 1, 0, stream))),
-            ("flat_native", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 0, 1, 0, stream))),
-            ("packed_poly", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, stream))),
-            ("packed_native", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 0, 1, 0, stream))),
+            ("flat_poly", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 3, 1, 0, S()))),
+            ("flat_native", 6, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), n, 0, 1, 0, S()))),
+            ("packed_poly", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, S()))),
+            ("packed_native", 6, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 0, 1, 0, S()))),
         ]
         _, t = time_sweep(ks, 10, 3)
         out[name] = {k: {"ms": v, "elements_per_s": n / (v * 1e-3), "gbs": 6 * n / (v * 1e-3) / 1e9,
@@ -346,15 +381,15 @@ def bench_swiglu(torch, lib, _lib, device, stream, hbm_peak, time_sweep):
     return out
 
 
-def bench_b3(torch, lib, _lib, device, stream, time_sweep):
+def bench_b3(torch, lib, _lib, device, S, time_graph):
     n = 1 << 24
     g = torch.Generator(device=device)
     g.manual_seed(SEED)
     x = (torch.rand(n, device=device, generator=g) * 32 - 16).to(torch.bfloat16)
     o = torch.empty_like(x)
-    ks = [("b3_direct_poly", 4, lambda: _lib.check("fpt_b3_sigmoid_direct", lib.fpt_b3_sigmoid_direct(o.data_ptr(), None, x.data_ptr(), n, 0, 12, stream))),
-          ("sigmoid_native", 4, lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, 0, 0, 0, 1, 0, stream)))]
-    _, t = time_sweep(ks, 50, 10)
+    ks = [("b3_direct_poly", 4, lambda: _lib.check("fpt_b3_sigmoid_direct", lib.fpt_b3_sigmoid_direct(o.data_ptr(), None, x.data_ptr(), n, 0, 12, S()))),
+          ("sigmoid_native", 4, lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, 0, 0, 0, 1, 0, S())))]
+    t = time_graph(ks)
     return {k: {"us": v * 1e3, "elements_per_s": n / (v * 1e-3)} for k, v in t.items()} | {"n": n, "regime": "64 MiB touched: L2 resident"}
 
 
@@ -403,15 +438,58 @@ def bench_e2e(torch, spline_ops, HostPipeline, device):
                     "sin/cos results are returned chunk by chunk as [cos | sin] blocks"}
 
 
+def run_profile_case(args):
+    """A small fixed case of ONE kernel for profiler captures: `--profile-case NAME --profile-n ELEMENTS`."""
+    import torch
+    from fast_polynomial_transcendentals_b200 import _lib
+    lib = _lib.load()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    stream = torch.cuda.current_stream().cuda_stream
+    n = args.profile_n
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    case = args.profile_case
+    if case in ("sigmoid", "tanh", "silu", "sigmoid_native"):
+        x = (torch.rand(n, device=device, generator=g) * 16 - 8).to(torch.float16)
+        o = torch.empty_like(x)
+        fn, deg = {"sigmoid": (0, 3), "tanh": (1, 4), "silu": (2, 3), "sigmoid_native": (0, 0)}[case]
+        run = lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, fn, 0, deg, 0, 0, stream))
+    elif case == "sincos":
+        x = torch.rand(n, device=device, generator=g) * (2 * math.pi) - math.pi
+        o = torch.empty(2, n, dtype=torch.float16, device=device)
+        run = lambda: _lib.check("fpt_sincos", lib.fpt_sincos(o.data_ptr(), x.data_ptr(), n, 3, 0, stream))
+    elif case in ("swiglu", "swiglu_packed"):
+        hidden = 1408
+        rows = n // hidden
+        packed = (torch.randn(rows, 2 * hidden, device=device, generator=g) * 1.5).to(torch.bfloat16)
+        gate, up = packed[:, :hidden].contiguous(), packed[:, hidden:].contiguous()
+        o = torch.empty_like(gate)
+        if case == "swiglu":
+            run = lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), rows * hidden, 3, 1, 0, stream))
+        else:
+            run = lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, stream))
+    else:
+        raise SystemExit(f"unknown profile case {case}")
+    for _ in range(args.steps):
+        run()
+    torch.cuda.synchronize()
+    print(json.dumps({"profile_case": case, "n": n, "launches": args.steps}))
+
+
 def main():
     ap = argparse.ArgumentParser()
+    ap.add_argument("--profile-case", default=None, help="run only one small kernel case (for ncu captures)")
+    ap.add_argument("--profile-n", type=int, default=1 << 26)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
-    if args.impl == "reference":
+    if args.profile_case:
+        run_profile_case(args)
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

@@ -26,6 +26,7 @@ __global__ void __launch_bounds__(kBlock) b3_from_f32_kernel(const B3Words k, co
                                                             uint16_t* __restrict__ prob, uint16_t* __restrict__ grad,
                                                             int64_t n) {
     const int64_t pairs = n / 2;
+#pragma unroll 1
     for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < pairs; i += int64_t(gridDim.x) * kBlock) {
         const float2 s = reinterpret_cast<const float2*>(scores)[i];
         const uint32_t x = Sfu<kBf16>::pack(s.x, s.y);

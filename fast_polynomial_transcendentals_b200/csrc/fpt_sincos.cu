@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(kBlock) sincos_kernel(const Ev ev, const Sinco
         store_vec<4, STREAM>(reinterpret_cast<Vec<4>*>(a.sin_out) + i, s);
     }
     if (blockIdx.x == gridDim.x - 1) {  // ragged tail
+#pragma unroll 1
         for (int64_t e = n_vec * 8 + threadIdx.x; e < a.n; e += kBlock) {
             float p = a.angles[e];
             uint32_t cw, sw;
@@ -170,6 +171,7 @@ __global__ void __launch_bounds__(kBlock) sincos_kernel(const Ev ev, const Sinco
 // element-at-a-time variant for planes that are not 16-byte aligned (n not a multiple of 8)
 template <class Ev, bool COMPUTE>
 __global__ void __launch_bounds__(kBlock) sincos_element_kernel(const Ev ev, const SincosArgs a) {
+#pragma unroll 1
     for (int64_t e = int64_t(blockIdx.x) * kBlock + threadIdx.x; e < a.n; e += int64_t(gridDim.x) * kBlock) {
         float p = a.angles[e];
         uint32_t cw, sw;
@@ -354,6 +356,7 @@ __global__ void __launch_bounds__(kBlock) rope_table_kernel(const uint32_t* __re
     const int64_t total = seq * pairs;
     uint32_t* cos_plane = reinterpret_cast<uint32_t*>(table);
     uint32_t* sin_plane = reinterpret_cast<uint32_t*>(table + seq * freq_count);
+#pragma unroll 1
     for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < total; i += int64_t(gridDim.x) * kBlock) {
         const int64_t pos = i / pairs, j = i - pos * pairs;
         const uint32_t a = params[2 * j], b = params[2 * j + 1];

@@ -20,7 +20,7 @@
 
 namespace fpt {
 
-constexpr int kBlock = 256;
+constexpr int kBlock = 256;  // fixed-shape kernels (packed rows, sin/cos, RoPE, scalar fallbacks)
 
 template <int WORDS>
 struct alignas(WORDS * 4) Vec {
@@ -76,18 +76,21 @@ struct StreamArgs {
 
 // Op contract:  static constexpr int NIN, NOUT;
 //               __device__ void apply(const uint32_t (&in)[NIN], uint32_t (&out)[NOUT]) const;   (two lanes per word)
-template <class Op, int WORDS, int UNROLL, bool STREAM>
-__global__ void __launch_bounds__(kBlock) stream_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
+template <class Op, int WORDS, int UNROLL, bool STREAM, int BLOCK>
+__global__ void __launch_bounds__(BLOCK) stream_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
     constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
-    constexpr int64_t kTile = int64_t(kBlock) * UNROLL;
+    constexpr int block = BLOCK;
+    constexpr int64_t kTile = int64_t(block) * UNROLL;
     const int64_t stride = int64_t(gridDim.x) * kTile;
+    // never unrolled: an unrolled grid-stride loop needs its trip count, i.e. a 64-bit division per thread
+#pragma unroll 1
     for (int64_t tile = int64_t(blockIdx.x) * kTile; tile < a.n_vec; tile += stride) {
         const int64_t first = tile + threadIdx.x;
         Vec<WORDS> v[NIN][UNROLL];
         const bool full = tile + kTile <= a.n_vec;
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int64_t idx = first + int64_t(u) * kBlock;
+            const int64_t idx = first + int64_t(u) * block;
             if (full || idx < a.n_vec) {
 #pragma unroll
                 for (int i = 0; i < NIN; ++i)
@@ -96,7 +99,7 @@ __global__ void __launch_bounds__(kBlock) stream_kernel(const Op op, const Strea
         }
 #pragma unroll
         for (int u = 0; u < UNROLL; ++u) {
-            const int64_t idx = first + int64_t(u) * kBlock;
+            const int64_t idx = first + int64_t(u) * block;
             if (full || idx < a.n_vec) {
                 Vec<WORDS> r[NOUT];
 #pragma unroll
@@ -115,7 +118,8 @@ __global__ void __launch_bounds__(kBlock) stream_kernel(const Op op, const Strea
         }
     }
     if (blockIdx.x == gridDim.x - 1) {  // ragged tail, one element per thread step
-        for (int64_t e = a.n_vec * (WORDS * 2) + threadIdx.x; e < a.n_elem; e += kBlock) {
+#pragma unroll 1
+        for (int64_t e = a.n_vec * (WORDS * 2) + threadIdx.x; e < a.n_elem; e += block) {
             uint32_t xi[NIN], yo[NOUT];
 #pragma unroll
             for (int i = 0; i < NIN; ++i) xi[i] = uint32_t(a.in[i][e]) * 0x00010001u;
@@ -130,6 +134,7 @@ __global__ void __launch_bounds__(kBlock) stream_kernel(const Op op, const Strea
 template <class Op>
 __global__ void __launch_bounds__(kBlock) element_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
     constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
+#pragma unroll 1
     for (int64_t e = int64_t(blockIdx.x) * kBlock + threadIdx.x; e < a.n_elem; e += int64_t(gridDim.x) * kBlock) {
         uint32_t xi[NIN], yo[NOUT];
 #pragma unroll
@@ -140,18 +145,19 @@ __global__ void __launch_bounds__(kBlock) element_kernel(const Op op, const Stre
     }
 }
 
-template <class Op, int WORDS, int UNROLL, bool STREAM>
+template <class Op, int WORDS, int UNROLL, bool STREAM, int BLOCK>
 static int launch_stream_config(const Op& op, const StreamArgs<Op::NIN, Op::NOUT>& a, const DeviceInfo& dev,
                                 const Tuning& t, cudaStream_t stream) {
-    auto kernel = stream_kernel<Op, WORDS, UNROLL, STREAM>;
-    const int64_t tiles = (a.n_vec + int64_t(kBlock) * UNROLL - 1) / (int64_t(kBlock) * UNROLL);
+    auto kernel = stream_kernel<Op, WORDS, UNROLL, STREAM, BLOCK>;
+    constexpr int block = BLOCK;
+    const int64_t tiles = (a.n_vec + int64_t(block) * UNROLL - 1) / (int64_t(block) * UNROLL);
     int64_t grid = tiles > 0 ? tiles : 1;
     if (t.blocks_per_sm > 0) {
         const int64_t cap = int64_t(dev.sm_count) * t.blocks_per_sm;
         if (grid > cap) grid = cap;
     }
     if (grid > 0x7fffffff) grid = 0x7fffffff;
-    kernel<<<unsigned(grid), kBlock, 0, stream>>>(op, a);
+    kernel<<<unsigned(grid), block, 0, stream>>>(op, a);
     return cuda_status(cudaGetLastError());
 }
 
@@ -167,6 +173,15 @@ static int launch_stream_config(const Op& op, const StreamArgs<Op::NIN, Op::NOUT
 #define FPT_LOADS_IN_FLIGHT 2
 #endif
 #define FPT_RESIDENT_WORDS FPT_STREAM_WORDS
+// Threads per block: 256 while streaming from HBM; 128 for L2-resident sizes, where the finer blocks
+// balance the last wave over the 148 SMs (graph-replayed sigmoid, 2^20 / 2^22 elements: 1.78 / 3.03 us
+// against 1.97 / 3.34 us with 256 threads).
+#ifndef FPT_STREAM_BLOCK
+#define FPT_STREAM_BLOCK 256
+#endif
+#ifndef FPT_RESIDENT_BLOCK
+#define FPT_RESIDENT_BLOCK 128
+#endif
 template <int NIN>
 constexpr int stream_unroll() { return FPT_LOADS_IN_FLIGHT / NIN > 0 ? FPT_LOADS_IN_FLIGHT / NIN : 1; }
 
@@ -189,7 +204,7 @@ static int launch_stream(const Op& op, StreamArgs<Op::NIN, Op::NOUT> a, int64_t 
         if constexpr (FPT_STREAM_WORDS == 8 || FPT_RESIDENT_WORDS == 8) {
             if (!(align & 15u)) {  // 16-byte aligned but not 32: narrow vectors
                 a.n_vec = n_elem / 8;
-                return launch_stream_config<Op, 4, 2, false>(op, a, dev, t, stream);
+                return launch_stream_config<Op, 4, 2, false, FPT_RESIDENT_BLOCK>(op, a, dev, t, stream);
             }
         }
         a.n_vec = 0;
@@ -201,10 +216,10 @@ static int launch_stream(const Op& op, StreamArgs<Op::NIN, Op::NOUT> a, int64_t 
     }
     if (streaming) {
         a.n_vec = n_elem / (FPT_STREAM_WORDS * 2);
-        return launch_stream_config<Op, FPT_STREAM_WORDS, stream_unroll<Op::NIN>(), true>(op, a, dev, t, stream);
+        return launch_stream_config<Op, FPT_STREAM_WORDS, stream_unroll<Op::NIN>(), true, FPT_STREAM_BLOCK>(op, a, dev, t, stream);
     }
     a.n_vec = n_elem / (FPT_RESIDENT_WORDS * 2);
-    return launch_stream_config<Op, FPT_RESIDENT_WORDS, stream_unroll<Op::NIN>(), false>(op, a, dev, t, stream);
+    return launch_stream_config<Op, FPT_RESIDENT_WORDS, stream_unroll<Op::NIN>(), false, FPT_RESIDENT_BLOCK>(op, a, dev, t, stream);
 }
 
 }  // namespace fpt

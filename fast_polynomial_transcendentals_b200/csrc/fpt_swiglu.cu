@@ -71,6 +71,11 @@ constexpr unsigned kSwishShapes = (1u << kSwish) | (1u << kXmulHalf);
 // Thread layout inside a 256-thread block: 2^tx_shift column vectors x (256 >> tx_shift) rows, so that
 // narrow rows still fill the block; R rows per thread are loaded before any is computed.
 
+#ifndef FPT_PACKED_BLOCK
+#define FPT_PACKED_BLOCK 256
+#endif
+constexpr int kPackedBlock = FPT_PACKED_BLOCK;
+
 struct PackedArgs {
     const uint16_t* packed;    // [rows, 2*hidden]
     const uint16_t* grad_out;  // [rows, hidden] (backward only)
@@ -80,14 +85,19 @@ struct PackedArgs {
 };
 
 template <class Op, int R, bool STREAM>
-__global__ void __launch_bounds__(kBlock) packed_fwd_kernel(const Op op, const PackedArgs a) {
+__global__ void __launch_bounds__(kPackedBlock) packed_fwd_kernel(const Op op, const PackedArgs a) {
+    // grid.x walks along a row (column tile fastest in launch order), grid.y over row groups, so that the
+    // blocks resident at any moment cover a few long contiguous spans.  Index math stays 32-bit and free of
+    // divisions: with two loads per thread every extra instruction costs memory-level parallelism.
     const int tx = threadIdx.x & ((1 << a.tx_shift) - 1);
     const int ty = threadIdx.x >> a.tx_shift;
-    const int rows_per_block = kBlock >> a.tx_shift;
-    const int col = (blockIdx.y << a.tx_shift) + tx;
+    const int rows_per_block = kPackedBlock >> a.tx_shift;
+    const int col = (int(blockIdx.x) << a.tx_shift) + tx;
     if (col >= a.vecs_per_row) return;
-    const int64_t row_step = int64_t(gridDim.x) * rows_per_block * R;
-    for (int64_t row0 = int64_t(blockIdx.x) * rows_per_block * R + ty; row0 < a.rows; row0 += row_step) {
+    const int64_t row_step = int64_t(gridDim.y) * rows_per_block * R;
+    // never unrolled: an unrolled grid-stride loop needs its trip count, i.e. a 64-bit division per thread
+#pragma unroll 1
+    for (int64_t row0 = int64_t(blockIdx.y) * rows_per_block * R + ty; row0 < a.rows; row0 += row_step) {
         Vec<4> g[R], u[R];
 #pragma unroll
         for (int i = 0; i < R; ++i) {
@@ -117,14 +127,19 @@ __global__ void __launch_bounds__(kBlock) packed_fwd_kernel(const Op op, const P
 }
 
 template <class Op, int R, bool STREAM>
-__global__ void __launch_bounds__(kBlock) packed_bwd_kernel(const Op op, const PackedArgs a) {
+__global__ void __launch_bounds__(kPackedBlock) packed_bwd_kernel(const Op op, const PackedArgs a) {
+    // grid.x walks along a row (column tile fastest in launch order), grid.y over row groups, so that the
+    // blocks resident at any moment cover a few long contiguous spans.  Index math stays 32-bit and free of
+    // divisions: with two loads per thread every extra instruction costs memory-level parallelism.
     const int tx = threadIdx.x & ((1 << a.tx_shift) - 1);
     const int ty = threadIdx.x >> a.tx_shift;
-    const int rows_per_block = kBlock >> a.tx_shift;
-    const int col = (blockIdx.y << a.tx_shift) + tx;
+    const int rows_per_block = kPackedBlock >> a.tx_shift;
+    const int col = (int(blockIdx.x) << a.tx_shift) + tx;
     if (col >= a.vecs_per_row) return;
-    const int64_t row_step = int64_t(gridDim.x) * rows_per_block * R;
-    for (int64_t row0 = int64_t(blockIdx.x) * rows_per_block * R + ty; row0 < a.rows; row0 += row_step) {
+    const int64_t row_step = int64_t(gridDim.y) * rows_per_block * R;
+    // never unrolled: an unrolled grid-stride loop needs its trip count, i.e. a 64-bit division per thread
+#pragma unroll 1
+    for (int64_t row0 = int64_t(blockIdx.y) * rows_per_block * R + ty; row0 < a.rows; row0 += row_step) {
         Vec<4> go[R], g[R], u[R];
 #pragma unroll
         for (int i = 0; i < R; ++i) {
@@ -161,6 +176,7 @@ __global__ void __launch_bounds__(kBlock) packed_bwd_kernel(const Op op, const P
 template <class Op, bool BWD>
 __global__ void __launch_bounds__(kBlock) packed_element_kernel(const Op op, const PackedArgs a) {
     const int64_t total = a.rows * a.hidden;
+#pragma unroll 1
     for (int64_t e = int64_t(blockIdx.x) * kBlock + threadIdx.x; e < total; e += int64_t(gridDim.x) * kBlock) {
         const int64_t row = e / a.hidden, col = e - row * a.hidden;
         const uint32_t g = uint32_t(a.packed[row * 2 * a.hidden + col]) * 0x00010001u;
@@ -204,26 +220,25 @@ int launch_packed(const Op& op, PackedArgs a, cudaStream_t stream) {
     if (vpr > 0x7fffffff / 2) return FPT_ERR_BAD_SIZE;
     a.vecs_per_row = int(vpr);
     int shift = 0;
-    while ((1 << shift) < kBlock && (1 << shift) < a.vecs_per_row) ++shift;
+    while ((1 << shift) < kPackedBlock && (1 << shift) < a.vecs_per_row) ++shift;
     a.tx_shift = shift;
-    const int rows_per_block = (kBlock >> shift) * kPackedRows;
-    int64_t grid_x = (a.rows + rows_per_block - 1) / rows_per_block;
-    const int64_t grid_y = (vpr + (1 << shift) - 1) >> shift;
-    if (grid_y > 65535) return FPT_ERR_BAD_SIZE;
+    const int rows_per_block = (kPackedBlock >> shift) * kPackedRows;
+    int64_t row_groups = (a.rows + rows_per_block - 1) / rows_per_block;
+    const int64_t col_tiles = (vpr + (1 << shift) - 1) >> shift;
     if (t.blocks_per_sm > 0) {
-        const int64_t cap = (int64_t(dev.sm_count) * t.blocks_per_sm + grid_y - 1) / grid_y;
-        if (grid_x > cap) grid_x = cap;
+        const int64_t cap = (int64_t(dev.sm_count) * t.blocks_per_sm + col_tiles - 1) / col_tiles;
+        if (row_groups > cap) row_groups = cap;
     }
-    if (grid_x > 0x7fffffff) grid_x = 0x7fffffff;
+    if (row_groups > 65535) row_groups = 65535;  // grid.y limit; the kernel strides over the remaining rows
     const int64_t bytes = a.rows * a.hidden * 2 * (BWD ? 5 : 3);
     const bool streaming = t.streaming < 0 ? bytes > dev.l2_bytes : t.streaming != 0;
-    const dim3 grid{unsigned(grid_x), unsigned(grid_y), 1u};
+    const dim3 grid{unsigned(col_tiles), unsigned(row_groups), 1u};
     if constexpr (BWD) {
-        if (streaming) packed_bwd_kernel<Op, kPackedRows, true><<<grid, kBlock, 0, stream>>>(op, a);
-        else packed_bwd_kernel<Op, kPackedRows, false><<<grid, kBlock, 0, stream>>>(op, a);
+        if (streaming) packed_bwd_kernel<Op, kPackedRows, true><<<grid, kPackedBlock, 0, stream>>>(op, a);
+        else packed_bwd_kernel<Op, kPackedRows, false><<<grid, kPackedBlock, 0, stream>>>(op, a);
     } else {
-        if (streaming) packed_fwd_kernel<Op, kPackedRows, true><<<grid, kBlock, 0, stream>>>(op, a);
-        else packed_fwd_kernel<Op, kPackedRows, false><<<grid, kBlock, 0, stream>>>(op, a);
+        if (streaming) packed_fwd_kernel<Op, kPackedRows, true><<<grid, kPackedBlock, 0, stream>>>(op, a);
+        else packed_fwd_kernel<Op, kPackedRows, false><<<grid, kPackedBlock, 0, stream>>>(op, a);
     }
     return cuda_status(cudaGetLastError());
 }

@@ -282,7 +282,9 @@ int fpt_oracle_sincos_is_bf16(int variant) { return k_sincos[variant].out_fmt ==
 static void reduce_angle(int reducer, float angle, float* reduced, unsigned* quadrant_or_sign) {
     if (reducer == 0) {
         const float prod = angle * 0.63661977236758134308f;
-        const float q = nearbyintf(prod);   /* cvt.rni; the int wrap of huge angles is not modelled */
+        /* cvt.rni.s32.f32 then cvt.rn.f32.s32: the trip through an integer turns -0 into +0
+         * (saturation of huge angles is not modelled) */
+        const float q = (float)(int)nearbyintf(prod);
         float r = fmaf(q, -1.57079625129699707031f, angle);
         r = fmaf(q, -7.54978941586159635335e-08f, r);
         *reduced = r;
