@@ -1,0 +1,400 @@
+// Attention forward for sm_100a with a polynomial score-mod on the softmax warps.
+//
+// One CTA owns 256 query rows (two 128-row tiles, "slots") of one (batch, query head) and walks the key/value
+// sequence in tiles of 128 keys:
+//   warp 0        TMA producer: Q once, then K and V tiles into a 2-stage shared-memory ring (no multicast)
+//   warp 1        single-thread UMMA issuer: S = Q K^T into tensor memory, O += P V with P read from tensor memory
+//   warps 2..5    softmax / score-mod warpgroup of slot 0 (thread = one query row)
+//   warps 6..9    the same for slot 1
+// Tensor memory (512 columns): S[slot] 128 fp32 columns each, O[slot] 128 fp32 columns each; the bf16 P tile of a
+// slot overwrites the first 64 columns of its S tile once the row has been read into registers.  The two slots are
+// interleaved on the tensor pipe so that one slot's matrix products run under the other slot's score-mod.
+//
+// Score-mods (all on packed bf16 lanes, FMA pipe):
+//   mode 0  soft-capped softmax: s' = cap * tanh_D4(bf16(s*scale/cap)), then exp2 / running max / running sum
+//   mode 1  sigmoid attention:   p = direct piecewise cubic of bf16(s*scale) (B3), no normalisation, O = P V
+//   mode 2  plain softmax
+// Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
+#include "fpt_common.h"
+#include "fpt_programs.h"
+#include "fpt_scoremod.cuh"
+#include "fpt_sm100.cuh"
+
+namespace fpt {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTileM = 128;          // query rows per slot
+constexpr int kTileN = 128;          // keys per tile
+constexpr int kHeadDim = 128;
+constexpr int kSlots = 2;
+constexpr int kStages = 2;
+constexpr uint32_t kPanel = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
+constexpr uint32_t kTileBytes = 2 * kPanel;   // one 128 x 128 bf16 tile
+constexpr int kThreads = 32 * (2 + 4 * kSlots);
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.0f;     // lazy rescale: tolerate exp2 arguments up to +8
+
+struct AttnSmem {
+    alignas(1024) uint8_t q[kSlots][kTileBytes];
+    alignas(1024) uint8_t k[kStages][kTileBytes];
+    alignas(1024) uint8_t v[kStages][kTileBytes];
+    alignas(8) uint64_t q_full[kSlots];
+    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t s_full[kSlots], p_full[kSlots], pv_done[kSlots];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct AttnParams {
+    uint16_t* out;       // (B, S, Hq, D) strides below, D contiguous
+    float* lse;          // [B, Hq, S] or null
+    int64_t out_stride_b, out_stride_s, out_stride_h;
+    int batch, seq, q_heads, kv_heads;
+    int mode, causal;
+    float scale, softcap;
+    uint32_t* status;
+    ProgramWords tanh;   // bf16 TANH_FWD_D4
+    B3Words b3;
+};
+
+enum : uint32_t { kWhereQ = 1, kWhereKEmpty, kWhereVEmpty, kWhereKFull, kWhereVFull, kWherePFull, kWhereSFull, kWherePvDone };
+
+__device__ __forceinline__ float ex2(float x) { return mufu_ex2(x); }
+
+template <int MODE>
+__global__ void __launch_bounds__(kThreads, 1)
+attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int hq = blockIdx.x;
+    const int n_qblocks = gridDim.y;
+    const int qblock = p.causal ? n_qblocks - 1 - int(blockIdx.y) : int(blockIdx.y);  // heavy causal blocks first
+    const int b = blockIdx.z;
+    const int hk = hq / (p.q_heads / p.kv_heads);
+    const int m0 = qblock * (kSlots * kTileM);
+    const int total_tiles = p.seq / kTileN;
+    int n_tiles[kSlots];
+#pragma unroll
+    for (int s = 0; s < kSlots; ++s) {
+        const int row0 = m0 + s * kTileM;
+        n_tiles[s] = row0 >= p.seq ? 0 : (p.causal ? min(total_tiles, row0 / kTileN + 1) : total_tiles);
+    }
+    const int n_max = max(n_tiles[0], n_tiles[1]);
+    volatile uint32_t* abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kSlots; ++s) {
+            mbar_init(&sm.q_full[s], 1);
+            mbar_init(&sm.s_full[s], 1);
+            mbar_init(&sm.p_full[s], 4);   // one arrive per softmax warp
+            mbar_init(&sm.pv_done[s], 1);
+        }
+        for (int st = 0; st < kStages; ++st) {
+            mbar_init(&sm.k_full[st], 1);
+            mbar_init(&sm.k_empty[st], 1);
+            mbar_init(&sm.v_full[st], 1);
+            mbar_init(&sm.v_empty[st], 1);
+        }
+        // a CTA that starts after another one has reported a timeout does nothing, so that a fault in the
+        // pipeline costs one wait limit and not one per CTA
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        mbar_fence_init();
+        tma_prefetch_descriptor(&map_q);
+        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(&map_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(&sm.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const bool skip = sm.abort_flag != 0u;
+
+    if (skip) {
+        // fall through to the teardown
+    } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            for (int s = 0; s < kSlots; ++s) {
+                if (n_tiles[s] == 0) continue;
+                mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
+                tma_load_4d(sm.q[s], &map_q, &sm.q_full[s], 0, m0 + s * kTileM, hq, b);
+                tma_load_4d(sm.q[s] + kPanel, &map_q, &sm.q_full[s], 64, m0 + s * kTileM, hq, b);
+            }
+            bool ok = true;
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int st = j % kStages;
+                const uint32_t ph = uint32_t(j / kStages) & 1u;
+                if (j >= kStages) ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag, p.status, kWhereKEmpty);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+                tma_load_4d(sm.k[st], &map_k, &sm.k_full[st], 0, j * kTileN, hk, b);
+                tma_load_4d(sm.k[st] + kPanel, &map_k, &sm.k_full[st], 64, j * kTileN, hk, b);
+                if (j >= kStages) ok = mbar_wait(&sm.v_empty[st], ph ^ 1u, abort_flag, p.status, kWhereVEmpty);
+                if (!ok) break;
+                mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+                tma_load_4d(sm.v[st], &map_v, &sm.v_full[st], 0, j * kTileN, hk, b);
+                tma_load_4d(sm.v[st] + kPanel, &map_v, &sm.v_full[st], 64, j * kTileN, hk, b);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileM, kTileN, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileM, kHeadDim, 0, 1);
+            auto issue_qk = [&](int s, int st) {
+                const uint32_t qa = smem_u32(sm.q[s]), ka = smem_u32(sm.k[st]);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = uint32_t(kk >> 2) * kPanel + uint32_t(kk & 3) * 32u;
+                    umma_ss(tmem + uint32_t(s) * 128u, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024),
+                            idesc_qk, kk > 0);
+                }
+                umma_commit(&sm.s_full[s]);
+            };
+            auto issue_pv = [&](int s, int st, bool first) {
+                const uint32_t va = smem_u32(sm.v[st]);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)
+                    umma_ts(tmem + 256u + uint32_t(s) * 128u, tmem + uint32_t(s) * 128u + 8u * kk,
+                            umma_smem_desc(va + uint32_t(kk) * 2048u, kPanel, 1024), idesc_pv, (!first) || kk > 0);
+                umma_commit(&sm.pv_done[s]);
+            };
+            bool ok = true;
+            // prologue: S = Q K_0^T for both slots
+            for (int s = 0; s < kSlots && ok; ++s) {
+                if (n_tiles[s] == 0) continue;
+                ok = mbar_wait(&sm.q_full[s], 0, abort_flag, p.status, kWhereQ) &&
+                     mbar_wait(&sm.k_full[0], 0, abort_flag, p.status, kWhereKFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                issue_qk(s, 0);
+            }
+            if (ok && n_max > 0) umma_commit(&sm.k_empty[0]);
+            for (int j = 0; j < n_max && ok; ++j) {
+                const int st = j % kStages;
+                const uint32_t ph = uint32_t(j / kStages) & 1u;
+                const int st_next = (j + 1) % kStages;
+                const uint32_t ph_next = uint32_t((j + 1) / kStages) & 1u;
+                for (int s = 0; s < kSlots && ok; ++s) {
+                    if (j >= n_tiles[s]) continue;
+                    ok = mbar_wait(&sm.v_full[st], ph, abort_flag, p.status, kWhereVFull) &&
+                         mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv(s, st, j == 0);
+                    if (j + 1 < n_tiles[s]) {
+                        ok = mbar_wait(&sm.k_full[st_next], ph_next, abort_flag, p.status, kWhereKFull);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                        issue_qk(s, st_next);   // executes after the P V product above: same issuing thread
+                    }
+                }
+                if (!ok) break;
+                umma_commit(&sm.v_empty[st]);
+                if (j + 1 < n_max) umma_commit(&sm.k_empty[st_next]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ softmax / score-mod warpgroups
+        const int s = (warp - 2) >> 2;
+        const int row_in_tile = 32 * (warp & 3) + lane;          // tensor-memory lane owned by this thread
+        const int row = m0 + s * kTileM + row_in_tile;
+        const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+        const uint32_t t_s = tmem + lane_base + uint32_t(s) * 128u;
+        const uint32_t t_o = tmem + lane_base + 256u + uint32_t(s) * 128u;
+        const int n = n_tiles[s];
+        float row_max = -INFINITY, row_sum = 0.0f;
+        bool ok = true;
+        const float softcap_in = p.scale / p.softcap;           // score -> tanh argument
+        const float softcap_out = p.softcap * kLog2e;           // tanh -> log2-domain score
+        const float plain_scale = p.scale * kLog2e;
+        for (int j = 0; j < n && ok; ++j) {
+            ok = mbar_wait(&sm.s_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWhereSFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            float sc[kTileN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+                uint32_t v[32];
+                tmem_ld_32x32b_x32(t_s + c * 32, v);
+                tmem_ld_wait();
+#pragma unroll
+                for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(v[i]);
+            }
+            uint32_t pw[kTileN / 2];
+            if constexpr (MODE == 1) {
+#pragma unroll
+                for (int i = 0; i < kTileN / 2; ++i) {
+                    const uint32_t x = Sfu<kBf16>::pack(sc[2 * i] * p.scale, sc[2 * i + 1] * p.scale);
+                    uint32_t pr = b3_direct(x, p.b3);
+                    if (p.causal && j == n - 1) {  // keys beyond the diagonal contribute nothing
+                        const int col = j * kTileN + 2 * i;
+                        if (col > row) pr &= 0xffff0000u;
+                        if (col + 1 > row) pr &= 0x0000ffffu;
+                    }
+                    pw[i] = pr;
+                }
+            } else {
+                if constexpr (MODE == 0) {
+#pragma unroll
+                    for (int i = 0; i < kTileN / 2; ++i) {
+                        const uint32_t x = Sfu<kBf16>::pack(sc[2 * i] * softcap_in, sc[2 * i + 1] * softcap_in);
+                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
+                        sc[2 * i] = Sfu<kBf16>::lo(t) * softcap_out;
+                        sc[2 * i + 1] = Sfu<kBf16>::hi(t) * softcap_out;
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < kTileN; ++i) sc[i] *= plain_scale;
+                }
+                if (p.causal && j == n - 1) {
+#pragma unroll
+                    for (int i = 0; i < kTileN; ++i)
+                        if (j * kTileN + i > row) sc[i] = -INFINITY;
+                }
+                float tile_max = sc[0];
+#pragma unroll
+                for (int i = 1; i < kTileN; ++i) tile_max = fmaxf(tile_max, sc[i]);
+                if (tile_max > row_max + kRescaleThreshold || j == 0) {
+                    const float new_max = fmaxf(row_max, tile_max);
+                    if (j > 0) {  // bring the running sum and the accumulator to the new reference
+                        const float f = ex2(row_max - new_max);
+                        row_sum *= f;
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t v[32];
+                            tmem_ld_32x32b_x32(t_o + c * 32, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+                            tmem_st_32x32b_x32(t_o + c * 32, v);
+                        }
+                    }
+                    row_max = new_max;
+                }
+                float local = 0.0f;
+#pragma unroll
+                for (int i = 0; i < kTileN / 2; ++i) {
+                    const float e0 = ex2(sc[2 * i] - row_max), e1 = ex2(sc[2 * i + 1] - row_max);
+                    local += e0 + e1;
+                    pw[i] = Sfu<kBf16>::pack(e0, e1);
+                }
+                row_sum += local;
+            }
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t v[32];
+#pragma unroll
+                for (int i = 0; i < 32; ++i) v[i] = pw[c * 32 + i];
+                tmem_st_32x32b_x32(t_s + c * 32, v);
+            }
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_full[s]);
+        }
+        if (ok && n > 0) {
+            ok = mbar_wait(&sm.pv_done[s], uint32_t(n - 1) & 1u, abort_flag, p.status, kWherePvDone);
+            if (ok) {
+                tc_fence_after_sync();
+                const float inv = MODE == 1 ? 1.0f : 1.0f / row_sum;
+                uint16_t* out_row = p.out + int64_t(b) * p.out_stride_b + int64_t(row) * p.out_stride_s +
+                                    int64_t(hq) * p.out_stride_h;
+#pragma unroll
+                for (int c = 0; c < 4; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(t_o + c * 32, v);
+                    tmem_ld_wait();
+                    uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
+                        w.y = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
+                        w.z = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
+                        w.w = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
+                        dst[q4] = w;
+                    }
+                }
+                if (MODE != 1 && p.lse)
+                    p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
+            }
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+}  // namespace fpt
+
+using namespace fpt;
+
+extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
+                                 int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
+                                 void* status, fpt_stream_t stream) {
+    if (!out || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !out_strides)
+        return FPT_ERR_NULL_POINTER;
+    if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
+    if (head_dim != kHeadDim || seq % kTileN != 0 || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
+    if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
+    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
+    if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
+    if (mode == FPT_ATTN_SIGMOID_DIRECT && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
+    if (reinterpret_cast<uintptr_t>(out) & 15u) return FPT_ERR_MISALIGNED;
+    for (int i = 0; i < 3; ++i)
+        if ((out_strides[i] * 2) & 15) return FPT_ERR_MISALIGNED;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+
+    // strides arrive as (batch, seq, head) in elements; the tensor maps want (seq, head, batch) in bytes
+    auto make_map = [&](CUtensorMap* map, const void* base, const int64_t* st, int64_t heads) {
+        const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(seq), uint64_t(heads), uint64_t(batch)};
+        const uint64_t strides[3] = {uint64_t(st[1]) * 2, uint64_t(st[2]) * 2, uint64_t(st[0]) * 2};
+        return make_tensor_map_bf16_4d(map, base, dims, strides, kTileM);
+    };
+    CUtensorMap map_q, map_k, map_v;
+    if (int rc = make_map(&map_q, q, q_strides, q_heads)) return rc;
+    if (int rc = make_map(&map_k, k, k_strides, kv_heads)) return rc;
+    if (int rc = make_map(&map_v, v, v_strides, kv_heads)) return rc;
+
+    AttnParams p{};
+    p.out = static_cast<uint16_t*>(out);
+    p.lse = static_cast<float*>(lse);
+    p.out_stride_b = out_strides[0];
+    p.out_stride_s = out_strides[1];
+    p.out_stride_h = out_strides[2];
+    p.batch = int(batch); p.seq = int(seq); p.q_heads = int(q_heads); p.kv_heads = int(kv_heads);
+    p.mode = mode; p.causal = causal ? 1 : 0;
+    p.scale = scale; p.softcap = softcap;
+    p.status = static_cast<uint32_t*>(status);
+    const ProgramRow* tanh_row = find_program(FPT_FN_TANH, FPT_FWD, 4, FPT_BF16, FPT_SRC_CURRENT);
+    if (!tanh_row || tanh_row->shape != kOddSat) return FPT_ERR_UNKNOWN_PROGRAM;
+    p.tanh = program_words(*tanh_row);
+    p.b3 = b3_words(mode == FPT_ATTN_SIGMOID_DIRECT ? log2_n : 12);
+
+    const size_t smem = sizeof(AttnSmem) + 1024;
+    static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory budget");
+    const int n_qblocks = int((seq + kSlots * kTileM - 1) / (kSlots * kTileM));
+    const dim3 grid{unsigned(q_heads), unsigned(n_qblocks), unsigned(batch)};
+    auto launch = [&](auto kernel) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
+        kernel<<<grid, kThreads, smem, stream>>>(map_q, map_k, map_v, p);
+        return cuda_status(cudaGetLastError());
+    };
+    if (mode == FPT_ATTN_SOFTCAP_TANH) return launch(attention_fwd_kernel<0>);
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1>);
+    return launch(attention_fwd_kernel<2>);
+}

@@ -158,6 +158,32 @@ int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const
                    int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int kind, int dtype,
                    fpt_stream_t stream);
 
+/* ---- attention forward with a polynomial score-mod, bf16, head_dim 128, seq a multiple of 128
+ *      replaces the forward of the patched FlashAttention interface that the reference drives through
+ *      `_flash_attn_fwd(q, k, v, softmax_scale=, causal=, softcap=, score_mod=, sigmoid_attention=, ...) -> (out, lse)`
+ *      (reference: src/sfu_repro/fa4.py:755-826, wrapper :899-948, canonical configurations :650-709).
+ *      q [B,S,Hq,D], k / v [B,S,Hkv,D], out [B,S,Hq,D]: logical (batch, seq, head, dim) tensors addressed through
+ *      `*_strides` = element strides of (batch, seq, head); dim is contiguous.  Grouped-query attention:
+ *      kv head = q head / (Hq / Hkv).  lse fp32 [B,Hq,S] (may be NULL; unused in sigmoid mode).
+ *      mode FPT_ATTN_SOFTCAP_TANH:  softmax(softcap * tanhD4_bf16(score*scale/softcap)), the B2 score-mod
+ *      mode FPT_ATTN_SIGMOID_DIRECT: P = direct piecewise cubic sigmoid of bf16(score*scale) scaled for n = 2^log2_n
+ *                                    keys (B3), O = P V without normalisation
+ *      mode FPT_ATTN_SOFTMAX:        plain softmax (control)
+ *      status: one zero-initialised device word; non-zero after the launch means a bounded device-side wait ran
+ *      out (bit 31 set, low bits tell where) and the output is invalid. */
+enum { FPT_ATTN_SOFTCAP_TANH = 0, FPT_ATTN_SIGMOID_DIRECT = 1, FPT_ATTN_SOFTMAX = 2 };
+int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch, int64_t seq,
+                      int64_t q_heads, int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
+                      const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides, int mode,
+                      int causal, float scale, float softcap, int log2_n, void* status, fpt_stream_t stream);
+
+/* ---- diagnostic: one 128x128x128 bf16 tile through the tensor-core building blocks of the attention kernel
+ *      (no counterpart in the reference).  a, b: bf16 [128,128] row-major; c: fp32 [128,128];
+ *      mode 0: c = a * b^T (both operands K-major in shared memory); mode 1: c = a * b (a staged in tensor memory,
+ *      b an MN-major shared-memory operand).  status: one zero-initialised device word; non-zero afterwards means a
+ *      bounded device-side wait ran out. */
+int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* status, fpt_stream_t stream);
+
 /* ---- launch knobs for benchmarks (process-wide; defaults are the measured-best values) -------- */
 /* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1. */
 int fpt_set_tuning(const char* key, int value);

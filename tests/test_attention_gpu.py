@@ -1,0 +1,129 @@
+"""GPU: tensor-core building blocks and the attention forward against the fp32 CPU oracle."""
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_umma_tile_matches_matmul(fpt, cuda, mode):
+    """One 128^3 bf16 tile: Q K^T form (both operands K-major) and P V form (tensor-memory A, MN-major B)."""
+    import torch
+    g = torch.Generator(device=cuda)
+    g.manual_seed(1234 + mode)
+    a = torch.randn(128, 128, device=cuda, generator=g).to(torch.bfloat16)
+    b = torch.randn(128, 128, device=cuda, generator=g).to(torch.bfloat16)
+    c = torch.full((128, 128), float("nan"), device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    fpt.call("fpt_selftest_umma", c.data_ptr(), a.data_ptr(), b.data_ptr(), mode, status.data_ptr(), stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, hex(int(status.item()) & 0xFFFFFFFF)
+    want = a.float() @ (b.float().t() if mode == 0 else b.float())
+    err = (c - want).abs().max().item()
+    assert err < 1e-3 * max(1.0, want.abs().max().item()), err
+
+
+def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=12):
+    """q,k,v torch bf16 (B,S,H,D), any strides with D contiguous. Returns (out (B,S,Hq,D), lse, status)."""
+    import ctypes
+    import torch
+    B, S, Hq, D = q.shape
+    Hk = k.shape[2]
+    out = torch.full((B, S, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    lse = torch.full((B, Hq, S), float("nan"), dtype=torch.float32, device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    fpt.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk, D,
+             arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, status.data_ptr(), stream())
+    torch.cuda.synchronize()
+    return out, lse, int(status.item()) & 0xFFFFFFFF
+
+
+def bits(t):
+    import torch
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+CASES = [
+    # (B, S, Hq, Hk, mode, causal, softcap, log2_n)
+    (1, 128, 1, 1, 2, False, 0.0, 12),
+    (1, 256, 2, 1, 2, True, 0.0, 12),
+    (1, 384, 4, 2, 0, True, 50.0, 12),
+    (2, 512, 4, 1, 0, True, 30.0, 12),
+    (1, 512, 2, 2, 1, False, 0.0, 9),
+    (1, 384, 2, 1, 1, True, 0.0, 12),
+    (1, 1024, 8, 2, 0, True, 50.0, 12),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_attention_matches_fp32_oracle(fpt, cuda, oracle, case):
+    """Output within 2e-2 max-abs of the fp32 CPU attention that uses the same polynomial score-mod."""
+    import torch
+    B, S, Hq, Hk, mode, causal, softcap, log2_n = case
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(1234)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse, status = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    assert status == 0, hex(status)
+    assert not torch.isnan(out.float()).any()
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    rng = np.random.default_rng(7)
+    worst = 0.0
+    for b in range(B):
+        for h in range(Hq):
+            rows = np.arange(S) if (b == 0 and h in (0, Hq - 1)) else np.sort(rng.choice(S, size=min(S, 32), replace=False))
+            want = oracle.attention_rows(qb, kb, vb, b, h, rows, mode, causal, scale, softcap, log2_n)
+            got = out[b, rows, h, :].float().cpu().numpy()
+            worst = max(worst, float(np.abs(got - want).max()))
+    assert worst < 2e-2, worst
+
+
+def test_attention_accepts_head_major_layout(fpt, cuda):
+    """(B,H,S,D) storage (what the fused RoPE writes) addressed through strides gives the same result."""
+    import torch
+    B, S, H, D = 1, 256, 2, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(5)
+    q = torch.randn(B, S, H, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, H, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    ref, _, st0 = run_attention(fpt, cuda, q, k, v, 2, True, scale)
+    qh = q.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)   # same values, (B,H,S,D) memory
+    kh = k.permute(0, 2, 1, 3).contiguous().permute(0, 2, 1, 3)
+    alt, _, st1 = run_attention(fpt, cuda, qh, kh, v, 2, True, scale)
+    assert st0 == 0 and st1 == 0
+    assert torch.equal(ref.view(torch.int16), alt.view(torch.int16))
+
+
+def test_plain_softmax_mode_matches_torch_sdpa(fpt, cuda):
+    import torch
+    B, S, Hq, Hk, D = 1, 512, 4, 2, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(11)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    out, lse, status = run_attention(fpt, cuda, q, k, v, 2, True, 1.0 / math.sqrt(D))
+    assert status == 0
+    kk = k.repeat_interleave(Hq // Hk, dim=2)
+    vv = v.repeat_interleave(Hq // Hk, dim=2)
+    want = torch.nn.functional.scaled_dot_product_attention(
+        q.transpose(1, 2).float(), kk.transpose(1, 2).float(), vv.transpose(1, 2).float(), is_causal=True).transpose(1, 2)
+    assert float((out.float() - want).abs().max()) < 2e-2
+    scores = torch.einsum("bshd,bthd->bhst", q.float(), kk.float()) / math.sqrt(D)
+    mask = torch.ones(S, S, device=cuda, dtype=torch.bool).tril()
+    want_lse = torch.logsumexp(scores.masked_fill(~mask, float("-inf")), dim=-1)
+    assert float((lse - want_lse).abs().max()) < 1e-2
