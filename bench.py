@@ -469,6 +469,21 @@ def run_profile_case(args):
             run = lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), rows * hidden, 3, 1, 0, stream))
         else:
             run = lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, stream))
+    elif case in ("attn_softcap", "attn_sigmoid", "attn_softmax"):
+        import ctypes
+        B, S, Hq, Hk, D = 1, n, 32, 8, 128      # --profile-n is the sequence length here
+        mode = {"attn_softcap": 0, "attn_sigmoid": 1, "attn_softmax": 2}[case]
+        causal = 0 if mode == 1 else 1
+        q = torch.randn(B, S, Hq, D, device=device, generator=g).to(torch.bfloat16)
+        k = torch.randn(B, S, Hk, D, device=device, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, S, Hk, D, device=device, generator=g).to(torch.bfloat16)
+        o = torch.empty_like(q)
+        lse = torch.empty(B, Hq, S, device=device)
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+        run = lambda: _lib.check("fpt_attention_fwd", lib.fpt_attention_fwd(
+            o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
+            arr(o), mode, causal, 1.0 / math.sqrt(D), 50.0, 12, status.data_ptr(), stream))
     else:
         raise SystemExit(f"unknown profile case {case}")
     for _ in range(args.steps):
