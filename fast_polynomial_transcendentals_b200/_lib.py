@@ -42,10 +42,13 @@ SIGNATURES: dict[str, list] = {
     "fpt_attention_fwd": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _vp, _vp],
     "fpt_selftest_umma": [_vp, _vp, _vp, _int, _vp, _vp],
+    "fpt_rope_apply_static_table": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
+    "fpt_rope_static_table_capacity": [],
     "fpt_set_tuning": [ctypes.c_char_p, _int],
     "fpt_get_tuning": [ctypes.c_char_p, ctypes.POINTER(_int)],
 }
-_RESTYPES = {"fpt_status_string": ctypes.c_char_p, "fpt_version": ctypes.c_char_p}
+_RESTYPES = {"fpt_status_string": ctypes.c_char_p, "fpt_version": ctypes.c_char_p,
+             "fpt_rope_static_table_capacity": ctypes.c_int64}
 SIGNATURES["fpt_status_string"] = [_int]
 SIGNATURES["fpt_version"] = []
 

@@ -109,6 +109,7 @@ const char* fpt_status_string(int status) {
     case FPT_ERR_UNSUPPORTED_SHAPE: return "operation not defined for this program shape";
     case FPT_ERR_NO_DEVICE: return "no usable CUDA device of compute capability 10.x is current";
     case FPT_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+    case FPT_ERR_SCRATCH_TOO_SMALL: return "the problem needs more scratch than the library's fixed array holds";
     default: return status > 0 ? cudaGetErrorString(cudaError_t(status)) : "unknown status";
     }
 }

@@ -1,6 +1,8 @@
 // Paired sin/cos (fp32 angles -> packed fp16 / bf16 cos and sin planes), RoPE tables from Q0.32 phases and the
 // fused RoPE rotation with transpose.
+#include <atomic>
 #include <cstring>
+#include <mutex>
 
 #include "fpt_programs.h"
 #include "fpt_stream.cuh"
@@ -570,4 +572,71 @@ extern "C" int fpt_rope_apply(void* q_out, void* k_out, const void* q, const voi
     }
 #undef FPT_ROPE_CASE
     return cuda_status(cudaGetLastError());
+}
+
+// ---- fused RoPE from a cached table, for callers that cannot allocate device memory ----------------------
+//
+// The cached-table rotation needs a [2, seq, head_dim/2] fp16 table between its two kernels.  Code that runs
+// where device allocation is off limits -- a plugin called inside a serving loop whose host owns every byte of
+// device memory, a real-time path that may not take the allocator lock, a library user without a CUDA allocator
+// of its own -- cannot provide that buffer.  For them the table lives in the fixed array below, which every GPU
+// that loads this library holds until the process exits.
+namespace fpt {
+namespace {
+
+constexpr int64_t kStaticRopeTableHalves = int64_t(1) << 21;  // 4 MiB: seq * head_dim <= 2^21, e.g. 16384 x 128
+
+static __device__ __align__(256) uint16_t g_rope_table_scratch[kStaticRopeTableHalves];
+
+// The array's name is a host-side handle, not a device address: the address has to be asked for, once per
+// device, with that device current.
+struct StaticTableAddress {
+    std::atomic<int> ready{0};
+    void* ptr = nullptr;
+};
+StaticTableAddress g_static_table[64];
+std::mutex g_static_table_mutex;
+
+int static_rope_table_address(void** out) {
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return e == cudaErrorNoDevice || e == cudaErrorInsufficientDriver ? FPT_ERR_NO_DEVICE : int(e);
+    if (device < 0 || device >= 64) return FPT_ERR_NO_DEVICE;
+    StaticTableAddress& slot = g_static_table[device];
+    if (!slot.ready.load(std::memory_order_acquire)) {
+        std::lock_guard<std::mutex> lock(g_static_table_mutex);
+        if (!slot.ready.load(std::memory_order_relaxed)) {
+            void* p = nullptr;
+            e = cudaGetSymbolAddress(&p, g_rope_table_scratch);
+            if (e != cudaSuccess) return int(e);
+            if (!p) return FPT_ERR_NULL_POINTER;
+            slot.ptr = p;
+            slot.ready.store(1, std::memory_order_release);
+        }
+    }
+    *out = slot.ptr;
+    return FPT_OK;
+}
+
+}  // namespace
+}  // namespace fpt
+
+extern "C" int64_t fpt_rope_static_table_capacity(void) { return fpt::kStaticRopeTableHalves; }
+
+extern "C" int fpt_rope_apply_static_table(void* q_out, void* k_out, const void* q, const void* k,
+                                           const void* phase_increments, int64_t batch, int64_t seq, int64_t q_heads,
+                                           int64_t k_heads, int64_t head_dim, int table_kind, int dtype,
+                                           fpt_stream_t stream) {
+    if (batch < 0 || seq < 0 || q_heads < 0 || k_heads < 0 || head_dim < 0) return FPT_ERR_BAD_SIZE;
+    if (table_kind != FPT_ROPE_HALF_TURN_D5_D6 && table_kind != FPT_ROPE_QUARTER_TURN_D3_D4) return FPT_ERR_BAD_ENUM;
+    if (head_dim % 8) return FPT_ERR_BAD_SIZE;
+    if (seq > 0 && head_dim > 0 && seq > fpt::kStaticRopeTableHalves / head_dim) return FPT_ERR_SCRATCH_TOO_SMALL;
+    if (batch * seq * head_dim == 0 || q_heads + k_heads == 0) return FPT_OK;
+    if (!phase_increments) return FPT_ERR_NULL_POINTER;
+    void* table = nullptr;
+    if (int rc = fpt::static_rope_table_address(&table)) return rc;
+    // every entry of the [2, seq, head_dim/2] region used below is rewritten here, so nothing left over from an
+    // earlier call is ever read
+    if (int rc = fpt_rope_table(table, phase_increments, seq, head_dim / 2, table_kind, 0, stream)) return rc;
+    return fpt_rope_apply(q_out, k_out, q, k, table, batch, seq, q_heads, k_heads, head_dim, FPT_ROPE_CACHED, dtype, stream);
 }

@@ -41,6 +41,7 @@ typedef struct CUstream_st* fpt_stream_t; /* == cudaStream_t */
 #define FPT_ERR_UNSUPPORTED_SHAPE (-6)
 #define FPT_ERR_NO_DEVICE (-7)       /* no CUDA device, or not compute capability 10.x */
 #define FPT_ERR_DEVICE_TIMEOUT (-8)  /* a bounded device-side wait ran out (attention kernel status word) */
+#define FPT_ERR_SCRATCH_TOO_SMALL (-9) /* the problem needs more than the library's fixed scratch array holds */
 
 enum { FPT_FP16 = 0, FPT_BF16 = 1 };
 enum { FPT_SRC_CURRENT = 0, FPT_SRC_SOLLYA = 1 };
@@ -157,6 +158,21 @@ int fpt_rope_table(void* table, const void* params, int64_t seq, int64_t freq_co
 int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const void* params, int64_t batch,
                    int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int kind, int dtype,
                    fpt_stream_t stream);
+
+/* ---- fused RoPE from a cached table WITHOUT a caller-provided table (no counterpart in the reference)
+ *      Same result as fpt_rope_table followed by fpt_rope_apply(kind = FPT_ROPE_CACHED), for callers that may not
+ *      allocate device memory (a plugin inside a serving loop whose host owns all device memory, a real-time path
+ *      that must stay off the allocator, a user without a device allocator): the [2, seq, head_dim/2] fp16 table
+ *      lives in a fixed 4 MiB array inside the library, held by every GPU that loads it until the process exits.
+ *      Limit: seq * head_dim <= fpt_rope_static_table_capacity() (2^21, e.g. 16384 x 128); larger problems are
+ *      rejected with FPT_ERR_SCRATCH_TOO_SMALL.  The call allocates nothing.  The first call on a device looks up
+ *      the array's device address (cudaGetSymbolAddress); make that first call before any stream capture.
+ *      All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race on
+ *      it; calls on one stream are safe.  table_kind: FPT_ROPE_HALF_TURN_D5_D6 or FPT_ROPE_QUARTER_TURN_D3_D4. */
+int64_t fpt_rope_static_table_capacity(void);
+int fpt_rope_apply_static_table(void* q_out, void* k_out, const void* q, const void* k, const void* phase_increments,
+                                int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim,
+                                int table_kind, int dtype, fpt_stream_t stream);
 
 /* ---- attention forward with a polynomial score-mod, bf16, head_dim 128, seq a multiple of 128
  *      replaces the forward of the patched FlashAttention interface that the reference drives through
