@@ -33,6 +33,8 @@ N_HBM = 1 << 28
 N_L2 = 1 << 20
 SEED = 1234
 NOMINAL_HBM_GBS = 8000.0
+# dram__bytes_read + dram__bytes_write of the sigmoid kernel per 2^28-element launch, scaled from the 2^26 capture
+SIGMOID_TRAFFIC_BYTES_PER_LAUNCH = int(4 * 134.225152e6 + (4 * 134.217728e6 - (134.217728e6 - 82.393088e6)))
 
 
 def measured_peaks():
@@ -335,6 +337,7 @@ def run_gpu_arm(args):
     torch.cuda.empty_cache()
     extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep)
     extras["b3_config1"] = bench_b3(torch, lib, _lib, device, S, time_graph)
+    extras["attention_fwd_bf16"] = bench_attention(torch, lib, _lib, device, S, time_sweep)
 
     # ---- e2e through the public API with host buffers
     e2e = bench_e2e(torch, spline_ops, HostPipeline, device)
@@ -346,7 +349,10 @@ def run_gpu_arm(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
         "roofline": {"bound": "hbm", "achieved": dominant["poly_gbs"], "peak": hbm_peak, "unit": "GB/s",
-                     "frac": dominant["poly_gbs"] / hbm_peak, "traffic": None, "peak_kind": f"of {peak_kind}",
+                     "frac": dominant["poly_gbs"] / hbm_peak, "traffic": SIGMOID_TRAFFIC_BYTES_PER_LAUNCH,
+                     "traffic_source": "ncu capture at 2^26 elements (dram read 134.23 MB, write 82.39 MB = algorithmic minus "
+                                       "what stays dirty in L2), reads scaled x4, the L2-resident remainder kept constant",
+                     "algorithmic_bytes": 4 * N_HBM, "peak_kind": f"of {peak_kind}",
                      "kernel": "stream_kernel<UnaryOp<fp16, ODD_HALF, 3>> (sigmoid D3), 4 algorithmic bytes per element "
                                "x 2^28 elements per launch", "frac_of_nominal_8tbs": dominant["poly_gbs"] / NOMINAL_HBM_GBS},
         "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": gpu_launches, "clocks": clocks.summary(),
@@ -391,6 +397,43 @@ def bench_b3(torch, lib, _lib, device, S, time_graph):
           ("sigmoid_native", 4, lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, 0, 0, 0, 1, 0, S())))]
     t = time_graph(ks)
     return {k: {"us": v * 1e3, "elements_per_s": n / (v * 1e-3)} for k, v in t.items()} | {"n": n, "regime": "64 MiB touched: L2 resident"}
+
+
+def bench_attention(torch, lib, _lib, device, S, time_sweep):
+    """Configurations 4 and 5 of the baseline (plus the reference's published S=4096 shape), forward only."""
+    import ctypes
+    _, tensor_peak, _ = measured_peaks()
+    out = {}
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    D = 128
+    shapes = (("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 0, 1, 50.0, 12),
+              ("config5_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 1, 0, 0.0, 14),
+              ("published_shape_softcap30_B1_S4096_Hq32_Hkv8", 1, 4096, 32, 8, 0, 1, 30.0, 12),
+              ("published_shape_sigmoid_B1_S4096_Hq32_Hkv8_causal", 1, 4096, 32, 8, 1, 1, 0.0, 12),
+              ("control_plain_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12))
+    for name, B, Sq, Hq, Hk, mode, causal, cap, log2_n in shapes:
+        q = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
+        k = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
+        v = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
+        o = torch.empty_like(q)
+        lse = torch.empty(B, Hq, Sq, device=device)
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+        sq, sk, sv, so = arr(q), arr(k), arr(v), arr(o)
+        ks = [("attn", 0, lambda: _lib.check("fpt_attention_fwd", lib.fpt_attention_fwd(
+            o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, Sq, Hq, Hk, D, sq, sk, sv, so, mode,
+            causal, 1.0 / math.sqrt(D), cap, log2_n, status.data_ptr(), S())))]
+        _, t = time_sweep(ks, 5, 2)
+        if int(status.item()) != 0:
+            raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x}")
+        flops = 4.0 * B * Hq * Sq * Sq * D * (0.5 if causal else 1.0)
+        tf = flops / (t["attn"] * 1e-3) / 1e12
+        out[name] = {"ms": t["attn"], "tflops": tf, "frac_of_measured_bf16_peak": tf / tensor_peak,
+                     "flops_convention": "4*B*Hq*S^2*D, halved when causal"}
+        del q, k, v, o, lse
+    torch.cuda.empty_cache()
+    return out
 
 
 def bench_e2e(torch, spline_ops, HostPipeline, device):
