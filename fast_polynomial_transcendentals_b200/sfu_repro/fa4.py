@@ -1,0 +1,598 @@
+"""Declarative attention configuration and the PyTorch wrapper, bound to this package's attention kernel.
+
+Keeps the reference's configuration surface (reference: src/sfu_repro/fa4.py:50-103 the two dataclasses, :106-199
+exp2 routing variants, :271-415 validation, :454-647 resolution against a runtime mapping, :650-752 the canonical B2 /
+B3 / B5 configurations, :755-948 autograd function and module wrapper): same field names, defaults, accepted values
+and error messages, and the same seam -- ``resolve_fa4_config(config, runtime=...)`` takes a mapping with the keys
+``flash_attn_fwd``, ``flash_attn_bwd``, ``run_polynomial_coefficient_audit``, ``audit_polynomial_selection``,
+``audit_attention_handwritten_fast_path``, ``create_softcap_scoremod_backend``,
+``create_softcap_scoremod_bwd_backend``.  When no mapping is passed, the runtime is this package's own
+(``b200_runtime()``): forward on the tcgen05 kernel, backward not built yet (it raises).
+
+Inputs of :class:`FA4AttentionWrapper` are ``(batch, heads, sequence, dim)``; the kernel interface is
+``(batch, sequence, heads, dim)``.
+"""
+from __future__ import annotations
+
+import logging
+import math
+import os
+from collections.abc import Callable, Mapping
+from dataclasses import dataclass
+from functools import lru_cache
+from typing import Any
+
+import torch
+from torch import nn
+
+LOGGER = logging.getLogger(__name__)
+
+FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH = 4096
+
+SUPPORTED_EXP2_BACKENDS = ("d3", "pwl2", "pwl1_safe", "pwl1_safe_f16", "pwl2_safe", "pwl2_safe_f16", "pwl2_safe_bf16",
+                           "d2_safe", "d2_safe_noclamp", "d2_safe_f16", "d2_safe_bf16", "pwl2_f16")
+
+
+@dataclass(frozen=True)
+class FA4Config:
+    """What the user asks for; independent of any training framework."""
+
+    mode: str = "softmax"
+    exp2_emu_backend: str = "d3"
+    exp2_emu_freq: int | None = None
+    exp2_emu_freq_bwd: int = 0
+    softcap: float = 30.0
+    softcap_backend: str = "native"
+    softcap_degree: int = 4
+    softcap_coeff_source: str = "current"
+    softcap_backward_mode: str = "analytical"
+    sigmoid_variant: str = "poly"
+    sigmoid_poly_backend: str = "cute"
+    sigmoid_degree: int = 3
+    sigmoid_degree_bwd: int | None = None
+    sigmoid_coeff_source: str = "current"
+    sigmoid_backward_mode: str = "algebraic"
+    sigmoid_sfu_freq: int = 16
+    sigmoid_sfu_res: int = 0
+    sigmoid_sfu_freq_bwd: int | None = None
+    sigmoid_sfu_res_bwd: int | None = None
+    sigmoid_bias: float | None = None
+    sigmoid_qk_norm: bool = True
+    audit_coefficients: bool = True
+
+
+@dataclass(frozen=True)
+class ResolvedFA4Config:
+    """A validated configuration bound to an attention runtime."""
+
+    mode: str
+    flash_attn_fwd: Callable[..., Any]
+    flash_attn_bwd: Callable[..., Any]
+    exp2_emu_backend: str = "d3"
+    exp2_emu_freq: int | None = None
+    exp2_emu_freq_bwd: int = 0
+    softcap: float = 0.0
+    score_mod: Callable[..., Any] | None = None
+    score_mod_bwd: Callable[..., Any] | None = None
+    sigmoid_attention: bool = False
+    sigmoid_sfu_freq: int = 16
+    sigmoid_sfu_res: int = 0
+    sigmoid_sfu_freq_bwd: int | None = None
+    sigmoid_sfu_res_bwd: int | None = None
+    sigmoid_use_direct_bwd_poly: bool = False
+    sigmoid_bias: float | None = None
+    sigmoid_poly_backend: str = "cute"
+    sigmoid_degree: int = 3
+    sigmoid_degree_bwd: int | None = None
+    sigmoid_coeff_source: str = "current"
+    sigmoid_qk_norm: bool = True
+    implementation_summary: str = ""
+
+
+@dataclass(frozen=True)
+class Exp2Variant:
+    """One mixed SFU / software exp2 route of the softmax benchmark."""
+
+    name: str
+    backend: str
+    forward_frequency: int | None
+    backward_frequency: int
+
+    @staticmethod
+    def _fraction(frequency: int | None) -> float | None:
+        if frequency is None:
+            return None
+        return 0.0 if frequency == 0 else min(1.0, 4.0 / frequency)
+
+    @property
+    def nominal_forward_polynomial_fraction(self) -> float | None:
+        return self._fraction(self.forward_frequency)
+
+    @property
+    def nominal_backward_polynomial_fraction(self) -> float:
+        return float(self._fraction(self.backward_frequency))
+
+    @property
+    def nominal_forward_pwl_fraction(self) -> float | None:
+        return self.nominal_forward_polynomial_fraction
+
+    @property
+    def nominal_backward_pwl_fraction(self) -> float:
+        return self.nominal_backward_polynomial_fraction
+
+
+DEFAULT_EXP2_VARIANTS = ",".join(("sfu=d3:0:0", "d3_auto=d3:auto:0", "d2_safe_12p5=d2_safe:32:0", "d2_safe_16p7=d2_safe:24:0",
+                                  "d2_safe_20=d2_safe:20:0", "d2_safe_25=d2_safe:16:0", "d2_safe_33p3=d2_safe:12:0",
+                                  "d2_safe_40=d2_safe:10:0", "d2_safe_50=d2_safe:8:0", "d2_safe_66p7=d2_safe:6:0",
+                                  "d2_safe_100=d2_safe:4:0"))
+
+
+def _validate_exp2_route(frequency: int | None, label: str) -> int | None:
+    if frequency is None:
+        return None
+    frequency = int(frequency)
+    if frequency < 0 or (frequency != 0 and (frequency < 4 or frequency % 2)):
+        raise ValueError(f"{label} frequency must be 0 or an even integer >= 4, got {frequency}")
+    return frequency
+
+
+def parse_exp2_frequency(value: str, *, allow_auto: bool) -> int | None:
+    """One exp2 routing frequency: 'auto' (where allowed), 0, or an even integer >= 4."""
+    if allow_auto and value == "auto":
+        return None
+    try:
+        frequency = int(value)
+    except ValueError as error:
+        allowed = "'auto', 0, or an even integer >= 4" if allow_auto else "0 or an even integer >= 4"
+        raise ValueError(f"frequency must be {allowed}, got {value!r}") from error
+    return _validate_exp2_route(frequency, "exp2")
+
+
+def parse_exp2_variants(value: str) -> tuple[Exp2Variant, ...]:
+    """Parse ``name=backend:forward:backward`` items separated by commas."""
+    variants: list[Exp2Variant] = []
+    for raw in (item.strip() for item in value.split(",")):
+        if not raw:
+            continue
+        try:
+            name, route = raw.split("=", maxsplit=1)
+            backend, forward, backward = route.split(":")
+        except ValueError as error:
+            raise ValueError("variant must have name=backend:forward_frequency:backward_frequency syntax, "
+                             f"got {raw!r}") from error
+        name, backend = name.strip(), backend.strip()
+        if not name:
+            raise ValueError("variant name must not be empty")
+        if backend not in SUPPORTED_EXP2_BACKENDS:
+            raise ValueError(f"unsupported exp2 backend {backend!r}")
+        variants.append(Exp2Variant(name, backend, parse_exp2_frequency(forward.strip(), allow_auto=True),
+                                    int(parse_exp2_frequency(backward.strip(), allow_auto=False))))
+    if not variants:
+        raise ValueError("at least one variant is required")
+    if len({v.name for v in variants}) != len(variants):
+        raise ValueError("variant names must be unique")
+    return tuple(variants)
+
+
+def _env_flag(name: str) -> bool:
+    value = os.environ.get(name)
+    return value is not None and value.lower() in ("1", "true", "yes", "on")
+
+
+def _sigmoid_route(frequency: int, residue_count: int, label: str) -> tuple[int, int]:
+    frequency, residue_count = int(frequency), int(residue_count)
+    if frequency <= 0:
+        raise ValueError(f"{label} sigmoid_sfu_freq must be positive, got {frequency}")
+    if residue_count < 0 or residue_count > frequency:
+        raise ValueError(f"{label} sigmoid_sfu_res must lie in [0, sigmoid_sfu_freq], got {residue_count} for {frequency}")
+    return frequency, residue_count
+
+
+def _uses_sollya(c: FA4Config) -> bool:
+    return (c.mode == "softcap" and c.softcap_coeff_source == "sollya") or (
+        c.mode == "sigmoid_attention" and c.sigmoid_variant == "poly" and c.sigmoid_coeff_source == "sollya")
+
+
+def _is_device_current_poly(c: FA4Config, degree: int) -> bool:
+    return (c.mode == "sigmoid_attention" and c.sigmoid_variant == "poly" and c.sigmoid_poly_backend == "device"
+            and c.sigmoid_coeff_source == "current" and int(c.sigmoid_degree) == degree and c.sigmoid_bias is None)
+
+
+def _uses_direct_flash_sigmoid(c: FA4Config) -> bool:
+    return _is_device_current_poly(c, 3)
+
+
+def _check_choice(value, allowed, message):
+    if value not in allowed:
+        raise ValueError(message)
+
+
+def validate_fa4_config(config: FA4Config, *, sequence_length: int | None = None) -> FA4Config:
+    """Check a configuration without touching CUDA or any attention backend."""
+    c = config
+    _check_choice(c.mode, ("softmax", "softcap", "sigmoid_attention"), f"unsupported FA4 mode {c.mode!r}")
+    _check_choice(c.exp2_emu_backend, SUPPORTED_EXP2_BACKENDS, f"unsupported exp2 backend {c.exp2_emu_backend!r}")
+    _validate_exp2_route(c.exp2_emu_freq, "forward exp2")
+    _validate_exp2_route(c.exp2_emu_freq_bwd, "backward exp2")
+    if _uses_sollya(c) and not _env_flag("SFU_REPRO_ALLOW_SOLLYA_SWEEP"):
+        raise ValueError("Sollya coefficient sources are benchmark-only. Set SFU_REPRO_ALLOW_SOLLYA_SWEEP=1 for an "
+                         "explicit sweep.")
+
+    if c.mode == "softcap":
+        _check_choice(c.softcap_backend, ("native", "cute", "device"), f"unsupported softcap backend {c.softcap_backend!r}")
+        _check_choice(c.softcap_backward_mode, ("analytical", "ste", "exact_1mt2", "native"),
+                      f"unsupported softcap backward mode {c.softcap_backward_mode!r}")
+        _check_choice(c.softcap_coeff_source, ("current", "sollya"),
+                      f"unsupported softcap coefficient source {c.softcap_coeff_source!r}")
+        if c.softcap <= 0:
+            raise ValueError("softcap must be positive")
+        native = c.softcap_backend == "native"
+        if native and c.softcap_backward_mode != "native":
+            raise ValueError("native softcap requires softcap_backward_mode='native'")
+        if not native and c.softcap_backward_mode == "native":
+            raise ValueError("polynomial softcap cannot use softcap_backward_mode='native'")
+        if c.softcap_coeff_source == "sollya" and c.softcap_backend != "device":
+            raise ValueError("Sollya softcap fits require softcap_backend='device'")
+
+    if c.mode == "sigmoid_attention":
+        _check_choice(c.sigmoid_variant, ("poly", "sfu"), f"unsupported sigmoid variant {c.sigmoid_variant!r}")
+        _check_choice(c.sigmoid_poly_backend, ("cute", "device"),
+                      f"unsupported sigmoid polynomial backend {c.sigmoid_poly_backend!r}")
+        _check_choice(c.sigmoid_backward_mode, ("algebraic", "direct"),
+                      f"unsupported sigmoid backward mode {c.sigmoid_backward_mode!r}")
+        _check_choice(c.sigmoid_coeff_source, ("current", "sollya"),
+                      f"unsupported sigmoid coefficient source {c.sigmoid_coeff_source!r}")
+        if int(c.sigmoid_degree) not in (2, 3, 4, 5, 6):
+            raise ValueError("sigmoid_degree must be one of 2, 3, 4, 5, or 6")
+        if c.sigmoid_degree_bwd is not None and int(c.sigmoid_degree_bwd) not in (2, 3, 4, 5, 6):
+            raise ValueError("sigmoid_degree_bwd must be one of 2, 3, 4, 5, or 6")
+        poly = c.sigmoid_variant == "poly"
+        if poly and c.sigmoid_poly_backend == "cute":
+            raise ValueError("causal polynomial sigmoid attention requires sigmoid_poly_backend='device'")
+        if poly and c.sigmoid_coeff_source == "sollya" and c.sigmoid_poly_backend != "device":
+            raise ValueError("Sollya sigmoid fits require sigmoid_poly_backend='device'")
+        fwd_freq, fwd_res = _sigmoid_route(c.sigmoid_sfu_freq, c.sigmoid_sfu_res, "forward")
+        bwd_freq, bwd_res = _sigmoid_route(fwd_freq if c.sigmoid_sfu_freq_bwd is None else c.sigmoid_sfu_freq_bwd,
+                                           fwd_res if c.sigmoid_sfu_res_bwd is None else c.sigmoid_sfu_res_bwd, "backward")
+        if poly and (fwd_res != 0 or bwd_res != 0):
+            raise ValueError("sigmoid_variant='poly' must route every forward/backward lane through the polynomial")
+        if not poly and (fwd_res != fwd_freq or bwd_res != bwd_freq):
+            raise ValueError("sigmoid_variant='sfu' must route every forward/backward lane through the SFU")
+        if _is_device_current_poly(c, 2) and c.sigmoid_backward_mode != "algebraic":
+            raise ValueError("bias-aware FlashSigmoid D2 requires sigmoid_backward_mode='algebraic'")
+        if _uses_direct_flash_sigmoid(c):
+            if sequence_length is None:
+                raise ValueError("direct FlashSigmoid D3 requires an explicit sequence_length")
+            if int(sequence_length) != FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH:
+                raise ValueError("direct FlashSigmoid D3/D4 is fitted for sequence length "
+                                 f"{FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH}, got {sequence_length}")
+    return config
+
+
+# ---- this package's attention runtime ----------------------------------------------------------------
+
+@dataclass(frozen=True)
+class SoftcapScoreMod:
+    """Token for `score_mod=`: soft-cap through the packed bf16 tanh polynomial inside the attention kernel."""
+
+    softcap: float
+    degree: int = 4
+    backend: str = "device"
+    coeff_source: str = "current"
+
+
+def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.0, score_mod=None, sigmoid_attention=False,
+                         sigmoid_sfu_freq=16, sigmoid_sfu_res=0, sigmoid_bias=None, sigmoid_poly_backend="device",
+                         sigmoid_degree=3, sigmoid_coeff_source="current", exp2_emu_backend="d3", exp2_emu_freq=None):
+    """(out, lse) for (batch, seq, heads, dim) bf16 tensors on the tcgen05 kernel of this package."""
+    import ctypes
+
+    from .. import _lib
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16:
+        raise RuntimeError("the B200 attention kernel takes bfloat16 q, k, v")
+    if not (q.is_cuda and k.is_cuda and v.is_cuda):
+        raise RuntimeError("q, k, v must be CUDA tensors")
+    if q.stride(-1) != 1 or k.stride(-1) != 1 or v.stride(-1) != 1:
+        raise RuntimeError("the head dimension must be contiguous")
+    batch, seq, q_heads, dim = q.shape
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(dim)
+    log2_n = 12
+    if sigmoid_attention:
+        if not (sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3 and sigmoid_coeff_source == "current"
+                and sigmoid_bias is None and int(sigmoid_sfu_res) == 0):
+            raise NotImplementedError("only the direct piecewise-cubic sigmoid (device, degree 3, current coefficients, "
+                                      "bias -log n, every lane polynomial) is built")
+        if seq & (seq - 1):
+            raise NotImplementedError("direct sigmoid attention needs a power-of-two sequence length")
+        mode, log2_n, cap = 1, seq.bit_length() - 1, 0.0
+    elif score_mod is not None:
+        if not isinstance(score_mod, SoftcapScoreMod) or score_mod.degree != 4 or score_mod.coeff_source != "current":
+            raise NotImplementedError("only the degree-4 'current' tanh soft-cap score-mod is built")
+        mode, cap = 0, float(score_mod.softcap)
+    elif softcap and float(softcap) > 0.0:
+        raise NotImplementedError("native (SFU) tanh soft-cap is not built; use the polynomial score-mod")
+    else:
+        if exp2_emu_freq not in (None, 0):
+            raise NotImplementedError("software exp2 routing inside softmax is not built")
+        mode, cap = 2, 0.0
+    out = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((batch, q_heads, seq), dtype=torch.float32, device=q.device)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    with torch.cuda.device(q.device):
+        _lib.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), batch, seq,
+                  q_heads, k.shape[2], dim, strides(q), strides(k), strides(v), strides(out), mode, int(bool(causal)), scale,
+                  cap, log2_n, status.data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
+    return out, lse
+
+
+def _b200_flash_attn_bwd(*args, **kwargs):
+    raise NotImplementedError("attention backward is not built in this package yet (forward only)")
+
+
+@lru_cache(maxsize=1)
+def b200_runtime() -> Mapping[str, Any]:
+    """The runtime mapping `resolve_fa4_config` binds by default: this package's kernel and its own audits."""
+    from .. import _lib
+    _lib.load()
+
+    def run_polynomial_coefficient_audit():
+        # the constants compiled into the library are the ones pinned by tests/golden/program_table.json
+        return [f"program_table[{_lib.load().fpt_program_count()}]"]
+
+    def audit_polynomial_selection(selections):
+        names = []
+        for family, degree, source in selections:
+            ok = (family, int(degree), source) in (("tanh_fwd", 4, "current"), ("sigmoid_fwd", 3, "current"),
+                                                   ("sigmoid_bwd", 4, "current"))
+            if not ok:
+                raise RuntimeError(f"no audited attention polynomial for {family} degree {degree} source {source}")
+            names.append(f"{family}_d{degree}_{source}")
+        return names
+
+    def audit_attention_handwritten_fast_path(family, degree, source):
+        audit_polynomial_selection((({"flash_sigmoid_direct": "sigmoid_fwd", "flash_sigmoid_direct_with_grad": "sigmoid_bwd",
+                                      "tanh_grad_analytical": "tanh_fwd"}.get(family, family), degree, source),))
+        return f"B200 packed bf16 {family} D{int(degree)} {source}"
+
+    def create_softcap_scoremod_backend(softcap, *, degree, backend, coeff_source):
+        return SoftcapScoreMod(float(softcap), int(degree), backend, coeff_source)
+
+    def create_softcap_scoremod_bwd_backend(softcap, *, degree, backend, backward_mode, coeff_source):
+        return SoftcapScoreMod(float(softcap), int(degree), backend, coeff_source)
+
+    return {"flash_attn_fwd": _b200_flash_attn_fwd, "flash_attn_bwd": _b200_flash_attn_bwd,
+            "run_polynomial_coefficient_audit": run_polynomial_coefficient_audit,
+            "audit_polynomial_selection": audit_polynomial_selection,
+            "audit_attention_handwritten_fast_path": audit_attention_handwritten_fast_path,
+            "create_softcap_scoremod_backend": create_softcap_scoremod_backend,
+            "create_softcap_scoremod_bwd_backend": create_softcap_scoremod_bwd_backend}
+
+
+def _load_fa4_runtime() -> Mapping[str, Any]:
+    try:
+        return b200_runtime()
+    except (ImportError, OSError) as error:
+        raise RuntimeError("The attention runtime is unavailable: build the kernel library with "
+                           "`python -m fast_polynomial_transcendentals_b200.build`.") from error
+
+
+def resolve_fa4_config(config: FA4Config, *, sequence_length: int | None = None,
+                       runtime: Mapping[str, Any] | None = None) -> ResolvedFA4Config:
+    """Validate `config` and bind it to an attention runtime (this package's unless `runtime` is given)."""
+    validate_fa4_config(config, sequence_length=sequence_length)
+    runtime = _load_fa4_runtime() if runtime is None else runtime
+    c = config
+    fwd, bwd = runtime["flash_attn_fwd"], runtime["flash_attn_bwd"]
+    degree = int(c.sigmoid_degree)
+    degree_bwd = degree if c.sigmoid_degree_bwd is None else int(c.sigmoid_degree_bwd)
+    bias_aware_d2 = _is_device_current_poly(c, 2)
+    direct = _uses_direct_flash_sigmoid(c)
+
+    if c.audit_coefficients:
+        audited = list(runtime["run_polynomial_coefficient_audit"]())
+        selections: list[tuple[str, int, str]] = []
+        if c.mode == "softcap" and c.softcap_backend != "native":
+            selections.append(("tanh_fwd", int(c.softcap_degree), c.softcap_coeff_source))
+        if c.mode == "sigmoid_attention" and c.sigmoid_variant == "poly":
+            selections.append(("flash_sigmoid_exp2" if bias_aware_d2 else "sigmoid_fwd", degree, c.sigmoid_coeff_source))
+            if c.sigmoid_backward_mode == "direct":
+                selections.append(("sigmoid_bwd", degree_bwd, c.sigmoid_coeff_source))
+            elif degree_bwd != degree:
+                family = "flash_sigmoid_exp2" if bias_aware_d2 and degree_bwd == 2 else "sigmoid_fwd"
+                selections.append((family, degree_bwd, c.sigmoid_coeff_source))
+        if selections:
+            audited.extend(runtime["audit_polynomial_selection"](tuple(selections)))
+        LOGGER.info("FA4 polynomial audit passed: %s", ", ".join(audited))
+
+    if c.mode == "softmax":
+        route = "automatic" if c.exp2_emu_freq is None else c.exp2_emu_freq
+        return ResolvedFA4Config(
+            mode="softmax", flash_attn_fwd=fwd, flash_attn_bwd=bwd, exp2_emu_backend=c.exp2_emu_backend,
+            exp2_emu_freq=c.exp2_emu_freq, exp2_emu_freq_bwd=c.exp2_emu_freq_bwd, sigmoid_qk_norm=False,
+            implementation_summary=(f"FA4 softmax exp2 backend={c.exp2_emu_backend}, forward_freq={route}, "
+                                    f"backward_freq={c.exp2_emu_freq_bwd}"))
+
+    if c.mode == "softcap":
+        if c.softcap_backend == "native":
+            return ResolvedFA4Config(mode="softcap", flash_attn_fwd=fwd, flash_attn_bwd=bwd, softcap=float(c.softcap),
+                                     sigmoid_qk_norm=False, implementation_summary="FA4 native SFU tanh softcap")
+        paths: list[str] = []
+        if c.softcap_backend == "device":
+            audit = runtime["audit_attention_handwritten_fast_path"]
+            paths.append(audit("tanh_fwd", int(c.softcap_degree), c.softcap_coeff_source))
+            if c.softcap_backward_mode == "analytical":
+                paths.append(audit("tanh_grad_analytical", int(c.softcap_degree), c.softcap_coeff_source))
+        else:
+            paths.append(f"CuTe tanh D{int(c.softcap_degree)} {c.softcap_coeff_source}")
+        score_mod = runtime["create_softcap_scoremod_backend"](
+            c.softcap, degree=c.softcap_degree, backend=c.softcap_backend, coeff_source=c.softcap_coeff_source)
+        score_mod_bwd = runtime["create_softcap_scoremod_bwd_backend"](
+            c.softcap, degree=c.softcap_degree, backend=c.softcap_backend, backward_mode=c.softcap_backward_mode,
+            coeff_source=c.softcap_coeff_source)
+        return ResolvedFA4Config(mode="softcap", flash_attn_fwd=fwd, flash_attn_bwd=bwd, score_mod=score_mod,
+                                 score_mod_bwd=score_mod_bwd, sigmoid_qk_norm=False,
+                                 implementation_summary="; ".join(paths))
+
+    fwd_freq, fwd_res = _sigmoid_route(c.sigmoid_sfu_freq, c.sigmoid_sfu_res, "forward")
+    paths = []
+    if c.sigmoid_variant == "sfu":
+        paths.append("FA4 native SFU sigmoid + algebraic sigmoid gradient")
+    elif bias_aware_d2:
+        paths.append("FA4 bias-aware D2 exp2 polynomial")
+    elif c.sigmoid_poly_backend == "device":
+        audit = runtime["audit_attention_handwritten_fast_path"]
+        paths.append(audit("flash_sigmoid_direct" if direct else "sigmoid_fwd", degree, c.sigmoid_coeff_source))
+        if c.sigmoid_backward_mode == "direct":
+            family = "flash_sigmoid_direct_with_grad" if direct and degree_bwd == 4 else "sigmoid_grad"
+            paths.append(audit(family, degree_bwd, c.sigmoid_coeff_source))
+    return ResolvedFA4Config(
+        mode="sigmoid_attention", flash_attn_fwd=fwd, flash_attn_bwd=bwd, sigmoid_attention=True,
+        sigmoid_sfu_freq=fwd_freq, sigmoid_sfu_res=fwd_res, sigmoid_sfu_freq_bwd=c.sigmoid_sfu_freq_bwd,
+        sigmoid_sfu_res_bwd=c.sigmoid_sfu_res_bwd, sigmoid_use_direct_bwd_poly=(c.sigmoid_backward_mode == "direct"),
+        sigmoid_bias=c.sigmoid_bias, sigmoid_poly_backend=c.sigmoid_poly_backend, sigmoid_degree=degree,
+        sigmoid_degree_bwd=(degree_bwd if c.sigmoid_degree_bwd is not None else None),
+        sigmoid_coeff_source=c.sigmoid_coeff_source, sigmoid_qk_norm=c.sigmoid_qk_norm,
+        implementation_summary="; ".join(paths))
+
+
+def b2_component_configs() -> dict[str, FA4Config]:
+    """The native and the polynomial soft-cap configuration of the B2 component probe."""
+    return {"native": FA4Config(mode="softcap", softcap=30.0, softcap_backend="native", softcap_backward_mode="native"),
+            "polynomial": FA4Config(mode="softcap", softcap=30.0, softcap_backend="device", softcap_degree=4,
+                                    softcap_coeff_source="current", softcap_backward_mode="analytical")}
+
+
+def b3_component_configs(*, sequence_length: int = FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH) -> dict[str, FA4Config]:
+    """The SFU and the direct D3/D4 sigmoid configuration of B3; the fitted pair exists for length 4096 only."""
+    if int(sequence_length) != FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH:
+        raise ValueError(f"B3 direct D3/D4 requires sequence length {FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH}, "
+                         f"got {sequence_length}")
+    configs = {"native": FA4Config(mode="sigmoid_attention", sigmoid_variant="sfu", sigmoid_sfu_freq=16, sigmoid_sfu_res=16,
+                                   sigmoid_qk_norm=True),
+               "polynomial": FA4Config(mode="sigmoid_attention", sigmoid_variant="poly", sigmoid_poly_backend="device",
+                                       sigmoid_degree=3, sigmoid_degree_bwd=4, sigmoid_coeff_source="current",
+                                       sigmoid_backward_mode="direct", sigmoid_sfu_freq=16, sigmoid_sfu_res=0,
+                                       sigmoid_qk_norm=True)}
+    for config in configs.values():
+        validate_fa4_config(config, sequence_length=sequence_length)
+    return configs
+
+
+def softmax_exp2_config(variant: Exp2Variant) -> FA4Config:
+    return validate_fa4_config(FA4Config(mode="softmax", exp2_emu_backend=variant.backend,
+                                         exp2_emu_freq=variant.forward_frequency,
+                                         exp2_emu_freq_bwd=variant.backward_frequency))
+
+
+def b5_component_configs() -> dict[str, FA4Config]:
+    """The three retained routed-exp2 configurations: all-SFU, and two software routes at 1/3 forward, 1/8 backward."""
+    variants = (Exp2Variant("native", "d3", 0, 0), Exp2Variant("pwl2_safe_f16", "pwl2_safe_f16", 12, 32),
+                Exp2Variant("d2_safe", "d2_safe", 12, 32))
+    return {v.name: softmax_exp2_config(v) for v in variants}
+
+
+_FORWARD_KEYS = ("softcap", "sigmoid_attention", "sigmoid_sfu_freq", "sigmoid_sfu_res", "sigmoid_sfu_freq_bwd",
+                 "sigmoid_sfu_res_bwd", "sigmoid_use_direct_bwd_poly", "sigmoid_bias", "sigmoid_poly_backend",
+                 "sigmoid_degree", "sigmoid_degree_bwd", "sigmoid_coeff_source", "exp2_emu_backend", "exp2_emu_freq",
+                 "exp2_emu_freq_bwd", "score_mod", "score_mod_bwd", "flash_attn_fwd", "flash_attn_bwd")
+
+
+class _FA4Function(torch.autograd.Function):
+    """Forward / backward through the bound runtime; argument order follows the reference's function."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, softmax_scale, causal, *settings):
+        s = dict(zip(_FORWARD_KEYS, settings))
+        for key, fallback in (("sigmoid_sfu_freq_bwd", "sigmoid_sfu_freq"), ("sigmoid_sfu_res_bwd", "sigmoid_sfu_res"),
+                              ("sigmoid_degree_bwd", "sigmoid_degree")):
+            if s[key] is None:
+                s[key] = s[fallback]
+        effective_softcap = s["softcap"] if s["score_mod"] is None else 0.0
+        out, lse = s["flash_attn_fwd"](
+            q, k, v, softmax_scale=softmax_scale, causal=causal, softcap=effective_softcap, score_mod=s["score_mod"],
+            sigmoid_attention=s["sigmoid_attention"], sigmoid_sfu_freq=s["sigmoid_sfu_freq"],
+            sigmoid_sfu_res=s["sigmoid_sfu_res"], sigmoid_bias=s["sigmoid_bias"],
+            sigmoid_poly_backend=s["sigmoid_poly_backend"], sigmoid_degree=s["sigmoid_degree"],
+            sigmoid_coeff_source=s["sigmoid_coeff_source"], exp2_emu_backend=s["exp2_emu_backend"],
+            exp2_emu_freq=s["exp2_emu_freq"])
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.softmax_scale, ctx.causal, ctx.softcap, ctx.settings = softmax_scale, causal, effective_softcap, s
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        s = ctx.settings
+        direct = s["sigmoid_use_direct_bwd_poly"]
+        dq, dk, dv = s["flash_attn_bwd"](
+            q, k, v, out, dout.contiguous(), lse, ctx.softmax_scale, ctx.causal, ctx.softcap, score_mod=s["score_mod"],
+            score_mod_bwd=s["score_mod_bwd"], sigmoid_attention=s["sigmoid_attention"], sigmoid_bias=s["sigmoid_bias"],
+            sigmoid_sfu_freq=s["sigmoid_sfu_freq_bwd"], sigmoid_sfu_res=s["sigmoid_sfu_res_bwd"],
+            sigmoid_use_direct_bwd_poly=direct, sigmoid_poly_backend=s["sigmoid_poly_backend"],
+            sigmoid_degree=(s["sigmoid_degree"] if direct else s["sigmoid_degree_bwd"]),
+            sigmoid_gradient_degree=s["sigmoid_degree_bwd"], sigmoid_coeff_source=s["sigmoid_coeff_source"],
+            exp2_emu_backend=s["exp2_emu_backend"], exp2_emu_freq=s["exp2_emu_freq_bwd"])
+        return (dq, dk, dv, None, None, *([None] * len(_FORWARD_KEYS)))
+
+
+def _fa4(q, k, v, *, softmax_scale: float | None, causal: bool, config: ResolvedFA4Config) -> torch.Tensor:
+    return _FA4Function.apply(q, k, v, softmax_scale, causal, *(getattr(config, key) for key in _FORWARD_KEYS))
+
+
+class FA4AttentionWrapper(nn.Module):
+    """Attention module over (batch, heads, sequence, dim) tensors; always causal, like the reference's wrapper."""
+
+    def __init__(self, config: ResolvedFA4Config, head_dim: int):
+        super().__init__()
+        self.config = config
+        self.head_dim = int(head_dim)
+        with_norm = config.sigmoid_attention and config.sigmoid_qk_norm
+        self.q_norm: nn.Module | None = nn.RMSNorm(self.head_dim) if with_norm else None
+        self.k_norm: nn.Module | None = nn.RMSNorm(self.head_dim) if with_norm else None
+
+    def forward(self, q, k, v, *, score_mod: Callable[..., Any] | None = None, scale: float | None = None, **kwargs: Any):
+        if score_mod is not None:
+            raise NotImplementedError("external score_mod is unsupported; select it in FA4Config")
+        kwargs.pop("enable_gqa", None)
+        if kwargs:
+            raise TypeError("unsupported FA4 attention kwargs: " + ", ".join(sorted(kwargs)))
+        if self.q_norm is not None:
+            q, k = self.q_norm(q), self.k_norm(k)
+        dtype = torch.get_autocast_dtype("cuda") if torch.is_autocast_enabled("cuda") else q.dtype
+        to_kernel = lambda t: t.transpose(1, 2).contiguous().to(dtype)
+        out = _fa4(to_kernel(q), to_kernel(k), to_kernel(v), softmax_scale=scale, causal=True, config=self.config)
+        return out.transpose(1, 2).contiguous()
+
+
+def build_fa4_module(config: FA4Config, *, head_dim: int, sequence_length: int | None = None) -> FA4AttentionWrapper:
+    return FA4AttentionWrapper(resolve_fa4_config(config, sequence_length=sequence_length), head_dim=head_dim)
+
+
+def patch_attention_modules(model: nn.Module, config: ResolvedFA4Config) -> int:
+    """Put a wrapper into every module that has both `inner_attention` and `head_dim`; returns how many."""
+    patched = 0
+    for module in model.modules():
+        if not (hasattr(module, "inner_attention") and hasattr(module, "head_dim")):
+            continue
+        if isinstance(module.inner_attention, FA4AttentionWrapper):
+            continue
+        wrapper = FA4AttentionWrapper(config=config, head_dim=module.head_dim)
+        parameter = next(module.parameters(), None)
+        if parameter is not None:
+            wrapper = (wrapper.to(dtype=parameter.dtype) if parameter.device.type == "meta"
+                       else wrapper.to(device=parameter.device, dtype=parameter.dtype))
+        module.inner_attention = wrapper
+        if hasattr(module, "use_flex_attn"):
+            module.use_flex_attn = False
+        if hasattr(module, "attn_score_modifier"):
+            module.attn_score_modifier = None
+        patched += 1
+    return patched
+
+
+__all__ = ["DEFAULT_EXP2_VARIANTS", "Exp2Variant", "FA4AttentionWrapper", "FA4Config",
+           "FLASH_SIGMOID_DIRECT_SEQUENCE_LENGTH", "ResolvedFA4Config", "SUPPORTED_EXP2_BACKENDS", "SoftcapScoreMod",
+           "b200_runtime", "b2_component_configs", "b3_component_configs", "b5_component_configs", "build_fa4_module",
+           "parse_exp2_frequency", "parse_exp2_variants", "patch_attention_modules", "resolve_fa4_config",
+           "softmax_exp2_config", "validate_fa4_config"]

@@ -466,3 +466,89 @@ def b3_sigmoid_direct(scores, log2_n: int = 12, with_grad: bool = False):
     _call("fpt_b3_sigmoid_direct", scores, prob.data_ptr(), grad.data_ptr() if with_grad else None, scores.data_ptr(),
           scores.numel(), int(scores.dtype == torch.float32), int(log2_n))
     return (prob, grad) if with_grad else prob
+
+
+# ---- differentiable entry points (reference: C++ autograd Functions, spline_ops.cpp:1933-2205) ---
+
+class _UnaryAutograd(torch.autograd.Function):
+    """y = F(x); backward through the polynomial derivative program of the same degree and source."""
+
+    @staticmethod
+    def forward(ctx, x, function, degree, source):
+        ctx.save_for_backward(x)
+        ctx.spec = (function, degree, source)
+        return _unary(x, function, FWD, degree, source)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (x,) = ctx.saved_tensors
+        function, degree, source = ctx.spec
+        return _binary(grad_out.contiguous(), x, function, degree, source), None, None, None
+
+
+class _AlgebraicAutograd(torch.autograd.Function):
+    """sigmoid / tanh with the gradient computed from the saved output."""
+
+    @staticmethod
+    def forward(ctx, x, function):
+        y = _unary(x, function, FWD, 3)
+        ctx.save_for_backward(y)
+        ctx.function = function
+        return y
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (y,) = ctx.saved_tensors
+        return _alg(grad_out.contiguous(), y, ctx.function), None
+
+
+class _SwishMulAutograd(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gate, up, degree, source):
+        ctx.save_for_backward(gate, up)
+        ctx.spec = (degree, source)
+        return swish_mul_fwd_variant(gate, up, degree, source)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        gate, up = ctx.saved_tensors
+        grad_gate, grad_up = swish_mul_bwd_variant(grad_out.contiguous(), gate, up, *ctx.spec)
+        return grad_gate, grad_up, None, None
+
+
+def sigmoid_ag(x):
+    return _AlgebraicAutograd.apply(x, "sigmoid")
+
+
+def tanh_ag(x):
+    return _AlgebraicAutograd.apply(x, "tanh")
+
+
+def swish_ag(x):
+    """Forward D3, backward D4: the defaults of swish_fwd / swish_bwd."""
+    class _Mixed(torch.autograd.Function):
+        @staticmethod
+        def forward(ctx, t):
+            ctx.save_for_backward(t)
+            return swish_fwd(t)
+
+        @staticmethod
+        def backward(ctx, grad_out):
+            (t,) = ctx.saved_tensors
+            return swish_bwd(grad_out.contiguous(), t)
+    return _Mixed.apply(x)
+
+
+def swish_ag_variant(x, degree: int, coeff_source_id: int):
+    _check_input(x, "x")
+    return _UnaryAutograd.apply(x, "swish", int(degree), _source(coeff_source_id, x))
+
+
+def gelu_ag_variant(x, degree: int, coeff_source_id: int):
+    _check_input(x, "x")
+    return _UnaryAutograd.apply(x, "gelu", int(degree), _source(coeff_source_id, x))
+
+
+def swish_mul_ag_variant(gate, up, degree: int, coeff_source_id: int):
+    _check_input(gate, "gate")
+    return _SwishMulAutograd.apply(gate, up, int(degree), _source(coeff_source_id, gate))

@@ -1,0 +1,118 @@
+"""GPU: the op surface, the dispatcher operators with autograd, the activation resolver and the attention module."""
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def test_cross_path_equalities(cuda):
+    """Bit-exact agreement between paths that must compute the same thing (reference test_spline_ops.py:23-38, 57-81,
+    115-138, 186-204): dispatcher op == direct op (forward and both gradients), packed == unpacked, fused == split."""
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_compile, spline_ops
+    torch.manual_seed(0)
+    for dtype in (torch.bfloat16, torch.float16):
+        gate = (torch.randn(64, 512, device=cuda) * 2).to(dtype).requires_grad_(True)
+        up = torch.randn(64, 512, device=cuda).to(dtype).requires_grad_(True)
+        go = torch.randn(64, 512, device=cuda).to(dtype)
+        for degree in (3, 4, 5, 6):
+            fused = spline_compile.make_spline_silu_mul(degree)(gate, up)
+            direct = spline_ops.swish_mul_fwd_variant(gate.detach(), up.detach(), degree, 0)
+            assert torch.equal(fused, direct)
+            gg, gu = torch.autograd.grad(fused, (gate, up), go)
+            dgg, dgu = spline_ops.swish_mul_bwd_variant(go, gate.detach(), up.detach(), degree, 0)
+            assert torch.equal(gg, dgg) and torch.equal(gu, dgu)
+            ag = spline_ops.swish_mul_ag_variant(gate, up, degree, 0)
+            agg, agu = torch.autograd.grad(ag, (gate, up), go)
+            assert torch.equal(ag, direct) and torch.equal(agg, dgg) and torch.equal(agu, dgu)
+            packed = torch.cat([gate.detach(), up.detach()], dim=-1).requires_grad_(True)
+            out_p = spline_compile.make_spline_silu_packed(degree)(packed)
+            assert torch.equal(out_p, direct)
+            (gp,) = torch.autograd.grad(out_p, packed, go)
+            assert torch.equal(gp[:, :512], dgg) and torch.equal(gp[:, 512:], dgu)
+        native = spline_compile.make_native_silu_packed()(torch.cat([gate.detach(), up.detach()], dim=-1))
+        want = torch.nn.functional.silu(gate.detach().float()).to(dtype) * up.detach()
+        assert float((native.float() - want.float()).abs().max()) <= 0.07
+
+
+def test_unary_autograd_and_defaults(cuda):
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_compile, spline_ops
+    x = (torch.randn(4096, device=cuda) * 3).to(torch.float16).requires_grad_(True)
+    go = torch.randn(4096, device=cuda).to(torch.float16)
+    y = spline_compile.spline_silu(x)
+    assert torch.equal(y, spline_ops.swish_fwd_d3(x.detach()))
+    (g,) = torch.autograd.grad(y, x, go)
+    assert torch.equal(g, spline_ops.swish_bwd_d4(go, x.detach()))       # default backward degree is 4
+    s = spline_compile.spline_sigmoid(x)
+    (gs,) = torch.autograd.grad(s, x, go)
+    assert torch.equal(gs, spline_ops.sigmoid_bwd_alg(go, s.detach()))   # algebraic gradient from the saved output
+    t = spline_ops.tanh_ag(x)
+    (gt,) = torch.autograd.grad(t, x, go)
+    assert torch.equal(gt, spline_ops.tanh_bwd_alg(go, t.detach()))
+    ge = spline_compile.make_spline_gelu(4)(x)
+    assert torch.equal(ge, spline_ops.gelu_fwd_d4(x.detach()))
+    err = (spline_ops.sigmoid_fwd_d3((torch.randn(1 << 20, device=cuda) * 3).half()).float()
+           - torch.sigmoid((torch.randn(1, device=cuda) * 0).float())).abs()   # shape check only
+    assert err.numel() == 1 << 20
+
+
+def test_error_behaviour_matches_torch_check(cuda):
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_ops
+    x = torch.randn(16, 16, device=cuda).half()
+    with pytest.raises(RuntimeError, match="must be contiguous"):
+        spline_ops.sigmoid_fwd_d3(x.t())
+    with pytest.raises(RuntimeError, match="float16 or bfloat16"):
+        spline_ops.sigmoid_fwd_d3(x.float())
+    with pytest.raises(RuntimeError, match="same dtype"):
+        spline_ops.swish_mul_fwd_variant(x, x.bfloat16(), 3, 0)
+    with pytest.raises(RuntimeError, match="only support coeff_source=current"):
+        spline_ops.swish_fwd_variant(x, 3, 1)
+    with pytest.raises(RuntimeError, match="Unsupported"):
+        spline_ops.swish_fwd_variant(x, 7, 0)
+    with pytest.raises(RuntimeError, match="last dimension must be even"):
+        spline_ops.swish_mul_packed_fwd_variant(torch.zeros(4, 7, device=cuda).half(), 3, 0)
+    assert spline_ops.swish_mul_packed_fwd_variant(torch.zeros(0, 8, device=cuda).half(), 3, 0).shape == (0, 4)
+    with pytest.raises(RuntimeError, match="multiple of eight"):
+        spline_ops.rope_apply_fixed_half_turn_d5_d6_fp16(torch.zeros(1, 2, 1, 12, device=cuda).half(),
+                                                         torch.zeros(1, 2, 1, 12, device=cuda).half(),
+                                                         torch.zeros(6, dtype=torch.int32, device=cuda))
+
+
+def test_resolved_activations_run(cuda):
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_ops
+    from fast_polynomial_transcendentals_b200.sfu_repro import activations
+    packed = (torch.randn(32, 2816, device=cuda) * 1.5).to(torch.bfloat16)
+    _, act = activations.resolve_mlp_activation_packed_impl("spline_silu_compile", degree=3)
+    assert torch.equal(act(packed), spline_ops.swish_mul_packed_fwd_variant(packed, 3, 0))
+    _, mul = activations.resolve_mlp_activation_mul_impl("spline_silu", degree=3)
+    g, u = packed[:, :1408], packed[:, 1408:]
+    assert torch.equal(mul(g, u), spline_ops.swish_mul_fwd_variant(g.contiguous(), u.contiguous(), 3, 0))
+
+
+def test_attention_module_forward(cuda, oracle):
+    """FA4AttentionWrapper over (B,H,S,D): soft-cap polynomial and sigmoid modes against the fp32 oracle."""
+    import torch
+    from fast_polynomial_transcendentals_b200.sfu_repro import fa4
+    B, Hq, Hk, S, D = 1, 4, 2, 512, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(3)
+    q = torch.randn(B, Hq, S, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16)
+    module = fa4.build_fa4_module(fa4.b2_component_configs()["polynomial"], head_dim=D).to(cuda)
+    out = module(q, k, v)
+    assert out.shape == (B, Hq, S, D)
+    bits = lambda t: t.transpose(1, 2).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+    rows = np.arange(0, S, 7)
+    want = oracle.attention_rows(bits(q), bits(k), bits(v), 0, 3, rows, oracle.ATTN_SOFTCAP_TANH, True, 1 / math.sqrt(D), 30.0)
+    assert float(np.abs(out[0, 3, rows].float().cpu().numpy() - want).max()) < 2e-2
+    with pytest.raises(NotImplementedError):
+        module(q, k, v, score_mod=lambda s: s)
+    # sigmoid attention: the deployed pair exists for 4096 keys only, as in the reference
+    with pytest.raises(ValueError, match="4096"):
+        fa4.build_fa4_module(fa4.b3_component_configs()["polynomial"], head_dim=D, sequence_length=S)
