@@ -36,6 +36,7 @@ SIGNATURES: dict[str, list] = {
     "fpt_swish_mul_packed_bwd": [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_b3_sigmoid_direct": [_vp, _vp, _vp, _i64, _int, _int, _vp],
     "fpt_exp2_fraction": [_vp, _vp, _i64, _int, _int, _vp],
+    "fpt_exp2_poly_f32": [_vp, _vp, _i64, _vp],
     "fpt_sincos": [_vp, _vp, _i64, _int, _int, _vp],
     "fpt_rope_table": [_vp, _vp, _i64, _i64, _int, _int, _vp],
     "fpt_rope_apply": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],

@@ -4,8 +4,9 @@
 // sequence in tiles of 128 keys:
 //   warp 0        TMA producer: Q once, then K and V tiles into a 2-stage shared-memory ring (no multicast)
 //   warp 1        single-thread UMMA issuer: S = Q K^T into tensor memory, O += P V with P read from tensor memory
-//   warps 2..5    softmax / score-mod warpgroup of slot 0 (thread = one query row)
-//   warps 6..9    the same for slot 1
+//   warps 2..3    idle (they complete the first warpgroup, which gives most of its registers away)
+//   warps 4..7    softmax / score-mod warpgroup of slot 0 (thread = one query row = one tensor-memory lane)
+//   warps 8..11   the same for slot 1
 // Tensor memory (512 columns): S[slot] 128 fp32 columns each, O[slot] 128 fp32 columns each; the bf16 P tile of a
 // slot overwrites the first 64 columns of its S tile once the row has been read into registers.  The two slots are
 // interleaved on the tensor pipe so that one slot's matrix products run under the other slot's score-mod.
@@ -32,7 +33,7 @@ constexpr int kSlots = 2;
 constexpr int kStages = 2;
 constexpr uint32_t kPanel = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
 constexpr uint32_t kTileBytes = 2 * kPanel;   // one 128 x 128 bf16 tile
-constexpr int kThreads = 32 * (2 + 4 * kSlots);
+constexpr int kThreads = 128 * (1 + kSlots);  // warpgroup 0: producer + issuer; one warpgroup per slot
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.0f;     // lazy rescale: tolerate exp2 arguments up to +8
 
@@ -59,9 +60,67 @@ struct AttnParams {
     B3Words b3;
 };
 
+// Share of the soft-max exponentials evaluated by the fp32 cubic on the FMA pipe instead of the special-function
+// unit: pairs whose index modulo DEN is below NUM.  The unit delivers 16 results per clock and SM, which for a
+// 128 x 128 tile is exactly as long as the two tensor-core products of that tile, so without the split the
+// exponentials alone fill the whole time the tensor pipe leaves to the soft-max.
+#ifndef FPT_ATTN_POLY_NUM
+#define FPT_ATTN_POLY_NUM 0
+#endif
+#ifndef FPT_ATTN_POLY_DEN
+#define FPT_ATTN_POLY_DEN 2
+#endif
+
+// Optional timeline for tuning builds (-DFPT_ATTN_TRACE): block (0,0,0) stores (tag, SM clock) pairs behind the
+// status word, 4096 words per traced warp; the caller must then pass a status buffer of 64 KiB.
+#ifdef FPT_ATTN_TRACE
+#define FPT_TRACE(slot, tag)                                                                              \
+    do {                                                                                                  \
+        if (trace_on && lane == 0 && trace_n < 2046) {                                                    \
+            uint32_t* t_ = p.status + 64 + (slot) * 4096;                                                 \
+            t_[2 + trace_n] = uint32_t(tag);                                                              \
+            t_[3 + trace_n] = uint32_t(clock64());                                                        \
+            trace_n += 2;                                                                                 \
+            t_[0] = uint32_t(trace_n);                                                                    \
+        }                                                                                                 \
+    } while (0)
+#else
+#define FPT_TRACE(slot, tag) do { } while (0)
+#endif
+
 enum : uint32_t { kWhereQ = 1, kWhereKEmpty, kWhereVEmpty, kWhereKFull, kWhereVFull, kWherePFull, kWhereSFull, kWherePvDone };
 
 __device__ __forceinline__ float ex2(float x) { return mufu_ex2(x); }
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+// bf16x2( a*scale, b*scale ) from two fp32 bit patterns: one packed fp32 multiply, one conversion
+__device__ __forceinline__ uint32_t scale_pack_bf16x2(uint32_t a, uint32_t b, float scale) {
+    uint32_t d;
+    asm("{\n\t.reg .b64 v, s, r;\n\t.reg .b32 lo, hi;\n\t"
+        "mov.b64 v, {%1, %2};\n\tmov.b64 s, {%3, %3};\n\t"
+        "mul.rn.f32x2 r, v, s;\n\tmov.b64 {lo, hi}, r;\n\t"
+        "cvt.rn.bf16x2.f32 %0, hi, lo;\n\t}"
+        : "=r"(d) : "r"(a), "r"(b), "f"(scale));
+    return d;
+}
+// (o0, o1) = (a0, a1) * m + c
+__device__ __forceinline__ void fma_f32x2(float a0, float a1, float m, float c, float& o0, float& o1) {
+    asm("{\n\t.reg .b64 v, s, t, r;\n\t"
+        "mov.b64 v, {%2, %3};\n\tmov.b64 s, {%4, %4};\n\tmov.b64 t, {%5, %5};\n\t"
+        "fma.rn.f32x2 r, v, s, t;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(o0), "=f"(o1) : "f"(a0), "f"(a1), "f"(m), "f"(c));
+}
+// (acc0, acc1) += (e0, e1)
+__device__ __forceinline__ void add_f32x2(float& acc0, float& acc1, float e0, float e1) {
+    asm("{\n\t.reg .b64 a, e;\n\t"
+        "mov.b64 a, {%0, %1};\n\tmov.b64 e, {%2, %3};\n\t"
+        "add.rn.f32x2 a, a, e;\n\tmov.b64 {%0, %1}, a;\n\t}"
+        : "+f"(acc0), "+f"(acc1) : "f"(e0), "f"(e1));
+}
 
 template <int MODE>
 __global__ void __launch_bounds__(kThreads, 1)
@@ -85,6 +144,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     }
     const int n_max = max(n_tiles[0], n_tiles[1]);
     volatile uint32_t* abort_flag = &sm.abort_flag;
+#ifdef FPT_ATTN_TRACE
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8);
+    int trace_n = 0;
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < kSlots; ++s) {
@@ -117,9 +180,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t tmem = sm.tmem_base;
     const bool skip = sm.abort_flag != 0u;
 
-    if (skip) {
-        // fall through to the teardown
-    } else if (warp == 0) {
+    // Register budget: 128 x 80 + 256 x 208 = 63488 of the SM's 65536.  Each setmaxnreg sits at the head of the branch
+    // it governs, so that the assembler knows which limit holds for which role.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+      if (skip || warp >= 2) {
+        // warps 2 and 3 only hold registers for the others; fall through to the teardown
+      } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer
         if (lane == 0) {
             for (int s = 0; s < kSlots; ++s) {
@@ -144,27 +211,33 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tma_load_4d(sm.v[st] + kPanel, &map_v, &sm.v_full[st], 64, j * kTileN, hk, b);
             }
         }
-    } else if (warp == 1) {
+      } else {
         // ------------------------------------------------------------------ UMMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileM, kTileN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileM, kHeadDim, 0, 1);
+            // Every descriptor is "low word of the tile base + a compile-time constant" with one shared high word, so
+            // an issue costs the thread a few integer instructions and the tensor pipe, not the thread, sets the pace.
+            constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            static_assert(kSlots == 2 && kStages == 2, "the selects below assume two slots and two stages");
+            const uint32_t q_lo0 = umma_smem_desc_lo(smem_u32(sm.q[0]), 16), q_lo1 = umma_smem_desc_lo(smem_u32(sm.q[1]), 16);
+            const uint32_t k_lo0 = umma_smem_desc_lo(smem_u32(sm.k[0]), 16), k_lo1 = umma_smem_desc_lo(smem_u32(sm.k[1]), 16);
+            const uint32_t v_lo0 = umma_smem_desc_lo(smem_u32(sm.v[0]), kPanel), v_lo1 = umma_smem_desc_lo(smem_u32(sm.v[1]), kPanel);
             auto issue_qk = [&](int s, int st) {
-                const uint32_t qa = smem_u32(sm.q[s]), ka = smem_u32(sm.k[st]);
+                const uint32_t qa = s ? q_lo1 : q_lo0, ka = st ? k_lo1 : k_lo0, d = tmem + uint32_t(s) * 128u;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
-                    const uint32_t off = uint32_t(kk >> 2) * kPanel + uint32_t(kk & 3) * 32u;
-                    umma_ss(tmem + uint32_t(s) * 128u, umma_smem_desc(qa + off, 16, 1024), umma_smem_desc(ka + off, 16, 1024),
-                            idesc_qk, kk > 0);
+                    constexpr uint32_t unit = 16;   // descriptor addresses count 16-byte units
+                    const uint32_t off = (uint32_t(kk >> 2) * kPanel + uint32_t(kk & 3) * 32u) / unit;
+                    umma_ss_words(d, qa + off, ka + off, desc_hi, idesc_qk, kk > 0);
                 }
                 umma_commit(&sm.s_full[s]);
             };
             auto issue_pv = [&](int s, int st, bool first) {
-                const uint32_t va = smem_u32(sm.v[st]);
+                const uint32_t va = st ? v_lo1 : v_lo0, d = tmem + 256u + uint32_t(s) * 128u, a = tmem + uint32_t(s) * 128u;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)
-                    umma_ts(tmem + 256u + uint32_t(s) * 128u, tmem + uint32_t(s) * 128u + 8u * kk,
-                            umma_smem_desc(va + uint32_t(kk) * 2048u, kPanel, 1024), idesc_pv, (!first) || kk > 0);
+                    umma_ts_words(d, a + 8u * kk, va + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
                 umma_commit(&sm.pv_done[s]);
             };
             bool ok = true;
@@ -185,26 +258,35 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 const uint32_t ph_next = uint32_t((j + 1) / kStages) & 1u;
                 for (int s = 0; s < kSlots && ok; ++s) {
                     if (j >= n_tiles[s]) continue;
-                    ok = mbar_wait(&sm.v_full[st], ph, abort_flag, p.status, kWhereVFull) &&
-                         mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    ok = mbar_wait(&sm.v_full[st], ph, abort_flag, p.status, kWhereVFull);
+                    FPT_TRACE(2, 31);
+                    ok = ok && mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
                     if (!ok) break;
                     tc_fence_after_sync();
+                    FPT_TRACE(2, 10 + s);            // P of slot s seen
                     issue_pv(s, st, j == 0);
+                    FPT_TRACE(2, 12);
                     if (j + 1 < n_tiles[s]) {
                         ok = mbar_wait(&sm.k_full[st_next], ph_next, abort_flag, p.status, kWhereKFull);
                         if (!ok) break;
                         tc_fence_after_sync();
+                        FPT_TRACE(2, 13);
                         issue_qk(s, st_next);   // executes after the P V product above: same issuing thread
+                        FPT_TRACE(2, 20 + s);        // both products of slot s issued
                     }
                 }
                 if (!ok) break;
                 umma_commit(&sm.v_empty[st]);
                 if (j + 1 < n_max) umma_commit(&sm.k_empty[st_next]);
+                FPT_TRACE(2, 30);
             }
         }
+      }
     } else {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+      if (!skip) {
         // ------------------------------------------------------------------ softmax / score-mod warpgroups
-        const int s = (warp - 2) >> 2;
+        const int s = (warp - 4) >> 2;
         const int row_in_tile = 32 * (warp & 3) + lane;          // tensor-memory lane owned by this thread
         const int row = m0 + s * kTileM + row_in_tile;
         const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
@@ -217,25 +299,24 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const float softcap_out = p.softcap * kLog2e;           // tanh -> log2-domain score
         const float plain_scale = p.scale * kLog2e;
         for (int j = 0; j < n && ok; ++j) {
+            FPT_TRACE(s, 1);                         // start waiting for S
             ok = mbar_wait(&sm.s_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWhereSFull);
             if (!ok) break;
             tc_fence_after_sync();
-            float sc[kTileN];
+            FPT_TRACE(s, 2);                         // S ready
+            uint32_t pw[kTileN / 2];
+            const bool diagonal = p.causal && j == n - 1;
+            if constexpr (MODE == 1) {
+                // the whole S row: four tensor-memory loads in flight, one wait
+                uint32_t sr[kTileN];
 #pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                tmem_ld_32x32b_x32(t_s + c * 32, v);
+                for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
                 tmem_ld_wait();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) sc[c * 32 + i] = __uint_as_float(v[i]);
-            }
-            uint32_t pw[kTileN / 2];
-            if constexpr (MODE == 1) {
-#pragma unroll
                 for (int i = 0; i < kTileN / 2; ++i) {
-                    const uint32_t x = Sfu<kBf16>::pack(sc[2 * i] * p.scale, sc[2 * i + 1] * p.scale);
-                    uint32_t pr = b3_direct(x, p.b3);
-                    if (p.causal && j == n - 1) {  // keys beyond the diagonal contribute nothing
+                    const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
+                    uint32_t pr = b3_direct_select_late(x, p.b3);
+                    if (diagonal) {  // keys beyond the diagonal contribute nothing
                         const int col = j * kTileN + 2 * i;
                         if (col > row) pr &= 0xffff0000u;
                         if (col + 1 > row) pr &= 0x0000ffffu;
@@ -243,52 +324,84 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     pw[i] = pr;
                 }
             } else {
-                if constexpr (MODE == 0) {
+                // val[i] * mul is the score in log2 units: val = tanh polynomial (mode 0) or the raw score (mode 2).
+                // Common path: no maximum scan.  An exponential above 2^8 (the lazy-rescale limit) would push the tile
+                // sum above 2^8 too, so the sum tells when the reference has to move; then the row is read again from
+                // tensor memory (P has not been written yet), its maximum taken, O and the running sum rescaled.
+                const float mul = MODE == 0 ? softcap_out : plain_scale;
+                bool with_max = j == 0;
+                float sum_lo, sum_hi;
+#pragma unroll 1
+                for (;;) {
+                    uint32_t sr[kTileN];
 #pragma unroll
-                    for (int i = 0; i < kTileN / 2; ++i) {
-                        const uint32_t x = Sfu<kBf16>::pack(sc[2 * i] * softcap_in, sc[2 * i + 1] * softcap_in);
-                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
-                        sc[2 * i] = Sfu<kBf16>::lo(t) * softcap_out;
-                        sc[2 * i + 1] = Sfu<kBf16>::hi(t) * softcap_out;
-                    }
-                } else {
+                    for (int c = 0; c < 4; ++c)
+                        tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
+                    tmem_ld_wait();
+                    FPT_TRACE(s, 5);                 // S in registers
+                    if constexpr (MODE == 0) {
 #pragma unroll
-                    for (int i = 0; i < kTileN; ++i) sc[i] *= plain_scale;
-                }
-                if (p.causal && j == n - 1) {
-#pragma unroll
-                    for (int i = 0; i < kTileN; ++i)
-                        if (j * kTileN + i > row) sc[i] = -INFINITY;
-                }
-                float tile_max = sc[0];
-#pragma unroll
-                for (int i = 1; i < kTileN; ++i) tile_max = fmaxf(tile_max, sc[i]);
-                if (tile_max > row_max + kRescaleThreshold || j == 0) {
-                    const float new_max = fmaxf(row_max, tile_max);
-                    if (j > 0) {  // bring the running sum and the accumulator to the new reference
-                        const float f = ex2(row_max - new_max);
-                        row_sum *= f;
-#pragma unroll
-                        for (int c = 0; c < 4; ++c) {
-                            uint32_t v[32];
-                            tmem_ld_32x32b_x32(t_o + c * 32, v);
-                            tmem_ld_wait();
-#pragma unroll
-                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                            tmem_st_32x32b_x32(t_o + c * 32, v);
+                        for (int i = 0; i < kTileN / 2; ++i) {
+                            const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in);
+                            const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
+                            sr[2 * i] = t << 16;              // bf16 -> fp32 is a shift
+                            sr[2 * i + 1] = t & 0xffff0000u;
                         }
                     }
-                    row_max = new_max;
-                }
-                float local = 0.0f;
+                    if (diagonal) {
 #pragma unroll
-                for (int i = 0; i < kTileN / 2; ++i) {
-                    const float e0 = ex2(sc[2 * i] - row_max), e1 = ex2(sc[2 * i + 1] - row_max);
-                    local += e0 + e1;
-                    pw[i] = Sfu<kBf16>::pack(e0, e1);
+                        for (int i = 0; i < kTileN; ++i)
+                            if (j * kTileN + i > row) sr[i] = 0xff800000u;  // -inf
+                    }
+                    if (with_max) {
+                        float m3 = __uint_as_float(sr[0]);
+#pragma unroll
+                        for (int i = 1; i + 1 < kTileN; i += 2)
+                            m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+                        const float new_max = fmaxf(row_max, fmaxf(m3, __uint_as_float(sr[kTileN - 1])) * mul);
+                        if (j > 0 && new_max > row_max) {
+                            const float f = ex2(row_max - new_max);
+                            row_sum *= f;
+#pragma unroll 1
+                            for (int c = 0; c < 4; ++c) {
+                                uint32_t v[32];
+                                tmem_ld_32x32b_x32(t_o + c * 32, v);
+                                tmem_ld_wait();
+#pragma unroll
+                                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+                                tmem_st_32x32b_x32(t_o + c * 32, v);
+                            }
+                        }
+                        row_max = new_max;
+                    }
+                    sum_lo = sum_hi = 0.0f;
+                    const float neg_max = -row_max;
+#ifdef FPT_ATTN_EXPERIMENT   // timing experiments only: wrong results on purpose
+#pragma unroll
+                    for (int i = 0; i < kTileN / 2; ++i) pw[i] = (sr[2 * i] ^ sr[2 * i + 1]) & 0x3f003f00u;
+                    sum_lo = 1.0f;
+                    break;
+#endif
+#pragma unroll
+                    for (int i = 0; i < kTileN / 2; ++i) {
+                        float a0, a1;
+                        fma_f32x2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), mul, neg_max, a0, a1);
+                        float e0, e1;
+                        if ((i % FPT_ATTN_POLY_DEN) < FPT_ATTN_POLY_NUM) {
+                            exp2_poly3_x2(a0, a1, e0, e1);   // FMA pipe
+                        } else {
+                            e0 = ex2(a0);                    // special-function unit
+                            e1 = ex2(a1);
+                        }
+                        add_f32x2(sum_lo, sum_hi, e0, e1);
+                        pw[i] = Sfu<kBf16>::pack(e0, e1);
+                    }
+                    if (with_max || sum_lo + sum_hi <= 256.0f) break;
+                    with_max = true;
                 }
-                row_sum += local;
+                row_sum += sum_lo + sum_hi;
             }
+            FPT_TRACE(s, 3);                         // probabilities computed
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
@@ -300,6 +413,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full[s]);
+            FPT_TRACE(s, 4);                         // P handed over
         }
         if (ok && n > 0) {
             ok = mbar_wait(&sm.pv_done[s], uint32_t(n - 1) & 1u, abort_flag, p.status, kWherePvDone);
@@ -328,6 +442,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
             }
         }
+      }
     }
     tc_fence_before_sync();
     __syncthreads();

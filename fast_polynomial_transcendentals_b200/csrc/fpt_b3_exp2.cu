@@ -64,6 +64,25 @@ struct Exp2Op {
     }
 };
 
+// fp32 2^a through the degree-3 polynomial on the FMA pipe: the stand-alone form of the evaluator the attention
+// kernel mixes with the special-function unit.  Four values per thread and step, packed fp32 arithmetic.
+__global__ void __launch_bounds__(kBlock) exp2_poly_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+                                                              int64_t n) {
+    const int64_t quads = n / 4;
+#pragma unroll 1
+    for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < quads; i += int64_t(gridDim.x) * kBlock) {
+        const float4 a = reinterpret_cast<const float4*>(in)[i];
+        float4 e;
+        exp2_poly3_x2(a.x, a.y, e.x, e.y);
+        exp2_poly3_x2(a.z, a.w, e.z, e.w);
+        reinterpret_cast<float4*>(out)[i] = e;
+    }
+    if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+        const int64_t i = quads * 4 + threadIdx.x;
+        out[i] = exp2_poly3(in[i]);
+    }
+}
+
 }  // namespace
 }  // namespace fpt
 
@@ -116,4 +135,18 @@ extern "C" int fpt_exp2_fraction(void* out, const void* in, int64_t n, int varia
     a.out[0] = static_cast<uint16_t*>(out);
     if (variant == FPT_EXP2_NATIVE) return launch_stream(Exp2Op<0>{Exp2Words{}, repeats}, a, n, stream);
     return launch_stream(Exp2Op<1>{exp2_words(variant == FPT_EXP2_HINGE_ENDPOINT), repeats}, a, n, stream);
+}
+
+extern "C" int fpt_exp2_poly_f32(void* out, const void* in, int64_t n, fpt_stream_t stream) {
+    if (n < 0) return FPT_ERR_BAD_SIZE;
+    if (n == 0) return FPT_OK;
+    if (!out || !in) return FPT_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return FPT_ERR_MISALIGNED;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+    int64_t grid = (n / 4 + kBlock - 1) / kBlock;
+    if (grid < 1) grid = 1;
+    if (grid > 0x7fffffff) grid = 0x7fffffff;
+    exp2_poly_f32_kernel<<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
+    return cuda_status(cudaGetLastError());
 }

@@ -53,6 +53,23 @@ __device__ __forceinline__ uint32_t b3_direct(uint32_t x, const B3Words& k) {
     return b3_direct_core(x, k, mask, c);
 }
 
+// The same function with fewer half-rate ALU operations, for the attention warps: both cubics are evaluated on
+// the FMA pipe and ONE select picks the lane's row afterwards (identical arithmetic per lane, so identical bits),
+// and the lower clamp is dropped: below -6 the low-row cubic stays negative all the way to -inf (its derivative is
+// positive there), so the final max(., +0) returns the same +0 the clamped evaluation returns.
+__device__ __forceinline__ uint32_t b3_direct_select_late(uint32_t x, const B3Words& k) {
+    using P = Pk<kBf16>;
+    const uint32_t mask = P::ge_mask(x, k.split);
+    const uint32_t c = P::min(x, k.clamp_hi);
+    uint32_t lo = P::fma(c, k.lo[3], k.lo[2]);
+    uint32_t hi = P::fma(c, k.hi[3], k.hi[2]);
+    lo = P::fma(c, lo, k.lo[1]);
+    hi = P::fma(c, hi, k.hi[1]);
+    lo = P::fma(c, lo, k.lo[0]);
+    hi = P::fma(c, hi, k.hi[0]);
+    return P::max(select_bits(mask, hi, lo), 0u);
+}
+
 // value and value * (intercept + slope * clamp(x)), the coupled derivative of the deployed pair
 __device__ __forceinline__ uint32_t b3_direct_with_grad(uint32_t x, const B3Words& k, uint32_t& grad) {
     using P = Pk<kBf16>;
@@ -80,6 +97,58 @@ __device__ __forceinline__ uint32_t exp2_hinge(uint32_t x, const Exp2Words& k) {
     const uint32_t hinge = P::max(P::sub(x, 0x38003800u), 0u);
     const uint32_t base = P::fma(x, k.slope, k.offset);
     return P::fma(hinge, k.delta, base);
+}
+
+// ---------------------------------------------------------------------------------------------------------------
+// 2^a in fp32 on the FMA pipe, for the share of the soft-max exponentials taken off the special-function unit.
+//   a'  = max(a, -125)                      (results below 2^-125 are not needed; keeps the exponent field valid)
+//   xr  = a' + 1.5 * 2^23   (round to nearest even: the low mantissa bits of xr now hold n = round(a'))
+//   f   = a' - (xr - 1.5 * 2^23)            in [-1/2, 1/2], exact
+//   p   = c0 + f (c1 + f (c2 + f c3))       minimax for 2^f in relative error, 7.5e-5
+//   2^a = bits(p) + (bits(xr) << 23)        (the shift drops the magic constant's own bits, n lands on the exponent)
+// Every step is one IEEE operation, so a C restatement with fmaf gives the same bits.
+constexpr float kExp2PolyC0 = 0.9999280571937561f;   // 0x3f7ffb49
+constexpr float kExp2PolyC1 = 0.6932609677314758f;   // 0x3f31798d
+constexpr float kExp2PolyC2 = 0.2426111251115799f;   // 0x3e786f0d
+constexpr float kExp2PolyC3 = 0.0551716685295105f;   // 0x3d61fbb0
+constexpr float kExp2PolyMagic = 12582912.0f;        // 1.5 * 2^23
+constexpr float kExp2PolyFloor = -125.0f;
+
+__device__ __forceinline__ float exp2_poly3(float a) {
+    a = fmaxf(a, kExp2PolyFloor);
+    const float xr = __fadd_rn(a, kExp2PolyMagic);
+    const float f = __fsub_rn(a, __fsub_rn(xr, kExp2PolyMagic));
+    float p = __fmaf_rn(kExp2PolyC3, f, kExp2PolyC2);
+    p = __fmaf_rn(p, f, kExp2PolyC1);
+    p = __fmaf_rn(p, f, kExp2PolyC0);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(xr) << 23));
+}
+
+// The same function on two values at once with the packed fp32 instructions (two lanes per issue slot).
+__device__ __forceinline__ void exp2_poly3_x2(float a0, float a1, float& e0, float& e1) {
+    a0 = fmaxf(a0, kExp2PolyFloor);
+    a1 = fmaxf(a1, kExp2PolyFloor);
+    uint32_t p0, p1, x0, x1;
+    asm("{\n\t.reg .b64 a, m, xr, n, f, p, c;\n\t"
+        "mov.b64 a, {%4, %5};\n\t"
+        "mov.b64 m, {%6, %6};\n\t"
+        "add.rn.f32x2 xr, a, m;\n\t"
+        "sub.rn.f32x2 n, xr, m;\n\t"
+        "sub.rn.f32x2 f, a, n;\n\t"
+        "mov.b64 p, {%7, %7};\n\t"
+        "mov.b64 c, {%8, %8};\n\t"
+        "fma.rn.f32x2 p, p, f, c;\n\t"
+        "mov.b64 c, {%9, %9};\n\t"
+        "fma.rn.f32x2 p, p, f, c;\n\t"
+        "mov.b64 c, {%10, %10};\n\t"
+        "fma.rn.f32x2 p, p, f, c;\n\t"
+        "mov.b64 {%0, %1}, p;\n\t"
+        "mov.b64 {%2, %3}, xr;\n\t}"
+        : "=r"(p0), "=r"(p1), "=r"(x0), "=r"(x1)
+        : "f"(a0), "f"(a1), "f"(kExp2PolyMagic), "f"(kExp2PolyC3), "f"(kExp2PolyC2), "f"(kExp2PolyC1),
+          "f"(kExp2PolyC0));
+    e0 = __uint_as_float(p0 + (x0 << 23));
+    e1 = __uint_as_float(p1 + (x1 << 23));
 }
 
 }  // namespace fpt

@@ -123,6 +123,26 @@ __device__ __forceinline__ void umma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
         :: "r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
 }
 
+// The same two instructions with each 64-bit shared-memory descriptor given as (low word, high word).  The high word
+// (SBO, version, swizzle) is a constant of the tile layout and the low word is "base + constant" for every K step,
+// so the issuing thread spends one integer add per operand instead of rebuilding 64-bit values.
+__device__ __forceinline__ void umma_ss_words(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo, uint32_t desc_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %4, p;\n\t}"
+        :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_ts_words(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
+                                              uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+
 // 32 lanes x 32 columns of 32-bit: thread i of the warp receives columns [c, c+32) of lane (32*(warp%4) + i).
 __device__ __forceinline__ void tmem_ld_32x32b_x32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile(
@@ -170,6 +190,14 @@ __host__ __device__ constexpr uint64_t umma_smem_desc(uint32_t smem_addr, uint32
     return uint64_t((smem_addr & 0x3ffffu) >> 4) | (uint64_t((lbo_bytes >> 4) & 0x3fffu) << 16) |
            (uint64_t((sbo_bytes >> 4) & 0x3fffu) << 32) | (uint64_t(1) << 46) /* descriptor version for sm_100 */ |
            (uint64_t(2) << 61) /* SWIZZLE_128B */;
+}
+
+// The two 32-bit halves of that descriptor; adding (byte offset >> 4) to the low word moves the start address.
+__host__ __device__ constexpr uint32_t umma_smem_desc_lo(uint32_t smem_addr, uint32_t lbo_bytes) {
+    return ((smem_addr & 0x3ffffu) >> 4) | (((lbo_bytes >> 4) & 0x3fffu) << 16);
+}
+__host__ __device__ constexpr uint32_t umma_smem_desc_hi(uint32_t sbo_bytes) {
+    return uint32_t(umma_smem_desc(0, 0, sbo_bytes) >> 32);
 }
 
 // kind::f16 instruction descriptor: bf16 x bf16 -> fp32, M x N tile, operand majorness (0 = K-major, 1 = MN-major)

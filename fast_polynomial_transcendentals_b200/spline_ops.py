@@ -453,6 +453,15 @@ def exp2_fraction(x, variant: int = EXP2_HINGE_LEAST_SQUARES, repeats: int = 1):
     return out
 
 
+
+def exp2_poly_f32(x):
+    """2^x for fp32 x <= 127 on the FMA pipe (cubic after range reduction); inputs below -125 give 2^-125."""
+    if x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
+        raise ValueError("x must be a contiguous fp32 CUDA tensor")
+    out = torch.empty_like(x)
+    _call("fpt_exp2_poly_f32", x, out.data_ptr(), x.data_ptr(), x.numel())
+    return out
+
 def b3_sigmoid_direct(scores, log2_n: int = 12, with_grad: bool = False):
     """Direct piecewise-cubic sigmoid(score - log n) of sigmoid attention; scores bf16 or fp32 -> bf16."""
     if not isinstance(scores, torch.Tensor) or not scores.is_cuda:

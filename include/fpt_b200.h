@@ -120,6 +120,13 @@ int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n,
 enum { FPT_EXP2_NATIVE = 0, FPT_EXP2_HINGE_LEAST_SQUARES = 1, FPT_EXP2_HINGE_ENDPOINT = 2 };
 int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int repeats, fpt_stream_t stream);
 
+/* ---- fp32 2^a on the FMA pipe: a' = max(a, -125), n = round(a'), f = a' - n, degree-3 minimax polynomial in f
+ *      (relative error 7.5e-5), n added to the exponent field.  This is the software exponential that the attention
+ *      kernel interleaves with the special-function unit in its soft-max modes (the technique of the exp2-offload
+ *      probe, reference: autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:53-99, carried to fp32 with a
+ *      cubic so that the bf16 probabilities keep their precision).  in/out: fp32 [n], 16-byte aligned; a <= 127. */
+int fpt_exp2_poly_f32(void* out, const void* in, int64_t n, fpt_stream_t stream);
+
 /* ---- paired sin/cos: fp32 angles [n] -> out [2, n] 16-bit, cos plane first
  *      replaces launch_sincos_*_{fp16,bf16}[_compute] (reference: sincos_kernels.cu:527-975 evaluators,
  *      1084-1240 kernels).  iterations == 0: one evaluation; iterations > 0: the repeated-evaluation probe

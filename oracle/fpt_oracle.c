@@ -249,6 +249,29 @@ void fpt_oracle_exp2_hinge_repeat(const uint16_t* in, uint16_t* out, int64_t n, 
     }
 }
 
+/* fp32 2^a by range reduction and a cubic on the FMA pipe; this is the build's own evaluator (it has no counterpart
+ * in the reference, whose exp2 replacement is the 16-bit hinge above), restated here operation by operation so
+ * that the device result can be compared bit for bit: every step below is a single IEEE-754 binary32 operation. */
+static inline float exp2_poly3_lane(float a) {
+    volatile float xr, n, f, p;   /* volatile: no step may be fused or reassociated */
+    union { float f; uint32_t u; } pb, xb, r;
+    if (!(a >= -125.0f)) a = -125.0f;          /* max(a, -125) with the NaN-dropping rule of PTX max */
+    xr = a + 12582912.0f;
+    n = xr - 12582912.0f;
+    f = a - n;
+    p = fmaf(0.0551716685295105f, f, 0.2426111251115799f);
+    p = fmaf(p, f, 0.6932609677314758f);
+    p = fmaf(p, f, 0.9999280571937561f);
+    pb.f = p; xb.f = xr;
+    r.u = pb.u + (xb.u << 23);
+    return r.f;
+}
+
+void fpt_oracle_exp2_poly3_f32(const float* in, float* out, int64_t n) {
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = exp2_poly3_lane(in[i]);
+}
+
 /* ------------------------------------------------------------ paired sincos */
 
 typedef struct {

@@ -48,6 +48,7 @@ void fpt_oracle_b3_direct_f32(const float* scores, uint16_t* prob, uint16_t* gra
 
 void fpt_oracle_exp2_hinge(const uint16_t* in, uint16_t* out, int64_t n, int set);
 void fpt_oracle_exp2_hinge_repeat(const uint16_t* in, uint16_t* out, int64_t n, int set, int repeats);
+void fpt_oracle_exp2_poly3_f32(const float* in, float* out, int64_t n);
 
 int fpt_oracle_sincos_is_bf16(int variant);
 void fpt_oracle_sincos_packed(int variant, const float* angles, uint16_t* cos_out, uint16_t* sin_out, int64_t n);

@@ -66,6 +66,7 @@ def lib() -> ctypes.CDLL:
         L.fpt_oracle_b3_direct_f32.argtypes = [_f32p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_exp2_hinge.argtypes = [_u16p, _u16p, _i64, _int]
         L.fpt_oracle_exp2_hinge_repeat.argtypes = [_u16p, _u16p, _i64, _int, _int]
+        L.fpt_oracle_exp2_poly3_f32.argtypes = [_f32p, _f32p, _i64]
         L.fpt_oracle_sincos_packed.argtypes = [_int, _f32p, _u16p, _u16p, _i64]
         L.fpt_oracle_sincos_packed_compute.argtypes = [_int, _f32p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_rope_table.argtypes = [_int, _u32p, _u16p, _i64, _i64]
@@ -176,6 +177,14 @@ def exp2_hinge(x: np.ndarray, constant_set: int = 0, repeats: int = 1) -> np.nda
         lib().fpt_oracle_exp2_hinge(_p16(x), _p16(out), x.size, constant_set)
     else:
         lib().fpt_oracle_exp2_hinge_repeat(_p16(x), _p16(out), x.size, constant_set, repeats)
+    return out
+
+
+def exp2_poly3(x: np.ndarray) -> np.ndarray:
+    """fp32 2^x through the cubic evaluator (bit pattern of the device function)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    out = np.empty_like(x)
+    lib().fpt_oracle_exp2_poly3_f32(x.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), x.size)
     return out
 
 

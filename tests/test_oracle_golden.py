@@ -109,6 +109,20 @@ def test_exp2_hinge_pins_and_model(oracle, vectors):
     assert out.tolist() == [0x3C00, 0x4000]
 
 
+def test_exp2_poly3_restatement_accuracy_and_exponent_handling(oracle):
+    xs = np.concatenate([np.linspace(-125, 127, 2_000_001), np.arange(-125, 128) + 0.5, np.arange(-125, 128) - 0.5 + 1e-6])
+    xs = xs.astype(np.float32)
+    xs = xs[(xs >= -125) & (xs <= 127)]
+    got = oracle.exp2_poly3(xs).astype(np.float64)
+    rel = np.abs(got / np.exp2(xs.astype(np.float64)) - 1)
+    assert rel.max() < 7.6e-5
+    ints = np.arange(-125, 128, dtype=np.float32)
+    # at an integer the fraction is 0 and the result is c0 * 2^n exactly
+    assert np.array_equal(oracle.exp2_poly3(ints), (np.float32(0.9999280571937561) * np.exp2(ints.astype(np.float64))).astype(np.float32))
+    low = oracle.exp2_poly3(np.array([-125.5, -1e6, -np.inf, np.nan], dtype=np.float32))
+    assert np.all(low == oracle.exp2_poly3(np.array([-125.0], dtype=np.float32))[0])
+
+
 def test_error_ceilings_against_true_functions(oracle):
     """Published error bounds of the primary programs (struct comments / reference GPU checks)."""
     x = np.linspace(-15, 15, 30001).astype(np.float32)
