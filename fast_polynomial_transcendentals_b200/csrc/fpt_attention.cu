@@ -43,7 +43,7 @@ struct AttnSmem {
     alignas(1024) uint8_t v[kStages][kTileBytes];
     alignas(8) uint64_t q_full[kSlots];
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
-    uint64_t s_full[kSlots], p_full[kSlots], pv_done[kSlots];
+    uint64_t s_full[kSlots], p_half[kSlots], p_full[kSlots], pv_done[kSlots];
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -153,7 +153,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(&sm.q_full[s], 1);
             mbar_init(&sm.s_full[s], 1);
-            mbar_init(&sm.p_full[s], 4);   // one arrive per softmax warp
+            mbar_init(&sm.p_half[s], 4);   // one arrive per softmax warp: keys 0..63 of the tile are in place
+            mbar_init(&sm.p_full[s], 4);   // ... and keys 64..127
             mbar_init(&sm.pv_done[s], 1);
         }
         for (int st = 0; st < kStages; ++st) {
@@ -233,12 +234,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 }
                 umma_commit(&sm.s_full[s]);
             };
-            auto issue_pv = [&](int s, int st, bool first) {
+            // P V in two halves of four K steps: the first starts as soon as the probabilities of keys 0..63 are in
+            // tensor memory, while the score-mod warps still work on keys 64..127.
+            auto issue_pv_half = [&](int s, int st, int half, bool first) {
                 const uint32_t va = st ? v_lo1 : v_lo0, d = tmem + 256u + uint32_t(s) * 128u, a = tmem + uint32_t(s) * 128u;
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)
-                    umma_ts_words(d, a + 8u * kk, va + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
-                umma_commit(&sm.pv_done[s]);
+                for (int k4 = 0; k4 < 4; ++k4) {
+                    const uint32_t kk = uint32_t(half) * 4u + uint32_t(k4);
+                    umma_ts_words(d, a + 8u * kk, va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                }
+                if (half == 1) umma_commit(&sm.pv_done[s]);
             };
             bool ok = true;
             // prologue: S = Q K_0^T for both slots
@@ -260,11 +265,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     if (j >= n_tiles[s]) continue;
                     ok = mbar_wait(&sm.v_full[st], ph, abort_flag, p.status, kWhereVFull);
                     FPT_TRACE(2, 31);
-                    ok = ok && mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    ok = ok && mbar_wait(&sm.p_half[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
                     if (!ok) break;
                     tc_fence_after_sync();
-                    FPT_TRACE(2, 10 + s);            // P of slot s seen
-                    issue_pv(s, st, j == 0);
+                    FPT_TRACE(2, 10 + s);            // first half of P of slot s seen
+                    issue_pv_half(s, st, 0, j == 0);
+                    ok = mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    issue_pv_half(s, st, 1, j == 0);
                     FPT_TRACE(2, 12);
                     if (j + 1 < n_tiles[s]) {
                         ok = mbar_wait(&sm.k_full[st_next], ph_next, abort_flag, p.status, kWhereKFull);
@@ -304,86 +313,93 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (!ok) break;
             tc_fence_after_sync();
             FPT_TRACE(s, 2);                         // S ready
-            uint32_t pw[kTileN / 2];
             const bool diagonal = p.causal && j == n - 1;
+            // the whole S row: four tensor-memory loads in flight, one wait
+            uint32_t sr[kTileN];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
+            tmem_ld_wait();
+            FPT_TRACE(s, 5);                         // S in registers
+            // P goes back in two halves (keys 0..63, then 64..127), each with its own barrier, so that the first four
+            // K steps of P V run while this warp still works on the second half.
+            auto hand_over = [&](int half, const uint32_t (&words)[32]) {
+                tmem_st_32x32b_x32(t_s + half * 32, words);
+                tmem_st_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
+            };
             if constexpr (MODE == 1) {
-                // the whole S row: four tensor-memory loads in flight, one wait
-                uint32_t sr[kTileN];
 #pragma unroll
-                for (int c = 0; c < 4; ++c) tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
-                tmem_ld_wait();
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t pw[32];
 #pragma unroll
-                for (int i = 0; i < kTileN / 2; ++i) {
-                    const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
-                    uint32_t pr = b3_direct_select_late(x, p.b3);
-                    if (diagonal) {  // keys beyond the diagonal contribute nothing
-                        const int col = j * kTileN + 2 * i;
-                        if (col > row) pr &= 0xffff0000u;
-                        if (col + 1 > row) pr &= 0x0000ffffu;
+                    for (int w = 0; w < 32; ++w) {
+                        const int i = half * 32 + w;
+                        const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
+                        uint32_t pr = b3_direct_select_late(x, p.b3);
+                        if (diagonal) {  // keys beyond the diagonal contribute nothing
+                            const int col = j * kTileN + 2 * i;
+                            if (col > row) pr &= 0xffff0000u;
+                            if (col + 1 > row) pr &= 0x0000ffffu;
+                        }
+                        pw[w] = pr;
                     }
-                    pw[i] = pr;
+                    if (half == 1) FPT_TRACE(s, 3);  // probabilities computed
+                    hand_over(half, pw);
                 }
             } else {
                 // val[i] * mul is the score in log2 units: val = tanh polynomial (mode 0) or the raw score (mode 2).
-                // Common path: no maximum scan.  An exponential above 2^8 (the lazy-rescale limit) would push the tile
-                // sum above 2^8 too, so the sum tells when the reference has to move; then the row is read again from
-                // tensor memory (P has not been written yet), its maximum taken, O and the running sum rescaled.
                 const float mul = MODE == 0 ? softcap_out : plain_scale;
-                bool with_max = j == 0;
-                float sum_lo, sum_hi;
-#pragma unroll 1
-                for (;;) {
-                    uint32_t sr[kTileN];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c)
-                        tmem_ld_32x32b_x32(t_s + c * 32, reinterpret_cast<uint32_t(&)[32]>(sr[c * 32]));
-                    tmem_ld_wait();
-                    FPT_TRACE(s, 5);                 // S in registers
-                    if constexpr (MODE == 0) {
-#pragma unroll
-                        for (int i = 0; i < kTileN / 2; ++i) {
-                            const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in);
-                            const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
-                            sr[2 * i] = t << 16;              // bf16 -> fp32 is a shift
-                            sr[2 * i + 1] = t & 0xffff0000u;
-                        }
-                    }
-                    if (diagonal) {
-#pragma unroll
-                        for (int i = 0; i < kTileN; ++i)
-                            if (j * kTileN + i > row) sr[i] = 0xff800000u;  // -inf
-                    }
-                    if (with_max) {
-                        float m3 = __uint_as_float(sr[0]);
-#pragma unroll
-                        for (int i = 1; i + 1 < kTileN; i += 2)
-                            m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-                        const float new_max = fmaxf(row_max, fmaxf(m3, __uint_as_float(sr[kTileN - 1])) * mul);
-                        if (j > 0 && new_max > row_max) {
-                            const float f = ex2(row_max - new_max);
-                            row_sum *= f;
-#pragma unroll 1
-                            for (int c = 0; c < 4; ++c) {
-                                uint32_t v[32];
-                                tmem_ld_32x32b_x32(t_o + c * 32, v);
-                                tmem_ld_wait();
-#pragma unroll
-                                for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
-                                tmem_st_32x32b_x32(t_o + c * 32, v);
-                            }
-                        }
-                        row_max = new_max;
-                    }
-                    sum_lo = sum_hi = 0.0f;
-                    const float neg_max = -row_max;
-#ifdef FPT_ATTN_EXPERIMENT   // timing experiments only: wrong results on purpose
-#pragma unroll
-                    for (int i = 0; i < kTileN / 2; ++i) pw[i] = (sr[2 * i] ^ sr[2 * i + 1]) & 0x3f003f00u;
-                    sum_lo = 1.0f;
-                    break;
-#endif
+                if constexpr (MODE == 0) {
 #pragma unroll
                     for (int i = 0; i < kTileN / 2; ++i) {
+                        const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in);
+                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
+                        sr[2 * i] = t << 16;              // bf16 -> fp32 is a shift
+                        sr[2 * i + 1] = t & 0xffff0000u;
+                    }
+                }
+                if (diagonal) {
+#pragma unroll
+                    for (int i = 0; i < kTileN; ++i)
+                        if (j * kTileN + i > row) sr[i] = 0xff800000u;  // -inf
+                }
+                // Row maximum of the tile (three-input max on the ALU pipe, which has room beside the exponentials).
+                // The reference point of the exponentials moves only when the maximum grew by more than 2^8 (lazy
+                // rescale); the decision is taken for the whole warp because the tensor-memory accesses of the
+                // rescale are warp-wide instructions.
+                float m3 = __uint_as_float(sr[0]);
+#pragma unroll
+                for (int i = 1; i + 1 < kTileN; i += 2)
+                    m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+                const float tile_max = fmaxf(m3, __uint_as_float(sr[kTileN - 1])) * mul;
+                const bool move = tile_max > row_max + kRescaleThreshold;     // always true on the first tile
+                if (__any_sync(0xffffffffu, move)) {
+                    const float f = move ? ex2(row_max - tile_max) : 1.0f;
+                    if (move) row_max = tile_max;
+                    row_sum *= f;
+                    if (j > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            uint32_t v[32];
+                            tmem_ld_32x32b_x32(t_o + c * 32, v);
+                            tmem_ld_wait();
+#pragma unroll
+                            for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * f);
+                            tmem_st_32x32b_x32(t_o + c * 32, v);
+                        }
+                        tmem_st_wait();
+                    }
+                }
+                float sum_lo = 0.0f, sum_hi = 0.0f;
+                const float neg_max = -row_max;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    uint32_t pw[32];
+#pragma unroll
+                    for (int w = 0; w < 32; ++w) {
+                        const int i = half * 32 + w;
                         float a0, a1;
                         fma_f32x2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), mul, neg_max, a0, a1);
                         float e0, e1;
@@ -394,25 +410,13 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                             e1 = ex2(a1);
                         }
                         add_f32x2(sum_lo, sum_hi, e0, e1);
-                        pw[i] = Sfu<kBf16>::pack(e0, e1);
+                        pw[w] = Sfu<kBf16>::pack(e0, e1);
                     }
-                    if (with_max || sum_lo + sum_hi <= 256.0f) break;
-                    with_max = true;
+                    if (half == 1) FPT_TRACE(s, 3);  // probabilities computed
+                    hand_over(half, pw);
                 }
                 row_sum += sum_lo + sum_hi;
             }
-            FPT_TRACE(s, 3);                         // probabilities computed
-#pragma unroll
-            for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) v[i] = pw[c * 32 + i];
-                tmem_st_32x32b_x32(t_s + c * 32, v);
-            }
-            tmem_st_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.p_full[s]);
             FPT_TRACE(s, 4);                         // P handed over
         }
         if (ok && n > 0) {
