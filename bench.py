@@ -407,12 +407,15 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
     g = torch.Generator(device=device)
     g.manual_seed(SEED)
     D = 128
-    shapes = (("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 0, 1, 50.0, 12),
-              ("config5_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 1, 0, 0.0, 14),
-              ("published_shape_softcap30_B1_S4096_Hq32_Hkv8", 1, 4096, 32, 8, 0, 1, 30.0, 12),
-              ("published_shape_sigmoid_B1_S4096_Hq32_Hkv8_causal", 1, 4096, 32, 8, 1, 1, 0.0, 12),
-              ("control_plain_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12))
-    for name, B, Sq, Hq, Hk, mode, causal, cap, log2_n in shapes:
+    # last field: exp2 routing frequency (0 = every exponential on the SFU; f = four of every f keys on the FMA pipe)
+    shapes = (("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 0, 1, 50.0, 12, 0),
+              ("config5_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 1, 0, 0.0, 14, 0),
+              ("published_shape_softcap30_B1_S4096_Hq32_Hkv8", 1, 4096, 32, 8, 0, 1, 30.0, 12, 0),
+              ("published_shape_sigmoid_B1_S4096_Hq32_Hkv8_causal", 1, 4096, 32, 8, 1, 1, 0.0, 12, 0),
+              ("control_plain_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 0),
+              ("routed_exp2_d3_freq32_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 32),
+              ("routed_exp2_d3_freq12_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 12))
+    for name, B, Sq, Hq, Hk, mode, causal, cap, log2_n, route in shapes:
         q = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
         k = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
         v = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
@@ -421,9 +424,9 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
         status = torch.zeros(1, dtype=torch.int32, device=device)
         arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
         sq, sk, sv, so = arr(q), arr(k), arr(v), arr(o)
-        ks = [("attn", 0, lambda: _lib.check("fpt_attention_fwd", lib.fpt_attention_fwd(
+        ks = [("attn", 0, lambda: _lib.check("fpt_attention_fwd_routed", lib.fpt_attention_fwd_routed(
             o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, Sq, Hq, Hk, D, sq, sk, sv, so, mode,
-            causal, 1.0 / math.sqrt(D), cap, log2_n, status.data_ptr(), S())))]
+            causal, 1.0 / math.sqrt(D), cap, log2_n, route, status.data_ptr(), S())))]
         _, t = time_sweep(ks, 5, 2)
         if int(status.item()) != 0:
             raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x}")

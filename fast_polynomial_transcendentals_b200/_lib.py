@@ -42,6 +42,9 @@ SIGNATURES: dict[str, list] = {
     "fpt_rope_apply": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_attention_fwd": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _vp, _vp],
+    "fpt_attention_fwd_routed": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64),
+                                 ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int,
+                                 ctypes.c_float, ctypes.c_float, _int, _int, _vp, _vp],
     "fpt_selftest_umma": [_vp, _vp, _vp, _int, _vp, _vp],
     "fpt_rope_apply_static_table": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_rope_static_table_capacity": [],

@@ -60,17 +60,11 @@ struct AttnParams {
     B3Words b3;
 };
 
-// Share of the soft-max exponentials evaluated by the fp32 cubic on the FMA pipe instead of the special-function
-// unit: pairs whose index modulo DEN is below NUM.  The unit delivers 16 results per clock and SM, which for a
-// 128 x 128 tile is exactly as long as the two tensor-core products of that tile, so without the split the
-// exponentials alone fill the whole time the tensor pipe leaves to the soft-max.
-#ifndef FPT_ATTN_POLY_NUM
-#define FPT_ATTN_POLY_NUM 0
-#endif
-#ifndef FPT_ATTN_POLY_DEN
-#define FPT_ATTN_POLY_DEN 2
-#endif
-
+// EMU: routing frequency of the software exponential in the soft-max modes, with the meaning the reference gives
+// exp2_emu_freq (reference: src/sfu_repro/fa4.py:724-733): 0 keeps every lane on the special-function unit; a positive
+// frequency f sends four of every f keys of a row through the fp32 cubic on the FMA pipe (12 -> one third, 32 -> one
+// eighth).  The unit delivers 16 results per clock and SM, which for a 128 x 128 tile takes as long as the two
+// tensor-core products of that tile: that is the pressure the routing is meant to relieve.
 // Optional timeline for tuning builds (-DFPT_ATTN_TRACE): block (0,0,0) stores (tag, SM clock) pairs behind the
 // status word, 4096 words per traced warp; the caller must then pass a status buffer of 64 KiB.
 #ifdef FPT_ATTN_TRACE
@@ -122,7 +116,7 @@ __device__ __forceinline__ void add_f32x2(float& acc0, float& acc1, float e0, fl
         : "+f"(acc0), "+f"(acc1) : "f"(e0), "f"(e1));
 }
 
-template <int MODE>
+template <int MODE, int EMU>
 __global__ void __launch_bounds__(kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -403,8 +397,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         float a0, a1;
                         fma_f32x2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), mul, neg_max, a0, a1);
                         float e0, e1;
-                        if ((i % FPT_ATTN_POLY_DEN) < FPT_ATTN_POLY_NUM) {
-                            exp2_poly3_x2(a0, a1, e0, e1);   // FMA pipe
+                        if (EMU > 0 && (i % (EMU > 0 ? EMU / 2 : 1)) < 2) {
+                            exp2_poly3_x2(a0, a1, e0, e1);   // FMA pipe: keys 2i, 2i+1 fall in the routed four of their group
                         } else {
                             e0 = ex2(a0);                    // special-function unit
                             e1 = ex2(a1);
@@ -458,11 +452,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 
 using namespace fpt;
 
-extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
-                                 int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
-                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
-                                 const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
-                                 void* status, fpt_stream_t stream) {
+extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
+                                        int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                        const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                        const int64_t* out_strides, int mode, int causal, float scale, float softcap,
+                                        int log2_n, int exp2_emu_freq, void* status, fpt_stream_t stream) {
     if (!out || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !out_strides)
         return FPT_ERR_NULL_POINTER;
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
@@ -471,6 +465,9 @@ extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void
     if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
     if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
     if (mode == FPT_ATTN_SIGMOID_DIRECT && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
+    if (exp2_emu_freq != 0 && exp2_emu_freq != 8 && exp2_emu_freq != 12 && exp2_emu_freq != 16 && exp2_emu_freq != 32)
+        return FPT_ERR_BAD_ENUM;
+    if (mode == FPT_ATTN_SIGMOID_DIRECT && exp2_emu_freq != 0) return FPT_ERR_BAD_ENUM;   // no exponential to route
     if (reinterpret_cast<uintptr_t>(out) & 15u) return FPT_ERR_MISALIGNED;
     for (int i = 0; i < 3; ++i)
         if ((out_strides[i] * 2) & 15) return FPT_ERR_MISALIGNED;
@@ -513,7 +510,22 @@ extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void
         kernel<<<grid, kThreads, smem, stream>>>(map_q, map_k, map_v, p);
         return cuda_status(cudaGetLastError());
     };
-    if (mode == FPT_ATTN_SOFTCAP_TANH) return launch(attention_fwd_kernel<0>);
-    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1>);
-    return launch(attention_fwd_kernel<2>);
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1, 0>);
+    const bool softcap_mode = mode == FPT_ATTN_SOFTCAP_TANH;
+    switch (exp2_emu_freq) {
+        case 0: return softcap_mode ? launch(attention_fwd_kernel<0, 0>) : launch(attention_fwd_kernel<2, 0>);
+        case 8: return softcap_mode ? launch(attention_fwd_kernel<0, 8>) : launch(attention_fwd_kernel<2, 8>);
+        case 12: return softcap_mode ? launch(attention_fwd_kernel<0, 12>) : launch(attention_fwd_kernel<2, 12>);
+        case 16: return softcap_mode ? launch(attention_fwd_kernel<0, 16>) : launch(attention_fwd_kernel<2, 16>);
+        default: return softcap_mode ? launch(attention_fwd_kernel<0, 32>) : launch(attention_fwd_kernel<2, 32>);
+    }
+}
+
+extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
+                                 int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                                 const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                                 const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
+                                 void* status, fpt_stream_t stream) {
+    return fpt_attention_fwd_routed(out, lse, q, k, v, batch, seq, q_heads, kv_heads, head_dim, q_strides, k_strides,
+                                    v_strides, out_strides, mode, causal, scale, softcap, log2_n, 0, status, stream);
 }

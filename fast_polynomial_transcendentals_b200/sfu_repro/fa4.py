@@ -312,17 +312,24 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
     elif softcap and float(softcap) > 0.0:
         raise NotImplementedError("native (SFU) tanh soft-cap is not built; use the polynomial score-mod")
     else:
-        if exp2_emu_freq not in (None, 0):
-            raise NotImplementedError("software exp2 routing inside softmax is not built")
         mode, cap = 2, 0.0
+    route = 0 if exp2_emu_freq is None else int(exp2_emu_freq)   # "automatic" keeps every lane on the SFU here
+    if route:
+        if mode == 1:
+            raise NotImplementedError("sigmoid attention has no exponential to route")
+        if exp2_emu_backend != "d3":
+            raise NotImplementedError(f"exp2 backend {exp2_emu_backend!r} is not built; the routed software "
+                                      "exponential of this kernel is the fp32 cubic ('d3')")
+        if route not in (8, 12, 16, 32):
+            raise NotImplementedError("built routing frequencies: 0, 8, 12, 16, 32")
     out = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((batch, q_heads, seq), dtype=torch.float32, device=q.device)
     status = torch.zeros(1, dtype=torch.int32, device=q.device)
     strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
     with torch.cuda.device(q.device):
-        _lib.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), batch, seq,
-                  q_heads, k.shape[2], dim, strides(q), strides(k), strides(v), strides(out), mode, int(bool(causal)), scale,
-                  cap, log2_n, status.data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
+        _lib.call("fpt_attention_fwd_routed", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), batch,
+                  seq, q_heads, k.shape[2], dim, strides(q), strides(k), strides(v), strides(out), mode, int(bool(causal)),
+                  scale, cap, log2_n, route, status.data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
     return out, lse
 
 

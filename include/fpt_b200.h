@@ -200,6 +200,18 @@ int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const 
                       const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides, int mode,
                       int causal, float scale, float softcap, int log2_n, void* status, fpt_stream_t stream);
 
+/* ---- the same forward with the soft-max exponentials partly routed to the FMA pipe
+ *      replaces the exp2_emu_backend="d3" / exp2_emu_freq routing of the reference's attention interface
+ *      (reference: src/sfu_repro/fa4.py:34-47 backends, :724-752 routed configurations, forward kwargs :790-807):
+ *      exp2_emu_freq 0 keeps every exponential on the special-function unit; f in {8, 12, 16, 32} sends four of
+ *      every f keys of a row through fpt_exp2_poly_f32's cubic instead (one half, third, quarter, eighth).
+ *      Only the soft-max modes route; FPT_ATTN_SIGMOID_DIRECT has no exponential and accepts 0 only. */
+int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
+                             int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
+                             const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
+                             const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
+                             int exp2_emu_freq, void* status, fpt_stream_t stream);
+
 /* ---- diagnostic: one 128x128x128 bf16 tile through the tensor-core building blocks of the attention kernel
  *      (no counterpart in the reference).  a, b: bf16 [128,128] row-major; c: fp32 [128,128];
  *      mode 0: c = a * b^T (both operands K-major in shared memory); mode 1: c = a * b (a staged in tensor memory,

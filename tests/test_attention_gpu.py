@@ -30,7 +30,7 @@ def test_umma_tile_matches_matmul(fpt, cuda, mode):
     assert err < 1e-3 * max(1.0, want.abs().max().item()), err
 
 
-def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=12):
+def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=12, exp2_emu_freq=None):
     """q,k,v torch bf16 (B,S,H,D), any strides with D contiguous. Returns (out (B,S,Hq,D), lse, status)."""
     import ctypes
     import torch
@@ -40,8 +40,13 @@ def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=1
     lse = torch.full((B, Hq, S), float("nan"), dtype=torch.float32, device=cuda)
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
     arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
-    fpt.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk, D,
-             arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, status.data_ptr(), stream())
+    if exp2_emu_freq is None:
+        fpt.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk,
+                 D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, status.data_ptr(), stream())
+    else:
+        fpt.call("fpt_attention_fwd_routed", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S,
+                 Hq, Hk, D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, exp2_emu_freq,
+                 status.data_ptr(), stream())
     torch.cuda.synchronize()
     return out, lse, int(status.item()) & 0xFFFFFFFF
 
@@ -127,3 +132,63 @@ def test_plain_softmax_mode_matches_torch_sdpa(fpt, cuda):
     mask = torch.ones(S, S, device=cuda, dtype=torch.bool).tril()
     want_lse = torch.logsumexp(scores.masked_fill(~mask, float("-inf")), dim=-1)
     assert float((lse - want_lse).abs().max()) < 1e-2
+
+
+@pytest.mark.parametrize("freq", [8, 12, 16, 32])
+@pytest.mark.parametrize("mode,causal,softcap", [(2, True, 0.0), (0, True, 30.0), (2, False, 0.0)])
+def test_routed_exp2_stays_within_tolerance(fpt, cuda, oracle, freq, mode, causal, softcap):
+    """Four of every `freq` keys take the fp32 cubic exponential: same 2e-2 bound against the fp32 oracle, and
+    within bf16 rounding of the unrouted kernel."""
+    import torch
+    B, S, Hq, Hk, D = 1, 384, 2, 1, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(99)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    base, lse0, st0 = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, 12, exp2_emu_freq=0)
+    out, lse, st = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, 12, exp2_emu_freq=freq)
+    assert st0 == 0 and st == 0
+    assert float((out.float() - base.float()).abs().max()) < 8e-3
+    assert float((lse - lse0).abs().max()) < 1e-3
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    rows = np.arange(S)
+    for h in range(Hq):
+        want = oracle.attention_rows(qb, kb, vb, 0, h, rows, mode, causal, scale, softcap, 12)
+        assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
+
+
+def test_routed_exp2_rejects_unbuilt_frequencies(fpt, cuda):
+    import torch
+    q = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=cuda)
+    for mode, freq in ((2, 4), (2, 10), (2, -8), (1, 12)):
+        with pytest.raises(Exception):
+            run_attention(fpt, cuda, q, q, q, mode, False, 1.0, 0.0, 12, exp2_emu_freq=freq)
+
+
+def test_running_maximum_that_keeps_growing_is_rescaled(fpt, cuda, oracle):
+    """Keys whose scores grow along the sequence force the lazy rescale (maximum up by more than 2^8 between tiles)
+    several times per row; a second block of rows sees it shrink again."""
+    import torch
+    B, S, Hq, Hk, D = 1, 1024, 2, 1, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(3)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g)
+    ramp = torch.linspace(0.2, 6.0, S, device=cuda).view(1, S, 1, 1)
+    k = k * ramp                                    # later keys reach far larger scores
+    k[:, S // 2:, :, :] *= torch.linspace(1.0, 0.1, S // 2, device=cuda).view(1, -1, 1, 1)
+    q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    rows = np.arange(S)
+    for causal in (False, True):
+        for freq in (0, 12):
+            out, lse, st = run_attention(fpt, cuda, q, k, v, 2, causal, scale, 0.0, 12, exp2_emu_freq=freq)
+            assert st == 0
+            assert not torch.isnan(out.float()).any()
+            for h in range(Hq):
+                want = oracle.attention_rows(qb, kb, vb, 0, h, rows, 2, causal, scale, 0.0, 12)
+                assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
