@@ -35,10 +35,17 @@ SIGNATURES: dict[str, list] = {
     "fpt_swish_mul_packed": [_vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed_bwd": [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_b3_sigmoid_direct": [_vp, _vp, _vp, _i64, _int, _int, _vp],
+    "fpt_fwd_deriv": [_vp, _vp, _vp, _i64, _int, _int, _vp],
+    "fpt_fused_fwd_bwd": [_vp, _vp, _vp, _vp, _i64, _int, _vp],
+    "fpt_multiply": [_vp, _vp, _vp, _i64, _int, _vp],
+    "fpt_unary_hybrid": [_vp, _vp, _i64, _int, _vp],
+    "fpt_binary_bwd_hybrid": [_vp, _vp, _vp, _i64, _int, _vp],
     "fpt_exp2_fraction": [_vp, _vp, _i64, _int, _int, _vp],
     "fpt_exp2_poly_f32": [_vp, _vp, _i64, _vp],
     "fpt_sincos": [_vp, _vp, _i64, _int, _int, _vp],
+    "fpt_sincos_f32": [_vp, _vp, _i64, _int, _int, _vp],
     "fpt_rope_table": [_vp, _vp, _i64, _i64, _int, _int, _vp],
+    "fpt_rope_table_lut": [_vp, _vp, _vp, _i64, _i64, _int, _vp],
     "fpt_rope_apply": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_attention_fwd": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _vp, _vp],

@@ -379,6 +379,54 @@ __global__ void __launch_bounds__(kBlock) rope_table_kernel(const uint32_t* __re
     }
 }
 
+// Look-up variant: the seven top phase bits (rounded) pick (sin, cos) from a 128-entry table held in shared memory,
+// the signed remainder becomes an fp16 angle and one first-order step follows.
+__device__ __forceinline__ void rope_lut_pair(uint32_t position, uint32_t inc0, uint32_t inc1, const uint32_t* lut,
+                                              uint32_t& cos_w, uint32_t& sin_w) {
+    using P = Pk<kFp16>;
+    const uint32_t p0 = position * inc0, p1 = position * inc1;
+    const uint32_t i0 = ((p0 + (1u << 24)) >> 25) & 127u, i1 = ((p1 + (1u << 24)) >> 25) & 127u;
+    const float d0 = mul_rn(float(int(p0 - (i0 << 25))), 0x1.921fb6p-30f);   // 2 pi / 2^32 radians per phase unit
+    const float d1 = mul_rn(float(int(p1 - (i1 << 25))), 0x1.921fb6p-30f);
+    const uint32_t delta = Sfu<kFp16>::pack(d0, d1);
+    const uint32_t b0 = lut[i0], b1 = lut[i1];
+    const uint32_t sin_b = __byte_perm(b0, b1, 0x5410), cos_b = __byte_perm(b0, b1, 0x7632);
+    sin_w = P::fma(delta, cos_b, sin_b);
+    cos_w = P::fma(delta ^ kSignMask, sin_b, cos_b);
+}
+
+__global__ void __launch_bounds__(kBlock) rope_table_lut_kernel(const uint32_t* __restrict__ params,
+                                                               const uint32_t* __restrict__ phase_table,
+                                                               uint16_t* __restrict__ table, int64_t seq, int64_t freq_count,
+                                                               int iterations) {
+    __shared__ uint32_t lut[128];
+    if (threadIdx.x < 128) lut[threadIdx.x] = phase_table[threadIdx.x];
+    __syncthreads();
+    const int64_t pairs = freq_count / 2;
+    const int64_t total = seq * pairs;
+    uint32_t* cos_plane = reinterpret_cast<uint32_t*>(table);
+    uint32_t* sin_plane = reinterpret_cast<uint32_t*>(table + seq * freq_count);
+#pragma unroll 1
+    for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < total; i += int64_t(gridDim.x) * kBlock) {
+        const int64_t pos = i / pairs, j = i - pos * pairs;
+        const uint32_t a = params[2 * j], b = params[2 * j + 1];
+        uint32_t c, s;
+        if (iterations <= 0) {
+            rope_lut_pair(uint32_t(pos), a, b, lut, c, s);
+        } else {
+            c = s = 0u;
+            for (int it = 0; it < iterations; ++it) {
+                uint32_t c1, s1;
+                rope_lut_pair(uint32_t(pos) + uint32_t(it), a, b, lut, c1, s1);
+                c = Pk<kFp16>::add(c, c1);
+                s = Pk<kFp16>::add(s, s1);
+            }
+        }
+        cos_plane[pos * pairs + j] = c;
+        sin_plane[pos * pairs + j] = s;
+    }
+}
+
 // 8 halves = 4 interleaved (even, odd) pairs; cos/sin words hold pairs (0,1) and (2,3).
 template <bool IO_BF16>
 __device__ __forceinline__ Vec<4> rotate_chunk(Vec<4> v, uint32_t cos_lo, uint32_t sin_lo, uint32_t cos_hi, uint32_t sin_hi) {
@@ -527,6 +575,27 @@ extern "C" int fpt_rope_table(void* table, const void* params, int64_t seq, int6
     case FPT_ROPE_NATIVE: rope_table_kernel<FPT_ROPE_NATIVE><<<unsigned(grid), kBlock, 0, stream>>>(p, t, seq, freq_count, iterations); break;
     default: return FPT_ERR_BAD_ENUM;
     }
+    return cuda_status(cudaGetLastError());
+}
+
+extern "C" int fpt_rope_table_lut(void* table, const void* phase_increments, const void* phase_table, int64_t seq,
+                                  int64_t freq_count, int iterations, fpt_stream_t stream) {
+    if (seq < 0 || freq_count < 0 || iterations < 0) return FPT_ERR_BAD_SIZE;
+    if (freq_count % 2) return FPT_ERR_BAD_SIZE;
+    if (seq > 0x7fffffff) return FPT_ERR_BAD_SIZE;
+    if (seq * freq_count == 0) return FPT_OK;
+    if (!table || !phase_increments || !phase_table) return FPT_ERR_NULL_POINTER;
+    if ((reinterpret_cast<uintptr_t>(table) & 3u) || (reinterpret_cast<uintptr_t>(phase_increments) & 3u) ||
+        (reinterpret_cast<uintptr_t>(phase_table) & 3u))
+        return FPT_ERR_MISALIGNED;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+    int64_t grid = (seq * (freq_count / 2) + kBlock - 1) / kBlock;
+    const int64_t cap = int64_t(dev.sm_count) * 64;
+    if (grid > cap) grid = cap;
+    rope_table_lut_kernel<<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const uint32_t*>(phase_increments),
+                                                                static_cast<const uint32_t*>(phase_table),
+                                                                static_cast<uint16_t*>(table), seq, freq_count, iterations);
     return cuda_status(cudaGetLastError());
 }
 

@@ -14,6 +14,7 @@
 #pragma once
 
 #include <cstdint>
+#include <type_traits>
 #include <cuda_runtime.h>
 
 #include "fpt_common.h"
@@ -76,6 +77,14 @@ struct StreamArgs {
 
 // Op contract:  static constexpr int NIN, NOUT;
 //               __device__ void apply(const uint32_t (&in)[NIN], uint32_t (&out)[NOUT]) const;   (two lanes per word)
+// An Op with `static constexpr bool kIndexed = true` is instead called, inside whole vectors, as
+//               apply_at(word, in, out)   word = index of the packed word within its vector (16-byte groups of four),
+// which lets it treat the lanes of a group differently; tails and unaligned arrays still go through apply().
+template <class Op, class = void>
+struct op_indexed : std::false_type {};
+template <class Op>
+struct op_indexed<Op, std::void_t<decltype(Op::kIndexed)>> : std::integral_constant<bool, Op::kIndexed> {};
+
 template <class Op, int WORDS, int UNROLL, bool STREAM, int BLOCK>
 __global__ void __launch_bounds__(BLOCK) stream_kernel(const Op op, const StreamArgs<Op::NIN, Op::NOUT> a) {
     constexpr int NIN = Op::NIN, NOUT = Op::NOUT;
@@ -107,7 +116,8 @@ __global__ void __launch_bounds__(BLOCK) stream_kernel(const Op op, const Stream
                     uint32_t xi[NIN], yo[NOUT];
 #pragma unroll
                     for (int i = 0; i < NIN; ++i) xi[i] = v[i][u].w[w];
-                    op.apply(xi, yo);
+                    if constexpr (op_indexed<Op>::value) op.apply_at(w, xi, yo);
+                    else op.apply(xi, yo);
 #pragma unroll
                     for (int o = 0; o < NOUT; ++o) r[o].w[w] = yo[o];
                 }

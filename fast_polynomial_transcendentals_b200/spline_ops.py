@@ -183,6 +183,86 @@ def tanh_bwd_alg(grad_out, y):
     return _alg(grad_out, y, "tanh")
 
 
+# ---- FP16-only composites (reference: spline_ops.cpp:1547-1575 hybrid fwd, :1862-1864 hybrid bwd, :1866-1926) ----
+
+def _check_fp16_only(x: torch.Tensor, name: str) -> None:
+    _check_input(x, name)
+    if x.dtype != torch.float16:
+        raise RuntimeError(f"{name} must be float16 (no BF16 support for this op)")
+
+
+def _hybrid_fwd(function: str):
+    def op(x):
+        _check_fp16_only(x, "x")
+        out = torch.empty_like(x)
+        _call("fpt_unary_hybrid", x, out.data_ptr(), x.data_ptr(), x.numel(), _FUNCTIONS[function])
+        return out
+    op.__name__ = f"{function}_fwd_hybrid"
+    op.__doc__ = f"{function} forward, one packed word in four on the SFU and three on the D3 polynomial."
+    return op
+
+
+def _hybrid_bwd(function: str):
+    def op(grad_out, x):
+        _check_fp16_only(grad_out, "grad_out")
+        _check_fp16_only(x, "x")
+        grad_in = torch.empty_like(x)
+        _call("fpt_binary_bwd_hybrid", x, grad_in.data_ptr(), grad_out.data_ptr(), x.data_ptr(), x.numel(),
+              _FUNCTIONS[function])
+        return grad_in
+    op.__name__ = f"{function}_bwd_hybrid"
+    op.__doc__ = f"grad_out * d{function}/dx, one packed word in four on the SFU and three on the D4 polynomial."
+    return op
+
+
+def _fused(function: str):
+    def op(x, grad_out):
+        _check_fp16_only(x, "x")
+        _check_fp16_only(grad_out, "grad_out")
+        y, grad_in = torch.empty_like(x), torch.empty_like(x)
+        _call("fpt_fused_fwd_bwd", x, y.data_ptr(), grad_in.data_ptr(), x.data_ptr(), grad_out.data_ptr(), x.numel(),
+              _FUNCTIONS[function])
+        return [y, grad_in]
+    op.__name__ = f"{function}_fused"
+    op.__doc__ = f"[{function}_D3(x), grad_out * derivative] in one pass over x."
+    return op
+
+
+_DERIV_ALGEBRAIC, _DERIV_POLY, _DERIV_SHARED_SIGMOID = 0, 1, 2
+
+
+def _fwd_deriv(function: str, variant: int, name: str):
+    def op(x):
+        _check_fp16_only(x, "x")
+        y, dy = torch.empty_like(x), torch.empty_like(x)
+        _call("fpt_fwd_deriv", x, y.data_ptr(), dy.data_ptr(), x.data_ptr(), x.numel(), _FUNCTIONS[function], variant)
+        return [y, dy]
+    op.__name__ = name
+    op.__doc__ = "[y, dy/dx]: the forward value and the derivative saved for a multiply-only backward."
+    return op
+
+
+sigmoid_fwd_hybrid, tanh_fwd_hybrid, swish_fwd_hybrid = (_hybrid_fwd(f) for f in ("sigmoid", "tanh", "swish"))
+sigmoid_bwd_hybrid, tanh_bwd_hybrid, swish_bwd_hybrid = (_hybrid_bwd(f) for f in ("sigmoid", "tanh", "swish"))
+sigmoid_fused, tanh_fused, swish_fused = (_fused(f) for f in ("sigmoid", "tanh", "swish"))
+sigmoid_fwd_deriv_alg = _fwd_deriv("sigmoid", _DERIV_ALGEBRAIC, "sigmoid_fwd_deriv_alg")
+sigmoid_fwd_deriv_poly = _fwd_deriv("sigmoid", _DERIV_POLY, "sigmoid_fwd_deriv_poly")
+tanh_fwd_deriv_alg = _fwd_deriv("tanh", _DERIV_ALGEBRAIC, "tanh_fwd_deriv_alg")
+tanh_fwd_deriv_poly = _fwd_deriv("tanh", _DERIV_POLY, "tanh_fwd_deriv_poly")
+swish_fwd_deriv = _fwd_deriv("swish", _DERIV_SHARED_SIGMOID, "swish_fwd_deriv")
+swish_fwd_deriv_poly = _fwd_deriv("swish", _DERIV_POLY, "swish_fwd_deriv_poly")
+
+
+def multiply(a, b):
+    """a * b, one rounding per lane (the backward of the forward-with-derivative ops: grad_out * saved dy)."""
+    _check_input(a, "a")
+    _check_input(b, "b")
+    _same(a, b, "a", "b")
+    out = torch.empty_like(a)
+    _call("fpt_multiply", a, out.data_ptr(), a.data_ptr(), b.data_ptr(), a.numel(), _dtype_id(a))
+    return out
+
+
 # ---- SwiGLU --------------------------------------------------------------------------------
 
 def swish_mul_fwd_variant(gate, up, degree: int, coeff_source_id: int):
@@ -314,6 +394,41 @@ for _name, _variant in _SINCOS_VARIANTS.items():
     globals()[f"sincos_{_name}_compute"] = _make_sincos(_variant, _dtype, True)
 
 
+# fp32 family: `sincos_<variant>_f32(angles)` and `sincos_<variant>_compute_f32(angles, iterations)`
+_SINCOS_F32_VARIANTS = ("native", "d3_d4", "d3_d4_cycle", "d3_d4_magic_bias", "d5_d4_half_turn_ls",
+                        "d5_d4_half_turn_sollya", "d5_d4_half_turn_sollya_fast", "d5_d4", "d7_d6")
+
+
+def _sincos_f32(angles, variant: int, iterations: int = 0):
+    if not isinstance(angles, torch.Tensor) or not angles.is_cuda:
+        raise RuntimeError("angles must be a CUDA tensor")
+    if not angles.is_contiguous():
+        raise RuntimeError("angles must be contiguous")
+    if angles.dtype != torch.float32:
+        raise RuntimeError("angles must be float32")
+    out = torch.empty((2, *angles.shape), dtype=torch.float32, device=angles.device)
+    _call("fpt_sincos_f32", angles, out.data_ptr(), angles.data_ptr(), angles.numel(), variant, iterations)
+    return out
+
+
+def _make_sincos_f32(variant: int, compute: bool):
+    if compute:
+        def op(angles, iterations):
+            if int(iterations) <= 0:
+                raise RuntimeError("iterations must be positive")
+            return _sincos_f32(angles, variant, int(iterations))
+    else:
+        def op(angles):
+            return _sincos_f32(angles, variant)
+    op.__doc__ = "angles fp32 [...] -> fp32 [2, ...] (cos first)"
+    return op
+
+
+for _variant, _name in enumerate(_SINCOS_F32_VARIANTS):
+    globals()[f"sincos_{_name}_f32"] = _make_sincos_f32(_variant, False)
+    globals()[f"sincos_{_name}_compute_f32"] = _make_sincos_f32(_variant, True)
+
+
 # ---- RoPE (reference: spline_ops.cpp:562-1140) -------------------------------------------------
 
 ROPE_HALF_TURN_D5_D6, ROPE_QUARTER_TURN_D3_D4, ROPE_NATIVE, ROPE_CACHED = 0, 1, 2, 3
@@ -364,6 +479,47 @@ def rope_sincos_fixed_d3_d4_fp16_compute(phase_increments, sequence_length, iter
 def rope_sincos_fixed_half_turn_d5_d6_fp16_compute(phase_increments, sequence_length, iterations):
     return _rope_table(phase_increments, sequence_length, ROPE_HALF_TURN_D5_D6, torch.int32, "phase_increments",
                        int(iterations))
+
+
+def _rope_table_lut(phase_increments, phase_table, sequence_length, iterations: int = 0):
+    if not isinstance(phase_table, torch.Tensor) or not phase_table.is_cuda:
+        raise RuntimeError("phase_table must be a CUDA tensor")
+    if not phase_table.is_contiguous():
+        raise RuntimeError("phase_table must be contiguous")
+    if phase_table.dtype != torch.float16:
+        raise RuntimeError("phase_table must be float16")
+    if phase_table.dim() != 2 or phase_table.size(0) != 128 or phase_table.size(1) != 2:
+        raise RuntimeError("phase_table must have shape [128, 2]")
+    if not isinstance(phase_increments, torch.Tensor) or not phase_increments.is_cuda:
+        raise RuntimeError("phase_increments must be a CUDA tensor")
+    if phase_table.device != phase_increments.device:
+        raise RuntimeError("phase_table and phase_increments must be on the same CUDA device")
+    if not phase_increments.is_contiguous():
+        raise RuntimeError("phase_increments must be contiguous")
+    if phase_increments.dim() != 1:
+        raise RuntimeError("phase_increments must be one-dimensional")
+    if phase_increments.dtype != torch.int32:
+        raise RuntimeError("phase_increments has the wrong dtype")
+    if int(sequence_length) <= 0:
+        raise RuntimeError("sequence_length must be positive")
+    if phase_increments.numel() == 0 or phase_increments.numel() % 2:
+        raise RuntimeError("phase_increments must contain a positive even number of elements")
+    out = torch.empty((2, int(sequence_length), phase_increments.numel()), dtype=torch.float16,
+                      device=phase_increments.device)
+    _call("fpt_rope_table_lut", phase_increments, out.data_ptr(), phase_increments.data_ptr(), phase_table.data_ptr(),
+          int(sequence_length), phase_increments.numel(), iterations)
+    return out
+
+
+def rope_sincos_fixed_lut_fp16(phase_increments, phase_table, sequence_length):
+    """[2, S, F] fp16 (cos, sin) from a [128, 2] (sin, cos) table and one first-order correction step."""
+    return _rope_table_lut(phase_increments, phase_table, sequence_length)
+
+
+def rope_sincos_fixed_lut_fp16_compute(phase_increments, phase_table, sequence_length, iterations):
+    if int(iterations) <= 0:
+        raise RuntimeError("iterations must be positive")
+    return _rope_table_lut(phase_increments, phase_table, sequence_length, int(iterations))
 
 
 def _check_rope_qk(q, k, dtype, dtype_name):

@@ -82,6 +82,31 @@ int fpt_binary_bwd(void* grad_in, const void* grad_out, const void* x, int64_t n
 int fpt_bwd_algebraic(void* grad_in, const void* grad_out, const void* y, int64_t n, int function, int dtype,
                       fpt_stream_t stream);
 
+/* ---- FP16 composites of the degree-3 forward programs (sigmoid, tanh, SiLU), fp16 only like the reference's
+ *      replaces launch_{sigmoid,tanh}_fwd_deriv_{alg,poly}_kernel, launch_swish_fwd_deriv[_poly]_kernel,
+ *      launch_{sigmoid,tanh,swish}_fused_kernel, launch_multiply_kernel and the six launch_*_{fwd,bwd}_hybrid_kernel
+ *      (reference: autonumerics_zero/spline_ops/spline_kernels.cu:776-1027 kernels, :1394-1480 launchers).
+ *      fpt_fwd_deriv: y = F_D3(x) and the derivative saved for backward, dy =
+ *        FPT_DERIV_ALGEBRAIC      y(1-y) / 1-y^2 from y            (sigmoid, tanh)
+ *        FPT_DERIV_POLY           the D4 derivative program of x    (sigmoid, tanh, SiLU)
+ *        FPT_DERIV_SHARED_SIGMOID s = sigmoid_D3(x): y = x s, dy = s(1 + x(1-s))   (SiLU)
+ *      Every length takes the same arithmetic (the reference's fallback for short or ragged arrays multiplies
+ *      the algebraic derivative by y once more and drops the tail of `multiply`; neither is reproduced).
+ *      fpt_fused_fwd_bwd: y = F_D3(x), grad_in = grad_out * (algebraic derivative of y; SiLU: D4 program of x).
+ *      fpt_multiply: out = a * b (one rounding), fp16 or bf16.
+ *      fpt_unary_hybrid / fpt_binary_bwd_hybrid: of every four packed words (16 bytes) the first is evaluated on
+ *      the special-function unit (packed ex2 / rcp / tanh), the other three by the D3 (forward) or D4 (derivative)
+ *      program; as in the reference the routing applies when n is a multiple of 8 and n >= 8192, otherwise (and
+ *      for unaligned pointers) every lane is polynomial. */
+enum { FPT_DERIV_ALGEBRAIC = 0, FPT_DERIV_POLY = 1, FPT_DERIV_SHARED_SIGMOID = 2 };
+int fpt_fwd_deriv(void* y, void* dy, const void* x, int64_t n, int function, int variant, fpt_stream_t stream);
+int fpt_fused_fwd_bwd(void* y, void* grad_in, const void* x, const void* grad_out, int64_t n, int function,
+                      fpt_stream_t stream);
+int fpt_multiply(void* out, const void* a, const void* b, int64_t n, int dtype, fpt_stream_t stream);
+int fpt_unary_hybrid(void* out, const void* in, int64_t n, int function, fpt_stream_t stream);
+int fpt_binary_bwd_hybrid(void* grad_in, const void* grad_out, const void* x, int64_t n, int function,
+                          fpt_stream_t stream);
+
 /* ---- SwiGLU: out = swish(gate) * up over flat arrays (B4 routed experts, B1 unpacked)
  *      replaces launch_swish_mul_fwd_{native,d3..d6}_kernel[_bf16[_sollya]]
  *      (reference: spline_kernels.cu:137-158,609-642; spline_kernels_bf16.cu:143-164,705-739). */
@@ -148,6 +173,22 @@ enum {
 };
 int fpt_sincos(void* out, const void* angles, int64_t n, int variant, int iterations, fpt_stream_t stream);
 
+/* ---- paired sin/cos in fp32: fp32 angles [n] -> out [2, n] fp32, cos plane first
+ *      replaces launch_sincos_*_f32 and launch_sincos_*_compute_f32 (reference: sincos_kernels.cu:24-118 reducers,
+ *      :120-406 evaluators, :980-1082 kernels, :2125-2357 launchers).  iterations as in fpt_sincos. */
+enum {
+    FPT_SINCOS_F32_NATIVE = 0,
+    FPT_SINCOS_F32_D3_D4 = 1,
+    FPT_SINCOS_F32_D3_D4_CYCLE = 2,
+    FPT_SINCOS_F32_D3_D4_MAGIC_BIAS = 3,
+    FPT_SINCOS_F32_D5_D4_HALF_TURN_LS = 4,
+    FPT_SINCOS_F32_D5_D4_HALF_TURN_SOLLYA = 5,
+    FPT_SINCOS_F32_D5_D4_HALF_TURN_SOLLYA_FAST = 6,
+    FPT_SINCOS_F32_D5_D4 = 7,
+    FPT_SINCOS_F32_D7_D6 = 8
+};
+int fpt_sincos_f32(void* out, const void* angles, int64_t n, int variant, int iterations, fpt_stream_t stream);
+
 /* ---- RoPE tables: table [2, seq, freq_count] fp16 (cos plane, then sin plane)
  *      replaces launch_rope_sincos_{native,fixed_d3_d4,fixed_half_turn_d5_d6}_fp16[_compute]
  *      (reference: sincos_kernels.cu:1242-1348, 1387-1480).  params: int32 Q0.32 phase increments
@@ -155,6 +196,13 @@ int fpt_sincos(void* out, const void* angles, int64_t n, int variant, int iterat
 enum { FPT_ROPE_HALF_TURN_D5_D6 = 0, FPT_ROPE_QUARTER_TURN_D3_D4 = 1, FPT_ROPE_NATIVE = 2, FPT_ROPE_CACHED = 3 };
 int fpt_rope_table(void* table, const void* params, int64_t seq, int64_t freq_count, int kind, int iterations,
                    fpt_stream_t stream);
+
+/* ---- RoPE table by look-up: phase_table [128, 2] fp16 = (sin, cos) of 2*pi*i/128; the top phase bits pick an entry,
+ *      the remainder drives one first-order step in fp16
+ *      replaces launch_rope_sincos_fixed_lut_fp16[_compute] (reference: sincos_kernels.cu:1350-1385 evaluator,
+ *      :1482-1502 and :1894-1928 kernels).  iterations as in fpt_rope_table. */
+int fpt_rope_table_lut(void* table, const void* phase_increments, const void* phase_table, int64_t seq,
+                       int64_t freq_count, int iterations, fpt_stream_t stream);
 
 /* ---- fused RoPE rotation + transpose: q [B,S,Hq,D], k [B,S,Hk,D] -> q_out [B,Hq,S,D], k_out [B,Hk,S,D]
  *      replaces launch_rope_apply_{fixed_half_turn_d5_d6,native,cached}_fp16

@@ -218,6 +218,34 @@ void fpt_oracle_b3_direct_f32(const float* scores, uint16_t* prob, uint16_t* gra
         b3_lane(sf_from_float(SF_BF16, scores[i]), log2_n, &prob[i], grad ? &grad[i] : NULL);
 }
 
+/* ------------------------------------------------ FP16/BF16 composite helpers */
+
+/* one rounded product per lane (reference: multiply_vec_kernel, spline_kernels.cu:1009-1027) */
+void fpt_oracle_multiply(const uint16_t* a, const uint16_t* b, uint16_t* out, int64_t n, int dtype) {
+    const sf_format f = dtype ? SF_BF16 : SF_FP16;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = sf_mul(f, a[i], b[i]);
+}
+
+/* one fused multiply-add per lane: the form a compiler may contract `c + a*b` into */
+void fpt_oracle_fma16(const uint16_t* a, const uint16_t* b, const uint16_t* c, uint16_t* out, int64_t n, int dtype) {
+    const sf_format f = dtype ? SF_BF16 : SF_FP16;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) out[i] = sf_fma(f, a[i], b[i], c[i]);
+}
+
+/* SiLU forward with the derivative from one shared sigmoid (reference: fwd_deriv_swish_kernel,
+ * spline_kernels.cu:981-1006): s given, y = x*s, dy = s * fma(x, 1 - s, 1). */
+void fpt_oracle_swish_shared_sigmoid(const uint16_t* x, const uint16_t* s, uint16_t* y, uint16_t* dy, int64_t n, int dtype) {
+    const sf_format f = dtype ? SF_BF16 : SF_FP16;
+    const uint16_t one = dtype ? 0x3f80u : 0x3c00u;
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        y[i] = sf_mul(f, x[i], s[i]);
+        dy[i] = sf_mul(f, s[i], sf_fma(f, x[i], sf_sub(f, one, s[i]), one));
+    }
+}
+
 /* --------------------------------------------------------- fractional exp2 */
 
 /* set 0: least-squares constants compiled into the reference benchmark
@@ -378,6 +406,122 @@ void fpt_oracle_sincos_packed_compute(int variant, const float* angles, uint16_t
     }
 }
 
+/* ------------------------------------------------------- fp32 paired sincos */
+
+/* The fp32 family (reference: sincos_kernels.cu:24-118 reducers and quadrant restore, :129-406 evaluators):
+ * range reduction, Horner in r^2 and sign / swap restore, every step one binary32 operation.  Variants:
+ * 1 D3/D4 quarter turn, two-term pi/2, integer conversion   2 D3/D4 in turns with symmetry folding
+ * 3 D3/D4 quarter turn, two-term, magic bias                4 D5/D4 half turn, least squares
+ * 5 D5/D4 half turn, Sollya                                 6 the same with one-term pi
+ * 7 D5/D4 quarter turn                                      8 D7/D6 quarter turn            (0 = native: no oracle) */
+typedef struct { int reducer; int n_sin, n_cos; float sin_c[4]; float cos_c[4]; } sincos_f32_variant;
+enum { RED_QUARTER_CVT = 0, RED_CYCLE = 1, RED_QUARTER_MAGIC2 = 2, RED_HALF_MAGIC2 = 3, RED_HALF_MAGIC1 = 4 };
+
+static const sincos_f32_variant k_sincos_f32[9] = {
+    [1] = { RED_QUARTER_CVT, 2, 3, { 0.99903142452239990234375f, -0.16034401953220367431640625f },
+            { 0.999990046024322509765625f, -0.4997082054615020751953125f, 0.0403986163437366485595703125f } },
+    [2] = { RED_CYCLE, 2, 3, { 6.277099609375f, -39.77336883544921875f },
+            { 0.999990046024322509765625f, -19.7276897430419921875f, 62.96308135986328125f } },
+    [3] = { RED_QUARTER_MAGIC2, 2, 3, { 0.99903142452239990234375f, -0.16034401953220367431640625f },
+            { 0.999990046024322509765625f, -0.4997082054615020751953125f, 0.0403986163437366485595703125f } },
+    [4] = { RED_HALF_MAGIC2, 3, 3, { 0.999771416187286376953125f, -0.16582702100276947021484375f, 0.00757423602044582366943359375f },
+            { 0.999579489231109619140625f, -0.4963922202587127685546875f, 0.0372092612087726593017578125f } },
+    [5] = { RED_HALF_MAGIC2, 3, 3, { 0.999696791172027587890625f, -0.1656731069087982177734375f, 0.0075143859721720218658447265625f },
+            { 0.9994032382965087890625f, -0.495580852031707763671875f, 0.03679168224334716796875f } },
+    [6] = { RED_HALF_MAGIC1, 3, 3, { 0.999696791172027587890625f, -0.1656731069087982177734375f, 0.0075143859721720218658447265625f },
+            { 0.9994032382965087890625f, -0.495580852031707763671875f, 0.03679168224334716796875f } },
+    [7] = { RED_QUARTER_CVT, 3, 3, { 0.9999962449073792f, -0.16661198437213898f, 0.008137642405927181f },
+            { 0.999993085861206f, -0.499763548374176f, 0.04051213711500168f } },
+    [8] = { RED_QUARTER_CVT, 4, 4, { 1.0f, -0.1666664183139801f, 0.00833179522305727f, -0.00019484198128338903f },
+            { 1.0f, -0.49999886751174927f, 0.041656624525785446f, -0.0013605882413685322f } },
+};
+
+static inline float f32_xor(float v, unsigned sign) {
+    uint32_t u = sf_fbits(v) ^ sign;
+    float f;
+    memcpy(&f, &u, 4);
+    return f;
+}
+
+static void sincos_f32_lane(const sincos_f32_variant* v, float angle, float* cos_out, float* sin_out) {
+    volatile float r = 0.0f, r2, sp, cp;   /* volatile: each step stays a separate rounded operation */
+    unsigned sin_sign = 0, cos_sign = 0;
+    int swap = 0;
+    if (v->reducer == RED_QUARTER_CVT || v->reducer == RED_QUARTER_MAGIC2) {
+        unsigned q;
+        volatile float qf;
+        if (v->reducer == RED_QUARTER_CVT) {
+            volatile float prod = angle * 0.63661977236758134308f;
+            const int qi = (int)nearbyintf(prod);
+            qf = (float)qi;
+            q = (unsigned)qi;
+        } else {
+            volatile float biased = fmaf(angle, 0.63661977236758134308f, 12582912.0f);
+            qf = biased - 12582912.0f;
+            q = sf_fbits(biased);
+        }
+        r = fmaf(qf, -1.57079625129699707031f, angle);
+        r = fmaf(qf, -7.54978941586159635335e-08f, r);
+        swap = (int)(q & 1u);
+        sin_sign = (q & 2u) << 30;
+        cos_sign = ((q + 1u) & 2u) << 30;
+    } else if (v->reducer == RED_HALF_MAGIC2 || v->reducer == RED_HALF_MAGIC1) {
+        volatile float biased = fmaf(angle, 0.31830988618379067154f, 12582912.0f);
+        volatile float h = biased - 12582912.0f;
+        if (v->reducer == RED_HALF_MAGIC2) {
+            r = fmaf(h, -3.141592502593994140625f, angle);
+            r = fmaf(h, -1.50995788317231927067e-07f, r);
+        } else {
+            r = fmaf(h, -3.1415927410125732421875f, angle);
+        }
+        sin_sign = cos_sign = (sf_fbits(biased) & 1u) << 31;
+    } else {
+        volatile float cycles = angle * 0.15915494309189533577f;
+        volatile float wrapped = cycles - nearbyintf(cycles);
+        sin_sign = sf_fbits(wrapped) & 0x80000000u;
+        volatile float a = fabsf(wrapped);
+        const int outer = a > 0.25f;
+        if (outer) a = 0.5f - a;
+        swap = a > 0.125f;
+        if (swap) a = 0.25f - a;
+        r = a;
+        cos_sign = (unsigned)outer << 31;
+    }
+    r2 = r * r;
+    sp = fmaf(v->sin_c[v->n_sin - 1], r2, v->sin_c[v->n_sin - 2]);
+    for (int k = v->n_sin - 3; k >= 0; --k) sp = fmaf(sp, r2, v->sin_c[k]);
+    sp = r * sp;
+    cp = fmaf(v->cos_c[v->n_cos - 1], r2, v->cos_c[v->n_cos - 2]);
+    for (int k = v->n_cos - 3; k >= 0; --k) cp = fmaf(cp, r2, v->cos_c[k]);
+    const float sm = swap ? cp : sp, cm = swap ? sp : cp;
+    *sin_out = f32_xor(sm, sin_sign);
+    *cos_out = f32_xor(cm, cos_sign);
+}
+
+/* out [2, n]: cos plane then sin plane.  iterations == 0: one evaluation; > 0: the repeated-evaluation probe
+ * (sums of `iterations` evaluations, probe <- fma(probe, 1 - 2^-24, 2^-13) between them). */
+int fpt_oracle_sincos_f32(int variant, const float* angles, float* out, int64_t n, int iterations) {
+    if (variant < 1 || variant > 8) return -1;
+    const sincos_f32_variant* v = &k_sincos_f32[variant];
+#pragma omp parallel for schedule(static)
+    for (int64_t i = 0; i < n; ++i) {
+        if (iterations <= 0) {
+            sincos_f32_lane(v, angles[i], &out[i], &out[n + i]);
+        } else {
+            volatile float cs = 0.0f, ss = 0.0f, probe = angles[i];
+            for (int it = 0; it < iterations; ++it) {
+                float c, s2;
+                sincos_f32_lane(v, probe, &c, &s2);
+                cs = cs + c;
+                ss = ss + s2;
+                probe = fmaf(probe, 0.999999940395355224609375f, 0.0001220703125f);
+            }
+            out[i] = cs; out[n + i] = ss;
+        }
+    }
+    return 0;
+}
+
 /* ------------------------------------------------------------------- RoPE */
 
 static inline uint16_t f16c(float x) { return sf_from_float(SF_FP16, x); }
@@ -430,6 +574,46 @@ void fpt_oracle_rope_table(int kind, const uint32_t* increments, uint16_t* table
                 rope_half_turn_d5_d6((uint32_t)p, increments[j], &cos_plane[p * freq_count + j], &sin_plane[p * freq_count + j]);
             else
                 rope_quarter_turn_d3_d4((uint32_t)p, increments[j], &cos_plane[p * freq_count + j], &sin_plane[p * freq_count + j]);
+        }
+}
+
+/* Table-lookup RoPE sin/cos (reference: evaluate_rope_phase_lut_fp16, sincos_kernels.cu:1350-1385): the 7 top
+ * phase bits (rounded) pick (sin, cos) of a 128-entry table, the signed remainder becomes an fp16 angle delta and
+ * one first-order step follows: sin = fma(delta, cos_b, sin_b), cos = fma(-delta, sin_b, cos_b).
+ * lut: 128 words, low half sin, high half cos.  iterations > 0: sums over positions p, p+1, ... in fp16. */
+static void rope_lut_lane(uint32_t position, uint32_t inc, const uint32_t* lut, uint16_t* cos_out, uint16_t* sin_out) {
+    const sf_format f = SF_FP16;
+    const uint32_t phase = position * inc;
+    const uint32_t index = ((phase + (1u << 24)) >> 25) & 127u;
+    const int32_t residual = (int32_t)(phase - (index << 25));
+    volatile float radians = (float)residual * 0x1.921fb6p-30f;
+    const uint16_t delta = sf_from_float(f, radians);
+    const uint16_t sin_b = (uint16_t)(lut[index] & 0xffffu), cos_b = (uint16_t)(lut[index] >> 16);
+    *sin_out = sf_fma(f, delta, cos_b, sin_b);
+    *cos_out = sf_fma(f, delta ^ 0x8000u, sin_b, cos_b);
+}
+
+void fpt_oracle_rope_table_lut(const uint32_t* increments, const uint32_t* lut, uint16_t* table, int64_t seq,
+                               int64_t freq_count, int iterations) {
+    uint16_t* cos_plane = table;
+    uint16_t* sin_plane = table + seq * freq_count;
+#pragma omp parallel for schedule(static)
+    for (int64_t p = 0; p < seq; ++p)
+        for (int64_t j = 0; j < freq_count; ++j) {
+            uint16_t c, s;
+            if (iterations <= 0) {
+                rope_lut_lane((uint32_t)p, increments[j], lut, &c, &s);
+            } else {
+                c = s = 0;
+                for (int it = 0; it < iterations; ++it) {
+                    uint16_t c1, s1;
+                    rope_lut_lane((uint32_t)p + (uint32_t)it, increments[j], lut, &c1, &s1);
+                    c = sf_add(SF_FP16, c, c1);
+                    s = sf_add(SF_FP16, s, s1);
+                }
+            }
+            cos_plane[p * freq_count + j] = c;
+            sin_plane[p * freq_count + j] = s;
         }
 }
 

@@ -46,7 +46,11 @@ void fpt_oracle_swiglu_bwd_shared_sigmoid(int sigmoid_program, const uint16_t* g
 void fpt_oracle_b3_direct_bf16(const uint16_t* scores, uint16_t* prob, uint16_t* grad, int64_t n, int log2_n);
 void fpt_oracle_b3_direct_f32(const float* scores, uint16_t* prob, uint16_t* grad, int64_t n, int log2_n);
 
+void fpt_oracle_fma16(const uint16_t* a, const uint16_t* b, const uint16_t* c, uint16_t* out, int64_t n, int dtype);
+void fpt_oracle_multiply(const uint16_t* a, const uint16_t* b, uint16_t* out, int64_t n, int dtype);
+void fpt_oracle_swish_shared_sigmoid(const uint16_t* x, const uint16_t* s, uint16_t* y, uint16_t* dy, int64_t n, int dtype);
 void fpt_oracle_exp2_hinge(const uint16_t* in, uint16_t* out, int64_t n, int set);
+int fpt_oracle_sincos_f32(int variant, const float* angles, float* out, int64_t n, int iterations);
 void fpt_oracle_exp2_hinge_repeat(const uint16_t* in, uint16_t* out, int64_t n, int set, int repeats);
 void fpt_oracle_exp2_poly3_f32(const float* in, float* out, int64_t n);
 
@@ -56,6 +60,8 @@ void fpt_oracle_sincos_packed_compute(int variant, const float* angles, uint16_t
                                       int64_t n, int iterations);
 
 void fpt_oracle_rope_table(int kind, const uint32_t* increments, uint16_t* table, int64_t seq, int64_t freq_count);
+void fpt_oracle_rope_table_lut(const uint32_t* increments, const uint32_t* lut, uint16_t* table, int64_t seq,
+                               int64_t freq_count, int iterations);
 void fpt_oracle_rope_apply(const uint16_t* q, const uint16_t* k, const uint32_t* increments, uint16_t* q_out,
                            uint16_t* k_out, int64_t B, int64_t S, int64_t Hq, int64_t Hk, int64_t D, int io_bf16);
 

@@ -66,10 +66,16 @@ def lib() -> ctypes.CDLL:
         L.fpt_oracle_b3_direct_f32.argtypes = [_f32p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_exp2_hinge.argtypes = [_u16p, _u16p, _i64, _int]
         L.fpt_oracle_exp2_hinge_repeat.argtypes = [_u16p, _u16p, _i64, _int, _int]
+        L.fpt_oracle_multiply.argtypes = [_u16p, _u16p, _u16p, _i64, _int]
+        L.fpt_oracle_fma16.argtypes = [_u16p, _u16p, _u16p, _u16p, _i64, _int]
+        L.fpt_oracle_swish_shared_sigmoid.argtypes = [_u16p, _u16p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_exp2_poly3_f32.argtypes = [_f32p, _f32p, _i64]
+        L.fpt_oracle_sincos_f32.argtypes = [_int, _f32p, _f32p, _i64, _int]
+        L.fpt_oracle_sincos_f32.restype = ctypes.c_int
         L.fpt_oracle_sincos_packed.argtypes = [_int, _f32p, _u16p, _u16p, _i64]
         L.fpt_oracle_sincos_packed_compute.argtypes = [_int, _f32p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_rope_table.argtypes = [_int, _u32p, _u16p, _i64, _i64]
+        L.fpt_oracle_rope_table_lut.argtypes = [_u32p, _u32p, _u16p, _i64, _i64, _int]
         L.fpt_oracle_rope_apply.argtypes = [_u16p, _u16p, _u32p, _u16p, _u16p, _i64, _i64, _i64, _i64, _i64, _int]
         L.fpt_oracle_attention_rows.argtypes = [_u16p, _u16p, _u16p, _f32p, _i64, _i64, _i64, _i64, _i64, _i64, _i64,
                                                 _i64p, _i64, _int, _int, ctypes.c_float, ctypes.c_float, _int]
@@ -170,6 +176,46 @@ def b3_direct(scores: np.ndarray, log2_n: int = 12, with_grad: bool = False):
     return (prob, grad) if with_grad else prob
 
 
+def multiply(a: np.ndarray, b: np.ndarray, dtype: int) -> np.ndarray:
+    a, b = _c16(a), _c16(b)
+    out = np.empty_like(a)
+    lib().fpt_oracle_multiply(_p16(a), _p16(b), _p16(out), a.size, dtype)
+    return out
+
+
+def fma16(a: np.ndarray, b: np.ndarray, c: np.ndarray, dtype: int) -> np.ndarray:
+    """One fused multiply-add per lane, a*b + c with a single rounding."""
+    a, b, c = _c16(a), _c16(b), _c16(c)
+    out = np.empty_like(a)
+    lib().fpt_oracle_fma16(_p16(a), _p16(b), _p16(c), _p16(out), a.size, dtype)
+    return out
+
+
+def fwd_deriv(function: str, variant: str, x: np.ndarray):
+    """(y, dy) of the FP16 forward-with-derivative composites; variant in {"alg", "poly", "shared"}."""
+    x = _c16(x)
+    if variant == "shared":
+        s = unary(find_program("SIGMOID_FWD_D3", FP16), x)
+        y, dy = np.empty_like(x), np.empty_like(x)
+        lib().fpt_oracle_swish_shared_sigmoid(_p16(x), _p16(s), _p16(y), _p16(dy), x.size, FP16)
+        return y, dy
+    y = unary(find_program(f"{function}_FWD_D3", FP16), x)
+    if variant == "alg":
+        ones = np.full_like(x, 0x3c00)
+        return y, binary_bwd(find_program(f"{function}_BWD_ALGEBRAIC", FP16), ones, y)
+    ones = np.full_like(x, 0x3c00)
+    return y, binary_bwd(find_program(f"{function}_BWD_D4", FP16), ones, x)
+
+
+def fused_fwd_bwd(function: str, x: np.ndarray, grad_out: np.ndarray):
+    """(y, grad_in) of the fused FP16 forward + gradient composites."""
+    x, grad_out = _c16(x), _c16(grad_out)
+    y = unary(find_program(f"{function}_FWD_D3", FP16), x)
+    if function == "SWISH":
+        return y, binary_bwd(find_program("SWISH_BWD_D4", FP16), grad_out, x)
+    return y, binary_bwd(find_program(f"{function}_BWD_ALGEBRAIC", FP16), grad_out, y)
+
+
 def exp2_hinge(x: np.ndarray, constant_set: int = 0, repeats: int = 1) -> np.ndarray:
     x = _c16(x)
     out = np.empty_like(x)
@@ -185,6 +231,21 @@ def exp2_poly3(x: np.ndarray) -> np.ndarray:
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = np.empty_like(x)
     lib().fpt_oracle_exp2_poly3_f32(x.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), x.size)
+    return out
+
+
+SINCOS_F32_VARIANTS = ("native", "d3_d4", "d3_d4_cycle", "d3_d4_magic_bias", "d5_d4_half_turn_ls", "d5_d4_half_turn_sollya",
+                       "d5_d4_half_turn_sollya_fast", "d5_d4", "d7_d6")
+
+
+def sincos_f32(variant: str | int, angles: np.ndarray, iterations: int = 0) -> np.ndarray:
+    """fp32 [2, n] (cos plane, sin plane) of one fp32 polynomial variant (1..8; the native control has no oracle)."""
+    idx = SINCOS_F32_VARIANTS.index(variant) if isinstance(variant, str) else int(variant)
+    angles = np.ascontiguousarray(angles, dtype=np.float32)
+    out = np.empty((2, angles.size), dtype=np.float32)
+    rc = lib().fpt_oracle_sincos_f32(idx, angles.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), angles.size, iterations)
+    if rc != 0:
+        raise ValueError(f"no fp32 sin/cos oracle for variant {variant!r}")
     return out
 
 
@@ -205,6 +266,21 @@ def rope_table(kind: int, increments: np.ndarray, seq: int) -> np.ndarray:
     inc = np.ascontiguousarray(increments).view(np.uint32)
     table = np.empty((2, seq, inc.size), dtype=np.uint16)
     lib().fpt_oracle_rope_table(kind, inc.ctypes.data_as(_u32p), _p16(table), seq, inc.size)
+    return table
+
+
+def rope_phase_table() -> np.ndarray:
+    """The [128, 2] fp16 table the look-up variant expects: (sin, cos) of 2*pi*i/128, as uint16 bit patterns."""
+    t = 2.0 * np.pi * np.arange(128) / 128.0
+    return np.stack([np.sin(t), np.cos(t)], axis=1).astype(np.float16).view(np.uint16)
+
+
+def rope_table_lut(increments: np.ndarray, phase_table: np.ndarray, seq: int, iterations: int = 0) -> np.ndarray:
+    inc = np.ascontiguousarray(increments).view(np.uint32)
+    lut = np.ascontiguousarray(phase_table, dtype=np.uint16).reshape(128, 2).view(np.uint32).reshape(128)
+    table = np.empty((2, seq, inc.size), dtype=np.uint16)
+    lib().fpt_oracle_rope_table_lut(inc.ctypes.data_as(_u32p), lut.ctypes.data_as(_u32p), _p16(table), seq, inc.size,
+                                    iterations)
     return table
 
 
