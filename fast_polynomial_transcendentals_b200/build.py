@@ -18,6 +18,8 @@ PKG = Path(__file__).resolve().parent
 CSRC = PKG / "csrc"
 OBJ = PKG / "_build"
 LIB = PKG / "libfpt_b200.so"
+COMPAT_LIB = PKG / "libfpt_b200_compat.so"          # the reference's launch_* names over the fpt_* C ABI
+COMPAT_SRC = CSRC / "fpt_compat_launch.cpp"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
               "--expt-relaxed-constexpr", "-I", str(PKG.parent / "include")]
@@ -85,7 +87,22 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             raise RuntimeError(f"link failed:\n{proc.stderr[-4000:]}")
         if verbose:
             print(f"linked {LIB}")
+    _build_compat(force, verbose)
     return LIB
+
+
+def _build_compat(force: bool, verbose: bool) -> Path:
+    """Host-only shim library; resolves fpt_* from libfpt_b200.so beside it (rpath $ORIGIN)."""
+    deps = [COMPAT_SRC, LIB, PKG.parent / "include" / "fpt_b200.h", PKG.parent / "include" / "fpt_b200_compat.h"]
+    if force or _stale(COMPAT_LIB, deps):
+        cmd = [nvcc(), "-O2", "-std=c++17", "-Xcompiler", "-fPIC", "-shared", "-o", str(COMPAT_LIB), str(COMPAT_SRC),
+               "-L", str(PKG), "-lfpt_b200", "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart"]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"compat link failed:\n{proc.stderr[-4000:]}")
+        if verbose:
+            print(f"linked {COMPAT_LIB}")
+    return COMPAT_LIB
 
 
 if __name__ == "__main__":

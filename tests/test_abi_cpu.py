@@ -10,9 +10,9 @@ import pytest
 ROOT = Path(__file__).resolve().parents[1]
 
 
-def declared_symbols():
+def declared_symbols(header_name="fpt_b200.h"):
     names = []
-    for header in sorted((ROOT / "include").glob("*.h")):
+    for header in [ROOT / "include" / header_name]:
         text = re.sub(r"/\*.*?\*/", "", header.read_text(), flags=re.S)
         text = re.sub(r"//[^\n]*", "", text)
         names += re.findall(r"\b((?:fpt|launch)_\w+)\s*\(", text)
@@ -25,6 +25,17 @@ def test_library_exports_every_declared_symbol(fpt):
     assert len(names) >= 12
     missing = [n for n in names if not hasattr(lib, n)]
     assert not missing, missing
+
+
+def test_compat_header_symbols_are_all_exported():
+    lib = ctypes.CDLL(str(ROOT / "fast_polynomial_transcendentals_b200" / "libfpt_b200_compat.so"))
+    names = declared_symbols("fpt_b200_compat.h")
+    assert len(names) == 223
+    assert not [n for n in names if not hasattr(lib, n)]
+
+
+def test_every_header_is_covered():
+    assert sorted(p.name for p in (ROOT / "include").glob("*.h")) == ["fpt_b200.h", "fpt_b200_compat.h"]
 
 
 def test_every_bound_signature_is_declared(fpt):
@@ -83,3 +94,26 @@ def test_op_surface_rejects_cpu_tensors():
     from fast_polynomial_transcendentals_b200 import spline_ops
     with pytest.raises(RuntimeError, match="must be a CUDA tensor"):
         spline_ops.sigmoid_fwd_d3(torch.zeros(8, dtype=torch.float16))
+
+
+def test_compat_library_exports_every_launch_symbol_of_the_reference():
+    """libfpt_b200_compat.so carries the reference's launch_* names (fixture written from the reference's C++ by
+    tests/golden/make_op_surface.py); the generated header declares each with the same number of parameters."""
+    import ctypes
+    import json
+    import re
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parent.parent
+    lib_path = root / "fast_polynomial_transcendentals_b200" / "libfpt_b200_compat.so"
+    assert lib_path.exists(), "build the library first: python -m fast_polynomial_transcendentals_b200.build"
+    lib = ctypes.CDLL(str(lib_path))
+    surface = json.loads((root / "tests" / "golden" / "op_surface.json").read_text())
+    header = (root / "include" / "fpt_b200_compat.h").read_text()
+    declared = {name: params.count(",") + 1 for name, params in re.findall(r"void (launch_[a-z0-9_]+)\(([^)]*)\);", header)}
+    assert len(surface["launch_symbols"]) == 221
+    for name, parameter_count in surface["launch_symbols"]:
+        assert hasattr(lib, name), name
+        assert declared.get(name) == parameter_count, (name, declared.get(name), parameter_count)
+    assert lib.fpt_compat_symbol_count() == len(declared) == 221
+    assert lib.fpt_compat_last_status() == 0

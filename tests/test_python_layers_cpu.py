@@ -121,3 +121,19 @@ def test_sincos_polynomial_budgets_and_quadrants():
         reduce_to_quarter_turn(torch.arange(4))
     inc = rope_phase_increments(128)
     assert inc.dtype == torch.int32 and inc.numel() == 64 and int(inc[0]) == 683565276
+
+
+def test_every_name_of_the_reference_operator_module_exists():
+    """The fixture lists what the reference's extension module and dispatcher library export
+    (tests/golden/make_op_surface.py wrote it from the reference's C++ source)."""
+    import json
+    from pathlib import Path
+
+    import torch
+
+    from fast_polynomial_transcendentals_b200 import spline_compile, spline_ops  # noqa: F401  (registers the library)
+    surface = json.loads((Path(__file__).parent / "golden" / "op_surface.json").read_text())
+    missing = [name for name in surface["pybind"] if not callable(getattr(spline_ops, name, None))]
+    assert not missing, missing
+    missing = [name for name in surface["dispatcher"] if not hasattr(torch.ops.spline_ops, name)]
+    assert not missing, missing
