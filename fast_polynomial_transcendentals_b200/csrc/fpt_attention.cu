@@ -331,13 +331,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (int w = 0; w < 32; ++w) {
                         const int i = half * 32 + w;
                         const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
-                        uint32_t pr = b3_direct_select_late(x, p.b3);
-                        if (diagonal) {  // keys beyond the diagonal contribute nothing
-                            const int col = j * kTileN + 2 * i;
-                            if (col > row) pr &= 0xffff0000u;
-                            if (col + 1 > row) pr &= 0x0000ffffu;
+                        pw[w] = b3_direct_select_late(x, p.b3);
+                    }
+                    if (diagonal) {  // keys beyond the diagonal contribute nothing; a branch of its own, taken by
+                                     // the whole slot at once, so that the other tiles carry no compare / select
+#pragma unroll
+                        for (int w = 0; w < 32; ++w) {
+                            const int col = j * kTileN + 2 * (half * 32 + w);
+                            if (col > row) pw[w] &= 0xffff0000u;
+                            if (col + 1 > row) pw[w] &= 0x0000ffffu;
                         }
-                        pw[w] = pr;
                     }
                     if (half == 1) FPT_TRACE(s, 3);  // probabilities computed
                     hand_over(half, pw);
