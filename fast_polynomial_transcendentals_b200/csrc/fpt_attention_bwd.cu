@@ -1,0 +1,508 @@
+// Attention backward for sm_100a, same score-mods as the forward (soft-capped softmax, direct sigmoid, plain softmax).
+//
+// Two launches of one kernel template, each deterministic and free of atomics (S and dP are recomputed in both):
+//   WHICH = 0  dQ:      one CTA per (batch, query head, 128 query rows), loops over key tiles
+//                       S = Q K^T,  dP = dO V^T,  dS = f(S, dP),  dQ += dS K
+//   WHICH = 1  dK, dV:  one CTA per (batch, kv head, 128 keys), loops over the query heads of its group and their
+//                       query tiles;  S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
+// Written once in terms of "fixed" tiles X, Y (loaded once) and "streamed" tiles U, W (2-stage ring):
+//   S = X U^T and dP = Y W^T (both operands K-major from shared memory),
+//   acc0 += dS U and (WHICH = 1) acc1 += P W, with P / dS read from tensor memory and U / W as MN-major operands.
+// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
+// tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
+// (the backward has no row reduction, so the split needs no exchange).
+// Tensor memory: S 0..127 (bf16 P over its first 64 columns), dP 128..255 (bf16 dS over its first 64), acc0 256..383,
+// acc1 384..511.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
+// Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
+#include <cstring>
+#include <type_traits>
+
+#include "fpt_common.h"
+#include "fpt_programs.h"
+#include "fpt_scoremod.cuh"
+#include "fpt_sm100.cuh"
+
+namespace fpt {
+namespace {
+
+using namespace sm100;
+
+constexpr int kTile = 128;
+constexpr int kDim = 128;
+constexpr int kRing = 2;
+constexpr uint32_t kPanelB = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
+constexpr uint32_t kTileB = 2 * kPanelB;
+constexpr int kBwdThreads = 384;
+constexpr float kLog2eB = 1.4426950408889634f;
+
+struct BwdSmem {
+    alignas(1024) uint8_t x[kTileB];
+    alignas(1024) uint8_t y[kTileB];
+    alignas(1024) uint8_t u[kRing][kTileB];
+    alignas(1024) uint8_t w[kRing][kTileB];
+    alignas(16) float lse2[kRing][kTile];      // WHICH = 1: per streamed query column
+    alignas(16) float delta[kRing][kTile];
+    alignas(8) uint64_t xy_full;
+    uint64_t uw_full[kRing], uw_empty[kRing];
+    uint64_t s_full, ld_done, p_full, acc_done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct BwdParams {
+    uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
+    uint16_t* out1;        // dV (WHICH 1)
+    const float* lse2;     // workspace plane 0: [B, Hq, S]
+    const float* delta;    // workspace plane 1
+    int batch, seq, q_heads, kv_heads;
+    int causal;
+    int softcap_grad;      // 0 analytical derivative of the polynomial, 1 the identity 1 - t^2
+    float scale, softcap;
+    float tanh_clamp, tanh_d[4];   // derivative of the tanh program: d0 + d1 t + d2 t^2 + d3 t^3 for t < clamp
+    uint32_t* status;
+    ProgramWords tanh;
+    B3Words b3;
+};
+
+enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone };
+
+__device__ __forceinline__ float ex2f(float x) { return mufu_ex2(x); }
+
+// ---- pre-pass: lse2 = lse * log2(e), delta = sum_d dO * O, one warp per (batch, head, row) ------------------
+struct PrepassArgs {
+    const uint16_t* out;
+    const uint16_t* dout;
+    const float* lse;       // [B, Hq, S]
+    float* lse2;
+    float* delta;
+    int64_t o_stride_b, o_stride_s, o_stride_h, do_stride_b, do_stride_s, do_stride_h;
+    int batch, seq, q_heads;
+};
+
+__global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const PrepassArgs a) {
+    const int lane = threadIdx.x & 31;
+    const int64_t rows = int64_t(a.batch) * a.q_heads * a.seq;
+#pragma unroll 1
+    for (int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += int64_t(gridDim.x) * 8) {
+        const int s = int(row % a.seq);
+        const int64_t bh = row / a.seq;
+        const int h = int(bh % a.q_heads), b = int(bh / a.q_heads);
+        const uint2 o = *reinterpret_cast<const uint2*>(a.out + b * a.o_stride_b + s * a.o_stride_s + h * a.o_stride_h + lane * 4);
+        const uint2 d = *reinterpret_cast<const uint2*>(a.dout + b * a.do_stride_b + s * a.do_stride_s + h * a.do_stride_h + lane * 4);
+        float acc = Sfu<kBf16>::lo(o.x) * Sfu<kBf16>::lo(d.x);
+        acc = fmaf(Sfu<kBf16>::hi(o.x), Sfu<kBf16>::hi(d.x), acc);
+        acc = fmaf(Sfu<kBf16>::lo(o.y), Sfu<kBf16>::lo(d.y), acc);
+        acc = fmaf(Sfu<kBf16>::hi(o.y), Sfu<kBf16>::hi(d.y), acc);
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+        if (lane == 0) {
+            a.delta[row] = acc;
+            a.lse2[row] = a.lse[row] * kLog2eB;
+        }
+    }
+}
+
+// bf16x2 of two fp32 values (low lane first)
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return Sfu<kBf16>::pack(lo, hi); }
+
+// One pair of columns of one row: raw scores s0, s1 and dP values d0, d1 -> bf16x2 words of P and of dS (the factor
+// `scale` common to every dS is applied once, in the epilogue).
+//   l0, l1: lse * log2(e) of the two (row, column) positions' query;  t0, t1: their delta;  m0, m1: masked out
+template <int MODE>
+__device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s1, float d0, float d1, float l0, float l1,
+                                           float t0, float t1, bool m0, bool m1, uint32_t& p_word, uint32_t& ds_word) {
+    if constexpr (MODE == 1) {
+        const uint32_t x = pack_bf16(s0 * p.scale, s1 * p.scale);
+        uint32_t grad;
+        uint32_t pr = b3_direct_with_grad(x, p.b3, grad);
+        float g0 = Sfu<kBf16>::lo(grad) * d0, g1 = Sfu<kBf16>::hi(grad) * d1;
+        if (m0) { pr &= 0xffff0000u; g0 = 0.0f; }
+        if (m1) { pr &= 0x0000ffffu; g1 = 0.0f; }
+        p_word = pr;
+        ds_word = pack_bf16(g0, g1);
+    } else if constexpr (MODE == 2) {
+        const float c = p.scale * kLog2eB;
+        float p0 = ex2f(fmaf(s0, c, -l0)), p1 = ex2f(fmaf(s1, c, -l1));
+        if (m0) p0 = 0.0f;
+        if (m1) p1 = 0.0f;
+        p_word = pack_bf16(p0, p1);
+        ds_word = pack_bf16(p0 * (d0 - t0), p1 * (d1 - t1));
+    } else {
+        const float in = p.scale / p.softcap, out = p.softcap * kLog2eB;
+        const uint32_t x = pack_bf16(s0 * in, s1 * in);
+        const uint32_t th = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
+        const float th0 = Sfu<kBf16>::lo(th), th1 = Sfu<kBf16>::hi(th);
+        float p0 = ex2f(fmaf(th0, out, -l0)), p1 = ex2f(fmaf(th1, out, -l1));
+        if (m0) p0 = 0.0f;
+        if (m1) p1 = 0.0f;
+        float g0, g1;
+        if (p.softcap_grad == 1) {
+            g0 = fmaf(-th0, th0, 1.0f);
+            g1 = fmaf(-th1, th1, 1.0f);
+        } else {
+            const float a0 = fabsf(Sfu<kBf16>::lo(x)), a1 = fabsf(Sfu<kBf16>::hi(x));
+            const float c0 = fminf(a0, p.tanh_clamp), c1 = fminf(a1, p.tanh_clamp);
+            g0 = fmaf(fmaf(fmaf(p.tanh_d[3], c0, p.tanh_d[2]), c0, p.tanh_d[1]), c0, p.tanh_d[0]);
+            g1 = fmaf(fmaf(fmaf(p.tanh_d[3], c1, p.tanh_d[2]), c1, p.tanh_d[1]), c1, p.tanh_d[0]);
+            if (!(a0 < p.tanh_clamp) || !(fabsf(th0) < 1.0f)) g0 = 0.0f;   // clamped input or saturated output: flat
+            if (!(a1 < p.tanh_clamp) || !(fabsf(th1) < 1.0f)) g1 = 0.0f;
+        }
+        p_word = pack_bf16(p0, p1);
+        ds_word = pack_bf16(p0 * (d0 - t0) * g0, p1 * (d1 - t1) * g1);
+    }
+}
+
+template <int MODE, int WHICH>
+__global__ void __launch_bounds__(kBwdThreads, 1)
+attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                     const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
+                     const BwdParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = blockIdx.x;                  // query head (WHICH 0) or kv head (WHICH 1)
+    const int tile = p.causal && WHICH == 0 ? int(gridDim.y) - 1 - int(blockIdx.y) : int(blockIdx.y);  // long loops first
+    const int b = blockIdx.z;
+    const int total = p.seq / kTile;
+    const int group = p.q_heads / p.kv_heads;
+    const int row0 = tile * kTile;                // first row of the fixed tiles
+    // inner loop: WHICH 0 walks key tiles 0..(causal ? tile : total-1); WHICH 1 walks, for each query head of the
+    // group, query tiles (causal ? tile : 0)..total-1
+    const int first_inner = (WHICH == 1 && p.causal) ? tile : 0;
+    const int per_head = WHICH == 0 ? (p.causal ? tile + 1 : total) : total - first_inner;
+    const int n_inner = WHICH == 0 ? per_head : per_head * group;
+    const int fixed_head_x = head;
+    const int stream_head0 = WHICH == 0 ? head / group : head * group;
+    volatile uint32_t* abort_flag = &sm.abort_flag;
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.xy_full, 1);
+        for (int st = 0; st < kRing; ++st) {
+            mbar_init(&sm.uw_full[st], 1);
+            mbar_init(&sm.uw_empty[st], 1);
+        }
+        mbar_init(&sm.s_full, 1);
+        mbar_init(&sm.ld_done, 8);      // one arrive per score-mod warp: its S and dP values are in registers
+        mbar_init(&sm.p_full, 8);       // one arrive per score-mod warp: its P and dS words are in tensor memory
+        mbar_init(&sm.acc_done, 1);
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        mbar_fence_init();
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(&map_y);
+        tma_prefetch_descriptor(&map_u);
+        tma_prefetch_descriptor(&map_w);
+    }
+    if (warp == 1) {
+        tmem_alloc(&sm.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const bool skip = sm.abort_flag != 0u;
+
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+      if (skip || warp >= 2) {
+        // warps 2 and 3 only hold registers for the others
+      } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&sm.xy_full, 2 * kTileB);
+            tma_load_4d(sm.x, &map_x, &sm.xy_full, 0, row0, fixed_head_x, b);
+            tma_load_4d(sm.x + kPanelB, &map_x, &sm.xy_full, 64, row0, fixed_head_x, b);
+            tma_load_4d(sm.y, &map_y, &sm.xy_full, 0, row0, fixed_head_x, b);
+            tma_load_4d(sm.y + kPanelB, &map_y, &sm.xy_full, 64, row0, fixed_head_x, b);
+            bool ok = true;
+            for (int t = 0; t < n_inner && ok; ++t) {
+                const int st = t % kRing;
+                const uint32_t ph = uint32_t(t / kRing) & 1u;
+                if (t >= kRing) ok = mbar_wait(&sm.uw_empty[st], ph ^ 1u, abort_flag, p.status, kBwdUwEmpty);
+                if (!ok) break;
+                const int g = WHICH == 0 ? 0 : t / per_head;
+                const int r0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile;
+                const int sh = stream_head0 + g;
+                const uint32_t vec_bytes = WHICH == 1 && MODE != 1 ? 2u * kTile * 4u : 0u;
+                mbar_arrive_expect_tx(&sm.uw_full[st], 2 * kTileB + vec_bytes);
+                tma_load_4d(sm.u[st], &map_u, &sm.uw_full[st], 0, r0, sh, b);
+                tma_load_4d(sm.u[st] + kPanelB, &map_u, &sm.uw_full[st], 64, r0, sh, b);
+                tma_load_4d(sm.w[st], &map_w, &sm.uw_full[st], 0, r0, sh, b);
+                tma_load_4d(sm.w[st] + kPanelB, &map_w, &sm.uw_full[st], 64, r0, sh, b);
+                if (vec_bytes) {   // per-query vectors of the streamed query tile
+                    const int64_t off = (int64_t(b) * p.q_heads + sh) * p.seq + r0;
+                    bulk_load_1d(sm.lse2[st], p.lse2 + off, kTile * 4u, &sm.uw_full[st]);
+                    bulk_load_1d(sm.delta[st], p.delta + off, kTile * 4u, &sm.uw_full[st]);
+                }
+            }
+        }
+      } else {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
+            constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
+            constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            const uint32_t x_lo = umma_smem_desc_lo(smem_u32(sm.x), 16), y_lo = umma_smem_desc_lo(smem_u32(sm.y), 16);
+            bool ok = mbar_wait(&sm.xy_full, 0, abort_flag, p.status, kBwdXY);
+            for (int t = 0; t < n_inner && ok; ++t) {
+                const int st = t % kRing;
+                const uint32_t ph = uint32_t(t / kRing) & 1u;
+                ok = mbar_wait(&sm.uw_full[st], ph, abort_flag, p.status, kBwdUwFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                const uint32_t u_k = umma_smem_desc_lo(smem_u32(sm.u[st]), 16), w_k = umma_smem_desc_lo(smem_u32(sm.w[st]), 16);
+                const uint32_t u_mn = umma_smem_desc_lo(smem_u32(sm.u[st]), kPanelB), w_mn = umma_smem_desc_lo(smem_u32(sm.w[st]), kPanelB);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {     // S = X U^T
+                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
+                    umma_ss_words(tmem, x_lo + off, u_k + off, desc_hi, idesc_kk, kk > 0);
+                }
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {     // dP = Y W^T
+                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
+                    umma_ss_words(tmem + 128u, y_lo + off, w_k + off, desc_hi, idesc_kk, kk > 0);
+                }
+                umma_commit(&sm.s_full);
+                ok = mbar_wait(&sm.p_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdPFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)       // acc0 += dS U
+                    umma_ts_words(tmem + 256u, tmem + 128u + 8u * kk, u_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn,
+                                  t > 0 || kk > 0);
+                if constexpr (WHICH == 1) {
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)   // acc1 += P W
+                        umma_ts_words(tmem + 384u, tmem + 8u * kk, w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn,
+                                      t > 0 || kk > 0);
+                }
+                umma_commit(&sm.uw_empty[st]);
+            }
+            if (ok) umma_commit(&sm.acc_done);
+        }
+      }
+    } else {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+      if (!skip) {
+        // ------------------------------------------------------------------ score-mod warps
+        const int quarter = warp & 3, half = (warp - 4) >> 2;
+        const int r = 32 * quarter + lane;                       // row of the fixed tile = tensor-memory lane
+        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        const uint32_t t_s = tmem + lane_base + uint32_t(64 * half);
+        const uint32_t t_dp = tmem + lane_base + 128u + uint32_t(64 * half);
+        const uint32_t t_p = tmem + lane_base + uint32_t(32 * half);          // bf16 pairs: 32 words per half
+        const uint32_t t_ds = tmem + lane_base + 128u + uint32_t(32 * half);
+        float row_lse2 = 0.0f, row_delta = 0.0f;
+        if (WHICH == 0 && MODE != 1) {
+            const int64_t off = (int64_t(b) * p.q_heads + head) * p.seq + row0 + r;
+            row_lse2 = p.lse2[off];
+            row_delta = p.delta[off];
+        }
+        bool ok = true;
+        for (int t = 0; t < n_inner && ok; ++t) {
+            const int st = t % kRing;
+            ok = mbar_wait(&sm.s_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdSFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t sv[64], dv[64];
+            tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
+            tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+            tmem_ld_32x32b_x32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
+            tmem_ld_32x32b_x32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
+            tmem_ld_wait();
+            // P and dS overwrite columns from which the other warp of this lane quarter reads S and dP: every load
+            // first, then the stores (a bounded mbarrier wait rather than a named barrier, so that a warp that gave
+            // up after a timeout cannot leave the others waiting for ever)
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.ld_done);
+            ok = mbar_wait(&sm.ld_done, uint32_t(t) & 1u, abort_flag, p.status, kBwdLdDone);
+            if (WHICH == 1 && MODE != 1)   // the per-query vectors arrived on this barrier (already complete here)
+                ok = ok && mbar_wait(&sm.uw_full[st], uint32_t(t / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
+            if (!ok) break;
+            const int g = WHICH == 0 ? 0 : t / per_head;
+            const int c0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile + 64 * half;   // first column
+            const bool diagonal = p.causal && (c0 - 64 * half == row0);
+            uint32_t pw[32], dsw[32];
+            auto columns = [&](auto masked) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const int c = 2 * i;                 // column pair inside this half
+                    float l0 = row_lse2, l1 = row_lse2, e0 = row_delta, e1 = row_delta;
+                    if (WHICH == 1 && MODE != 1) {
+                        const float2 lv = *reinterpret_cast<const float2*>(&sm.lse2[st][64 * half + c]);
+                        const float2 dl = *reinterpret_cast<const float2*>(&sm.delta[st][64 * half + c]);
+                        l0 = lv.x; l1 = lv.y; e0 = dl.x; e1 = dl.y;
+                    }
+                    bool m0 = false, m1 = false;
+                    if constexpr (decltype(masked)::value) {   // rows are queries (WHICH 0) or keys (WHICH 1)
+                        const int row_abs = row0 + r, col_abs = c0 + c;
+                        m0 = WHICH == 0 ? col_abs > row_abs : row_abs > col_abs;
+                        m1 = WHICH == 0 ? col_abs + 1 > row_abs : row_abs > col_abs + 1;
+                    }
+                    score_pair<MODE>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
+                                     __uint_as_float(dv[c + 1]), l0, l1, e0, e1, m0, m1, pw[i], dsw[i]);
+                }
+            };
+            if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
+            else columns(std::false_type{});
+            tmem_st_32x32b_x32(t_p, pw);
+            tmem_st_32x32b_x32(t_ds, dsw);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_full);
+        }
+        if (ok && n_inner > 0) {
+            ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
+            if (ok) {
+                tc_fence_after_sync();
+                const int64_t heads_out = WHICH == 0 ? p.q_heads : p.kv_heads;
+                const int64_t off = ((int64_t(b) * p.seq + row0 + r) * heads_out + head) * kDim + 64 * half;
+#pragma unroll
+                for (int acc = 0; acc <= WHICH; ++acc) {
+                    const float f = acc == 0 ? p.scale : 1.0f;
+                    uint16_t* dst = (acc == 0 ? p.out0 : p.out1) + off;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(tmem + lane_base + 256u + 128u * acc + uint32_t(64 * half + 32 * c), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 o;
+                            o.x = pack_bf16(__uint_as_float(v[q4 * 8 + 0]) * f, __uint_as_float(v[q4 * 8 + 1]) * f);
+                            o.y = pack_bf16(__uint_as_float(v[q4 * 8 + 2]) * f, __uint_as_float(v[q4 * 8 + 3]) * f);
+                            o.z = pack_bf16(__uint_as_float(v[q4 * 8 + 4]) * f, __uint_as_float(v[q4 * 8 + 5]) * f);
+                            o.w = pack_bf16(__uint_as_float(v[q4 * 8 + 6]) * f, __uint_as_float(v[q4 * 8 + 7]) * f);
+                            reinterpret_cast<uint4*>(dst + 32 * c)[q4] = o;
+                        }
+                    }
+                }
+            }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+}  // namespace
+}  // namespace fpt
+
+using namespace fpt;
+
+extern "C" int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads) {
+    if (batch <= 0 || seq <= 0 || q_heads <= 0) return 0;
+    return 2 * batch * q_heads * seq * int64_t(sizeof(float));
+}
+
+extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+                                 const void* v, const void* out, const void* lse, void* workspace,
+                                 int64_t workspace_bytes, int64_t batch, int64_t seq, int64_t q_heads, int64_t kv_heads,
+                                 int64_t head_dim, const int64_t* q_strides, const int64_t* k_strides,
+                                 const int64_t* v_strides, const int64_t* out_strides, const int64_t* dout_strides,
+                                 int mode, int causal, float scale, float softcap, int log2_n, int softcap_grad,
+                                 void* status, fpt_stream_t stream) {
+    if (!dq || !dk || !dv || !dout || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !dout_strides)
+        return FPT_ERR_NULL_POINTER;
+    if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
+    if (head_dim != kDim || seq % kTile != 0 || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
+    if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
+    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
+    if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
+    if (mode == FPT_ATTN_SIGMOID_DIRECT && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
+    if (softcap_grad != FPT_SOFTCAP_GRAD_ANALYTICAL && softcap_grad != FPT_SOFTCAP_GRAD_ONE_MINUS_T2) return FPT_ERR_BAD_ENUM;
+    const bool normalised = mode != FPT_ATTN_SIGMOID_DIRECT;
+    if (normalised) {
+        if (!out || !lse || !out_strides || !workspace) return FPT_ERR_NULL_POINTER;
+        if (workspace_bytes < fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) return FPT_ERR_SCRATCH_TOO_SMALL;
+        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return FPT_ERR_MISALIGNED;
+        for (int i = 0; i < 3; ++i)
+            if ((out_strides[i] * 2) & 7 || (dout_strides[i] * 2) & 7) return FPT_ERR_MISALIGNED;
+        if ((reinterpret_cast<uintptr_t>(out) & 7u) || (reinterpret_cast<uintptr_t>(dout) & 7u)) return FPT_ERR_MISALIGNED;
+    }
+    if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15u)
+        return FPT_ERR_MISALIGNED;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+
+    auto make_map = [&](CUtensorMap* map, const void* base, const int64_t* st, int64_t heads) {
+        const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(seq), uint64_t(heads), uint64_t(batch)};
+        const uint64_t strides[3] = {uint64_t(st[1]) * 2, uint64_t(st[2]) * 2, uint64_t(st[0]) * 2};
+        return make_tensor_map_bf16_4d(map, base, dims, strides, kTile);
+    };
+    CUtensorMap map_q, map_k, map_v, map_do;
+    if (int rc = make_map(&map_q, q, q_strides, q_heads)) return rc;
+    if (int rc = make_map(&map_k, k, k_strides, kv_heads)) return rc;
+    if (int rc = make_map(&map_v, v, v_strides, kv_heads)) return rc;
+    if (int rc = make_map(&map_do, dout, dout_strides, q_heads)) return rc;
+
+    float* lse2 = static_cast<float*>(workspace);
+    float* delta = lse2 ? lse2 + batch * q_heads * seq : nullptr;
+    if (normalised) {
+        PrepassArgs a{};
+        a.out = static_cast<const uint16_t*>(out);
+        a.dout = static_cast<const uint16_t*>(dout);
+        a.lse = static_cast<const float*>(lse);
+        a.lse2 = lse2;
+        a.delta = delta;
+        a.o_stride_b = out_strides[0]; a.o_stride_s = out_strides[1]; a.o_stride_h = out_strides[2];
+        a.do_stride_b = dout_strides[0]; a.do_stride_s = dout_strides[1]; a.do_stride_h = dout_strides[2];
+        a.batch = int(batch); a.seq = int(seq); a.q_heads = int(q_heads);
+        int64_t grid = (batch * q_heads * seq + 7) / 8;
+        const int64_t cap = int64_t(dev.sm_count) * 32;
+        if (grid > cap) grid = cap;
+        attention_bwd_prepass_kernel<<<unsigned(grid), 256, 0, stream>>>(a);
+        if (int rc = cuda_status(cudaGetLastError())) return rc;
+    }
+
+    BwdParams p{};
+    p.lse2 = lse2;
+    p.delta = delta;
+    p.batch = int(batch); p.seq = int(seq); p.q_heads = int(q_heads); p.kv_heads = int(kv_heads);
+    p.causal = causal ? 1 : 0;
+    p.softcap_grad = softcap_grad;
+    p.scale = scale; p.softcap = softcap;
+    p.status = static_cast<uint32_t*>(status);
+    const ProgramRow* tanh_row = find_program(FPT_FN_TANH, FPT_FWD, 4, FPT_BF16, FPT_SRC_CURRENT);
+    if (!tanh_row || tanh_row->shape != kOddSat) return FPT_ERR_UNKNOWN_PROGRAM;
+    p.tanh = program_words(*tanh_row);
+    auto bf16_value = [](uint16_t bits) {
+        const uint32_t u = uint32_t(bits) << 16;
+        float f;
+        memcpy(&f, &u, 4);
+        return f;
+    };
+    // y = t (c1 + t (c2 + t (c3 + t c4)))  ->  dy/dt = c1 + 2 c2 t + 3 c3 t^2 + 4 c4 t^3
+    p.tanh_clamp = bf16_value(tanh_row->clamp);
+    for (int i = 0; i < 4; ++i) p.tanh_d[i] = float(i + 1) * bf16_value(tanh_row->c[i]);
+    p.b3 = b3_words(mode == FPT_ATTN_SIGMOID_DIRECT ? log2_n : 12);
+
+    const size_t smem = sizeof(BwdSmem) + 1024;
+    static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "shared memory budget");
+    const unsigned tiles = unsigned(seq / kTile);
+    auto launch = [&](auto kernel, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap& mu,
+                      const CUtensorMap& mw, uint16_t* o0, uint16_t* o1) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
+        BwdParams pp = p;
+        pp.out0 = o0;
+        pp.out1 = o1;
+        const dim3 grid{heads, tiles, unsigned(batch)};
+        kernel<<<grid, kBwdThreads, smem, stream>>>(mx, my, mu, mw, pp);
+        return cuda_status(cudaGetLastError());
+    };
+    auto run = [&](auto mode_tag) {
+        constexpr int M = decltype(mode_tag)::value;
+        // dQ: fixed Q, dO; streamed K, V.   dK, dV: fixed K, V; streamed Q, dO
+        if (int rc = launch(attention_bwd_kernel<M, 0>, unsigned(q_heads), map_q, map_do, map_k, map_v,
+                            static_cast<uint16_t*>(dq), nullptr))
+            return rc;
+        return launch(attention_bwd_kernel<M, 1>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
+                      static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv));
+    };
+    if (mode == FPT_ATTN_SOFTCAP_TANH) return run(IC<0>{});
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return run(IC<1>{});
+    return run(IC<2>{});
+}

@@ -260,6 +260,26 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
                              const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
                              int exp2_emu_freq, void* status, fpt_stream_t stream);
 
+/* ---- attention backward for the same three modes, bf16, head_dim 128, seq a multiple of 128
+ *      replaces the backward of the patched FlashAttention interface the reference drives through
+ *      `flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale, causal, softcap, score_mod=, score_mod_bwd=,
+ *      sigmoid_attention=, ...) -> (dq, dk, dv)` (reference: src/sfu_repro/fa4.py:828-859).
+ *      q, k, v, out, dout: (batch, seq, head, dim) tensors through element strides as in the forward; lse fp32
+ *      [B,Hq,S] from the forward; dq [B,S,Hq,D], dk / dv [B,S,Hkv,D] contiguous bf16 outputs.
+ *      Soft-max modes need out, lse and a workspace of fpt_attention_bwd_workspace_bytes() (16-byte aligned);
+ *      FPT_ATTN_SIGMOID_DIRECT needs none of the three (NULL accepted): dS = dP * p(x) * (intercept + slope*clamp(x)),
+ *      the coupled derivative of the direct cubic.  softcap_grad picks d tanh_poly / dx for FPT_ATTN_SOFTCAP_TANH:
+ *      the derivative of the polynomial itself (zero where the input is clamped or the output saturated), or
+ *      1 - t^2 of its value.  Deterministic: two launches (dQ; dK and dV), no atomics.  status as in the forward. */
+enum { FPT_SOFTCAP_GRAD_ANALYTICAL = 0, FPT_SOFTCAP_GRAD_ONE_MINUS_T2 = 1 };
+int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
+int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k, const void* v,
+                      const void* out, const void* lse, void* workspace, int64_t workspace_bytes, int64_t batch,
+                      int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
+                      const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
+                      const int64_t* dout_strides, int mode, int causal, float scale, float softcap, int log2_n,
+                      int softcap_grad, void* status, fpt_stream_t stream);
+
 /* ---- diagnostic: one 128x128x128 bf16 tile through the tensor-core building blocks of the attention kernel
  *      (no counterpart in the reference).  a, b: bf16 [128,128] row-major; c: fp32 [128,128];
  *      mode 0: c = a * b^T (both operands K-major in shared memory); mode 1: c = a * b (a staged in tensor memory,

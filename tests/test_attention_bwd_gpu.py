@@ -1,0 +1,140 @@
+"""GPU: attention backward (dQ, dK, dV) of the three modes against the float64 CPU restatement that uses the same
+polynomial score-mods, and plain softmax against torch autograd."""
+import ctypes
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def stream():
+    import torch
+    return torch.cuda.current_stream().cuda_stream
+
+
+def bits(t):
+    import torch
+    return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+
+def forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n):
+    import torch
+    B, S, Hq, D = q.shape
+    out = torch.empty(B, S, Hq, D, dtype=torch.bfloat16, device=cuda)
+    lse = torch.zeros(B, Hq, S, dtype=torch.float32, device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    fpt.call("fpt_attention_fwd", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq,
+             k.shape[2], D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, status.data_ptr(), stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    return out, lse
+
+
+def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad=0):
+    import torch
+    B, S, Hq, D = q.shape
+    Hk = k.shape[2]
+    dq = torch.full((B, S, Hq, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    dk = torch.full((B, S, Hk, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    dv = torch.full((B, S, Hk, D), float("nan"), dtype=torch.bfloat16, device=cuda)
+    need = fpt.load().fpt_attention_bwd_workspace_bytes(B, S, Hq)
+    assert need == 2 * B * Hq * S * 4
+    workspace = torch.empty(need, dtype=torch.uint8, device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    fpt.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(),
+             v.data_ptr(), out.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
+             arr(out), arr(dout), mode, int(causal), scale, softcap, log2_n, softcap_grad, status.data_ptr(), stream())
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, hex(int(status.item()) & 0xFFFFFFFF)
+    return dq, dk, dv
+
+
+def close(got, want, what, rel=2e-2):
+    import torch
+    g = got.float().cpu().numpy().astype(np.float64)
+    assert not np.isnan(g).any(), what
+    err = np.abs(g - want).max()
+    assert err <= rel * max(np.abs(want).max(), 1e-6), (what, err, np.abs(want).max())
+
+
+CASES = [
+    # (B, S, Hq, Hk, mode, causal, softcap, log2_n, softcap_grad)
+    (1, 128, 1, 1, 2, False, 0.0, 12, 0),
+    (1, 256, 2, 1, 2, True, 0.0, 12, 0),
+    (2, 384, 4, 2, 2, True, 0.0, 12, 0),
+    (1, 384, 4, 2, 0, True, 50.0, 12, 0),
+    (1, 256, 2, 2, 0, False, 30.0, 12, 1),
+    (1, 512, 2, 1, 1, False, 0.0, 9, 0),
+    (1, 384, 4, 2, 1, True, 0.0, 12, 0),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_backward_matches_the_cpu_restatement(fpt, cuda, oracle, case):
+    import torch
+    from oracle import attention_bwd
+    B, S, Hq, Hk, mode, causal, softcap, log2_n, softcap_grad = case
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(4321)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    dout = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse = forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    dq, dk, dv = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad)
+    _, _, want_dq, want_dk, want_dv = attention_bwd.attention_fwd_bwd(bits(q), bits(k), bits(v), bits(dout), mode, causal, scale,
+                                                                      softcap, log2_n, softcap_grad)
+    close(dq, want_dq, "dq")
+    close(dk, want_dk, "dk")
+    close(dv, want_dv, "dv")
+
+
+def test_plain_softmax_backward_matches_torch_autograd(fpt, cuda):
+    import torch
+    B, S, Hq, Hk, D = 1, 512, 4, 2, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(77)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    dout = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse = forward(fpt, cuda, q, k, v, 2, True, scale, 0.0, 12)
+    dq, dk, dv = backward(fpt, cuda, q, k, v, out, lse, dout, 2, True, scale, 0.0, 12)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    kk = kf.repeat_interleave(Hq // Hk, dim=2)
+    vv = vf.repeat_interleave(Hq // Hk, dim=2)
+    ref = torch.nn.functional.scaled_dot_product_attention(qf.transpose(1, 2), kk.transpose(1, 2), vv.transpose(1, 2),
+                                                           is_causal=True).transpose(1, 2)
+    ref.backward(dout.float())
+    for got, want, name in ((dq, qf.grad, "dq"), (dk, kf.grad, "dk"), (dv, vf.grad, "dv")):
+        err = float((got.float() - want).abs().max())
+        assert err <= 2e-2 * float(want.abs().max()), (name, err)
+
+
+def test_backward_rejects_bad_arguments(fpt, cuda):
+    import torch
+    lib = fpt.load()
+    t = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=cuda)
+    lse = torch.zeros(1, 1, 128, device=cuda)
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    ws = torch.zeros(2048, dtype=torch.uint8, device=cuda)
+    arr = (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+
+    def call(workspace_bytes=1024, mode=2, seq=128, out=t.data_ptr()):
+        return lib.fpt_attention_bwd(t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+                                     t.data_ptr(), out, lse.data_ptr(), ws.data_ptr(), workspace_bytes, 1, seq, 1, 1, 128,
+                                     arr, arr, arr, arr, arr, mode, 0, 1.0, 1.0, 12, 0, status.data_ptr(), None)
+
+    assert call(workspace_bytes=8) == -9                 # workspace too small
+    assert call(seq=100) < 0                             # not a multiple of 128
+    assert call(mode=7) < 0
+    assert call(out=None) < 0                            # soft-max modes need the forward output
+    assert call(mode=1, out=None, workspace_bytes=0) == 0   # the sigmoid mode needs neither out, lse nor workspace
+    torch.cuda.synchronize()
