@@ -7,7 +7,7 @@ and error messages, and the same seam -- ``resolve_fa4_config(config, runtime=..
 ``flash_attn_fwd``, ``flash_attn_bwd``, ``run_polynomial_coefficient_audit``, ``audit_polynomial_selection``,
 ``audit_attention_handwritten_fast_path``, ``create_softcap_scoremod_backend``,
 ``create_softcap_scoremod_bwd_backend``.  When no mapping is passed, the runtime is this package's own
-(``b200_runtime()``): forward on the tcgen05 kernel, backward not built yet (it raises).
+(``b200_runtime()``): forward and backward on the tcgen05 kernels of this package.
 
 Inputs of :class:`FA4AttentionWrapper` are ``(batch, heads, sequence, dim)``; the kernel interface is
 ``(batch, sequence, heads, dim)``.
@@ -279,6 +279,7 @@ class SoftcapScoreMod:
     degree: int = 4
     backend: str = "device"
     coeff_source: str = "current"
+    backward_mode: str = "analytical"
 
 
 def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.0, score_mod=None, sigmoid_attention=False,
@@ -333,8 +334,62 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
     return out, lse
 
 
-def _b200_flash_attn_bwd(*args, **kwargs):
-    raise NotImplementedError("attention backward is not built in this package yet (forward only)")
+def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=True, softcap=0.0, *, score_mod=None,
+                         score_mod_bwd=None, sigmoid_attention=False, sigmoid_bias=None, sigmoid_sfu_freq=16,
+                         sigmoid_sfu_res=0, sigmoid_use_direct_bwd_poly=True, sigmoid_poly_backend="device",
+                         sigmoid_degree=3, sigmoid_gradient_degree=4, sigmoid_coeff_source="current",
+                         exp2_emu_backend="d3", exp2_emu_freq=0):
+    """(dq, dk, dv) for the forward above (reference contract: src/sfu_repro/fa4.py:828-859)."""
+    import ctypes
+
+    from .. import _lib
+    for name, t in (("q", q), ("k", k), ("v", v), ("dout", dout)):
+        if t.dtype != torch.bfloat16 or not t.is_cuda or t.stride(-1) != 1:
+            raise RuntimeError(f"{name} must be a bfloat16 CUDA tensor with a contiguous head dimension")
+    batch, seq, q_heads, dim = q.shape
+    scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(dim)
+    log2_n, grad_mode = 12, 0
+    if sigmoid_attention:
+        if not (sigmoid_use_direct_bwd_poly and sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3
+                and int(sigmoid_gradient_degree) == 4 and sigmoid_coeff_source == "current" and sigmoid_bias is None
+                and int(sigmoid_sfu_res) == 0):
+            raise NotImplementedError("only the direct cubic with its coupled degree-4 derivative (device, current "
+                                      "coefficients, bias -log n, every lane polynomial) is built")
+        if seq & (seq - 1):
+            raise NotImplementedError("direct sigmoid attention needs a power-of-two sequence length")
+        mode, log2_n, cap = 1, seq.bit_length() - 1, 0.0
+    elif score_mod is not None or score_mod_bwd is not None:
+        token = score_mod_bwd if score_mod_bwd is not None else score_mod
+        if not isinstance(token, SoftcapScoreMod) or token.degree != 4 or token.coeff_source != "current":
+            raise NotImplementedError("only the degree-4 'current' tanh soft-cap score-mod is built")
+        if token.backward_mode not in ("analytical", "exact_1mt2"):
+            raise NotImplementedError(f"soft-cap backward mode {token.backward_mode!r} is not built "
+                                      "(built: 'analytical', 'exact_1mt2')")
+        mode, cap, grad_mode = 0, float(token.softcap), (0 if token.backward_mode == "analytical" else 1)
+    elif softcap and float(softcap) > 0.0:
+        raise NotImplementedError("native (SFU) tanh soft-cap is not built; use the polynomial score-mod")
+    else:
+        mode, cap = 2, 0.0
+    if exp2_emu_freq not in (None, 0):
+        raise NotImplementedError("software exp2 routing is not built for the backward pass")
+    dq = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
+    dk = torch.empty((batch, seq, k.shape[2], dim), dtype=torch.bfloat16, device=q.device)
+    dv = torch.empty_like(dk)
+    status = torch.zeros(1, dtype=torch.int32, device=q.device)
+    strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    needs_forward = mode != 1
+    if needs_forward and (out is None or lse is None):
+        raise RuntimeError("soft-max attention backward needs the forward's out and lse")
+    need = int(_lib.load().fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) if needs_forward else 0
+    workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
+    with torch.cuda.device(q.device):
+        _lib.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(),
+                  k.data_ptr(), v.data_ptr(), out.data_ptr() if needs_forward else None,
+                  lse.data_ptr() if needs_forward else None, workspace.data_ptr(), need, batch, seq, q_heads, k.shape[2],
+                  dim, strides(q), strides(k), strides(v), strides(out) if needs_forward else strides(q), strides(dout),
+                  mode, int(bool(causal)), scale, cap, log2_n, grad_mode, status.data_ptr(),
+                  torch.cuda.current_stream(q.device).cuda_stream)
+    return dq, dk, dv
 
 
 @lru_cache(maxsize=1)
@@ -366,7 +421,7 @@ def b200_runtime() -> Mapping[str, Any]:
         return SoftcapScoreMod(float(softcap), int(degree), backend, coeff_source)
 
     def create_softcap_scoremod_bwd_backend(softcap, *, degree, backend, backward_mode, coeff_source):
-        return SoftcapScoreMod(float(softcap), int(degree), backend, coeff_source)
+        return SoftcapScoreMod(float(softcap), int(degree), backend, coeff_source, backward_mode)
 
     return {"flash_attn_fwd": _b200_flash_attn_fwd, "flash_attn_bwd": _b200_flash_attn_bwd,
             "run_polynomial_coefficient_audit": run_polynomial_coefficient_audit,

@@ -116,3 +116,34 @@ def test_attention_module_forward(cuda, oracle):
     # sigmoid attention: the deployed pair exists for 4096 keys only, as in the reference
     with pytest.raises(ValueError, match="4096"):
         fa4.build_fa4_module(fa4.b3_component_configs()["polynomial"], head_dim=D, sequence_length=S)
+
+
+def test_attention_module_trains(cuda):
+    """Gradients flow through the wrapper: soft-cap polynomial (analytical derivative) and the direct sigmoid at the
+    4096 keys it is fitted for, against the float64 CPU restatement."""
+    import torch
+    from fast_polynomial_transcendentals_b200.sfu_repro import fa4
+    from oracle import attention_bwd, oracle as orc
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(8)
+    bits = lambda t: t.detach().transpose(1, 2).contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
+
+    def check(module, B, Hq, Hk, S, mode, softcap, log2_n):
+        q = torch.randn(B, Hq, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        k = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        v = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        dout = torch.randn(B, Hq, S, D, device=cuda, generator=g).to(torch.bfloat16)
+        out = module(q, k, v)
+        out.backward(dout)
+        _, _, dq, dk, dv = attention_bwd.attention_fwd_bwd(bits(q), bits(k), bits(v), bits(dout), mode, True, 1 / math.sqrt(D),
+                                                           softcap, log2_n, 0)
+        for got, want, name in ((q.grad, dq, "dq"), (k.grad, dk, "dk"), (v.grad, dv, "dv")):
+            got = got.transpose(1, 2).float().cpu().numpy()
+            assert np.abs(got - want).max() <= 2e-2 * np.abs(want).max(), name
+
+    check(fa4.build_fa4_module(fa4.b2_component_configs()["polynomial"], head_dim=D).to(cuda), 1, 4, 2, 384, orc.ATTN_SOFTCAP_TANH,
+          30.0, 12)
+    sigmoid = fa4.build_fa4_module(fa4.b3_component_configs()["polynomial"], head_dim=D, sequence_length=4096).to(cuda)
+    sigmoid.q_norm = sigmoid.k_norm = None        # compare the attention itself; the norms are plain torch modules
+    check(sigmoid, 1, 1, 1, 4096, orc.ATTN_SIGMOID_B3, 0.0, 12)
