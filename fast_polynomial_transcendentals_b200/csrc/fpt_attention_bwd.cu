@@ -58,7 +58,7 @@ struct BwdParams {
     int causal;
     int softcap_grad;      // 0 analytical derivative of the polynomial, 1 the identity 1 - t^2
     float scale, softcap;
-    float tanh_clamp, tanh_d[4];   // derivative of the tanh program: d0 + d1 t + d2 t^2 + d3 t^3 for t < clamp
+    uint32_t tanh_dw[4];   // derivative of the tanh program as packed bf16 words: d0 + d1 t + d2 t^2 + d3 t^3
     uint32_t* status;
     ProgramWords tanh;
     B3Words b3;
@@ -140,12 +140,17 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
             g0 = fmaf(-th0, th0, 1.0f);
             g1 = fmaf(-th1, th1, 1.0f);
         } else {
-            const float a0 = fabsf(Sfu<kBf16>::lo(x)), a1 = fabsf(Sfu<kBf16>::hi(x));
-            const float c0 = fminf(a0, p.tanh_clamp), c1 = fminf(a1, p.tanh_clamp);
-            g0 = fmaf(fmaf(fmaf(p.tanh_d[3], c0, p.tanh_d[2]), c0, p.tanh_d[1]), c0, p.tanh_d[0]);
-            g1 = fmaf(fmaf(fmaf(p.tanh_d[3], c1, p.tanh_d[2]), c1, p.tanh_d[1]), c1, p.tanh_d[0]);
-            if (!(a0 < p.tanh_clamp) || !(fabsf(th0) < 1.0f)) g0 = 0.0f;   // clamped input or saturated output: flat
-            if (!(a1 < p.tanh_clamp) || !(fabsf(th1) < 1.0f)) g1 = 0.0f;
+            // derivative of the polynomial on packed bf16 lanes, like the polynomial itself: three fused
+            // multiply-adds per pair; zero where the input is clamped or the output saturated (flat regions)
+            using P = Pk<kBf16>;
+            const uint32_t ax = x & ~kSignMask;
+            const uint32_t c = P::min(ax, p.tanh.clamp);
+            uint32_t gw = P::fma(c, p.tanh_dw[3], p.tanh_dw[2]);
+            gw = P::fma(c, gw, p.tanh_dw[1]);
+            gw = P::fma(c, gw, p.tanh_dw[0]);
+            gw &= ~(P::ge_mask(ax, p.tanh.clamp) | P::ge_mask(th & ~kSignMask, Consts<kBf16>::one));
+            g0 = Sfu<kBf16>::lo(gw);
+            g1 = Sfu<kBf16>::hi(gw);
         }
         p_word = pack_bf16(p0, p1);
         ds_word = pack_bf16(p0 * (d0 - t0) * g0, p1 * (d1 - t1) * g1);
@@ -468,15 +473,18 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     const ProgramRow* tanh_row = find_program(FPT_FN_TANH, FPT_FWD, 4, FPT_BF16, FPT_SRC_CURRENT);
     if (!tanh_row || tanh_row->shape != kOddSat) return FPT_ERR_UNKNOWN_PROGRAM;
     p.tanh = program_words(*tanh_row);
-    auto bf16_value = [](uint16_t bits) {
-        const uint32_t u = uint32_t(bits) << 16;
+    // y = t (c1 + t (c2 + t (c3 + t c4)))  ->  dy/dt = c1 + 2 c2 t + 3 c3 t^2 + 4 c4 t^3, each coefficient rounded to
+    // bf16 (nearest even) from the exact multiple of the program's bf16 coefficient
+    auto scaled_bf16 = [](uint16_t bits, float factor) {
+        uint32_t u = uint32_t(bits) << 16;
         float f;
         memcpy(&f, &u, 4);
-        return f;
+        f *= factor;                                   // exact: a bf16 value times 1..4 fits in fp32
+        memcpy(&u, &f, 4);
+        u += 0x7fffu + ((u >> 16) & 1u);
+        return (u >> 16) * 0x00010001u;
     };
-    // y = t (c1 + t (c2 + t (c3 + t c4)))  ->  dy/dt = c1 + 2 c2 t + 3 c3 t^2 + 4 c4 t^3
-    p.tanh_clamp = bf16_value(tanh_row->clamp);
-    for (int i = 0; i < 4; ++i) p.tanh_d[i] = float(i + 1) * bf16_value(tanh_row->c[i]);
+    for (int i = 0; i < 4; ++i) p.tanh_dw[i] = scaled_bf16(tanh_row->c[i], float(i + 1));
     p.b3 = b3_words(mode == FPT_ATTN_SIGMOID_DIRECT ? log2_n : 12);
 
     const size_t smem = sizeof(BwdSmem) + 1024;
