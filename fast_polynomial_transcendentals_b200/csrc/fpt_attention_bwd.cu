@@ -11,8 +11,8 @@
 // Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
 // tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
 // (the backward has no row reduction, so the split needs no exchange).
-// Tensor memory: S 0..127 (bf16 P over its first 64 columns), dP 128..255 (bf16 dS over its first 64), acc0 256..383,
-// acc1 384..511.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
+// Tensor memory: S is never overwritten by P (dQ stores no P; dK/dV keep P in the upper half of the dP tile), so the
+// S product of the next step runs under the score-mod of the current one; dQ also double-buffers dP.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
 // Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
 #include <cstring>
 #include <type_traits>
@@ -157,6 +157,16 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
     }
 }
 
+// Tensor-memory columns.  WHICH 0 (dQ): S 0..127, two dP tiles 128..255 and 256..383 (bf16 dS over the first 64 columns
+// of the tile it was computed from), acc0 384..511.  WHICH 1 (dK, dV): S 0..127, one dP tile 128..255 with bf16 dS over
+// columns 128..191 and bf16 P over 192..255, acc0 (dK) 256..383, acc1 (dV) 384..511.
+constexpr uint32_t kColS = 0, kColDp = 128, kColP = 192, kColAcc1 = 384;
+template <int WHICH>
+struct Cols {
+    static constexpr uint32_t acc0 = WHICH == 0 ? 384u : 256u;
+    static __device__ __forceinline__ uint32_t dp(int t) { return WHICH == 0 ? kColDp + 128u * uint32_t(t & 1) : kColDp; }
+};
+
 template <int MODE, int WHICH>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -247,41 +257,84 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            constexpr uint32_t kColAcc0 = Cols<WHICH>::acc0;
+            auto dp_col = [](int t) { return Cols<WHICH>::dp(t); };
             const uint32_t x_lo = umma_smem_desc_lo(smem_u32(sm.x), 16), y_lo = umma_smem_desc_lo(smem_u32(sm.y), 16);
+            // Software pipeline.  S is not aliased by anything (P sits in the upper half of the dP tile, WHICH 1, or
+            // is not stored at all, WHICH 0), so S of step t+1 is issued as soon as the score-mod warps have S of
+            // step t in registers.  WHICH 0 also has room for two dP tiles and issues dP of step t+1 at the same
+            // point; WHICH 1 issues it behind the products that read dS and P of step t from that tile.
+            auto stage_words = [&](int st, uint32_t& u_k, uint32_t& w_k, uint32_t& u_mn, uint32_t& w_mn) {
+                u_k = umma_smem_desc_lo(smem_u32(sm.u[st]), 16);
+                w_k = umma_smem_desc_lo(smem_u32(sm.w[st]), 16);
+                u_mn = umma_smem_desc_lo(smem_u32(sm.u[st]), kPanelB);
+                w_mn = umma_smem_desc_lo(smem_u32(sm.w[st]), kPanelB);
+            };
+            auto issue_s = [&](uint32_t u_k) {           // S = X U^T
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
+                    umma_ss_words(tmem + kColS, x_lo + off, u_k + off, desc_hi, idesc_kk, kk > 0);
+                }
+            };
+            auto issue_dp = [&](uint32_t w_k, int t) {   // dP = Y W^T into the tile of step t
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
+                    umma_ss_words(tmem + dp_col(t), y_lo + off, w_k + off, desc_hi, idesc_kk, kk > 0);
+                }
+            };
             bool ok = mbar_wait(&sm.xy_full, 0, abort_flag, p.status, kBwdXY);
-            for (int t = 0; t < n_inner && ok; ++t) {
-                const int st = t % kRing;
-                const uint32_t ph = uint32_t(t / kRing) & 1u;
-                ok = mbar_wait(&sm.uw_full[st], ph, abort_flag, p.status, kBwdUwFull);
-                if (!ok) break;
+            uint32_t u_k = 0, w_k = 0, u_mn = 0, w_mn = 0;
+            if (ok) ok = mbar_wait(&sm.uw_full[0], 0, abort_flag, p.status, kBwdUwFull);
+            if (ok) {
                 tc_fence_after_sync();
-                const uint32_t u_k = umma_smem_desc_lo(smem_u32(sm.u[st]), 16), w_k = umma_smem_desc_lo(smem_u32(sm.w[st]), 16);
-                const uint32_t u_mn = umma_smem_desc_lo(smem_u32(sm.u[st]), kPanelB), w_mn = umma_smem_desc_lo(smem_u32(sm.w[st]), kPanelB);
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {     // S = X U^T
-                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
-                    umma_ss_words(tmem, x_lo + off, u_k + off, desc_hi, idesc_kk, kk > 0);
-                }
-#pragma unroll
-                for (int kk = 0; kk < 8; ++kk) {     // dP = Y W^T
-                    const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
-                    umma_ss_words(tmem + 128u, y_lo + off, w_k + off, desc_hi, idesc_kk, kk > 0);
-                }
+                stage_words(0, u_k, w_k, u_mn, w_mn);
+                issue_s(u_k);
+                issue_dp(w_k, 0);
                 umma_commit(&sm.s_full);
+            }
+            for (int t = 0; t < n_inner && ok; ++t) {
+                const int st = t % kRing, st_next = (t + 1) % kRing;
+                const bool more = t + 1 < n_inner;
+                uint32_t nu_k = 0, nw_k = 0, nu_mn = 0, nw_mn = 0;
+                // [A] S (and dP) of step t are in registers: S of step t+1 may overwrite S
+                ok = mbar_wait(&sm.ld_done, uint32_t(t) & 1u, abort_flag, p.status, kBwdLdDone);
+                if (!ok) break;
+                if (more) {
+                    ok = mbar_wait(&sm.uw_full[st_next], uint32_t((t + 1) / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    stage_words(st_next, nu_k, nw_k, nu_mn, nw_mn);
+                    issue_s(nu_k);
+                    if constexpr (WHICH == 0) {
+                        issue_dp(nw_k, t + 1);
+                        umma_commit(&sm.s_full);
+                    }
+                }
+                // [B] dS (and P) of step t are in tensor memory
                 ok = mbar_wait(&sm.p_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdPFull);
                 if (!ok) break;
                 tc_fence_after_sync();
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)       // acc0 += dS U
-                    umma_ts_words(tmem + 256u, tmem + 128u + 8u * kk, u_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn,
-                                  t > 0 || kk > 0);
+                    umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 8u * kk, u_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
+                                  idesc_mn, t > 0 || kk > 0);
                 if constexpr (WHICH == 1) {
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)   // acc1 += P W
-                        umma_ts_words(tmem + 384u, tmem + 8u * kk, w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn,
-                                      t > 0 || kk > 0);
+                        umma_ts_words(tmem + kColAcc1, tmem + kColP + 8u * kk, w_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
+                                      idesc_mn, t > 0 || kk > 0);
                 }
                 umma_commit(&sm.uw_empty[st]);
+                // [C] WHICH 1: the one dP tile is free again once the products above have read it (same thread, in order)
+                if constexpr (WHICH == 1) {
+                    if (more) {
+                        issue_dp(nw_k, t + 1);
+                        umma_commit(&sm.s_full);
+                    }
+                }
+                u_k = nu_k; w_k = nw_k; u_mn = nu_mn; w_mn = nw_mn;
             }
             if (ok) umma_commit(&sm.acc_done);
         }
@@ -293,10 +346,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const int quarter = warp & 3, half = (warp - 4) >> 2;
         const int r = 32 * quarter + lane;                       // row of the fixed tile = tensor-memory lane
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
-        const uint32_t t_s = tmem + lane_base + uint32_t(64 * half);
-        const uint32_t t_dp = tmem + lane_base + 128u + uint32_t(64 * half);
-        const uint32_t t_p = tmem + lane_base + uint32_t(32 * half);          // bf16 pairs: 32 words per half
-        const uint32_t t_ds = tmem + lane_base + 128u + uint32_t(32 * half);
+        const uint32_t t_s = tmem + lane_base + kColS + uint32_t(64 * half);
+        const uint32_t t_p = tmem + lane_base + kColP + uint32_t(32 * half);   // bf16 pairs: 32 words per half
         float row_lse2 = 0.0f, row_delta = 0.0f;
         if (WHICH == 0 && MODE != 1) {
             const int64_t off = (int64_t(b) * p.q_heads + head) * p.seq + row0 + r;
@@ -312,12 +363,15 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             uint32_t sv[64], dv[64];
             tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
             tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
+            const uint32_t t_dp = tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * half);
+            const uint32_t t_ds = tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(32 * half);
             tmem_ld_32x32b_x32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
             tmem_ld_32x32b_x32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
             tmem_ld_wait();
             // P and dS overwrite columns from which the other warp of this lane quarter reads S and dP: every load
             // first, then the stores (a bounded mbarrier wait rather than a named barrier, so that a warp that gave
             // up after a timeout cannot leave the others waiting for ever)
+            tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ld_done);
             ok = mbar_wait(&sm.ld_done, uint32_t(t) & 1u, abort_flag, p.status, kBwdLdDone);
@@ -350,7 +404,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             };
             if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
             else columns(std::false_type{});
-            tmem_st_32x32b_x32(t_p, pw);
+            if constexpr (WHICH == 1) tmem_st_32x32b_x32(t_p, pw);   // only dK / dV need P itself
             tmem_st_32x32b_x32(t_ds, dsw);
             tmem_st_wait();
             tc_fence_before_sync();
@@ -370,7 +424,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
-                        tmem_ld_32x32b_x32(tmem + lane_base + 256u + 128u * acc + uint32_t(64 * half + 32 * c), v);
+                        tmem_ld_32x32b_x32(tmem + lane_base + (acc == 0 ? Cols<WHICH>::acc0 : kColAcc1) + uint32_t(64 * half + 32 * c), v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
