@@ -445,6 +445,25 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
         tf = flops / (t["attn"] * 1e-3) / 1e12
         out[name] = {"ms": t["attn"], "tflops": tf, "frac_of_measured_bf16_peak": tf / tensor_peak,
                      "flops_convention": "4*B*Hq*S^2*D, halved when causal"}
+        if route == 0 and name.startswith(("config", "control")):
+            # backward of the same shape: dQ and dK/dV kernels plus the delta pre-pass, forward output as input
+            dout = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
+            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+            need = int(lib.fpt_attention_bwd_workspace_bytes(B, Sq, Hq))
+            workspace = torch.empty(need, dtype=torch.uint8, device=device)
+            sdo = arr(dout)
+            kb = [("bwd", 0, lambda: _lib.check("fpt_attention_bwd", lib.fpt_attention_bwd(
+                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                o.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, Sq, Hq, Hk, D, sq, sk, sv, so, sdo, mode, causal,
+                1.0 / math.sqrt(D), cap, log2_n, 0, status.data_ptr(), S())))]
+            _, tb = time_sweep(kb, 3, 2)
+            if int(status.item()) != 0:
+                raise RuntimeError(f"attention backward reported status {int(status.item()) & 0xffffffff:#x}")
+            tfb = 2.5 * flops / (tb["bwd"] * 1e-3) / 1e12
+            out[name]["backward"] = {"ms": tb["bwd"], "tflops": tfb, "frac_of_measured_bf16_peak": tfb / tensor_peak,
+                                     "flops_convention": "5 matrix products = 2.5 x the forward count (7 are executed: S and "
+                                                         "dP are recomputed in the dQ and in the dK/dV kernel)"}
+            del dout, dq, dk, dv, workspace
         del q, k, v, o, lse
     torch.cuda.empty_cache()
     return out
