@@ -129,7 +129,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int b = blockIdx.z;
     const int hk = hq / (p.q_heads / p.kv_heads);
     const int m0 = qblock * (kSlots * kTileM);
-    const int total_tiles = p.seq / kTileN;
+    const int total_tiles = (p.seq + kTileN - 1) / kTileN;   // a ragged last tile is zero-filled by TMA and masked below
     int n_tiles[kSlots];
 #pragma unroll
     for (int s = 0; s < kSlots; ++s) {
@@ -307,7 +307,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (!ok) break;
             tc_fence_after_sync();
             FPT_TRACE(s, 2);                         // S ready
-            const bool diagonal = p.causal && j == n - 1;
+            // Tiles that need a mask: the causal diagonal, and the last key tile of a sequence that is not a multiple of
+            // the tile size.  Both are "column > limit" with limit = min(row if causal, last key).
+            const bool diagonal = (p.causal && j == n - 1) || (j == total_tiles - 1 && (p.seq % kTileN) != 0);
+            const int limit = min(p.causal ? row : 0x7fffffff, p.seq - 1);
             // the whole S row: four tensor-memory loads in flight, one wait
             uint32_t sr[kTileN];
 #pragma unroll
@@ -338,8 +341,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
                         for (int w = 0; w < 32; ++w) {
                             const int col = j * kTileN + 2 * (half * 32 + w);
-                            if (col > row) pw[w] &= 0xffff0000u;
-                            if (col + 1 > row) pw[w] &= 0x0000ffffu;
+                            if (col > limit) pw[w] &= 0xffff0000u;
+                            if (col + 1 > limit) pw[w] &= 0x0000ffffu;
                         }
                     }
                     if (half == 1) FPT_TRACE(s, 3);  // probabilities computed
@@ -360,7 +363,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 if (diagonal) {
 #pragma unroll
                     for (int i = 0; i < kTileN; ++i)
-                        if (j * kTileN + i > row) sr[i] = 0xff800000u;  // -inf
+                        if (j * kTileN + i > limit) sr[i] = 0xff800000u;  // -inf
                 }
                 // Row maximum of the tile (three-input max on the ALU pipe, which has room beside the exponentials).
                 // The reference point of the exponentials moves only when the maximum grew by more than 2^8 (lazy
@@ -421,6 +424,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             if (ok) {
                 tc_fence_after_sync();
                 const float inv = MODE == 1 ? 1.0f : 1.0f / row_sum;
+                const bool real_row = row < p.seq;       // rows of a ragged last tile beyond the sequence are dropped
                 uint16_t* out_row = p.out + int64_t(b) * p.out_stride_b + int64_t(row) * p.out_stride_s +
                                     int64_t(hq) * p.out_stride_h;
 #pragma unroll
@@ -436,10 +440,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         w.y = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
                         w.z = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
                         w.w = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
-                        dst[q4] = w;
+                        if (real_row) dst[q4] = w;
                     }
                 }
-                if (MODE != 1 && p.lse)
+                if (MODE != 1 && p.lse && real_row)
                     p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
             }
         }
@@ -463,7 +467,7 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     if (!out || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !out_strides)
         return FPT_ERR_NULL_POINTER;
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
-    if (head_dim != kHeadDim || seq % kTileN != 0 || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
+    if (head_dim != kHeadDim || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
     if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
     if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
     if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;

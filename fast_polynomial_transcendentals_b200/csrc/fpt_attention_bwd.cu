@@ -52,7 +52,7 @@ struct BwdSmem {
 struct BwdParams {
     uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
     uint16_t* out1;        // dV (WHICH 1)
-    const float* lse2;     // workspace plane 0: [B, Hq, S]
+    const float* lse2;     // workspace plane 0: [B, Hq, S rounded up to whole tiles]
     const float* delta;    // workspace plane 1
     int batch, seq, q_heads, kv_heads;
     int causal;
@@ -76,16 +76,23 @@ struct PrepassArgs {
     float* lse2;
     float* delta;
     int64_t o_stride_b, o_stride_s, o_stride_h, do_stride_b, do_stride_s, do_stride_h;
-    int batch, seq, q_heads;
+    int batch, seq, seq_pad, q_heads;
 };
 
 __global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const PrepassArgs a) {
     const int lane = threadIdx.x & 31;
-    const int64_t rows = int64_t(a.batch) * a.q_heads * a.seq;
+    const int64_t rows = int64_t(a.batch) * a.q_heads * a.seq_pad;   // planes are padded to whole tiles
 #pragma unroll 1
     for (int64_t row = int64_t(blockIdx.x) * 8 + (threadIdx.x >> 5); row < rows; row += int64_t(gridDim.x) * 8) {
-        const int s = int(row % a.seq);
-        const int64_t bh = row / a.seq;
+        const int s = int(row % a.seq_pad);
+        const int64_t bh = row / a.seq_pad;
+        if (s >= a.seq) {                      // padding rows: defined values, so that nothing downstream meets a NaN
+            if (lane == 0) {
+                a.delta[row] = 0.0f;
+                a.lse2[row] = 0.0f;
+            }
+            continue;
+        }
         const int h = int(bh % a.q_heads), b = int(bh / a.q_heads);
         const uint2 o = *reinterpret_cast<const uint2*>(a.out + b * a.o_stride_b + s * a.o_stride_s + h * a.o_stride_h + lane * 4);
         const uint2 d = *reinterpret_cast<const uint2*>(a.dout + b * a.do_stride_b + s * a.do_stride_s + h * a.do_stride_h + lane * 4);
@@ -97,7 +104,7 @@ __global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const Prepas
         for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
         if (lane == 0) {
             a.delta[row] = acc;
-            a.lse2[row] = a.lse[row] * kLog2eB;
+            a.lse2[row] = a.lse[bh * a.seq + s] * kLog2eB;
         }
     }
 }
@@ -178,7 +185,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int head = blockIdx.x;                  // query head (WHICH 0) or kv head (WHICH 1)
     const int tile = p.causal && WHICH == 0 ? int(gridDim.y) - 1 - int(blockIdx.y) : int(blockIdx.y);  // long loops first
     const int b = blockIdx.z;
-    const int total = p.seq / kTile;
+    const int total = (p.seq + kTile - 1) / kTile;   // a ragged last tile is zero-filled by TMA and masked below
+    const int seq_pad = total * kTile;
+    const bool ragged = (p.seq % kTile) != 0;
     const int group = p.q_heads / p.kv_heads;
     const int row0 = tile * kTile;                // first row of the fixed tiles
     // inner loop: WHICH 0 walks key tiles 0..(causal ? tile : total-1); WHICH 1 walks, for each query head of the
@@ -245,7 +254,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 tma_load_4d(sm.w[st], &map_w, &sm.uw_full[st], 0, r0, sh, b);
                 tma_load_4d(sm.w[st] + kPanelB, &map_w, &sm.uw_full[st], 64, r0, sh, b);
                 if (vec_bytes) {   // per-query vectors of the streamed query tile
-                    const int64_t off = (int64_t(b) * p.q_heads + sh) * p.seq + r0;
+                    const int64_t off = (int64_t(b) * p.q_heads + sh) * seq_pad + r0;
                     bulk_load_1d(sm.lse2[st], p.lse2 + off, kTile * 4u, &sm.uw_full[st]);
                     bulk_load_1d(sm.delta[st], p.delta + off, kTile * 4u, &sm.uw_full[st]);
                 }
@@ -350,7 +359,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const uint32_t t_p = tmem + lane_base + kColP + uint32_t(32 * half);   // bf16 pairs: 32 words per half
         float row_lse2 = 0.0f, row_delta = 0.0f;
         if (WHICH == 0 && MODE != 1) {
-            const int64_t off = (int64_t(b) * p.q_heads + head) * p.seq + row0 + r;
+            const int64_t off = (int64_t(b) * p.q_heads + head) * seq_pad + row0 + r;
             row_lse2 = p.lse2[off];
             row_delta = p.delta[off];
         }
@@ -380,7 +389,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             if (!ok) break;
             const int g = WHICH == 0 ? 0 : t / per_head;
             const int c0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile + 64 * half;   // first column
-            const bool diagonal = p.causal && (c0 - 64 * half == row0);
+            // tiles that need a mask: the causal diagonal, and any tile pair that touches a ragged end of the sequence
+            const int tile_c0 = c0 - 64 * half;
+            const bool diagonal = (p.causal && tile_c0 == row0) ||
+                                  (ragged && (tile_c0 + kTile > p.seq || row0 + kTile > p.seq));
             uint32_t pw[32], dsw[32];
             auto columns = [&](auto masked) {
 #pragma unroll
@@ -395,8 +407,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     bool m0 = false, m1 = false;
                     if constexpr (decltype(masked)::value) {   // rows are queries (WHICH 0) or keys (WHICH 1)
                         const int row_abs = row0 + r, col_abs = c0 + c;
-                        m0 = WHICH == 0 ? col_abs > row_abs : row_abs > col_abs;
-                        m1 = WHICH == 0 ? col_abs + 1 > row_abs : row_abs > col_abs + 1;
+                        const int query0 = WHICH == 0 ? row_abs : col_abs, key0 = WHICH == 0 ? col_abs : row_abs;
+                        const int query1 = WHICH == 0 ? row_abs : col_abs + 1, key1 = WHICH == 0 ? col_abs + 1 : row_abs;
+                        m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
+                        m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
                     }
                     score_pair<MODE>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
                                      __uint_as_float(dv[c + 1]), l0, l1, e0, e1, m0, m1, pw[i], dsw[i]);
@@ -417,6 +431,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 tc_fence_after_sync();
                 const int64_t heads_out = WHICH == 0 ? p.q_heads : p.kv_heads;
                 const int64_t off = ((int64_t(b) * p.seq + row0 + r) * heads_out + head) * kDim + 64 * half;
+                const bool real_row = row0 + r < p.seq;
 #pragma unroll
                 for (int acc = 0; acc <= WHICH; ++acc) {
                     const float f = acc == 0 ? p.scale : 1.0f;
@@ -433,7 +448,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                             o.y = pack_bf16(__uint_as_float(v[q4 * 8 + 2]) * f, __uint_as_float(v[q4 * 8 + 3]) * f);
                             o.z = pack_bf16(__uint_as_float(v[q4 * 8 + 4]) * f, __uint_as_float(v[q4 * 8 + 5]) * f);
                             o.w = pack_bf16(__uint_as_float(v[q4 * 8 + 6]) * f, __uint_as_float(v[q4 * 8 + 7]) * f);
-                            reinterpret_cast<uint4*>(dst + 32 * c)[q4] = o;
+                            if (real_row) reinterpret_cast<uint4*>(dst + 32 * c)[q4] = o;
                         }
                     }
                 }
@@ -453,7 +468,8 @@ using namespace fpt;
 
 extern "C" int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads) {
     if (batch <= 0 || seq <= 0 || q_heads <= 0) return 0;
-    return 2 * batch * q_heads * seq * int64_t(sizeof(float));
+    const int64_t seq_pad = (seq + kTile - 1) / kTile * kTile;      // planes padded to whole tiles
+    return 2 * batch * q_heads * seq_pad * int64_t(sizeof(float));
 }
 
 extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
@@ -466,7 +482,7 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     if (!dq || !dk || !dv || !dout || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !dout_strides)
         return FPT_ERR_NULL_POINTER;
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
-    if (head_dim != kDim || seq % kTile != 0 || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
+    if (head_dim != kDim || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
     if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
     if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
     if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
@@ -498,7 +514,8 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     if (int rc = make_map(&map_do, dout, dout_strides, q_heads)) return rc;
 
     float* lse2 = static_cast<float*>(workspace);
-    float* delta = lse2 ? lse2 + batch * q_heads * seq : nullptr;
+    const int64_t seq_pad = (seq + kTile - 1) / kTile * kTile;
+    float* delta = lse2 ? lse2 + batch * q_heads * seq_pad : nullptr;
     if (normalised) {
         PrepassArgs a{};
         a.out = static_cast<const uint16_t*>(out);
@@ -508,8 +525,8 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
         a.delta = delta;
         a.o_stride_b = out_strides[0]; a.o_stride_s = out_strides[1]; a.o_stride_h = out_strides[2];
         a.do_stride_b = dout_strides[0]; a.do_stride_s = dout_strides[1]; a.do_stride_h = dout_strides[2];
-        a.batch = int(batch); a.seq = int(seq); a.q_heads = int(q_heads);
-        int64_t grid = (batch * q_heads * seq + 7) / 8;
+        a.batch = int(batch); a.seq = int(seq); a.seq_pad = int(seq_pad); a.q_heads = int(q_heads);
+        int64_t grid = (batch * q_heads * seq_pad + 7) / 8;
         const int64_t cap = int64_t(dev.sm_count) * 32;
         if (grid > cap) grid = cap;
         attention_bwd_prepass_kernel<<<unsigned(grid), 256, 0, stream>>>(a);
@@ -543,7 +560,7 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
 
     const size_t smem = sizeof(BwdSmem) + 1024;
     static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "shared memory budget");
-    const unsigned tiles = unsigned(seq / kTile);
+    const unsigned tiles = unsigned(seq_pad / kTile);
     auto launch = [&](auto kernel, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap& mu,
                       const CUtensorMap& mw, uint16_t* o0, uint16_t* o1) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

@@ -229,7 +229,7 @@ int fpt_rope_apply_static_table(void* q_out, void* k_out, const void* q, const v
                                 int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim,
                                 int table_kind, int dtype, fpt_stream_t stream);
 
-/* ---- attention forward with a polynomial score-mod, bf16, head_dim 128, seq a multiple of 128
+/* ---- attention forward with a polynomial score-mod, bf16, head_dim 128, any sequence length
  *      replaces the forward of the patched FlashAttention interface that the reference drives through
  *      `_flash_attn_fwd(q, k, v, softmax_scale=, causal=, softcap=, score_mod=, sigmoid_attention=, ...) -> (out, lse)`
  *      (reference: src/sfu_repro/fa4.py:755-826, wrapper :899-948, canonical configurations :650-709).
@@ -260,7 +260,7 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
                              const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
                              int exp2_emu_freq, void* status, fpt_stream_t stream);
 
-/* ---- attention backward for the same three modes, bf16, head_dim 128, seq a multiple of 128
+/* ---- attention backward for the same three modes, bf16, head_dim 128, any sequence length
  *      replaces the backward of the patched FlashAttention interface the reference drives through
  *      `flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale, causal, softcap, score_mod=, score_mod_bwd=,
  *      sigmoid_attention=, ...) -> (dq, dk, dv)` (reference: src/sfu_repro/fa4.py:828-859).

@@ -41,7 +41,7 @@ def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, l
     dk = torch.full((B, S, Hk, D), float("nan"), dtype=torch.bfloat16, device=cuda)
     dv = torch.full((B, S, Hk, D), float("nan"), dtype=torch.bfloat16, device=cuda)
     need = fpt.load().fpt_attention_bwd_workspace_bytes(B, S, Hq)
-    assert need == 2 * B * Hq * S * 4
+    assert need == 2 * B * Hq * ((S + 127) // 128 * 128) * 4
     workspace = torch.empty(need, dtype=torch.uint8, device=cuda)
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
     arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
@@ -70,6 +70,12 @@ CASES = [
     (1, 256, 2, 2, 0, False, 30.0, 12, 1),
     (1, 512, 2, 1, 1, False, 0.0, 9, 0),
     (1, 384, 4, 2, 1, True, 0.0, 12, 0),
+    # ragged sequence lengths
+    (1, 200, 2, 1, 2, True, 0.0, 12, 0),
+    (2, 333, 4, 2, 0, False, 30.0, 12, 0),
+    (1, 77, 1, 1, 1, False, 0.0, 12, 0),
+    (1, 257, 4, 2, 2, False, 0.0, 12, 0),
+    (1, 130, 2, 1, 1, True, 0.0, 12, 0),
 ]
 
 
@@ -133,7 +139,6 @@ def test_backward_rejects_bad_arguments(fpt, cuda):
                                      arr, arr, arr, arr, arr, mode, 0, 1.0, 1.0, 12, 0, status.data_ptr(), None)
 
     assert call(workspace_bytes=8) == -9                 # workspace too small
-    assert call(seq=100) < 0                             # not a multiple of 128
     assert call(mode=7) < 0
     assert call(out=None) < 0                            # soft-max modes need the forward output
     assert call(mode=1, out=None, workspace_bytes=0) == 0   # the sigmoid mode needs neither out, lse nor workspace

@@ -65,6 +65,12 @@ CASES = [
     (1, 512, 2, 2, 1, False, 0.0, 9),
     (1, 384, 2, 1, 1, True, 0.0, 12),
     (1, 1024, 8, 2, 0, True, 50.0, 12),
+    # sequence lengths that are not multiples of the 128-key tile (ragged last tile, zero-filled and masked)
+    (1, 200, 2, 1, 2, True, 0.0, 12),
+    (2, 333, 4, 2, 0, False, 30.0, 12),
+    (1, 77, 1, 1, 1, False, 0.0, 12),
+    (1, 257, 2, 2, 1, True, 0.0, 12),
+    (1, 130, 2, 1, 2, False, 0.0, 12),
 ]
 
 
