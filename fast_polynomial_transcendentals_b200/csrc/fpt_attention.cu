@@ -44,6 +44,8 @@ struct AttnSmem {
     alignas(8) uint64_t q_full[kSlots];
     uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
     uint64_t s_full[kSlots], p_half[kSlots], p_full[kSlots], pv_done[kSlots];
+    uint64_t ld_done[kSlots];            // column-split variant: the eight warps of a slot have their S values in registers
+    float xchg[kSlots][2][kTileM];       // column-split variant: row maximum / row sum of the other column half
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -116,8 +118,17 @@ __device__ __forceinline__ void add_f32x2(float& acc0, float& acc1, float e0, fl
         : "+f"(acc0), "+f"(acc1) : "f"(e0), "f"(e1));
 }
 
-template <int MODE, int EMU>
-__global__ void __launch_bounds__(kThreads, 1)
+// SPLIT: sixteen score-mod warps instead of eight; the two warps that share a lane quarter of a slot take 64 key
+// columns each (keys 0..63 answer on the first hand-over barrier, keys 64..127 on the second).  It needs a mode without
+// per-tile row reductions; the host uses it for the soft-capped mode with a bounded score range (fixed exponent
+// reference, see below).
+constexpr int kThreadsSplit = 128 + 256 * kSlots;
+// soft-cap * log2(e) up to which the fixed reference cannot overflow or underflow (see the derivation at its use)
+constexpr float kFixedReferenceLimit = 98.0f;
+constexpr float kFixedReferenceSpan = 96.0f;
+
+template <int MODE, int EMU, bool SPLIT>
+__global__ void __launch_bounds__(SPLIT ? kThreadsSplit : kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -150,6 +161,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             mbar_init(&sm.p_half[s], 4);   // one arrive per softmax warp: keys 0..63 of the tile are in place
             mbar_init(&sm.p_full[s], 4);   // ... and keys 64..127
             mbar_init(&sm.pv_done[s], 1);
+            mbar_init(&sm.ld_done[s], 8);
         }
         for (int st = 0; st < kStages; ++st) {
             mbar_init(&sm.k_full[st], 1);
@@ -175,10 +187,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const uint32_t tmem = sm.tmem_base;
     const bool skip = sm.abort_flag != 0u;
 
-    // Register budget: 128 x 80 + 256 x 208 = 63488 of the SM's 65536.  Each setmaxnreg sits at the head of the branch
-    // it governs, so that the assembler knows which limit holds for which role.
+    // Register budget.  A CTA can only re-distribute the registers it was launched with (threads x the per-thread count
+    // the launch bound allows): what the score-mod warps gain must have been given up by warpgroup 0 first, or
+    // setmaxnreg.inc waits for ever.  384 threads: 168 at launch, 128 x (168-80) = 11264 released >= 256 x (208-168) = 10240
+    // taken.  640 threads (column-split): 96 at launch, 128 x (96-56) = 5120 released >= 512 x (104-96) = 4096 taken.
+    // Each setmaxnreg sits at the head of the branch it governs, so that the assembler knows which limit holds where.
+    static_assert(128 * (168 - 80) >= 256 * (208 - 168) && 128 * (96 - 56) >= 512 * (104 - 96), "register hand-over");
+    static_assert(65536 / kThreads / 8 * 8 == 168 && 65536 / kThreadsSplit / 8 * 8 == 96, "registers per thread at launch");
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+      if constexpr (SPLIT) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      else asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
       if (skip || warp >= 2) {
         // warps 2 and 3 only hold registers for the others; fall through to the teardown
       } else if (warp == 0) {
@@ -282,6 +300,138 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 umma_commit(&sm.v_empty[st]);
                 if (j + 1 < n_max) umma_commit(&sm.k_empty[st_next]);
                 FPT_TRACE(2, 30);
+            }
+        }
+      }
+    } else if constexpr (SPLIT) {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+      if (!skip) {
+        // ------------------------------------------------------------------ score-mod warps, column-split variant
+        const int sw = warp - 4;
+        const int s = sw >> 3, half = (sw >> 2) & 1;
+        const int row_in_tile = 32 * (warp & 3) + lane;
+        const int row = m0 + s * kTileM + row_in_tile;
+        const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+        const uint32_t t_s = tmem + lane_base + uint32_t(s) * 128u + uint32_t(64 * half);
+        const uint32_t t_p = tmem + lane_base + uint32_t(s) * 128u + uint32_t(32 * half);
+        const uint32_t t_o = tmem + lane_base + 256u + uint32_t(s) * 128u + uint32_t(64 * half);
+        const int n = n_tiles[s];
+        const float softcap_in = p.scale / p.softcap, mul = p.softcap * kLog2e;
+        float reference = 0.0f, sum_lo = 0.0f, sum_hi = 0.0f;
+        bool ok = true;
+        // all eight warps of the slot have their S values in registers (P overwrites columns the other half reads);
+        // a bounded mbarrier wait, so that a warp that gave up after a timeout cannot strand the others
+        auto slot_sync = [&](int phase) {
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.ld_done[s]);
+            return mbar_wait(&sm.ld_done[s], uint32_t(phase) & 1u, abort_flag, p.status, kWhereSFull);
+        };
+        for (int j = 0; j < n && ok; ++j) {
+            ok = mbar_wait(&sm.s_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWhereSFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            uint32_t sr[64];
+            tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
+            tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
+            tmem_ld_wait();
+            const bool diagonal = (p.causal && j == n - 1) || (j == total_tiles - 1 && (p.seq % kTileN) != 0);
+            const int limit = min(p.causal ? row : 0x7fffffff, p.seq - 1);
+            const int col0 = j * kTileN + 64 * half;
+            uint32_t pw[32];
+            if constexpr (MODE == 1) {
+#pragma unroll
+                for (int w = 0; w < 32; ++w)
+                    pw[w] = b3_direct_select_late(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], p.scale), p.b3);
+                if (diagonal) {
+#pragma unroll
+                    for (int w = 0; w < 32; ++w) {
+                        if (col0 + 2 * w > limit) pw[w] &= 0xffff0000u;
+                        if (col0 + 2 * w + 1 > limit) pw[w] &= 0x0000ffffu;
+                    }
+                }
+                ok = slot_sync(j);
+                if (!ok) break;
+            } else {
+                // soft-capped scores live in [-cap, cap], so one reference per row serves every tile: the row maximum of
+                // the first tile, but not below cap*log2(e) - 96.  Exponents then stay within [-196, 96] (cap*log2(e)
+                // <= 98): no overflow, and what underflows is at least 2^-126 below an entry of the same row.  No
+                // maximum scan after the first tile and no rescaling of O at all.
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in), p.tanh);
+                    sr[2 * i] = t << 16;
+                    sr[2 * i + 1] = t & 0xffff0000u;
+                }
+                if (diagonal) {
+#pragma unroll
+                    for (int i = 0; i < 64; ++i)
+                        if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
+                }
+                if (j == 0) {
+                    float m3 = __uint_as_float(sr[0]);
+#pragma unroll
+                    for (int i = 1; i + 1 < 64; i += 2) m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+                    m3 = fmaxf(m3, __uint_as_float(sr[63]));
+                    sm.xchg[s][half][row_in_tile] = m3;
+                }
+                ok = slot_sync(j);
+                if (!ok) break;
+                if (j == 0)
+                    reference = fmaxf(fmaxf(sm.xchg[s][0][row_in_tile], sm.xchg[s][1][row_in_tile]) * mul, mul - kFixedReferenceSpan);
+                const float neg_ref = -reference;
+#pragma unroll
+                for (int w = 0; w < 32; ++w) {
+                    float a0, a1, e0, e1;
+                    fma_f32x2(__uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), mul, neg_ref, a0, a1);
+                    if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
+                        exp2_poly3_x2(a0, a1, e0, e1);
+                    } else {
+                        e0 = ex2(a0);
+                        e1 = ex2(a1);
+                    }
+                    add_f32x2(sum_lo, sum_hi, e0, e1);
+                    pw[w] = Sfu<kBf16>::pack(e0, e1);
+                }
+            }
+            tmem_st_32x32b_x32(t_p, pw);
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
+        }
+        if (ok && n > 0) {
+            float inv = 1.0f, total = 1.0f;
+            if constexpr (MODE != 1) {       // the two column halves add their sums
+                sm.xchg[s][half][row_in_tile] = sum_lo + sum_hi;
+                ok = slot_sync(n);
+                total = sm.xchg[s][0][row_in_tile] + sm.xchg[s][1][row_in_tile];
+                inv = 1.0f / total;
+            }
+            ok = ok && mbar_wait(&sm.pv_done[s], uint32_t(n - 1) & 1u, abort_flag, p.status, kWherePvDone);
+            if (ok) {
+                tc_fence_after_sync();
+                const bool real_row = row < p.seq;
+                uint16_t* out_row = p.out + int64_t(b) * p.out_stride_b + int64_t(row) * p.out_stride_s +
+                                    int64_t(hq) * p.out_stride_h + 64 * half;
+#pragma unroll
+                for (int c = 0; c < 2; ++c) {
+                    uint32_t v[32];
+                    tmem_ld_32x32b_x32(t_o + c * 32, v);
+                    tmem_ld_wait();
+                    uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4) {
+                        uint4 w;
+                        w.x = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
+                        w.y = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
+                        w.z = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
+                        w.w = Sfu<kBf16>::pack(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
+                        if (real_row) dst[q4] = w;
+                    }
+                }
+                if (MODE != 1 && p.lse && real_row && half == 0)
+                    p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (reference + log2f(total)) * 0.6931471805599453f;
             }
         }
       }
@@ -511,20 +661,33 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory budget");
     const int n_qblocks = int((seq + kSlots * kTileM - 1) / (kSlots * kTileM));
     const dim3 grid{unsigned(q_heads), unsigned(n_qblocks), unsigned(batch)};
-    auto launch = [&](auto kernel) {
+    auto launch = [&](auto kernel, int threads) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
-        kernel<<<grid, kThreads, smem, stream>>>(map_q, map_k, map_v, p);
+        kernel<<<grid, threads, smem, stream>>>(map_q, map_k, map_v, p);
         return cuda_status(cudaGetLastError());
     };
-    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1, 0>);
+    // The column-split variant pays where the score-mod is instruction-heavy and needs no per-tile row reduction: the
+    // soft-capped mode while cap * log2(e) stays within the range its fixed exponent reference covers (measured +5..10 %).
+    // The sigmoid mode also qualifies but measured 12 % slower with it at S = 16384, so it keeps one thread per row.
+    const bool split = mode == FPT_ATTN_SOFTCAP_TANH && softcap * kLog2e <= kFixedReferenceLimit && fpt::tuning_attention_split();
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1, 0, false>, kThreads);
     const bool softcap_mode = mode == FPT_ATTN_SOFTCAP_TANH;
+    if (softcap_mode && split) {
+        switch (exp2_emu_freq) {
+            case 0: return launch(attention_fwd_kernel<0, 0, true>, kThreadsSplit);
+            case 8: return launch(attention_fwd_kernel<0, 8, true>, kThreadsSplit);
+            case 12: return launch(attention_fwd_kernel<0, 12, true>, kThreadsSplit);
+            case 16: return launch(attention_fwd_kernel<0, 16, true>, kThreadsSplit);
+            default: return launch(attention_fwd_kernel<0, 32, true>, kThreadsSplit);
+        }
+    }
     switch (exp2_emu_freq) {
-        case 0: return softcap_mode ? launch(attention_fwd_kernel<0, 0>) : launch(attention_fwd_kernel<2, 0>);
-        case 8: return softcap_mode ? launch(attention_fwd_kernel<0, 8>) : launch(attention_fwd_kernel<2, 8>);
-        case 12: return softcap_mode ? launch(attention_fwd_kernel<0, 12>) : launch(attention_fwd_kernel<2, 12>);
-        case 16: return softcap_mode ? launch(attention_fwd_kernel<0, 16>) : launch(attention_fwd_kernel<2, 16>);
-        default: return softcap_mode ? launch(attention_fwd_kernel<0, 32>) : launch(attention_fwd_kernel<2, 32>);
+        case 0: return softcap_mode ? launch(attention_fwd_kernel<0, 0, false>, kThreads) : launch(attention_fwd_kernel<2, 0, false>, kThreads);
+        case 8: return softcap_mode ? launch(attention_fwd_kernel<0, 8, false>, kThreads) : launch(attention_fwd_kernel<2, 8, false>, kThreads);
+        case 12: return softcap_mode ? launch(attention_fwd_kernel<0, 12, false>, kThreads) : launch(attention_fwd_kernel<2, 12, false>, kThreads);
+        case 16: return softcap_mode ? launch(attention_fwd_kernel<0, 16, false>, kThreads) : launch(attention_fwd_kernel<2, 16, false>, kThreads);
+        default: return softcap_mode ? launch(attention_fwd_kernel<0, 32, false>, kThreads) : launch(attention_fwd_kernel<2, 32, false>, kThreads);
     }
 }
 

@@ -24,6 +24,7 @@ struct Tuning {
 
 int current_device_info(DeviceInfo* out);
 Tuning tuning();
+bool tuning_attention_split();   // attention forward: column-split score-mod warps where the mode allows (default on)
 
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? FPT_OK : int(e); }
 

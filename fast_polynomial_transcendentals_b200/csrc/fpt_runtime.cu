@@ -18,6 +18,7 @@ DeviceSlot g_devices[kMaxDevices];
 std::mutex g_device_mutex;
 std::atomic<int> g_blocks_per_sm{0};
 std::atomic<int> g_streaming{-1};
+std::atomic<int> g_attention_split{1};
 
 enum { DT_FP16 = kFp16, DT_BF16 = kBf16 };
 enum { SRC_CURRENT = FPT_SRC_CURRENT, SRC_SOLLYA = FPT_SRC_SOLLYA };
@@ -59,6 +60,7 @@ int current_device_info(DeviceInfo* out) {
 }
 
 Tuning tuning() { return Tuning{g_blocks_per_sm.load(), g_streaming.load()}; }
+bool tuning_attention_split() { return g_attention_split.load() != 0; }
 
 const ProgramRow* program_table(int* count) {
     if (count) *count = k_row_count;
@@ -139,6 +141,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!key) return FPT_ERR_NULL_POINTER;
     if (!std::strcmp(key, "blocks_per_sm")) { if (value < 0 || value > 64) return FPT_ERR_BAD_SIZE; fpt::g_blocks_per_sm = value; return FPT_OK; }
     if (!std::strcmp(key, "streaming")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_streaming = value; return FPT_OK; }
+    if (!std::strcmp(key, "attention_split")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_split = value; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
 
@@ -146,6 +149,7 @@ int fpt_get_tuning(const char* key, int* value) {
     if (!key || !value) return FPT_ERR_NULL_POINTER;
     if (!std::strcmp(key, "blocks_per_sm")) { *value = fpt::g_blocks_per_sm; return FPT_OK; }
     if (!std::strcmp(key, "streaming")) { *value = fpt::g_streaming; return FPT_OK; }
+    if (!std::strcmp(key, "attention_split")) { *value = fpt::g_attention_split; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
 
