@@ -198,3 +198,38 @@ def test_running_maximum_that_keeps_growing_is_rescaled(fpt, cuda, oracle):
             for h in range(Hq):
                 want = oracle.attention_rows(qb, kb, vb, 0, h, rows, 2, causal, scale, 0.0, 12)
                 assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
+
+
+@pytest.mark.parametrize("softcap,gain", [(50.0, 1.0), (50.0, 12.0), (30.0, 30.0), (100.0, 1.0), (100.0, 12.0)])
+def test_softcap_layouts_and_saturating_scores(fpt, cuda, oracle, softcap, gain):
+    """Soft-cap 30 / 50 take the column-split layout with its fixed exponent reference, 100 the one-thread-per-row
+    layout with a running maximum; `gain` pushes most scores into the saturated part of the tanh program (rows whose
+    first tile sits at -cap while later tiles reach +cap are the reference's worst case)."""
+    import torch
+    B, S, Hq, Hk, D = 1, 640, 2, 1, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(2024)
+    q = (torch.randn(B, S, Hq, D, device=cuda, generator=g) * gain).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g)
+    k[:, :128] = -k[:, :128].abs() * torch.sign(q[:, :1, :1, :].float().mean(dim=2, keepdim=True))   # a hostile first tile
+    k = k.to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    rows = np.arange(S)
+    for causal in (False, True):
+        results = []
+        for split in (1, 0):
+            assert fpt.load().fpt_set_tuning(b"attention_split", split) == 0
+            out, lse, status = run_attention(fpt, cuda, q, k, v, 0, causal, scale, softcap, 12)
+            assert status == 0 and not torch.isnan(out.float()).any() and not torch.isnan(lse).any()
+            results.append((out, lse))
+        assert fpt.load().fpt_set_tuning(b"attention_split", 1) == 0
+        # the two layouts round P against different exponent references: both must sit within the tolerance of the
+        # oracle, and their log-sum-exp (not rounded to bf16) must agree closely
+        assert float((results[0][1] - results[1][1]).abs().max()) < 2e-3, "lse of the two layouts"
+        for h in range(Hq):
+            want = oracle.attention_rows(qb, kb, vb, 0, h, rows, 0, causal, scale, softcap, 12)
+            for out, _ in results:
+                err = float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max())
+                assert err < 2e-2, (softcap, gain, causal, h, err)
