@@ -1,0 +1,192 @@
+"""Module surgery that puts the fused polynomial kernels into existing models, by structure rather than by class.
+
+The reference patches TorchTitan's Llama feed-forward and grouped experts (reference: src/sfu_repro/torchtitan/plugin.py:197-265
+fused gate/up projection + packed SwiGLU, :294-372 routed experts) and Hugging Face MLPs and activation slots (reference:
+scripts/benchmark_open_weights.py:1072-1158).  Neither framework is a dependency here: a module qualifies by its
+attributes (`gate_proj / up_proj / down_proj` or `w1 / w3 / w2`), so the same functions serve both families.
+
+Every patch is reversible (`restore(model)`) except the weight-fusing one, which rewrites parameters in place as the
+reference does.
+"""
+from __future__ import annotations
+
+from types import MethodType
+from typing import Any, Callable
+
+import torch
+from torch import nn
+
+from .activations import (resolve_mlp_activation_impl, resolve_mlp_activation_mul_impl,
+                          resolve_mlp_activation_packed_impl)
+
+_ORIGINAL = "_sfu_original_forward"
+_SLOT = "_sfu_original_activation"
+
+
+def _projection_names(module: nn.Module) -> tuple[str, str, str] | None:
+    """(gate, up, down) attribute names of a gated MLP, or None."""
+    for names in (("gate_proj", "up_proj", "down_proj"), ("w1", "w3", "w2")):
+        if all(isinstance(getattr(module, n, None), nn.Linear) for n in names):
+            return names
+    return None
+
+
+def dense_swiglu_modules(model: nn.Module) -> list[nn.Module]:
+    return [m for m in model.modules() if _projection_names(m) is not None]
+
+
+def patch_dense_swiglu(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
+                       coeff_source: str = "current") -> int:
+    """down(act(gate(x)) * up(x)) with the fused SwiGLU kernel between the projections; weights untouched."""
+    implementation = "native_silu" if variant == "native" else "spline_silu_compile"
+    _, activation_mul = resolve_mlp_activation_mul_impl(implementation, degree=degree, coeff_source=coeff_source)
+    patched = 0
+    for module in dense_swiglu_modules(model):
+        gate, up, down = _projection_names(module)
+
+        def forward(self, x, *args, _g=gate, _u=up, _d=down, **kwargs):
+            return getattr(self, _d)(activation_mul(getattr(self, _g)(x), getattr(self, _u)(x)))
+
+        if _ORIGINAL not in module.__dict__:
+            module.__dict__[_ORIGINAL] = module.forward
+        module.forward = MethodType(forward, module)
+        patched += 1
+    return patched
+
+
+class FusedGateUpFeedForward(nn.Module):
+    """One [dim -> 2*hidden] projection, packed SwiGLU, one [hidden -> dim] projection (the B1 layout)."""
+
+    def __init__(self, w_in: nn.Linear, w_out: nn.Linear, activation_packed: Callable[[torch.Tensor], torch.Tensor]):
+        super().__init__()
+        self.w_in, self.w_out = w_in, w_out
+        self.sfu_activation_packed = activation_packed
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.w_out(self.sfu_activation_packed(self.w_in(x)))
+
+    def init_weights(self, init_std: float) -> None:
+        hidden = self.w_out.weight.shape[-1]
+        nn.init.trunc_normal_(self.w_in.weight, mean=0.0, std=0.02)
+        with torch.no_grad():
+            self.w_in.weight[hidden:].mul_(init_std / 0.02)
+        nn.init.trunc_normal_(self.w_out.weight, mean=0.0, std=init_std)
+
+
+@torch.no_grad()
+def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
+                             coeff_source: str = "current", backward_impl: str = "matched") -> int:
+    """Replace every bias-free gated MLP by `FusedGateUpFeedForward` with w_in = cat(gate, up) (rows)."""
+    implementation = "native_silu" if variant == "native" else "spline_silu_compile"
+    _, activation_packed = resolve_mlp_activation_packed_impl(implementation, degree=degree, coeff_source=coeff_source,
+                                                              backward_impl=backward_impl)
+    replaced = 0
+    for parent in list(model.modules()):
+        for child_name, child in list(parent.named_children()):
+            names = _projection_names(child)
+            if names is None:
+                continue
+            gate, up, down = (getattr(child, n) for n in names)
+            if gate.bias is not None or up.bias is not None:
+                continue
+            hidden, dim = gate.weight.shape
+            device, dtype = gate.weight.device, gate.weight.dtype
+            w_in = nn.Linear(dim, 2 * hidden, bias=False, device=device, dtype=dtype)
+            w_out = nn.Linear(hidden, dim, bias=down.bias is not None, device=device, dtype=dtype)
+            if device.type != "meta":
+                w_in.weight.copy_(torch.cat((gate.weight, up.weight), dim=0))
+                w_out.weight.copy_(down.weight)
+                if down.bias is not None:
+                    w_out.bias.copy_(down.bias)
+            setattr(parent, child_name, FusedGateUpFeedForward(w_in, w_out, activation_packed))
+            replaced += 1
+    return replaced
+
+
+def _is_grouped_experts(module: nn.Module) -> bool:
+    weights = [getattr(module, n, None) for n in ("w1", "w2", "w3")]
+    return all(isinstance(w, (torch.Tensor, nn.Parameter)) and w.dim() == 3 for w in weights)
+
+
+def run_grouped_experts(w1, w2, w3, x, num_tokens_per_expert, activation_mul) -> torch.Tensor:
+    """Expert-sorted rows through three grouped GEMMs with the fused SwiGLU between them (the B4 site)."""
+    offsets = torch.cumsum(num_tokens_per_expert, dim=0, dtype=torch.int32)
+    xb = x.bfloat16()
+    gate = torch._grouped_mm(xb, w1.bfloat16().transpose(-2, -1), offs=offsets)
+    up = torch._grouped_mm(xb, w3.bfloat16().transpose(-2, -1), offs=offsets)
+    hidden = activation_mul(gate, up)
+    return torch._grouped_mm(hidden, w2.bfloat16().transpose(-2, -1), offs=offsets).type_as(x)
+
+
+def patch_grouped_experts(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
+                          coeff_source: str = "current") -> int:
+    """Modules holding 3-D `w1 / w2 / w3` ([experts, hidden, dim], [experts, dim, hidden], [experts, hidden, dim])
+    and called as `forward(x, num_tokens_per_expert)`."""
+    implementation = "native_silu" if variant == "native" else "spline_silu_compile"
+    _, activation_mul = resolve_mlp_activation_mul_impl(implementation, degree=degree, coeff_source=coeff_source)
+    patched = 0
+    for module in model.modules():
+        if not _is_grouped_experts(module):
+            continue
+
+        def forward(self, x, num_tokens_per_expert):
+            return run_grouped_experts(self.w1, self.w2, self.w3, x, num_tokens_per_expert, self.sfu_activation_mul)
+
+        module.sfu_activation_mul = activation_mul
+        if _ORIGINAL not in module.__dict__:
+            module.__dict__[_ORIGINAL] = module.forward
+        module.forward = MethodType(forward, module)
+        patched += 1
+    return patched
+
+
+class FunctionActivation(nn.Module):
+    """An activation function in a slot that used to hold a module."""
+
+    def __init__(self, function: Callable[[torch.Tensor], torch.Tensor]):
+        super().__init__()
+        self.function = function
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.function(x if x.is_contiguous() else x.contiguous())
+
+
+def patch_activation_slots(model: nn.Module, *, kind: str = "silu", degree: int | None = None,
+                           coeff_source: str = "current", attributes: tuple[str, ...] = ("act_fn", "activation_fn", "act")) -> int:
+    """Swap SiLU (or GELU) activations held in the usual attribute slots for the polynomial kernel."""
+    targets = {"silu": (nn.SiLU, torch.nn.functional.silu), "gelu": (nn.GELU, torch.nn.functional.gelu)}[kind]
+    _, activation = resolve_mlp_activation_impl(f"spline_{kind}_compile", degree=degree, coeff_source=coeff_source)
+    patched = 0
+    for module in model.modules():
+        for attr in attributes:
+            current = getattr(module, attr, None)
+            if current is None or isinstance(current, FunctionActivation):
+                continue
+            if isinstance(current, targets[0]) or current is targets[1] or type(current).__name__.lower().startswith(kind):
+                module.__dict__.setdefault(_SLOT, {})[attr] = current
+                replacement: Any = FunctionActivation(activation) if isinstance(current, nn.Module) else activation
+                setattr(module, attr, replacement)
+                patched += 1
+    return patched
+
+
+def restore(model: nn.Module) -> int:
+    """Undo `patch_dense_swiglu`, `patch_grouped_experts` and `patch_activation_slots`."""
+    restored = 0
+    for module in model.modules():
+        if hasattr(module, _ORIGINAL):
+            original = module.__dict__.pop(_ORIGINAL)
+            module.__dict__.pop("forward", None)                 # back to the class's own forward ...
+            if getattr(original, "__func__", None) is not type(module).forward:
+                module.forward = original                        # ... unless the instance already carried its own
+            restored += 1
+        slots = module.__dict__.pop(_SLOT, None)
+        if slots:
+            for attr, original in slots.items():
+                setattr(module, attr, original)
+                restored += 1
+    return restored
+
+
+__all__ = ["FunctionActivation", "FusedGateUpFeedForward", "dense_swiglu_modules", "fuse_gate_up_projections",
+           "patch_activation_slots", "patch_dense_swiglu", "patch_grouped_experts", "restore", "run_grouped_experts"]
