@@ -1,6 +1,7 @@
 """GPU: throughput of our kernels next to the reference's own kernels (compiled from the reference sources into
-oracle/_ref with the reference's flags) on the same B200, same inputs, same timing protocol.  Writes the table to
-gpurun_out/perf_vs_reference.json and asserts only that we are not slower than the reference beyond noise."""
+oracle/_ref with the reference's flags) on the same B200, same inputs, same timing protocol.  Writes the table as
+perf_vs_reference.json into the directory named by FPT_PERF_OUT (default: a scratch folder at the repository root)
+and asserts only that we are not slower than the reference beyond noise."""
 import ctypes
 import json
 from pathlib import Path
@@ -142,7 +143,8 @@ def test_throughput_next_to_reference_kernels(fpt, cuda, ref_kernels):
     by = 4 * q.numel() * 2
     rows.append({"what": "rope_apply_d5_d6_fp16_B2_S16384_H32_D128", "ref_ms": t_ref, "ours_ms": t_our,
                  "ref_gbs": by / t_ref / 1e6, "ours_gbs": by / t_our / 1e6})
-    out_dir = ROOT / "gpurun_out"
+    import os
+    out_dir = Path(os.environ.get("FPT_PERF_OUT", ROOT / "gpurun_out"))
     out_dir.mkdir(exist_ok=True)
     (out_dir / "perf_vs_reference.json").write_text(json.dumps(rows, indent=1))
     for row in rows:
