@@ -11,8 +11,9 @@
 // Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
 // tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
 // (the backward has no row reduction, so the split needs no exchange).
-// Tensor memory: S is never overwritten by P (dQ stores no P; dK/dV keep P in the upper half of the dP tile), so the
-// S product of the next step runs under the score-mod of the current one; dQ also double-buffers dP.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
+// Tensor memory: S is never overwritten (each score-mod warp writes its bf16 dS and P words over its own 64 columns of
+// the dP tile), so the S product of the next step runs under the score-mod of the current one; dQ also double-buffers
+// dP.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
 // Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
 #include <cstring>
 #include <type_traits>
@@ -64,6 +65,23 @@ struct BwdParams {
     B3Words b3;
 };
 
+// Optional timeline for tuning builds (-DFPT_ATTN_TRACE): block (0,0,0) stores (tag, SM clock) pairs behind the status
+// word, 4096 words per traced warp and kernel; the caller must then pass a status buffer of 128 KiB.
+#ifdef FPT_ATTN_TRACE
+#define FPT_BTRACE(slot, tag)                                                                             \
+    do {                                                                                                  \
+        if (trace_on && lane == 0 && trace_n < 2046) {                                                    \
+            uint32_t* t_ = p.status + 64 + ((slot) + 3 * WHICH) * 4096;                                   \
+            t_[2 + trace_n] = uint32_t(tag);                                                              \
+            t_[3 + trace_n] = uint32_t(clock64());                                                        \
+            trace_n += 2;                                                                                 \
+            t_[0] = uint32_t(trace_n);                                                                    \
+        }                                                                                                 \
+    } while (0)
+#else
+#define FPT_BTRACE(slot, tag) do { } while (0)
+#endif
+
 enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone };
 
 __device__ __forceinline__ float ex2f(float x) { return mufu_ex2(x); }
@@ -107,6 +125,11 @@ __global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const Prepas
             a.lse2[row] = a.lse[bh * a.seq + s] * kLog2eB;
         }
     }
+}
+
+// four consecutive floats from shared memory (address from smem_u32, 16-byte aligned)
+__device__ __forceinline__ void lds128(uint32_t addr, float (&v)[4]) {
+    asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]) : "r"(addr));
 }
 
 // bf16x2 of two fp32 values (low lane first)
@@ -164,10 +187,12 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
     }
 }
 
-// Tensor-memory columns.  WHICH 0 (dQ): S 0..127, two dP tiles 128..255 and 256..383 (bf16 dS over the first 64 columns
-// of the tile it was computed from), acc0 384..511.  WHICH 1 (dK, dV): S 0..127, one dP tile 128..255 with bf16 dS over
-// columns 128..191 and bf16 P over 192..255, acc0 (dK) 256..383, acc1 (dV) 384..511.
-constexpr uint32_t kColS = 0, kColDp = 128, kColP = 192, kColAcc1 = 384;
+// Tensor-memory columns.  WHICH 0 (dQ): S 0..127, two dP tiles 128..255 and 256..383, acc0 384..511.  WHICH 1 (dK, dV):
+// S 0..127, one dP tile 128..255, acc0 (dK) 256..383, acc1 (dV) 384..511.  Inside a dP tile each column half (64 fp32
+// columns = the 64 keys or queries of one score-mod warp per lane quarter) is overwritten by that warp's own results:
+// 32 columns of bf16 dS pairs, then 32 columns of bf16 P pairs; the products read K steps 0..3 from the first half and
+// 4..7 from the second.
+constexpr uint32_t kColS = 0, kColDp = 128, kColAcc1 = 384;
 template <int WHICH>
 struct Cols {
     static constexpr uint32_t acc0 = WHICH == 0 ? 384u : 256u;
@@ -198,6 +223,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int fixed_head_x = head;
     const int stream_head0 = WHICH == 0 ? head / group : head * group;
     volatile uint32_t* abort_flag = &sm.abort_flag;
+#ifdef FPT_ATTN_TRACE
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8);
+    int trace_n = 0;
+#endif
 
     if (threadIdx.x == 0) {
         mbar_init(&sm.xy_full, 1);
@@ -310,6 +339,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 // [A] S (and dP) of step t are in registers: S of step t+1 may overwrite S
                 ok = mbar_wait(&sm.ld_done, uint32_t(t) & 1u, abort_flag, p.status, kBwdLdDone);
                 if (!ok) break;
+                FPT_BTRACE(2, 10);
                 if (more) {
                     ok = mbar_wait(&sm.uw_full[st_next], uint32_t((t + 1) / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
                     if (!ok) break;
@@ -321,21 +351,24 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         umma_commit(&sm.s_full);
                     }
                 }
+                FPT_BTRACE(2, 11);
                 // [B] dS (and P) of step t are in tensor memory
                 ok = mbar_wait(&sm.p_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdPFull);
                 if (!ok) break;
                 tc_fence_after_sync();
+                FPT_BTRACE(2, 12);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)       // acc0 += dS U
-                    umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 8u * kk, u_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
-                                  idesc_mn, t > 0 || kk > 0);
+                    umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 64u * (kk >> 2) + 8u * (kk & 3),
+                                  u_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 if constexpr (WHICH == 1) {
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)   // acc1 += P W
-                        umma_ts_words(tmem + kColAcc1, tmem + kColP + 8u * kk, w_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
-                                      idesc_mn, t > 0 || kk > 0);
+                        umma_ts_words(tmem + kColAcc1, tmem + dp_col(t) + 64u * (kk >> 2) + 32u + 8u * (kk & 3),
+                                      w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 }
                 umma_commit(&sm.uw_empty[st]);
+                FPT_BTRACE(2, 13);
                 // [C] WHICH 1: the one dP tile is free again once the products above have read it (same thread, in order)
                 if constexpr (WHICH == 1) {
                     if (more) {
@@ -356,7 +389,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const int r = 32 * quarter + lane;                       // row of the fixed tile = tensor-memory lane
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
         const uint32_t t_s = tmem + lane_base + kColS + uint32_t(64 * half);
-        const uint32_t t_p = tmem + lane_base + kColP + uint32_t(32 * half);   // bf16 pairs: 32 words per half
         float row_lse2 = 0.0f, row_delta = 0.0f;
         if (WHICH == 0 && MODE != 1) {
             const int64_t off = (int64_t(b) * p.q_heads + head) * seq_pad + row0 + r;
@@ -366,26 +398,28 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         bool ok = true;
         for (int t = 0; t < n_inner && ok; ++t) {
             const int st = t % kRing;
+            FPT_BTRACE(half, 1);
             ok = mbar_wait(&sm.s_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdSFull);
             if (!ok) break;
             tc_fence_after_sync();
-            uint32_t sv[64], dv[64];
+            FPT_BTRACE(half, 2);
+            // This warp owns columns [64 half, 64 half + 64) of the dP tile: it reads its dP values from there and writes
+            // its bf16 dS words over the first 32 and its bf16 P words over the last 32 of them, so no other warp's loads
+            // are in the way and nobody waits for anybody.  S and dP are read in full first; then the issuer is told
+            // at once (S of the next step can start under this step's arithmetic), and the results leave in two chunks.
+            uint32_t dv[64], sv[64];
+            const uint32_t t_own = tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * half);
+            tmem_ld_32x32b_x32(t_own, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
+            tmem_ld_32x32b_x32(t_own + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
             tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sv[0]));
             tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sv[32]));
-            const uint32_t t_dp = tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * half);
-            const uint32_t t_ds = tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(32 * half);
-            tmem_ld_32x32b_x32(t_dp, reinterpret_cast<uint32_t(&)[32]>(dv[0]));
-            tmem_ld_32x32b_x32(t_dp + 32, reinterpret_cast<uint32_t(&)[32]>(dv[32]));
             tmem_ld_wait();
-            // P and dS overwrite columns from which the other warp of this lane quarter reads S and dP: every load
-            // first, then the stores (a bounded mbarrier wait rather than a named barrier, so that a warp that gave
-            // up after a timeout cannot leave the others waiting for ever)
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ld_done);
-            ok = mbar_wait(&sm.ld_done, uint32_t(t) & 1u, abort_flag, p.status, kBwdLdDone);
+            FPT_BTRACE(half, 3);
             if (WHICH == 1 && MODE != 1)   // the per-query vectors arrived on this barrier (already complete here)
-                ok = ok && mbar_wait(&sm.uw_full[st], uint32_t(t / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
+                ok = mbar_wait(&sm.uw_full[st], uint32_t(t / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
             if (!ok) break;
             const int g = WHICH == 0 ? 0 : t / per_head;
             const int c0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile + 64 * half;   // first column
@@ -393,37 +427,59 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             const int tile_c0 = c0 - 64 * half;
             const bool diagonal = (p.causal && tile_c0 == row0) ||
                                   (ragged && (tile_c0 + kTile > p.seq || row0 + kTile > p.seq));
+            const uint32_t lse_addr = smem_u32(&sm.lse2[st][64 * half]), delta_addr = smem_u32(&sm.delta[st][64 * half]);
+            // results leave in two chunks of 16 words where the arithmetic is light (plain softmax: the stores overlap the
+            // second chunk's exponentials) and in one piece where it is heavy (measured: the instruction-bound modes lose
+            // about 10 % when their arithmetic is cut in two by the stores)
+            constexpr bool kChunkedStores = MODE == 2;
             uint32_t pw[32], dsw[32];
-            auto columns = [&](auto masked) {
 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const int c = 2 * i;                 // column pair inside this half
-                    float l0 = row_lse2, l1 = row_lse2, e0 = row_delta, e1 = row_delta;
-                    if (WHICH == 1 && MODE != 1) {
-                        const float2 lv = *reinterpret_cast<const float2*>(&sm.lse2[st][64 * half + c]);
-                        const float2 dl = *reinterpret_cast<const float2*>(&sm.delta[st][64 * half + c]);
-                        l0 = lv.x; l1 = lv.y; e0 = dl.x; e1 = dl.y;
+            for (int chunk = 0; chunk < 2; ++chunk) {
+                auto columns = [&](auto masked) {
+#pragma unroll
+                    for (int quad = 0; quad < 8; ++quad) {       // four columns = two pairs per 128-bit shared load
+                        const int cq = 32 * chunk + 4 * quad;
+                        float lv[4] = {row_lse2, row_lse2, row_lse2, row_lse2};
+                        float dl[4] = {row_delta, row_delta, row_delta, row_delta};
+                        if (WHICH == 1 && MODE != 1) {
+                            lds128(lse_addr + 4u * cq, lv);
+                            lds128(delta_addr + 4u * cq, dl);
+                        }
+#pragma unroll
+                        for (int h2 = 0; h2 < 2; ++h2) {
+                            const int c = cq + 2 * h2;           // column pair inside this half
+                            bool m0 = false, m1 = false;
+                            if constexpr (decltype(masked)::value) {   // rows are queries (WHICH 0) or keys (WHICH 1)
+                                const int row_abs = row0 + r, col_abs = c0 + c;
+                                const int query0 = WHICH == 0 ? row_abs : col_abs, key0 = WHICH == 0 ? col_abs : row_abs;
+                                const int query1 = WHICH == 0 ? row_abs : col_abs + 1, key1 = WHICH == 0 ? col_abs + 1 : row_abs;
+                                m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
+                                m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
+                            }
+                            score_pair<MODE>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
+                                             __uint_as_float(dv[c + 1]), lv[2 * h2], lv[2 * h2 + 1], dl[2 * h2], dl[2 * h2 + 1],
+                                             m0, m1, pw[16 * chunk + 2 * quad + h2], dsw[16 * chunk + 2 * quad + h2]);
+                        }
                     }
-                    bool m0 = false, m1 = false;
-                    if constexpr (decltype(masked)::value) {   // rows are queries (WHICH 0) or keys (WHICH 1)
-                        const int row_abs = row0 + r, col_abs = c0 + c;
-                        const int query0 = WHICH == 0 ? row_abs : col_abs, key0 = WHICH == 0 ? col_abs : row_abs;
-                        const int query1 = WHICH == 0 ? row_abs : col_abs + 1, key1 = WHICH == 0 ? col_abs + 1 : row_abs;
-                        m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
-                        m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
-                    }
-                    score_pair<MODE>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
-                                     __uint_as_float(dv[c + 1]), l0, l1, e0, e1, m0, m1, pw[i], dsw[i]);
+                };
+                if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
+                else columns(std::false_type{});
+                if constexpr (kChunkedStores) {
+                    tmem_st_32x32b_x16(t_own + 16 * chunk, reinterpret_cast<const uint32_t(&)[16]>(dsw[16 * chunk]));
+                    if constexpr (WHICH == 1)                  // only dK / dV need P itself
+                        tmem_st_32x32b_x16(t_own + 32 + 16 * chunk, reinterpret_cast<const uint32_t(&)[16]>(pw[16 * chunk]));
                 }
-            };
-            if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
-            else columns(std::false_type{});
-            if constexpr (WHICH == 1) tmem_st_32x32b_x32(t_p, pw);   // only dK / dV need P itself
-            tmem_st_32x32b_x32(t_ds, dsw);
+            }
+            if constexpr (!kChunkedStores) {
+                tmem_st_32x32b_x32(t_own, dsw);
+                if constexpr (WHICH == 1) tmem_st_32x32b_x32(t_own + 32, pw);
+            }
+            FPT_BTRACE(half, 5);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full);
+            FPT_BTRACE(half, 6);
         }
         if (ok && n_inner > 0) {
             ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
