@@ -137,3 +137,55 @@ def test_every_name_of_the_reference_operator_module_exists():
     assert not missing, missing
     missing = [name for name in surface["dispatcher"] if not hasattr(torch.ops.spline_ops, name)]
     assert not missing, missing
+
+
+def test_module_surgery_finds_patches_and_restores_by_structure():
+    """No kernel runs here: the adapters recognise gated MLPs, experts and activation slots by their attributes."""
+    import torch
+    from torch import nn
+
+    from fast_polynomial_transcendentals_b200.sfu_repro import adapters
+
+    class HF(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.gate_proj, self.up_proj, self.down_proj = nn.Linear(8, 16, bias=False), nn.Linear(8, 16, bias=False), nn.Linear(16, 8, bias=False)
+            self.act_fn = nn.SiLU()
+
+        def forward(self, x):
+            return self.down_proj(self.act_fn(self.gate_proj(x)) * self.up_proj(x))
+
+    class Titan(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1, self.w2, self.w3 = nn.Linear(8, 16, bias=False), nn.Linear(16, 8, bias=False), nn.Linear(8, 16, bias=False)
+
+        def forward(self, x):
+            return self.w2(torch.nn.functional.silu(self.w1(x)) * self.w3(x))
+
+    class Experts(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1, self.w2, self.w3 = (nn.Parameter(torch.zeros(2, 16, 8)), nn.Parameter(torch.zeros(2, 8, 16)),
+                                         nn.Parameter(torch.zeros(2, 16, 8)))
+
+        def forward(self, x, counts):
+            return x
+
+    model = nn.ModuleDict({"a": HF(), "b": Titan(), "c": Experts(), "d": nn.Linear(8, 8)})
+    assert len(adapters.dense_swiglu_modules(model)) == 2
+    x = torch.randn(3, 8)
+    want = model["a"](x)
+    assert adapters.patch_dense_swiglu(model) == 2
+    assert adapters.patch_grouped_experts(model) == 1
+    assert adapters.patch_activation_slots(model, kind="silu") == 1
+    assert isinstance(model["a"].act_fn, adapters.FunctionActivation)
+    assert adapters.restore(model) == 4
+    assert isinstance(model["a"].act_fn, nn.SiLU) and "forward" not in model["a"].__dict__
+    assert torch.equal(model["a"](x), want)
+    before = sum(p.numel() for p in model.parameters())
+    w1, w3 = model["b"].w1.weight.clone(), model["b"].w3.weight.clone()
+    assert adapters.fuse_gate_up_projections(model) == 2
+    assert sum(p.numel() for p in model.parameters()) == before
+    assert torch.equal(model["b"].w_in.weight, torch.cat((w1, w3), dim=0))
+    assert getattr(model["b"].sfu_activation_packed, "__spline_op__", None) == "spline_ops::swish_mul_packed_variant_fwd"
