@@ -90,3 +90,34 @@ def test_error_statistics_sit_beside_the_published_ones(cuda, case):
     out_dir = Path(os.environ.get("FPT_PERF_OUT", Path(__file__).resolve().parents[1] / "gpurun_out"))
     out_dir.mkdir(exist_ok=True)
     (out_dir / f"attention_numerics_{case}.json").write_text(json.dumps(report, indent=1))
+
+
+def test_elementwise_sites_reproduce_the_published_statistics(cuda):
+    """B1 (SiLU D3) and B4 (SwiGLU D3) against the degree-0 SFU kernels, N(0,1) bf16 inputs, the reference's shapes
+    (reference: scripts/benchmark_components.py:150-222, 366-430)."""
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_ops
+    g = torch.Generator(device=cuda)
+    g.manual_seed(1234)
+    report = {}
+    n = GOLDEN["B1"]["shape"]["elements"]
+    x = torch.randn(n, device=cuda, dtype=torch.bfloat16, generator=g)
+    go = torch.randn(n, device=cuda, dtype=torch.bfloat16, generator=g)
+    report["B1"] = {"forward": tensor_error(spline_ops.swish_fwd_variant(x, 3, 0), spline_ops.swish_fwd_variant(x, 0, 0)),
+                    "backward": tensor_error(spline_ops.swish_bwd_variant(go, x, 3, 0), spline_ops.swish_bwd_variant(go, x, 0, 0))}
+    del x, go
+    rows, hidden = GOLDEN["B4"]["shape"]["rows"], GOLDEN["B4"]["shape"]["hidden_size"]
+    gate = torch.randn(rows, hidden, device=cuda, dtype=torch.bfloat16, generator=g)
+    up = torch.randn(rows, hidden, device=cuda, dtype=torch.bfloat16, generator=g)
+    go = torch.randn(rows, hidden, device=cuda, dtype=torch.bfloat16, generator=g)
+    poly_g, poly_u = spline_ops.swish_mul_bwd_variant(go, gate, up, 3, 0)
+    nat_g, nat_u = spline_ops.swish_mul_bwd_variant(go, gate, up, 0, 0)
+    report["B4"] = {"forward": tensor_error(spline_ops.swish_mul_fwd_variant(gate, up, 3, 0), spline_ops.swish_mul_fwd_variant(gate, up, 0, 0)),
+                    "grad_gate": tensor_error(poly_g, nat_g), "grad_up": tensor_error(poly_u, nat_u)}
+    print(json.dumps(report, indent=1))
+    for case, tensors in report.items():
+        for name, ours in tensors.items():
+            want = GOLDEN[case]["tensors"][name]
+            assert 0.9 * want["relative_mae"] <= ours["relative_mae"] <= 1.1 * want["relative_mae"], (case, name, ours, want)
+            assert abs(ours["cosine"] - want["cosine"]) <= 5e-5, (case, name, ours, want)
+            assert ours["max_abs"] <= 2.0 * want["max_abs"], (case, name, ours, want)
