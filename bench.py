@@ -70,6 +70,7 @@ def cpu_sweep(oracle, inputs):
 def cpu_baseline(sample_elems=1 << 22, budget_s=12.0):
     from oracle import oracle
     oracle.build()
+    threads = oracle.set_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1
     inputs = cpu_sample_inputs(sample_elems)
     cpu_sweep(oracle, inputs)
     t0 = time.perf_counter()
@@ -78,7 +79,7 @@ def cpu_baseline(sample_elems=1 << 22, budget_s=12.0):
         done += cpu_sweep(oracle, inputs)
         passes += 1
     dt = time.perf_counter() - t0
-    return {"value": done / dt, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+    return {"value": done / dt, "unit": "elements/s", "cores": threads, "kind": "port",
             "sample": f"{passes} passes of the 5-function sweep at 2^{int(math.log2(sample_elems))} elements per "
                       f"function, exact packed-FMA emulator (OpenMP, all host threads)"}
 
@@ -89,6 +90,7 @@ def run_reference_arm(args):
         return
     from oracle import oracle
     oracle.build()
+    threads = oracle.set_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1
     n = 1 << 21
     inputs = cpu_sample_inputs(n)
     for _ in range(max(1, min(args.warmup, 2))):
@@ -104,7 +106,7 @@ def run_reference_arm(args):
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": os.cpu_count(), "kind": "port",
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": threads, "kind": "port",
                          "sample": f"each step = the 5-function sweep at 2^21 elements per function (bounded "
                                    f"sample of the 2^28 workload), exact packed-FMA emulator, all host threads"},
         "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},

@@ -20,6 +20,24 @@
 
 #include <stdlib.h>
 
+/* ------------------------------------------------------------- threading */
+
+#ifdef _OPENMP
+#include <omp.h>
+#endif
+
+/* Number of OpenMP threads the loops below use from now on (n <= 0: leave as is); returns the count in effect.
+ * Launchers such as torchrun export OMP_NUM_THREADS=1, which would otherwise silently make the timed CPU legs scalar. */
+int fpt_oracle_set_threads(int n) {
+#ifdef _OPENMP
+    if (n > 0) omp_set_num_threads(n);
+    return omp_get_max_threads();
+#else
+    (void)n;
+    return 1;
+#endif
+}
+
 /* ------------------------------------------------------------------ table */
 
 enum { SH_ODD_HALF, SH_ODD, SH_ODD_SAT, SH_SWISH, SH_XMUL_HALF, SH_EVEN, SH_ALG_SIG, SH_ALG_TANH };

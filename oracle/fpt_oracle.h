@@ -33,6 +33,7 @@ int fpt_oracle_program_info(int program, char* name_out, int name_cap, int* dtyp
                             int* shape, int* degree, uint16_t* clamp, uint16_t* coeffs7);
 uint16_t fpt_oracle_eval_lane(int program, uint16_t x);
 
+int fpt_oracle_set_threads(int n);
 void fpt_oracle_unary(int program, const uint16_t* in, uint16_t* out, int64_t n);
 void fpt_oracle_unary_repeat(int program, const uint16_t* in, uint16_t* out, int64_t n, int repeats);
 void fpt_oracle_binary_bwd(int program, const uint16_t* grad_out, const uint16_t* x, uint16_t* grad_in, int64_t n);

@@ -92,6 +92,14 @@ def _c16(a) -> np.ndarray:
     return np.ascontiguousarray(a, dtype=np.uint16)
 
 
+def set_threads(n: int = 0) -> int:
+    """Use `n` OpenMP threads from now on (0: keep the current setting); returns the number in effect."""
+    fn = lib().fpt_oracle_set_threads
+    fn.argtypes = [ctypes.c_int]
+    fn.restype = ctypes.c_int
+    return int(fn(int(n)))
+
+
 def find_program(name: str, dtype: int, source: int = CURRENT) -> int:
     idx = lib().fpt_oracle_find_program(name.encode(), dtype, source)
     if idx < 0:
