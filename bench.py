@@ -439,7 +439,7 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
         sq, sk, sv, so = arr(q), arr(k), arr(v), arr(o)
         ks = [("attn", 0, lambda: _lib.check("fpt_attention_fwd_routed", lib.fpt_attention_fwd_routed(
             o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, Sq, Hq, Hk, D, sq, sk, sv, so, mode,
-            causal, 1.0 / math.sqrt(D), cap, log2_n, route, status.data_ptr(), S())))]
+            causal, 1.0 / math.sqrt(D), cap, log2_n, 0, route, status.data_ptr(), S())))]
         _, t = time_sweep(ks, 5, 2)
         if int(status.item()) != 0:
             raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x}")

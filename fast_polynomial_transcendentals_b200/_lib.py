@@ -41,7 +41,7 @@ SIGNATURES: dict[str, list] = {
     "fpt_unary_hybrid": [_vp, _vp, _i64, _int, _vp],
     "fpt_binary_bwd_hybrid": [_vp, _vp, _vp, _i64, _int, _vp],
     "fpt_exp2_fraction": [_vp, _vp, _i64, _int, _int, _vp],
-    "fpt_exp2_poly_f32": [_vp, _vp, _i64, _vp],
+    "fpt_exp2_full_f32": [_vp, _vp, _i64, _int, _vp],
     "fpt_sincos": [_vp, _vp, _i64, _int, _int, _vp],
     "fpt_sincos_f32": [_vp, _vp, _i64, _int, _int, _vp],
     "fpt_rope_table": [_vp, _vp, _i64, _i64, _int, _int, _vp],
@@ -55,7 +55,7 @@ SIGNATURES: dict[str, list] = {
                           ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _int, _vp, _vp],
     "fpt_attention_fwd_routed": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64),
                                  ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int,
-                                 ctypes.c_float, ctypes.c_float, _int, _int, _vp, _vp],
+                                 ctypes.c_float, ctypes.c_float, _int, _int, _int, _vp, _vp],
     "fpt_selftest_umma": [_vp, _vp, _vp, _int, _vp, _vp],
     "fpt_rope_apply_static_table": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_rope_static_table_capacity": [],

@@ -64,8 +64,8 @@ struct AttnParams {
 
 // EMU: routing frequency of the software exponential in the soft-max modes, with the meaning the reference gives
 // exp2_emu_freq (reference: src/sfu_repro/fa4.py:724-733): 0 keeps every lane on the special-function unit; a positive
-// frequency f sends four of every f keys of a row through the fp32 cubic on the FMA pipe (12 -> one third, 32 -> one
-// eighth).  The unit delivers 16 results per clock and SM, which for a 128 x 128 tile takes as long as the two
+// frequency f sends four of every f keys of a row through a software exponential on the FMA pipe (12 -> one third,
+// 32 -> one eighth); EK picks it: the cubic ("d3") or the two-piece line ("pwl2") of fpt_scoremod.cuh.  The unit delivers 16 results per clock and SM, which for a 128 x 128 tile takes as long as the two
 // tensor-core products of that tile: that is the pressure the routing is meant to relieve.
 // Optional timeline for tuning builds (-DFPT_ATTN_TRACE): block (0,0,0) stores (tag, SM clock) pairs behind the
 // status word, 4096 words per traced warp; the caller must then pass a status buffer of 64 KiB.
@@ -127,7 +127,7 @@ constexpr int kThreadsSplit = 128 + 256 * kSlots;
 constexpr float kFixedReferenceLimit = 98.0f;
 constexpr float kFixedReferenceSpan = 96.0f;
 
-template <int MODE, int EMU, bool SPLIT>
+template <int MODE, int EMU, bool SPLIT, int EK = kExp2FullD3>
 __global__ void __launch_bounds__(SPLIT ? kThreadsSplit : kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                      const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
@@ -385,7 +385,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     float a0, a1, e0, e1;
                     fma_f32x2(__uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), mul, neg_ref, a0, a1);
                     if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
-                        exp2_poly3_x2(a0, a1, e0, e1);
+                        exp2_full_x2<EK>(a0, a1, e0, e1);
                     } else {
                         e0 = ex2(a0);
                         e1 = ex2(a1);
@@ -554,7 +554,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         fma_f32x2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), mul, neg_max, a0, a1);
                         float e0, e1;
                         if (EMU > 0 && (i % (EMU > 0 ? EMU / 2 : 1)) < 2) {
-                            exp2_poly3_x2(a0, a1, e0, e1);   // FMA pipe: keys 2i, 2i+1 fall in the routed four of their group
+                            exp2_full_x2<EK>(a0, a1, e0, e1);   // FMA pipe: keys 2i, 2i+1 fall in the routed four of their group
                         } else {
                             e0 = ex2(a0);                    // special-function unit
                             e1 = ex2(a1);
@@ -613,7 +613,8 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
                                         int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                                         const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                                         const int64_t* out_strides, int mode, int causal, float scale, float softcap,
-                                        int log2_n, int exp2_emu_freq, void* status, fpt_stream_t stream) {
+                                        int log2_n, int exp2_emu_backend, int exp2_emu_freq, void* status,
+                                        fpt_stream_t stream) {
     if (!out || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !out_strides)
         return FPT_ERR_NULL_POINTER;
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
@@ -625,6 +626,8 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     if (exp2_emu_freq != 0 && exp2_emu_freq != 8 && exp2_emu_freq != 12 && exp2_emu_freq != 16 && exp2_emu_freq != 32)
         return FPT_ERR_BAD_ENUM;
     if (mode == FPT_ATTN_SIGMOID_DIRECT && exp2_emu_freq != 0) return FPT_ERR_BAD_ENUM;   // no exponential to route
+    if (exp2_emu_backend != FPT_EXP2_FULL_D3 && exp2_emu_backend != FPT_EXP2_FULL_PWL2) return FPT_ERR_BAD_ENUM;
+    if (exp2_emu_backend == FPT_EXP2_FULL_PWL2 && exp2_emu_freq != 0 && mode != FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
     if (reinterpret_cast<uintptr_t>(out) & 15u) return FPT_ERR_MISALIGNED;
     for (int i = 0; i < 3; ++i)
         if ((out_strides[i] * 2) & 15) return FPT_ERR_MISALIGNED;
@@ -682,6 +685,15 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
             default: return launch(attention_fwd_kernel<0, 32, true>, kThreadsSplit);
         }
     }
+    if (!softcap_mode && exp2_emu_backend == FPT_EXP2_FULL_PWL2) {
+        switch (exp2_emu_freq) {
+            case 0: break;
+            case 8: return launch(attention_fwd_kernel<2, 8, false, kExp2FullPwl2>, kThreads);
+            case 12: return launch(attention_fwd_kernel<2, 12, false, kExp2FullPwl2>, kThreads);
+            case 16: return launch(attention_fwd_kernel<2, 16, false, kExp2FullPwl2>, kThreads);
+            default: return launch(attention_fwd_kernel<2, 32, false, kExp2FullPwl2>, kThreads);
+        }
+    }
     switch (exp2_emu_freq) {
         case 0: return softcap_mode ? launch(attention_fwd_kernel<0, 0, false>, kThreads) : launch(attention_fwd_kernel<2, 0, false>, kThreads);
         case 8: return softcap_mode ? launch(attention_fwd_kernel<0, 8, false>, kThreads) : launch(attention_fwd_kernel<2, 8, false>, kThreads);
@@ -697,5 +709,6 @@ extern "C" int fpt_attention_fwd(void* out, void* lse, const void* q, const void
                                  const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
                                  void* status, fpt_stream_t stream) {
     return fpt_attention_fwd_routed(out, lse, q, k, v, batch, seq, q_heads, kv_heads, head_dim, q_strides, k_strides,
-                                    v_strides, out_strides, mode, causal, scale, softcap, log2_n, 0, status, stream);
+                                    v_strides, out_strides, mode, causal, scale, softcap, log2_n, FPT_EXP2_FULL_D3, 0,
+                                    status, stream);
 }

@@ -64,22 +64,23 @@ struct Exp2Op {
     }
 };
 
-// fp32 2^a through the degree-3 polynomial on the FMA pipe: the stand-alone form of the evaluator the attention
-// kernel mixes with the special-function unit.  Four values per thread and step, packed fp32 arithmetic.
-__global__ void __launch_bounds__(kBlock) exp2_poly_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
+// fp32 2^a through the full-range software evaluators (cubic or two-piece line after floor reduction): the
+// stand-alone form of what the attention kernel mixes with the special-function unit.  Four values per thread and step.
+template <int KIND>
+__global__ void __launch_bounds__(kBlock) exp2_full_f32_kernel(const float* __restrict__ in, float* __restrict__ out,
                                                               int64_t n) {
     const int64_t quads = n / 4;
 #pragma unroll 1
     for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < quads; i += int64_t(gridDim.x) * kBlock) {
         const float4 a = reinterpret_cast<const float4*>(in)[i];
         float4 e;
-        exp2_poly3_x2(a.x, a.y, e.x, e.y);
-        exp2_poly3_x2(a.z, a.w, e.z, e.w);
+        exp2_full_x2<KIND>(a.x, a.y, e.x, e.y);
+        exp2_full_x2<KIND>(a.z, a.w, e.z, e.w);
         reinterpret_cast<float4*>(out)[i] = e;
     }
     if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
         const int64_t i = quads * 4 + threadIdx.x;
-        out[i] = exp2_poly3(in[i]);
+        out[i] = exp2_full<KIND>(in[i]);
     }
 }
 
@@ -137,8 +138,9 @@ extern "C" int fpt_exp2_fraction(void* out, const void* in, int64_t n, int varia
     return launch_stream(Exp2Op<1>{exp2_words(variant == FPT_EXP2_HINGE_ENDPOINT), repeats}, a, n, stream);
 }
 
-extern "C" int fpt_exp2_poly_f32(void* out, const void* in, int64_t n, fpt_stream_t stream) {
+extern "C" int fpt_exp2_full_f32(void* out, const void* in, int64_t n, int variant, fpt_stream_t stream) {
     if (n < 0) return FPT_ERR_BAD_SIZE;
+    if (variant != FPT_EXP2_FULL_D3 && variant != FPT_EXP2_FULL_PWL2) return FPT_ERR_BAD_ENUM;
     if (n == 0) return FPT_OK;
     if (!out || !in) return FPT_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return FPT_ERR_MISALIGNED;
@@ -147,6 +149,9 @@ extern "C" int fpt_exp2_poly_f32(void* out, const void* in, int64_t n, fpt_strea
     int64_t grid = (n / 4 + kBlock - 1) / kBlock;
     if (grid < 1) grid = 1;
     if (grid > 0x7fffffff) grid = 0x7fffffff;
-    exp2_poly_f32_kernel<<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
+    if (variant == FPT_EXP2_FULL_D3)
+        exp2_full_f32_kernel<kExp2FullD3><<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
+    else
+        exp2_full_f32_kernel<kExp2FullPwl2><<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
     return cuda_status(cudaGetLastError());
 }

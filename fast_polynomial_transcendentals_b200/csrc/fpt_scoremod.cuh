@@ -100,53 +100,94 @@ __device__ __forceinline__ uint32_t exp2_hinge(uint32_t x, const Exp2Words& k) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------
-// 2^a in fp32 on the FMA pipe, for the share of the soft-max exponentials taken off the special-function unit.
-//   a'  = max(a, -125)                      (results below 2^-125 are not needed; keeps the exponent field valid)
-//   xr  = a' + 1.5 * 2^23   (round to nearest even: the low mantissa bits of xr now hold n = round(a'))
-//   f   = a' - (xr - 1.5 * 2^23)            in [-1/2, 1/2], exact
-//   p   = c0 + f (c1 + f (c2 + f c3))       minimax for 2^f in relative error, 7.5e-5
-//   2^a = bits(p) + (bits(xr) << 23)        (the shift drops the magic constant's own bits, n lands on the exponent)
-// Every step is one IEEE operation, so a C restatement with fmaf gives the same bits.
-constexpr float kExp2PolyC0 = 0.9999280571937561f;   // 0x3f7ffb49
-constexpr float kExp2PolyC1 = 0.6932609677314758f;   // 0x3f31798d
-constexpr float kExp2PolyC2 = 0.2426111251115799f;   // 0x3e786f0d
-constexpr float kExp2PolyC3 = 0.0551716685295105f;   // 0x3d61fbb0
-constexpr float kExp2PolyMagic = 12582912.0f;        // 1.5 * 2^23
-constexpr float kExp2PolyFloor = -125.0f;
+// Full-range 2^a in fp32 on the FMA pipe: the software exponentials that take a share of the soft-max work off the
+// special-function unit (reference: autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:106-198, FullDegree3 and
+// FullPwl2Hinge; the same sequences, operation for operation, so that results agree bit for bit):
+//   a'  = max(a, -127)
+//   xr  = a' + 1.5 * 2^23  rounded TOWARDS MINUS INFINITY (the low mantissa bits of xr now hold n = floor(a'))
+//   f   = a' - (xr - 1.5 * 2^23)             in [0, 1), exact
+//   D3:   p = 1 + f (c1 + f (c2 + f c3))                         cubic, relative error 8.8e-5
+//   PWL2: p = k0 + k1 f + k2 max(f - 1/2, 0)                     continuous two-piece line, relative error 2.1e-2
+//   2^a = bits(p) + (bits(xr) << 23)         (the shift drops the magic constant's own bits, n lands on the exponent)
+// Every step is one IEEE operation (flush-to-zero as in the reference; no step here meets a subnormal for a <= 127).
+enum Exp2Full : int { kExp2FullD3 = 0, kExp2FullPwl2 = 1 };
+constexpr float kExp2Magic = 12582912.0f;            // 0x4B400000
+// Lowest argument: -127 for the cubic (p >= 1, so the sum of bit patterns ends exactly at +0); -126 for the two-piece
+// line, which starts at p = 0.989 < 1: one exponent lower its bit pattern would wrap to a negative NaN pattern (the
+// reference clamps both at -127 and only feeds the line arguments above that; masked soft-max scores are -inf).
+template <int KIND> constexpr float kExp2Floor = KIND == 0 ? -127.0f : -126.0f;
+constexpr float kExp2D3C1 = 0.6951461434364319f;     // 0x3F31F519
+constexpr float kExp2D3C2 = 0.22756439447402954f;    // 0x3E6906A4
+constexpr float kExp2D3C3 = 0.07711908966302872f;    // 0x3D9DF09D
+constexpr float kExp2PwlK0 = 0.9894611835479736f;    // 0x3F7D4D54
+constexpr float kExp2PwlK1 = 0.820852518081665f;     // 0x3F522364
+constexpr float kExp2PwlK2 = 0.34246066212654114f;   // 0x3EAF5701
 
-__device__ __forceinline__ float exp2_poly3(float a) {
-    a = fmaxf(a, kExp2PolyFloor);
-    const float xr = __fadd_rn(a, kExp2PolyMagic);
-    const float f = __fsub_rn(a, __fsub_rn(xr, kExp2PolyMagic));
-    float p = __fmaf_rn(kExp2PolyC3, f, kExp2PolyC2);
-    p = __fmaf_rn(p, f, kExp2PolyC1);
-    p = __fmaf_rn(p, f, kExp2PolyC0);
+template <int KIND>
+__device__ __forceinline__ float exp2_full(float a) {
+    a = fmaxf(a, kExp2Floor<KIND>);
+    const float xr = __fadd_rd(a, kExp2Magic);
+    const float f = __fsub_rn(a, __fsub_rn(xr, kExp2Magic));
+    float p;
+    if constexpr (KIND == kExp2FullD3) {
+        p = __fmaf_rn(f, kExp2D3C3, kExp2D3C2);
+        p = __fmaf_rn(p, f, kExp2D3C1);
+        p = __fmaf_rn(p, f, 1.0f);
+    } else {
+        const float h = fmaxf(__fsub_rn(f, 0.5f), 0.0f);
+        p = __fmaf_rn(f, kExp2PwlK1, kExp2PwlK0);
+        p = __fmaf_rn(h, kExp2PwlK2, p);
+    }
     return __uint_as_float(__float_as_uint(p) + (__float_as_uint(xr) << 23));
 }
 
-// The same function on two values at once with the packed fp32 instructions (two lanes per issue slot).
-__device__ __forceinline__ void exp2_poly3_x2(float a0, float a1, float& e0, float& e1) {
-    a0 = fmaxf(a0, kExp2PolyFloor);
-    a1 = fmaxf(a1, kExp2PolyFloor);
+// The same on two values at once with the packed fp32 instructions (two lanes per issue slot).
+template <int KIND>
+__device__ __forceinline__ void exp2_full_x2(float a0, float a1, float& e0, float& e1) {
+    a0 = fmaxf(a0, kExp2Floor<KIND>);
+    a1 = fmaxf(a1, kExp2Floor<KIND>);
     uint32_t p0, p1, x0, x1;
-    asm("{\n\t.reg .b64 a, m, xr, n, f, p, c;\n\t"
-        "mov.b64 a, {%4, %5};\n\t"
-        "mov.b64 m, {%6, %6};\n\t"
-        "add.rn.f32x2 xr, a, m;\n\t"
-        "sub.rn.f32x2 n, xr, m;\n\t"
-        "sub.rn.f32x2 f, a, n;\n\t"
-        "mov.b64 p, {%7, %7};\n\t"
-        "mov.b64 c, {%8, %8};\n\t"
-        "fma.rn.f32x2 p, p, f, c;\n\t"
-        "mov.b64 c, {%9, %9};\n\t"
-        "fma.rn.f32x2 p, p, f, c;\n\t"
-        "mov.b64 c, {%10, %10};\n\t"
-        "fma.rn.f32x2 p, p, f, c;\n\t"
-        "mov.b64 {%0, %1}, p;\n\t"
-        "mov.b64 {%2, %3}, xr;\n\t}"
-        : "=r"(p0), "=r"(p1), "=r"(x0), "=r"(x1)
-        : "f"(a0), "f"(a1), "f"(kExp2PolyMagic), "f"(kExp2PolyC3), "f"(kExp2PolyC2), "f"(kExp2PolyC1),
-          "f"(kExp2PolyC0));
+    if constexpr (KIND == kExp2FullD3) {
+        asm("{\n\t.reg .b64 a, m, xr, n, f, p, c;\n\t"
+            "mov.b64 a, {%4, %5};\n\t"
+            "mov.b64 m, {%6, %6};\n\t"
+            "add.rm.ftz.f32x2 xr, a, m;\n\t"
+            "sub.rn.ftz.f32x2 n, xr, m;\n\t"
+            "sub.rn.ftz.f32x2 f, a, n;\n\t"
+            "mov.b64 p, {%7, %7};\n\t"
+            "mov.b64 c, {%8, %8};\n\t"
+            "fma.rn.ftz.f32x2 p, f, p, c;\n\t"
+            "mov.b64 c, {%9, %9};\n\t"
+            "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+            "mov.b64 c, {%10, %10};\n\t"
+            "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+            "mov.b64 {%0, %1}, p;\n\t"
+            "mov.b64 {%2, %3}, xr;\n\t}"
+            : "=r"(p0), "=r"(p1), "=r"(x0), "=r"(x1)
+            : "f"(a0), "f"(a1), "f"(kExp2Magic), "f"(kExp2D3C3), "f"(kExp2D3C2), "f"(kExp2D3C1), "f"(1.0f));
+    } else {
+        float f0, f1;
+        asm("{\n\t.reg .b64 a, m, xr, n, f;\n\t"
+            "mov.b64 a, {%4, %5};\n\t"
+            "mov.b64 m, {%6, %6};\n\t"
+            "add.rm.ftz.f32x2 xr, a, m;\n\t"
+            "sub.rn.ftz.f32x2 n, xr, m;\n\t"
+            "sub.rn.ftz.f32x2 f, a, n;\n\t"
+            "mov.b64 {%0, %1}, f;\n\t"
+            "mov.b64 {%2, %3}, xr;\n\t}"
+            : "=f"(f0), "=f"(f1), "=r"(x0), "=r"(x1) : "f"(a0), "f"(a1), "f"(kExp2Magic));
+        const float h0 = fmaxf(__fsub_rn(f0, 0.5f), 0.0f), h1 = fmaxf(__fsub_rn(f1, 0.5f), 0.0f);
+        asm("{\n\t.reg .b64 f, h, p, c;\n\t"
+            "mov.b64 f, {%2, %3};\n\t"
+            "mov.b64 h, {%4, %5};\n\t"
+            "mov.b64 p, {%6, %6};\n\t"
+            "mov.b64 c, {%7, %7};\n\t"
+            "fma.rn.ftz.f32x2 p, f, p, c;\n\t"
+            "mov.b64 c, {%8, %8};\n\t"
+            "fma.rn.ftz.f32x2 p, h, c, p;\n\t"
+            "mov.b64 {%0, %1}, p;\n\t}"
+            : "=r"(p0), "=r"(p1) : "f"(f0), "f"(f1), "f"(h0), "f"(h1), "f"(kExp2PwlK1), "f"(kExp2PwlK0), "f"(kExp2PwlK2));
+    }
     e0 = __uint_as_float(p0 + (x0 << 23));
     e1 = __uint_as_float(p1 + (x1 << 23));
 }

@@ -318,9 +318,10 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
     if route:
         if mode == 1:
             raise NotImplementedError("sigmoid attention has no exponential to route")
-        if exp2_emu_backend != "d3":
-            raise NotImplementedError(f"exp2 backend {exp2_emu_backend!r} is not built; the routed software "
-                                      "exponential of this kernel is the fp32 cubic ('d3')")
+        if exp2_emu_backend not in ("d3", "pwl2") or (exp2_emu_backend == "pwl2" and mode != 2):
+            raise NotImplementedError(f"exp2 backend {exp2_emu_backend!r} is not built for this mode; built: the fp32 "
+                                      "cubic 'd3' (soft-max modes) and the two-piece line 'pwl2' (plain soft-max), the "
+                                      "two full-range evaluators whose instruction sequences the reference publishes")
         if route not in (8, 12, 16, 32):
             raise NotImplementedError("built routing frequencies: 0, 8, 12, 16, 32")
     out = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
@@ -330,7 +331,8 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
     with torch.cuda.device(q.device):
         _lib.call("fpt_attention_fwd_routed", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), batch,
                   seq, q_heads, k.shape[2], dim, strides(q), strides(k), strides(v), strides(out), mode, int(bool(causal)),
-                  scale, cap, log2_n, route, status.data_ptr(), torch.cuda.current_stream(q.device).cuda_stream)
+                  scale, cap, log2_n, 1 if exp2_emu_backend == "pwl2" else 0, route, status.data_ptr(),
+                  torch.cuda.current_stream(q.device).cuda_stream)
     return out, lse
 
 

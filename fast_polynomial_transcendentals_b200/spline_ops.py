@@ -610,27 +610,17 @@ def exp2_fraction(x, variant: int = EXP2_HINGE_LEAST_SQUARES, repeats: int = 1):
 
 
 
-def exp2_poly_f32(x):
-    """2^x for fp32 x <= 127 on the FMA pipe (cubic after range reduction); inputs below -125 give 2^-125."""
+EXP2_FULL_D3, EXP2_FULL_PWL2 = 0, 1
+
+
+def exp2_full_f32(x, variant: int = EXP2_FULL_D3):
+    """2^x for fp32 x <= 127 on the FMA pipe: floor reduction, then a cubic (D3) or a two-piece line (PWL2) in the
+    fraction; inputs below -127 give the value at -127."""
     if x.dtype != torch.float32 or not x.is_cuda or not x.is_contiguous():
         raise ValueError("x must be a contiguous fp32 CUDA tensor")
     out = torch.empty_like(x)
-    _call("fpt_exp2_poly_f32", x, out.data_ptr(), x.data_ptr(), x.numel())
+    _call("fpt_exp2_full_f32", x, out.data_ptr(), x.data_ptr(), x.numel(), int(variant))
     return out
-
-def b3_sigmoid_direct(scores, log2_n: int = 12, with_grad: bool = False):
-    """Direct piecewise-cubic sigmoid(score - log n) of sigmoid attention; scores bf16 or fp32 -> bf16."""
-    if not isinstance(scores, torch.Tensor) or not scores.is_cuda:
-        raise RuntimeError("scores must be a CUDA tensor")
-    if not scores.is_contiguous():
-        raise RuntimeError("scores must be contiguous")
-    if scores.dtype not in (torch.bfloat16, torch.float32):
-        raise RuntimeError("scores must be bfloat16 or float32")
-    prob = torch.empty(scores.shape, dtype=torch.bfloat16, device=scores.device)
-    grad = torch.empty_like(prob) if with_grad else None
-    _call("fpt_b3_sigmoid_direct", scores, prob.data_ptr(), grad.data_ptr() if with_grad else None, scores.data_ptr(),
-          scores.numel(), int(scores.dtype == torch.float32), int(log2_n))
-    return (prob, grad) if with_grad else prob
 
 
 # ---- differentiable entry points (reference: C++ autograd Functions, spline_ops.cpp:1933-2205) ---

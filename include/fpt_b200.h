@@ -145,12 +145,16 @@ int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n,
 enum { FPT_EXP2_NATIVE = 0, FPT_EXP2_HINGE_LEAST_SQUARES = 1, FPT_EXP2_HINGE_ENDPOINT = 2 };
 int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int repeats, fpt_stream_t stream);
 
-/* ---- fp32 2^a on the FMA pipe: a' = max(a, -125), n = round(a'), f = a' - n, degree-3 minimax polynomial in f
- *      (relative error 7.5e-5), n added to the exponent field.  This is the software exponential that the attention
- *      kernel interleaves with the special-function unit in its soft-max modes (the technique of the exp2-offload
- *      probe, reference: autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:53-99, carried to fp32 with a
- *      cubic so that the bf16 probabilities keep their precision).  in/out: fp32 [n], 16-byte aligned; a <= 127. */
-int fpt_exp2_poly_f32(void* out, const void* in, int64_t n, fpt_stream_t stream);
+/* ---- full-range fp32 2^a on the FMA pipe: a' = max(a, -127), n = floor(a') through a round-down magic-constant add,
+ *      f = a' - n, then a cubic in f (FPT_EXP2_FULL_D3, relative error 8.8e-5) or a continuous two-piece line
+ *      (FPT_EXP2_FULL_PWL2, 2.1e-2), n added to the exponent field
+ *      replaces FullDegree3 / FullPwl2Hinge of the reference's benchmark, operation for operation (reference:
+ *      autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:106-198); these are the software exponentials the
+ *      attention kernel routes a share of its soft-max lanes through.  in/out: fp32 [n], 16-byte aligned; a <= 127.
+ *      One difference: the two-piece line clamps at -126, not -127 (its p starts below 1, so at n = -127 the
+ *      reference's bit arithmetic wraps into a NaN pattern; -inf is a regular input of a masked soft-max). */
+enum { FPT_EXP2_FULL_D3 = 0, FPT_EXP2_FULL_PWL2 = 1 };
+int fpt_exp2_full_f32(void* out, const void* in, int64_t n, int variant, fpt_stream_t stream);
 
 /* ---- paired sin/cos: fp32 angles [n] -> out [2, n] 16-bit, cos plane first
  *      replaces launch_sincos_*_{fp16,bf16}[_compute] (reference: sincos_kernels.cu:527-975 evaluators,
@@ -249,16 +253,17 @@ int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const 
                       int causal, float scale, float softcap, int log2_n, void* status, fpt_stream_t stream);
 
 /* ---- the same forward with the soft-max exponentials partly routed to the FMA pipe
- *      replaces the exp2_emu_backend="d3" / exp2_emu_freq routing of the reference's attention interface
+ *      replaces the exp2_emu_backend / exp2_emu_freq routing of the reference's attention interface
  *      (reference: src/sfu_repro/fa4.py:34-47 backends, :724-752 routed configurations, forward kwargs :790-807):
  *      exp2_emu_freq 0 keeps every exponential on the special-function unit; f in {8, 12, 16, 32} sends four of
- *      every f keys of a row through fpt_exp2_poly_f32's cubic instead (one half, third, quarter, eighth).
- *      Only the soft-max modes route; FPT_ATTN_SIGMOID_DIRECT has no exponential and accepts 0 only. */
+ *      every f keys of a row through a software exponential of fpt_exp2_full_f32 instead (one half, third, quarter,
+ *      eighth): exp2_emu_backend FPT_EXP2_FULL_D3 ("d3") in both soft-max modes, FPT_EXP2_FULL_PWL2 ("pwl2") in
+ *      FPT_ATTN_SOFTMAX.  FPT_ATTN_SIGMOID_DIRECT has no exponential and accepts frequency 0 only. */
 int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
                              int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                              const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
                              const int64_t* out_strides, int mode, int causal, float scale, float softcap, int log2_n,
-                             int exp2_emu_freq, void* status, fpt_stream_t stream);
+                             int exp2_emu_backend, int exp2_emu_freq, void* status, fpt_stream_t stream);
 
 /* ---- attention backward for the same three modes, bf16, head_dim 128, any sequence length
  *      replaces the backward of the patched FlashAttention interface the reference drives through

@@ -295,27 +295,57 @@ void fpt_oracle_exp2_hinge_repeat(const uint16_t* in, uint16_t* out, int64_t n, 
     }
 }
 
-/* fp32 2^a by range reduction and a cubic on the FMA pipe; this is the build's own evaluator (it has no counterpart
- * in the reference, whose exp2 replacement is the 16-bit hinge above), restated here operation by operation so
- * that the device result can be compared bit for bit: every step below is a single IEEE-754 binary32 operation. */
-static inline float exp2_poly3_lane(float a) {
+/* Full-range fp32 2^a of the reference's routed soft-max exponentials (reference:
+ * autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:106-198, FullDegree3 and FullPwl2Hinge), restated operation
+ * by operation: clamp at -127, floor through a round-DOWN add of 1.5*2^23, fraction in [0,1), a cubic (variant 0) or
+ * a continuous two-piece line (variant 1) in the fraction, and the integer part added to the exponent field.  Every
+ * step is a single IEEE-754 binary32 operation, so the device result can be compared bit for bit. */
+#include <fenv.h>
+
+static inline float add_round_down(float a, float b) {
+    /* nearest sum, its exact error by the two-sum identity (every step volatile binary32), one step down if the
+     * nearest sum lies above the exact one */
+    volatile float r = a + b;
+    volatile float bb = r - a;
+    volatile float t = r - bb;
+    volatile float ea = a - t;
+    volatile float eb = b - bb;
+    volatile float err = ea + eb;
+    float out = r;
+    if (err < 0.0f) out = nextafterf(out, -INFINITY);
+    return out;
+}
+
+static inline float exp2_full_lane(float a, int variant) {
     volatile float xr, n, f, p;   /* volatile: no step may be fused or reassociated */
     union { float f; uint32_t u; } pb, xb, r;
-    if (!(a >= -125.0f)) a = -125.0f;          /* max(a, -125) with the NaN-dropping rule of PTX max */
-    xr = a + 12582912.0f;
+    /* max(a, floor) with the NaN-dropping rule of PTX max.  The cubic has p >= 1, so -127 ends at bit pattern 0; the
+     * two-piece line starts at p = 0.989 < 1, whose exponent field would wrap below -126 (the reference's sequence,
+     * floor -127 for both, is only used above that): the device clamps that kind at -126 and so does this. */
+    const float floor_value = variant == 0 ? -127.0f : -126.0f;
+    if (!(a >= floor_value)) a = floor_value;
+    if (fabsf(a) < 1.17549435e-38f) a = copysignf(0.0f, a);   /* .ftz on every device step: subnormal inputs are zero */
+    xr = add_round_down(a, 12582912.0f);
     n = xr - 12582912.0f;
     f = a - n;
-    p = fmaf(0.0551716685295105f, f, 0.2426111251115799f);
-    p = fmaf(p, f, 0.6932609677314758f);
-    p = fmaf(p, f, 0.9999280571937561f);
+    if (variant == 0) {
+        p = fmaf(f, 0.07711908966302872f, 0.22756439447402954f);
+        p = fmaf(p, f, 0.6951461434364319f);
+        p = fmaf(p, f, 1.0f);
+    } else {
+        volatile float h = f - 0.5f;
+        if (!(h > 0.0f)) h = 0.0f;
+        p = fmaf(f, 0.820852518081665f, 0.9894611835479736f);
+        p = fmaf(h, 0.34246066212654114f, p);
+    }
     pb.f = p; xb.f = xr;
     r.u = pb.u + (xb.u << 23);
     return r.f;
 }
 
-void fpt_oracle_exp2_poly3_f32(const float* in, float* out, int64_t n) {
+void fpt_oracle_exp2_full_f32(const float* in, float* out, int64_t n, int variant) {
 #pragma omp parallel for schedule(static)
-    for (int64_t i = 0; i < n; ++i) out[i] = exp2_poly3_lane(in[i]);
+    for (int64_t i = 0; i < n; ++i) out[i] = exp2_full_lane(in[i], variant);
 }
 
 /* ------------------------------------------------------------ paired sincos */

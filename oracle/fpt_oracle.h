@@ -53,7 +53,7 @@ void fpt_oracle_swish_shared_sigmoid(const uint16_t* x, const uint16_t* s, uint1
 void fpt_oracle_exp2_hinge(const uint16_t* in, uint16_t* out, int64_t n, int set);
 int fpt_oracle_sincos_f32(int variant, const float* angles, float* out, int64_t n, int iterations);
 void fpt_oracle_exp2_hinge_repeat(const uint16_t* in, uint16_t* out, int64_t n, int set, int repeats);
-void fpt_oracle_exp2_poly3_f32(const float* in, float* out, int64_t n);
+void fpt_oracle_exp2_full_f32(const float* in, float* out, int64_t n, int variant);
 
 int fpt_oracle_sincos_is_bf16(int variant);
 void fpt_oracle_sincos_packed(int variant, const float* angles, uint16_t* cos_out, uint16_t* sin_out, int64_t n);

@@ -69,7 +69,7 @@ def lib() -> ctypes.CDLL:
         L.fpt_oracle_multiply.argtypes = [_u16p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_fma16.argtypes = [_u16p, _u16p, _u16p, _u16p, _i64, _int]
         L.fpt_oracle_swish_shared_sigmoid.argtypes = [_u16p, _u16p, _u16p, _u16p, _i64, _int]
-        L.fpt_oracle_exp2_poly3_f32.argtypes = [_f32p, _f32p, _i64]
+        L.fpt_oracle_exp2_full_f32.argtypes = [_f32p, _f32p, _i64, _int]
         L.fpt_oracle_sincos_f32.argtypes = [_int, _f32p, _f32p, _i64, _int]
         L.fpt_oracle_sincos_f32.restype = ctypes.c_int
         L.fpt_oracle_sincos_packed.argtypes = [_int, _f32p, _u16p, _u16p, _i64]
@@ -234,11 +234,14 @@ def exp2_hinge(x: np.ndarray, constant_set: int = 0, repeats: int = 1) -> np.nda
     return out
 
 
-def exp2_poly3(x: np.ndarray) -> np.ndarray:
-    """fp32 2^x through the cubic evaluator (bit pattern of the device function)."""
+EXP2_FULL_D3, EXP2_FULL_PWL2 = 0, 1
+
+
+def exp2_full(x: np.ndarray, variant: int = EXP2_FULL_D3) -> np.ndarray:
+    """fp32 2^x through the full-range software evaluators (bit pattern of the device functions)."""
     x = np.ascontiguousarray(x, dtype=np.float32)
     out = np.empty_like(x)
-    lib().fpt_oracle_exp2_poly3_f32(x.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), x.size)
+    lib().fpt_oracle_exp2_full_f32(x.ctypes.data_as(_f32p), out.ctypes.data_as(_f32p), x.size, variant)
     return out
 
 

@@ -30,7 +30,7 @@ def test_umma_tile_matches_matmul(fpt, cuda, mode):
     assert err < 1e-3 * max(1.0, want.abs().max().item()), err
 
 
-def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=12, exp2_emu_freq=None):
+def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=12, exp2_emu_freq=None, exp2_emu_backend=0):
     """q,k,v torch bf16 (B,S,H,D), any strides with D contiguous. Returns (out (B,S,Hq,D), lse, status)."""
     import ctypes
     import torch
@@ -45,8 +45,8 @@ def run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap=0.0, log2_n=1
                  D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, status.data_ptr(), stream())
     else:
         fpt.call("fpt_attention_fwd_routed", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S,
-                 Hq, Hk, D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, exp2_emu_freq,
-                 status.data_ptr(), stream())
+                 Hq, Hk, D, arr(q), arr(k), arr(v), arr(out), mode, int(causal), scale, softcap, log2_n, exp2_emu_backend,
+                 exp2_emu_freq, status.data_ptr(), stream())
     torch.cuda.synchronize()
     return out, lse, int(status.item()) & 0xFFFFFFFF
 
@@ -163,6 +163,28 @@ def test_routed_exp2_stays_within_tolerance(fpt, cuda, oracle, freq, mode, causa
     for h in range(Hq):
         want = oracle.attention_rows(qb, kb, vb, 0, h, rows, mode, causal, scale, softcap, 12)
         assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
+
+
+@pytest.mark.parametrize("freq", [8, 32])
+def test_routed_two_piece_exponential(fpt, cuda, oracle, freq):
+    """Backend "pwl2" (2 % exponential) on a share of the lanes: outputs stay within a bound that scales with the share."""
+    import torch
+    B, S, Hq, Hk, D = 1, 384, 2, 1, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(98)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    base, lse0, st0 = run_attention(fpt, cuda, q, k, v, 2, True, scale, 0.0, 12, exp2_emu_freq=0)
+    out, lse, st = run_attention(fpt, cuda, q, k, v, 2, True, scale, 0.0, 12, exp2_emu_freq=freq, exp2_emu_backend=1)
+    assert st0 == 0 and st == 0
+    diff = float((out.float() - base.float()).abs().max())
+    lse_diff = float((lse - lse0).abs().max())
+    assert diff < 0.03 * 4 / freq * 8 + 8e-3, diff
+    assert lse_diff < 0.03, lse_diff
+    with pytest.raises(Exception):      # the two-piece line is offered for the plain soft-max only
+        run_attention(fpt, cuda, q, k, v, 0, True, scale, 30.0, 12, exp2_emu_freq=freq, exp2_emu_backend=1)
 
 
 def test_routed_exp2_rejects_unbuilt_frequencies(fpt, cuda):

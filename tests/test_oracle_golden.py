@@ -109,18 +109,29 @@ def test_exp2_hinge_pins_and_model(oracle, vectors):
     assert out.tolist() == [0x3C00, 0x4000]
 
 
-def test_exp2_poly3_restatement_accuracy_and_exponent_handling(oracle):
-    xs = np.concatenate([np.linspace(-125, 127, 2_000_001), np.arange(-125, 128) + 0.5, np.arange(-125, 128) - 0.5 + 1e-6])
+def test_full_range_exp2_restatements(oracle):
+    """Floor reduction + cubic / two-piece line (the reference's FullDegree3 / FullPwl2Hinge sequences)."""
+    xs = np.concatenate([np.linspace(-126, 127, 2_000_001), np.arange(-126, 128) + 0.5, np.arange(-126, 128) - 1e-6])
     xs = xs.astype(np.float32)
-    xs = xs[(xs >= -125) & (xs <= 127)]
-    got = oracle.exp2_poly3(xs).astype(np.float64)
-    rel = np.abs(got / np.exp2(xs.astype(np.float64)) - 1)
-    assert rel.max() < 7.6e-5
-    ints = np.arange(-125, 128, dtype=np.float32)
-    # at an integer the fraction is 0 and the result is c0 * 2^n exactly
-    assert np.array_equal(oracle.exp2_poly3(ints), (np.float32(0.9999280571937561) * np.exp2(ints.astype(np.float64))).astype(np.float32))
-    low = oracle.exp2_poly3(np.array([-125.5, -1e6, -np.inf, np.nan], dtype=np.float32))
-    assert np.all(low == oracle.exp2_poly3(np.array([-125.0], dtype=np.float32))[0])
+    xs = xs[(xs >= -126) & (xs <= 127)]
+    truth = np.exp2(xs.astype(np.float64))
+    d3 = oracle.exp2_full(xs, oracle.EXP2_FULL_D3).astype(np.float64)
+    pwl = oracle.exp2_full(xs, oracle.EXP2_FULL_PWL2).astype(np.float64)
+    assert np.abs(d3 / truth - 1).max() < 8.9e-5          # published for this cubic: 8.8e-5
+    assert np.abs(pwl / truth - 1).max() < 2.2e-2
+    ints = np.arange(-126, 128, dtype=np.float32)
+    assert np.array_equal(oracle.exp2_full(ints, 0), np.exp2(ints.astype(np.float64)).astype(np.float32))   # f = 0: p = 1
+    # below -127 the clamp holds, and the exponent field reaches zero there: the result is +0
+    low = oracle.exp2_full(np.array([-127.0, -127.5, -1e6, -np.inf, np.nan], dtype=np.float32), 0)
+    assert np.all(low == 0.0)
+    low = oracle.exp2_full(np.array([-126.0, -127.5, -1e6, -np.inf, np.nan], dtype=np.float32), 1)
+    assert np.all(low.view(np.uint32) == 0x007D4D54)     # the line clamps one exponent higher: p's mantissa, exponent field 0
+    # subnormal inputs are zero (flush-to-zero on every step); the smallest normal negative rounds down to n = -1, f = 1
+    tiny = oracle.exp2_full(np.array([-1e-40, 1e-40, -1e-30], dtype=np.float32), 0)
+    assert tiny[0] == 1.0 and tiny[1] == 1.0 and 0.9999 < tiny[2] < 1.0
+    # the fraction never leaves [0, 1): just below an integer the round-down add takes the lower integer
+    x = np.nextafter(np.float32(3.0), np.float32(0.0))
+    assert 7.99 < float(oracle.exp2_full(np.array([x], dtype=np.float32), 0)[0]) < 8.0
 
 
 def test_error_ceilings_against_true_functions(oracle):

@@ -91,30 +91,32 @@ def test_exp2_hinge_bit_exact_and_native_close(fpt, cuda, oracle):
     assert float(rel) < 0.0115  # published max-rel 0.0109
 
 
-def test_exp2_poly_f32_bit_exact_and_accurate(fpt, cuda, oracle):
-    """The fp32 cubic that the attention kernel mixes with the special-function unit, as a flat kernel."""
+@pytest.mark.parametrize("variant,bound", [(0, 8.9e-5), (1, 2.2e-2)])
+def test_full_range_exp2_bit_exact_and_accurate(fpt, cuda, oracle, variant, bound):
+    """The software exponentials that the attention kernel mixes with the special-function unit, as a flat kernel."""
     import torch
     rng = np.random.default_rng(77)
-    edge = np.array([0.0, -0.0, 0.5, -0.5, 1.0, -1.0, 8.0, -125.0, -126.0, -1000.0, -np.inf, 127.0, 126.99999,
-                     -124.5, 0.49999997, -0.49999997, 1.5, 2.5, -1.5, 1e-30, -1e-30], dtype=np.float32)
+    edge = np.array([0.0, -0.0, 0.5, -0.5, 1.0, -1.0, 8.0, -126.0, -127.0, -1000.0, -np.inf, 127.0, 126.99999,
+                     -124.5, 0.49999997, -0.49999997, 1.5, 2.5, -1.5, 1e-30, -1e-30, 2.9999998, -3.0000002], dtype=np.float32)
     for n in (1, 3, 4, 7, (1 << 20) + 3):
         xs = np.concatenate([edge, rng.uniform(-140, 127, n).astype(np.float32)])[:max(n, 1)] if n < 64 else \
             np.concatenate([edge, rng.uniform(-140, 127, n).astype(np.float32), rng.uniform(-30, 8, n).astype(np.float32)])
         x = torch.from_numpy(xs).to(cuda)
         out = torch.empty_like(x)
-        fpt.call("fpt_exp2_poly_f32", out.data_ptr(), x.data_ptr(), x.numel(), stream())
+        fpt.call("fpt_exp2_full_f32", out.data_ptr(), x.data_ptr(), x.numel(), variant, stream())
         torch.cuda.synchronize()
         got = out.cpu().numpy()
-        want = oracle.exp2_poly3(xs)
+        want = oracle.exp2_full(xs, variant)
         bad = np.nonzero(got.view(np.uint32) != want.view(np.uint32))[0]
         assert bad.size == 0, (n, bad[:5], xs[bad[:5]], got[bad[:5]], want[bad[:5]])
-        inside = xs >= -125
+        inside = xs >= -126
         rel = np.abs(got[inside].astype(np.float64) / np.exp2(xs[inside].astype(np.float64)) - 1)
-        assert rel.max() < 7.6e-5    # the minimax error of the cubic, 7.48e-5, plus fp32 rounding
-        assert np.all(got[~inside] == oracle.exp2_poly3(np.array([-125.0], dtype=np.float32))[0])   # clamped
-    assert fpt.load().fpt_exp2_poly_f32(None, None, 5, None) != 0            # null pointers
+        assert rel.max() < bound
+        assert np.all(got[xs <= -127] < 1.2e-38) and np.all(got[xs <= -127] >= 0.0)   # cubic: +0; line: 0.989 * 2^-126
+    assert fpt.load().fpt_exp2_full_f32(None, None, 5, variant, None) != 0            # null pointers
     x = torch.zeros(9, dtype=torch.float32, device=cuda)
-    assert fpt.load().fpt_exp2_poly_f32(x.data_ptr() + 4, x.data_ptr(), 4, None) != 0   # misaligned
+    assert fpt.load().fpt_exp2_full_f32(x.data_ptr() + 4, x.data_ptr(), 4, variant, None) != 0   # misaligned
+    assert fpt.load().fpt_exp2_full_f32(x.data_ptr(), x.data_ptr(), 4, 7, None) != 0              # unknown variant
 
 
 # ---- sin/cos -------------------------------------------------------------------------------------
