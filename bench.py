@@ -533,6 +533,28 @@ def run_profile_case(args):
         o = torch.empty_like(x)
         fn, deg = {"sigmoid": (0, 3), "tanh": (1, 4), "silu": (2, 3), "sigmoid_native": (0, 0)}[case]
         run = lambda: _lib.check("fpt_unary", lib.fpt_unary(o.data_ptr(), x.data_ptr(), n, fn, 0, deg, 0, 0, stream))
+    elif case.startswith("rep16_"):
+        # ALU-bound probes at an L2-resident size (use --profile-n 1048576): 16 evaluations per loaded element, polynomial
+        # and native twin of each function, to read FMA-pipe against XU-pipe (MUFU) use
+        name = case[len("rep16_"):]
+        if name in ("sigmoid", "tanh", "silu", "sigmoid_native", "tanh_native", "silu_native"):
+            x = (torch.rand(n, device=device, generator=g) * 16 - 8).to(torch.float16)
+            o = torch.empty_like(x)
+            fn, deg = {"sigmoid": (0, 3), "tanh": (1, 4), "silu": (2, 3), "sigmoid_native": (0, 0), "tanh_native": (1, 0),
+                       "silu_native": (2, 0)}[name]
+            run = lambda: _lib.check("fpt_unary_repeat", lib.fpt_unary_repeat(o.data_ptr(), x.data_ptr(), n, fn, 0, deg, 0, 0, 16, stream))
+        elif name in ("exp2", "exp2_native"):
+            x = torch.rand(n, device=device, generator=g).to(torch.float16).clamp_(max=0.9995)
+            o = torch.empty_like(x)
+            variant = 1 if name == "exp2" else 0
+            run = lambda: _lib.check("fpt_exp2_fraction", lib.fpt_exp2_fraction(o.data_ptr(), x.data_ptr(), n, variant, 16, stream))
+        elif name in ("sincos", "sincos_native"):
+            x = torch.rand(n, device=device, generator=g) * (2 * math.pi) - math.pi
+            o = torch.empty(2, n, dtype=torch.float16, device=device)
+            variant = 3 if name == "sincos" else 10
+            run = lambda: _lib.check("fpt_sincos", lib.fpt_sincos(o.data_ptr(), x.data_ptr(), n, variant, 16, stream))
+        else:
+            raise SystemExit(f"unknown profile case {case}")
     elif case == "sincos":
         x = torch.rand(n, device=device, generator=g) * (2 * math.pi) - math.pi
         o = torch.empty(2, n, dtype=torch.float16, device=device)
