@@ -150,7 +150,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     const int n_max = max(n_tiles[0], n_tiles[1]);
     volatile uint32_t* abort_flag = &sm.abort_flag;
 #ifdef FPT_ATTN_TRACE
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8);
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == (SPLIT ? 12 : 8));
     int trace_n = 0;
 #endif
 
@@ -248,12 +248,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             };
             // P V in two halves of four K steps: the first starts as soon as the probabilities of keys 0..63 are in
             // tensor memory, while the score-mod warps still work on keys 64..127.
+            // Where P sits: the one-warp-per-row layout packs all 128 keys into the first 64 score columns; in the
+            // column-split layout each half writes onto the first 32 columns of its OWN 64 score columns, so that neither
+            // half ever touches a column the other still has to read.
             auto issue_pv_half = [&](int s, int st, int half, bool first) {
-                const uint32_t va = st ? v_lo1 : v_lo0, d = tmem + 256u + uint32_t(s) * 128u, a = tmem + uint32_t(s) * 128u;
+                const uint32_t va = st ? v_lo1 : v_lo0, d = tmem + 256u + uint32_t(s) * 128u;
+                const uint32_t a = tmem + uint32_t(s) * 128u + uint32_t(half) * (SPLIT ? 64u : 32u);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                     const uint32_t kk = uint32_t(half) * 4u + uint32_t(k4);
-                    umma_ts_words(d, a + 8u * kk, va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                    umma_ts_words(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
                 }
                 if (half == 1) umma_commit(&sm.pv_done[s]);
             };
@@ -313,14 +317,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const int row = m0 + s * kTileM + row_in_tile;
         const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
         const uint32_t t_s = tmem + lane_base + uint32_t(s) * 128u + uint32_t(64 * half);
-        const uint32_t t_p = tmem + lane_base + uint32_t(s) * 128u + uint32_t(32 * half);
+        const uint32_t t_p = t_s;     // probabilities (bf16 pairs) go back onto the first 32 of this half's own score columns
         const uint32_t t_o = tmem + lane_base + 256u + uint32_t(s) * 128u + uint32_t(64 * half);
         const int n = n_tiles[s];
         const float softcap_in = p.scale / p.softcap, mul = p.softcap * kLog2e;
         float reference = 0.0f, sum_lo = 0.0f, sum_hi = 0.0f;
         bool ok = true;
-        // all eight warps of the slot have their S values in registers (P overwrites columns the other half reads);
-        // a bounded mbarrier wait, so that a warp that gave up after a timeout cannot strand the others
+        // The eight warps of the slot meet twice: after the first tile (row reference) and at the end (row sums).  A
+        // bounded mbarrier wait, so that a warp that gave up after a timeout cannot strand the others.
         auto slot_sync = [&](int phase) {
             tc_fence_before_sync();
             __syncwarp();
@@ -328,13 +332,16 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             return mbar_wait(&sm.ld_done[s], uint32_t(phase) & 1u, abort_flag, p.status, kWhereSFull);
         };
         for (int j = 0; j < n && ok; ++j) {
+            FPT_TRACE(s, 1);                         // start waiting for S
             ok = mbar_wait(&sm.s_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWhereSFull);
             if (!ok) break;
             tc_fence_after_sync();
+            FPT_TRACE(s, 2);                         // S ready
             uint32_t sr[64];
             tmem_ld_32x32b_x32(t_s, reinterpret_cast<uint32_t(&)[32]>(sr[0]));
             tmem_ld_32x32b_x32(t_s + 32, reinterpret_cast<uint32_t(&)[32]>(sr[32]));
             tmem_ld_wait();
+            FPT_TRACE(s, 5);                         // S in registers
             const bool diagonal = (p.causal && j == n - 1) || (j == total_tiles - 1 && (p.seq % kTileN) != 0);
             const int limit = min(p.causal ? row : 0x7fffffff, p.seq - 1);
             const int col0 = j * kTileN + 64 * half;
@@ -350,40 +357,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         if (col0 + 2 * w + 1 > limit) pw[w] &= 0x0000ffffu;
                     }
                 }
-                ok = slot_sync(j);
-                if (!ok) break;
             } else {
                 // soft-capped scores live in [-cap, cap], so one reference per row serves every tile: the row maximum of
                 // the first tile, but not below cap*log2(e) - 96.  Exponents then stay within [-196, 96] (cap*log2(e)
                 // <= 98): no overflow, and what underflows is at least 2^-126 below an entry of the same row.  No
                 // maximum scan after the first tile and no rescaling of O at all.
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in), p.tanh);
-                    sr[2 * i] = t << 16;
-                    sr[2 * i + 1] = t & 0xffff0000u;
-                }
-                if (diagonal) {
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
-                }
-                if (j == 0) {
-                    float m3 = __uint_as_float(sr[0]);
-#pragma unroll
-                    for (int i = 1; i + 1 < 64; i += 2) m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-                    m3 = fmaxf(m3, __uint_as_float(sr[63]));
-                    sm.xchg[s][half][row_in_tile] = m3;
-                }
-                ok = slot_sync(j);
-                if (!ok) break;
-                if (j == 0)
-                    reference = fmaxf(fmaxf(sm.xchg[s][0][row_in_tile], sm.xchg[s][1][row_in_tile]) * mul, mul - kFixedReferenceSpan);
-                const float neg_ref = -reference;
-#pragma unroll
-                for (int w = 0; w < 32; ++w) {
+                auto exponentials = [&](int w, float t0, float t1, float neg_ref) {
                     float a0, a1, e0, e1;
-                    fma_f32x2(__uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), mul, neg_ref, a0, a1);
+                    fma_f32x2(t0, t1, mul, neg_ref, a0, a1);
                     if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
                         exp2_full_x2<EK>(a0, a1, e0, e1);
                     } else {
@@ -392,19 +373,57 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                     add_f32x2(sum_lo, sum_hi, e0, e1);
                     pw[w] = Sfu<kBf16>::pack(e0, e1);
+                };
+                if (j > 0 && !diagonal) {
+                    // The common tile: tanh polynomial (ALU and FMA pipes) and exponential (special-function unit) of
+                    // one pair of keys back to back, so that the two bounds overlap instead of adding up.
+#pragma unroll
+                    for (int w = 0; w < 32; ++w) {
+                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
+                        exponentials(w, __uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u), -reference);
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in), p.tanh);
+                        sr[2 * i] = t << 16;
+                        sr[2 * i + 1] = t & 0xffff0000u;
+                    }
+                    if (diagonal) {
+#pragma unroll
+                        for (int i = 0; i < 64; ++i)
+                            if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
+                    }
+                    FPT_TRACE(s, 6);                     // tanh done
+                    if (j == 0) {
+                        float m3 = __uint_as_float(sr[0]);
+#pragma unroll
+                        for (int i = 1; i + 1 < 64; i += 2) m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
+                        m3 = fmaxf(m3, __uint_as_float(sr[63]));
+                        sm.xchg[s][half][row_in_tile] = m3;
+                        ok = slot_sync(0);
+                        if (!ok) break;
+                        reference = fmaxf(fmaxf(sm.xchg[s][0][row_in_tile], sm.xchg[s][1][row_in_tile]) * mul, mul - kFixedReferenceSpan);
+                    }
+                    FPT_TRACE(s, 7);
+#pragma unroll
+                    for (int w = 0; w < 32; ++w)
+                        exponentials(w, __uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), -reference);
                 }
             }
+            FPT_TRACE(s, 3);                         // probabilities computed
             tmem_st_32x32b_x32(t_p, pw);
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
+            FPT_TRACE(s, 4);                         // P handed over
         }
         if (ok && n > 0) {
             float inv = 1.0f, total = 1.0f;
             if constexpr (MODE != 1) {       // the two column halves add their sums
                 sm.xchg[s][half][row_in_tile] = sum_lo + sum_hi;
-                ok = slot_sync(n);
+                ok = slot_sync(1);
                 total = sm.xchg[s][0][row_in_tile] + sm.xchg[s][1][row_in_tile];
                 inv = 1.0f / total;
             }
@@ -671,10 +690,13 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
         return cuda_status(cudaGetLastError());
     };
     // The column-split variant pays where the score-mod is instruction-heavy and needs no per-tile row reduction: the
-    // soft-capped mode while cap * log2(e) stays within the range its fixed exponent reference covers (measured +5..10 %).
-    // The sigmoid mode also qualifies but measured 12 % slower with it at S = 16384, so it keeps one thread per row.
-    const bool split = mode == FPT_ATTN_SOFTCAP_TANH && softcap * kLog2e <= kFixedReferenceLimit && fpt::tuning_attention_split();
-    if (mode == FPT_ATTN_SIGMOID_DIRECT) return launch(attention_fwd_kernel<1, 0, false>, kThreads);
+    // soft-capped mode while cap * log2(e) stays within the range its fixed exponent reference covers (measured +15..28 %
+    // since its tanh and exponential run back to back per key pair).  The sigmoid mode also qualifies but measures no
+    // faster with it (0.98..1.0x), so it keeps one thread per row unless the tuning key asks for the split layout.
+    const int split_tuning = fpt::tuning_attention_split();
+    const bool split = mode == FPT_ATTN_SOFTCAP_TANH && softcap * kLog2e <= kFixedReferenceLimit && split_tuning >= 1;
+    if (mode == FPT_ATTN_SIGMOID_DIRECT)
+        return split_tuning >= 2 ? launch(attention_fwd_kernel<1, 0, true>, kThreadsSplit) : launch(attention_fwd_kernel<1, 0, false>, kThreads);
     const bool softcap_mode = mode == FPT_ATTN_SOFTCAP_TANH;
     if (softcap_mode && split) {
         switch (exp2_emu_freq) {

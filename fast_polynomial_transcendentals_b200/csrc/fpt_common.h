@@ -24,7 +24,7 @@ struct Tuning {
 
 int current_device_info(DeviceInfo* out);
 Tuning tuning();
-bool tuning_attention_split();   // attention forward: column-split score-mod warps where the mode allows (default on)
+int tuning_attention_split();    // attention forward, column-split score-mod warps: 0 never, 1 soft-capped mode (default), 2 sigmoid mode too
 
 inline int cuda_status(cudaError_t e) { return e == cudaSuccess ? FPT_OK : int(e); }
 

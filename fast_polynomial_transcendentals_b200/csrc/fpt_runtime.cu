@@ -60,7 +60,7 @@ int current_device_info(DeviceInfo* out) {
 }
 
 Tuning tuning() { return Tuning{g_blocks_per_sm.load(), g_streaming.load()}; }
-bool tuning_attention_split() { return g_attention_split.load() != 0; }
+int tuning_attention_split() { return g_attention_split.load(); }
 
 const ProgramRow* program_table(int* count) {
     if (count) *count = k_row_count;
@@ -141,7 +141,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!key) return FPT_ERR_NULL_POINTER;
     if (!std::strcmp(key, "blocks_per_sm")) { if (value < 0 || value > 64) return FPT_ERR_BAD_SIZE; fpt::g_blocks_per_sm = value; return FPT_OK; }
     if (!std::strcmp(key, "streaming")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_streaming = value; return FPT_OK; }
-    if (!std::strcmp(key, "attention_split")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_split = value; return FPT_OK; }
+    if (!std::strcmp(key, "attention_split")) { if (value < 0 || value > 2) return FPT_ERR_BAD_SIZE; fpt::g_attention_split = value; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
 

@@ -295,7 +295,8 @@ int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* sta
 /* ---- launch knobs for benchmarks (process-wide; defaults are the measured-best values) -------- */
 /* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1;
  * key "attention_split": 1 (default) lets the attention forward use its column-split score-mod warps where the mode
- * allows (soft-cap with cap*log2(e) <= 98), 0 forces the one-thread-per-row layout. */
+ * allows (soft-cap with cap*log2(e) <= 98), 0 forces the one-thread-per-row layout, 2 uses the column-split layout for
+ * the sigmoid mode as well (measured no faster; kept for comparison runs). */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 
