@@ -141,49 +141,68 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return Sfu<k
 template <int MODE>
 __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s1, float d0, float d1, float l0, float l1,
                                            float t0, float t1, bool m0, bool m1, uint32_t& p_word, uint32_t& ds_word) {
+    // fp32 steps run two lanes per instruction (mul2 / sub2 / fma2): these loops are bound by issue slots
     if constexpr (MODE == 1) {
-        const uint32_t x = pack_bf16(s0 * p.scale, s1 * p.scale);
+        float x0, x1;
+        mul2(s0, s1, p.scale, p.scale, x0, x1);
         uint32_t grad;
-        uint32_t pr = b3_direct_with_grad(x, p.b3, grad);
-        float g0 = Sfu<kBf16>::lo(grad) * d0, g1 = Sfu<kBf16>::hi(grad) * d1;
+        uint32_t pr = b3_direct_with_grad(pack_bf16(x0, x1), p.b3, grad);
+        float g0, g1;
+        unpack_bf16x2(grad, g0, g1);
+        mul2(g0, g1, d0, d1, g0, g1);
         if (m0) { pr &= 0xffff0000u; g0 = 0.0f; }
         if (m1) { pr &= 0x0000ffffu; g1 = 0.0f; }
         p_word = pr;
         ds_word = pack_bf16(g0, g1);
     } else if constexpr (MODE == 2) {
         const float c = p.scale * kLog2eB;
-        float p0 = ex2f(fmaf(s0, c, -l0)), p1 = ex2f(fmaf(s1, c, -l1));
+        float a0, a1, e0, e1;
+        fma2(s0, s1, c, c, -l0, -l1, a0, a1);
+        float p0 = ex2f(a0), p1 = ex2f(a1);
         if (m0) p0 = 0.0f;
         if (m1) p1 = 0.0f;
         p_word = pack_bf16(p0, p1);
-        ds_word = pack_bf16(p0 * (d0 - t0), p1 * (d1 - t1));
+        sub2(d0, d1, t0, t1, e0, e1);
+        mul2(p0, p1, e0, e1, e0, e1);
+        ds_word = pack_bf16(e0, e1);
     } else {
         const float in = p.scale / p.softcap, out = p.softcap * kLog2eB;
-        const uint32_t x = pack_bf16(s0 * in, s1 * in);
-        const uint32_t th = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
-        const float th0 = Sfu<kBf16>::lo(th), th1 = Sfu<kBf16>::hi(th);
-        float p0 = ex2f(fmaf(th0, out, -l0)), p1 = ex2f(fmaf(th1, out, -l1));
+        float x0, x1;
+        mul2(s0, s1, in, in, x0, x1);
+        const uint32_t x = pack_bf16(x0, x1);
+        // The saturating odd program written out (the same operations in the same order as eval_program<kBf16, kOddSat,
+        // 4>), because its clamped argument c and its unsigned result also feed the derivative below.
+        using P = Pk<kBf16>;
+        const uint32_t c = P::min_abs(x, p.tanh.clamp);
+        uint32_t h = P::fma(c, p.tanh.c[3], p.tanh.c[2]);
+        h = P::fma(c, h, p.tanh.c[1]);
+        h = P::fma(c, h, p.tanh.c[0]);
+        const uint32_t sat = P::min(P::mul(c, h), Consts<kBf16>::one);
+        const uint32_t th = sat ^ (x & kSignMask);
+        float th0, th1, a0, a1;
+        unpack_bf16x2(th, th0, th1);
+        fma2(th0, th1, out, out, -l0, -l1, a0, a1);
+        float p0 = ex2f(a0), p1 = ex2f(a1);
         if (m0) p0 = 0.0f;
         if (m1) p1 = 0.0f;
         float g0, g1;
         if (p.softcap_grad == 1) {
-            g0 = fmaf(-th0, th0, 1.0f);
-            g1 = fmaf(-th1, th1, 1.0f);
+            fma2(-th0, -th1, th0, th1, 1.0f, 1.0f, g0, g1);
         } else {
             // derivative of the polynomial on packed bf16 lanes, like the polynomial itself: three fused
             // multiply-adds per pair; zero where the input is clamped or the output saturated (flat regions)
-            using P = Pk<kBf16>;
-            const uint32_t ax = x & ~kSignMask;
-            const uint32_t c = P::min(ax, p.tanh.clamp);
             uint32_t gw = P::fma(c, p.tanh_dw[3], p.tanh_dw[2]);
             gw = P::fma(c, gw, p.tanh_dw[1]);
             gw = P::fma(c, gw, p.tanh_dw[0]);
-            gw &= ~(P::ge_mask(ax, p.tanh.clamp) | P::ge_mask(th & ~kSignMask, Consts<kBf16>::one));
-            g0 = Sfu<kBf16>::lo(gw);
-            g1 = Sfu<kBf16>::hi(gw);
+            gw &= ~(P::ge_mask(c, p.tanh.clamp) | P::ge_mask(sat, Consts<kBf16>::one));
+            unpack_bf16x2(gw, g0, g1);
         }
         p_word = pack_bf16(p0, p1);
-        ds_word = pack_bf16(p0 * (d0 - t0) * g0, p1 * (d1 - t1) * g1);
+        float e0, e1;
+        sub2(d0, d1, t0, t1, e0, e1);
+        mul2(p0, p1, e0, e1, e0, e1);
+        mul2(e0, e1, g0, g1, e0, e1);
+        ds_word = pack_bf16(e0, e1);
     }
 }
 

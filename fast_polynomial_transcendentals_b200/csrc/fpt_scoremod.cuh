@@ -192,4 +192,29 @@ __device__ __forceinline__ void exp2_full_x2(float a0, float a1, float& e0, floa
     e1 = __uint_as_float(p1 + (x1 << 23));
 }
 
+// ---- two fp32 lanes per instruction (add / sub / mul / fma .f32x2): one issue slot for a pair of keys ------------
+// (o0, o1) = (a0, a1) * (b0, b1)
+__device__ __forceinline__ void mul2(float a0, float a1, float b0, float b1, float& o0, float& o1) {
+    asm("{\n\t.reg .b64 a, b, r;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t"
+        "mul.rn.f32x2 r, a, b;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(o0), "=f"(o1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// (o0, o1) = (a0, a1) - (b0, b1)
+__device__ __forceinline__ void sub2(float a0, float a1, float b0, float b1, float& o0, float& o1) {
+    asm("{\n\t.reg .b64 a, b, r;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\t"
+        "sub.rn.f32x2 r, a, b;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(o0), "=f"(o1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1));
+}
+// (o0, o1) = (a0, a1) * (b0, b1) + (c0, c1)
+__device__ __forceinline__ void fma2(float a0, float a1, float b0, float b1, float c0, float c1, float& o0, float& o1) {
+    asm("{\n\t.reg .b64 a, b, c, r;\n\tmov.b64 a, {%2, %3};\n\tmov.b64 b, {%4, %5};\n\tmov.b64 c, {%6, %7};\n\t"
+        "fma.rn.f32x2 r, a, b, c;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(o0), "=f"(o1) : "f"(a0), "f"(a1), "f"(b0), "f"(b1), "f"(c0), "f"(c1));
+}
+// the two bf16 lanes of a word as fp32 (a shift and a mask)
+__device__ __forceinline__ void unpack_bf16x2(uint32_t w, float& lo, float& hi) {
+    lo = __uint_as_float(w << 16);
+    hi = __uint_as_float(w & 0xffff0000u);
+}
+
 }  // namespace fpt
