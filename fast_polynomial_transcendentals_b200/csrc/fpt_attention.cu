@@ -56,6 +56,7 @@ struct AttnParams {
     int64_t out_stride_b, out_stride_s, out_stride_h;
     int batch, seq, q_heads, kv_heads;
     int mode, causal;
+    int rows_fastest;    // grid = (row blocks, heads, batch) instead of (heads, row blocks, batch)
     float scale, softcap;
     uint32_t* status;
     ProgramWords tanh;   // bf16 TANH_FWD_D4
@@ -134,9 +135,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
     extern __shared__ uint8_t smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int hq = blockIdx.x;
-    const int n_qblocks = gridDim.y;
-    const int qblock = p.causal ? n_qblocks - 1 - int(blockIdx.y) : int(blockIdx.y);  // heavy causal blocks first
+    // Blocks are handed out x fastest.  With heads on x the blocks that run together share their length (causal) but walk
+    // the K/V of every head at once; with row blocks on x they share one head's K/V, which then stays in L2.
+    const int hq = p.rows_fastest ? blockIdx.y : blockIdx.x;
+    const int n_qblocks = p.rows_fastest ? gridDim.x : gridDim.y;
+    const int qb = p.rows_fastest ? blockIdx.x : blockIdx.y;
+    const int qblock = p.causal ? n_qblocks - 1 - qb : qb;  // heavy causal blocks first
     const int b = blockIdx.z;
     const int hk = hq / (p.q_heads / p.kv_heads);
     const int m0 = qblock * (kSlots * kTileM);
@@ -682,7 +686,12 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     const size_t smem = sizeof(AttnSmem) + 1024;
     static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory budget");
     const int n_qblocks = int((seq + kSlots * kTileM - 1) / (kSlots * kTileM));
-    const dim3 grid{unsigned(q_heads), unsigned(n_qblocks), unsigned(batch)};
+    // Measured: the forward is not bound by K/V traffic in either order (B=2, S=16384, 32 heads: within 1 %), and with a
+    // causal mask heads fastest wins by 3-20 % (blocks that run together have the same length), so that is the default.
+    const int raster = fpt::tuning_attention_raster();
+    p.rows_fastest = raster >= 0 ? raster : 0;
+    const dim3 grid = p.rows_fastest ? dim3{unsigned(n_qblocks), unsigned(q_heads), unsigned(batch)}
+                                     : dim3{unsigned(q_heads), unsigned(n_qblocks), unsigned(batch)};
     auto launch = [&](auto kernel, int threads) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);

@@ -44,6 +44,12 @@ struct Pk;
             asm("fma.rn." SUF " %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));               \
             return d;                                                                               \
         }                                                                                           \
+        /* max(a * b + c, +0) in the multiply-add itself */                                          \
+        static __device__ __forceinline__ uint32_t fma_relu(uint32_t a, uint32_t b, uint32_t c) {   \
+            uint32_t d;                                                                             \
+            asm("fma.rn.relu." SUF " %0, %1, %2, %3;" : "=r"(d) : "r"(a), "r"(b), "r"(c));          \
+            return d;                                                                               \
+        }                                                                                           \
         static __device__ __forceinline__ uint32_t mul(uint32_t a, uint32_t b) {                    \
             uint32_t d;                                                                             \
             asm("mul.rn." SUF " %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));                           \

@@ -65,9 +65,11 @@ __device__ __forceinline__ uint32_t b3_direct_select_late(uint32_t x, const B3Wo
     uint32_t hi = P::fma(c, k.hi[3], k.hi[2]);
     lo = P::fma(c, lo, k.lo[1]);
     hi = P::fma(c, hi, k.hi[1]);
-    lo = P::fma(c, lo, k.lo[0]);
-    hi = P::fma(c, hi, k.hi[0]);
-    return P::max(select_bits(mask, hi, lo), 0u);
+    // The floor at +0 rides on the last multiply-add of each row (max(select(hi, lo), 0) = select(max(hi, 0), max(lo, 0));
+    // neither row can end in -0, its last addend being a non-zero constant), which saves the separate maximum.
+    lo = P::fma_relu(c, lo, k.lo[0]);
+    hi = P::fma_relu(c, hi, k.hi[0]);
+    return select_bits(mask, hi, lo);
 }
 
 // value and value * (intercept + slope * clamp(x)), the coupled derivative of the deployed pair

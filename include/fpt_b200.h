@@ -296,7 +296,9 @@ int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* sta
 /* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1;
  * key "attention_split": 1 (default) lets the attention forward use its column-split score-mod warps where the mode
  * allows (soft-cap with cap*log2(e) <= 98), 0 forces the one-thread-per-row layout, 2 uses the column-split layout for
- * the sigmoid mode as well (measured no faster; kept for comparison runs). */
+ * the sigmoid mode as well (measured no faster; kept for comparison runs);
+ * key "attention_raster": order in which attention blocks are handed out: 0 heads fastest, 1 row blocks of one head
+ * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large). */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 

@@ -143,3 +143,34 @@ def test_backward_rejects_bad_arguments(fpt, cuda):
     assert call(out=None) < 0                            # soft-max modes need the forward output
     assert call(mode=1, out=None, workspace_bytes=0) == 0   # the sigmoid mode needs neither out, lse nor workspace
     torch.cuda.synchronize()
+
+
+@pytest.mark.parametrize("mode,causal", [(2, True), (1, False), (0, True)])
+def test_block_order_does_not_change_a_bit(fpt, cuda, mode, causal):
+    """The two hand-out orders of the blocks (tuning key "attention_raster") run the same per-block work: forward and
+    backward results are identical bit for bit; the sigmoid-mode column-split layout (attention_split 2) likewise."""
+    import torch
+    B, S, Hq, Hk, D = 2, 600, 4, 2, 128           # ragged: 600 is not a multiple of the tile
+    g = torch.Generator(device=cuda)
+    g.manual_seed(31)
+    mk = lambda h: torch.randn(B, S, h, D, device=cuda, generator=g).to(torch.bfloat16)
+    q, k, v, dout = mk(Hq), mk(Hk), mk(Hk), mk(Hq)
+    scale = 1.0 / math.sqrt(D)
+    lib = fpt.load()
+    results = []
+    try:
+        for raster, split in ((0, 1), (1, 1), (-1, 2)):
+            assert lib.fpt_set_tuning(b"attention_raster", raster) == 0
+            assert lib.fpt_set_tuning(b"attention_split", split) == 0
+            out, lse = forward(fpt, cuda, q, k, v, mode, causal, scale, 30.0, 10)
+            dq, dk, dv = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, 30.0, 10)
+            results.append((out, dq, dk, dv) + (() if mode == 1 else (lse,)))
+    finally:
+        assert lib.fpt_set_tuning(b"attention_raster", -1) == 0
+        assert lib.fpt_set_tuning(b"attention_split", 1) == 0
+    for other in results[1:]:
+        for a, b in zip(results[0], other):
+            assert torch.equal(a, b)
+    value = ctypes.c_int(7)
+    assert lib.fpt_get_tuning(b"attention_raster", ctypes.byref(value)) == 0 and value.value == -1
+    assert lib.fpt_set_tuning(b"attention_raster", 2) != 0
