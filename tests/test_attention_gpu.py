@@ -71,6 +71,10 @@ CASES = [
     (1, 77, 1, 1, 1, False, 0.0, 12),
     (1, 257, 2, 2, 1, True, 0.0, 12),
     (1, 130, 2, 1, 2, False, 0.0, 12),
+    # a single position, and one key more than two tiles
+    (1, 1, 2, 1, 2, True, 0.0, 12),
+    (1, 1, 1, 1, 0, False, 50.0, 12),
+    (1, 257, 4, 1, 0, True, 50.0, 12),
 ]
 
 
