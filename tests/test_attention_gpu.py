@@ -169,6 +169,59 @@ def test_routed_exp2_stays_within_tolerance(fpt, cuda, oracle, freq, mode, causa
         assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
 
 
+FULL_SIZE = [
+    # the two attention workloads of the benchmark, at their full sizes: (B, S, Hq, Hk, mode, causal, softcap, log2_n)
+    ("causal GQA, soft-cap 50", 4, 8192, 32, 8, 0, True, 50.0, 12),
+    ("sigmoid, bidirectional", 2, 16384, 32, 32, 1, False, 0.0, 14),
+]
+
+
+@pytest.mark.parametrize("case", FULL_SIZE, ids=[c[0] for c in FULL_SIZE])
+def test_full_size_workloads_by_sampled_rows_and_properties(fpt, cuda, oracle, case):
+    """At the benchmark's sizes the oracle cannot redo everything, but a row of attention costs it only S x D: sampled
+    rows of sampled heads against the fp32 oracle (2e-2), plus two properties that need no oracle.  Causal: rows before
+    position p do not change by a bit when keys and values from p on are replaced.  Both modes: the output is linear in
+    V, so O(V) + O(V') agrees with O(V + V') up to the bf16 roundings of the three outputs."""
+    import torch
+    _, B, S, Hq, Hk, mode, causal, softcap, log2_n = case
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(4242)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse, status = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    assert status == 0 and not torch.isnan(out.float()).any()
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    rng = np.random.default_rng(11)
+    worst = 0.0
+    for b, h in ((0, 0), (B - 1, Hq - 1), (B // 2, Hq // 2 + 1)):
+        rows = np.sort(np.concatenate([[0, 1, 127, 128, S - 129, S - 1], rng.choice(S, size=10, replace=False)]))
+        want = oracle.attention_rows(qb, kb, vb, b, h, rows, mode, causal, scale, softcap, log2_n)
+        got = out[b, rows, h, :].float().cpu().numpy()
+        worst = max(worst, float(np.abs(got - want).max()))
+    assert worst <= 2e-2, worst
+    if causal:
+        cut = S // 2 + 37
+        k2, v2 = k.clone(), v.clone()
+        k2[:, cut:] = torch.randn(B, S - cut, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+        v2[:, cut:] = torch.randn(B, S - cut, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+        out2, lse2, status2 = run_attention(fpt, cuda, q, k2, v2, mode, causal, scale, softcap, log2_n)
+        assert status2 == 0
+        assert torch.equal(out[:, :cut], out2[:, :cut]) and torch.equal(lse[:, :, :cut], lse2[:, :, :cut])
+        assert not torch.equal(out[:, cut:], out2[:, cut:])
+        del k2, v2, out2, lse2
+    v_other = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v_sum = (v.float() + v_other.float()).to(torch.bfloat16)
+    out_other, _, st1 = run_attention(fpt, cuda, q, k, v_other, mode, causal, scale, softcap, log2_n)
+    out_sum, _, st2 = run_attention(fpt, cuda, q, k, v_sum, mode, causal, scale, softcap, log2_n)
+    assert st1 == 0 and st2 == 0
+    # the sum of V itself is rounded to bf16 (relative 2^-9 per element) before it is averaged by the probabilities
+    residual = (out.float() + out_other.float() - out_sum.float()).abs().max()
+    assert float(residual) < 3e-2 * max(1.0, float(out_sum.float().abs().max())), float(residual)
+
+
 @pytest.mark.parametrize("freq", [8, 32])
 def test_routed_two_piece_exponential(fpt, cuda, oracle, freq):
     """Backend "pwl2" (2 % exponential) on a share of the lanes: outputs stay within a bound that scales with the share."""
