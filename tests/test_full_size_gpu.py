@@ -109,3 +109,28 @@ def test_swiglu_full_size_layouts_agree_and_samples_match(fpt, cuda, oracle, row
     bits_of = lambda t: t.reshape(-1)[idx].view(torch.int16).cpu().numpy().view(np.uint16)
     want = oracle.swiglu(oracle.find_program("SWISH_FWD_D3", 1, 0), bits_of(gate), bits_of(up))
     assert_bits_equal(bits_of(flat), want, "SwiGLU at sampled positions")
+
+
+def test_rope_prologue_at_the_sigmoid_attention_size(fpt, cuda, oracle):
+    """B=2, S=16384, 32 heads, D=128, theta = 500000, bf16 in and out: the whole tensor against the oracle (its phase
+    arithmetic is integer, so position 16383 is as exact as position 0)."""
+    import torch
+    B, S, H, D = 2, 16384, 32, 128
+    freqs = 500000.0 ** (-np.arange(0, D, 2, dtype=np.float64) / D)
+    inc = np.round(freqs / (2 * math.pi) * 2.0 ** 32).astype(np.uint64).astype(np.uint32)
+    incd = torch.from_numpy(inc.view(np.int32)).to(cuda)
+    g = torch.Generator(device=cuda)
+    g.manual_seed(34)
+    q = torch.randn(B, S, H, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, H, D, device=cuda, generator=g).to(torch.bfloat16)
+    qo = torch.empty(B, H, S, D, dtype=q.dtype, device=cuda)
+    ko = torch.empty_like(qo)
+    fpt.call("fpt_rope_apply", qo.data_ptr(), ko.data_ptr(), q.data_ptr(), k.data_ptr(), incd.data_ptr(), B, S, H, H, D, 0, 1,
+             stream())
+    torch.cuda.synchronize()
+    bits = lambda t: t.view(torch.int16).cpu().numpy().view(np.uint16)
+    import os
+    oracle.set_threads(os.cpu_count() or 1)
+    want_q, want_k = oracle.rope_apply(bits(q), bits(k), inc, io_bf16=True)
+    assert np.array_equal(bits(qo), want_q)
+    assert np.array_equal(bits(ko), want_k)
