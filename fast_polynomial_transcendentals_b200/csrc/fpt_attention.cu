@@ -325,10 +325,11 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         const uint32_t t_o = tmem + lane_base + 256u + uint32_t(s) * 128u + uint32_t(64 * half);
         const int n = n_tiles[s];
         const float softcap_in = p.scale / p.softcap, mul = p.softcap * kLog2e;
-        float reference = 0.0f, sum_lo = 0.0f, sum_hi = 0.0f;
+        const float reference = fmaxf(mul - kFixedReferenceSpan, -mul);   // small caps: exponents in [0, 2 cap*log2(e)]
+        float sum_lo = 0.0f, sum_hi = 0.0f;
         bool ok = true;
-        // The eight warps of the slot meet twice: after the first tile (row reference) and at the end (row sums).  A
-        // bounded mbarrier wait, so that a warp that gave up after a timeout cannot strand the others.
+        // The eight warps of the slot meet once, at the end (the two column halves add their row sums).  A bounded
+        // mbarrier wait, so that a warp that gave up after a timeout cannot strand the others.
         auto slot_sync = [&](int phase) {
             tc_fence_before_sync();
             __syncwarp();
@@ -362,13 +363,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                 }
             } else {
-                // soft-capped scores live in [-cap, cap], so one reference per row serves every tile: the row maximum of
-                // the first tile, but not below cap*log2(e) - 96.  Exponents then stay within [-196, 96] (cap*log2(e)
-                // <= 98): no overflow, and what underflows is at least 2^-126 below an entry of the same row.  No
-                // maximum scan after the first tile and no rescaling of O at all.
-                auto exponentials = [&](int w, float t0, float t1, float neg_ref) {
+                // Soft-capped scores live in [-cap, cap], so ONE exponent reference serves every row and every tile:
+                // cap*log2(e) - 96 (or -cap*log2(e) when that is larger, which keeps small caps near 2^0).  Exponents then
+                // stay within [96 - 2 cap*log2(e), 96], i.e. [-100, 96] while
+                // cap*log2(e) <= 98: nothing overflows (a row sum stays below 2^96 times the sequence length) and nothing
+                // underflows.  No maximum scan, no rescaling of O, and the two column halves of a row never have to agree
+                // on anything before the end.
+                auto exponentials = [&](int w, float t0, float t1) {
                     float a0, a1, e0, e1;
-                    fma_f32x2(t0, t1, mul, neg_ref, a0, a1);
+                    fma_f32x2(t0, t1, mul, -reference, a0, a1);
                     if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
                         exp2_full_x2<EK>(a0, a1, e0, e1);
                     } else {
@@ -378,41 +381,29 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     add_f32x2(sum_lo, sum_hi, e0, e1);
                     pw[w] = Sfu<kBf16>::pack(e0, e1);
                 };
-                if (j > 0 && !diagonal) {
+                if (!diagonal) {
                     // The common tile: tanh polynomial (ALU and FMA pipes) and exponential (special-function unit) of
                     // one pair of keys back to back, so that the two bounds overlap instead of adding up.
 #pragma unroll
                     for (int w = 0; w < 32; ++w) {
                         const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
-                        exponentials(w, __uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u), -reference);
+                        exponentials(w, __uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u));
                     }
                 } else {
+                    // a tile with masked keys: their tanh values become -inf before the exponentials
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in), p.tanh);
                         sr[2 * i] = t << 16;
                         sr[2 * i + 1] = t & 0xffff0000u;
                     }
-                    if (diagonal) {
 #pragma unroll
-                        for (int i = 0; i < 64; ++i)
-                            if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
-                    }
+                    for (int i = 0; i < 64; ++i)
+                        if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
                     FPT_TRACE(s, 6);                     // tanh done
-                    if (j == 0) {
-                        float m3 = __uint_as_float(sr[0]);
-#pragma unroll
-                        for (int i = 1; i + 1 < 64; i += 2) m3 = max3(m3, __uint_as_float(sr[i]), __uint_as_float(sr[i + 1]));
-                        m3 = fmaxf(m3, __uint_as_float(sr[63]));
-                        sm.xchg[s][half][row_in_tile] = m3;
-                        ok = slot_sync(0);
-                        if (!ok) break;
-                        reference = fmaxf(fmaxf(sm.xchg[s][0][row_in_tile], sm.xchg[s][1][row_in_tile]) * mul, mul - kFixedReferenceSpan);
-                    }
-                    FPT_TRACE(s, 7);
 #pragma unroll
                     for (int w = 0; w < 32; ++w)
-                        exponentials(w, __uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), -reference);
+                        exponentials(w, __uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]));
                 }
             }
             FPT_TRACE(s, 3);                         // probabilities computed
@@ -427,7 +418,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             float inv = 1.0f, total = 1.0f;
             if constexpr (MODE != 1) {       // the two column halves add their sums
                 sm.xchg[s][half][row_in_tile] = sum_lo + sum_hi;
-                ok = slot_sync(1);
+                ok = slot_sync(0);
                 total = sm.xchg[s][0][row_in_tile] + sm.xchg[s][1][row_in_tile];
                 inv = 1.0f / total;
             }

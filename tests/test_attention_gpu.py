@@ -160,7 +160,8 @@ def test_routed_exp2_stays_within_tolerance(fpt, cuda, oracle, freq, mode, causa
     base, lse0, st0 = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, 12, exp2_emu_freq=0)
     out, lse, st = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, 12, exp2_emu_freq=freq)
     assert st0 == 0 and st == 0
-    assert float((out.float() - base.float()).abs().max()) < 8e-3
+    # the two differ by a rounding flip of the bf16 output at most: one unit in the last place of the value
+    assert bool(((out.float() - base.float()).abs() <= 0.0079 * base.float().abs().clamp(min=1.0)).all())
     assert float((lse - lse0).abs().max()) < 1e-3
     qb, kb, vb = bits(q), bits(k), bits(v)
     rows = np.arange(S)
