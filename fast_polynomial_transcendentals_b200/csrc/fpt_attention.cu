@@ -16,6 +16,8 @@
 //   mode 1  sigmoid attention:   p = direct piecewise cubic of bf16(s*scale) (B3), no normalisation, O = P V
 //   mode 2  plain softmax
 // Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
+#include <type_traits>
+
 #include "fpt_common.h"
 #include "fpt_programs.h"
 #include "fpt_scoremod.cuh"
@@ -369,41 +371,31 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 // cap*log2(e) <= 98: nothing overflows (a row sum stays below 2^96 times the sequence length) and nothing
                 // underflows.  No maximum scan, no rescaling of O, and the two column halves of a row never have to agree
                 // on anything before the end.
-                auto exponentials = [&](int w, float t0, float t1) {
+                // One pair of keys: tanh polynomial (ALU and FMA pipes), then the exponential (special-function unit), back
+                // to back, so that the two bounds overlap instead of adding up.
+                auto key_pair = [&](int w, auto masked) {
+                    const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
                     float a0, a1, e0, e1;
-                    fma_f32x2(t0, t1, mul, -reference, a0, a1);
+                    fma_f32x2(__uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u), mul, -reference, a0, a1);
                     if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
                         exp2_full_x2<EK>(a0, a1, e0, e1);
                     } else {
                         e0 = ex2(a0);
                         e1 = ex2(a1);
                     }
+                    if constexpr (decltype(masked)::value) {   // keys beyond the diagonal or the end of the sequence
+                        if (col0 + 2 * w > limit) e0 = 0.0f;
+                        if (col0 + 2 * w + 1 > limit) e1 = 0.0f;
+                    }
                     add_f32x2(sum_lo, sum_hi, e0, e1);
                     pw[w] = Sfu<kBf16>::pack(e0, e1);
                 };
                 if (!diagonal) {
-                    // The common tile: tanh polynomial (ALU and FMA pipes) and exponential (special-function unit) of
-                    // one pair of keys back to back, so that the two bounds overlap instead of adding up.
 #pragma unroll
-                    for (int w = 0; w < 32; ++w) {
-                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
-                        exponentials(w, __uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u));
-                    }
-                } else {
-                    // a tile with masked keys: their tanh values become -inf before the exponentials
+                    for (int w = 0; w < 32; ++w) key_pair(w, std::false_type{});
+                } else {       // a branch the whole slot takes together, so that the other tiles carry no compare / select
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], softcap_in), p.tanh);
-                        sr[2 * i] = t << 16;
-                        sr[2 * i + 1] = t & 0xffff0000u;
-                    }
-#pragma unroll
-                    for (int i = 0; i < 64; ++i)
-                        if (col0 + i > limit) sr[i] = 0xff800000u;  // -inf
-                    FPT_TRACE(s, 6);                     // tanh done
-#pragma unroll
-                    for (int w = 0; w < 32; ++w)
-                        exponentials(w, __uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]));
+                    for (int w = 0; w < 32; ++w) key_pair(w, std::true_type{});
                 }
             }
             FPT_TRACE(s, 3);                         // probabilities computed
