@@ -83,6 +83,26 @@ __device__ __forceinline__ uint32_t b3_direct_with_grad(uint32_t x, const B3Word
     return v;
 }
 
+// The pair (value, coupled derivative) with the late select of b3_direct_select_late: both rows' cubics and both rows'
+// derivative factors on the FMA pipe, one select each, no lower clamp (below -6 the value is +0 and so is its product with
+// the finite factor; the sign of that zero may differ from the clamped form, nothing else).  For the attention backward,
+// whose score-mod warps are bound by the half-rate ALU pipe.
+__device__ __forceinline__ uint32_t b3_direct_with_grad_select_late(uint32_t x, const B3Words& k, uint32_t& grad) {
+    using P = Pk<kBf16>;
+    const uint32_t mask = P::ge_mask(x, k.split);
+    const uint32_t c = P::min(x, k.clamp_hi);
+    uint32_t lo = P::fma(c, k.lo[3], k.lo[2]);
+    uint32_t hi = P::fma(c, k.hi[3], k.hi[2]);
+    lo = P::fma(c, lo, k.lo[1]);
+    hi = P::fma(c, hi, k.hi[1]);
+    lo = P::fma_relu(c, lo, k.lo[0]);
+    hi = P::fma_relu(c, hi, k.hi[0]);
+    const uint32_t v = select_bits(mask, hi, lo);
+    const uint32_t factor = select_bits(mask, P::fma(c, k.grad_hi[1], k.grad_hi[0]), P::fma(c, k.grad_lo[1], k.grad_lo[0]));
+    grad = P::mul(v, factor);
+    return v;
+}
+
 // ---- fractional exp2, x in [0, 1): two-segment hinge  p(x) = offset + slope*x + delta*max(x - 1/2, 0) --
 struct Exp2Words {
     uint32_t slope, offset, delta;
