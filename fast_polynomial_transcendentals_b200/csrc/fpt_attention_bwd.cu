@@ -139,7 +139,7 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return Sfu<k
 // One pair of columns of one row: raw scores s0, s1 and dP values d0, d1 -> bf16x2 words of P and of dS (the factor
 // `scale` common to every dS is applied once, in the epilogue).
 //   l0, l1: lse * log2(e) of the two (row, column) positions' query;  t0, t1: their delta;  m0, m1: masked out
-template <int MODE>
+template <int MODE, int GRAD>
 __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s1, float d0, float d1, float l0, float l1,
                                            float t0, float t1, bool m0, bool m1, uint32_t& p_word, uint32_t& ds_word) {
     // fp32 steps run two lanes per instruction (mul2 / sub2 / fma2): these loops are bound by issue slots
@@ -187,7 +187,7 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         if (m0) p0 = 0.0f;
         if (m1) p1 = 0.0f;
         float g0, g1;
-        if (p.softcap_grad == 1) {
+        if constexpr (GRAD == 1) {
             fma2(-th0, -th1, th0, th1, 1.0f, 1.0f, g0, g1);
         } else {
             // derivative of the polynomial on packed bf16 lanes, like the polynomial itself: three fused
@@ -219,7 +219,9 @@ struct Cols {
     static __device__ __forceinline__ uint32_t dp(int t) { return WHICH == 0 ? kColDp + 128u * uint32_t(t & 1) : kColDp; }
 };
 
-template <int MODE, int WHICH>
+// GRAD (soft-capped mode only): 0 the analytical derivative of the tanh polynomial, 1 the identity 1 - t^2; a template
+// parameter because the choice sits inside the per-pair arithmetic.
+template <int MODE, int WHICH, int GRAD = 0>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                      const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
@@ -479,7 +481,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                 m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
                                 m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
                             }
-                            score_pair<MODE>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
+                            score_pair<MODE, GRAD>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
                                              __uint_as_float(dv[c + 1]), lv[2 * h2], lv[2 * h2 + 1], dl[2 * h2], dl[2 * h2 + 1],
                                              m0, m1, pw[16 * chunk + 2 * quad + h2], dsw[16 * chunk + 2 * quad + h2]);
                         }
@@ -657,16 +659,17 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     const int raster = fpt::tuning_attention_raster();
     const double streamed_all_heads = double(q_heads) * double(seq) * kDim * 2.0 * 2.0;
     p.rows_fastest = raster >= 0 ? raster : (!causal && streamed_all_heads > 64.0 * 1024 * 1024 ? 1 : 0);
-    auto run = [&](auto mode_tag) {
+    auto run = [&](auto mode_tag, auto grad_tag) {
         constexpr int M = decltype(mode_tag)::value;
+        constexpr int G = decltype(grad_tag)::value;
         // dQ: fixed Q, dO; streamed K, V.   dK, dV: fixed K, V; streamed Q, dO
-        if (int rc = launch(attention_bwd_kernel<M, 0>, unsigned(q_heads), map_q, map_do, map_k, map_v,
+        if (int rc = launch(attention_bwd_kernel<M, 0, G>, unsigned(q_heads), map_q, map_do, map_k, map_v,
                             static_cast<uint16_t*>(dq), nullptr))
             return rc;
-        return launch(attention_bwd_kernel<M, 1>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
+        return launch(attention_bwd_kernel<M, 1, G>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
                       static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv));
     };
-    if (mode == FPT_ATTN_SOFTCAP_TANH) return run(IC<0>{});
-    if (mode == FPT_ATTN_SIGMOID_DIRECT) return run(IC<1>{});
-    return run(IC<2>{});
+    if (mode == FPT_ATTN_SOFTCAP_TANH) return softcap_grad == 1 ? run(IC<0>{}, IC<1>{}) : run(IC<0>{}, IC<0>{});
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return run(IC<1>{}, IC<0>{});
+    return run(IC<2>{}, IC<0>{});
 }
