@@ -60,6 +60,9 @@ struct BwdParams {
     int rows_fastest;      // grid = (row tiles, heads, batch) instead of (heads, row tiles, batch)
     int softcap_grad;      // 0 analytical derivative of the polynomial, 1 the identity 1 - t^2
     float scale, softcap;
+    float score_to_log2;   // scale * log2(e): raw score -> log2-domain score (plain softmax)
+    float score_to_tanh;   // scale / softcap: raw score -> tanh argument
+    float tanh_to_log2;    // softcap * log2(e): tanh value -> log2-domain score
     uint32_t tanh_dw[4];   // derivative of the tanh program as packed bf16 words: d0 + d1 t + d2 t^2 + d3 t^3
     uint32_t* status;
     ProgramWords tanh;
@@ -156,7 +159,7 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         p_word = pr;
         ds_word = pack_bf16(g0, g1);
     } else if constexpr (MODE == 2) {
-        const float c = p.scale * kLog2eB;
+        const float c = p.score_to_log2;
         float a0, a1, e0, e1;
         fma2(s0, s1, c, c, -l0, -l1, a0, a1);
         float p0 = ex2f(a0), p1 = ex2f(a1);
@@ -167,7 +170,7 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         mul2(p0, p1, e0, e1, e0, e1);
         ds_word = pack_bf16(e0, e1);
     } else {
-        const float in = p.scale / p.softcap, out = p.softcap * kLog2eB;
+        const float in = p.score_to_tanh, out = p.tanh_to_log2;
         float x0, x1;
         mul2(s0, s1, in, in, x0, x1);
         const uint32_t x = pack_bf16(x0, x1);
@@ -621,6 +624,9 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     p.causal = causal ? 1 : 0;
     p.softcap_grad = softcap_grad;
     p.scale = scale; p.softcap = softcap;
+    p.score_to_log2 = scale * kLog2eB;
+    p.score_to_tanh = softcap != 0.0f ? scale / softcap : 0.0f;
+    p.tanh_to_log2 = softcap * kLog2eB;
     p.status = static_cast<uint32_t*>(status);
     const ProgramRow* tanh_row = find_program(FPT_FN_TANH, FPT_FWD, 4, FPT_BF16, FPT_SRC_CURRENT);
     if (!tanh_row || tanh_row->shape != kOddSat) return FPT_ERR_UNKNOWN_PROGRAM;
