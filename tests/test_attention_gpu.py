@@ -280,7 +280,8 @@ def test_running_maximum_that_keeps_growing_is_rescaled(fpt, cuda, oracle):
                 assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < 2e-2
 
 
-@pytest.mark.parametrize("softcap,gain", [(50.0, 1.0), (50.0, 12.0), (30.0, 30.0), (100.0, 1.0), (100.0, 12.0)])
+@pytest.mark.parametrize("softcap,gain", [(50.0, 1.0), (50.0, 12.0), (30.0, 30.0), (100.0, 1.0), (100.0, 12.0),
+                                          (0.5, 1.0), (67.5, 40.0), (67.5, 1.0)])   # the ends of the column-split range
 def test_softcap_layouts_and_saturating_scores(fpt, cuda, oracle, softcap, gain):
     """Soft-cap 30 / 50 take the column-split layout with its fixed exponent reference, 100 the one-thread-per-row
     layout with a running maximum; `gain` pushes most scores into the saturated part of the tanh program (rows whose
