@@ -199,6 +199,10 @@ __global__ void __launch_bounds__(kBlock) packed_element_kernel(const Op op, con
 // One row per thread: like the flat kernels, two 128-bit loads in flight per thread and many short
 // blocks measured best (B1 shape, 16384 x 14336: 4 rows per thread 6.85 TB/s).
 constexpr int kPackedRows = 1;
+#ifndef FPT_PACKED_ROWS_BWD
+#define FPT_PACKED_ROWS_BWD 2
+#endif
+constexpr int kPackedRowsBwd = FPT_PACKED_ROWS_BWD;   // rows per thread and pass in the backward: two measured 0.6 % (16384 x 14336) to 2-3 % (131072 x 1408) faster than one
 
 template <bool BWD, class Op>
 int launch_packed(const Op& op, PackedArgs a, cudaStream_t stream) {
@@ -222,7 +226,7 @@ int launch_packed(const Op& op, PackedArgs a, cudaStream_t stream) {
     int shift = 0;
     while ((1 << shift) < kPackedBlock && (1 << shift) < a.vecs_per_row) ++shift;
     a.tx_shift = shift;
-    const int rows_per_block = (kPackedBlock >> shift) * kPackedRows;
+    const int rows_per_block = (kPackedBlock >> shift) * (BWD ? kPackedRowsBwd : kPackedRows);
     int64_t row_groups = (a.rows + rows_per_block - 1) / rows_per_block;
     const int64_t col_tiles = (vpr + (1 << shift) - 1) >> shift;
     if (t.blocks_per_sm > 0) {
@@ -234,8 +238,8 @@ int launch_packed(const Op& op, PackedArgs a, cudaStream_t stream) {
     const bool streaming = t.streaming < 0 ? bytes > dev.l2_bytes : t.streaming != 0;
     const dim3 grid{unsigned(col_tiles), unsigned(row_groups), 1u};
     if constexpr (BWD) {
-        if (streaming) packed_bwd_kernel<Op, kPackedRows, true><<<grid, kPackedBlock, 0, stream>>>(op, a);
-        else packed_bwd_kernel<Op, kPackedRows, false><<<grid, kPackedBlock, 0, stream>>>(op, a);
+        if (streaming) packed_bwd_kernel<Op, kPackedRowsBwd, true><<<grid, kPackedBlock, 0, stream>>>(op, a);
+        else packed_bwd_kernel<Op, kPackedRowsBwd, false><<<grid, kPackedBlock, 0, stream>>>(op, a);
     } else {
         if (streaming) packed_fwd_kernel<Op, kPackedRows, true><<<grid, kPackedBlock, 0, stream>>>(op, a);
         else packed_fwd_kernel<Op, kPackedRows, false><<<grid, kPackedBlock, 0, stream>>>(op, a);
