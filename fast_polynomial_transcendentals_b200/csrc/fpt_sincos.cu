@@ -461,6 +461,7 @@ struct RopeApplyArgs {
     int chunks;              // head_dim / 8
     int pos_per_block;       // 256 / chunks_pow2
     int chunk_shift;
+    int heads_per_block;     // heads of Q and of K one block rotates (grid.z walks the head groups)
 };
 
 // Block = (2^chunk_shift chunks) x (positions); each thread owns one (position, 8-wide chunk): it evaluates
@@ -487,8 +488,9 @@ __global__ void __launch_bounds__(kBlock) rope_apply_kernel(const RopeApplyArgs 
         const Vec<4>* in = reinterpret_cast<const Vec<4>*>(a.q) + token * a.q_heads * a.chunks + chunk;
         Vec<4>* out = reinterpret_cast<Vec<4>*>(a.q_out) + (b * a.q_heads * a.seq + pos) * a.chunks + chunk;
         const int64_t out_step = a.seq * a.chunks;
-        int64_t h = 0;
-        for (; h + 4 <= a.q_heads; h += 4) {
+        int64_t h = int64_t(blockIdx.z) * a.heads_per_block;
+        const int64_t h_end = min(a.q_heads, h + a.heads_per_block);
+        for (; h + 4 <= h_end; h += 4) {
             Vec<4> v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = load_vec<4, true>(in + (h + u) * a.chunks);
@@ -496,7 +498,7 @@ __global__ void __launch_bounds__(kBlock) rope_apply_kernel(const RopeApplyArgs 
             for (int u = 0; u < 4; ++u)
                 store_vec<4, true>(out + (h + u) * out_step, rotate_chunk<IO_BF16>(v[u], cos_lo, sin_lo, cos_hi, sin_hi));
         }
-        for (; h < a.q_heads; ++h)
+        for (; h < h_end; ++h)
             store_vec<4, true>(out + h * out_step,
                                rotate_chunk<IO_BF16>(load_vec<4, true>(in + h * a.chunks), cos_lo, sin_lo, cos_hi, sin_hi));
     }
@@ -504,8 +506,9 @@ __global__ void __launch_bounds__(kBlock) rope_apply_kernel(const RopeApplyArgs 
         const Vec<4>* in = reinterpret_cast<const Vec<4>*>(a.k) + token * a.k_heads * a.chunks + chunk;
         Vec<4>* out = reinterpret_cast<Vec<4>*>(a.k_out) + (b * a.k_heads * a.seq + pos) * a.chunks + chunk;
         const int64_t out_step = a.seq * a.chunks;
-        int64_t h = 0;
-        for (; h + 4 <= a.k_heads; h += 4) {
+        int64_t h = int64_t(blockIdx.z) * a.heads_per_block;
+        const int64_t h_end = min(a.k_heads, h + a.heads_per_block);
+        for (; h + 4 <= h_end; h += 4) {
             Vec<4> v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) v[u] = load_vec<4, true>(in + (h + u) * a.chunks);
@@ -513,7 +516,7 @@ __global__ void __launch_bounds__(kBlock) rope_apply_kernel(const RopeApplyArgs 
             for (int u = 0; u < 4; ++u)
                 store_vec<4, true>(out + (h + u) * out_step, rotate_chunk<IO_BF16>(v[u], cos_lo, sin_lo, cos_hi, sin_hi));
         }
-        for (; h < a.k_heads; ++h)
+        for (; h < h_end; ++h)
             store_vec<4, true>(out + h * out_step,
                                rotate_chunk<IO_BF16>(load_vec<4, true>(in + h * a.chunks), cos_lo, sin_lo, cos_hi, sin_hi));
     }
@@ -627,7 +630,12 @@ extern "C" int fpt_rope_apply(void* q_out, void* k_out, const void* q, const voi
     a.chunk_shift = shift;
     a.pos_per_block = kBlock >> shift;
     if (a.pos_per_block < 1) return FPT_ERR_BAD_SIZE;
-    const dim3 grid{unsigned((seq + a.pos_per_block - 1) / a.pos_per_block), unsigned(batch), 1u};
+    const int64_t most_heads = q_heads > k_heads ? q_heads : k_heads;
+    const int tuned = fpt::tuning_rope_heads_per_block();
+    a.heads_per_block = int(tuned > 0 && tuned < most_heads ? tuned : most_heads);
+    const int64_t head_groups = (most_heads + a.heads_per_block - 1) / a.heads_per_block;
+    if (head_groups > 65535) return FPT_ERR_BAD_SIZE;
+    const dim3 grid{unsigned((seq + a.pos_per_block - 1) / a.pos_per_block), unsigned(batch), unsigned(head_groups)};
 #define FPT_ROPE_CASE(K)                                                                              \
     case K:                                                                                           \
         if (dtype == FPT_BF16) rope_apply_kernel<K, true><<<grid, kBlock, 0, stream>>>(a);            \

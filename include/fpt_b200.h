@@ -298,7 +298,8 @@ int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* sta
  * allows (soft-cap with cap*log2(e) <= 98), 0 forces the one-thread-per-row layout, 2 uses the column-split layout for
  * the sigmoid mode as well (measured no faster; kept for comparison runs);
  * key "attention_raster": order in which attention blocks are handed out: 0 heads fastest, 1 row blocks of one head
- * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large). */
+ * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large);
+ * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads). */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 
