@@ -11,6 +11,14 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (B200, sm_100a)")
+    # A fresh checkout has no built library (build products are not tracked): compile it once, where nvcc is present.
+    # This is the package's own build step, not a fallback: without the library the package still refuses to load.
+    import shutil
+    lib = ROOT / "fast_polynomial_transcendentals_b200" / "libfpt_b200.so"
+    compat = ROOT / "fast_polynomial_transcendentals_b200" / "libfpt_b200_compat.so"
+    if not (lib.exists() and compat.exists()) and (shutil.which("nvcc") or Path("/usr/local/cuda/bin/nvcc").exists()):
+        from fast_polynomial_transcendentals_b200 import build
+        build.build()
 
 
 @pytest.fixture(scope="session")
