@@ -191,6 +191,9 @@ def run_gpu_arm(args):
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)")
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
+    from fast_polynomial_transcendentals_b200.pipeline import bind_host_thread_to_device_node
+    all_cpus = os.sched_getaffinity(0)
+    host_binding = bind_host_thread_to_device_node(local) if world > 1 else None   # pinned buffers local to the GPU
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     lib = _lib.load()
@@ -299,6 +302,9 @@ def run_gpu_arm(args):
     if world > 1:
         dist.barrier()
     e2e = bench_e2e(torch, spline_ops, HostPipeline, device)
+    if host_binding:
+        e2e["host_binding"] = host_binding
+        os.sched_setaffinity(0, all_cpus)      # the CPU legs below use every core again
     if world > 1:
         t = torch.tensor([e2e["ms_per_step"]], device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)

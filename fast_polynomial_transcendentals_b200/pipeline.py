@@ -11,6 +11,33 @@ from typing import Callable, Sequence
 import torch
 
 
+def bind_host_thread_to_device_node(device_index: int) -> str | None:
+    """Restrict the calling thread to the CPUs of the NUMA node the GPU hangs off, so that the pinned buffers it
+    allocates next land in memory local to that GPU's PCIe root (first touch).  With one process per GPU on a two-socket
+    host this keeps half of the copies off the socket interconnect.  Returns a short description, or None when the
+    topology cannot be read or the node's CPUs are not available to this process (then nothing is changed)."""
+    import os
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bdf = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bdf}/numa_node") as fh:
+            node = int(fh.read().strip())
+        if node < 0:
+            return None
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as fh:
+            cpus: set[int] = set()
+            for part in fh.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = cpus & os.sched_getaffinity(0)
+        if not allowed:
+            return None
+        os.sched_setaffinity(0, allowed)
+        return f"numa node {node}, {len(allowed)} cpus"
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
 class HostPipeline:
     """Double-buffered chunk pipeline for operators of the form outs = fn(*ins) on flat tensors.
 
