@@ -35,6 +35,7 @@ SIGNATURES: dict[str, list] = {
     "fpt_swish_mul_packed": [_vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed_bwd": [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_b3_sigmoid_direct": [_vp, _vp, _vp, _i64, _int, _int, _vp],
+    "fpt_b3_sigmoid_direct_variant": [_vp, _vp, _vp, _i64, _int, _int, _int, _vp],
     "fpt_fwd_deriv": [_vp, _vp, _vp, _i64, _int, _int, _vp],
     "fpt_fused_fwd_bwd": [_vp, _vp, _vp, _vp, _i64, _int, _vp],
     "fpt_multiply": [_vp, _vp, _vp, _i64, _int, _vp],
@@ -57,6 +58,7 @@ SIGNATURES: dict[str, list] = {
                                  ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int,
                                  ctypes.c_float, ctypes.c_float, _int, _int, _int, _vp, _vp],
     "fpt_selftest_umma": [_vp, _vp, _vp, _int, _vp, _vp],
+    "fpt_selftest_bounded_wait": [_vp, _vp, _i64, _int, _vp],
     "fpt_rope_apply_static_table": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _int, _int, _vp],
     "fpt_rope_static_table_capacity": [],
     "fpt_set_tuning": [ctypes.c_char_p, _int],

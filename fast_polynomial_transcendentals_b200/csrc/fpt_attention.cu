@@ -68,8 +68,9 @@ struct AttnParams {
 // EMU: routing frequency of the software exponential in the soft-max modes, with the meaning the reference gives
 // exp2_emu_freq (reference: src/sfu_repro/fa4.py:724-733): 0 keeps every lane on the special-function unit; a positive
 // frequency f sends four of every f keys of a row through a software exponential on the FMA pipe (12 -> one third,
-// 32 -> one eighth); EK picks it: the cubic ("d3") or the two-piece line ("pwl2") of fpt_scoremod.cuh.  The unit delivers 16 results per clock and SM, which for a 128 x 128 tile takes as long as the two
-// tensor-core products of that tile: that is the pressure the routing is meant to relieve.
+// 32 -> one eighth); EK picks it: the cubic ("d3") or the two-piece line ("pwl2") of fpt_scoremod.cuh.  The unit
+// delivers 16 results per clock and SM, which for a 128 x 128 tile takes as long as the two tensor-core products of
+// that tile: that is the pressure the routing is meant to relieve.
 // Optional timeline for tuning builds (-DFPT_ATTN_TRACE): block (0,0,0) stores (tag, SM clock) pairs behind the
 // status word, 4096 words per traced warp; the caller must then pass a status buffer of 64 KiB.
 #ifdef FPT_ATTN_TRACE

@@ -150,7 +150,8 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         float x0, x1;
         mul2(s0, s1, p.scale, p.scale, x0, x1);
         uint32_t grad;
-        uint32_t pr = b3_direct_with_grad_select_late(pack_bf16(x0, x1), p.b3, grad);
+        // infinite scores are made finite by the conversion (see b3_direct_with_grad_select_late)
+        uint32_t pr = b3_direct_with_grad_select_late(Sfu<kBf16>::pack_satfinite(x0, x1), p.b3, grad);
         float g0, g1;
         unpack_bf16x2(grad, g0, g1);
         mul2(g0, g1, d0, d1, g0, g1);

@@ -1,5 +1,7 @@
 // Isolated score-mod evaluators: the direct piecewise-cubic sigmoid of sigmoid attention (B3) and the
 // fractional exp2 hinge, as flat element-wise kernels.
+#include <type_traits>
+
 #include "fpt_programs.h"
 #include "fpt_scoremod.cuh"
 #include "fpt_stream.cuh"
@@ -7,21 +9,27 @@
 namespace fpt {
 namespace {
 
-template <bool WITH_GRAD>
+// LATE: the evaluation order of the attention kernels (both rows on the FMA pipe, one select afterwards, no lower
+// clamp, floor folded into the last multiply-add) instead of the deployed instruction order.
+template <bool WITH_GRAD, bool LATE>
+__device__ __forceinline__ uint32_t b3_eval(uint32_t x, const B3Words& k, uint32_t& grad) {
+    if constexpr (WITH_GRAD) return LATE ? b3_direct_with_grad_select_late(x, k, grad) : b3_direct_with_grad(x, k, grad);
+    else return LATE ? b3_direct_select_late(x, k) : b3_direct(x, k);
+}
+
+template <bool WITH_GRAD, bool LATE>
 struct B3Op {
     static constexpr int NIN = 1, NOUT = WITH_GRAD ? 2 : 1;
     B3Words k;
     __device__ __forceinline__ void apply(const uint32_t (&in)[1], uint32_t (&out)[NOUT]) const {
-        if constexpr (WITH_GRAD) {
-            out[0] = b3_direct_with_grad(in[0], k, out[1]);
-        } else {
-            out[0] = b3_direct(in[0], k);
-        }
+        uint32_t g = 0;
+        out[0] = b3_eval<WITH_GRAD, LATE>(in[0], k, g);
+        if constexpr (WITH_GRAD) out[1] = g;
     }
 };
 
 // fp32 scores -> bf16 probabilities (the form in which the attention kernel meets the evaluator)
-template <bool WITH_GRAD>
+template <bool WITH_GRAD, bool LATE>
 __global__ void __launch_bounds__(kBlock) b3_from_f32_kernel(const B3Words k, const float* __restrict__ scores,
                                                             uint16_t* __restrict__ prob, uint16_t* __restrict__ grad,
                                                             int64_t n) {
@@ -29,19 +37,17 @@ __global__ void __launch_bounds__(kBlock) b3_from_f32_kernel(const B3Words k, co
 #pragma unroll 1
     for (int64_t i = int64_t(blockIdx.x) * kBlock + threadIdx.x; i < pairs; i += int64_t(gridDim.x) * kBlock) {
         const float2 s = reinterpret_cast<const float2*>(scores)[i];
-        const uint32_t x = Sfu<kBf16>::pack(s.x, s.y);
-        if constexpr (WITH_GRAD) {
-            uint32_t g;
-            reinterpret_cast<uint32_t*>(prob)[i] = b3_direct_with_grad(x, k, g);
-            reinterpret_cast<uint32_t*>(grad)[i] = g;
-        } else {
-            reinterpret_cast<uint32_t*>(prob)[i] = b3_direct(x, k);
-        }
+        // the late-select order with a gradient converts as the attention backward does (no infinite lanes)
+        const uint32_t x = (LATE && WITH_GRAD) ? Sfu<kBf16>::pack_satfinite(s.x, s.y) : Sfu<kBf16>::pack(s.x, s.y);
+        uint32_t g = 0;
+        reinterpret_cast<uint32_t*>(prob)[i] = b3_eval<WITH_GRAD, LATE>(x, k, g);
+        if constexpr (WITH_GRAD) reinterpret_cast<uint32_t*>(grad)[i] = g;
     }
     if ((n & 1) && blockIdx.x == 0 && threadIdx.x == 0) {
-        const uint32_t x = Sfu<kBf16>::pack(scores[n - 1], scores[n - 1]);
+        const uint32_t x = (LATE && WITH_GRAD) ? Sfu<kBf16>::pack_satfinite(scores[n - 1], scores[n - 1])
+                                                : Sfu<kBf16>::pack(scores[n - 1], scores[n - 1]);
         uint32_t g = 0;
-        const uint32_t p = WITH_GRAD ? b3_direct_with_grad(x, k, g) : b3_direct(x, k);
+        const uint32_t p = b3_eval<WITH_GRAD, LATE>(x, k, g);
         prob[n - 1] = uint16_t(p);
         if constexpr (WITH_GRAD) grad[n - 1] = uint16_t(g);
     }
@@ -89,42 +95,44 @@ __global__ void __launch_bounds__(kBlock) exp2_full_f32_kernel(const float* __re
 
 using namespace fpt;
 
-extern "C" int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
-                                     int log2_n, fpt_stream_t stream) {
+extern "C" int fpt_b3_sigmoid_direct_variant(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
+                                             int log2_n, int variant, fpt_stream_t stream) {
     if (n < 0) return FPT_ERR_BAD_SIZE;
     if (n > 0 && (!prob || !scores)) return FPT_ERR_NULL_POINTER;
     if (log2_n < 1 || log2_n > 24) return FPT_ERR_BAD_SIZE;
+    if (variant != FPT_B3_DEPLOYED_ORDER && variant != FPT_B3_SELECT_LATE) return FPT_ERR_BAD_ENUM;
     const B3Words k = b3_words(log2_n);
     if (n == 0) return FPT_OK;
-    if (scores_are_f32) {
-        DeviceInfo dev;
-        if (int rc = current_device_info(&dev)) return rc;
-        if ((reinterpret_cast<uintptr_t>(scores) & 7u) || (reinterpret_cast<uintptr_t>(prob) & 3u) ||
-            (reinterpret_cast<uintptr_t>(grad) & 3u))
-            return FPT_ERR_MISALIGNED;
-        int64_t grid = (n / 2 + kBlock - 1) / kBlock;
-        if (grid < 1) grid = 1;
-        const int64_t cap = int64_t(dev.sm_count) * 64;
-        if (grid > cap) grid = cap;
-        if (grad)
-            b3_from_f32_kernel<true><<<unsigned(grid), kBlock, 0, stream>>>(
+    auto run = [&](auto with_grad, auto late) -> int {
+        constexpr bool G = decltype(with_grad)::value, L = decltype(late)::value;
+        if (scores_are_f32) {
+            DeviceInfo dev;
+            if (int rc = current_device_info(&dev)) return rc;
+            if ((reinterpret_cast<uintptr_t>(scores) & 7u) || (reinterpret_cast<uintptr_t>(prob) & 3u) ||
+                (reinterpret_cast<uintptr_t>(grad) & 3u))
+                return FPT_ERR_MISALIGNED;
+            int64_t grid = (n / 2 + kBlock - 1) / kBlock;
+            if (grid < 1) grid = 1;
+            const int64_t cap = int64_t(dev.sm_count) * 64;
+            if (grid > cap) grid = cap;
+            b3_from_f32_kernel<G, L><<<unsigned(grid), kBlock, 0, stream>>>(
                 k, static_cast<const float*>(scores), static_cast<uint16_t*>(prob), static_cast<uint16_t*>(grad), n);
-        else
-            b3_from_f32_kernel<false><<<unsigned(grid), kBlock, 0, stream>>>(
-                k, static_cast<const float*>(scores), static_cast<uint16_t*>(prob), nullptr, n);
-        return cuda_status(cudaGetLastError());
-    }
-    if (grad) {
-        StreamArgs<1, 2> a{};
+            return cuda_status(cudaGetLastError());
+        }
+        StreamArgs<1, G ? 2 : 1> a{};
         a.in[0] = static_cast<const uint16_t*>(scores);
         a.out[0] = static_cast<uint16_t*>(prob);
-        a.out[1] = static_cast<uint16_t*>(grad);
-        return launch_stream(B3Op<true>{k}, a, n, stream);
-    }
-    StreamArgs<1, 1> a{};
-    a.in[0] = static_cast<const uint16_t*>(scores);
-    a.out[0] = static_cast<uint16_t*>(prob);
-    return launch_stream(B3Op<false>{k}, a, n, stream);
+        if constexpr (G) a.out[1] = static_cast<uint16_t*>(grad);
+        return launch_stream(B3Op<G, L>{k}, a, n, stream);
+    };
+    const bool late = variant == FPT_B3_SELECT_LATE;
+    if (grad) return late ? run(std::true_type{}, std::true_type{}) : run(std::true_type{}, std::false_type{});
+    return late ? run(std::false_type{}, std::true_type{}) : run(std::false_type{}, std::false_type{});
+}
+
+extern "C" int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
+                                     int log2_n, fpt_stream_t stream) {
+    return fpt_b3_sigmoid_direct_variant(prob, grad, scores, n, scores_are_f32, log2_n, FPT_B3_DEPLOYED_ORDER, stream);
 }
 
 extern "C" int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int repeats, fpt_stream_t stream) {

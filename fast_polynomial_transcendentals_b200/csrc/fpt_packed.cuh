@@ -192,6 +192,12 @@ struct Sfu<kBf16> {
         asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
         return d;
     }
+    // the same conversion with infinities replaced by the largest finite value of their sign (NaN stays NaN)
+    static __device__ __forceinline__ uint32_t pack_satfinite(float lo, float hi) {
+        uint32_t d;
+        asm("cvt.rn.satfinite.bf16x2.f32 %0, %1, %2;" : "=r"(d) : "f"(hi), "f"(lo));
+        return d;
+    }
     static constexpr uint32_t log2e = 0x3fb93fb9u;      // 1.4453 in bf16
     static constexpr uint32_t neg_log2e = 0xbfb9bfb9u;
 };

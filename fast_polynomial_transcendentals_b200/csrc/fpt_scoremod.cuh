@@ -84,9 +84,12 @@ __device__ __forceinline__ uint32_t b3_direct_with_grad(uint32_t x, const B3Word
 }
 
 // The pair (value, coupled derivative) with the late select of b3_direct_select_late: both rows' cubics and both rows'
-// derivative factors on the FMA pipe, one select each, no lower clamp (below -6 the value is +0 and so is its product with
-// the finite factor; the sign of that zero may differ from the clamped form, nothing else).  For the attention backward,
-// whose score-mod warps are bound by the half-rate ALU pipe.
+// derivative factors on the FMA pipe, one select each, no lower clamp.  Below -6 the value is +0 and the low-row factor
+// 1 - slope |x| stays positive and finite for every finite x, so the product is the same +0 the clamped form gives.  The
+// one input that differs is -inf: its factor is +inf and 0 * inf is NaN where the clamped form returns +0.  Callers that
+// can meet an infinite score (an overflowed dot product) therefore convert their fp32 scores with
+// Sfu<kBf16>::pack_satfinite, which costs nothing and maps -inf to the largest finite negative value (result +0, +0).
+// For the attention backward, whose score-mod warps are bound by the half-rate ALU pipe.
 __device__ __forceinline__ uint32_t b3_direct_with_grad_select_late(uint32_t x, const B3Words& k, uint32_t& grad) {
     using P = Pk<kBf16>;
     const uint32_t mask = P::ge_mask(x, k.split);

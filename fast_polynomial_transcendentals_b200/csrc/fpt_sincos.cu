@@ -602,19 +602,40 @@ extern "C" int fpt_rope_table_lut(void* table, const void* phase_increments, con
     return cuda_status(cudaGetLastError());
 }
 
-extern "C" int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const void* params, int64_t batch,
-                              int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int kind, int dtype,
-                              fpt_stream_t stream) {
+// Argument checks of the fused rotation, separate from the launch so that an entry point which enqueues other work
+// first can run them before anything is enqueued.  *empty is set when there is nothing to do.
+static int rope_apply_validate(const void* q_out, const void* k_out, const void* q, const void* k, const void* params,
+                               int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int dtype,
+                               bool* empty) {
+    *empty = false;
     if (batch < 0 || seq < 0 || q_heads < 0 || k_heads < 0 || head_dim < 0) return FPT_ERR_BAD_SIZE;
     if (head_dim % 8 || head_dim > 2048) return FPT_ERR_BAD_SIZE;
     if (batch > 65535 || seq > 0x7fffffff) return FPT_ERR_BAD_SIZE;
     if (dtype != FPT_FP16 && dtype != FPT_BF16) return FPT_ERR_BAD_ENUM;
-    if (batch * seq * head_dim == 0 || q_heads + k_heads == 0) return FPT_OK;
+    if (batch * seq * head_dim == 0 || q_heads + k_heads == 0) {
+        *empty = true;
+        return FPT_OK;
+    }
     if (!q_out || !k_out || !q || !k || !params) return FPT_ERR_NULL_POINTER;
     const uintptr_t align = reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out) |
                             reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |
                             reinterpret_cast<uintptr_t>(params);
     if (align & 15u) return FPT_ERR_MISALIGNED;
+    const int64_t most_heads = q_heads > k_heads ? q_heads : k_heads;
+    const int tuned = fpt::tuning_rope_heads_per_block();
+    const int64_t heads_per_block = tuned > 0 && tuned < most_heads ? tuned : most_heads;
+    if ((most_heads + heads_per_block - 1) / heads_per_block > 65535) return FPT_ERR_BAD_SIZE;
+    return FPT_OK;
+}
+
+extern "C" int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const void* params, int64_t batch,
+                              int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim, int kind, int dtype,
+                              fpt_stream_t stream) {
+    bool empty = false;
+    if (int rc = rope_apply_validate(q_out, k_out, q, k, params, batch, seq, q_heads, k_heads, head_dim, dtype, &empty))
+        return rc;
+    if (empty) return FPT_OK;
+    if (kind != FPT_ROPE_HALF_TURN_D5_D6 && kind != FPT_ROPE_NATIVE && kind != FPT_ROPE_CACHED) return FPT_ERR_BAD_ENUM;
     DeviceInfo dev;
     if (int rc = current_device_info(&dev)) return rc;
     RopeApplyArgs a{};
@@ -704,12 +725,20 @@ extern "C" int fpt_rope_apply_static_table(void* q_out, void* k_out, const void*
                                            const void* phase_increments, int64_t batch, int64_t seq, int64_t q_heads,
                                            int64_t k_heads, int64_t head_dim, int table_kind, int dtype,
                                            fpt_stream_t stream) {
-    if (batch < 0 || seq < 0 || q_heads < 0 || k_heads < 0 || head_dim < 0) return FPT_ERR_BAD_SIZE;
     if (table_kind != FPT_ROPE_HALF_TURN_D5_D6 && table_kind != FPT_ROPE_QUARTER_TURN_D3_D4) return FPT_ERR_BAD_ENUM;
-    if (head_dim % 8) return FPT_ERR_BAD_SIZE;
+    // every check of the two steps comes first: an error return means that nothing was enqueued and the shared table
+    // still holds what the last successful call left in it
+    bool empty = false;
+    alignas(16) static const char aligned_stand_in = 0;      // stands for the table until its address is known
+    if (int rc = rope_apply_validate(q_out, k_out, q, k, &aligned_stand_in, batch, seq, q_heads, k_heads, head_dim, dtype,
+                                     &empty))
+        return rc;
     if (seq > 0 && head_dim > 0 && seq > fpt::kStaticRopeTableHalves / head_dim) return FPT_ERR_SCRATCH_TOO_SMALL;
-    if (batch * seq * head_dim == 0 || q_heads + k_heads == 0) return FPT_OK;
+    if (empty) return FPT_OK;
     if (!phase_increments) return FPT_ERR_NULL_POINTER;
+    if (reinterpret_cast<uintptr_t>(phase_increments) & 3u) return FPT_ERR_MISALIGNED;
+    fpt::DeviceInfo dev;
+    if (int rc = fpt::current_device_info(&dev)) return rc;
     void* table = nullptr;
     if (int rc = fpt::static_rope_table_address(&table)) return rc;
     // every entry of the [2, seq, head_dim/2] region used below is rewritten here, so nothing left over from an

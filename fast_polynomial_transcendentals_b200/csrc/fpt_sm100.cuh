@@ -50,16 +50,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far above any legitimate wait inside one kernel
 
 // Bounded wait.  `abort_flag` (shared memory) lets one timed-out waiter release all the others quickly.
-// Returns false on timeout / abort; the caller must then skip to the kernel's teardown.
+// Returns false on timeout / abort; the caller must then skip to the kernel's teardown.  The kernels wait with the
+// default limit; only the wait self-test passes a shorter one.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile uint32_t* abort_flag,
-                                          uint32_t* status, uint32_t where) {
+                                          uint32_t* status, uint32_t where, uint64_t limit_ns = kWaitLimitNs) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t start = global_timer_ns();
     uint32_t spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 0x3ffu) == 0) {
             if (*abort_flag) return false;
-            if (global_timer_ns() - start > kWaitLimitNs) {
+            if (global_timer_ns() - start > limit_ns) {
                 *abort_flag = 1u;
                 if (status) atomicCAS(status, 0u, 0x80000000u | where);
                 return false;

@@ -4,8 +4,9 @@
 // library (unary activations, gradient products, SwiGLU, B3 sigmoid, fractional
 // exp2): NIN input arrays and NOUT output arrays of the same length, processed in
 // per-thread vectors of 128 or 256 bits.  Each thread issues UNROLL independent
-// vector loads per input before it computes, so that a persistent grid of
-// (SM count x resident blocks) keeps enough bytes in flight to cover HBM latency.
+// vector loads per input before it computes; the default grid is one block per
+// tile (persistent grids of SM count x resident blocks measured 3-12 % slower on
+// B200 and remain available through the "blocks_per_sm" tuning key).
 // Above the L2 size the loads and stores carry streaming (evict-first) hints;
 // below it they use the read-only path and plain stores so that back-to-back
 // launches stay L2 resident.  A ragged tail (length not a multiple of the vector

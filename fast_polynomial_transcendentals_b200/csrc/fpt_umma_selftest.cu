@@ -150,10 +150,47 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
     if (warp == 0) tmem_dealloc(tmem, 256);
 }
 
+// The bounded wait of the attention kernels on a barrier nobody arrives on: one thread, one mbarrier, no TMA, no tensor
+// memory, no tensor-core operation, so the block that gives up has nothing in flight.  report[0]: 1 = the wait ran out,
+// 2 = the block found the status word already set and did not wait, 3 = the wait succeeded (cannot happen);
+// report[1], report[2]: low / high word of the nanoseconds spent waiting.
+__global__ void __launch_bounds__(32) bounded_wait_selftest_kernel(uint32_t* status, uint32_t* report, uint64_t limit_ns,
+                                                                   uint32_t where) {
+    __shared__ alignas(8) uint64_t bar;
+    __shared__ uint32_t abort_word;
+    if (threadIdx.x != 0) return;
+    volatile uint32_t* abort_flag = &abort_word;
+    mbar_init(&bar, 1);
+    abort_word = *reinterpret_cast<volatile uint32_t*>(status) != 0u ? 1u : 0u;   // the attention kernels' entry check
+    mbar_fence_init();
+    if (*abort_flag) {
+        report[0] = 2u;
+        report[1] = report[2] = 0u;
+        return;
+    }
+    const uint64_t t0 = global_timer_ns();
+    const bool ok = mbar_wait(&bar, 0, abort_flag, status, where, limit_ns);
+    const uint64_t dt = global_timer_ns() - t0;
+    report[0] = ok ? 3u : 1u;
+    report[1] = uint32_t(dt);
+    report[2] = uint32_t(dt >> 32);
+}
+
 }  // namespace
 }  // namespace fpt
 
 using namespace fpt;
+
+extern "C" int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int where, fpt_stream_t stream) {
+    if (!status || !report) return FPT_ERR_NULL_POINTER;
+    if (limit_ns < 1000 || limit_ns > 1000000) return FPT_ERR_BAD_SIZE;     // 1 us .. 1 ms
+    if (where < 1 || where > 0xffff) return FPT_ERR_BAD_ENUM;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+    bounded_wait_selftest_kernel<<<1, 32, 0, stream>>>(static_cast<uint32_t*>(status), static_cast<uint32_t*>(report),
+                                                       uint64_t(limit_ns), uint32_t(where));
+    return cuda_status(cudaGetLastError());
+}
 
 // a, b: bf16 [128, 128] row-major device arrays; c: fp32 [128, 128]; status: one device word, 0 on success.
 // mode 0: c = a * b^T.  mode 1: c = a * b.

@@ -271,6 +271,9 @@ def validate_fa4_config(config: FA4Config, *, sequence_length: int | None = None
 
 # ---- this package's attention runtime ----------------------------------------------------------------
 
+_EXP2_BACKEND_IDS = {"d3": 0, "pwl2": 1}
+
+
 @dataclass(frozen=True)
 class SoftcapScoreMod:
     """Token for `score_mod=`: soft-cap through the packed bf16 tanh polynomial inside the attention kernel."""
@@ -280,6 +283,80 @@ class SoftcapScoreMod:
     backend: str = "device"
     coeff_source: str = "current"
     backward_mode: str = "analytical"
+
+
+class _AttentionStatus:
+    """The status word the attention kernels report bounded-wait timeouts through, one per device.
+
+    The word lives on the device for the life of the process (no allocation or memset per call).  After every launch
+    its value is copied to pinned host memory on the launching stream; `poll` reads that copy once the copy has
+    completed (never blocking), `check` waits for it.  A non-zero word means a device-side wait ran out and the outputs
+    of the call that set it (and of every later call: blocks that find the word set do no work) are invalid.  The word
+    is cleared when the error is raised, so the call after the exception runs normally."""
+
+    def __init__(self, device):
+        self.device = device
+        self.word = torch.zeros(1, dtype=torch.int32, device=device)
+        self.host = torch.zeros(1, dtype=torch.int32).pin_memory()
+        self.event = torch.cuda.Event()
+        self.pending = False
+        self.where = ""
+
+    def after_launch(self, where: str) -> None:
+        if torch.cuda.is_current_stream_capturing():     # a captured launch is checked when the caller asks (check())
+            return
+        self.host.copy_(self.word, non_blocking=True)
+        self.event.record(torch.cuda.current_stream(self.device))
+        self.pending, self.where = True, where
+
+    def _raise_if_set(self) -> None:
+        self.pending = False
+        value = int(self.host.item()) & 0xFFFFFFFF
+        if value:
+            from .. import _lib
+            self.word.zero_()
+            self.host.zero_()
+            message = _lib.load().fpt_status_string(-8).decode()      # FPT_ERR_DEVICE_TIMEOUT
+            raise RuntimeError(f"{message}: status word {value:#010x} (waiting point {value & 0xFFFF}) seen after "
+                               f"{self.where}; the outputs of that call are invalid")
+
+    def poll(self) -> None:
+        if self.pending and not torch.cuda.is_current_stream_capturing() and self.event.query():
+            self._raise_if_set()
+
+    def check(self) -> None:
+        if not self.pending:             # nothing copied yet (captured launches): read the word itself
+            self.host.copy_(self.word)
+            self.where = self.where or "an attention launch"
+        else:
+            self.event.synchronize()
+        self._raise_if_set()
+
+
+_STATUS: dict[Any, _AttentionStatus] = {}
+
+
+def _status_for(device) -> _AttentionStatus:
+    key = torch.device(device)
+    key = torch.device("cuda", torch.cuda.current_device()) if key.index is None else key
+    state = _STATUS.get(key)
+    if state is None:
+        state = _STATUS[key] = _AttentionStatus(key)
+    return state
+
+
+def check_attention_status(device=None) -> None:
+    """Wait for the attention launches enqueued so far on `device` (default: every device used) and raise RuntimeError
+    if one of them reported a device-side timeout.  Without this call the same error surfaces, without blocking, at the
+    first attention call made after the failed launch has finished; FPT_CHECK_STATUS=1 checks after every call."""
+    for state in ([_status_for(device)] if device is not None else list(_STATUS.values())):
+        state.check()
+
+
+def _finish_launch(state: _AttentionStatus, where: str) -> None:
+    state.after_launch(where)
+    if _env_flag("FPT_CHECK_STATUS"):
+        state.check()
 
 
 def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.0, score_mod=None, sigmoid_attention=False,
@@ -326,13 +403,15 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
             raise NotImplementedError("built routing frequencies: 0, 8, 12, 16, 32")
     out = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((batch, q_heads, seq), dtype=torch.float32, device=q.device)
-    status = torch.zeros(1, dtype=torch.int32, device=q.device)
     strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
     with torch.cuda.device(q.device):
+        status = _status_for(q.device)
+        status.poll()
         _lib.call("fpt_attention_fwd_routed", out.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), batch,
                   seq, q_heads, k.shape[2], dim, strides(q), strides(k), strides(v), strides(out), mode, int(bool(causal)),
-                  scale, cap, log2_n, 1 if exp2_emu_backend == "pwl2" else 0, route, status.data_ptr(),
+                  scale, cap, log2_n, _EXP2_BACKEND_IDS.get(exp2_emu_backend, 0), route, status.word.data_ptr(),
                   torch.cuda.current_stream(q.device).cuda_stream)
+        _finish_launch(status, "the attention forward")
     return out, lse
 
 
@@ -377,7 +456,6 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     dq = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
     dk = torch.empty((batch, seq, k.shape[2], dim), dtype=torch.bfloat16, device=q.device)
     dv = torch.empty_like(dk)
-    status = torch.zeros(1, dtype=torch.int32, device=q.device)
     strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
     needs_forward = mode != 1
     if needs_forward and (out is None or lse is None):
@@ -385,12 +463,15 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     need = int(_lib.load().fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) if needs_forward else 0
     workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
+        status = _status_for(q.device)
+        status.poll()
         _lib.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(),
                   k.data_ptr(), v.data_ptr(), out.data_ptr() if needs_forward else None,
                   lse.data_ptr() if needs_forward else None, workspace.data_ptr(), need, batch, seq, q_heads, k.shape[2],
                   dim, strides(q), strides(k), strides(v), strides(out) if needs_forward else strides(q), strides(dout),
-                  mode, int(bool(causal)), scale, cap, log2_n, grad_mode, status.data_ptr(),
+                  mode, int(bool(causal)), scale, cap, log2_n, grad_mode, status.word.data_ptr(),
                   torch.cuda.current_stream(q.device).cuda_stream)
+        _finish_launch(status, "the attention backward")
     return dq, dk, dv
 
 

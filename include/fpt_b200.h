@@ -137,6 +137,14 @@ int fpt_swish_mul_packed_bwd(void* grad_packed, const void* grad_out, const void
  *      derivative of the deployed pair. */
 int fpt_b3_sigmoid_direct(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
                           int log2_n, fpt_stream_t stream);
+/* The same evaluator in a chosen instruction order.  FPT_B3_DEPLOYED_ORDER is fpt_b3_sigmoid_direct: clamp to
+ * [-6, 6], row selected before the cubic, floor by a separate maximum (reference: extras/paper/manuscript/
+ * main.tex:1042-1072).  FPT_B3_SELECT_LATE is the order the attention kernels of this library run: both rows'
+ * cubics, one select afterwards, upper clamp only, floor folded into the last multiply-add.  Probabilities are the
+ * same bits for every input; the gradient may differ in the sign of a zero below the lower clamp and nowhere else. */
+enum { FPT_B3_DEPLOYED_ORDER = 0, FPT_B3_SELECT_LATE = 1 };
+int fpt_b3_sigmoid_direct_variant(void* prob, void* grad, const void* scores, int64_t n, int scores_are_f32,
+                                  int log2_n, int variant, fpt_stream_t stream);
 
 /* ---- fractional exp2 on packed fp16, x in [0, 1)
  *      replaces FractionalNative / FractionalPwl2Hinge of the reference's stand-alone benchmark
@@ -227,7 +235,10 @@ int fpt_rope_apply(void* q_out, void* k_out, const void* q, const void* k, const
  *      rejected with FPT_ERR_SCRATCH_TOO_SMALL.  The call allocates nothing.  The first call on a device looks up
  *      the array's device address (cudaGetSymbolAddress); make that first call before any stream capture.
  *      All calls share the one array: two calls whose kernels may overlap on the GPU (different streams) race on
- *      it; calls on one stream are safe.  table_kind: FPT_ROPE_HALF_TURN_D5_D6 or FPT_ROPE_QUARTER_TURN_D3_D4. */
+ *      it; calls on one stream are safe.  table_kind: FPT_ROPE_HALF_TURN_D5_D6 or FPT_ROPE_QUARTER_TURN_D3_D4.
+ *      Every argument is checked before anything is enqueued: after an error return the array holds what the last
+ *      successful call left in it.  The looked-up address is kept per device for the life of the process; a program
+ *      that calls cudaDeviceReset must not use this entry point on that device afterwards. */
 int64_t fpt_rope_static_table_capacity(void);
 int fpt_rope_apply_static_table(void* q_out, void* k_out, const void* q, const void* k, const void* phase_increments,
                                 int64_t batch, int64_t seq, int64_t q_heads, int64_t k_heads, int64_t head_dim,
@@ -291,6 +302,15 @@ int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void
  *      b an MN-major shared-memory operand).  status: one zero-initialised device word; non-zero afterwards means a
  *      bounded device-side wait ran out. */
 int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* status, fpt_stream_t stream);
+
+/* ---- diagnostic: the bounded device-side wait of the attention kernels, run on a barrier nobody arrives on
+ *      (no counterpart in the reference).  One thread waits at most limit_ns (1 us .. 1 ms) on an mbarrier of its own;
+ *      the kernel uses no TMA, no tensor memory and no tensor-core operation, so nothing is in flight when it gives up.
+ *      status: one device word, as in the attention entry points: zero before the call; afterwards 0x80000000 | where.
+ *      A call whose status word is already non-zero does not wait at all (the attention kernels' behaviour for blocks
+ *      that start after a timeout).  report: three device words: [0] 1 = timed out, 2 = skipped, 3 = wait succeeded;
+ *      [1], [2] = nanoseconds waited (low, high). */
+int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int where, fpt_stream_t stream);
 
 /* ---- launch knobs for benchmarks (process-wide; defaults are the measured-best values) -------- */
 /* key "blocks_per_sm": persistent-grid cap (0 = one block per tile); key "streaming": -1 auto, 0, 1;

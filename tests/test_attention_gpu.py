@@ -56,6 +56,37 @@ def bits(t):
     return t.detach().contiguous().view(torch.int16).cpu().numpy().view(np.uint16)
 
 
+UNNORMALISED = (1, 4)     # sigmoid attention (polynomial, special-function unit): O = P V without a row sum
+
+
+class Tolerance:
+    """Accumulates |got - want| over the (batch, head) blocks of one case and judges it by the mode.
+
+    Soft-max modes: 2e-2 max-abs on the bf16 output (rows are convex combinations of V, so values are of order one).
+    Sigmoid modes: the output is a plain sum with probabilities of order 1/n, its size shrinks like 1/sqrt(n) (standard
+    deviation 0.12 at 512 keys, 0.02 at 16384), so an absolute bound says nothing there: per block the largest error
+    must stay within 2e-2 of the block's largest value, and over the whole case the mean error within 5e-3 of the mean
+    magnitude."""
+
+    def __init__(self, mode):
+        self.unnormalised = mode in UNNORMALISED
+        self.worst_abs = self.worst_rel = self.sum_err = self.sum_ref = 0.0
+
+    def add(self, got, want):
+        err = np.abs(got.astype(np.float64) - want.astype(np.float64))
+        self.worst_abs = max(self.worst_abs, float(err.max()))
+        self.worst_rel = max(self.worst_rel, float(err.max()) / max(float(np.abs(want).max()), 1e-30))
+        self.sum_err += float(err.sum())
+        self.sum_ref += float(np.abs(want).sum())
+
+    def check(self, what=""):
+        if self.unnormalised:
+            assert self.worst_rel <= 2e-2, (what, "largest error relative to the block's largest value", self.worst_rel)
+            assert self.sum_err <= 5e-3 * self.sum_ref, (what, "relative mean error", self.sum_err / max(self.sum_ref, 1e-30))
+        else:
+            assert self.worst_abs <= 2e-2, (what, self.worst_abs)
+
+
 CASES = [
     # (B, S, Hq, Hk, mode, causal, softcap, log2_n)
     (1, 128, 1, 1, 2, False, 0.0, 12),
@@ -80,7 +111,8 @@ CASES = [
 
 @pytest.mark.parametrize("case", CASES)
 def test_attention_matches_fp32_oracle(fpt, cuda, oracle, case):
-    """Output within 2e-2 max-abs of the fp32 CPU attention that uses the same polynomial score-mod."""
+    """Output against the fp32 CPU attention that uses the same score-mod: 2e-2 max-abs for the soft-max modes, bounds
+    relative to the signal for the unnormalised sigmoid modes (class Tolerance)."""
     import torch
     B, S, Hq, Hk, mode, causal, softcap, log2_n = case
     D = 128
@@ -95,14 +127,13 @@ def test_attention_matches_fp32_oracle(fpt, cuda, oracle, case):
     assert not torch.isnan(out.float()).any()
     qb, kb, vb = bits(q), bits(k), bits(v)
     rng = np.random.default_rng(7)
-    worst = 0.0
+    tol = Tolerance(mode)
     for b in range(B):
         for h in range(Hq):
             rows = np.arange(S) if (b == 0 and h in (0, Hq - 1)) else np.sort(rng.choice(S, size=min(S, 32), replace=False))
             want = oracle.attention_rows(qb, kb, vb, b, h, rows, mode, causal, scale, softcap, log2_n)
-            got = out[b, rows, h, :].float().cpu().numpy()
-            worst = max(worst, float(np.abs(got - want).max()))
-    assert worst < 2e-2, worst
+            tol.add(out[b, rows, h, :].float().cpu().numpy(), want)
+    tol.check(case)
 
 
 def test_attention_accepts_head_major_layout(fpt, cuda):
@@ -180,7 +211,7 @@ FULL_SIZE = [
 @pytest.mark.parametrize("case", FULL_SIZE, ids=[c[0] for c in FULL_SIZE])
 def test_full_size_workloads_by_sampled_rows_and_properties(fpt, cuda, oracle, case):
     """At the benchmark's sizes the oracle cannot redo everything, but a row of attention costs it only S x D: sampled
-    rows of sampled heads against the fp32 oracle (2e-2), plus two properties that need no oracle.  Causal: rows before
+    rows of sampled heads against the fp32 oracle (bounds of class Tolerance), plus two properties that need no oracle.  Causal: rows before
     position p do not change by a bit when keys and values from p on are replaced.  Both modes: the output is linear in
     V, so O(V) + O(V') agrees with O(V + V') up to the bf16 roundings of the three outputs."""
     import torch
@@ -196,13 +227,13 @@ def test_full_size_workloads_by_sampled_rows_and_properties(fpt, cuda, oracle, c
     assert status == 0 and not torch.isnan(out.float()).any()
     qb, kb, vb = bits(q), bits(k), bits(v)
     rng = np.random.default_rng(11)
-    worst = 0.0
-    for b, h in ((0, 0), (B - 1, Hq - 1), (B // 2, Hq // 2 + 1)):
-        rows = np.sort(np.concatenate([[0, 1, 127, 128, S - 129, S - 1], rng.choice(S, size=10, replace=False)]))
-        want = oracle.attention_rows(qb, kb, vb, b, h, rows, mode, causal, scale, softcap, log2_n)
-        got = out[b, rows, h, :].float().cpu().numpy()
-        worst = max(worst, float(np.abs(got - want).max()))
-    assert worst <= 2e-2, worst
+    tol = Tolerance(mode)
+    for b in range(B):
+        for h in range(0, Hq, 8):      # every 8th head of every batch entry, 64 rows each (a row costs the oracle S x D)
+            rows = np.unique(np.concatenate([[0, 1, 127, 128, S - 129, S - 1], rng.choice(S, size=58, replace=False)]))
+            want = oracle.attention_rows(qb, kb, vb, b, h, rows, mode, causal, scale, softcap, log2_n)
+            tol.add(out[b, rows, h, :].float().cpu().numpy(), want)
+    tol.check(case[0])
     if causal:
         cut = S // 2 + 37
         k2, v2 = k.clone(), v.clone()
@@ -220,7 +251,7 @@ def test_full_size_workloads_by_sampled_rows_and_properties(fpt, cuda, oracle, c
     assert st1 == 0 and st2 == 0
     # the sum of V itself is rounded to bf16 (relative 2^-9 per element) before it is averaged by the probabilities
     residual = (out.float() + out_other.float() - out_sum.float()).abs().max()
-    assert float(residual) < 3e-2 * max(1.0, float(out_sum.float().abs().max())), float(residual)
+    assert float(residual) < 3e-2 * float(out_sum.float().abs().max()), float(residual)
 
 
 @pytest.mark.parametrize("freq", [8, 32])
@@ -314,3 +345,35 @@ def test_softcap_layouts_and_saturating_scores(fpt, cuda, oracle, softcap, gain)
             for out, _ in results:
                 err = float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max())
                 assert err < 2e-2, (softcap, gain, causal, h, err)
+
+
+def test_bounded_wait_runs_out_and_later_blocks_skip(fpt, cuda):
+    """The bounded mbarrier wait of the attention kernels, on a barrier nobody arrives on (one thread, no TMA, no tensor
+    memory, nothing in flight): it gives up after the limit, records 0x80000000 | where in the status word, and a block
+    started afterwards finds the word set and does not wait at all."""
+    import torch
+    status = torch.zeros(1, dtype=torch.int32, device=cuda)
+    report = torch.zeros(3, dtype=torch.int32, device=cuda)
+    limit_ns, where = 200_000, 7
+    fpt.call("fpt_selftest_bounded_wait", status.data_ptr(), report.data_ptr(), limit_ns, where, stream())
+    torch.cuda.synchronize()
+    r = report.cpu().numpy().view(np.uint32)
+    waited = int(r[1]) | (int(r[2]) << 32)
+    assert int(status.item()) & 0xFFFFFFFF == 0x80000000 | where
+    assert int(r[0]) == 1, "the wait must have timed out"
+    assert limit_ns <= waited < 50 * limit_ns, waited       # gave up after the limit, and soon after it
+    report.zero_()
+    fpt.call("fpt_selftest_bounded_wait", status.data_ptr(), report.data_ptr(), limit_ns, where + 1, stream())
+    torch.cuda.synchronize()
+    r = report.cpu().numpy().view(np.uint32)
+    assert int(r[0]) == 2 and int(r[1]) == 0, "a block that starts after a timeout must skip its work at once"
+    assert int(status.item()) & 0xFFFFFFFF == 0x80000000 | where    # the first report is kept
+    for bad in (0, 999, 1_000_001):
+        assert fpt.load().fpt_selftest_bounded_wait(status.data_ptr(), report.data_ptr(), bad, where, stream()) == -2
+    # the context is intact: a tensor-core self-test right afterwards passes
+    a = torch.randn(128, 128, device=cuda).to(torch.bfloat16)
+    c = torch.empty(128, 128, device=cuda)
+    ok = torch.zeros(1, dtype=torch.int32, device=cuda)
+    fpt.call("fpt_selftest_umma", c.data_ptr(), a.data_ptr(), a.data_ptr(), 0, ok.data_ptr(), stream())
+    torch.cuda.synchronize()
+    assert int(ok.item()) == 0 and float((c - a.float() @ a.float().t()).abs().max()) < 1e-3 * float(c.abs().max())

@@ -147,3 +147,30 @@ def test_attention_module_trains(cuda):
     sigmoid = fa4.build_fa4_module(fa4.b3_component_configs()["polynomial"], head_dim=D, sequence_length=4096).to(cuda)
     sigmoid.q_norm = sigmoid.k_norm = None        # compare the attention itself; the norms are plain torch modules
     check(sigmoid, 1, 1, 1, 4096, orc.ATTN_SIGMOID_B3, 0.0, 12)
+
+
+def test_device_timeout_reported_by_the_kernel_raises_in_python(cuda):
+    """A non-zero status word means a bounded device-side wait ran out and the outputs are invalid; the wrapper must
+    turn it into an exception instead of returning them.  The word is set by hand here (blocks that find it set do no
+    work, so nothing waits and nothing faults); after the exception the word is clear again and calls succeed."""
+    import torch
+    from fast_polynomial_transcendentals_b200.sfu_repro import fa4
+    q = torch.randn(1, 256, 2, 128, device=cuda).to(torch.bfloat16)
+    out, lse = fa4._b200_flash_attn_fwd(q, q, q, causal=True)
+    fa4.check_attention_status(cuda)                      # a clean run raises nothing
+    state = fa4._status_for(cuda)
+    state.word.fill_(-2147483648 + 5)                     # 0x80000005: "timed out at waiting point 5"
+    fa4._b200_flash_attn_fwd(q, q, q, causal=True)
+    with pytest.raises(RuntimeError, match="device-side wait.*0x80000005"):
+        fa4.check_attention_status(cuda)
+    assert int(state.word.item()) == 0
+    again, _ = fa4._b200_flash_attn_fwd(q, q, q, causal=True)
+    fa4.check_attention_status(cuda)
+    assert torch.equal(again, out)
+    # without an explicit check the error surfaces at the next attention call made after the failed launch finished
+    state.word.fill_(-2147483648 + 6)
+    fa4._b200_flash_attn_fwd(q, q, q, causal=True)
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="0x80000006"):
+        fa4._b200_flash_attn_bwd(q, q, q, out, out, lse, None, True, 0.0)
+    fa4.check_attention_status(cuda)

@@ -60,6 +60,41 @@ def test_b3_all_patterns_and_f32_scores(fpt, cuda, oracle):
     assert_bits_equal(to_bits(grad), want_g, "b3 grad from f32")
 
 
+@pytest.mark.parametrize("log2_n", [12, 14])
+def test_b3_evaluation_order_of_the_attention_kernels_all_patterns(fpt, cuda, oracle, log2_n):
+    """The attention kernels run the cubic in another instruction order (both rows, one select afterwards, no lower
+    clamp, floor inside the last multiply-add).  Every bf16 pattern: probabilities equal the oracle bit for bit; the
+    coupled gradient too, except at -inf, where the unclamped derivative factor is +inf and 0 * inf gives NaN
+    (the kernels never meet that lane: they convert fp32 scores with saturation, checked below)."""
+    import torch
+    allbits = np.arange(65536, dtype=np.uint16)
+    x = to_device(allbits, "bf16", cuda)
+    want_p, want_g = oracle.b3_direct(allbits, log2_n, with_grad=True)
+    only = torch.empty_like(x)
+    fpt.call("fpt_b3_sigmoid_direct_variant", only.data_ptr(), None, x.data_ptr(), x.numel(), 0, log2_n, 1, stream())
+    prob, grad = torch.empty_like(x), torch.empty_like(x)
+    fpt.call("fpt_b3_sigmoid_direct_variant", prob.data_ptr(), grad.data_ptr(), x.data_ptr(), x.numel(), 0, log2_n, 1, stream())
+    torch.cuda.synchronize()
+    assert_bits_equal(to_bits(only), want_p, "b3 late select, value only", allbits)
+    assert_bits_equal(to_bits(prob), want_p, "b3 late select, value", allbits)
+    got_g = to_bits(grad)
+    differs = np.nonzero(got_g != want_g)[0]
+    assert differs.tolist() == [0xFF80], [hex(i) for i in differs[:16]]
+    assert want_g[0xFF80] == 0x0000 and (got_g[0xFF80] & 0x7FFF) > 0x7F80      # +0 in the deployed order, NaN here
+    # fp32 scores, the form in which the attention backward meets the evaluator: specials included, no lane differs
+    rng = np.random.default_rng(11)
+    sf = (rng.standard_normal(200003) * 4).astype(np.float32)
+    sf[:10] = [np.nan, np.inf, -np.inf, -0.0, 0.0, -3.4e38, 3.4e38, -6.0, 6.0, 1.25]
+    s = torch.from_numpy(sf).to(cuda)
+    prob = torch.empty(sf.size, dtype=torch.bfloat16, device=cuda)
+    grad = torch.empty_like(prob)
+    fpt.call("fpt_b3_sigmoid_direct_variant", prob.data_ptr(), grad.data_ptr(), s.data_ptr(), s.numel(), 1, log2_n, 1, stream())
+    torch.cuda.synchronize()
+    want_p, want_g = oracle.b3_direct(sf, log2_n, with_grad=True)
+    assert_bits_equal(to_bits(prob), want_p, "b3 late select from f32")
+    assert_bits_equal(to_bits(grad), want_g, "b3 late select gradient from f32")
+
+
 # ---- exp2 ----------------------------------------------------------------------------------------
 
 def test_exp2_hinge_bit_exact_and_native_close(fpt, cuda, oracle):
@@ -117,6 +152,54 @@ def test_full_range_exp2_bit_exact_and_accurate(fpt, cuda, oracle, variant, boun
     x = torch.zeros(9, dtype=torch.float32, device=cuda)
     assert fpt.load().fpt_exp2_full_f32(x.data_ptr() + 4, x.data_ptr(), 4, variant, None) != 0   # misaligned
     assert fpt.load().fpt_exp2_full_f32(x.data_ptr(), x.data_ptr(), 4, 7, None) != 0              # unknown variant
+
+
+def test_exp2_error_metrics_equal_the_reference_benchmark(fpt, cuda):
+    """The reference's stand-alone exp2 benchmark (compiled from its own source by `make -C oracle ref`) prints, for a
+    fixed arithmetic input sequence, max-abs / max-rel / rms error of each evaluator against fp64 exp2 with nine
+    significant digits.  The same three figures computed from this library's kernels on the same 2^21 inputs must
+    print identically: a checksum over every output bit that reaches an error figure."""
+    import re
+    import subprocess
+    from pathlib import Path
+
+    import torch
+    binary = Path(__file__).resolve().parents[1] / "oracle" / "_ref" / "benchmark_exp2_pwl2"
+    if not binary.exists():
+        pytest.skip("oracle/_ref/benchmark_exp2_pwl2 not built")
+    printed = subprocess.run([str(binary)], capture_output=True, text=True, timeout=600, check=True).stdout
+    theirs = {}
+    for m in re.finditer(r"ERROR domain=(\S+) variant=(\S+) max_abs=(\S+) max_rel=(\S+) rmse=(\S+) samples=(\d+)", printed):
+        theirs[(m.group(1), m.group(2))] = m.groups()[2:]
+    pairs = 1 << 20
+
+    def metrics(got, x):
+        ref = np.exp2(x.astype(np.float64))
+        err = np.abs(got.astype(np.float64) - ref)
+        # the benchmark accumulates the squares in input order in a double; a pairwise sum may differ in the last
+        # digits, so the root-mean-square figure is compared to 1e-7 relative and the two maxima exactly
+        return "%.9g" % err.max(), "%.9g" % (err / np.abs(ref)).max(), float(np.sqrt(np.sum(err * err) / err.size)), str(err.size)
+
+    i = np.arange(2 * pairs, dtype=np.int64)
+    frac = ((i % 65521).astype(np.float32) / np.float32(65521.0)).astype(np.float16)
+    full = np.float32(-16.0) * ((i % 1048573).astype(np.float32) / np.float32(1048573.0))
+    x16 = torch.from_numpy(frac.view(np.int16)).to(cuda).view(torch.float16)
+    x32 = torch.from_numpy(full).to(cuda)
+    cases = []
+    for variant, name in ((1, "pwl2_hinge"),):     # the polynomial evaluators; the native rows are hardware approximations
+        out = torch.empty_like(x16)
+        fpt.call("fpt_exp2_fraction", out.data_ptr(), x16.data_ptr(), x16.numel(), variant, 1, stream())
+        cases.append((("fractional_h2", name), out.float().cpu().numpy(), frac.astype(np.float32)))
+    for variant, name in ((0, "degree3"), (1, "pwl2_hinge")):
+        out = torch.empty_like(x32)
+        fpt.call("fpt_exp2_full_f32", out.data_ptr(), x32.data_ptr(), x32.numel(), variant, stream())
+        cases.append((("full_f32", name), out.cpu().numpy(), full))
+    torch.cuda.synchronize()
+    for key, got, x in cases:
+        assert key in theirs, (key, sorted(theirs))
+        max_abs, max_rel, rms, count = metrics(got, x)
+        assert (max_abs, max_rel, count) == (theirs[key][0], theirs[key][1], theirs[key][3]), (key, max_abs, max_rel, theirs[key])
+        assert abs(rms / float(theirs[key][2]) - 1) < 1e-7, (key, rms, theirs[key][2])
 
 
 # ---- sin/cos -------------------------------------------------------------------------------------

@@ -28,22 +28,29 @@ def test_static_table_route_equals_the_allocating_route_twice(fpt, cuda):
     assert lib.fpt_rope_static_table_capacity() == 1 << 21
     g = torch.Generator(device=cuda)
     g.manual_seed(99)
-    # two different shapes back to back: the second call must not see anything left by the first
-    for (B, S, Hq, Hk, D), dtype, dt in (((2, 1024, 4, 2, 128), torch.float16, 0), ((1, 300, 3, 1, 64), torch.bfloat16, 1)):
+    # different shapes, dtypes and table programs back to back: a call must not see anything left by the one before;
+    # the third fills the fixed array to its last entry (16384 x 128 = 2^21)
+    cases = (((2, 1024, 4, 2, 128), torch.float16, 0, 0), ((1, 300, 3, 1, 64), torch.bfloat16, 1, 1),
+             ((1, 16384, 1, 1, 128), torch.float16, 0, 1), ((1, 512, 2, 2, 128), torch.bfloat16, 1, 0))
+    for (B, S, Hq, Hk, D), dtype, dt, table_kind in cases:
         inc = torch.from_numpy(increments(D).view(np.int32)).to(cuda)
         q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(dtype)
         k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(dtype)
         table = torch.empty(2, S, D // 2, dtype=torch.float16, device=cuda)
         want_q = torch.empty(B, Hq, S, D, dtype=dtype, device=cuda)
         want_k = torch.empty(B, Hk, S, D, dtype=dtype, device=cuda)
-        fpt.call("fpt_rope_table", table.data_ptr(), inc.data_ptr(), S, D // 2, 0, 0, stream)
+        fpt.call("fpt_rope_table", table.data_ptr(), inc.data_ptr(), S, D // 2, table_kind, 0, stream)
         fpt.call("fpt_rope_apply", want_q.data_ptr(), want_k.data_ptr(), q.data_ptr(), k.data_ptr(), table.data_ptr(),
                  B, S, Hq, Hk, D, 3, dt, stream)
         got_q = torch.full_like(want_q, float("nan"))
         got_k = torch.full_like(want_k, float("nan"))
-        fpt.call("fpt_rope_apply_static_table", got_q.data_ptr(), got_k.data_ptr(), q.data_ptr(), k.data_ptr(),
-                 inc.data_ptr(), B, S, Hq, Hk, D, 0, dt, stream)
         torch.cuda.synchronize()
+        free_before, _ = torch.cuda.mem_get_info(cuda)
+        fpt.call("fpt_rope_apply_static_table", got_q.data_ptr(), got_k.data_ptr(), q.data_ptr(), k.data_ptr(),
+                 inc.data_ptr(), B, S, Hq, Hk, D, table_kind, dt, stream)
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(cuda)
+        assert free_after == free_before, "the call must not take device memory from the driver"
         assert torch.equal(got_q.view(torch.int16), want_q.view(torch.int16))
         assert torch.equal(got_k.view(torch.int16), want_k.view(torch.int16))
 
@@ -56,3 +63,31 @@ def test_static_table_route_refuses_what_does_not_fit(fpt, cuda):
     status = lib.fpt_rope_apply_static_table(p, p, p, p, p, 1, too_long, 1, 1, 128, 0, 0, None)
     assert status == -9
     assert b"scratch" in lib.fpt_status_string(status)
+
+
+def test_static_table_route_checks_everything_before_it_enqueues(fpt, cuda):
+    """Calls with a null or misaligned tensor, no increments, or an unknown table program or dtype are refused with the
+    status of the failing check (the entry point runs every check of both of its steps before it enqueues the table
+    kernel), and a valid call afterwards gives the same bits as before them."""
+    import torch
+    lib = fpt.load()
+    stream = torch.cuda.current_stream().cuda_stream
+    B, S, H, D = 1, 256, 2, 128
+    inc = torch.from_numpy(increments(D).view(np.int32)).to(cuda)
+    other = torch.from_numpy(increments(D, theta=10000.0).view(np.int32)).to(cuda)
+    q = torch.randn(B, S, H, D, device=cuda).to(torch.float16)
+    out_q, out_k = torch.empty(B, H, S, D, dtype=torch.float16, device=cuda), torch.empty(B, H, S, D, dtype=torch.float16, device=cuda)
+    args = lambda qo, ko, qi, ki, params, kind=0, dt=0: (qo, ko, qi, ki, params, B, S, H, H, D, kind, dt, stream)
+    fpt.call("fpt_rope_apply_static_table", *args(out_q.data_ptr(), out_k.data_ptr(), q.data_ptr(), q.data_ptr(), inc.data_ptr()))
+    torch.cuda.synchronize()
+    first = out_q.clone()
+    ptr = q.data_ptr()
+    assert lib.fpt_rope_apply_static_table(*args(None, out_k.data_ptr(), ptr, ptr, other.data_ptr())) == -1       # null output
+    assert lib.fpt_rope_apply_static_table(*args(out_q.data_ptr(), out_k.data_ptr(), ptr + 2, ptr, other.data_ptr())) == -3  # misaligned q
+    assert lib.fpt_rope_apply_static_table(*args(out_q.data_ptr(), out_k.data_ptr(), ptr, ptr, None)) == -1      # no increments
+    assert lib.fpt_rope_apply_static_table(*args(out_q.data_ptr(), out_k.data_ptr(), ptr, ptr, other.data_ptr(), kind=2)) == -5
+    assert lib.fpt_rope_apply_static_table(*args(out_q.data_ptr(), out_k.data_ptr(), ptr, ptr, other.data_ptr(), dt=4)) == -5
+    torch.cuda.synchronize()
+    fpt.call("fpt_rope_apply_static_table", *args(out_q.data_ptr(), out_k.data_ptr(), q.data_ptr(), q.data_ptr(), inc.data_ptr()))
+    torch.cuda.synchronize()
+    assert torch.equal(out_q, first)
