@@ -54,6 +54,10 @@ SIGNATURES: dict[str, list] = {
     "fpt_attention_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _int, _vp, _vp],
+    "fpt_attention_bwd_routed": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
+                                 ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                                 ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _int, _int, _int,
+                                 _vp, _vp],
     "fpt_attention_fwd_routed": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64),
                                  ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int,
                                  ctypes.c_float, ctypes.c_float, _int, _int, _int, _vp, _vp],

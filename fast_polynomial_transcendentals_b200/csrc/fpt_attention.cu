@@ -15,6 +15,9 @@
 //   mode 0  soft-capped softmax: s' = cap * tanh_D4(bf16(s*scale/cap)), then exp2 / running max / running sum
 //   mode 1  sigmoid attention:   p = direct piecewise cubic of bf16(s*scale) (B3), no normalisation, O = P V
 //   mode 2  plain softmax
+// and their native twins on the special-function unit, the controls every polynomial number is compared with:
+//   mode 3  soft-capped softmax with tanh.approx.f32 on the fp32 score (same layouts as mode 0)
+//   mode 4  sigmoid attention with p = rcp(1 + ex2(log2 n - s*scale*log2 e)), two special-function operations per key
 // Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
 #include <type_traits>
 
@@ -60,6 +63,7 @@ struct AttnParams {
     int mode, causal;
     int rows_fastest;    // grid = (row blocks, heads, batch) instead of (heads, row blocks, batch)
     float scale, softcap;
+    float sigmoid_mul, sigmoid_add;   // native sigmoid: exponent = score * sigmoid_mul + sigmoid_add (log2 units)
     uint32_t* status;
     ProgramWords tanh;   // bf16 TANH_FWD_D4
     B3Words b3;
@@ -91,6 +95,21 @@ struct AttnParams {
 enum : uint32_t { kWhereQ = 1, kWhereKEmpty, kWhereVEmpty, kWhereKFull, kWhereVFull, kWherePFull, kWhereSFull, kWherePvDone };
 
 __device__ __forceinline__ float ex2(float x) { return mufu_ex2(x); }
+
+// mode families: the native twins share everything but the score-mod arithmetic with the polynomial modes
+constexpr bool is_sigmoid(int mode) { return mode == 1 || mode == 4; }
+constexpr bool is_softcap(int mode) { return mode == 0 || mode == 3; }
+
+// native sigmoid of a pair of raw scores: two special-function operations per key (ex2, rcp)
+__device__ __forceinline__ uint32_t native_sigmoid_pair(uint32_t s0, uint32_t s1, float mul, float add) {
+    float a0, a1;
+    asm("{\n\t.reg .b64 v, s, t, r;\n\t"
+        "mov.b64 v, {%2, %3};\n\tmov.b64 s, {%4, %4};\n\tmov.b64 t, {%5, %5};\n\t"
+        "fma.rn.f32x2 r, v, s, t;\n\tmov.b64 {%0, %1}, r;\n\t}"
+        : "=f"(a0), "=f"(a1) : "r"(s0), "r"(s1), "f"(mul), "f"(add));
+    const float p0 = mufu_rcp(1.0f + mufu_ex2(a0)), p1 = mufu_rcp(1.0f + mufu_ex2(a1));
+    return Sfu<kBf16>::pack(p0, p1);
+}
 
 __device__ __forceinline__ float max3(float a, float b, float c) {
     float d;
@@ -354,10 +373,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             const int limit = min(p.causal ? row : 0x7fffffff, p.seq - 1);
             const int col0 = j * kTileN + 64 * half;
             uint32_t pw[32];
-            if constexpr (MODE == 1) {
+            if constexpr (is_sigmoid(MODE)) {
 #pragma unroll
-                for (int w = 0; w < 32; ++w)
-                    pw[w] = b3_direct_select_late(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], p.scale), p.b3);
+                for (int w = 0; w < 32; ++w) {
+                    if constexpr (MODE == 1) pw[w] = b3_direct_select_late(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], p.scale), p.b3);
+                    else pw[w] = native_sigmoid_pair(sr[2 * w], sr[2 * w + 1], p.sigmoid_mul, p.sigmoid_add);
+                }
                 if (diagonal) {
 #pragma unroll
                     for (int w = 0; w < 32; ++w) {
@@ -375,9 +396,18 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 // One pair of keys: tanh polynomial (ALU and FMA pipes), then the exponential (special-function unit), back
                 // to back, so that the two bounds overlap instead of adding up.
                 auto key_pair = [&](int w, auto masked) {
-                    const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
+                    float t0, t1;
+                    if constexpr (MODE == 3) {    // native twin: both the tanh and the exponential on the special-function unit
+                        mul2(__uint_as_float(sr[2 * w]), __uint_as_float(sr[2 * w + 1]), softcap_in, softcap_in, t0, t1);
+                        t0 = mufu_tanh(t0);
+                        t1 = mufu_tanh(t1);
+                    } else {
+                        const uint32_t t = eval_program<kBf16, kOddSat, 4>(scale_pack_bf16x2(sr[2 * w], sr[2 * w + 1], softcap_in), p.tanh);
+                        t0 = __uint_as_float(t << 16);
+                        t1 = __uint_as_float(t & 0xffff0000u);
+                    }
                     float a0, a1, e0, e1;
-                    fma_f32x2(__uint_as_float(t << 16), __uint_as_float(t & 0xffff0000u), mul, -reference, a0, a1);
+                    fma_f32x2(t0, t1, mul, -reference, a0, a1);
                     if (EMU > 0 && ((half * 32 + w) % (EMU > 0 ? EMU / 2 : 1)) < 2) {
                         exp2_full_x2<EK>(a0, a1, e0, e1);
                     } else {
@@ -409,7 +439,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
         if (ok && n > 0) {
             float inv = 1.0f, total = 1.0f;
-            if constexpr (MODE != 1) {       // the two column halves add their sums
+            if constexpr (!is_sigmoid(MODE)) {       // the two column halves add their sums
                 sm.xchg[s][half][row_in_tile] = sum_lo + sum_hi;
                 ok = slot_sync(0);
                 total = sm.xchg[s][0][row_in_tile] + sm.xchg[s][1][row_in_tile];
@@ -437,7 +467,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         if (real_row) dst[q4] = w;
                     }
                 }
-                if (MODE != 1 && p.lse && real_row && half == 0)
+                if (!is_sigmoid(MODE) && p.lse && real_row && half == 0)
                     p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (reference + log2f(total)) * 0.6931471805599453f;
             }
         }
@@ -483,15 +513,19 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 __syncwarp();
                 if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
             };
-            if constexpr (MODE == 1) {
+            if constexpr (is_sigmoid(MODE)) {
 #pragma unroll
                 for (int half = 0; half < 2; ++half) {
                     uint32_t pw[32];
 #pragma unroll
                     for (int w = 0; w < 32; ++w) {
                         const int i = half * 32 + w;
-                        const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
-                        pw[w] = b3_direct_select_late(x, p.b3);
+                        if constexpr (MODE == 1) {
+                            const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
+                            pw[w] = b3_direct_select_late(x, p.b3);
+                        } else {
+                            pw[w] = native_sigmoid_pair(sr[2 * i], sr[2 * i + 1], p.sigmoid_mul, p.sigmoid_add);
+                        }
                     }
                     if (diagonal) {  // keys beyond the diagonal contribute nothing; a branch of its own, taken by
                                      // the whole slot at once, so that the other tiles carry no compare / select
@@ -506,8 +540,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     hand_over(half, pw);
                 }
             } else {
-                // val[i] * mul is the score in log2 units: val = tanh polynomial (mode 0) or the raw score (mode 2).
-                const float mul = MODE == 0 ? softcap_out : plain_scale;
+                // val[i] * mul is the score in log2 units: val = tanh (modes 0 and 3) or the raw score (mode 2).
+                const float mul = is_softcap(MODE) ? softcap_out : plain_scale;
                 if constexpr (MODE == 0) {
 #pragma unroll
                     for (int i = 0; i < kTileN / 2; ++i) {
@@ -515,6 +549,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         const uint32_t t = eval_program<kBf16, kOddSat, 4>(x, p.tanh);
                         sr[2 * i] = t << 16;              // bf16 -> fp32 is a shift
                         sr[2 * i + 1] = t & 0xffff0000u;
+                    }
+                } else if constexpr (MODE == 3) {
+#pragma unroll
+                    for (int i = 0; i < kTileN / 2; ++i) {
+                        float x0, x1;
+                        mul2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), softcap_in, softcap_in, x0, x1);
+                        sr[2 * i] = __float_as_uint(mufu_tanh(x0));
+                        sr[2 * i + 1] = __float_as_uint(mufu_tanh(x1));
                     }
                 }
                 if (diagonal) {
@@ -580,7 +622,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             ok = mbar_wait(&sm.pv_done[s], uint32_t(n - 1) & 1u, abort_flag, p.status, kWherePvDone);
             if (ok) {
                 tc_fence_after_sync();
-                const float inv = MODE == 1 ? 1.0f : 1.0f / row_sum;
+                const float inv = is_sigmoid(MODE) ? 1.0f : 1.0f / row_sum;
                 const bool real_row = row < p.seq;       // rows of a ragged last tile beyond the sequence are dropped
                 uint16_t* out_row = p.out + int64_t(b) * p.out_stride_b + int64_t(row) * p.out_stride_s +
                                     int64_t(hq) * p.out_stride_h;
@@ -600,7 +642,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         if (real_row) dst[q4] = w;
                     }
                 }
-                if (MODE != 1 && p.lse && real_row)
+                if (!is_sigmoid(MODE) && p.lse && real_row)
                     p.lse[(int64_t(b) * p.q_heads + hq) * p.seq + row] = (row_max + log2f(row_sum)) * 0.6931471805599453f;
             }
         }
@@ -627,14 +669,18 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
     if (head_dim != kHeadDim || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
     if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
-    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
-    if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
-    if (mode == FPT_ATTN_SIGMOID_DIRECT && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
+    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SIGMOID_NATIVE) return FPT_ERR_BAD_ENUM;
+    const bool softcap_family = mode == FPT_ATTN_SOFTCAP_TANH || mode == FPT_ATTN_SOFTCAP_NATIVE;
+    const bool sigmoid_family = mode == FPT_ATTN_SIGMOID_DIRECT || mode == FPT_ATTN_SIGMOID_NATIVE;
+    if (softcap_family && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
+    if (sigmoid_family && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
     if (exp2_emu_freq != 0 && exp2_emu_freq != 8 && exp2_emu_freq != 12 && exp2_emu_freq != 16 && exp2_emu_freq != 32)
         return FPT_ERR_BAD_ENUM;
-    if (mode == FPT_ATTN_SIGMOID_DIRECT && exp2_emu_freq != 0) return FPT_ERR_BAD_ENUM;   // no exponential to route
-    if (exp2_emu_backend != FPT_EXP2_FULL_D3 && exp2_emu_backend != FPT_EXP2_FULL_PWL2) return FPT_ERR_BAD_ENUM;
-    if (exp2_emu_backend == FPT_EXP2_FULL_PWL2 && exp2_emu_freq != 0 && mode != FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
+    // routing exists where an exponential exists and a polynomial is asked for: not in the sigmoid modes, not in the
+    // all-native soft-cap twin
+    if ((sigmoid_family || mode == FPT_ATTN_SOFTCAP_NATIVE) && exp2_emu_freq != 0) return FPT_ERR_BAD_ENUM;
+    if (exp2_emu_backend < FPT_EXP2_FULL_D3 || exp2_emu_backend > FPT_EXP2_FULL_PWL2_SAFE_F16) return FPT_ERR_BAD_ENUM;
+    if (exp2_emu_backend != FPT_EXP2_FULL_D3 && exp2_emu_freq != 0 && mode != FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
     if (reinterpret_cast<uintptr_t>(out) & 15u) return FPT_ERR_MISALIGNED;
     for (int i = 0; i < 3; ++i)
         if ((out_strides[i] * 2) & 15) return FPT_ERR_MISALIGNED;
@@ -666,6 +712,8 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     if (!tanh_row || tanh_row->shape != kOddSat) return FPT_ERR_UNKNOWN_PROGRAM;
     p.tanh = program_words(*tanh_row);
     p.b3 = b3_words(mode == FPT_ATTN_SIGMOID_DIRECT ? log2_n : 12);
+    p.sigmoid_mul = -scale * kLog2e;          // 1 / (1 + 2^(log2 n - s*scale*log2 e)) = sigmoid(s*scale - ln n)
+    p.sigmoid_add = float(log2_n);
 
     const size_t smem = sizeof(AttnSmem) + 1024;
     static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory budget");
@@ -687,9 +735,12 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     // since its tanh and exponential run back to back per key pair).  The sigmoid mode also qualifies but measures no
     // faster with it (0.98..1.0x), so it keeps one thread per row unless the tuning key asks for the split layout.
     const int split_tuning = fpt::tuning_attention_split();
-    const bool split = mode == FPT_ATTN_SOFTCAP_TANH && softcap * kLog2e <= kFixedReferenceLimit && split_tuning >= 1;
+    const bool split = softcap_family && softcap * kLog2e <= kFixedReferenceLimit && split_tuning >= 1;
     if (mode == FPT_ATTN_SIGMOID_DIRECT)
         return split_tuning >= 2 ? launch(attention_fwd_kernel<1, 0, true>, kThreadsSplit) : launch(attention_fwd_kernel<1, 0, false>, kThreads);
+    if (mode == FPT_ATTN_SIGMOID_NATIVE) return launch(attention_fwd_kernel<4, 0, false>, kThreads);
+    if (mode == FPT_ATTN_SOFTCAP_NATIVE)
+        return split ? launch(attention_fwd_kernel<3, 0, true>, kThreadsSplit) : launch(attention_fwd_kernel<3, 0, false>, kThreads);
     const bool softcap_mode = mode == FPT_ATTN_SOFTCAP_TANH;
     if (softcap_mode && split) {
         switch (exp2_emu_freq) {
@@ -700,14 +751,20 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
             default: return launch(attention_fwd_kernel<0, 32, true>, kThreadsSplit);
         }
     }
-    if (!softcap_mode && exp2_emu_backend == FPT_EXP2_FULL_PWL2) {
+    // plain soft-max with a routed software exponential other than the cubic
+    auto routed_softmax = [&](auto kind) {
+        constexpr int EK = decltype(kind)::value;
         switch (exp2_emu_freq) {
-            case 0: break;
-            case 8: return launch(attention_fwd_kernel<2, 8, false, kExp2FullPwl2>, kThreads);
-            case 12: return launch(attention_fwd_kernel<2, 12, false, kExp2FullPwl2>, kThreads);
-            case 16: return launch(attention_fwd_kernel<2, 16, false, kExp2FullPwl2>, kThreads);
-            default: return launch(attention_fwd_kernel<2, 32, false, kExp2FullPwl2>, kThreads);
+            case 8: return launch(attention_fwd_kernel<2, 8, false, EK>, kThreads);
+            case 12: return launch(attention_fwd_kernel<2, 12, false, EK>, kThreads);
+            case 16: return launch(attention_fwd_kernel<2, 16, false, EK>, kThreads);
+            default: return launch(attention_fwd_kernel<2, 32, false, EK>, kThreads);
         }
+    };
+    if (!softcap_mode && exp2_emu_freq != 0) {
+        if (exp2_emu_backend == FPT_EXP2_FULL_PWL2) return routed_softmax(IC<kExp2FullPwl2>{});
+        if (exp2_emu_backend == FPT_EXP2_FULL_D2_SAFE) return routed_softmax(IC<kExp2FullD2Safe>{});
+        if (exp2_emu_backend == FPT_EXP2_FULL_PWL2_SAFE_F16) return routed_softmax(IC<kExp2FullPwl2SafeF16>{});
     }
     switch (exp2_emu_freq) {
         case 0: return softcap_mode ? launch(attention_fwd_kernel<0, 0, false>, kThreads) : launch(attention_fwd_kernel<2, 0, false>, kThreads);

@@ -63,6 +63,7 @@ struct BwdParams {
     float score_to_log2;   // scale * log2(e): raw score -> log2-domain score (plain softmax)
     float score_to_tanh;   // scale / softcap: raw score -> tanh argument
     float tanh_to_log2;    // softcap * log2(e): tanh value -> log2-domain score
+    float sigmoid_mul, sigmoid_add;   // native sigmoid: p = 1 / (1 + 2^(score * sigmoid_mul + sigmoid_add))
     uint32_t tanh_dw[4];   // derivative of the tanh program as packed bf16 words: d0 + d1 t + d2 t^2 + d3 t^3
     uint32_t* status;
     ProgramWords tanh;
@@ -142,9 +143,11 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) { return Sfu<k
 // One pair of columns of one row: raw scores s0, s1 and dP values d0, d1 -> bf16x2 words of P and of dS (the factor
 // `scale` common to every dS is applied once, in the epilogue).
 //   l0, l1: lse * log2(e) of the two (row, column) positions' query;  t0, t1: their delta;  m0, m1: masked out
-template <int MODE, int GRAD>
+//   routed: this pair takes the software exponential EK instead of the special-function unit (plain soft-max only)
+template <int MODE, int GRAD, int EK>
 __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s1, float d0, float d1, float l0, float l1,
-                                           float t0, float t1, bool m0, bool m1, uint32_t& p_word, uint32_t& ds_word) {
+                                           float t0, float t1, bool m0, bool m1, bool routed, uint32_t& p_word,
+                                           uint32_t& ds_word) {
     // fp32 steps run two lanes per instruction (mul2 / sub2 / fma2): these loops are bound by issue slots
     if constexpr (MODE == 1) {
         float x0, x1;
@@ -159,11 +162,29 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         if (m1) { pr &= 0x0000ffffu; g1 = 0.0f; }
         p_word = pr;
         ds_word = pack_bf16(g0, g1);
+    } else if constexpr (MODE == 4) {
+        // native twin of the direct cubic: p = sigmoid(score*scale - ln n) through ex2 and rcp, dS = dP p (1 - p)
+        float a0, a1;
+        fma2(s0, s1, p.sigmoid_mul, p.sigmoid_mul, p.sigmoid_add, p.sigmoid_add, a0, a1);
+        float p0 = mufu_rcp(1.0f + ex2f(a0)), p1 = mufu_rcp(1.0f + ex2f(a1));
+        if (m0) p0 = 0.0f;
+        if (m1) p1 = 0.0f;
+        float g0, g1;
+        fma2(-p0, -p1, p0, p1, p0, p1, g0, g1);          // p - p^2
+        mul2(g0, g1, d0, d1, g0, g1);
+        p_word = pack_bf16(p0, p1);
+        ds_word = pack_bf16(g0, g1);
     } else if constexpr (MODE == 2) {
         const float c = p.score_to_log2;
         float a0, a1, e0, e1;
         fma2(s0, s1, c, c, -l0, -l1, a0, a1);
-        float p0 = ex2f(a0), p1 = ex2f(a1);
+        float p0, p1;
+        if (routed) {
+            exp2_full_x2<EK>(a0, a1, p0, p1);
+        } else {
+            p0 = ex2f(a0);
+            p1 = ex2f(a1);
+        }
         if (m0) p0 = 0.0f;
         if (m1) p1 = 0.0f;
         p_word = pack_bf16(p0, p1);
@@ -174,6 +195,22 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         const float in = p.score_to_tanh, out = p.tanh_to_log2;
         float x0, x1;
         mul2(s0, s1, in, in, x0, x1);
+        if constexpr (MODE == 3) {
+            // native twin: tanh on the special-function unit, derivative 1 - t^2 of its value
+            const float th0 = mufu_tanh(x0), th1 = mufu_tanh(x1);
+            float a0, a1, g0, g1, e0, e1;
+            fma2(th0, th1, out, out, -l0, -l1, a0, a1);
+            float p0 = ex2f(a0), p1 = ex2f(a1);
+            if (m0) p0 = 0.0f;
+            if (m1) p1 = 0.0f;
+            fma2(-th0, -th1, th0, th1, 1.0f, 1.0f, g0, g1);
+            p_word = pack_bf16(p0, p1);
+            sub2(d0, d1, t0, t1, e0, e1);
+            mul2(p0, p1, e0, e1, e0, e1);
+            mul2(e0, e1, g0, g1, e0, e1);
+            ds_word = pack_bf16(e0, e1);
+            return;
+        }
         const uint32_t x = pack_bf16(x0, x1);
         // The saturating odd program written out (the same operations in the same order as eval_program<kBf16, kOddSat,
         // 4>), because its clamped argument c and its unsigned result also feed the derivative below.
@@ -225,11 +262,15 @@ struct Cols {
 
 // GRAD (soft-capped mode only): 0 the analytical derivative of the tanh polynomial, 1 the identity 1 - t^2; a template
 // parameter because the choice sits inside the per-pair arithmetic.
-template <int MODE, int WHICH, int GRAD = 0>
+// EMU, EK (plain soft-max only): routing frequency and kind of the software exponential, as in the forward: four of
+// every EMU columns of a score-mod warp's 64 take exp2_full_x2<EK> on the FMA pipe (reference: exp2_emu_freq_bwd,
+// src/sfu_repro/fa4.py:724-752).
+template <int MODE, int WHICH, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                      const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                      const BwdParams p) {
+    constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;    // no normalisation: neither lse nor delta
     extern __shared__ uint8_t smem_raw[];
     BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -305,7 +346,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 const int g = WHICH == 0 ? 0 : t / per_head;
                 const int r0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile;
                 const int sh = stream_head0 + g;
-                const uint32_t vec_bytes = WHICH == 1 && MODE != 1 ? 2u * kTile * 4u : 0u;
+                const uint32_t vec_bytes = WHICH == 1 && !kSigmoidMode ? 2u * kTile * 4u : 0u;
                 mbar_arrive_expect_tx(&sm.uw_full[st], 2 * kTileB + vec_bytes);
                 tma_load_4d(sm.u[st], &map_u, &sm.uw_full[st], 0, r0, sh, b);
                 tma_load_4d(sm.u[st] + kPanelB, &map_u, &sm.uw_full[st], 64, r0, sh, b);
@@ -419,7 +460,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
         const uint32_t t_s = tmem + lane_base + kColS + uint32_t(64 * half);
         float row_lse2 = 0.0f, row_delta = 0.0f;
-        if (WHICH == 0 && MODE != 1) {
+        if (WHICH == 0 && !kSigmoidMode) {
             const int64_t off = (int64_t(b) * p.q_heads + head) * seq_pad + row0 + r;
             row_lse2 = p.lse2[off];
             row_delta = p.delta[off];
@@ -447,7 +488,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ld_done);
             FPT_BTRACE(half, 3);
-            if (WHICH == 1 && MODE != 1)   // the per-query vectors arrived on this barrier (already complete here)
+            if (WHICH == 1 && !kSigmoidMode)   // the per-query vectors arrived on this barrier (already complete here)
                 ok = mbar_wait(&sm.uw_full[st], uint32_t(t / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
             if (!ok) break;
             const int g = WHICH == 0 ? 0 : t / per_head;
@@ -460,7 +501,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             // results leave in two chunks of 16 words where the arithmetic is light (plain softmax: the stores overlap the
             // second chunk's exponentials) and in one piece where it is heavy (measured: the instruction-bound modes lose
             // about 10 % when their arithmetic is cut in two by the stores)
-            constexpr bool kChunkedStores = MODE == 2;
+            constexpr bool kChunkedStores = MODE == 2 && EMU == 0;
             uint32_t pw[32], dsw[32];
 #pragma unroll
             for (int chunk = 0; chunk < 2; ++chunk) {
@@ -470,7 +511,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         const int cq = 32 * chunk + 4 * quad;
                         float lv[4] = {row_lse2, row_lse2, row_lse2, row_lse2};
                         float dl[4] = {row_delta, row_delta, row_delta, row_delta};
-                        if (WHICH == 1 && MODE != 1) {
+                        if (WHICH == 1 && !kSigmoidMode) {
                             lds128(lse_addr + 4u * cq, lv);
                             lds128(delta_addr + 4u * cq, dl);
                         }
@@ -485,9 +526,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                 m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
                                 m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
                             }
-                            score_pair<MODE, GRAD>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
+                            const bool routed = EMU > 0 && ((c / 2) % (EMU > 0 ? EMU / 2 : 1)) < 2;
+                            score_pair<MODE, GRAD, EK>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
                                              __uint_as_float(dv[c + 1]), lv[2 * h2], lv[2 * h2 + 1], dl[2 * h2], dl[2 * h2 + 1],
-                                             m0, m1, pw[16 * chunk + 2 * quad + h2], dsw[16 * chunk + 2 * quad + h2]);
+                                             m0, m1, routed, pw[16 * chunk + 2 * quad + h2], dsw[16 * chunk + 2 * quad + h2]);
                         }
                     }
                 };
@@ -557,23 +599,29 @@ extern "C" int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq,
     return 2 * batch * q_heads * seq_pad * int64_t(sizeof(float));
 }
 
-extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
-                                 const void* v, const void* out, const void* lse, void* workspace,
-                                 int64_t workspace_bytes, int64_t batch, int64_t seq, int64_t q_heads, int64_t kv_heads,
-                                 int64_t head_dim, const int64_t* q_strides, const int64_t* k_strides,
-                                 const int64_t* v_strides, const int64_t* out_strides, const int64_t* dout_strides,
-                                 int mode, int causal, float scale, float softcap, int log2_n, int softcap_grad,
-                                 void* status, fpt_stream_t stream) {
+extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+                                        const void* v, const void* out, const void* lse, void* workspace,
+                                        int64_t workspace_bytes, int64_t batch, int64_t seq, int64_t q_heads,
+                                        int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
+                                        const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
+                                        const int64_t* dout_strides, int mode, int causal, float scale, float softcap,
+                                        int log2_n, int softcap_grad, int exp2_emu_backend, int exp2_emu_freq,
+                                        void* status, fpt_stream_t stream) {
     if (!dq || !dk || !dv || !dout || !q || !k || !v || !status || !q_strides || !k_strides || !v_strides || !dout_strides)
         return FPT_ERR_NULL_POINTER;
     if (batch <= 0 || seq <= 0 || q_heads <= 0 || kv_heads <= 0) return FPT_ERR_BAD_SIZE;
     if (head_dim != kDim || q_heads % kv_heads != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
     if (batch > 65535 || q_heads > 0x7fffffff || seq > 0x3fffffff) return FPT_ERR_BAD_SIZE;
-    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;
-    if (mode == FPT_ATTN_SOFTCAP_TANH && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
-    if (mode == FPT_ATTN_SIGMOID_DIRECT && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
+    if (mode < FPT_ATTN_SOFTCAP_TANH || mode > FPT_ATTN_SIGMOID_NATIVE) return FPT_ERR_BAD_ENUM;
+    const bool softcap_family = mode == FPT_ATTN_SOFTCAP_TANH || mode == FPT_ATTN_SOFTCAP_NATIVE;
+    const bool normalised = mode != FPT_ATTN_SIGMOID_DIRECT && mode != FPT_ATTN_SIGMOID_NATIVE;
+    if (softcap_family && !(softcap > 0.0f)) return FPT_ERR_BAD_SIZE;
+    if (!normalised && (log2_n < 1 || log2_n > 24)) return FPT_ERR_BAD_SIZE;
     if (softcap_grad != FPT_SOFTCAP_GRAD_ANALYTICAL && softcap_grad != FPT_SOFTCAP_GRAD_ONE_MINUS_T2) return FPT_ERR_BAD_ENUM;
-    const bool normalised = mode != FPT_ATTN_SIGMOID_DIRECT;
+    if (exp2_emu_freq != 0 && exp2_emu_freq != 8 && exp2_emu_freq != 12 && exp2_emu_freq != 16 && exp2_emu_freq != 32)
+        return FPT_ERR_BAD_ENUM;
+    if (exp2_emu_backend < FPT_EXP2_FULL_D3 || exp2_emu_backend > FPT_EXP2_FULL_PWL2_SAFE_F16) return FPT_ERR_BAD_ENUM;
+    if (exp2_emu_freq != 0 && mode != FPT_ATTN_SOFTMAX) return FPT_ERR_BAD_ENUM;     // routed for the plain soft-max only
     if (normalised) {
         if (!out || !lse || !out_strides || !workspace) return FPT_ERR_NULL_POINTER;
         if (workspace_bytes < fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) return FPT_ERR_SCRATCH_TOO_SMALL;
@@ -645,6 +693,8 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     };
     for (int i = 0; i < 4; ++i) p.tanh_dw[i] = scaled_bf16(tanh_row->c[i], float(i + 1));
     p.b3 = b3_words(mode == FPT_ATTN_SIGMOID_DIRECT ? log2_n : 12);
+    p.sigmoid_mul = -scale * kLog2eB;
+    p.sigmoid_add = float(log2_n);
 
     const size_t smem = sizeof(BwdSmem) + 1024;
     static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "shared memory budget");
@@ -666,17 +716,48 @@ extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout,
     const int raster = fpt::tuning_attention_raster();
     const double streamed_all_heads = double(q_heads) * double(seq) * kDim * 2.0 * 2.0;
     p.rows_fastest = raster >= 0 ? raster : (!causal && streamed_all_heads > 64.0 * 1024 * 1024 ? 1 : 0);
-    auto run = [&](auto mode_tag, auto grad_tag) {
+    auto run = [&](auto mode_tag, auto grad_tag, auto emu_tag, auto kind_tag) {
         constexpr int M = decltype(mode_tag)::value;
         constexpr int G = decltype(grad_tag)::value;
+        constexpr int E = decltype(emu_tag)::value;
+        constexpr int EK = decltype(kind_tag)::value;
         // dQ: fixed Q, dO; streamed K, V.   dK, dV: fixed K, V; streamed Q, dO
-        if (int rc = launch(attention_bwd_kernel<M, 0, G>, unsigned(q_heads), map_q, map_do, map_k, map_v,
+        if (int rc = launch(attention_bwd_kernel<M, 0, G, E, EK>, unsigned(q_heads), map_q, map_do, map_k, map_v,
                             static_cast<uint16_t*>(dq), nullptr))
             return rc;
-        return launch(attention_bwd_kernel<M, 1, G>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
+        return launch(attention_bwd_kernel<M, 1, G, E, EK>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
                       static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv));
     };
-    if (mode == FPT_ATTN_SOFTCAP_TANH) return softcap_grad == 1 ? run(IC<0>{}, IC<1>{}) : run(IC<0>{}, IC<0>{});
-    if (mode == FPT_ATTN_SIGMOID_DIRECT) return run(IC<1>{}, IC<0>{});
-    return run(IC<2>{}, IC<0>{});
+    if (mode == FPT_ATTN_SOFTCAP_TANH)
+        return softcap_grad == 1 ? run(IC<0>{}, IC<1>{}, IC<0>{}, IC<0>{}) : run(IC<0>{}, IC<0>{}, IC<0>{}, IC<0>{});
+    if (mode == FPT_ATTN_SIGMOID_DIRECT) return run(IC<1>{}, IC<0>{}, IC<0>{}, IC<0>{});
+    if (mode == FPT_ATTN_SOFTCAP_NATIVE) return run(IC<3>{}, IC<0>{}, IC<0>{}, IC<0>{});
+    if (mode == FPT_ATTN_SIGMOID_NATIVE) return run(IC<4>{}, IC<0>{}, IC<0>{}, IC<0>{});
+    auto routed = [&](auto kind_tag) {
+        switch (exp2_emu_freq) {
+            case 8: return run(IC<2>{}, IC<0>{}, IC<8>{}, kind_tag);
+            case 12: return run(IC<2>{}, IC<0>{}, IC<12>{}, kind_tag);
+            case 16: return run(IC<2>{}, IC<0>{}, IC<16>{}, kind_tag);
+            default: return run(IC<2>{}, IC<0>{}, IC<32>{}, kind_tag);
+        }
+    };
+    if (exp2_emu_freq == 0) return run(IC<2>{}, IC<0>{}, IC<0>{}, IC<0>{});
+    switch (exp2_emu_backend) {
+        case FPT_EXP2_FULL_D3: return routed(IC<kExp2FullD3>{});
+        case FPT_EXP2_FULL_PWL2: return routed(IC<kExp2FullPwl2>{});
+        case FPT_EXP2_FULL_D2_SAFE: return routed(IC<kExp2FullD2Safe>{});
+        default: return routed(IC<kExp2FullPwl2SafeF16>{});
+    }
+}
+
+extern "C" int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
+                                 const void* v, const void* out, const void* lse, void* workspace,
+                                 int64_t workspace_bytes, int64_t batch, int64_t seq, int64_t q_heads, int64_t kv_heads,
+                                 int64_t head_dim, const int64_t* q_strides, const int64_t* k_strides,
+                                 const int64_t* v_strides, const int64_t* out_strides, const int64_t* dout_strides,
+                                 int mode, int causal, float scale, float softcap, int log2_n, int softcap_grad,
+                                 void* status, fpt_stream_t stream) {
+    return fpt_attention_bwd_routed(dq, dk, dv, dout, q, k, v, out, lse, workspace, workspace_bytes, batch, seq, q_heads,
+                                    kv_heads, head_dim, q_strides, k_strides, v_strides, out_strides, dout_strides, mode,
+                                    causal, scale, softcap, log2_n, softcap_grad, FPT_EXP2_FULL_D3, 0, status, stream);
 }

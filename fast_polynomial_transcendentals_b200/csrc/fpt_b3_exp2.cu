@@ -148,7 +148,7 @@ extern "C" int fpt_exp2_fraction(void* out, const void* in, int64_t n, int varia
 
 extern "C" int fpt_exp2_full_f32(void* out, const void* in, int64_t n, int variant, fpt_stream_t stream) {
     if (n < 0) return FPT_ERR_BAD_SIZE;
-    if (variant != FPT_EXP2_FULL_D3 && variant != FPT_EXP2_FULL_PWL2) return FPT_ERR_BAD_ENUM;
+    if (variant < FPT_EXP2_FULL_D3 || variant > FPT_EXP2_FULL_PWL2_SAFE_F16) return FPT_ERR_BAD_ENUM;
     if (n == 0) return FPT_OK;
     if (!out || !in) return FPT_ERR_NULL_POINTER;
     if ((reinterpret_cast<uintptr_t>(in) & 15u) || (reinterpret_cast<uintptr_t>(out) & 15u)) return FPT_ERR_MISALIGNED;
@@ -157,9 +157,13 @@ extern "C" int fpt_exp2_full_f32(void* out, const void* in, int64_t n, int varia
     int64_t grid = (n / 4 + kBlock - 1) / kBlock;
     if (grid < 1) grid = 1;
     if (grid > 0x7fffffff) grid = 0x7fffffff;
-    if (variant == FPT_EXP2_FULL_D3)
-        exp2_full_f32_kernel<kExp2FullD3><<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
-    else
-        exp2_full_f32_kernel<kExp2FullPwl2><<<unsigned(grid), kBlock, 0, stream>>>(static_cast<const float*>(in), static_cast<float*>(out), n);
+    const float* src = static_cast<const float*>(in);
+    float* dst = static_cast<float*>(out);
+    switch (variant) {
+    case FPT_EXP2_FULL_D3: exp2_full_f32_kernel<kExp2FullD3><<<unsigned(grid), kBlock, 0, stream>>>(src, dst, n); break;
+    case FPT_EXP2_FULL_PWL2: exp2_full_f32_kernel<kExp2FullPwl2><<<unsigned(grid), kBlock, 0, stream>>>(src, dst, n); break;
+    case FPT_EXP2_FULL_D2_SAFE: exp2_full_f32_kernel<kExp2FullD2Safe><<<unsigned(grid), kBlock, 0, stream>>>(src, dst, n); break;
+    default: exp2_full_f32_kernel<kExp2FullPwl2SafeF16><<<unsigned(grid), kBlock, 0, stream>>>(src, dst, n); break;
+    }
     return cuda_status(cudaGetLastError());
 }

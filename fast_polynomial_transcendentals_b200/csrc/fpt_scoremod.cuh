@@ -135,18 +135,35 @@ __device__ __forceinline__ uint32_t exp2_hinge(uint32_t x, const Exp2Words& k) {
 //   PWL2: p = k0 + k1 f + k2 max(f - 1/2, 0)                     continuous two-piece line, relative error 2.1e-2
 //   2^a = bits(p) + (bits(xr) << 23)         (the shift drops the magic constant's own bits, n lands on the exponent)
 // Every step is one IEEE operation (flush-to-zero as in the reference; no step here meets a subnormal for a <= 127).
-enum Exp2Full : int { kExp2FullD3 = 0, kExp2FullPwl2 = 1 };
+// Two more fractional evaluators keep the same reduction and reconstruction and preserve both endpoints (p(0) = 1,
+// p(1) = 2), which an online soft-max needs for its rescaling steps to compose (reference:
+// extras/paper/manuscript/appendix_exp2.tex:18-33 fits, :74-80 packed fp16 constants; the reference's own instruction
+// listing for them sits in its attention submodule, so the operation order below is this library's):
+//   D2_SAFE:       p = 1 + a f + (1 - a) f^2, a = 0.6602339719      two fp32 multiply-adds, relative error 2.7e-3
+//   PWL2_SAFE_F16: p = 1 + A f + C max(f - 1/2, 0) on a packed fp16 pair, A = 0.7978515625, C = 0.40380859375:
+//                  f -> fp16, subtract, maximum, two fp16 multiply-adds, back to fp32; relative error 1.1e-2
+enum Exp2Full : int { kExp2FullD3 = 0, kExp2FullPwl2 = 1, kExp2FullD2Safe = 2, kExp2FullPwl2SafeF16 = 3 };
 constexpr float kExp2Magic = 12582912.0f;            // 0x4B400000
 // Lowest argument: -127 for the cubic (p >= 1, so the sum of bit patterns ends exactly at +0); -126 for the two-piece
 // line, which starts at p = 0.989 < 1: one exponent lower its bit pattern would wrap to a negative NaN pattern (the
 // reference clamps both at -127 and only feeds the line arguments above that; masked soft-max scores are -inf).
-template <int KIND> constexpr float kExp2Floor = KIND == 0 ? -127.0f : -126.0f;
+template <int KIND> constexpr float kExp2Floor = KIND == 1 ? -126.0f : -127.0f;
 constexpr float kExp2D3C1 = 0.6951461434364319f;     // 0x3F31F519
 constexpr float kExp2D3C2 = 0.22756439447402954f;    // 0x3E6906A4
 constexpr float kExp2D3C3 = 0.07711908966302872f;    // 0x3D9DF09D
 constexpr float kExp2PwlK0 = 0.9894611835479736f;    // 0x3F7D4D54
 constexpr float kExp2PwlK1 = 0.820852518081665f;     // 0x3F522364
 constexpr float kExp2PwlK2 = 0.34246066212654114f;   // 0x3EAF5701
+constexpr float kExp2D2A = 0.6602339719f;            // endpoint-preserving quadratic: a
+constexpr float kExp2D2B = 0.3397660281f;            //                                1 - a
+
+// 2^f for a pair f0, f1 in [0, 1) on packed fp16 lanes (endpoint-preserving two-piece line), widened to fp32
+__device__ __forceinline__ void exp2_fraction_pwl2_f16(float f0, float f1, float& p0, float& p1) {
+    const uint32_t fh = Sfu<kFp16>::pack(f0, f1);
+    const uint32_t ph = exp2_hinge(fh, Exp2Words{0x3a623a62u, 0x3c003c00u, 0x36763676u});   // A, 1, C in fp16
+    p0 = Sfu<kFp16>::lo(ph);
+    p1 = Sfu<kFp16>::hi(ph);
+}
 
 template <int KIND>
 __device__ __forceinline__ float exp2_full(float a) {
@@ -158,10 +175,16 @@ __device__ __forceinline__ float exp2_full(float a) {
         p = __fmaf_rn(f, kExp2D3C3, kExp2D3C2);
         p = __fmaf_rn(p, f, kExp2D3C1);
         p = __fmaf_rn(p, f, 1.0f);
-    } else {
+    } else if constexpr (KIND == kExp2FullPwl2) {
         const float h = fmaxf(__fsub_rn(f, 0.5f), 0.0f);
         p = __fmaf_rn(f, kExp2PwlK1, kExp2PwlK0);
         p = __fmaf_rn(h, kExp2PwlK2, p);
+    } else if constexpr (KIND == kExp2FullD2Safe) {
+        p = __fmaf_rn(f, kExp2D2B, kExp2D2A);
+        p = __fmaf_rn(p, f, 1.0f);
+    } else {
+        float unused;
+        exp2_fraction_pwl2_f16(f, f, p, unused);
     }
     return __uint_as_float(__float_as_uint(p) + (__float_as_uint(xr) << 23));
 }
@@ -190,6 +213,36 @@ __device__ __forceinline__ void exp2_full_x2(float a0, float a1, float& e0, floa
             "mov.b64 {%2, %3}, xr;\n\t}"
             : "=r"(p0), "=r"(p1), "=r"(x0), "=r"(x1)
             : "f"(a0), "f"(a1), "f"(kExp2Magic), "f"(kExp2D3C3), "f"(kExp2D3C2), "f"(kExp2D3C1), "f"(1.0f));
+    } else if constexpr (KIND == kExp2FullD2Safe) {
+        asm("{\n\t.reg .b64 a, m, xr, n, f, p, c;\n\t"
+            "mov.b64 a, {%4, %5};\n\t"
+            "mov.b64 m, {%6, %6};\n\t"
+            "add.rm.ftz.f32x2 xr, a, m;\n\t"
+            "sub.rn.ftz.f32x2 n, xr, m;\n\t"
+            "sub.rn.ftz.f32x2 f, a, n;\n\t"
+            "mov.b64 p, {%7, %7};\n\t"
+            "mov.b64 c, {%8, %8};\n\t"
+            "fma.rn.ftz.f32x2 p, f, p, c;\n\t"
+            "mov.b64 c, {%9, %9};\n\t"
+            "fma.rn.ftz.f32x2 p, p, f, c;\n\t"
+            "mov.b64 {%0, %1}, p;\n\t"
+            "mov.b64 {%2, %3}, xr;\n\t}"
+            : "=r"(p0), "=r"(p1), "=r"(x0), "=r"(x1)
+            : "f"(a0), "f"(a1), "f"(kExp2Magic), "f"(kExp2D2B), "f"(kExp2D2A), "f"(1.0f));
+    } else if constexpr (KIND == kExp2FullPwl2SafeF16) {
+        float f0, f1, q0, q1;
+        asm("{\n\t.reg .b64 a, m, xr, n, f;\n\t"
+            "mov.b64 a, {%4, %5};\n\t"
+            "mov.b64 m, {%6, %6};\n\t"
+            "add.rm.ftz.f32x2 xr, a, m;\n\t"
+            "sub.rn.ftz.f32x2 n, xr, m;\n\t"
+            "sub.rn.ftz.f32x2 f, a, n;\n\t"
+            "mov.b64 {%0, %1}, f;\n\t"
+            "mov.b64 {%2, %3}, xr;\n\t}"
+            : "=f"(f0), "=f"(f1), "=r"(x0), "=r"(x1) : "f"(a0), "f"(a1), "f"(kExp2Magic));
+        exp2_fraction_pwl2_f16(f0, f1, q0, q1);
+        p0 = __float_as_uint(q0);
+        p1 = __float_as_uint(q1);
     } else {
         float f0, f1;
         asm("{\n\t.reg .b64 a, m, xr, n, f;\n\t"

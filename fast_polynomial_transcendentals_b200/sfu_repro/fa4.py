@@ -271,7 +271,9 @@ def validate_fa4_config(config: FA4Config, *, sequence_length: int | None = None
 
 # ---- this package's attention runtime ----------------------------------------------------------------
 
-_EXP2_BACKEND_IDS = {"d3": 0, "pwl2": 1}
+# exp2 backends built into this package's attention kernels -> FPT_EXP2_FULL_* of the C ABI
+_EXP2_BACKEND_IDS = {"d3": 0, "pwl2": 1, "d2_safe": 2, "pwl2_safe_f16": 3}
+_BUILT_EXP2_FREQUENCIES = (0, 8, 12, 16, 32)
 
 
 @dataclass(frozen=True)
@@ -283,6 +285,41 @@ class SoftcapScoreMod:
     backend: str = "device"
     coeff_source: str = "current"
     backward_mode: str = "analytical"
+
+
+def _exp2_route(mode: int, backend: str, frequency, where: str) -> int:
+    """Validated routing frequency for the kernels; None ('automatic') keeps every lane on the SFU here."""
+    route = 0 if frequency is None else int(frequency)
+    if route == 0:
+        return 0
+    if mode != 2:
+        raise NotImplementedError(f"{where}: software exp2 routing is built for the plain soft-max only"
+                                  + ("" if mode != 0 or where != "forward" else " (and the cubic 'd3' under a soft-cap)"))
+    if backend not in _EXP2_BACKEND_IDS:
+        raise NotImplementedError(f"{where}: exp2 backend {backend!r} is not built; built: "
+                                  + ", ".join(repr(b) for b in _EXP2_BACKEND_IDS))
+    if route not in _BUILT_EXP2_FREQUENCIES:
+        raise NotImplementedError(f"{where}: built routing frequencies are {_BUILT_EXP2_FREQUENCIES}, got {route}")
+    return route
+
+
+def _sigmoid_mode(seq: int, *, sigmoid_sfu_freq, sigmoid_sfu_res, sigmoid_bias, polynomial_ok: bool, what: str):
+    """(kernel mode, log2_n) of a sigmoid-attention call: the direct cubic (every lane polynomial) or its native twin
+    (every lane on the SFU).  Both take the bias -log(n) for a power of two n (default n = sequence length)."""
+    if sigmoid_bias is None:
+        if seq & (seq - 1):
+            raise NotImplementedError("sigmoid attention needs a power-of-two sequence length (bias -log n)")
+        log2_n = seq.bit_length() - 1
+    else:
+        log2_n = round(-float(sigmoid_bias) / math.log(2.0))
+        if log2_n < 1 or log2_n > 24 or abs(-log2_n * math.log(2.0) - float(sigmoid_bias)) > 1e-6:
+            raise NotImplementedError("sigmoid_bias must be -log(n) for a power of two n in [2, 2^24]")
+    all_poly, all_sfu = int(sigmoid_sfu_res) == 0, int(sigmoid_sfu_res) == int(sigmoid_sfu_freq)
+    if all_sfu:
+        return 4, log2_n
+    if not (all_poly and polynomial_ok and sigmoid_bias is None):
+        raise NotImplementedError(what)
+    return 1, log2_n
 
 
 class _AttentionStatus:
@@ -376,31 +413,24 @@ def _b200_flash_attn_fwd(q, k, v, *, softmax_scale=None, causal=True, softcap=0.
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(dim)
     log2_n = 12
     if sigmoid_attention:
-        if not (sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3 and sigmoid_coeff_source == "current"
-                and sigmoid_bias is None and int(sigmoid_sfu_res) == 0):
-            raise NotImplementedError("only the direct piecewise-cubic sigmoid (device, degree 3, current coefficients, "
-                                      "bias -log n, every lane polynomial) is built")
-        if seq & (seq - 1):
-            raise NotImplementedError("direct sigmoid attention needs a power-of-two sequence length")
-        mode, log2_n, cap = 1, seq.bit_length() - 1, 0.0
+        mode, log2_n = _sigmoid_mode(
+            seq, sigmoid_sfu_freq=sigmoid_sfu_freq, sigmoid_sfu_res=sigmoid_sfu_res, sigmoid_bias=sigmoid_bias,
+            polynomial_ok=(sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3 and sigmoid_coeff_source == "current"),
+            what="built sigmoid routes: the direct piecewise cubic on every lane (device, degree 3, current "
+                 "coefficients, bias -log n) and the SFU sigmoid on every lane")
+        cap = 0.0
     elif score_mod is not None:
         if not isinstance(score_mod, SoftcapScoreMod) or score_mod.degree != 4 or score_mod.coeff_source != "current":
             raise NotImplementedError("only the degree-4 'current' tanh soft-cap score-mod is built")
         mode, cap = 0, float(score_mod.softcap)
     elif softcap and float(softcap) > 0.0:
-        raise NotImplementedError("native (SFU) tanh soft-cap is not built; use the polynomial score-mod")
+        mode, cap = 3, float(softcap)          # native twin: tanh on the special-function unit
     else:
         mode, cap = 2, 0.0
-    route = 0 if exp2_emu_freq is None else int(exp2_emu_freq)   # "automatic" keeps every lane on the SFU here
-    if route:
-        if mode == 1:
-            raise NotImplementedError("sigmoid attention has no exponential to route")
-        if exp2_emu_backend not in ("d3", "pwl2") or (exp2_emu_backend == "pwl2" and mode != 2):
-            raise NotImplementedError(f"exp2 backend {exp2_emu_backend!r} is not built for this mode; built: the fp32 "
-                                      "cubic 'd3' (soft-max modes) and the two-piece line 'pwl2' (plain soft-max), the "
-                                      "two full-range evaluators whose instruction sequences the reference publishes")
-        if route not in (8, 12, 16, 32):
-            raise NotImplementedError("built routing frequencies: 0, 8, 12, 16, 32")
+    if mode == 0 and exp2_emu_freq not in (None, 0) and exp2_emu_backend == "d3" and int(exp2_emu_freq) in _BUILT_EXP2_FREQUENCIES:
+        route = int(exp2_emu_freq)             # the cubic is also routed under the polynomial soft-cap
+    else:
+        route = _exp2_route(mode, exp2_emu_backend, exp2_emu_freq, "forward")
     out = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((batch, q_heads, seq), dtype=torch.float32, device=q.device)
     strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
@@ -431,14 +461,13 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(dim)
     log2_n, grad_mode = 12, 0
     if sigmoid_attention:
-        if not (sigmoid_use_direct_bwd_poly and sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3
-                and int(sigmoid_gradient_degree) == 4 and sigmoid_coeff_source == "current" and sigmoid_bias is None
-                and int(sigmoid_sfu_res) == 0):
-            raise NotImplementedError("only the direct cubic with its coupled degree-4 derivative (device, current "
-                                      "coefficients, bias -log n, every lane polynomial) is built")
-        if seq & (seq - 1):
-            raise NotImplementedError("direct sigmoid attention needs a power-of-two sequence length")
-        mode, log2_n, cap = 1, seq.bit_length() - 1, 0.0
+        mode, log2_n = _sigmoid_mode(
+            seq, sigmoid_sfu_freq=sigmoid_sfu_freq, sigmoid_sfu_res=sigmoid_sfu_res, sigmoid_bias=sigmoid_bias,
+            polynomial_ok=(sigmoid_use_direct_bwd_poly and sigmoid_poly_backend == "device" and int(sigmoid_degree) == 3
+                           and int(sigmoid_gradient_degree) == 4 and sigmoid_coeff_source == "current"),
+            what="built sigmoid backward routes: the direct cubic with its coupled degree-4 derivative on every lane "
+                 "(device, current coefficients, bias -log n) and the SFU sigmoid with p(1-p) on every lane")
+        cap = 0.0
     elif score_mod is not None or score_mod_bwd is not None:
         token = score_mod_bwd if score_mod_bwd is not None else score_mod
         if not isinstance(token, SoftcapScoreMod) or token.degree != 4 or token.coeff_source != "current":
@@ -448,16 +477,15 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
                                       "(built: 'analytical', 'exact_1mt2')")
         mode, cap, grad_mode = 0, float(token.softcap), (0 if token.backward_mode == "analytical" else 1)
     elif softcap and float(softcap) > 0.0:
-        raise NotImplementedError("native (SFU) tanh soft-cap is not built; use the polynomial score-mod")
+        mode, cap, grad_mode = 3, float(softcap), 1      # native twin: SFU tanh, derivative 1 - t^2
     else:
         mode, cap = 2, 0.0
-    if exp2_emu_freq not in (None, 0):
-        raise NotImplementedError("software exp2 routing is not built for the backward pass")
+    route = _exp2_route(mode, exp2_emu_backend, exp2_emu_freq, "backward")
     dq = torch.empty((batch, seq, q_heads, dim), dtype=torch.bfloat16, device=q.device)
     dk = torch.empty((batch, seq, k.shape[2], dim), dtype=torch.bfloat16, device=q.device)
     dv = torch.empty_like(dk)
     strides = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
-    needs_forward = mode != 1
+    needs_forward = mode not in (1, 4)
     if needs_forward and (out is None or lse is None):
         raise RuntimeError("soft-max attention backward needs the forward's out and lse")
     need = int(_lib.load().fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) if needs_forward else 0
@@ -465,11 +493,12 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     with torch.cuda.device(q.device):
         status = _status_for(q.device)
         status.poll()
-        _lib.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(),
+        _lib.call("fpt_attention_bwd_routed", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(),
                   k.data_ptr(), v.data_ptr(), out.data_ptr() if needs_forward else None,
                   lse.data_ptr() if needs_forward else None, workspace.data_ptr(), need, batch, seq, q_heads, k.shape[2],
                   dim, strides(q), strides(k), strides(v), strides(out) if needs_forward else strides(q), strides(dout),
-                  mode, int(bool(causal)), scale, cap, log2_n, grad_mode, status.word.data_ptr(),
+                  mode, int(bool(causal)), scale, cap, log2_n, grad_mode, _EXP2_BACKEND_IDS.get(exp2_emu_backend, 0), route,
+                  status.word.data_ptr(),
                   torch.cuda.current_stream(q.device).cuda_stream)
         _finish_launch(status, "the attention backward")
     return dq, dk, dv
@@ -522,10 +551,45 @@ def _load_fa4_runtime() -> Mapping[str, Any]:
                            "`python -m fast_polynomial_transcendentals_b200.build`.") from error
 
 
+def _require_built(c: FA4Config) -> None:
+    """Reject, at resolution time, what this package's kernels do not run (a foreign runtime decides for itself)."""
+    def refuse(what: str):
+        raise NotImplementedError(
+            f"{what} is not built in this package's attention kernels.  Built: soft-max with exp2 backends "
+            f"{', '.join(_EXP2_BACKEND_IDS)} at routing frequencies {_BUILT_EXP2_FREQUENCIES} forward and backward "
+            "('automatic' keeps every lane on the SFU); soft-cap native (SFU tanh) or polynomial degree 4 'current' "
+            "with backward 'analytical' / 'exact_1mt2'; sigmoid attention 'sfu' or the direct D3 / coupled D4 "
+            "polynomial pair with bias -log n")
+    if c.mode == "softmax":
+        routes = [f for f in (c.exp2_emu_freq, c.exp2_emu_freq_bwd) if f not in (None, 0)]
+        if routes and c.exp2_emu_backend not in _EXP2_BACKEND_IDS:
+            refuse(f"exp2 backend {c.exp2_emu_backend!r}")
+        for f in routes:
+            if int(f) not in _BUILT_EXP2_FREQUENCIES:
+                refuse(f"exp2 routing frequency {f}")
+    elif c.mode == "softcap" and c.softcap_backend != "native":
+        if int(c.softcap_degree) != 4 or c.softcap_coeff_source != "current":
+            refuse(f"soft-cap polynomial degree {c.softcap_degree} source {c.softcap_coeff_source!r}")
+        if c.softcap_backward_mode not in ("analytical", "exact_1mt2"):
+            refuse(f"soft-cap backward mode {c.softcap_backward_mode!r}")
+    elif c.mode == "sigmoid_attention":
+        if c.sigmoid_variant == "sfu":
+            if c.sigmoid_bias is not None:
+                k = round(-float(c.sigmoid_bias) / math.log(2.0))
+                if k < 1 or k > 24 or abs(-k * math.log(2.0) - float(c.sigmoid_bias)) > 1e-6:
+                    refuse(f"sigmoid_bias {c.sigmoid_bias} (not -log of a power of two)")
+        elif not (_uses_direct_flash_sigmoid(c) and c.sigmoid_backward_mode == "direct"
+                  and (c.sigmoid_degree_bwd is None or int(c.sigmoid_degree_bwd) == 4)):
+            refuse("this polynomial sigmoid selection")
+
+
 def resolve_fa4_config(config: FA4Config, *, sequence_length: int | None = None,
                        runtime: Mapping[str, Any] | None = None) -> ResolvedFA4Config:
     """Validate `config` and bind it to an attention runtime (this package's unless `runtime` is given)."""
     validate_fa4_config(config, sequence_length=sequence_length)
+    own_runtime = runtime is None
+    if own_runtime:
+        _require_built(config)
     runtime = _load_fa4_runtime() if runtime is None else runtime
     c = config
     fwd, bwd = runtime["flash_attn_fwd"], runtime["flash_attn_bwd"]
@@ -552,6 +616,8 @@ def resolve_fa4_config(config: FA4Config, *, sequence_length: int | None = None,
 
     if c.mode == "softmax":
         route = "automatic" if c.exp2_emu_freq is None else c.exp2_emu_freq
+        if own_runtime and c.exp2_emu_freq is None:
+            route = "automatic -> 0 (all SFU)"
         return ResolvedFA4Config(
             mode="softmax", flash_attn_fwd=fwd, flash_attn_bwd=bwd, exp2_emu_backend=c.exp2_emu_backend,
             exp2_emu_freq=c.exp2_emu_freq, exp2_emu_freq_bwd=c.exp2_emu_freq_bwd, sigmoid_qk_norm=False,

@@ -160,8 +160,13 @@ int fpt_exp2_fraction(void* out, const void* in, int64_t n, int variant, int rep
  *      autonumerics_zero/cuda_benchmarks/benchmark_exp2_pwl2.cu:106-198); these are the software exponentials the
  *      attention kernel routes a share of its soft-max lanes through.  in/out: fp32 [n], 16-byte aligned; a <= 127.
  *      One difference: the two-piece line clamps at -126, not -127 (its p starts below 1, so at n = -127 the
- *      reference's bit arithmetic wraps into a NaN pattern; -inf is a regular input of a masked soft-max). */
-enum { FPT_EXP2_FULL_D3 = 0, FPT_EXP2_FULL_PWL2 = 1 };
+ *      reference's bit arithmetic wraps into a NaN pattern; -inf is a regular input of a masked soft-max).
+ *      FPT_EXP2_FULL_D2_SAFE ("d2_safe") and FPT_EXP2_FULL_PWL2_SAFE_F16 ("pwl2_safe_f16") keep the same reduction and
+ *      reconstruction and change the fractional evaluator to the two endpoint-preserving fits of the reference
+ *      (reference: extras/paper/manuscript/appendix_exp2.tex:18-33 and :74-80): p = 1 + a f + (1 - a) f^2 with
+ *      a = 0.6602339719 in fp32 (relative error 2.7e-3), and p = 1 + A f + C max(f - 1/2, 0) on a packed fp16 pair with
+ *      A = 0.7978515625, C = 0.40380859375 (1.1e-2).  Both give p(0) = 1 and p(1) = 2 exactly; both clamp at -127. */
+enum { FPT_EXP2_FULL_D3 = 0, FPT_EXP2_FULL_PWL2 = 1, FPT_EXP2_FULL_D2_SAFE = 2, FPT_EXP2_FULL_PWL2_SAFE_F16 = 3 };
 int fpt_exp2_full_f32(void* out, const void* in, int64_t n, int variant, fpt_stream_t stream);
 
 /* ---- paired sin/cos: fp32 angles [n] -> out [2, n] 16-bit, cos plane first
@@ -255,9 +260,16 @@ int fpt_rope_apply_static_table(void* q_out, void* k_out, const void* q, const v
  *      mode FPT_ATTN_SIGMOID_DIRECT: P = direct piecewise cubic sigmoid of bf16(score*scale) scaled for n = 2^log2_n
  *                                    keys (B3), O = P V without normalisation
  *      mode FPT_ATTN_SOFTMAX:        plain softmax (control)
+ *      mode FPT_ATTN_SOFTCAP_NATIVE: the native twin of FPT_ATTN_SOFTCAP_TANH: softmax(softcap * tanh(score*scale/softcap))
+ *                                    with the special-function unit's fp32 tanh (the reference's softcap_backend =
+ *                                    "native", src/sfu_repro/fa4.py:650-659), same kernel otherwise
+ *      mode FPT_ATTN_SIGMOID_NATIVE: the native twin of FPT_ATTN_SIGMOID_DIRECT: P = 1 / (1 + 2^(log2_n - score*scale*
+ *                                    log2 e)) = sigmoid(score*scale - ln 2^log2_n) through ex2 and rcp (the reference's
+ *                                    sigmoid_variant = "sfu", src/sfu_repro/fa4.py:686-692), O = P V
  *      status: one zero-initialised device word; non-zero after the launch means a bounded device-side wait ran
  *      out (bit 31 set, low bits tell where) and the output is invalid. */
-enum { FPT_ATTN_SOFTCAP_TANH = 0, FPT_ATTN_SIGMOID_DIRECT = 1, FPT_ATTN_SOFTMAX = 2 };
+enum { FPT_ATTN_SOFTCAP_TANH = 0, FPT_ATTN_SIGMOID_DIRECT = 1, FPT_ATTN_SOFTMAX = 2, FPT_ATTN_SOFTCAP_NATIVE = 3,
+       FPT_ATTN_SIGMOID_NATIVE = 4 };
 int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch, int64_t seq,
                       int64_t q_heads, int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
                       const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides, int mode,
@@ -268,8 +280,10 @@ int fpt_attention_fwd(void* out, void* lse, const void* q, const void* k, const 
  *      (reference: src/sfu_repro/fa4.py:34-47 backends, :724-752 routed configurations, forward kwargs :790-807):
  *      exp2_emu_freq 0 keeps every exponential on the special-function unit; f in {8, 12, 16, 32} sends four of
  *      every f keys of a row through a software exponential of fpt_exp2_full_f32 instead (one half, third, quarter,
- *      eighth): exp2_emu_backend FPT_EXP2_FULL_D3 ("d3") in both soft-max modes, FPT_EXP2_FULL_PWL2 ("pwl2") in
- *      FPT_ATTN_SOFTMAX.  FPT_ATTN_SIGMOID_DIRECT has no exponential and accepts frequency 0 only. */
+ *      eighth): exp2_emu_backend FPT_EXP2_FULL_D3 ("d3") in both polynomial soft-max modes; FPT_EXP2_FULL_PWL2
+ *      ("pwl2"), FPT_EXP2_FULL_D2_SAFE ("d2_safe") and FPT_EXP2_FULL_PWL2_SAFE_F16 ("pwl2_safe_f16") in
+ *      FPT_ATTN_SOFTMAX.  The sigmoid modes have no soft-max exponential and FPT_ATTN_SOFTCAP_NATIVE is the all-native
+ *      control: they accept frequency 0 only. */
 int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k, const void* v, int64_t batch,
                              int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim,
                              const int64_t* q_strides, const int64_t* k_strides, const int64_t* v_strides,
@@ -283,7 +297,7 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
  *      q, k, v, out, dout: (batch, seq, head, dim) tensors through element strides as in the forward; lse fp32
  *      [B,Hq,S] from the forward; dq [B,S,Hq,D], dk / dv [B,S,Hkv,D] contiguous bf16 outputs.
  *      Soft-max modes need out, lse and a workspace of fpt_attention_bwd_workspace_bytes() (16-byte aligned);
- *      FPT_ATTN_SIGMOID_DIRECT needs none of the three (NULL accepted): dS = dP * p(x) * (intercept + slope*clamp(x)),
+ *      FPT_ATTN_SIGMOID_DIRECT and FPT_ATTN_SIGMOID_NATIVE need none of the three (NULL accepted): dS = dP * p(x) * (intercept + slope*clamp(x)),
  *      the coupled derivative of the direct cubic.  softcap_grad picks d tanh_poly / dx for FPT_ATTN_SOFTCAP_TANH:
  *      the derivative of the polynomial itself (zero where the input is clamped or the output saturated), or
  *      1 - t^2 of its value.  Deterministic: two launches (dQ; dK and dV), no atomics.  status as in the forward. */
@@ -295,6 +309,20 @@ int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void
                       const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
                       const int64_t* dout_strides, int mode, int causal, float scale, float softcap, int log2_n,
                       int softcap_grad, void* status, fpt_stream_t stream);
+
+/* The same backward with the soft-max exponentials of the recomputed probabilities partly routed to the FMA pipe
+ *      replaces exp2_emu_freq_bwd of the reference's attention interface (reference: src/sfu_repro/fa4.py:724-752, the
+ *      retained routed configurations use forward frequency 12 and backward frequency 32; backward kwargs :828-859).
+ *      FPT_ATTN_SOFTMAX only; frequencies 0, 8, 12, 16, 32: four of every f columns of each 64-column half of a score
+ *      tile take the software exponential exp2_emu_backend (any FPT_EXP2_FULL_* value).  The native twins take
+ *      softcap_grad as given for FPT_ATTN_SOFTCAP_NATIVE (1 - t^2 is what they compute) and need neither out nor lse
+ *      for FPT_ATTN_SIGMOID_NATIVE (dS = dP p (1 - p)). */
+int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k, const void* v,
+                             const void* out, const void* lse, void* workspace, int64_t workspace_bytes, int64_t batch,
+                             int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
+                             const int64_t* k_strides, const int64_t* v_strides, const int64_t* out_strides,
+                             const int64_t* dout_strides, int mode, int causal, float scale, float softcap, int log2_n,
+                             int softcap_grad, int exp2_emu_backend, int exp2_emu_freq, void* status, fpt_stream_t stream);
 
 /* ---- diagnostic: one 128x128x128 bf16 tile through the tensor-core building blocks of the attention kernel
  *      (no counterpart in the reference).  a, b: bf16 [128,128] row-major; c: fp32 [128,128];

@@ -9,6 +9,8 @@ the mathematics with the same polynomial score-mods, not a pin to reference outp
     mode 2   P = softmax(s);                       dS = P (dP - delta)
     mode 0   P = softmax(cap * tanhD4(bf16(s/cap))); dS = P (dP - delta) * g(x),  g = d tanhD4/dx (analytical) or 1 - t^2
     mode 1   P = B3(bf16(s)) (no normalisation);   dS = dP * P'(x), P' the coupled derivative of the direct cubic
+    mode 3   native twin of mode 0: P = softmax(cap * tanh(s/cap)) with the exact tanh; dS = P (dP - delta) (1 - t^2)
+    mode 4   native twin of mode 1: P = sigmoid(s - log n) exactly (no normalisation); dS = dP * P (1 - P)
     dP = dO V^T,  delta = rowsum(dO * O),  dV = bf16(P)^T dO,  dQ = scale * bf16(dS) K,  dK = scale * bf16(dS)^T Q
 
 with P and dS rounded to bf16 where the tensor cores consume them.
@@ -58,8 +60,16 @@ def attention_fwd_bwd(q_bits, k_bits, v_bits, dout_bits, mode: int, causal: bool
                 p = oracle.bf16_bits_to_f32(p_bits).astype(np.float64).reshape(S, S) * mask
                 grad = oracle.bf16_bits_to_f32(grad_bits).astype(np.float64).reshape(S, S) * mask
                 p_mma = p                                    # already bf16 values
+            elif mode == 4:
+                p = 1.0 / (1.0 + np.exp(log2_n * np.log(2.0) - raw * scale)) * mask
+                grad = p * (1.0 - p)
+                p_mma = _bf16_round(p)
             else:
-                if mode == 0:
+                if mode == 3:
+                    t = np.tanh(raw * (scale / softcap))
+                    s = softcap * t
+                    g = 1.0 - t * t
+                elif mode == 0:
                     x_bits = oracle.f32_to_bf16_bits((raw * (scale / softcap)).astype(np.float32))
                     t_bits = oracle.unary(tanh_idx, x_bits.ravel())
                     t = oracle.bf16_bits_to_f32(t_bits).astype(np.float64).reshape(S, S)
@@ -82,7 +92,7 @@ def attention_fwd_bwd(q_bits, k_bits, v_bits, dout_bits, mode: int, causal: bool
             o = p_mma @ v[b, :, hk, :]
             out[b, :, h, :] = o
             dp = do[b, :, h, :] @ v[b, :, hk, :].T
-            if mode == 1:
+            if mode in (1, 4):
                 ds = dp * grad
             else:
                 delta = (do[b, :, h, :] * _bf16_round(o)).sum(axis=1, keepdims=True)

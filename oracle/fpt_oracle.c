@@ -322,7 +322,7 @@ static inline float exp2_full_lane(float a, int variant) {
     /* max(a, floor) with the NaN-dropping rule of PTX max.  The cubic has p >= 1, so -127 ends at bit pattern 0; the
      * two-piece line starts at p = 0.989 < 1, whose exponent field would wrap below -126 (the reference's sequence,
      * floor -127 for both, is only used above that): the device clamps that kind at -126 and so does this. */
-    const float floor_value = variant == 0 ? -127.0f : -126.0f;
+    const float floor_value = variant == 1 ? -126.0f : -127.0f;   /* variants 2 and 3 have p(0) = 1 exactly, like the cubic */
     if (!(a >= floor_value)) a = floor_value;
     if (fabsf(a) < 1.17549435e-38f) a = copysignf(0.0f, a);   /* .ftz on every device step: subnormal inputs are zero */
     xr = add_round_down(a, 12582912.0f);
@@ -332,11 +332,25 @@ static inline float exp2_full_lane(float a, int variant) {
         p = fmaf(f, 0.07711908966302872f, 0.22756439447402954f);
         p = fmaf(p, f, 0.6951461434364319f);
         p = fmaf(p, f, 1.0f);
-    } else {
+    } else if (variant == 1) {
         volatile float h = f - 0.5f;
         if (!(h > 0.0f)) h = 0.0f;
         p = fmaf(f, 0.820852518081665f, 0.9894611835479736f);
         p = fmaf(h, 0.34246066212654114f, p);
+    } else if (variant == 2) {
+        /* endpoint-preserving quadratic p = 1 + a f + (1 - a) f^2, a = 0.6602339719 (reference:
+         * extras/paper/manuscript/appendix_exp2.tex:28-33), two fp32 multiply-adds */
+        p = fmaf(f, 0.3397660281f, 0.6602339719f);
+        p = fmaf(p, f, 1.0f);
+    } else {
+        /* endpoint-preserving two-piece line on an fp16 lane, p = 1 + A f + C max(f - 1/2, 0) with the packed fp16
+         * constants A = 0.7978515625, C = 0.40380859375 (reference: extras/paper/manuscript/appendix_exp2.tex:23-27,
+         * 74-76): f rounded to fp16, hinge by subtract and maximum, two fp16 multiply-adds, widened to fp32 */
+        const uint16_t fh = sf_from_float(SF_FP16, f);
+        const uint16_t hinge = sf_max(SF_FP16, sf_sub(SF_FP16, fh, 0x3800u), 0x0000u);
+        uint16_t ph = sf_fma(SF_FP16, fh, 0x3a62u, 0x3c00u);
+        ph = sf_fma(SF_FP16, hinge, 0x3676u, ph);
+        p = sf_to_float(SF_FP16, ph);
     }
     pb.f = p; xb.f = xr;
     r.u = pb.u + (xb.u << 23);
@@ -733,22 +747,28 @@ void fpt_oracle_attention_rows(const uint16_t* q, const uint16_t* k, const uint1
                 uint16_t p, xb = sf_from_float(SF_BF16, s);
                 b3_lane(xb, log2_n, &p, NULL);
                 s = bf16f(p);
+            } else if (mode == 3) {            /* native control of mode 0: exact tanh in fp32, no polynomial */
+                s = softcap * tanhf(s / softcap);
+            } else if (mode == 4) {            /* native control of mode 1: exact sigmoid(s - log n), rounded to bf16 */
+                const double bias = (double)log2_n * 0.69314718055994530942;
+                s = bf16f(sf_from_float(SF_BF16, (float)(1.0 / (1.0 + exp(bias - (double)s)))));
             }
             sc[j] = s;
             if (s > row_max) row_max = s;
         }
+        const int unnormalised = mode == 1 || mode == 4;
         double denom = 0.0;
-        if (mode != 1) {
+        if (!unnormalised) {
             for (int64_t j = 0; j < limit; ++j) { sc[j] = expf(sc[j] - row_max); denom += sc[j]; }
         }
         float* o = out + ri * D;
         for (int64_t d = 0; d < D; ++d) o[d] = 0.f;
         for (int64_t j = 0; j < limit; ++j) {
-            const float p = mode == 1 ? sc[j] : bf16f(sf_from_float(SF_BF16, sc[j]));
+            const float p = unnormalised ? sc[j] : bf16f(sf_from_float(SF_BF16, sc[j]));
             const uint16_t* vj = v + ((b * S + j) * Hk + hk) * D;
             for (int64_t d = 0; d < D; ++d) o[d] += p * bf16f(vj[d]);
         }
-        if (mode != 1) for (int64_t d = 0; d < D; ++d) o[d] = (float)(o[d] / denom);
+        if (!unnormalised) for (int64_t d = 0; d < D; ++d) o[d] = (float)(o[d] / denom);
         free(sc);
     }
 }

@@ -111,7 +111,8 @@ def parse_header(path: Path, dtype: str, source: str):
 
 
 def main() -> None:
-    reference = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    import os
+    reference = Path(sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FPT_REFERENCE_ROOT", REPO.parent / "reference"))
     table = []
     for rel, dtype, source in HEADERS:
         table.extend(parse_header(reference / rel, dtype, source))

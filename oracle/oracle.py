@@ -234,7 +234,7 @@ def exp2_hinge(x: np.ndarray, constant_set: int = 0, repeats: int = 1) -> np.nda
     return out
 
 
-EXP2_FULL_D3, EXP2_FULL_PWL2 = 0, 1
+EXP2_FULL_D3, EXP2_FULL_PWL2, EXP2_FULL_D2_SAFE, EXP2_FULL_PWL2_SAFE_F16 = 0, 1, 2, 3
 
 
 def exp2_full(x: np.ndarray, variant: int = EXP2_FULL_D3) -> np.ndarray:
@@ -308,7 +308,7 @@ def rope_apply(q: np.ndarray, k: np.ndarray, increments: np.ndarray, io_bf16: bo
     return qo, ko
 
 
-ATTN_SOFTCAP_TANH, ATTN_SIGMOID_B3, ATTN_SOFTMAX = 0, 1, 2
+ATTN_SOFTCAP_TANH, ATTN_SIGMOID_B3, ATTN_SOFTMAX, ATTN_SOFTCAP_NATIVE, ATTN_SIGMOID_NATIVE = 0, 1, 2, 3, 4
 
 
 def attention_rows(q, k, v, b: int, hq: int, rows, mode: int, causal: bool, scale: float,

@@ -33,7 +33,7 @@ def forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n):
     return out, lse
 
 
-def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad=0):
+def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad=0, emu=None):
     import torch
     B, S, Hq, D = q.shape
     Hk = k.shape[2]
@@ -45,9 +45,15 @@ def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, l
     workspace = torch.empty(need, dtype=torch.uint8, device=cuda)
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
     arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
-    fpt.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(),
-             v.data_ptr(), out.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
-             arr(out), arr(dout), mode, int(causal), scale, softcap, log2_n, softcap_grad, status.data_ptr(), stream())
+    if emu is None:
+        fpt.call("fpt_attention_bwd", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(),
+                 v.data_ptr(), out.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
+                 arr(out), arr(dout), mode, int(causal), scale, softcap, log2_n, softcap_grad, status.data_ptr(), stream())
+    else:           # (backend, frequency) of the software exponential
+        fpt.call("fpt_attention_bwd_routed", dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(),
+                 k.data_ptr(), v.data_ptr(), out.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q),
+                 arr(k), arr(v), arr(out), arr(dout), mode, int(causal), scale, softcap, log2_n, softcap_grad, emu[0], emu[1],
+                 status.data_ptr(), stream())
     torch.cuda.synchronize()
     assert int(status.item()) == 0, hex(int(status.item()) & 0xFFFFFFFF)
     return dq, dk, dv
@@ -76,6 +82,13 @@ CASES = [
     (1, 77, 1, 1, 1, False, 0.0, 12, 0),
     (1, 257, 4, 2, 2, False, 0.0, 12, 0),
     (1, 130, 2, 1, 1, True, 0.0, 12, 0),
+    # the native twins: tanh on the special-function unit with 1 - t^2, exact sigmoid with p (1 - p)
+    (1, 384, 4, 2, 3, True, 50.0, 12, 1),
+    (2, 333, 4, 2, 3, False, 30.0, 12, 1),
+    (1, 256, 2, 1, 3, True, 100.0, 12, 1),
+    (1, 512, 2, 1, 4, False, 0.0, 9, 0),
+    (1, 384, 4, 2, 4, True, 0.0, 12, 0),
+    (1, 77, 1, 1, 4, False, 0.0, 7, 0),
 ]
 
 
@@ -99,6 +112,45 @@ def test_backward_matches_the_cpu_restatement(fpt, cuda, oracle, case):
     close(dq, want_dq, "dq")
     close(dk, want_dk, "dk")
     close(dv, want_dv, "dv")
+
+
+@pytest.mark.parametrize("backend,freq,bound", [(0, 8, 2e-2), (0, 32, 2e-2), (2, 12, 2e-2), (2, 32, 2e-2), (3, 12, 3e-2),
+                                                (3, 32, 2e-2), (1, 16, 5e-2)])
+def test_backward_with_routed_software_exponential(fpt, cuda, backend, freq, bound):
+    """Four of every `freq` columns recompute their probability with a software exponential (cubic 8.8e-5, quadratic
+    2.7e-3, fp16 two-piece line 1.1e-2, two-piece line 2.1e-2 relative): gradients stay within the bound of the float64
+    restatement, relative to the largest gradient, and differ from the unrouted kernel (the route is taken)."""
+    import torch
+    from oracle import attention_bwd
+    B, S, Hq, Hk, D = 1, 384, 4, 2, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(2468)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    dout = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    for causal in (True, False):
+        out, lse = forward(fpt, cuda, q, k, v, 2, causal, scale, 0.0, 12)
+        base = backward(fpt, cuda, q, k, v, out, lse, dout, 2, causal, scale, 0.0, 12, emu=(backend, 0))
+        dq, dk, dv = backward(fpt, cuda, q, k, v, out, lse, dout, 2, causal, scale, 0.0, 12, emu=(backend, freq))
+        _, _, want_dq, want_dk, want_dv = attention_bwd.attention_fwd_bwd(bits(q), bits(k), bits(v), bits(dout), 2, causal, scale)
+        close(dq, want_dq, "dq", bound)
+        close(dk, want_dk, "dk", bound)
+        close(dv, want_dv, "dv", bound)
+        assert not torch.equal(dv, base[2]), "the routed kernel must not be the unrouted one"
+    lib = fpt.load()
+    t = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=cuda)
+    ws = torch.zeros(4096, dtype=torch.uint8, device=cuda)
+    st = torch.zeros(1, dtype=torch.int32, device=cuda)
+    arr = (ctypes.c_int64 * 3)(128 * 128, 128, 128)
+    lse1 = torch.zeros(1, 1, 128, device=cuda)
+    common = lambda mode, be, fr: lib.fpt_attention_bwd_routed(
+        t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(), t.data_ptr(),
+        lse1.data_ptr(), ws.data_ptr(), 4096, 1, 128, 1, 1, 128, arr, arr, arr, arr, arr, mode, 0, 1.0, 30.0, 12, 0, be, fr,
+        st.data_ptr(), None)
+    assert common(2, 0, 10) == -5 and common(2, 9, 8) == -5      # unknown frequency, unknown backend
+    assert common(0, 0, 8) == -5 and common(1, 0, 8) == -5       # routed for the plain soft-max only
 
 
 def test_plain_softmax_backward_matches_torch_autograd(fpt, cuda):

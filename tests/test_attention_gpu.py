@@ -106,6 +106,16 @@ CASES = [
     (1, 1, 2, 1, 2, True, 0.0, 12),
     (1, 1, 1, 1, 0, False, 50.0, 12),
     (1, 257, 4, 1, 0, True, 50.0, 12),
+    # the native twins of the two score-mods: tanh.approx soft-cap (both layouts: cap 50 column-split, cap 100 not) and
+    # the ex2 + rcp sigmoid, against the oracle's exact tanh / exact sigmoid
+    (1, 384, 4, 2, 3, True, 50.0, 12),
+    (2, 333, 4, 2, 3, False, 30.0, 12),
+    (1, 640, 2, 1, 3, True, 100.0, 12),
+    (1, 1, 1, 1, 3, False, 50.0, 12),
+    (1, 512, 2, 2, 4, False, 0.0, 9),
+    (1, 384, 2, 1, 4, True, 0.0, 12),
+    (1, 77, 1, 1, 4, False, 0.0, 7),
+    (1, 2048, 2, 1, 4, False, 0.0, 11),
 ]
 
 
@@ -276,10 +286,42 @@ def test_routed_two_piece_exponential(fpt, cuda, oracle, freq):
         run_attention(fpt, cuda, q, k, v, 0, True, scale, 30.0, 12, exp2_emu_freq=freq, exp2_emu_backend=1)
 
 
+@pytest.mark.parametrize("backend,name,err,oracle_bound", [(2, "d2_safe", 2.7e-3, 2e-2), (3, "pwl2_safe_f16", 1.14e-2, 3.5e-2)])
+@pytest.mark.parametrize("freq", [12, 32])
+def test_routed_endpoint_preserving_exponentials(fpt, cuda, oracle, backend, name, err, oracle_bound, freq):
+    """The two retained routed backends of the reference (forward frequency 12): outputs stay within 2e-2 of the
+    fp32 oracle (3.5e-2 for the fp16 line, whose own error is 1.1e-2 on the routed weights) and within the evaluator's
+    error plus two bf16 roundings of the all-SFU kernel;
+    rows that rescale several times (scores growing along the sequence) stay finite and within the same bound, which is
+    what the endpoint constraints p(0) = 1, p(1) = 2 are for."""
+    import torch
+    B, S, Hq, Hk, D = 1, 640, 2, 1, 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(97)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g) * torch.linspace(0.3, 5.0, S, device=cuda).view(1, S, 1, 1)
+    q, k = q.to(torch.bfloat16), k.to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    qb, kb, vb = bits(q), bits(k), bits(v)
+    for causal in (True, False):
+        base, lse0, st0 = run_attention(fpt, cuda, q, k, v, 2, causal, scale, 0.0, 12, exp2_emu_freq=0)
+        out, lse, st = run_attention(fpt, cuda, q, k, v, 2, causal, scale, 0.0, 12, exp2_emu_freq=freq, exp2_emu_backend=backend)
+        assert st0 == 0 and st == 0 and not torch.isnan(out.float()).any()
+        assert not torch.equal(out, base), "the routed kernel must not be the unrouted one"
+        assert float((lse - lse0).abs().max()) < 2 * err
+        assert float((out.float() - base.float()).abs().max()) < 1.2 * err + 1.6e-2
+        for h in range(Hq):
+            want = oracle.attention_rows(qb, kb, vb, 0, h, np.arange(S), 2, causal, scale, 0.0, 12)
+            assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < oracle_bound, (name, freq, causal)
+    with pytest.raises(Exception):      # offered for the plain soft-max only
+        run_attention(fpt, cuda, q, k, v, 0, True, scale, 30.0, 12, exp2_emu_freq=freq, exp2_emu_backend=backend)
+
+
 def test_routed_exp2_rejects_unbuilt_frequencies(fpt, cuda):
     import torch
     q = torch.zeros(1, 128, 1, 128, dtype=torch.bfloat16, device=cuda)
-    for mode, freq in ((2, 4), (2, 10), (2, -8), (1, 12)):
+    for mode, freq in ((2, 4), (2, 10), (2, -8), (1, 12), (3, 8), (4, 8)):
         with pytest.raises(Exception):
             run_attention(fpt, cuda, q, q, q, mode, False, 1.0, 0.0, 12, exp2_emu_freq=freq)
 

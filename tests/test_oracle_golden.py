@@ -134,6 +134,24 @@ def test_full_range_exp2_restatements(oracle):
     assert 7.99 < float(oracle.exp2_full(np.array([x], dtype=np.float32), 0)[0]) < 8.0
 
 
+def test_endpoint_preserving_exp2_fits_reproduce_the_published_errors(oracle):
+    """The two routed backends the reference retains: their maximum relative errors as published (quadratic 2.679e-3,
+    packed fp16 two-piece line 1.132e-2 after coefficient rounding; reference: extras/paper/manuscript/
+    appendix_exp2.tex:60-62 and :74-77), exact powers of two at every integer, +0 at and below the clamp."""
+    xs = np.linspace(-20, 10, 2_000_001).astype(np.float32)
+    truth = np.exp2(xs.astype(np.float64))
+    for variant, published in ((oracle.EXP2_FULL_D2_SAFE, 2.679e-3), (oracle.EXP2_FULL_PWL2_SAFE_F16, 1.132e-2)):
+        worst = np.abs(oracle.exp2_full(xs, variant).astype(np.float64) / truth - 1).max()
+        assert abs(worst / published - 1) < 2e-3, (variant, worst)
+        ints = np.arange(-126, 128, dtype=np.float32)
+        assert np.array_equal(oracle.exp2_full(ints, variant), np.exp2(ints.astype(np.float64)).astype(np.float32))
+        low = oracle.exp2_full(np.array([-127.0, -127.5, -1e6, -np.inf, np.nan], dtype=np.float32), variant)
+        assert np.all(low.view(np.uint32) == 0)
+    # a fraction that rounds to 1 in fp16 lands on the next power of two exactly (continuity across the integer)
+    x = np.nextafter(np.float32(3.0), np.float32(0.0))
+    assert float(oracle.exp2_full(np.array([x], dtype=np.float32), oracle.EXP2_FULL_PWL2_SAFE_F16)[0]) == 8.0
+
+
 def test_error_ceilings_against_true_functions(oracle):
     """Published error bounds of the primary programs (struct comments / reference GPU checks)."""
     x = np.linspace(-15, 15, 30001).astype(np.float32)

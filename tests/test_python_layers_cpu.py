@@ -15,7 +15,7 @@ from fast_polynomial_transcendentals_b200.sfu_repro.rope import (SOLLYA_D3_D4, U
                                                                  reduce_to_quarter_turn, rope_phase_increments)
 
 ROOT = Path(__file__).resolve().parents[1]
-REFERENCE_TEST = Path("/root/reference/tests/test_fa4_config.py")
+REFERENCE_TEST = Path(os.environ.get("FPT_REFERENCE_ROOT", ROOT.parent / "reference")) / "tests" / "test_fa4_config.py"
 
 
 def test_canonical_attention_configs_resolve_against_our_runtime():

@@ -174,3 +174,58 @@ def test_device_timeout_reported_by_the_kernel_raises_in_python(cuda):
     with pytest.raises(RuntimeError, match="0x80000006"):
         fa4._b200_flash_attn_bwd(q, q, q, out, out, lse, None, True, 0.0)
     fa4.check_attention_status(cuda)
+
+
+def test_every_canonical_component_configuration_runs_forward_and_backward(cuda):
+    """`b2_component_configs()`, `b3_component_configs()` and `b5_component_configs()` of the reference (reference:
+    src/sfu_repro/fa4.py:650-752), every entry, through `build_fa4_module` on this package's runtime: the native arms
+    (SFU tanh soft-cap, SFU sigmoid) and the routed soft-max arms (forward frequency 12, backward 32) included.  Outputs
+    and gradients against plain torch with the exact functions (the polynomial arms within their published error)."""
+    import torch
+    from fast_polynomial_transcendentals_b200.sfu_repro import fa4
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(21)
+
+    def torch_attention(q, k, v, kind, cap=30.0):
+        qf, kf, vf = (t.detach().float().requires_grad_(True) for t in (q, k, v))
+        group = qf.shape[1] // kf.shape[1]
+        kk, vv = kf.repeat_interleave(group, dim=1), vf.repeat_interleave(group, dim=1)
+        s = qf @ kk.transpose(-1, -2) / math.sqrt(D)
+        S = s.shape[-1]
+        mask = torch.ones(S, S, dtype=torch.bool, device=cuda).tril()
+        if kind == "sigmoid":
+            p = torch.sigmoid(s - math.log(S)) * mask
+        else:
+            if kind == "softcap":
+                s = cap * torch.tanh(s / cap)
+            p = torch.softmax(s.masked_fill(~mask, float("-inf")), dim=-1)
+        return p @ vv, (qf, kf, vf)
+
+    def run(config, kind, B, Hq, Hk, S, out_tol, grad_tol, sequence_length=None):
+        module = fa4.build_fa4_module(config, head_dim=D, sequence_length=sequence_length).to(cuda)
+        module.q_norm = module.k_norm = None
+        q = torch.randn(B, Hq, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        k = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        v = torch.randn(B, Hk, S, D, device=cuda, generator=g).to(torch.bfloat16).requires_grad_(True)
+        dout = torch.randn(B, Hq, S, D, device=cuda, generator=g).to(torch.bfloat16)
+        out = module(q, k, v)
+        out.backward(dout)
+        fa4.check_attention_status(cuda)
+        want, leaves = torch_attention(q, k, v, kind)
+        want.backward(dout.float())
+        scale = float(want.abs().max()) if kind == "sigmoid" else 1.0
+        assert float((out.float() - want).abs().max()) <= out_tol * scale, (kind, "out")
+        for got, leaf, name in ((q.grad, leaves[0], "dq"), (k.grad, leaves[1], "dk"), (v.grad, leaves[2], "dv")):
+            err = float((got.float() - leaf.grad).abs().max())
+            assert err <= grad_tol * float(leaf.grad.abs().max()), (kind, name, err)
+
+    b2 = fa4.b2_component_configs()
+    run(b2["native"], "softcap", 1, 4, 2, 384, 2e-2, 2e-2)
+    run(b2["polynomial"], "softcap", 1, 4, 2, 384, 0.3, 0.5)           # the D4 tanh inflates small scores by 8.6 %
+    b3 = fa4.b3_component_configs()
+    run(b3["native"], "sigmoid", 1, 1, 1, 4096, 2e-2, 2e-2, sequence_length=4096)
+    run(b3["polynomial"], "sigmoid", 1, 1, 1, 4096, 0.15, 0.15, sequence_length=4096)
+    for name, config in fa4.b5_component_configs().items():
+        loose = name == "pwl2_safe_f16"
+        run(config, "softmax", 1, 4, 2, 384, 3.5e-2 if loose else 2e-2, 3e-2 if loose else 2e-2)

@@ -126,7 +126,7 @@ def test_exp2_hinge_bit_exact_and_native_close(fpt, cuda, oracle):
     assert float(rel) < 0.0115  # published max-rel 0.0109
 
 
-@pytest.mark.parametrize("variant,bound", [(0, 8.9e-5), (1, 2.2e-2)])
+@pytest.mark.parametrize("variant,bound", [(0, 8.9e-5), (1, 2.2e-2), (2, 2.7e-3), (3, 1.14e-2)])
 def test_full_range_exp2_bit_exact_and_accurate(fpt, cuda, oracle, variant, bound):
     """The software exponentials that the attention kernel mixes with the special-function unit, as a flat kernel."""
     import torch
@@ -147,7 +147,14 @@ def test_full_range_exp2_bit_exact_and_accurate(fpt, cuda, oracle, variant, boun
         inside = xs >= -126
         rel = np.abs(got[inside].astype(np.float64) / np.exp2(xs[inside].astype(np.float64)) - 1)
         assert rel.max() < bound
-        assert np.all(got[xs <= -127] < 1.2e-38) and np.all(got[xs <= -127] >= 0.0)   # cubic: +0; line: 0.989 * 2^-126
+        assert np.all(got[xs <= -127] < 1.2e-38) and np.all(got[xs <= -127] >= 0.0)   # +0 (0.989 * 2^-126 for the line of variant 1)
+        if variant >= 2:        # endpoint-preserving fits: 2^n exactly at every integer, so rescaling steps compose
+            ints = np.arange(-126, 128, dtype=np.float32)
+            xi = torch.from_numpy(ints).to(cuda)
+            oi = torch.empty(256, dtype=torch.float32, device=cuda)[:ints.size]
+            fpt.call("fpt_exp2_full_f32", oi.data_ptr(), xi.data_ptr(), ints.size, variant, stream())
+            torch.cuda.synchronize()
+            assert np.array_equal(oi.cpu().numpy(), np.exp2(ints.astype(np.float64)).astype(np.float32))
     assert fpt.load().fpt_exp2_full_f32(None, None, 5, variant, None) != 0            # null pointers
     x = torch.zeros(9, dtype=torch.float32, device=cuda)
     assert fpt.load().fpt_exp2_full_f32(x.data_ptr() + 4, x.data_ptr(), 4, variant, None) != 0   # misaligned
