@@ -11,8 +11,14 @@ L2-resident endpoint N = 2^20, in both forms; those numbers, the SwiGLU and B3 l
 `functions` / `extras`.  `e2e` is the same sweep through the public `spline_ops` API from pinned HOST buffers
 with both PCIe copies inside the timed region.  Prints ONE JSON line on rank 0.
 
-`--impl reference` times the CPU path instead: this repository's exact packed-arithmetic emulator (the port of
-the reference's programs used as the parity oracle) with all host threads on a bounded sample of the sweep.
+`--impl reference` times the reference's CPU path instead, on the host cores: (i) PyTorch's native CPU functions on
+the same seeded inputs with every host thread, and (ii) the reference's own vectorised packed-arithmetic replays
+(its fitters' split-rounded Horner in numpy float16, its polynomial sin/cos in torch), each step a bounded sample of
+2^24 elements per function.  The exact single-rounding emulator this repository uses as its parity oracle is timed
+beside them as a third leg and reported, not counted into the value.
+
+`--compare-reference-kernels` (a separate invocation, 1 GPU) times this library's kernels next to the reference's own
+kernels where those have been compiled into oracle/_ref (`make -C oracle ref`), same inputs, same protocol.
 """
 from __future__ import annotations
 
@@ -37,6 +43,13 @@ NOMINAL_HBM_GBS = 8000.0
 SIGMOID_TRAFFIC_BYTES_PER_LAUNCH = int(4 * 134.225152e6 + (4 * 134.217728e6 - (134.217728e6 - 82.393088e6)))
 
 
+def measured_sustained_tflops():
+    path = ROOT / "MEASURED_PEAKS.json"
+    if path.exists():
+        return float(json.loads(path.read_text()).get("bf16_tflops_sustained", 1400.0))
+    return 1400.0
+
+
 def measured_peaks():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -47,68 +60,160 @@ def measured_peaks():
 
 # ------------------------------------------------------------------------------------ CPU arm
 
+CPU_FUNCTIONS = ("sigmoid", "tanh", "silu", "exp2", "sincos")
+
+
 def cpu_sample_inputs(n):
     import numpy as np
     rng = np.random.default_rng(SEED)
-    u8 = rng.uniform(-8, 8, n).astype(np.float16).view(np.uint16)
-    frac = rng.uniform(0, 1, n).astype(np.float16).view(np.uint16)
+    u8 = rng.uniform(-8, 8, n).astype(np.float16)
+    frac = rng.uniform(0, 1, n).astype(np.float16)
     ang = rng.uniform(-math.pi, math.pi, n).astype(np.float32)
     return u8, frac, ang
 
 
-def cpu_sweep(oracle, inputs):
-    """One pass of the sweep on the CPU emulator; returns elements processed."""
-    u8, frac, ang = inputs
-    oracle.unary(oracle.find_program("SIGMOID_FWD_D3", 0), u8)
-    oracle.unary(oracle.find_program("TANH_FWD_D4", 0), u8)
-    oracle.unary(oracle.find_program("SWISH_FWD_D3", 0), u8)
-    oracle.exp2_hinge(frac, 0)
-    oracle.sincos_packed("d5_d6_half_turn_fp16", ang)
-    return 5 * u8.size
+def host_threads():
+    """Every core this process may use (torchrun exports OMP_NUM_THREADS=1, which the CPU legs override)."""
+    try:
+        return len(os.sched_getaffinity(0))
+    except AttributeError:
+        return os.cpu_count() or 1
 
 
-def cpu_baseline(sample_elems=1 << 22, budget_s=12.0):
-    from oracle import oracle
-    oracle.build()
-    threads = oracle.set_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1
-    inputs = cpu_sample_inputs(sample_elems)
-    cpu_sweep(oracle, inputs)
-    t0 = time.perf_counter()
-    done, passes = 0, 0
-    while time.perf_counter() - t0 < budget_s and passes < 8:
-        done += cpu_sweep(oracle, inputs)
-        passes += 1
-    dt = time.perf_counter() - t0
-    return {"value": done / dt, "unit": "elements/s", "cores": threads, "kind": "port",
-            "sample": f"{passes} passes of the 5-function sweep at 2^{int(math.log2(sample_elems))} elements per "
-                      f"function, exact packed-FMA emulator (OpenMP, all host threads)"}
+class CpuLegs:
+    """The three CPU legs over one set of seeded inputs; every leg returns {function: seconds} for one pass.
+
+    (i)   torch_native: torch.sigmoid / tanh / F.silu / exp2 on fp16 tensors, torch.sin + torch.cos on fp32 angles,
+          intra-op threads = every host core (the reference's isolated sweep compares against these PyTorch natives,
+          scripts/benchmark_report_function_speed.py:112-134, there on the GPU);
+    (ii)  reference_replay: the reference's own CPU arithmetic for the polynomial programs: split-rounded fp16 Horner
+          (autonumerics_zero/evolution/fit_all_degrees.py:59-96) for sigmoid D3, tanh D4, SiLU D3 in numpy, the array cut
+          into one slice per host core and the slices run on a thread pool (numpy's element-wise loops release the
+          interpreter lock; the reference itself calls the function on one thread), polynomial_sincos
+          (src/sfu_repro/rope/polynomial_sincos.py:138-165) in torch with every core; the reference has no CPU evaluator
+          of the exp2 hinge, so that function has no entry;
+    (iii) exact_emulator: this repository's single-rounding soft-float port (OpenMP, every core)."""
+
+    def __init__(self, n_native, n_replay, n_emulator):
+        import numpy as np
+        import torch
+        self.np, self.torch = np, torch
+        self.threads = host_threads()
+        torch.set_num_threads(self.threads)
+        self.n = {"torch_native": n_native, "reference_replay": n_replay, "exact_emulator": n_emulator}
+        u8, frac, ang = cpu_sample_inputs(max(n_native, n_replay, n_emulator))
+        self.u8, self.frac, self.ang = u8, frac, ang
+        self.t_u8, self.t_frac, self.t_ang = (torch.from_numpy(a[:n_native]) for a in (u8, frac, ang))
+        self.oracle = None
+
+    @staticmethod
+    def _timed(fn):
+        t0 = time.perf_counter()
+        fn()
+        return time.perf_counter() - t0
+
+    def torch_native(self):
+        torch, F = self.torch, self.torch.nn.functional
+        return {"sigmoid": self._timed(lambda: torch.sigmoid(self.t_u8)), "tanh": self._timed(lambda: torch.tanh(self.t_u8)),
+                "silu": self._timed(lambda: F.silu(self.t_u8)), "exp2": self._timed(lambda: torch.exp2(self.t_frac)),
+                "sincos": self._timed(lambda: (torch.sin(self.t_ang), torch.cos(self.t_ang)))}
+
+    def reference_replay(self):
+        from fast_polynomial_transcendentals_b200.sfu_repro.rope.polynomial_sincos import polynomial_sincos
+        from oracle import reference_replays
+        from concurrent.futures import ThreadPoolExecutor
+        n = self.n["reference_replay"]
+        ang = self.torch.from_numpy(self.ang[:n])
+        slices = self.np.array_split(self.u8[:n], self.threads)
+
+        def replay(name):
+            with ThreadPoolExecutor(self.threads) as pool:
+                list(pool.map(lambda part: reference_replays.activation_replay_fp16(name, part), slices))
+        out = {name: self._timed(lambda name=name: replay(name)) for name in ("sigmoid", "tanh", "silu")}
+        out["sincos"] = self._timed(lambda: polynomial_sincos(ang, accurate_reduction=False))
+        return out
+
+    def exact_emulator(self):
+        if self.oracle is None:
+            from oracle import oracle
+            oracle.build()
+            oracle.set_threads(self.threads)
+            self.oracle = oracle
+        o, n, np = self.oracle, self.n["exact_emulator"], self.np
+        u8, frac, ang = self.u8[:n].view(np.uint16), self.frac[:n].view(np.uint16), self.ang[:n]
+        return {"sigmoid": self._timed(lambda: o.unary(o.find_program("SIGMOID_FWD_D3", 0), u8)),
+                "tanh": self._timed(lambda: o.unary(o.find_program("TANH_FWD_D4", 0), u8)),
+                "silu": self._timed(lambda: o.unary(o.find_program("SWISH_FWD_D3", 0), u8)),
+                "exp2": self._timed(lambda: o.exp2_hinge(frac, 0)),
+                "sincos": self._timed(lambda: o.sincos_packed("d5_d6_half_turn_fp16", ang))}
+
+    def cores(self, leg):
+        return self.threads
+
+    def summarise(self, leg, passes):
+        """passes: list of {function: seconds}.  Median seconds per function -> elements/s per function and for the leg."""
+        n = self.n[leg]
+        per = {}
+        for fn in passes[0]:
+            ts = sorted(p[fn] for p in passes)
+            per[fn] = n / ts[len(ts) // 2]
+        total_s = sum(n / v for v in per.values())
+        return {"elements_per_s": len(per) * n / total_s, "per_function_elements_per_s": per, "functions": len(per),
+                "elements_per_function": n, "passes": len(passes), "cores": self.cores(leg)}
+
+
+def cpu_baseline():
+    """Bounded CPU legs for the GPU arm's line: about 10-20 s of CPU work on rank 0."""
+    legs = CpuLegs(1 << 24, 1 << 22, 1 << 22)
+    out = {}
+    for leg, passes in (("torch_native", 4), ("reference_replay", 1), ("exact_emulator", 2)):
+        fn = getattr(legs, leg)
+        if leg != "reference_replay":
+            fn()
+        out[leg] = legs.summarise(leg, [fn() for _ in range(passes)])
+    done = sum(out[leg]["functions"] * out[leg]["elements_per_function"] for leg in ("torch_native", "reference_replay"))
+    spent = sum(out[leg]["functions"] * out[leg]["elements_per_function"] / out[leg]["elements_per_s"]
+                for leg in ("torch_native", "reference_replay"))
+    return {"value": done / spent, "unit": "elements/s", "cores": legs.threads, "kind": "port",
+            "sample": "the reference's CPU path restated: torch CPU natives (5 functions, 2^24 fp16 / fp32 elements each, all "
+                      "host threads) + the reference's vectorised replays (split-rounded fp16 Horner for sigmoid / tanh / "
+                      "SiLU in numpy, polynomial_sincos in torch; 2^22 elements each); value = all their elements over all "
+                      "their time; the exact single-rounding emulator (2^22 per function) rides in `legs` and is not counted",
+            "legs": out}
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    from oracle import oracle
-    oracle.build()
-    threads = oracle.set_threads(os.cpu_count() or 1)     # torchrun exports OMP_NUM_THREADS=1
-    n = 1 << 21
-    inputs = cpu_sample_inputs(n)
+    n = 1 << 24
+    legs = CpuLegs(n, n, 1 << 21)
+    counted = ("torch_native", "reference_replay")
     for _ in range(max(1, min(args.warmup, 2))):
-        cpu_sweep(oracle, inputs)
+        legs.torch_native()
+    legs.reference_replay()
+    passes = {leg: [] for leg in counted}
     t0 = time.perf_counter()
-    done = 0
     for _ in range(args.steps):
-        done += cpu_sweep(oracle, inputs)
+        for leg in counted:
+            passes[leg].append(getattr(legs, leg)())
     dt = time.perf_counter() - t0
-    value = done / dt
+    detail = {leg: legs.summarise(leg, passes[leg]) for leg in counted}
+    emulator = legs.exact_emulator()
+    detail["exact_emulator"] = legs.summarise("exact_emulator", [legs.exact_emulator(), emulator])
+    elements_per_step = sum(detail[leg]["functions"] for leg in counted) * n
+    value = elements_per_step * args.steps / dt
+    sample = (f"each step = torch CPU natives (sigmoid, tanh, SiLU, exp2 on fp16; sin + cos on fp32) and the reference's "
+              f"vectorised replays (split-rounded fp16 Horner for sigmoid D3 / tanh D4 / SiLU D3, polynomial_sincos), 2^24 "
+              f"elements per function (a bounded sample of the 2^28 workload); value = elements of both legs over the "
+              f"wall time of the step loop")
     line = {
         "impl": "reference", "metric": "elements_per_s_fp16_function_sweep", "value": value, "unit": "elements/s",
         "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt / args.steps * 1e3,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
         "config": workload_config(args.gpus),
-        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": threads, "kind": "port",
-                         "sample": f"each step = the 5-function sweep at 2^21 elements per function (bounded "
-                                   f"sample of the 2^28 workload), exact packed-FMA emulator, all host threads"},
+        "cpu_baseline": {"value": value, "unit": "elements/s", "cores": legs.threads, "kind": "port", "sample": sample,
+                         "legs": detail},
         "e2e": {"value": value, "unit": "elements/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
@@ -117,7 +222,9 @@ def run_reference_arm(args):
 def workload_config(n_gpus):
     return {"workload": "BASELINE config[1]: isolated FP16 function sweep, HBM endpoint N=2^28 per function "
                         "(sigmoid D3, tanh D4, SiLU D3, exp2 hinge, sin/cos D5/D6), polynomial vs native SFU",
-            "elements_per_function_per_gpu": N_HBM, "functions": 5, "sharding": f"{n_gpus} x independent element ranges",
+            "elements_per_function_per_gpu": N_HBM, "functions": 5,
+            "sharding": f"headline: {n_gpus} x independent 2^28-element ranges (weak scaling); the partitioning of ONE seeded "
+                        "problem by element ranges, expert groups and (batch, head) blocks is timed under extras.sharded",
             "l2": "inputs of 512 MiB..1 GiB per function exceed the 126 MB L2; no flush needed"}
 
 
@@ -297,22 +404,34 @@ def run_gpu_arm(args):
     value = elements_per_step * args.steps / (total_ms * 1e-3)
     gpu_launches = len(poly_hbm) * args.steps * world   # whole job: every rank launches the same five kernels per step
 
-    # ---- e2e through the public API with host buffers: every rank its own sweep, whole-job value = all ranks'
-    # elements over the slowest rank's time
+    # the headline buffers are needed again only on rank 0 (native twins, L2 endpoint); free them elsewhere
+    if rank != 0:
+        del u8, frac, ang, out16, out_sc, poly_hbm
+        torch.cuda.empty_cache()
+
+    # ---- e2e through the public API with host buffers: every rank its own 2^28-element sweep, whole-job value = all
+    # ranks' elements over the slowest rank's time; beside it the same copies with no kernel between them
     if world > 1:
         dist.barrier()
-    e2e = bench_e2e(torch, spline_ops, HostPipeline, device)
+    e2e = bench_e2e(torch, spline_ops, HostPipeline, device, max(5, args.steps), lambda: barrier(True))
     if host_binding:
         e2e["host_binding"] = host_binding
         os.sched_setaffinity(0, all_cpus)      # the CPU legs below use every core again
     if world > 1:
-        t = torch.tensor([e2e["ms_per_step"]], device=device)
+        t = torch.tensor([e2e["ms_per_step"], e2e["copy_only"]["ms_per_step"]], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e["ms_per_step"] = float(t.item())
-        e2e["value"] = world * 5 * e2e["elements_per_function"] / (e2e["ms_per_step"] * 1e-3)
+        e2e["ms_per_step"], e2e["copy_only"]["ms_per_step"] = float(t[0].item()), float(t[1].item())
         e2e["h2d_bytes_per_step"] *= world
         e2e["d2h_bytes_per_step"] *= world
         e2e["path"] += f"; {world} ranks at once, slowest rank's time"
+    e2e["value"] = world * 5 * e2e["elements_per_function"] / (e2e["ms_per_step"] * 1e-3)
+    copy = e2e["copy_only"]
+    copy["value"] = world * 5 * e2e["elements_per_function"] / (copy["ms_per_step"] * 1e-3)
+    copy["gbs_per_direction_per_rank"] = e2e["h2d_bytes_per_step"] / world / (copy["ms_per_step"] * 1e-3) / 1e9
+    e2e["fraction_of_copy_only_rate"] = copy["ms_per_step"] / e2e["ms_per_step"]
+
+    # ---- the partitioning of one seeded problem over the ranks (all ranks take part)
+    sharded = bench_sharded(torch, dist, lib, _lib, device, rank, world, hbm_peak, measured_peaks()[1])
 
     if rank != 0:
         if world > 1:
@@ -360,6 +479,7 @@ def run_gpu_arm(args):
     extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep)
     extras["b3_config1"] = bench_b3(torch, lib, _lib, device, S, time_graph)
     extras["attention_fwd_bf16"] = bench_attention(torch, lib, _lib, device, S, time_sweep)
+    extras["sharded"] = sharded
 
     cpu = cpu_baseline()
     dominant = functions["sigmoid"]
@@ -367,7 +487,7 @@ def run_gpu_arm(args):
         "metric": "elements_per_s_fp16_function_sweep", "value": value, "unit": "elements/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": workload_config(world),
-        "roofline": {"bound": "hbm", "achieved": dominant["poly_gbs"], "peak": hbm_peak, "unit": "GB/s",
+        "impl": "ours", "roofline": {"bound": "hbm", "achieved": dominant["poly_gbs"], "peak": hbm_peak, "unit": "GB/s",
                      "frac": dominant["poly_gbs"] / hbm_peak, "traffic": SIGMOID_TRAFFIC_BYTES_PER_LAUNCH,
                      "traffic_source": "ncu capture at 2^26 elements (dram read 134.23 MB, write 82.39 MB = algorithmic minus "
                                        "what stays dirty in L2), reads scaled x4, the L2-resident remainder kept constant",
@@ -381,6 +501,272 @@ def run_gpu_arm(args):
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
+
+
+# ---- one seeded problem, addressed by GLOBAL element index, so that a shard is a slice of the same tensor at every N
+
+def hashed_uniform(torch, lo, hi, stream_id, device, chunk=1 << 26):
+    """U[0,1) fp32 for global indices [lo, hi): a 32-bit integer hash of (index, stream), generated in chunks."""
+    out = torch.empty(hi - lo, dtype=torch.float32, device=device)
+    for a in range(lo, hi, chunk):
+        b = min(hi, a + chunk)
+        x = torch.arange(a, b, device=device, dtype=torch.int64)
+        x = (x * 2654435761 + (SEED + 7919 * stream_id) * 40503) & 0xFFFFFFFF
+        for _ in range(2):
+            x = ((x ^ (x >> 16)) * 0x45D9F3B) & 0xFFFFFFFF
+        x = x ^ (x >> 16)
+        out[a - lo:b - lo] = x.to(torch.float32) * (1.0 / 4294967296.0)
+    return out
+
+
+def hashed_normal(torch, index, stream_id, std=1.0):
+    """N(0, std^2) fp32 for a tensor of global int64 indices (Box-Muller on two hashed uniforms)."""
+    def u(salt):
+        x = (index * 2654435761 + (SEED + 7919 * stream_id + salt) * 40503) & 0xFFFFFFFF
+        for _ in range(2):
+            x = ((x ^ (x >> 16)) * 0x45D9F3B) & 0xFFFFFFFF
+        x = x ^ (x >> 16)
+        return (x.to(torch.float32) + 0.5) * (1.0 / 4294967296.0)
+    return torch.sqrt(-2.0 * torch.log(u(1))) * torch.cos(6.283185307179586 * u(2)) * std
+
+
+def bits_checksum(torch, t):
+    """Integer sum of the 16-bit patterns of a tensor (order-independent, so shard sums add up to the whole)."""
+    return int(t.contiguous().view(torch.int16).sum(dtype=torch.int64).item())
+
+
+class L2Flush:
+    """Overwrites a buffer larger than the L2 between timed launches whose working set is not itself larger."""
+
+    def __init__(self, torch, device, nbytes=256 << 20):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+
+    def __call__(self):
+        self.buf.zero_()
+
+
+def time_launch(torch, fn, reps, flush=None, warm=2):
+    """Median CUDA-event duration (ms) of fn() over `reps` launches, an L2 flush before each when given."""
+    for _ in range(warm):
+        fn()
+    times = []
+    for _ in range(reps):
+        if flush:
+            flush()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    times.sort()
+    return times[len(times) // 2]
+
+
+def gather_floats(torch, dist, world, device, values):
+    t = torch.tensor(values, dtype=torch.float64, device=device)
+    if world == 1:
+        return [list(values)]
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [o.tolist() for o in out]
+
+
+def gather_ints(torch, dist, world, device, values):
+    t = torch.tensor(values, dtype=torch.int64, device=device)
+    if world == 1:
+        return [list(values)]
+    out = [torch.empty_like(t) for _ in range(world)]
+    dist.all_gather(out, t)
+    return [o.tolist() for o in out]
+
+
+def bench_sharded(torch, dist, lib, _lib, device, rank, world, hbm_peak, tensor_peak):
+    """north_star's partitioning of ONE seeded problem over the N ranks: contiguous element ranges (function sweep,
+    2^30 elements per function in total: strong scaling), expert groups over the Zipf token counts (B4 SwiGLU), (batch,
+    kv-head group) blocks (attention configurations 4 and 5, the latter with its fused RoPE prologue).  Inputs are a
+    function of the GLOBAL element index, so a shard holds the same values at every N; each shard's output checksum is
+    gathered, their sum is the checksum of the whole output (equal at every N), and rank 0 recomputes the last rank's
+    shard to show that a shard does not depend on who computes it.  No collective touches the data."""
+    import ctypes
+
+    import numpy as np
+    from fast_polynomial_transcendentals_b200 import sharding
+    stream = torch.cuda.current_stream().cuda_stream
+    flush = L2Flush(torch, device)
+    out = {"generator": "inputs are hashes of the global element index (seed 1234): shards are slices of one tensor"}
+
+    # ---- (1) function sweep, contiguous element ranges of 2^30 elements per function
+    total = 1 << 30
+
+    def sweep_shard(r):
+        lo, hi = sharding.element_range(total, r, world)
+        n = hi - lo
+        u8 = (hashed_uniform(torch, lo, hi, 1, device) * 16 - 8).to(torch.float16)
+        frac = hashed_uniform(torch, lo, hi, 2, device).to(torch.float16)
+        ang = hashed_uniform(torch, lo, hi, 3, device) * (2 * math.pi) - math.pi
+        o16 = torch.empty(n, dtype=torch.float16, device=device)
+        osc = torch.empty(2, n, dtype=torch.float16, device=device)
+        kernels = [("sigmoid", lambda: lib.fpt_unary(o16.data_ptr(), u8.data_ptr(), n, 0, 0, 3, 0, 0, stream), o16),
+                   ("tanh", lambda: lib.fpt_unary(o16.data_ptr(), u8.data_ptr(), n, 1, 0, 4, 0, 0, stream), o16),
+                   ("silu", lambda: lib.fpt_unary(o16.data_ptr(), u8.data_ptr(), n, 2, 0, 3, 0, 0, stream), o16),
+                   ("exp2", lambda: lib.fpt_exp2_fraction(o16.data_ptr(), frac.data_ptr(), n, 1, 1, stream), o16),
+                   ("sincos", lambda: lib.fpt_sincos(osc.data_ptr(), ang.data_ptr(), n, 3, 0, stream), osc)]
+        return n, kernels
+
+    n, kernels = sweep_shard(rank)
+    ms, sums = [], []
+    for name, k, result in kernels:
+        def run(k=k, name=name):
+            _lib.check(name, k())
+        ms.append(time_launch(torch, run, 5, flush if n * 4 < (192 << 20) else None))
+        sums.append(bits_checksum(torch, result))
+    del kernels
+    torch.cuda.empty_cache()
+    all_ms = gather_floats(torch, dist, world, device, ms)
+    all_sums = gather_ints(torch, dist, world, device, sums)
+    recheck = None
+    if world > 1 and rank == 0:        # the last rank's shard, recomputed here
+        _, other = sweep_shard(world - 1)
+        redo = []
+        for name, k, result in other:
+            _lib.check(name, k())
+            redo.append(bits_checksum(torch, result))
+        recheck = redo == all_sums[world - 1]
+        del other
+        torch.cuda.empty_cache()
+    names = ("sigmoid", "tanh", "silu", "exp2", "sincos")
+    makespan = sum(max(all_ms[r][i] for r in range(world)) for i in range(5))
+    out["function_sweep_2^30_total"] = {
+        "scaling": "strong: 2^30 elements per function in total, contiguous element ranges of 2^30/N per GPU",
+        "per_function_ms_max_over_ranks": {nm: max(all_ms[r][i] for r in range(world)) for i, nm in enumerate(names)},
+        "elements_per_s": 5 * total / (makespan * 1e-3),
+        "checksum_total_per_function": {nm: sum(all_sums[r][i] for r in range(world)) for i, nm in enumerate(names)},
+        "last_shard_recomputed_on_rank0_equal": recheck}
+
+    # ---- (2) B4 routed experts: 131072 expert-sorted rows x 1408, experts sharded in contiguous groups
+    rows_total, hidden, experts = 16384 * 8, 1408, 64
+    counts = sharding.zipf_expert_counts(rows_total, experts)
+
+    def b4_shard(r):
+        shard = sharding.expert_group(counts, r, world)
+        nrows = shard.last_row - shard.first_row
+        idx = torch.arange(shard.first_row * hidden, shard.last_row * hidden, device=device, dtype=torch.int64)
+        gate = hashed_normal(torch, idx, 11, 1.5).to(torch.bfloat16)
+        up = hashed_normal(torch, idx, 12, 1.5).to(torch.bfloat16)
+        del idx
+        o = torch.empty_like(gate)
+        nel = nrows * hidden
+        return shard, nrows, o, (lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(
+            o.data_ptr(), gate.data_ptr(), up.data_ptr(), nel, 3, 1, 0, stream)))
+
+    shard, nrows, o, run = b4_shard(rank)
+    b4_ms = time_launch(torch, run, 7, flush)
+    b4_sum = bits_checksum(torch, o)
+    del o, run
+    torch.cuda.empty_cache()
+    per_ms = [v[0] for v in gather_floats(torch, dist, world, device, [b4_ms])]
+    per_rows = [v[0] for v in gather_ints(torch, dist, world, device, [nrows])]
+    per_sum = [v[0] for v in gather_ints(torch, dist, world, device, [b4_sum])]
+    recheck = None
+    if world > 1 and rank == 0:
+        _, _, o2, run2 = b4_shard(world - 1)
+        run2()
+        recheck = bits_checksum(torch, o2) == per_sum[world - 1]
+        del o2, run2
+        torch.cuda.empty_cache()
+    out["b4_routed_experts_131072x1408"] = {
+        "experts_per_gpu": experts // world if experts % world == 0 else f"{experts}/{world}",
+        "rows_per_gpu": per_rows, "ms_per_gpu": per_ms, "makespan_ms": max(per_ms),
+        "imbalance_rows_max_over_mean": max(per_rows) / (sum(per_rows) / world),
+        "elements_per_s": rows_total * hidden / (max(per_ms) * 1e-3),
+        "gbs_aggregate": 6 * rows_total * hidden / (max(per_ms) * 1e-3) / 1e9,
+        "frac_of_measured_hbm_per_gpu_at_makespan": 6 * max(per_rows) * hidden / (max(per_ms) * 1e-3) / 1e9 / hbm_peak,
+        "token_counts": "seeded Zipf(1.1) weights over a seeded permutation of 64 experts, multinomial of 131072 assignments",
+        "timing": "median of 7 launches, 256 MiB written between launches (a shard can be smaller than the L2)",
+        "checksum_total": sum(per_sum), "last_shard_recomputed_on_rank0_equal": recheck}
+
+    # ---- (3) attention, (batch, kv-head group) blocks
+    D = 128
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+
+    def block_tensor(b, h0, h1, heads_total, S, stream_id):
+        """[1, S, h1-h0, D] bf16 slice of the global [B, S, heads_total, D] tensor"""
+        s_i = torch.arange(S, device=device, dtype=torch.int64).view(S, 1, 1)
+        h_i = torch.arange(h0, h1, device=device, dtype=torch.int64).view(1, -1, 1)
+        d_i = torch.arange(D, device=device, dtype=torch.int64).view(1, 1, D)
+        idx = ((b * S + s_i) * heads_total + h_i) * D + d_i
+        return hashed_normal(torch, idx, stream_id).to(torch.bfloat16).unsqueeze(0)
+
+    def attention_shard(r, B, S, Hq, Hk, mode, causal, cap, log2_n, with_rope):
+        group = Hq // Hk
+        work = []
+        for blk in sharding.attention_blocks(B, Hq, Hk, r, world):
+            h0, h1 = blk.first_q_head, blk.last_q_head
+            q = block_tensor(blk.batch, h0, h1, Hq, S, 21)
+            k = block_tensor(blk.batch, h0 // group, h1 // group, Hk, S, 22)
+            v = block_tensor(blk.batch, h0 // group, h1 // group, Hk, S, 23)
+            o = torch.empty_like(q)
+            lse = torch.empty(1, h1 - h0, S, device=device)
+            work.append((q, k, v, o, lse))
+        inc = None
+        if with_rope:
+            freqs = 500000.0 ** (-np.arange(0, D, 2, dtype=np.float64) / D)
+            inc = torch.from_numpy(np.round(freqs * 2.0 ** 32 / (2 * math.pi)).astype(np.int64).astype(np.uint32)
+                                   .view(np.int32)).to(device)
+            rotated = [(torch.empty(1, q.shape[2], S, D, dtype=q.dtype, device=device),
+                        torch.empty(1, k.shape[2], S, D, dtype=k.dtype, device=device)) for q, k, *_ in work]
+
+        def rope():
+            for (q, k, *_), (qr, kr) in zip(work, rotated):
+                _lib.check("fpt_rope_apply", lib.fpt_rope_apply(qr.data_ptr(), kr.data_ptr(), q.data_ptr(), k.data_ptr(),
+                                                                inc.data_ptr(), 1, S, q.shape[2], k.shape[2], D, 0, 1, stream))
+
+        def attend():
+            for i, (q, k, v, o, lse) in enumerate(work):
+                if with_rope:       # the rotation writes (batch, head, seq, dim); the attention reads it through strides
+                    q, k = rotated[i][0].permute(0, 2, 1, 3), rotated[i][1].permute(0, 2, 1, 3)
+                _lib.check("fpt_attention_fwd", lib.fpt_attention_fwd(
+                    o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), 1, S, q.shape[2], k.shape[2], D,
+                    arr(q), arr(k), arr(v), arr(o), mode, causal, 1.0 / math.sqrt(D), cap, log2_n, status.data_ptr(), stream))
+        return work, (rope if with_rope else None), attend
+
+    for name, B, S, Hq, Hk, mode, causal, cap, log2_n, with_rope in (
+            ("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 0, 1, 50.0, 12, False),
+            ("config5_rope_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 1, 0, 0.0, 14, True)):
+        work, rope, attend = attention_shard(rank, B, S, Hq, Hk, mode, causal, cap, log2_n, with_rope)
+        rope_ms = time_launch(torch, rope, 3) if rope else 0.0
+        attn_ms = time_launch(torch, attend, 5)
+        if int(status.item()) != 0:
+            raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x}")
+        csum = sum(bits_checksum(torch, w[3]) for w in work)
+        units = sum(w[0].shape[2] for w in work)
+        del work, rope, attend
+        torch.cuda.empty_cache()
+        per = gather_floats(torch, dist, world, device, [attn_ms, rope_ms])
+        sums = [v[0] for v in gather_ints(torch, dist, world, device, [csum])]
+        heads = [v[0] for v in gather_ints(torch, dist, world, device, [units])]
+        recheck = None
+        if world > 1 and rank == 0:
+            work2, rope2, attend2 = attention_shard(world - 1, B, S, Hq, Hk, mode, causal, cap, log2_n, with_rope)
+            if rope2:
+                rope2()
+            attend2()
+            recheck = sum(bits_checksum(torch, w[3]) for w in work2) == sums[world - 1]
+            del work2, rope2, attend2
+            torch.cuda.empty_cache()
+        flops = 4.0 * B * Hq * S * S * D * (0.5 if causal else 1.0)
+        makespan = max(p[0] for p in per)
+        with_rope_ms = max(p[0] + p[1] for p in per)
+        out[name] = {"q_heads_per_gpu": heads, "attention_ms_per_gpu": [p[0] for p in per], "rope_ms_per_gpu": [p[1] for p in per],
+                     "makespan_ms": makespan, "tflops_aggregate": flops / (makespan * 1e-3) / 1e12,
+                     "tflops_per_gpu": flops / world / (makespan * 1e-3) / 1e12,
+                     "frac_of_measured_bf16_peak_per_gpu": flops / world / (makespan * 1e-3) / 1e12 / tensor_peak,
+                     "tflops_aggregate_with_rope_prologue": flops / (with_rope_ms * 1e-3) / 1e12 if with_rope else None,
+                     "timing": "median of 5 passes over the rank's blocks (bursts, not power-capped)",
+                     "checksum_total": sum(sums), "last_shard_recomputed_on_rank0_equal": recheck}
+    return out
 
 
 def bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep):
@@ -419,107 +805,266 @@ def bench_b3(torch, lib, _lib, device, S, time_graph):
 
 
 def bench_attention(torch, lib, _lib, device, S, time_sweep):
-    """Configurations 4 and 5 of the baseline (plus the reference's published S=4096 shape), forward only."""
+    """Configurations 4 and 5 of the baseline and the reference's two published S=4096 shapes, every polynomial
+    score-mod next to its native special-function twin (the reference's B2 / B3 pairs, src/sfu_repro/fa4.py:650-709),
+    the plain soft-max control with the routed software exponentials of B5 (:724-752), forward and backward."""
     import ctypes
     _, tensor_peak, _ = measured_peaks()
-    out = {}
+    sustained = measured_sustained_tflops()
+    out = {"published_gb200_speedups_poly_over_native": {"B2_softcap_S4096_fwd_bwd": 2.05, "B3_sigmoid_S4096_fwd_bwd": 1.07,
+           "source": "evidence/report-data/b1_b4_100_iteration_phase_probes_gb200.json rows 1-2 (631.4 -> 307.5 us, 395.1 -> 368.0 us)"}}
     g = torch.Generator(device=device)
     g.manual_seed(SEED)
     D = 128
-    # last field: exp2 routing frequency (0 = every exponential on the SFU; f = four of every f keys on the FMA pipe)
-    shapes = (("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 0, 1, 50.0, 12, 0),
-              ("config5_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 1, 0, 0.0, 14, 0),
-              ("published_shape_softcap30_B1_S4096_Hq32_Hkv8", 1, 4096, 32, 8, 0, 1, 30.0, 12, 0),
-              ("published_shape_sigmoid_B1_S4096_Hq32_Hkv8_causal", 1, 4096, 32, 8, 1, 1, 0.0, 12, 0),
-              ("control_plain_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 0),
-              ("routed_exp2_d3_freq32_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 32),
-              ("routed_exp2_d3_freq12_softmax_B4_S8192_Hq32_Hkv8_causal", 4, 8192, 32, 8, 2, 1, 0.0, 12, 12))
-    for name, B, Sq, Hq, Hk, mode, causal, cap, log2_n, route in shapes:
+    arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    # variants: (label, mode, exp2 backend, forward route, backward route, softcap_grad)
+    softcap_pair = (("poly", 0, 0, 0, 0, 0), ("native", 3, 0, 0, 0, 1))
+    sigmoid_pair = (("poly", 1, 0, 0, 0, 0), ("native", 4, 0, 0, 0, 0))
+    routed = (("native", 2, 0, 0, 0, 0), ("d2_safe_fwd12_bwd32", 2, 2, 12, 32, 0), ("pwl2_safe_f16_fwd12_bwd32", 2, 3, 12, 32, 0),
+              ("d3_fwd12_bwd32", 2, 0, 12, 32, 0), ("d3_fwd32_bwd32", 2, 0, 32, 32, 0))
+    shapes = (("config4_causal_gqa_softcap50_tanhD4_B4_S8192_Hq32_Hkv8", 4, 8192, 32, 8, 1, 50.0, 12, softcap_pair, True),
+              ("config5_sigmoid_direct_B2_S16384_H32", 2, 16384, 32, 32, 0, 0.0, 14, sigmoid_pair, True),
+              ("published_shape_softcap30_B1_S4096_Hq32_Hkv8", 1, 4096, 32, 8, 1, 30.0, 12, softcap_pair, True),
+              ("published_shape_sigmoid_B1_S4096_Hq32_Hkv8_causal", 1, 4096, 32, 8, 1, 0.0, 12, sigmoid_pair, True),
+              ("control_plain_softmax_B4_S8192_Hq32_Hkv8_causal_and_routed_exp2", 4, 8192, 32, 8, 1, 0.0, 12, routed, True))
+    for name, B, Sq, Hq, Hk, causal, cap, log2_n, variants, with_backward in shapes:
         q = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
         k = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
         v = torch.randn(B, Sq, Hk, D, device=device, generator=g).to(torch.bfloat16)
+        dout = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
         o = torch.empty_like(q)
         lse = torch.empty(B, Hq, Sq, device=device)
-        status = torch.zeros(1, dtype=torch.int32, device=device)
-        arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
-        sq, sk, sv, so = arr(q), arr(k), arr(v), arr(o)
-        ks = [("attn", 0, lambda: _lib.check("fpt_attention_fwd_routed", lib.fpt_attention_fwd_routed(
-            o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, Sq, Hq, Hk, D, sq, sk, sv, so, mode,
-            causal, 1.0 / math.sqrt(D), cap, log2_n, 0, route, status.data_ptr(), S())))]
-        _, t = time_sweep(ks, 5, 2)
-        if int(status.item()) != 0:
-            raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x}")
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        need = int(lib.fpt_attention_bwd_workspace_bytes(B, Sq, Hq))
+        workspace = torch.empty(need, dtype=torch.uint8, device=device)
+        sq, sk, sv, so, sdo = arr(q), arr(k), arr(v), arr(o), arr(dout)
         flops = 4.0 * B * Hq * Sq * Sq * D * (0.5 if causal else 1.0)
-        tf = flops / (t["attn"] * 1e-3) / 1e12
-        out[name] = {"ms": t["attn"], "tflops": tf, "frac_of_measured_bf16_peak": tf / tensor_peak,
-                     "flops_convention": "4*B*Hq*S^2*D, halved when causal"}
-        if route == 0 and name.startswith(("config", "control")):
-            # backward of the same shape: dQ and dK/dV kernels plus the delta pre-pass, forward output as input
-            dout = torch.randn(B, Sq, Hq, D, device=device, generator=g).to(torch.bfloat16)
-            dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-            need = int(lib.fpt_attention_bwd_workspace_bytes(B, Sq, Hq))
-            workspace = torch.empty(need, dtype=torch.uint8, device=device)
-            sdo = arr(dout)
-            kb = [("bwd", 0, lambda: _lib.check("fpt_attention_bwd", lib.fpt_attention_bwd(
-                dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
-                o.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, Sq, Hq, Hk, D, sq, sk, sv, so, sdo, mode, causal,
-                1.0 / math.sqrt(D), cap, log2_n, 0, status.data_ptr(), S())))]
-            _, tb = time_sweep(kb, 3, 2)
+        entry = {"flops_convention": "forward 4*B*Hq*S^2*D, halved when causal; backward 2.5 x that (5 matrix products counted, "
+                                     "7 executed: S and dP are recomputed in the dQ and in the dK/dV kernel)"}
+        for label, mode, backend, route, route_bwd, grad in variants:
+            fwd = [("attn", 0, lambda: _lib.check("fpt_attention_fwd_routed", lib.fpt_attention_fwd_routed(
+                o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, Sq, Hq, Hk, D, sq, sk, sv, so, mode,
+                causal, 1.0 / math.sqrt(D), cap, log2_n, backend, route, status.data_ptr(), S())))]
+            _, t = time_sweep(fwd, 5, 2)
+            tf = flops / (t["attn"] * 1e-3) / 1e12
+            entry[label] = {"ms": t["attn"], "tflops": tf, "frac_of_measured_bf16_peak": tf / tensor_peak,
+                            "frac_of_sustained_bf16_peak": tf / sustained}
+            if with_backward:
+                bwd = [("bwd", 0, lambda: _lib.check("fpt_attention_bwd_routed", lib.fpt_attention_bwd_routed(
+                    dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),
+                    o.data_ptr(), lse.data_ptr(), workspace.data_ptr(), need, B, Sq, Hq, Hk, D, sq, sk, sv, so, sdo, mode, causal,
+                    1.0 / math.sqrt(D), cap, log2_n, grad, backend, route_bwd, status.data_ptr(), S())))]
+                _, tb = time_sweep(bwd, 3, 2)
+                tfb = 2.5 * flops / (tb["bwd"] * 1e-3) / 1e12
+                entry[label]["backward"] = {"ms": tb["bwd"], "tflops": tfb, "frac_of_measured_bf16_peak": tfb / tensor_peak,
+                                            "frac_of_sustained_bf16_peak": tfb / sustained}
             if int(status.item()) != 0:
-                raise RuntimeError(f"attention backward reported status {int(status.item()) & 0xffffffff:#x}")
-            tfb = 2.5 * flops / (tb["bwd"] * 1e-3) / 1e12
-            out[name]["backward"] = {"ms": tb["bwd"], "tflops": tfb, "frac_of_measured_bf16_peak": tfb / tensor_peak,
-                                     "flops_convention": "5 matrix products = 2.5 x the forward count (7 are executed: S and "
-                                                         "dP are recomputed in the dQ and in the dK/dV kernel)"}
-            del dout, dq, dk, dv, workspace
-        del q, k, v, o, lse
+                raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x} in {name}/{label}")
+        base = entry["native"]
+        for label, *_ in variants:
+            if label == "native":
+                continue
+            e = entry[label]
+            e["speedup_vs_native"] = base["ms"] / e["ms"]
+            if "backward" in e:
+                e["backward"]["speedup_vs_native"] = base["backward"]["ms"] / e["backward"]["ms"]
+                e["fwd_bwd_speedup_vs_native"] = (base["ms"] + base["backward"]["ms"]) / (e["ms"] + e["backward"]["ms"])
+        out[name] = entry
+        del q, k, v, dout, o, lse, dq, dk, dv, workspace
     torch.cuda.empty_cache()
     return out
 
 
-def bench_e2e(torch, spline_ops, HostPipeline, device):
-    """The sweep from pinned host memory through spline_ops: chunked H2D -> kernel -> D2H on three streams."""
-    n = 1 << 26          # per function; bounded so that the default run stays within minutes
+def bench_e2e(torch, spline_ops, HostPipeline, device, steps, barrier):
+    """The sweep from pinned host memory through spline_ops at the headline size (2^28 elements per function): chunked
+    H2D -> kernel -> D2H on three streams, `steps` timed repetitions.  Beside it the same chunked copies with no kernel
+    between them: what the host's copy path delivers when this many ranks use it at once."""
+    n = N_HBM
     chunk = 1 << 23
-    g = torch.Generator()
+    g = torch.Generator(device=device)
     g.manual_seed(SEED)
-    host_u8 = (torch.rand(n, generator=g) * 16 - 8).to(torch.float16).pin_memory()
-    host_frac = torch.rand(n, generator=g).to(torch.float16).pin_memory()
-    host_ang = (torch.rand(n, generator=g) * (2 * math.pi) - math.pi).pin_memory()
+
+    def pinned_from_device(make):
+        t = make()
+        host = torch.empty(t.shape, dtype=t.dtype).pin_memory()
+        host.copy_(t)
+        return host
+    host_u8 = pinned_from_device(lambda: (torch.rand(n, device=device, generator=g) * 16 - 8).to(torch.float16))
+    host_frac = pinned_from_device(lambda: torch.rand(n, device=device, generator=g).to(torch.float16))
+    host_ang = pinned_from_device(lambda: torch.rand(n, device=device, generator=g) * (2 * math.pi) - math.pi)
+    torch.cuda.empty_cache()
     host_out = torch.empty(n, dtype=torch.float16).pin_memory()
     host_sc = torch.empty(2 * n, dtype=torch.float16).pin_memory()
     unary_pipe = HostPipeline(device, [(torch.float16, 1)], [(torch.float16, 1)], chunk)
     # sin/cos keeps the two planes of a chunk adjacent in the device buffer; the host copy de-interleaves per chunk
     sincos_pipe = HostPipeline(device, [(torch.float32, 1)], [(torch.float16, 2)], chunk)
 
-    def run_once():
-        launches = 0
+    def run_once(compute=True):
         for op, src in ((spline_ops.sigmoid_fwd_d3, host_u8), (spline_ops.tanh_fwd_d4, host_u8),
                         (spline_ops.swish_fwd_d3, host_u8), (spline_ops.exp2_fraction, host_frac)):
             def fn(ins, outs, m, op=op):
-                outs[0].copy_(op(ins[0]))
-            launches += 2 * unary_pipe.run(fn, [src], [host_out], n)
+                if compute:
+                    outs[0].copy_(op(ins[0]))
+            unary_pipe.run(fn, [src], [host_out], n)
         def fn_sc(ins, outs, m):
-            outs[0].copy_(spline_ops.sincos_d5_d6_half_turn_fp16(ins[0]).view(-1))
-        launches += 2 * sincos_pipe.run(fn_sc, [host_ang], [host_sc], n)
+            if compute:
+                outs[0].copy_(spline_ops.sincos_d5_d6_half_turn_fp16(ins[0]).view(-1))
+        sincos_pipe.run(fn_sc, [host_ang], [host_sc], n)
         unary_pipe.synchronize()
         sincos_pipe.synchronize()
-        return launches
 
-    run_once()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    reps = 2
-    for _ in range(reps):
-        run_once()
-    torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / reps
+    def timed(compute, reps):
+        run_once(compute)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            run_once(compute)
+        torch.cuda.synchronize()
+        return (time.perf_counter() - t0) / reps
+    dt = timed(True, steps)
+    dt_copy = timed(False, max(3, steps // 4))
     h2d = 4 * n * 2 + n * 4
     d2h = 4 * n * 2 + 2 * n * 2
     return {"value": 5 * n / dt, "unit": "elements/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-            "elements_per_function": n, "ms_per_step": dt * 1e3,
+            "elements_per_function": n, "ms_per_step": dt * 1e3, "steps": steps,
             "path": "spline_ops.* on pinned host buffers, 2^23-element chunks, H2D / kernel / D2H on three streams; "
-                    "sin/cos results are returned chunk by chunk as [cos | sin] blocks"}
+                    "sin/cos results are returned chunk by chunk as [cos | sin] blocks",
+            "copy_only": {"ms_per_step": dt_copy * 1e3, "steps": max(3, steps // 4),
+                          "what": "the same pinned H2D and D2H copies, same chunks and streams, no kernel"}}
+
+
+def run_compare_reference_kernels(args):
+    """This library's kernels next to the reference's own kernels (compiled from the reference's sources with its flags
+    into oracle/_ref by `make -C oracle ref`) on the same GPU, same inputs, same timing protocol: median over 7 rounds of
+    the mean of back-to-back launches; L2-resident sizes also as CUDA-graph replays (no host launch cost) and as eager
+    calls through the Python operator surface.  Prints one JSON line {"compare_reference_kernels": [rows]}."""
+    import ctypes
+
+    import numpy as np
+    import torch
+    from fast_polynomial_transcendentals_b200 import _lib, spline_ops
+    path = ROOT / "oracle" / "_ref" / "libref_spline_kernels.so"
+    if not path.exists():
+        print(json.dumps({"compare_reference_kernels": "unavailable: oracle/_ref/libref_spline_kernels.so is not built"}))
+        return
+    ref_kernels = ctypes.CDLL(str(path))
+    lib = _lib.load()
+    device = torch.device("cuda:0")
+    torch.cuda.set_device(device)
+    vp, ci = ctypes.c_void_p, ctypes.c_int
+    rows = []
+
+    def timed(fn, reps, rounds=7, graph=False):
+        for _ in range(5):
+            fn()
+        torch.cuda.synchronize()
+        runner = fn
+        if graph:
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.stream(side):
+                with torch.cuda.graph(g, stream=side):
+                    for _ in range(reps):
+                        fn(side.cuda_stream)
+            torch.cuda.current_stream().wait_stream(side)
+            runner = g.replay
+        times = []
+        for _ in range(rounds):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            if graph:
+                runner()
+            else:
+                for _ in range(reps):
+                    fn()
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b) / reps)
+        times.sort()
+        return times[len(times) // 2]
+
+    def ref(symbol, *a):
+        f = getattr(ref_kernels, symbol)
+        f.restype = None
+        conv = [vp(x.data_ptr()) if hasattr(x, "data_ptr") else ci(int(x)) for x in a]
+        return lambda s=None: f(*conv, vp(s or torch.cuda.current_stream().cuda_stream))
+
+    def ours(name, *a):
+        f = getattr(lib, name)
+        return lambda s=None: f(*a, s or torch.cuda.current_stream().cuda_stream)
+
+    def row(what, t_ref, t_our, nbytes=None):
+        r = {"what": what, "ref_ms": t_ref, "ours_ms": t_our, "ours_over_ref_speed": t_ref / t_our}
+        if nbytes:
+            r.update(ref_gbs=nbytes / t_ref / 1e6, ours_gbs=nbytes / t_our / 1e6)
+        rows.append(r)
+
+    n = 1 << 28
+    x = (torch.rand(n, device=device) * 16 - 8).to(torch.float16)
+    o = torch.empty_like(x)
+    for fn_name, fn, degree in (("sigmoid", 0, 3), ("tanh", 1, 4), ("swish", 2, 3), ("gelu", 4, 5)):
+        row(f"{fn_name}_fwd_d{degree}_fp16_2^28", timed(ref(f"launch_{fn_name}_fwd_d{degree}_kernel", o, x, n), 10),
+            timed(ours("fpt_unary", o.data_ptr(), x.data_ptr(), n, fn, 0, degree, 0, 0), 10), 4 * n)
+    row("swish_native_fp16_2^28", timed(ref("launch_swish_fwd_native_kernel", o, x, n), 10),
+        timed(ours("fpt_unary", o.data_ptr(), x.data_ptr(), n, 2, 0, 0, 0, 0), 10), 4 * n)
+    t_torch = timed(lambda s=None: torch.sigmoid(x, out=o), 10)
+    rows.append({"what": "torch_sigmoid_fp16_2^28", "torch_ms": t_torch, "torch_gbs": 4 * n / t_torch / 1e6})
+    go = torch.randn(n, device=device).to(torch.float16)
+    for fn_name, fn, degree in (("sigmoid", 0, 4), ("swish", 2, 3)):
+        row(f"{fn_name}_bwd_d{degree}_fp16_2^28", timed(ref(f"launch_{fn_name}_bwd_d{degree}_kernel", o, go, x, n), 10),
+            timed(ours("fpt_binary_bwd", o.data_ptr(), go.data_ptr(), x.data_ptr(), n, fn, degree, 0, 0), 10), 6 * n)
+    del go
+    for m in (1 << 20, 1 << 22):     # L2-resident: eager C-ABI calls, graph replays, and the Python operator surface
+        xs, os_ = x[:m], o[:m]
+        e = {"what": f"sigmoid_fwd_d3_fp16_{m}"}
+        e["ref_us"] = timed(ref("launch_sigmoid_fwd_d3_kernel", os_, xs, m), 200) * 1e3
+        e["ours_us"] = timed(ours("fpt_unary", os_.data_ptr(), xs.data_ptr(), m, 0, 0, 3, 0, 0), 200) * 1e3
+        e["ours_native_us"] = timed(ours("fpt_unary", os_.data_ptr(), xs.data_ptr(), m, 0, 0, 0, 0, 0), 200) * 1e3
+        e["torch_native_us"] = timed(lambda s=None: torch.sigmoid(xs, out=os_), 200) * 1e3
+        e["ours_python_op_us"] = timed(lambda s=None: spline_ops.sigmoid_fwd_d3(xs), 200) * 1e3
+        e["ours_python_op_path"] = spline_ops.binding_kind()
+        e["torch_native_allocating_us"] = timed(lambda s=None: torch.sigmoid(xs), 200) * 1e3
+        e["ref_graph_us"] = timed(ref("launch_sigmoid_fwd_d3_kernel", os_, xs, m), 50, graph=True) * 1e3
+        e["ours_graph_us"] = timed(ours("fpt_unary", os_.data_ptr(), xs.data_ptr(), m, 0, 0, 3, 0, 0), 50, graph=True) * 1e3
+        e["ours_native_graph_us"] = timed(ours("fpt_unary", os_.data_ptr(), xs.data_ptr(), m, 0, 0, 0, 0, 0), 50, graph=True) * 1e3
+        rows.append(e)
+    m = 1 << 27
+    ang = torch.rand(m, device=device) * 6.2831853 - 3.14159265
+    sc = torch.empty(2, m, dtype=torch.float16, device=device)
+    row("sincos_d5_d6_half_turn_fp16_2^27", timed(ref("launch_sincos_d5_d6_half_turn_fp16", sc, ang, m), 10),
+        timed(ours("fpt_sincos", sc.data_ptr(), ang.data_ptr(), m, 3, 0), 10), 8 * m)
+    row("sincos_native_fp16_2^27", timed(ref("launch_sincos_native_fp16", sc, ang, m), 10),
+        timed(ours("fpt_sincos", sc.data_ptr(), ang.data_ptr(), m, 10, 0), 10), 8 * m)
+    del x, o, ang, sc
+    torch.cuda.empty_cache()
+    for name, r, h in (("B1_16384x14336", 16384, 14336), ("B4_131072x1408", 131072, 1408)):
+        packed = (torch.randn(r, 2 * h, device=device) * 1.5).to(torch.bfloat16)
+        gate, up = packed[:, :h].contiguous(), packed[:, h:].contiguous()
+        out = torch.empty_like(gate)
+        nn = r * h
+        row(f"swiglu_flat_d3_bf16_{name}", timed(ref("launch_swish_mul_fwd_d3_kernel_bf16", out, gate, up, nn), 10),
+            timed(ours("fpt_swish_mul", out.data_ptr(), gate.data_ptr(), up.data_ptr(), nn, 3, 1, 0), 10), 6 * nn)
+        row(f"swiglu_packed_d3_bf16_{name}", timed(ref("launch_swish_mul_packed_fwd_d3_kernel_bf16", out, packed, r, h), 10),
+            timed(ours("fpt_swish_mul_packed", out.data_ptr(), packed.data_ptr(), r, h, 3, 1, 0), 10), 6 * nn)
+        go = torch.randn(r, h, device=device).to(torch.bfloat16)
+        gp = torch.empty_like(packed)
+        row(f"swiglu_packed_bwd_d3_bf16_{name}", timed(ref("launch_swish_mul_packed_bwd_d3_kernel_bf16", gp, go, packed, r, h), 10),
+            timed(ours("fpt_swish_mul_packed_bwd", gp.data_ptr(), go.data_ptr(), packed.data_ptr(), r, h, 3, 1, 0), 10), 10 * nn)
+        del packed, gate, up, out, go, gp
+        torch.cuda.empty_cache()
+    B, S, H, D = 2, 16384, 32, 128
+    q = torch.randn(B, S, H, D, device=device).to(torch.float16)
+    k = torch.randn(B, S, H, D, device=device).to(torch.float16)
+    qo, ko = torch.empty(B, H, S, D, dtype=q.dtype, device=device), torch.empty(B, H, S, D, dtype=q.dtype, device=device)
+    freqs = 500000.0 ** (-np.arange(0, D, 2, dtype=np.float64) / D)
+    inc = torch.from_numpy(np.round(freqs * 2.0 ** 32 / (2 * math.pi)).astype(np.int64).astype(np.uint32).view(np.int32)).to(device)
+    row("rope_apply_d5_d6_fp16_B2_S16384_H32_D128",
+        timed(ref("launch_rope_apply_fixed_half_turn_d5_d6_fp16", qo, ko, q, k, inc, B, S, H, H, D), 10),
+        timed(ours("fpt_rope_apply", qo.data_ptr(), ko.data_ptr(), q.data_ptr(), k.data_ptr(), inc.data_ptr(), B, S, H, H, D, 0, 0), 10),
+        4 * q.numel() * 2)
+    print(json.dumps({"compare_reference_kernels": rows}), flush=True)
 
 
 def run_profile_case(args):
@@ -623,13 +1168,17 @@ def main():
     ap.add_argument("--profile-case", default=None, help="run only one small kernel case (for ncu captures)")
     ap.add_argument("--profile-n", type=int, default=1 << 26)
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=300)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--compare-reference-kernels", action="store_true",
+                    help="time this library's kernels next to the reference's compiled kernels (oracle/_ref), 1 GPU")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.profile_case:
         run_profile_case(args)
+    elif args.compare_reference_kernels:
+        run_compare_reference_kernels(args)
     elif args.impl == "reference":
         run_reference_arm(args)
     else:

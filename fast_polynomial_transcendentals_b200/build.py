@@ -20,6 +20,8 @@ OBJ = PKG / "_build"
 LIB = PKG / "libfpt_b200.so"
 COMPAT_LIB = PKG / "libfpt_b200_compat.so"          # the reference's launch_* names over the fpt_* C ABI
 COMPAT_SRC = CSRC / "fpt_compat_launch.cpp"
+TORCH_BINDING_SRC = CSRC / "fpt_torch_binding.cpp"   # compiled PyTorch binding of the hot element-wise operators
+TORCH_BINDING_NAME = "_fpt_torch"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-Xptxas", "-v",
               "--expt-relaxed-constexpr", "-I", str(PKG.parent / "include")]
@@ -88,7 +90,38 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         if verbose:
             print(f"linked {LIB}")
     _build_compat(force, verbose)
+    _build_torch_binding(force, verbose)
     return LIB
+
+
+def torch_binding_path() -> Path:
+    import sysconfig
+    return PKG / (TORCH_BINDING_NAME + (sysconfig.get_config_var("EXT_SUFFIX") or ".so"))
+
+
+def _build_torch_binding(force: bool, verbose: bool) -> Path:
+    """Host-only C++ against the PyTorch headers; resolves fpt_* from libfpt_b200.so beside it (rpath $ORIGIN)."""
+    import sysconfig
+
+    import torch
+    from torch.utils import cpp_extension
+    out = torch_binding_path()
+    deps = [TORCH_BINDING_SRC, LIB, PKG.parent / "include" / "fpt_b200.h"]
+    if force or _stale(out, deps):
+        cuda_home = Path(shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc").resolve().parents[1]
+        includes = [*cpp_extension.include_paths(), sysconfig.get_paths()["include"], str(cuda_home / "include")]
+        libdirs = cpp_extension.library_paths()
+        cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", "-w", f"-DTORCH_EXTENSION_NAME={TORCH_BINDING_NAME}",
+               "-DTORCH_API_INCLUDE_EXTENSION_H", f"-D_GLIBCXX_USE_CXX11_ABI={int(torch._C._GLIBCXX_USE_CXX11_ABI)}",
+               *[f"-I{i}" for i in includes], str(TORCH_BINDING_SRC), "-o", str(out),
+               *[f"-L{d}" for d in libdirs], "-lc10", "-lc10_cuda", "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python",
+               f"-L{PKG}", "-lfpt_b200", "-Wl,-rpath,$ORIGIN", *[f"-Wl,-rpath,{d}" for d in libdirs]]
+        proc = subprocess.run(cmd, capture_output=True, text=True)
+        if proc.returncode != 0:
+            raise RuntimeError(f"torch binding build failed:\n{proc.stderr[-4000:]}")
+        if verbose:
+            print(f"built {out}")
+    return out
 
 
 def _build_compat(force: bool, verbose: bool) -> Path:

@@ -31,17 +31,63 @@ def _projection_names(module: nn.Module) -> tuple[str, str, str] | None:
     return None
 
 
-def dense_swiglu_modules(model: nn.Module) -> list[nn.Module]:
-    return [m for m in model.modules() if _projection_names(m) is not None]
+_ACTIVATION_SLOTS = ("act_fn", "activation_fn", "act")
+
+
+def _is_silu(module: nn.Module, fn: Any) -> bool:
+    """The test the reference applies before it treats a gated MLP as SwiGLU (reference:
+    scripts/benchmark_open_weights.py:649-664): the module's config names SiLU / swish, or the activation object is one."""
+    config = getattr(module, "config", None)
+    for name in (getattr(config, "hidden_act", None), getattr(config, "hidden_activation", None)):
+        if isinstance(name, str) and name.lower() in ("silu", "swish"):
+            return True
+    if isinstance(fn, nn.SiLU) or fn is torch.nn.functional.silu:
+        return True
+    names = (type(fn).__name__.lower(), str(getattr(fn, "__name__", "")).lower())
+    return any(n in ("silu", "swish", "siluactivation") for n in names)
+
+
+def gated_mlp_activation(module: nn.Module) -> str:
+    """'silu' when the gated MLP computes down(silu(gate(x)) * up(x)), else a description of what it holds instead.
+
+    A module with an activation slot (`act_fn`, `activation_fn`, `act`) qualifies only if that slot is SiLU: a GELU- or
+    ReLU-gated MLP has the same three projections and must not be turned into SwiGLU.  A module without any slot
+    qualifies when all three projections are bias-free (the Llama feed-forward that calls `F.silu` in its forward,
+    reference: src/sfu_repro/torchtitan/plugin.py:197-265)."""
+    slots = [(a, getattr(module, a)) for a in _ACTIVATION_SLOTS if getattr(module, a, None) is not None]
+    if slots:
+        for _, fn in slots:
+            if isinstance(fn, FunctionActivation) or _is_silu(module, fn):
+                return "silu"
+        return f"{slots[0][0]}={type(slots[0][1]).__name__}"
+    names = _projection_names(module)
+    if names and all(getattr(module, n).bias is None for n in names):
+        return "silu"
+    return "no activation slot and biased projections"
+
+
+def dense_swiglu_modules(model: nn.Module, skipped: list[tuple[str, str]] | None = None) -> list[nn.Module]:
+    """Gated MLPs whose activation is SiLU; the others are appended to `skipped` as (module name, what they hold)."""
+    found = []
+    for name, module in model.named_modules():
+        if _projection_names(module) is None:
+            continue
+        kind = gated_mlp_activation(module)
+        if kind == "silu":
+            found.append(module)
+        elif skipped is not None:
+            skipped.append((name, kind))
+    return found
 
 
 def patch_dense_swiglu(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
-                       coeff_source: str = "current") -> int:
-    """down(act(gate(x)) * up(x)) with the fused SwiGLU kernel between the projections; weights untouched."""
+                       coeff_source: str = "current", skipped: list[tuple[str, str]] | None = None) -> int:
+    """down(act(gate(x)) * up(x)) with the fused SwiGLU kernel between the projections; weights untouched.  Gated MLPs
+    whose activation is not SiLU are left alone and reported through `skipped`."""
     implementation = "native_silu" if variant == "native" else "spline_silu_compile"
     _, activation_mul = resolve_mlp_activation_mul_impl(implementation, degree=degree, coeff_source=coeff_source)
     patched = 0
-    for module in dense_swiglu_modules(model):
+    for module in dense_swiglu_modules(model, skipped):
         gate, up, down = _projection_names(module)
 
         def forward(self, x, *args, _g=gate, _u=up, _d=down, **kwargs):
@@ -75,8 +121,10 @@ class FusedGateUpFeedForward(nn.Module):
 
 @torch.no_grad()
 def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
-                             coeff_source: str = "current", backward_impl: str = "matched") -> int:
-    """Replace every bias-free gated MLP by `FusedGateUpFeedForward` with w_in = cat(gate, up) (rows)."""
+                             coeff_source: str = "current", backward_impl: str = "matched",
+                             skipped: list[tuple[str, str]] | None = None) -> int:
+    """Replace every bias-free SiLU-gated MLP by `FusedGateUpFeedForward` with w_in = cat(gate, up) (rows); gated MLPs
+    with another activation are left alone and reported through `skipped`."""
     implementation = "native_silu" if variant == "native" else "spline_silu_compile"
     _, activation_packed = resolve_mlp_activation_packed_impl(implementation, degree=degree, coeff_source=coeff_source,
                                                               backward_impl=backward_impl)
@@ -85,6 +133,11 @@ def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", d
         for child_name, child in list(parent.named_children()):
             names = _projection_names(child)
             if names is None:
+                continue
+            kind = gated_mlp_activation(child)
+            if kind != "silu":
+                if skipped is not None:
+                    skipped.append((child_name, kind))
                 continue
             gate, up, down = (getattr(child, n) for n in names)
             if gate.bias is not None or up.bias is not None:
@@ -152,7 +205,7 @@ class FunctionActivation(nn.Module):
 
 
 def patch_activation_slots(model: nn.Module, *, kind: str = "silu", degree: int | None = None,
-                           coeff_source: str = "current", attributes: tuple[str, ...] = ("act_fn", "activation_fn", "act")) -> int:
+                           coeff_source: str = "current", attributes: tuple[str, ...] = _ACTIVATION_SLOTS) -> int:
     """Swap SiLU (or GELU) activations held in the usual attribute slots for the polynomial kernel."""
     targets = {"silu": (nn.SiLU, torch.nn.functional.silu), "gelu": (nn.GELU, torch.nn.functional.gelu)}[kind]
     _, activation = resolve_mlp_activation_impl(f"spline_{kind}_compile", degree=degree, coeff_source=coeff_source)
@@ -189,4 +242,5 @@ def restore(model: nn.Module) -> int:
 
 
 __all__ = ["FunctionActivation", "FusedGateUpFeedForward", "dense_swiglu_modules", "fuse_gate_up_projections",
+           "gated_mlp_activation",
            "patch_activation_slots", "patch_dense_swiglu", "patch_grouped_experts", "restore", "run_grouped_experts"]

@@ -7,6 +7,11 @@ autonumerics_zero/spline_ops/spline_ops.cpp:2285-2452; argument checks
 validate torch CUDA tensors, allocate the output and call
 ``libfpt_b200.so`` on the current stream of the tensor's device.
 
+The hot element-wise operators (unary, gradient product, the four SwiGLU forms) go through a compiled PyTorch
+binding when it has been built (``_fpt_torch``: checks, allocation, device guard and the C-ABI call in C++; the same
+functions are also registered as dispatcher operators ``torch.ops.fpt_b200.*``); everything else, and those six when the
+binding is absent, goes through ``ctypes`` on the same library.  Either way the work is done by ``libfpt_b200.so``.
+
 Differences kept on purpose:
   * the call runs under a device guard for the input tensor's device (the
     reference assumes the current device already matches);
@@ -20,6 +25,18 @@ import torch
 
 from . import _lib
 from ._lib import BF16, BWD, FN_GELU, FN_SIGMOID, FN_SWISH, FN_TANH, FP16, FWD
+
+try:                                    # the compiled binding (built by build.py next to the CUDA library)
+    _lib.load()
+    from . import _fpt_torch as _ext
+except ImportError:
+    _ext = None
+
+
+def binding_kind() -> str:
+    """How the hot element-wise operators reach the CUDA library in this process."""
+    return "compiled torch extension (_fpt_torch)" if _ext is not None else "ctypes"
+
 
 _FUNCTIONS = {"sigmoid": FN_SIGMOID, "tanh": FN_TANH, "swish": FN_SWISH, "gelu": FN_GELU}
 _DEFAULT_DEGREE = {("sigmoid", "fwd"): 3, ("sigmoid", "bwd"): 4, ("tanh", "fwd"): 3, ("tanh", "bwd"): 4,
@@ -54,10 +71,14 @@ def _source(coeff_source_id: int, x: torch.Tensor) -> int:
 
 
 def _same(a: torch.Tensor, b: torch.Tensor, an: str, bn: str) -> None:
+    """Two tensors of one launch: the kernel indexes both with one element count, reads both as one lane format and
+    runs on one device, so all three must agree before anything is launched."""
     if a.dtype != b.dtype:
         raise RuntimeError(f"{an} and {bn} must have the same dtype")
     if a.numel() != b.numel():
         raise RuntimeError(f"{an} and {bn} must have the same number of elements")
+    if a.device != b.device:
+        raise RuntimeError(f"{an} and {bn} must be on the same device")
 
 
 class _Guard:
@@ -93,6 +114,8 @@ def _call(name: str, x: torch.Tensor, *args) -> None:
 # ---- unary / gradient products -------------------------------------------------------------
 
 def _unary(x, function: str, direction: int, degree: int, source: int = 0):
+    if _ext is not None and isinstance(x, torch.Tensor):
+        return _ext.unary(x, _FUNCTIONS[function], direction, degree, source)
     _check_input(x, "x")
     out = torch.empty_like(x)
     try:
@@ -107,6 +130,8 @@ def _unary(x, function: str, direction: int, degree: int, source: int = 0):
 
 
 def _binary(grad_out, x, function: str, degree: int, source: int = 0):
+    if _ext is not None and isinstance(grad_out, torch.Tensor) and isinstance(x, torch.Tensor):
+        return _ext.binary_bwd(grad_out, x, _FUNCTIONS[function], degree, source)
     _check_input(grad_out, "grad_out")
     _check_input(x, "x")
     _same(grad_out, x, "grad_out", "x")
@@ -167,6 +192,7 @@ def gelu_bwd_variant(grad_out, x, degree: int, coeff_source_id: int):
 def _alg(grad_out, y, function: str):
     _check_input(grad_out, "grad_out")
     _check_input(y, "x")
+    _same(grad_out, y, "grad_out", "x")
     grad_in = torch.empty_like(y)
     _call("fpt_bwd_algebraic", y, grad_in.data_ptr(), grad_out.data_ptr(), y.data_ptr(), y.numel(),
           _FUNCTIONS[function], _dtype_id(y))
@@ -206,6 +232,7 @@ def _hybrid_bwd(function: str):
     def op(grad_out, x):
         _check_fp16_only(grad_out, "grad_out")
         _check_fp16_only(x, "x")
+        _same(grad_out, x, "grad_out", "x")
         grad_in = torch.empty_like(x)
         _call("fpt_binary_bwd_hybrid", x, grad_in.data_ptr(), grad_out.data_ptr(), x.data_ptr(), x.numel(),
               _FUNCTIONS[function])
@@ -219,6 +246,7 @@ def _fused(function: str):
     def op(x, grad_out):
         _check_fp16_only(x, "x")
         _check_fp16_only(grad_out, "grad_out")
+        _same(x, grad_out, "x", "grad_out")
         y, grad_in = torch.empty_like(x), torch.empty_like(x)
         _call("fpt_fused_fwd_bwd", x, y.data_ptr(), grad_in.data_ptr(), x.data_ptr(), grad_out.data_ptr(), x.numel(),
               _FUNCTIONS[function])
@@ -266,6 +294,8 @@ def multiply(a, b):
 # ---- SwiGLU --------------------------------------------------------------------------------
 
 def swish_mul_fwd_variant(gate, up, degree: int, coeff_source_id: int):
+    if _ext is not None and isinstance(gate, torch.Tensor) and isinstance(up, torch.Tensor):
+        return _ext.swish_mul(gate, up, int(degree), int(coeff_source_id))
     _check_input(gate, "gate")
     _check_input(up, "up")
     _same(gate, up, "gate", "up")
@@ -282,12 +312,16 @@ def swish_mul_fwd_variant(gate, up, degree: int, coeff_source_id: int):
 
 
 def swish_mul_bwd_variant(grad_out, gate, up, degree: int, coeff_source_id: int):
+    if _ext is not None and all(isinstance(t, torch.Tensor) for t in (grad_out, gate, up)):
+        return list(_ext.swish_mul_bwd(grad_out, gate, up, int(degree), int(coeff_source_id)))
     for t, n in ((grad_out, "grad_out"), (gate, "gate"), (up, "up")):
         _check_input(t, n)
     if not (grad_out.dtype == gate.dtype == up.dtype):
         raise RuntimeError("grad_out, gate, and up must have the same dtype")
     if not (grad_out.numel() == gate.numel() == up.numel()):
         raise RuntimeError("grad_out, gate, and up must have the same number of elements")
+    if not (grad_out.device == gate.device == up.device):
+        raise RuntimeError("grad_out, gate, and up must be on the same device")
     source = _source(coeff_source_id, gate)
     grad_gate, grad_up = torch.empty_like(gate), torch.empty_like(up)
     try:
@@ -314,6 +348,8 @@ def _packed_dims(packed):
 
 def swish_mul_packed_fwd_variant(packed, degree: int, coeff_source_id: int):
     """packed [..., 2H] = [gate | up]  ->  [..., H]."""
+    if _ext is not None and isinstance(packed, torch.Tensor):
+        return _ext.swish_mul_packed(packed, int(degree), int(coeff_source_id))
     _check_input(packed, "packed")
     width, hidden = _packed_dims(packed)
     source = _source(coeff_source_id, packed)
@@ -332,10 +368,14 @@ def swish_mul_packed_fwd_variant(packed, degree: int, coeff_source_id: int):
 
 
 def swish_mul_packed_bwd_variant(grad_out, packed, degree: int, coeff_source_id: int):
+    if _ext is not None and isinstance(grad_out, torch.Tensor) and isinstance(packed, torch.Tensor):
+        return _ext.swish_mul_packed_bwd(grad_out, packed, int(degree), int(coeff_source_id))
     _check_input(grad_out, "grad_out")
     _check_input(packed, "packed")
     if grad_out.dtype != packed.dtype:
         raise RuntimeError("grad_out and packed must have the same dtype")
+    if grad_out.device != packed.device:
+        raise RuntimeError("grad_out and packed must be on the same device")
     width, hidden = _packed_dims(packed)
     if grad_out.numel() * 2 != packed.numel() or (grad_out.dim() and grad_out.size(-1) != hidden):
         raise RuntimeError("grad_out must match the packed tensor with its last dimension halved")

@@ -310,7 +310,9 @@ def test_routed_endpoint_preserving_exponentials(fpt, cuda, oracle, backend, nam
         assert st0 == 0 and st == 0 and not torch.isnan(out.float()).any()
         assert not torch.equal(out, base), "the routed kernel must not be the unrouted one"
         assert float((lse - lse0).abs().max()) < 2 * err
-        assert float((out.float() - base.float()).abs().max()) < 1.2 * err + 1.6e-2
+        # the evaluator's error on the routed weights plus one bf16 rounding of each of the two outputs
+        largest = max(1.0, float(base.float().abs().max()))
+        assert float((out.float() - base.float()).abs().max()) < (1.2 * err + 2.0 ** -7) * largest
         for h in range(Hq):
             want = oracle.attention_rows(qb, kb, vb, 0, h, np.arange(S), 2, causal, scale, 0.0, 12)
             assert float(np.abs(out[0, :, h, :].float().cpu().numpy() - want).max()) < oracle_bound, (name, freq, causal)

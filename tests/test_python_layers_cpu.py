@@ -189,3 +189,41 @@ def test_module_surgery_finds_patches_and_restores_by_structure():
     assert sum(p.numel() for p in model.parameters()) == before
     assert torch.equal(model["b"].w_in.weight, torch.cat((w1, w3), dim=0))
     assert getattr(model["b"].sfu_activation_packed, "__spline_op__", None) == "spline_ops::swish_mul_packed_variant_fwd"
+
+
+def test_gated_mlps_with_another_activation_are_not_turned_into_swiglu():
+    """GeGLU / ReGLU MLPs have the same three projections as SwiGLU; patching them would silently change the model's
+    function.  Only SiLU-gated modules qualify (the reference's own test, scripts/benchmark_open_weights.py:649-664)."""
+    from torch import nn
+
+    from fast_polynomial_transcendentals_b200.sfu_repro import adapters
+
+    class Gated(nn.Module):
+        def __init__(self, act, bias=False, names=("gate_proj", "up_proj", "down_proj")):
+            super().__init__()
+            for n, (i, o) in zip(names, ((16, 32), (16, 32), (32, 16))):
+                setattr(self, n, nn.Linear(i, o, bias=bias))
+            if act is not None:
+                self.act_fn = act
+
+    class Config:
+        hidden_act = "silu"
+
+    model = nn.ModuleDict({"silu": Gated(nn.SiLU()), "gelu": Gated(nn.GELU(approximate="tanh")), "relu": Gated(nn.ReLU()),
+                           "functional": Gated(torch.nn.functional.silu), "slotless": Gated(None, names=("w1", "w3", "w2")),
+                           "slotless_biased": Gated(None, bias=True)})
+    model["by_config"] = Gated(nn.Identity())
+    model["by_config"].config = Config()
+    assert {n: adapters.gated_mlp_activation(m) == "silu" for n, m in model.items()} == {
+        "silu": True, "gelu": False, "relu": False, "functional": True, "slotless": True, "slotless_biased": False,
+        "by_config": True}
+    skipped = []
+    assert adapters.patch_dense_swiglu(model, skipped=skipped) == 4
+    assert sorted(n for n, _ in skipped) == ["gelu", "relu", "slotless_biased"]
+    assert "forward" not in model["gelu"].__dict__ and "forward" in model["silu"].__dict__
+    assert adapters.restore(model) == 4
+    skipped = []
+    assert adapters.fuse_gate_up_projections(model, skipped=skipped) == 4
+    assert isinstance(model["gelu"], Gated) and isinstance(model["relu"], Gated)
+    assert isinstance(model["silu"], adapters.FusedGateUpFeedForward)
+    assert sorted(n for n, _ in skipped) == ["gelu", "relu", "slotless_biased"]

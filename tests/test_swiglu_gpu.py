@@ -140,3 +140,36 @@ def test_reference_kernels_agree_bit_for_bit(fpt, cuda, ref_kernels):
             torch.cuda.synchronize()
             assert_bits_equal(to_bits(gg), to_bits(rgg), f"swish_mul_bwd gate d{degree}{suffix}", gb)
             assert_bits_equal(to_bits(gu), to_bits(rgu), f"swish_mul_bwd up d{degree}{suffix}", gb)
+
+
+@pytest.mark.parametrize("hidden", [512, 768])
+def test_packed_row_offsets_cross_two_to_the_31(fpt, cuda, hidden):
+    """The reference's large-row-offset check (reference: autonumerics_zero/spline_ops/test_spline_ops.py:207-235, there
+    behind SPLINE_OPS_TEST_LARGE_PACKED=1): 2^31 / (2 hidden) + 8 rows of ones, so that the element offset of the last
+    rows no longer fits a signed 32-bit integer; probe rows on both sides of the boundary must hold swish_D4(1) * 1.
+    The packed backward crosses the same boundary here as well.  About 11 GB of device memory; set
+    SPLINE_OPS_TEST_LARGE_PACKED=0 to skip."""
+    import os
+
+    import torch
+    from fast_polynomial_transcendentals_b200 import spline_ops
+    if os.environ.get("SPLINE_OPS_TEST_LARGE_PACKED") == "0":
+        pytest.skip("switched off by SPLINE_OPS_TEST_LARGE_PACKED=0")
+    if torch.cuda.mem_get_info(cuda)[0] < 16 << 30:
+        pytest.skip("needs 16 GB of free device memory")
+    one = torch.ones(1, device=cuda, dtype=torch.bfloat16)
+    expected = spline_ops.swish_mul_fwd_variant(one, one, 4, 0)
+    boundary = 2 ** 31 // (2 * hidden)
+    rows = boundary + 8
+    packed = torch.ones((rows, 2 * hidden), device=cuda, dtype=torch.bfloat16)
+    out = spline_ops.swish_mul_packed_fwd_variant(packed, 4, 0)
+    probe = torch.tensor([0, boundary - 1, boundary, rows - 1], device=cuda)
+    assert torch.equal(out.index_select(0, probe), expected.expand(probe.numel(), hidden))
+    assert int((out.view(torch.int16) != expected.view(torch.int16)).sum()) == 0        # and every other row
+    grads = spline_ops.swish_mul_bwd_variant(one, one, one, 4, 0)
+    del out
+    grad_packed = spline_ops.swish_mul_packed_bwd_variant(torch.ones((rows, hidden), device=cuda, dtype=torch.bfloat16), packed, 4, 0)
+    for half, want in ((grad_packed[:, :hidden], grads[0]), (grad_packed[:, hidden:], grads[1])):
+        assert int((half.view(torch.int16) != want.view(torch.int16)).sum()) == 0
+    del packed, grad_packed
+    torch.cuda.empty_cache()
