@@ -521,8 +521,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     for (int w = 0; w < 32; ++w) {
                         const int i = half * 32 + w;
                         if constexpr (MODE == 1) {
+#ifdef FPT_DIAG_SKIP_SCOREMOD       // tuning builds only: no arithmetic, to see what the rest of the pipeline sustains
+                            pw[w] = sr[2 * i] ^ sr[2 * i + 1];
+#else
                             const uint32_t x = scale_pack_bf16x2(sr[2 * i], sr[2 * i + 1], p.scale);
                             pw[w] = b3_direct_select_late(x, p.b3);
+#endif
                         } else {
                             pw[w] = native_sigmoid_pair(sr[2 * i], sr[2 * i + 1], p.sigmoid_mul, p.sigmoid_add);
                         }
