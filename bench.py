@@ -1120,11 +1120,13 @@ def run_profile_case(args):
             run = lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gate.data_ptr(), up.data_ptr(), rows * hidden, 3, 1, 0, stream))
         else:
             run = lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, stream))
-    elif case in ("attn_softcap", "attn_sigmoid", "attn_softmax", "attn_softmax_full", "attn_softcap_full"):
+    elif case in ("attn_softcap", "attn_sigmoid", "attn_softmax", "attn_softmax_full", "attn_softcap_full",
+                  "attn_softcap_native_full", "attn_sigmoid_native"):
         import ctypes
         B, S, Hq, Hk, D = 1, n, 32, 8, 128      # --profile-n is the sequence length here
-        mode = {"attn_softcap": 0, "attn_sigmoid": 1, "attn_softmax": 2, "attn_softmax_full": 2, "attn_softcap_full": 0}[case]
-        causal = 0 if mode == 1 or case.endswith("_full") else 1   # "_full": every key tile, no mask
+        mode = {"attn_softcap": 0, "attn_sigmoid": 1, "attn_softmax": 2, "attn_softmax_full": 2, "attn_softcap_full": 0,
+                "attn_softcap_native_full": 3, "attn_sigmoid_native": 4}[case]
+        causal = 0 if mode in (1, 4) or case.endswith("_full") else 1   # "_full": every key tile, no mask
         q = torch.randn(B, S, Hq, D, device=device, generator=g).to(torch.bfloat16)
         k = torch.randn(B, S, Hk, D, device=device, generator=g).to(torch.bfloat16)
         v = torch.randn(B, S, Hk, D, device=device, generator=g).to(torch.bfloat16)

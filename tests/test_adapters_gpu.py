@@ -145,3 +145,36 @@ def test_a_hugging_face_llama_mlp_is_recognised(cuda):
         got = model(ids).logits
     assert float((got.float() - want.float()).abs().max()) < 0.08 * float(want.float().abs().max())
     assert adapters.restore(model) == 2
+
+
+def test_b1_converter_on_a_torchtitan_llama(cuda):
+    """The trainer-side converter on TorchTitan's own Llama (whichever version is installed): after B1 every feed-forward
+    is one fused projection + packed polynomial SwiGLU + one projection, and the logits stay within the polynomial's error
+    of the unconverted model; the native variant of the same conversion reproduces them to bf16 rounding."""
+    pytest.importorskip("torchtitan")
+    import copy
+    from types import SimpleNamespace as NS
+
+    import torch
+    from torchtitan.models.llama3.model.args import TransformerModelArgs
+    from torchtitan.models.llama3.model.model import Transformer
+
+    from fast_polynomial_transcendentals_b200.sfu_repro import adapters, torchtitan_plugin as plugin
+    args = TransformerModelArgs(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, vocab_size=512, multiple_of=64, max_seq_len=128)
+    torch.manual_seed(0)
+    base = Transformer(args)
+    with torch.device(cuda):
+        base.to_empty(device=cuda)
+        base.init_weights()
+    base = base.to(torch.bfloat16)
+    tokens = torch.randint(0, 512, (2, 128), device=cuda)
+    want = base(tokens).float()
+    job = lambda variant: NS(sfu=NS(case="b1", variant=variant, strict=True), model=NS(name="sfu_llama3"),
+                             compile=NS(enable=False), training=NS(seq_len=128, local_batch_size=2, global_batch_size=2, steps=1))
+    for variant, bound in (("native", 0.02), ("polynomial", 0.08)):
+        model = copy.deepcopy(base)
+        plugin.SFUReproConverter(job(variant), NS(tp=1)).convert(model)
+        blocks = list(model.layers.values()) if hasattr(model.layers, "values") else list(model.layers)
+        assert all(isinstance(b.feed_forward, adapters.FusedGateUpFeedForward) for b in blocks)
+        got = model(tokens).float()
+        assert float((got - want).abs().max()) <= bound * float(want.abs().max()), variant

@@ -227,3 +227,97 @@ def test_gated_mlps_with_another_activation_are_not_turned_into_swiglu():
     assert isinstance(model["gelu"], Gated) and isinstance(model["relu"], Gated)
     assert isinstance(model["silu"], adapters.FusedGateUpFeedForward)
     assert sorted(n for n, _ in skipped) == ["gelu", "relu", "slotless_biased"]
+
+
+def test_trainer_converter_checks_and_converts_by_structure():
+    """The B1-B5 converter (reference: src/sfu_repro/torchtitan/plugin.py:386-482): constructor checks and messages, and
+    `convert` on stand-in modules that only look like a trainer's (no trainer installed here)."""
+    from types import SimpleNamespace as NS
+
+    from torch import nn
+
+    from fast_polynomial_transcendentals_b200.sfu_repro import adapters, torchtitan_plugin as plugin
+
+    def job(case, variant="polynomial", strict=False, model="sfu_llama3", seq_len=4096, compile_enable=False,
+            local=1, global_=1, steps=80):
+        return NS(sfu=NS(case=case, variant=variant, strict=strict), model=NS(name=model), compile=NS(enable=compile_enable),
+                  training=NS(seq_len=seq_len, local_batch_size=local, global_batch_size=global_, steps=steps))
+
+    dims = NS(tp=1)
+    for bad, message in ((job("b9"), "unknown SFU case"), (job("b2", "fast"), "unknown SFU variant"),
+                         (job("b4", strict=True), "requires model.name='sfu_deepseek_v3'"),
+                         (job("b3", seq_len=8192), "requires training.seq_len=4096"),
+                         (job("b5", "d2_safe", compile_enable=True), "compile.enable=false"),
+                         (job("b5", "d2_safe", strict=True, steps=10), "80 steps")):
+        with pytest.raises(ValueError, match=message):
+            plugin.SFUReproConverter(bad, dims)
+    with pytest.raises(ValueError, match="tensor_parallel_degree=1"):
+        plugin.SFUReproConverter(job("b1"), NS(tp=2))
+    assert plugin.attention_config("b4", "polynomial") is None
+    assert plugin.attention_config("b5", "pwl2_safe_f16").exp2_emu_freq_bwd == 32
+
+    class Attention(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.head_dim, self.attn_type = 128, "sdpa"
+            self.inner_attention = nn.Identity()
+            self.wq = nn.Linear(8, 8)
+            self.resets = 0
+
+        def init_weights(self, init_std):
+            self.resets += 1
+
+    class FeedForward(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w1, self.w2, self.w3 = nn.Linear(16, 32, bias=False), nn.Linear(32, 16, bias=False), nn.Linear(16, 32, bias=False)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.attention, self.feed_forward = Attention(), FeedForward()
+
+    class Model(nn.Module):
+        def __init__(self, layers=3):
+            super().__init__()
+            self.n_layers = layers
+            self.layers = nn.ModuleList(Block() for _ in range(layers))
+
+    model = Model()
+    plugin.SFUReproConverter(job("b1", strict=True), dims).convert(model)
+    assert all(isinstance(b.feed_forward, adapters.FusedGateUpFeedForward) for b in model.layers)
+    assert all(isinstance(b.attention.inner_attention, fa4.FA4AttentionWrapper) for b in model.layers)
+    model = Model()
+    plugin.SFUReproConverter(job("b3", strict=True), dims).convert(model)
+    wrapper = model.layers[0].attention.inner_attention
+    assert wrapper.config.sigmoid_attention and wrapper.q_norm is not None
+    with torch.no_grad():
+        wrapper.q_norm.weight.fill_(3.0)
+    model.layers[0].attention.init_weights(0.02)          # resets the norms the wrapper added, then the module's own
+    assert model.layers[0].attention.resets == 1 and float(wrapper.q_norm.weight[0]) == 1.0
+    with pytest.raises(RuntimeError, match="expected 5 patched modules, observed 3"):
+        bigger = Model()
+        bigger.n_layers = 5
+        plugin.SFUReproConverter(job("b2", "native", strict=True), dims).convert(bigger)
+    flex = Model()
+    flex.layers[1].attention.attn_type = "flex"
+    with pytest.raises(ValueError, match="requires TorchTitan SDPA attention"):
+        plugin.SFUReproConverter(job("b2"), dims).convert(flex)
+    try:
+        from torchtitan.protocols import model_converter
+    except ImportError:
+        assert plugin.register() is False                  # no trainer here: says so, does not fail
+        return
+    assert plugin.register() is True and plugin.register() is True          # idempotent
+    assert model_converter._registry_model_converter_cls[plugin.CONVERTER_NAME] is plugin.SFUReproConverter
+    # a real TorchTitan Llama (whatever version is installed): B1 replaces every feed-forward by the fused form
+    from torchtitan.models.llama3.model.args import TransformerModelArgs
+    from torchtitan.models.llama3.model.model import Transformer
+    args = TransformerModelArgs(dim=64, n_layers=2, n_heads=2, n_kv_heads=1, vocab_size=128, multiple_of=16, max_seq_len=64)
+    with torch.device("meta"):
+        titan = Transformer(args)
+    plugin.SFUReproConverter(job("b1", strict=True), dims).convert(titan)
+    blocks = list(titan.layers.values()) if hasattr(titan.layers, "values") else list(titan.layers)
+    assert len(blocks) == 2 and all(isinstance(b.feed_forward, adapters.FusedGateUpFeedForward) for b in blocks)
+    hidden = blocks[0].feed_forward.w_out.weight.shape[1]
+    assert blocks[0].feed_forward.w_in.weight.shape == (2 * hidden, 64)
