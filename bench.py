@@ -836,7 +836,7 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
         o = torch.empty_like(q)
         lse = torch.empty(B, Hq, Sq, device=device)
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        need = int(lib.fpt_attention_bwd_workspace_bytes(B, Sq, Hq))
+        need = int(lib.fpt_attention_bwd_fused_workspace_bytes(B, Sq, Hq))     # large enough for either form of the backward
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
         sq, sk, sv, so, sdo = arr(q), arr(k), arr(v), arr(o), arr(dout)
         flops = 4.0 * B * Hq * Sq * Sq * D * (0.5 if causal else 1.0)
@@ -858,7 +858,17 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
                 _, tb = time_sweep(bwd, 3, 2)
                 tfb = 2.5 * flops / (tb["bwd"] * 1e-3) / 1e12
                 entry[label]["backward"] = {"ms": tb["bwd"], "tflops": tfb, "frac_of_measured_bf16_peak": tfb / tensor_peak,
-                                            "frac_of_sustained_bf16_peak": tfb / sustained}
+                                            "frac_of_sustained_bf16_peak": tfb / sustained,
+                                            "form": "two passes, 7 matrix products executed, deterministic (the default)"}
+                if label in ("poly", "native") and route_bwd == 0:
+                    # the opt-in single pass: 5 products, partial dQ tiles reduce-added into an fp32 buffer
+                    _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"attention_bwd_fused", 1))
+                    try:
+                        _, ts = time_sweep(bwd, 3, 2)
+                    finally:
+                        _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"attention_bwd_fused", 0))
+                    entry[label]["backward_single_pass"] = {"ms": ts["bwd"], "tflops": 2.5 * flops / (ts["bwd"] * 1e-3) / 1e12,
+                                                            "vs_two_passes": tb["bwd"] / ts["bwd"]}
             if int(status.item()) != 0:
                 raise RuntimeError(f"attention kernel reported status {int(status.item()) & 0xffffffff:#x} in {name}/{label}")
         base = entry["native"]

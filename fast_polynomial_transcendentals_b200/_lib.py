@@ -51,6 +51,7 @@ SIGNATURES: dict[str, list] = {
     "fpt_attention_fwd": [_vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _vp, _vp],
     "fpt_attention_bwd_workspace_bytes": [_i64, _i64, _i64],
+    "fpt_attention_bwd_fused_workspace_bytes": [_i64, _i64, _i64],
     "fpt_attention_bwd": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64,
                           ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                           ctypes.POINTER(_i64), _int, _int, ctypes.c_float, ctypes.c_float, _int, _int, _vp, _vp],
@@ -69,7 +70,8 @@ SIGNATURES: dict[str, list] = {
     "fpt_get_tuning": [ctypes.c_char_p, ctypes.POINTER(_int)],
 }
 _RESTYPES = {"fpt_status_string": ctypes.c_char_p, "fpt_version": ctypes.c_char_p,
-             "fpt_rope_static_table_capacity": ctypes.c_int64, "fpt_attention_bwd_workspace_bytes": ctypes.c_int64}
+             "fpt_rope_static_table_capacity": ctypes.c_int64, "fpt_attention_bwd_workspace_bytes": ctypes.c_int64,
+             "fpt_attention_bwd_fused_workspace_bytes": ctypes.c_int64}
 SIGNATURES["fpt_status_string"] = [_int]
 SIGNATURES["fpt_version"] = []
 

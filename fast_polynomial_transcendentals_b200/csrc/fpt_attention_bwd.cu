@@ -5,6 +5,13 @@
 //                       S = Q K^T,  dP = dO V^T,  dS = f(S, dP),  dQ += dS K
 //   WHICH = 1  dK, dV:  one CTA per (batch, kv head, 128 keys), loops over the query heads of its group and their
 //                       query tiles;  S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
+//   WHICH = 2  dK, dV and dQ in one pass (5 matrix products per tile pair instead of 7): the dK / dV block also forms
+//                       dQ_partial = dS K for the streamed query tile (dS^T goes to shared memory as well, read back as
+//                       an MN-major A operand; K is the block's fixed tile, read as an MN-major B operand), the score-mod
+//                       warps read the partial tile out of tensor memory, stage it in shared memory and add it into an
+//                       fp32 dQ buffer with tiled reduce-add copies (one partial per key tile: the order of the
+//                       additions, and so the last bits of dQ, is not fixed from run to run); a last pass scales and
+//                       rounds the buffer to bf16
 // Written once in terms of "fixed" tiles X, Y (loaded once) and "streamed" tiles U, W (2-stage ring):
 //   S = X U^T and dP = Y W^T (both operands K-major from shared memory),
 //   acc0 += dS U and (WHICH = 1) acc1 += P W, with P / dS read from tensor memory and U / W as MN-major operands.
@@ -36,23 +43,28 @@ constexpr uint32_t kTileB = 2 * kPanelB;
 constexpr int kBwdThreads = 384;
 constexpr float kLog2eB = 1.4426950408889634f;
 
-struct BwdSmem {
+template <bool WITH_DS_TILE>
+struct BwdSmemT {
     alignas(1024) uint8_t x[kTileB];
     alignas(1024) uint8_t y[kTileB];
     alignas(1024) uint8_t u[kRing][kTileB];
     alignas(1024) uint8_t w[kRing][kTileB];
-    alignas(16) float lse2[kRing][kTile];      // WHICH = 1: per streamed query column
+    alignas(1024) uint8_t ds[WITH_DS_TILE ? kTileB : 16];   // WHICH = 2: dS^T [keys x queries] bf16, two swizzled panels
+    alignas(16) float lse2[kRing][kTile];      // WHICH >= 1: per streamed query column
     alignas(16) float delta[kRing][kTile];
     alignas(8) uint64_t xy_full;
     uint64_t uw_full[kRing], uw_empty[kRing];
     uint64_t s_full, ld_done, p_full, acc_done;
+    uint64_t dq_full, dq_read;                 // WHICH = 2: partial dQ tile complete / read out of tensor memory
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
+using BwdSmem = BwdSmemT<false>;
 
 struct BwdParams {
     uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
-    uint16_t* out1;        // dV (WHICH 1)
+    uint16_t* out1;        // dV (WHICH 1, 2)
+    float* dq_accum;       // WHICH 2: fp32 [B, S, Hq, D], zeroed before the launch (reached through its tensor map)
     const float* lse2;     // workspace plane 0: [B, Hq, S rounded up to whole tiles]
     const float* delta;    // workspace plane 1
     int batch, seq, q_heads, kv_heads;
@@ -87,7 +99,12 @@ struct BwdParams {
 #define FPT_BTRACE(slot, tag) do { } while (0)
 #endif
 
-enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone };
+enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone, kBwdDqFull, kBwdDqRead };
+
+// 16 bytes to shared memory (address from smem_u32)
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+    asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
 
 __device__ __forceinline__ float ex2f(float x) { return mufu_ex2(x); }
 
@@ -129,6 +146,21 @@ __global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const Prepas
             a.delta[row] = acc;
             a.lse2[row] = a.lse[bh * a.seq + s] * kLog2eB;
         }
+    }
+}
+
+// ---- last pass of the fused form: dq = bf16(scale * accumulated fp32 dQ), eight elements per thread and step ----------
+__global__ void __launch_bounds__(256) attention_bwd_dq_convert_kernel(const float* __restrict__ accum, uint16_t* __restrict__ dq,
+                                                                      int64_t n8, float scale) {
+#pragma unroll 1
+    for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n8; i += int64_t(gridDim.x) * 256) {
+        const float4 a = reinterpret_cast<const float4*>(accum)[2 * i], b = reinterpret_cast<const float4*>(accum)[2 * i + 1];
+        uint4 o;
+        o.x = Sfu<kBf16>::pack(a.x * scale, a.y * scale);
+        o.y = Sfu<kBf16>::pack(a.z * scale, a.w * scale);
+        o.z = Sfu<kBf16>::pack(b.x * scale, b.y * scale);
+        o.w = Sfu<kBf16>::pack(b.z * scale, b.w * scale);
+        reinterpret_cast<uint4*>(dq)[i] = o;
     }
 }
 
@@ -254,6 +286,8 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
 // 32 columns of bf16 dS pairs, then 32 columns of bf16 P pairs; the products read K steps 0..3 from the first half and
 // 4..7 from the second.
 constexpr uint32_t kColS = 0, kColDp = 128, kColAcc1 = 384;
+// WHICH 2 uses the WHICH 1 layout; its partial dQ tile (128 fp32 columns) takes the place of the dP tile once the products
+// that read dS and P from it have been issued, and is read out before dP of the next step is issued.
 template <int WHICH>
 struct Cols {
     static constexpr uint32_t acc0 = WHICH == 0 ? 384u : 256u;
@@ -269,16 +303,22 @@ template <int MODE, int WHICH, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                      const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
-                     const BwdParams p) {
+                     const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
     constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;    // no normalisation: neither lse nor delta
+    constexpr bool kKeysFixed = WHICH >= 1;                   // rows of the fixed tiles are keys, streamed tiles are queries
+    constexpr bool kFusedDq = WHICH == 2;
+    using Smem = BwdSmemT<kFusedDq>;
     extern __shared__ uint8_t smem_raw[];
-    BwdSmem& sm = *reinterpret_cast<BwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // WHICH 2 fills the shared memory of an SM to the last kilobyte and cannot afford alignment slack: the host gives it
+    // exactly sizeof(Smem) and the base is checked below (a misaligned base is reported, not used)
+    Smem& sm = *reinterpret_cast<Smem*>(kFusedDq ? reinterpret_cast<uintptr_t>(smem_raw)
+                                                 : (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Blocks are handed out x fastest: with row tiles on x the blocks that run together stream the same head's tiles,
     // which then come from L2; with heads on x they share their loop length (causal).
     const int head = p.rows_fastest ? blockIdx.y : blockIdx.x;                  // query head (WHICH 0) or kv head (WHICH 1)
     const int n_row_tiles = p.rows_fastest ? gridDim.x : gridDim.y, tile_id = p.rows_fastest ? blockIdx.x : blockIdx.y;
-    const int tile = p.causal && WHICH == 0 ? n_row_tiles - 1 - tile_id : tile_id;  // long loops first
+    const int tile = p.causal && !kKeysFixed ? n_row_tiles - 1 - tile_id : tile_id;  // long loops first
     const int b = blockIdx.z;
     const int total = (p.seq + kTile - 1) / kTile;   // a ragged last tile is zero-filled by TMA and masked below
     const int seq_pad = total * kTile;
@@ -287,11 +327,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const int row0 = tile * kTile;                // first row of the fixed tiles
     // inner loop: WHICH 0 walks key tiles 0..(causal ? tile : total-1); WHICH 1 walks, for each query head of the
     // group, query tiles (causal ? tile : 0)..total-1
-    const int first_inner = (WHICH == 1 && p.causal) ? tile : 0;
-    const int per_head = WHICH == 0 ? (p.causal ? tile + 1 : total) : total - first_inner;
-    const int n_inner = WHICH == 0 ? per_head : per_head * group;
+    const int first_inner = (kKeysFixed && p.causal) ? tile : 0;
+    const int per_head = !kKeysFixed ? (p.causal ? tile + 1 : total) : total - first_inner;
+    const int n_inner = !kKeysFixed ? per_head : per_head * group;
     const int fixed_head_x = head;
-    const int stream_head0 = WHICH == 0 ? head / group : head * group;
+    const int stream_head0 = !kKeysFixed ? head / group : head * group;
     volatile uint32_t* abort_flag = &sm.abort_flag;
 #ifdef FPT_ATTN_TRACE
     const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8);
@@ -308,7 +348,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         mbar_init(&sm.ld_done, 8);      // one arrive per score-mod warp: its S and dP values are in registers
         mbar_init(&sm.p_full, 8);       // one arrive per score-mod warp: its P and dS words are in tensor memory
         mbar_init(&sm.acc_done, 1);
+        mbar_init(&sm.dq_full, 1);
+        mbar_init(&sm.dq_read, 8);      // one arrive per score-mod warp: its part of the partial dQ tile is in registers
         sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        if (kFusedDq && (smem_u32(&sm) & 1023u) != 0u) {      // the operand layouts need 1024-byte alignment
+            sm.abort_flag = 1u;
+            atomicCAS(p.status, 0u, 0x80000000u | kBwdXY | 0x100u);
+        }
         mbar_fence_init();
         tma_prefetch_descriptor(&map_x);
         tma_prefetch_descriptor(&map_y);
@@ -343,10 +389,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 const uint32_t ph = uint32_t(t / kRing) & 1u;
                 if (t >= kRing) ok = mbar_wait(&sm.uw_empty[st], ph ^ 1u, abort_flag, p.status, kBwdUwEmpty);
                 if (!ok) break;
-                const int g = WHICH == 0 ? 0 : t / per_head;
-                const int r0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile;
+                const int g = !kKeysFixed ? 0 : t / per_head;
+                const int r0 = (first_inner + (!kKeysFixed ? t : t - g * per_head)) * kTile;
                 const int sh = stream_head0 + g;
-                const uint32_t vec_bytes = WHICH == 1 && !kSigmoidMode ? 2u * kTile * 4u : 0u;
+                const uint32_t vec_bytes = kKeysFixed && !kSigmoidMode ? 2u * kTile * 4u : 0u;
                 mbar_arrive_expect_tx(&sm.uw_full[st], 2 * kTileB + vec_bytes);
                 tma_load_4d(sm.u[st], &map_u, &sm.uw_full[st], 0, r0, sh, b);
                 tma_load_4d(sm.u[st] + kPanelB, &map_u, &sm.uw_full[st], 64, r0, sh, b);
@@ -364,6 +410,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
+            constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kTile, kDim, 1, 1);  // both operands MN-major (partial dQ)
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
             constexpr uint32_t kColAcc0 = Cols<WHICH>::acc0;
             auto dp_col = [](int t) { return Cols<WHICH>::dp(t); };
@@ -431,16 +478,34 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 for (int kk = 0; kk < 8; ++kk)       // acc0 += dS U
                     umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 64u * (kk >> 2) + 8u * (kk & 3),
                                   u_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
-                if constexpr (WHICH == 1) {
+                if constexpr (kKeysFixed) {
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)   // acc1 += P W
                         umma_ts_words(tmem + kColAcc1, tmem + dp_col(t) + 64u * (kk >> 2) + 32u + 8u * (kk & 3),
                                       w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 }
+                if constexpr (kFusedDq) {
+                    // partial dQ of the streamed query tile: dS (queries x keys: the dS^T tile in shared memory read as an
+                    // MN-major A operand) times K (the fixed tile, read as an MN-major B operand), into the dP tile's
+                    // columns, which the two products above have finished reading by the time this one runs (in order)
+                    const uint32_t ds_mn = umma_smem_desc_lo(smem_u32(sm.ds), kPanelB);
+                    const uint32_t x_mn = umma_smem_desc_lo(smem_u32(sm.x), kPanelB);
+#pragma unroll
+                    for (int kk = 0; kk < 8; ++kk)
+                        umma_ss_words(tmem + dp_col(t), ds_mn + uint32_t(kk) * (2048u / 16u), x_mn + uint32_t(kk) * (2048u / 16u),
+                                      desc_hi, idesc_mnmn, kk > 0);
+                    umma_commit(&sm.dq_full);
+                }
                 umma_commit(&sm.uw_empty[st]);
                 FPT_BTRACE(2, 13);
-                // [C] WHICH 1: the one dP tile is free again once the products above have read it (same thread, in order)
-                if constexpr (WHICH == 1) {
+                // [C] WHICH 1, 2: the one dP tile is free again once the products above have read it (same thread, in
+                // order) and, WHICH 2, once the score-mod warps have read the partial dQ tile out of it
+                if constexpr (kKeysFixed) {
+                    if constexpr (kFusedDq) {
+                        ok = mbar_wait(&sm.dq_read, uint32_t(t) & 1u, abort_flag, p.status, kBwdDqRead);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
                     if (more) {
                         issue_dp(nw_k, t + 1);
                         umma_commit(&sm.s_full);
@@ -460,7 +525,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
         const uint32_t t_s = tmem + lane_base + kColS + uint32_t(64 * half);
         float row_lse2 = 0.0f, row_delta = 0.0f;
-        if (WHICH == 0 && !kSigmoidMode) {
+        if (!kKeysFixed && !kSigmoidMode) {
             const int64_t off = (int64_t(b) * p.q_heads + head) * seq_pad + row0 + r;
             row_lse2 = p.lse2[off];
             row_delta = p.delta[off];
@@ -488,11 +553,11 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.ld_done);
             FPT_BTRACE(half, 3);
-            if (WHICH == 1 && !kSigmoidMode)   // the per-query vectors arrived on this barrier (already complete here)
+            if (kKeysFixed && !kSigmoidMode)   // the per-query vectors arrived on this barrier (already complete here)
                 ok = mbar_wait(&sm.uw_full[st], uint32_t(t / kRing) & 1u, abort_flag, p.status, kBwdUwFull);
             if (!ok) break;
-            const int g = WHICH == 0 ? 0 : t / per_head;
-            const int c0 = (first_inner + (WHICH == 0 ? t : t - g * per_head)) * kTile + 64 * half;   // first column
+            const int g = !kKeysFixed ? 0 : t / per_head;
+            const int c0 = (first_inner + (!kKeysFixed ? t : t - g * per_head)) * kTile + 64 * half;   // first column
             // tiles that need a mask: the causal diagonal, and any tile pair that touches a ragged end of the sequence
             const int tile_c0 = c0 - 64 * half;
             const bool diagonal = (p.causal && tile_c0 == row0) ||
@@ -511,7 +576,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         const int cq = 32 * chunk + 4 * quad;
                         float lv[4] = {row_lse2, row_lse2, row_lse2, row_lse2};
                         float dl[4] = {row_delta, row_delta, row_delta, row_delta};
-                        if (WHICH == 1 && !kSigmoidMode) {
+                        if (kKeysFixed && !kSigmoidMode) {
                             lds128(lse_addr + 4u * cq, lv);
                             lds128(delta_addr + 4u * cq, dl);
                         }
@@ -521,8 +586,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                             bool m0 = false, m1 = false;
                             if constexpr (decltype(masked)::value) {   // rows are queries (WHICH 0) or keys (WHICH 1)
                                 const int row_abs = row0 + r, col_abs = c0 + c;
-                                const int query0 = WHICH == 0 ? row_abs : col_abs, key0 = WHICH == 0 ? col_abs : row_abs;
-                                const int query1 = WHICH == 0 ? row_abs : col_abs + 1, key1 = WHICH == 0 ? col_abs + 1 : row_abs;
+                                const int query0 = !kKeysFixed ? row_abs : col_abs, key0 = !kKeysFixed ? col_abs : row_abs;
+                                const int query1 = !kKeysFixed ? row_abs : col_abs + 1, key1 = !kKeysFixed ? col_abs + 1 : row_abs;
                                 m0 = (p.causal && key0 > query0) || key0 >= p.seq || query0 >= p.seq;
                                 m1 = (p.causal && key1 > query1) || key1 >= p.seq || query1 >= p.seq;
                             }
@@ -537,13 +602,23 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 else columns(std::false_type{});
                 if constexpr (kChunkedStores) {
                     tmem_st_32x32b_x16(t_own + 16 * chunk, reinterpret_cast<const uint32_t(&)[16]>(dsw[16 * chunk]));
-                    if constexpr (WHICH == 1)                  // only dK / dV need P itself
+                    if constexpr (kKeysFixed)                  // only dK / dV need P itself
                         tmem_st_32x32b_x16(t_own + 32 + 16 * chunk, reinterpret_cast<const uint32_t(&)[16]>(pw[16 * chunk]));
                 }
             }
             if constexpr (!kChunkedStores) {
                 tmem_st_32x32b_x32(t_own, dsw);
-                if constexpr (WHICH == 1) tmem_st_32x32b_x32(t_own + 32, pw);
+                if constexpr (kKeysFixed) tmem_st_32x32b_x32(t_own + 32, pw);
+            }
+            if constexpr (kFusedDq) {
+                // dS^T also goes to shared memory for the partial dQ product: this thread's key row, the 64 queries of its
+                // column half = one 128-byte line of panel `half`, chunk c stored at position c ^ (row % 8) (the 128-byte
+                // swizzle of the operand layout); made visible to the tensor core's reads by the proxy fence
+                const uint32_t line = smem_u32(sm.ds) + uint32_t(half) * kPanelB + uint32_t(r) * 128u;
+#pragma unroll
+                for (int c = 0; c < 8; ++c)
+                    sts128(line + (uint32_t(c ^ (r & 7)) << 4), dsw[4 * c], dsw[4 * c + 1], dsw[4 * c + 2], dsw[4 * c + 3]);
+                fence_async_shared();
             }
             FPT_BTRACE(half, 5);
             tmem_st_wait();
@@ -551,16 +626,58 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full);
             FPT_BTRACE(half, 6);
+            if constexpr (kFusedDq) {
+                // read the partial dQ tile (rows = the streamed tile's queries, this warp's 32 lanes x its 64 columns of
+                // the head dimension) out of the dP tile's columns, release them, and add the values into the fp32 buffer
+                ok = mbar_wait(&sm.dq_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdDqFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t dq[64];
+                tmem_ld_32x32b_x32(t_own, reinterpret_cast<uint32_t(&)[32]>(dq[0]));
+                tmem_ld_32x32b_x32(t_own + 32, reinterpret_cast<uint32_t(&)[32]>(dq[32]));
+                tmem_ld_wait();
+                tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.dq_read);
+#ifndef FPT_DIAG_NO_RED            // tuning builds only: what the pass costs without the global additions
+                // The warp stages its 32 rows x 64 columns in shared memory, 32 columns per round, in its own 32 lines of the
+                // dS^T tile (4 KiB nobody else touches; the product that read them is complete), swizzled like the operand
+                // layout (chunk c of line l at position c ^ (l % 8)).  Measured: per-lane red.global.add.v4 straight from
+                // registers (every lane a different row) 472 TFLOP/s on the causal soft-cap workload, the same additions
+                // coalesced through this staging 566, the tiled reduction below 567: all three run into the L2's fp32
+                // reduction rate (~2.1 TB/s), which is what bounds the single-pass form.
+                const uint32_t scratch = smem_u32(sm.ds) + uint32_t(half) * kPanelB + uint32_t(32 * quarter) * 128u;
+                const int q_first = c0 - 64 * half + 32 * quarter;       // query of this warp's lane 0
+                // the warp's 32 rows x 32 columns of a round leave as ONE tiled reduction (the copy engine adds the box
+                // into the fp32 tensor, undoing the swizzle; rows beyond the sequence are dropped by the tensor map)
+#pragma unroll
+                for (int round = 0; round < 2; ++round) {
+#pragma unroll
+                    for (int c = 0; c < 8; ++c)
+                        sts128(scratch + uint32_t(lane) * 128u + (uint32_t(c ^ (lane & 7)) << 4), dq[32 * round + 4 * c],
+                               dq[32 * round + 4 * c + 1], dq[32 * round + 4 * c + 2], dq[32 * round + 4 * c + 3]);
+                    fence_async_shared();
+                    __syncwarp();
+                    if (lane == 0 && q_first < p.seq) {
+                        tma_reduce_add_4d(&map_dq, sm.ds + half * kPanelB + (32 * quarter) * 128, 64 * half + 32 * round, q_first,
+                                          stream_head0 + g, b);
+                        bulk_commit_group();
+                        bulk_wait_group_read0();      // the lines are free again (next round, next step's dS^T)
+                    }
+                    __syncwarp();
+                }
+#endif
+            }
         }
         if (ok && n_inner > 0) {
             ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
             if (ok) {
                 tc_fence_after_sync();
-                const int64_t heads_out = WHICH == 0 ? p.q_heads : p.kv_heads;
+                const int64_t heads_out = !kKeysFixed ? p.q_heads : p.kv_heads;
                 const int64_t off = ((int64_t(b) * p.seq + row0 + r) * heads_out + head) * kDim + 64 * half;
                 const bool real_row = row0 + r < p.seq;
 #pragma unroll
-                for (int acc = 0; acc <= WHICH; ++acc) {
+                for (int acc = 0; acc <= (kKeysFixed ? 1 : 0); ++acc) {
                     const float f = acc == 0 ? p.scale : 1.0f;
                     uint16_t* dst = (acc == 0 ? p.out0 : p.out1) + off;
 #pragma unroll
@@ -593,10 +710,21 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 
 using namespace fpt;
 
+// two planes [B, Hq, S padded to whole tiles] fp32 (lse * log2 e, delta)
+static int64_t bwd_planes_bytes(int64_t batch, int64_t seq, int64_t q_heads) {
+    const int64_t seq_pad = (seq + kTile - 1) / kTile * kTile;
+    return 2 * batch * q_heads * seq_pad * int64_t(sizeof(float));
+}
+
 extern "C" int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads) {
     if (batch <= 0 || seq <= 0 || q_heads <= 0) return 0;
-    const int64_t seq_pad = (seq + kTile - 1) / kTile * kTile;      // planes padded to whole tiles
-    return 2 * batch * q_heads * seq_pad * int64_t(sizeof(float));
+    return bwd_planes_bytes(batch, seq, q_heads);
+}
+
+// the planes, then the fp32 dQ buffer [B, S, Hq, 128] of the single-pass form
+extern "C" int64_t fpt_attention_bwd_fused_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads) {
+    if (batch <= 0 || seq <= 0 || q_heads <= 0) return 0;
+    return bwd_planes_bytes(batch, seq, q_heads) + batch * seq * q_heads * kDim * int64_t(sizeof(float));
 }
 
 extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k,
@@ -625,13 +753,17 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     if (normalised) {
         if (!out || !lse || !out_strides || !workspace) return FPT_ERR_NULL_POINTER;
         if (workspace_bytes < fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) return FPT_ERR_SCRATCH_TOO_SMALL;
-        if (reinterpret_cast<uintptr_t>(workspace) & 15u) return FPT_ERR_MISALIGNED;
         for (int i = 0; i < 3; ++i)
             if ((out_strides[i] * 2) & 7 || (dout_strides[i] * 2) & 7) return FPT_ERR_MISALIGNED;
         if ((reinterpret_cast<uintptr_t>(out) & 7u) || (reinterpret_cast<uintptr_t>(dout) & 7u)) return FPT_ERR_MISALIGNED;
     }
+    if (workspace && (reinterpret_cast<uintptr_t>(workspace) & 15u)) return FPT_ERR_MISALIGNED;
     if ((reinterpret_cast<uintptr_t>(dq) | reinterpret_cast<uintptr_t>(dk) | reinterpret_cast<uintptr_t>(dv)) & 15u)
         return FPT_ERR_MISALIGNED;
+    // the single-pass form (5 matrix products) runs when the caller's workspace also holds the fp32 dQ buffer and the
+    // tuning key allows it; otherwise the two-pass form (7 products, deterministic), which needs the planes only
+    const bool fused = workspace && workspace_bytes >= fpt_attention_bwd_fused_workspace_bytes(batch, seq, q_heads) &&
+                       fpt::tuning_attention_bwd_fused() != 0;
     DeviceInfo dev;
     if (int rc = current_device_info(&dev)) return rc;
 
@@ -696,18 +828,28 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     p.sigmoid_mul = -scale * kLog2eB;
     p.sigmoid_add = float(log2_n);
 
-    const size_t smem = sizeof(BwdSmem) + 1024;
     static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "shared memory budget");
+    static_assert(sizeof(BwdSmemT<true>) <= 227 * 1024, "shared memory budget of the single-pass form (no alignment slack)");
     const unsigned tiles = unsigned(seq_pad / kTile);
-    auto launch = [&](auto kernel, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my, const CUtensorMap& mu,
-                      const CUtensorMap& mw, uint16_t* o0, uint16_t* o1) {
+    float* dq_accum = fused ? reinterpret_cast<float*>(static_cast<char*>(workspace) + bwd_planes_bytes(batch, seq, q_heads)) : nullptr;
+    CUtensorMap map_dq = map_q;          // only the single-pass form reads it
+    if (fused) {
+        // fp32 [B, S, Hq, 128] as (dim, seq, head, batch); a box is 32 columns (one 128-byte line) x 32 query rows
+        const uint64_t dims[4] = {uint64_t(kDim), uint64_t(seq), uint64_t(q_heads), uint64_t(batch)};
+        const uint64_t strides[3] = {uint64_t(q_heads) * kDim * 4, uint64_t(kDim) * 4, uint64_t(seq) * q_heads * kDim * 4};
+        const uint32_t box[4] = {32u, 32u, 1u, 1u};
+        if (int rc = make_tensor_map_f32_4d(&map_dq, dq_accum, dims, strides, box)) return rc;
+    }
+    auto launch = [&](auto kernel, size_t smem, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my,
+                      const CUtensorMap& mu, const CUtensorMap& mw, uint16_t* o0, uint16_t* o1) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
         BwdParams pp = p;
         pp.out0 = o0;
         pp.out1 = o1;
+        pp.dq_accum = dq_accum;
         const dim3 grid = pp.rows_fastest ? dim3{tiles, heads, unsigned(batch)} : dim3{heads, tiles, unsigned(batch)};
-        kernel<<<grid, kBwdThreads, smem, stream>>>(mx, my, mu, mw, pp);
+        kernel<<<grid, kBwdThreads, smem, stream>>>(mx, my, mu, mw, map_dq, pp);
         return cuda_status(cudaGetLastError());
     };
     // Measured: with full (unmasked) attention over many heads, row tiles fastest is 10-12 % faster (B=2, S=16384, 32 heads:
@@ -721,11 +863,26 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
         constexpr int G = decltype(grad_tag)::value;
         constexpr int E = decltype(emu_tag)::value;
         constexpr int EK = decltype(kind_tag)::value;
+        if (fused) {
+            // one pass: fixed K, V; streamed Q, dO; partial dQ tiles added into the fp32 buffer, then scaled and rounded
+            const int64_t n = batch * seq * q_heads * kDim;
+            cudaError_t e = cudaMemsetAsync(dq_accum, 0, size_t(n) * sizeof(float), stream);
+            if (e != cudaSuccess) return int(e);
+            if (int rc = launch(attention_bwd_kernel<M, 2, G, E, EK>, sizeof(BwdSmemT<true>), unsigned(kv_heads), map_k, map_v,
+                                map_q, map_do, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv)))
+                return rc;
+            int64_t grid = (n / 8 + 255) / 256;
+            const int64_t cap = int64_t(dev.sm_count) * 16;
+            if (grid > cap) grid = cap;
+            attention_bwd_dq_convert_kernel<<<unsigned(grid), 256, 0, stream>>>(dq_accum, static_cast<uint16_t*>(dq), n / 8, scale);
+            return cuda_status(cudaGetLastError());
+        }
         // dQ: fixed Q, dO; streamed K, V.   dK, dV: fixed K, V; streamed Q, dO
-        if (int rc = launch(attention_bwd_kernel<M, 0, G, E, EK>, unsigned(q_heads), map_q, map_do, map_k, map_v,
+        const size_t smem = sizeof(BwdSmem) + 1024;
+        if (int rc = launch(attention_bwd_kernel<M, 0, G, E, EK>, smem, unsigned(q_heads), map_q, map_do, map_k, map_v,
                             static_cast<uint16_t*>(dq), nullptr))
             return rc;
-        return launch(attention_bwd_kernel<M, 1, G, E, EK>, unsigned(kv_heads), map_k, map_v, map_q, map_do,
+        return launch(attention_bwd_kernel<M, 1, G, E, EK>, smem, unsigned(kv_heads), map_k, map_v, map_q, map_do,
                       static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv));
     };
     if (mode == FPT_ATTN_SOFTCAP_TANH)

@@ -27,6 +27,7 @@ Tuning tuning();
 // attention kernels, order in which blocks are handed out: 0 heads fastest, 1 row blocks of one head fastest,
 // -1 (default) picks by the size of the K/V working set of the blocks that run together
 int tuning_attention_raster();
+int tuning_attention_bwd_fused();
 int tuning_rope_heads_per_block();   // fused RoPE: heads one block rotates (0: all of them)
 int tuning_attention_split();    // attention forward, column-split score-mod warps: 0 never, 1 soft-capped mode (default), 2 sigmoid mode too
 

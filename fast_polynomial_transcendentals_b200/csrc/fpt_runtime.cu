@@ -20,6 +20,7 @@ std::atomic<int> g_blocks_per_sm{0};
 std::atomic<int> g_streaming{-1};
 std::atomic<int> g_attention_split{1};
 std::atomic<int> g_attention_raster{-1};
+std::atomic<int> g_attention_bwd_fused{0};
 std::atomic<int> g_rope_heads_per_block{8};   // measured: 8 is 1.5-3 % ahead of "all heads in one block" at 32 heads
 
 enum { DT_FP16 = kFp16, DT_BF16 = kBf16 };
@@ -64,6 +65,7 @@ int current_device_info(DeviceInfo* out) {
 Tuning tuning() { return Tuning{g_blocks_per_sm.load(), g_streaming.load()}; }
 int tuning_attention_split() { return g_attention_split.load(); }
 int tuning_attention_raster() { return g_attention_raster.load(); }
+int tuning_attention_bwd_fused() { return g_attention_bwd_fused.load(); }
 int tuning_rope_heads_per_block() { return g_rope_heads_per_block.load(); }
 
 const ProgramRow* program_table(int* count) {
@@ -147,6 +149,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!std::strcmp(key, "streaming")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_streaming = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_split")) { if (value < 0 || value > 2) return FPT_ERR_BAD_SIZE; fpt::g_attention_split = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_raster")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_raster = value; return FPT_OK; }
+    if (!std::strcmp(key, "attention_bwd_fused")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_bwd_fused = value; return FPT_OK; }
     if (!std::strcmp(key, "rope_heads_per_block")) { if (value < 0 || value > 65535) return FPT_ERR_BAD_SIZE; fpt::g_rope_heads_per_block = value; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
@@ -157,6 +160,7 @@ int fpt_get_tuning(const char* key, int* value) {
     if (!std::strcmp(key, "streaming")) { *value = fpt::g_streaming; return FPT_OK; }
     if (!std::strcmp(key, "attention_split")) { *value = fpt::g_attention_split; return FPT_OK; }
     if (!std::strcmp(key, "attention_raster")) { *value = fpt::g_attention_raster; return FPT_OK; }
+    if (!std::strcmp(key, "attention_bwd_fused")) { *value = fpt::g_attention_bwd_fused; return FPT_OK; }
     if (!std::strcmp(key, "rope_heads_per_block")) { *value = fpt::g_rope_heads_per_block; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }

@@ -1,6 +1,8 @@
 // Self-test of the two tensor-core building blocks of the attention kernel on one 128x128x128 tile:
 //   mode 0:  C = A * B^T   both operands K-major in shared memory (the Q K^T form)
 //   mode 1:  C = P * V     P (bf16) staged in tensor memory, V as an MN-major shared-memory operand (the P V form)
+//   mode 2:  C = A^T * B   A written to shared memory by the threads themselves in the swizzled panel layout and read as
+//                          an MN-major A operand, B MN-major (the dQ += dS K form of the fused attention backward)
 // It exists so that descriptor encodings are validated against a plain matrix product before the full pipeline
 // depends on them, and it stays in the library as a diagnostic entry point.
 #include <cstring>
@@ -41,6 +43,24 @@ int make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, const uint64_t d
     cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
     const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), gdim, gstride, box, estride,
                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FPT_OK : FPT_ERR_BAD_SIZE;
+}
+
+int make_tensor_map_f32_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
+                           const uint32_t box[4]) {
+    EncodeTiledFn encode = encode_tiled_fn();
+    if (!encode) return FPT_ERR_NO_DEVICE;
+    if (reinterpret_cast<uintptr_t>(base) & 15u) return FPT_ERR_MISALIGNED;
+    for (int i = 0; i < 3; ++i)
+        if (strides_bytes[i] & 15u) return FPT_ERR_MISALIGNED;
+    if (box[0] * 4u != 128u) return FPT_ERR_BAD_SIZE;       // one 128-byte line per row: the span of the swizzle
+    cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
+    cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
+    cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+    cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), gdim, gstride, b, estride,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? FPT_OK : FPT_ERR_BAD_SIZE;
 }
@@ -99,6 +119,17 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
         tmem_st_wait();
         tc_fence_before_sync();
     }
+    if (mode == 2) {  // thread t owns row t (a K index) of A: 128 bf16 = two panels of eight 16-byte chunks, chunk c of
+                      // row t stored at chunk position c ^ (t % 8) of its 128-byte line (the 128-byte swizzle TMA applies)
+        const uint4* row = reinterpret_cast<const uint4*>(p_global + size_t(threadIdx.x) * 128);
+#pragma unroll
+        for (int panel = 0; panel < 2; ++panel)
+#pragma unroll
+            for (int chunk = 0; chunk < 8; ++chunk)
+                *reinterpret_cast<uint4*>(s.a + panel * kPanelBytes + threadIdx.x * 128 + ((chunk ^ (threadIdx.x & 7)) << 4)) =
+                    row[panel * 8 + chunk];
+        fence_async_shared();     // generic-proxy stores, read next by the tensor core through the async proxy
+    }
     __syncthreads();
     tc_fence_after_sync();
 
@@ -121,6 +152,12 @@ __global__ void __launch_bounds__(128) umma_selftest_kernel(const __grid_constan
                     umma_ss(tmem_c, umma_smem_desc(smem_u32(s.a) + off, 16, 1024), umma_smem_desc(smem_u32(s.b) + off, 16, 1024),
                             idesc, k > 0);
                 }
+            } else if (mode == 2) {
+                constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 1, 1);
+#pragma unroll
+                for (int k = 0; k < 8; ++k)
+                    umma_ss(tmem_c, umma_smem_desc(smem_u32(s.a) + uint32_t(k) * 2048u, kPanelBytes, 1024),
+                            umma_smem_desc(smem_u32(s.b) + uint32_t(k) * 2048u, kPanelBytes, 1024), idesc, k > 0);
             } else {
                 constexpr uint32_t idesc = umma_idesc_bf16(128, 128, 0, 1);
 #pragma unroll
@@ -193,10 +230,10 @@ extern "C" int fpt_selftest_bounded_wait(void* status, void* report, int64_t lim
 }
 
 // a, b: bf16 [128, 128] row-major device arrays; c: fp32 [128, 128]; status: one device word, 0 on success.
-// mode 0: c = a * b^T.  mode 1: c = a * b.
+// mode 0: c = a * b^T.  mode 1: c = a * b.  mode 2: c = a^T * b.
 extern "C" int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* status, fpt_stream_t stream) {
     if (!c || !a || !b || !status) return FPT_ERR_NULL_POINTER;
-    if (mode != 0 && mode != 1) return FPT_ERR_BAD_ENUM;
+    if (mode < 0 || mode > 2) return FPT_ERR_BAD_ENUM;
     DeviceInfo dev;
     if (int rc = current_device_info(&dev)) return rc;
     const uint64_t dims[4] = {128, 128, 1, 1};

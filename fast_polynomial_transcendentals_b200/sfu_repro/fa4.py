@@ -488,7 +488,13 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     needs_forward = mode not in (1, 4)
     if needs_forward and (out is None or lse is None):
         raise RuntimeError("soft-max attention backward needs the forward's out and lse")
-    need = int(_lib.load().fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) if needs_forward else 0
+    # the deterministic two-pass form by default; FPT_ATTENTION_BWD_SINGLE_PASS=1 asks for the one-pass form (5 matrix
+    # products, fp32 dQ buffer in the workspace, last bit of dQ not reproducible): it also needs the library's tuning key
+    if _env_flag("FPT_ATTENTION_BWD_SINGLE_PASS"):
+        _lib.load().fpt_set_tuning(b"attention_bwd_fused", 1)
+        need = int(_lib.load().fpt_attention_bwd_fused_workspace_bytes(batch, seq, q_heads))
+    else:
+        need = int(_lib.load().fpt_attention_bwd_workspace_bytes(batch, seq, q_heads)) if needs_forward else 0
     workspace = torch.empty(max(need, 16), dtype=torch.uint8, device=q.device)
     with torch.cuda.device(q.device):
         status = _status_for(q.device)

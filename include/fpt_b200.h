@@ -300,9 +300,20 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
  *      FPT_ATTN_SIGMOID_DIRECT and FPT_ATTN_SIGMOID_NATIVE need none of the three (NULL accepted): dS = dP * p(x) * (intercept + slope*clamp(x)),
  *      the coupled derivative of the direct cubic.  softcap_grad picks d tanh_poly / dx for FPT_ATTN_SOFTCAP_TANH:
  *      the derivative of the polynomial itself (zero where the input is clamped or the output saturated), or
- *      1 - t^2 of its value.  Deterministic: two launches (dQ; dK and dV), no atomics.  status as in the forward. */
+ *      1 - t^2 of its value.  status as in the forward.
+ *      Two forms, chosen by the size of the workspace the caller passes:
+ *        two passes (workspace >= fpt_attention_bwd_workspace_bytes; none needed in the sigmoid modes): one launch for dQ,
+ *          one for dK and dV, each recomputing S and dP: 7 matrix products per tile pair, no atomics, deterministic;
+ *        one pass (workspace >= fpt_attention_bwd_fused_workspace_bytes, in every mode, AND tuning key
+ *          "attention_bwd_fused" set to 1; the default is 0): the dK / dV blocks also form the partial dQ of every
+ *          query tile they stream (5 products per tile pair) and add it into an fp32 [B, S, Hq, 128] buffer inside
+ *          the workspace with tiled reduce-add copies; a last pass scales and rounds it to bf16.  The order of the fp32
+ *          additions is not fixed, so the last bit of a dQ element can differ from run to run (dK and dV stay
+ *          deterministic).  Measured on B200: 0.92-1.09x the two-pass form (the L2's fp32 reduction rate bounds it),
+ *          which is why it is opt-in. */
 enum { FPT_SOFTCAP_GRAD_ANALYTICAL = 0, FPT_SOFTCAP_GRAD_ONE_MINUS_T2 = 1 };
 int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
+int64_t fpt_attention_bwd_fused_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
 int fpt_attention_bwd(void* dq, void* dk, void* dv, const void* dout, const void* q, const void* k, const void* v,
                       const void* out, const void* lse, void* workspace, int64_t workspace_bytes, int64_t batch,
                       int64_t seq, int64_t q_heads, int64_t kv_heads, int64_t head_dim, const int64_t* q_strides,
@@ -327,7 +338,9 @@ int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void* dout, con
 /* ---- diagnostic: one 128x128x128 bf16 tile through the tensor-core building blocks of the attention kernel
  *      (no counterpart in the reference).  a, b: bf16 [128,128] row-major; c: fp32 [128,128];
  *      mode 0: c = a * b^T (both operands K-major in shared memory); mode 1: c = a * b (a staged in tensor memory,
- *      b an MN-major shared-memory operand).  status: one zero-initialised device word; non-zero afterwards means a
+ *      b an MN-major shared-memory operand); mode 2: c = a^T * b (a stored to shared memory by the threads in the swizzled
+ *      panel layout and read as an MN-major A operand, b MN-major: the form the fused attention backward uses for dQ).
+ *      status: one zero-initialised device word; non-zero afterwards means a
  *      bounded device-side wait ran out. */
 int fpt_selftest_umma(void* c, const void* a, const void* b, int mode, void* status, fpt_stream_t stream);
 
@@ -347,7 +360,9 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * the sigmoid mode as well (measured no faster; kept for comparison runs);
  * key "attention_raster": order in which attention blocks are handed out: 0 heads fastest, 1 row blocks of one head
  * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large);
- * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads). */
+ * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
+ * key "attention_bwd_fused": 1 lets the attention backward take its one-pass form when the workspace allows, 0 (default)
+ * keeps the deterministic two-pass form. */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 

@@ -33,7 +33,7 @@ def forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n):
     return out, lse
 
 
-def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad=0, emu=None):
+def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad=0, emu=None, single_pass=False):
     import torch
     B, S, Hq, D = q.shape
     Hk = k.shape[2]
@@ -42,7 +42,10 @@ def backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, l
     dv = torch.full((B, S, Hk, D), float("nan"), dtype=torch.bfloat16, device=cuda)
     need = fpt.load().fpt_attention_bwd_workspace_bytes(B, S, Hq)
     assert need == 2 * B * Hq * ((S + 127) // 128 * 128) * 4
-    workspace = torch.empty(need, dtype=torch.uint8, device=cuda)
+    if single_pass:      # the planes plus the fp32 dQ buffer: the entry point then takes its one-pass form
+        need = fpt.load().fpt_attention_bwd_fused_workspace_bytes(B, S, Hq)
+        assert need == 2 * B * Hq * ((S + 127) // 128 * 128) * 4 + B * S * Hq * D * 4
+    workspace = torch.full((need,), 0x7F, dtype=torch.uint8, device=cuda)       # garbage: the entry point clears what it needs
     status = torch.zeros(1, dtype=torch.int32, device=cuda)
     arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
     if emu is None:
@@ -151,6 +154,44 @@ def test_backward_with_routed_software_exponential(fpt, cuda, backend, freq, bou
         st.data_ptr(), None)
     assert common(2, 0, 10) == -5 and common(2, 9, 8) == -5      # unknown frequency, unknown backend
     assert common(0, 0, 8) == -5 and common(1, 0, 8) == -5       # routed for the plain soft-max only
+
+
+@pytest.mark.parametrize("case", CASES)
+def test_single_pass_backward_matches_the_cpu_restatement_and_the_two_pass_form(fpt, cuda, oracle, case):
+    """The one-pass form (dK / dV blocks also produce the partial dQ tiles, added in fp32; 5 matrix products instead of
+    7): same tolerance against the float64 restatement; dK and dV are the same bits as the two-pass form (same
+    arithmetic, same order); dQ differs from it by the rounding of one fp32 sum at most (one bf16 unit in the last place
+    of the largest gradients)."""
+    import torch
+    from oracle import attention_bwd
+    B, S, Hq, Hk, mode, causal, softcap, log2_n, softcap_grad = case
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(4321)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    dout = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    out, lse = forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    two = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad)
+    lib = fpt.load()
+    assert lib.fpt_set_tuning(b"attention_bwd_fused", 1) == 0          # the one-pass form is opt-in
+    try:
+        one = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
+    finally:
+        assert lib.fpt_set_tuning(b"attention_bwd_fused", 0) == 0
+    _, _, want_dq, want_dk, want_dv = attention_bwd.attention_fwd_bwd(bits(q), bits(k), bits(v), bits(dout), mode, causal, scale,
+                                                                      softcap, log2_n, softcap_grad)
+    close(one[0], want_dq, "dq")
+    close(one[1], want_dk, "dk")
+    close(one[2], want_dv, "dv")
+    assert torch.equal(one[1], two[1]) and torch.equal(one[2], two[2]), "dK / dV of the two forms must be the same bits"
+    gap = (one[0].float() - two[0].float()).abs().max()
+    assert float(gap) <= 2.0 ** -7 * float(two[0].float().abs().max()), float(gap)
+    # with the tuning key off (the default) the same call, large workspace and all, takes the two-pass form: bits equal
+    forced = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
+    assert all(torch.equal(a, b) for a, b in zip(forced, two))
 
 
 def test_plain_softmax_backward_matches_torch_autograd(fpt, cuda):

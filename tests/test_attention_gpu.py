@@ -12,9 +12,10 @@ def stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 def test_umma_tile_matches_matmul(fpt, cuda, mode):
-    """One 128^3 bf16 tile: Q K^T form (both operands K-major) and P V form (tensor-memory A, MN-major B)."""
+    """One 128^3 bf16 tile: Q K^T form (both operands K-major), P V form (tensor-memory A, MN-major B) and the dQ form
+    (A stored by the threads into swizzled shared memory and read MN-major, B MN-major)."""
     import torch
     g = torch.Generator(device=cuda)
     g.manual_seed(1234 + mode)
@@ -25,7 +26,7 @@ def test_umma_tile_matches_matmul(fpt, cuda, mode):
     fpt.call("fpt_selftest_umma", c.data_ptr(), a.data_ptr(), b.data_ptr(), mode, status.data_ptr(), stream())
     torch.cuda.synchronize()
     assert int(status.item()) == 0, hex(int(status.item()) & 0xFFFFFFFF)
-    want = a.float() @ (b.float().t() if mode == 0 else b.float())
+    want = (a.float() @ b.float().t()) if mode == 0 else (a.float() @ b.float()) if mode == 1 else (a.float().t() @ b.float())
     err = (c - want).abs().max().item()
     assert err < 1e-3 * max(1.0, want.abs().max().item()), err
 
