@@ -477,11 +477,12 @@ def run_gpu_arm(args):
     del u8, frac, ang, out16, out_sc
     torch.cuda.empty_cache()
     extras["swiglu_bf16"] = bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep)
+    extras["gate_up_swiglu_bf16"] = bench_gate_up(torch, lib, _lib, device, S, time_sweep)
     extras["b3_config1"] = bench_b3(torch, lib, _lib, device, S, time_graph)
     extras["attention_fwd_bf16"] = bench_attention(torch, lib, _lib, device, S, time_sweep)
     extras["sharded"] = sharded
 
-    cpu = cpu_baseline()
+    cpu = cpu_baseline() if world == 1 else None     # the host cores are timed alone, not beside other ranks' work
     dominant = functions["sigmoid"]
     line = {
         "metric": "elements_per_s_fp16_function_sweep", "value": value, "unit": "elements/s", "n_gpus": world,
@@ -788,6 +789,87 @@ def bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep):
         out[name] = {k: {"ms": v, "elements_per_s": n / (v * 1e-3), "gbs": 6 * n / (v * 1e-3) / 1e9,
                          "frac_of_measured_hbm": 6 * n / (v * 1e-3) / 1e9 / hbm_peak} for k, v in t.items()}
         del packed, gate, up, o
+    torch.cuda.empty_cache()
+    return out
+
+
+def bench_gate_up(torch, lib, _lib, device, S, time_sweep):
+    """The projection that feeds the SwiGLU with the activation in its epilogue (`fpt_gate_up_swiglu`) next to the two-step
+    path it replaces, at the B1 and B4 sizes: library matrix product(s) writing [gate | up], then this library's SwiGLU
+    kernel reading them back.  The candidates alternate inside one timed loop, so that they meet the same clocks."""
+    import ctypes
+    _, tensor_peak, _ = measured_peaks()
+    sustained = measured_sustained_tflops()
+    vp = ctypes.c_void_p
+    status = torch.zeros(1, dtype=torch.int32, device=device)
+    g = torch.Generator(device=device)
+    g.manual_seed(SEED)
+    out = {"timing": "20 rounds of [fused, products, activation] back to back (about 0.1 s: clocks as in a training step)"}
+
+    def fused_call(o, x, wg, wu, rows, dim, hidden, group_stride, ends, groups):
+        return lambda: _lib.check("fpt_gate_up_swiglu", lib.fpt_gate_up_swiglu(
+            o.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), rows, dim, hidden, dim, dim, group_stride, hidden,
+            vp(ends.data_ptr()) if ends is not None else None, groups, 3, 0, 0, status.data_ptr(), S()))
+
+    # B1: Llama-3-8B feed-forward, 16384 tokens
+    rows, dim, hidden = 16384, 4096, 14336
+    x = torch.randn(rows, dim, device=device, generator=g).to(torch.bfloat16)
+    w = (torch.randn(2 * hidden, dim, device=device, generator=g) * dim ** -0.5).to(torch.bfloat16)
+    o = torch.empty(rows, hidden, dtype=torch.bfloat16, device=device)
+    packed = torch.empty(rows, 2 * hidden, dtype=torch.bfloat16, device=device)
+    ks = [("fused", 0, fused_call(o, x, w[:hidden], w[hidden:], rows, dim, hidden, 0, None, 1)),
+          ("matmul", 0, lambda: torch.matmul(x, w.T, out=packed)),
+          ("packed_swiglu", 0, lambda: _lib.check("fpt_swish_mul_packed", lib.fpt_swish_mul_packed(
+              o.data_ptr(), packed.data_ptr(), rows, hidden, 3, 1, 0, S())))]
+    _, t = time_sweep(ks, 20, 3)
+    flops = 2.0 * rows * dim * 2 * hidden
+    two_step = t["matmul"] + t["packed_swiglu"]
+    out["B1_dense_16384x4096_to_14336"] = {
+        "fused_ms": t["fused"], "fused_tflops": flops / (t["fused"] * 1e-3) / 1e12,
+        "fused_frac_of_measured_bf16_peak": flops / (t["fused"] * 1e-3) / 1e12 / tensor_peak,
+        "fused_frac_of_sustained_bf16_peak": flops / (t["fused"] * 1e-3) / 1e12 / sustained,
+        "library_matmul_ms": t["matmul"], "library_matmul_tflops": flops / (t["matmul"] * 1e-3) / 1e12,
+        "packed_swiglu_ms": t["packed_swiglu"], "two_step_ms": two_step, "fused_speedup_vs_two_step": two_step / t["fused"],
+        "intermediate_bytes_not_written": rows * 2 * hidden * 2}
+    del x, w, o, packed
+    torch.cuda.empty_cache()
+
+    # B4: 64 routed experts, Zipf(1.1) token counts, 131072 rows
+    rows, dim, hidden, groups = 131072, 2048, 1408, 64
+    x = torch.randn(rows, dim, device=device, generator=g).to(torch.bfloat16)
+    wg = (torch.randn(groups, hidden, dim, device=device, generator=g) * dim ** -0.5).to(torch.bfloat16)
+    wu = (torch.randn(groups, hidden, dim, device=device, generator=g) * dim ** -0.5).to(torch.bfloat16)
+    weights = 1.0 / torch.arange(1, groups + 1, dtype=torch.float64) ** 1.1
+    counts = torch.multinomial(weights / weights.sum(), rows, replacement=True,
+                               generator=torch.Generator().manual_seed(SEED)).bincount(minlength=groups)
+    ends = torch.cumsum(counts, 0).to(torch.int32).to(device)
+    o = torch.empty(rows, hidden, dtype=torch.bfloat16, device=device)
+    entry = {}
+    ks = [("fused", 0, fused_call(o, x, wg, wu, rows, dim, hidden, hidden * dim, ends, groups))]
+    if hasattr(torch, "_grouped_mm"):
+        held = {}
+        def products():
+            held["gate"] = torch._grouped_mm(x, wg.transpose(-2, -1), offs=ends)
+            held["up"] = torch._grouped_mm(x, wu.transpose(-2, -1), offs=ends)
+        products()
+        ks += [("grouped_mm_x2", 0, products),
+               ("flat_swiglu", 0, lambda: _lib.check("fpt_swish_mul", lib.fpt_swish_mul(
+                   o.data_ptr(), held["gate"].data_ptr(), held["up"].data_ptr(), rows * hidden, 3, 1, 0, S())))]
+    _, t = time_sweep(ks, 20, 3)
+    flops = 2.0 * rows * dim * 2 * hidden
+    entry = {"fused_ms": t["fused"], "fused_tflops": flops / (t["fused"] * 1e-3) / 1e12,
+             "fused_frac_of_measured_bf16_peak": flops / (t["fused"] * 1e-3) / 1e12 / tensor_peak,
+             "fused_frac_of_sustained_bf16_peak": flops / (t["fused"] * 1e-3) / 1e12 / sustained,
+             "rows_of_largest_and_smallest_expert": [int(counts.max()), int(counts.min())],
+             "intermediate_bytes_not_written": rows * 2 * hidden * 2}
+    if "grouped_mm_x2" in t:
+        two_step = t["grouped_mm_x2"] + t["flat_swiglu"]
+        entry |= {"library_grouped_mm_x2_ms": t["grouped_mm_x2"], "flat_swiglu_ms": t["flat_swiglu"], "two_step_ms": two_step,
+                  "fused_speedup_vs_two_step": two_step / t["fused"]}
+    out["B4_routed_131072x2048_to_1408_x64_experts"] = entry
+    if int(status.item()) != 0:
+        raise RuntimeError(f"fpt_gate_up_swiglu reported status {int(status.item()) & 0xffffffff:#x}")
+    del x, wg, wu, o
     torch.cuda.empty_cache()
     return out
 
@@ -1167,6 +1249,19 @@ def run_profile_case(args):
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
             lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q), arr(k), arr(v), arr(o), arr(dout), mode, 0,
             1.0 / math.sqrt(D), 50.0, 12, 0, status.data_ptr(), stream))
+    elif case in ("gate_up_dense", "gate_up_grouped"):
+        # --profile-n is the number of rows; dim 4096 -> hidden 3584 (dense) or 16 groups of dim 2048 -> hidden 1408
+        rows = n
+        dim, hidden, groups = (4096, 3584, 1) if case == "gate_up_dense" else (2048, 1408, 16)
+        x = torch.randn(rows, dim, device=device, generator=g).to(torch.bfloat16)
+        wg = (torch.randn(groups, hidden, dim, device=device, generator=g) * dim ** -0.5).to(torch.bfloat16)
+        wu = (torch.randn(groups, hidden, dim, device=device, generator=g) * dim ** -0.5).to(torch.bfloat16)
+        o = torch.empty(rows, hidden, dtype=torch.bfloat16, device=device)
+        status = torch.zeros(1, dtype=torch.int32, device=device)
+        ends = torch.linspace(rows / groups, rows, groups).to(torch.int32).to(device) if groups > 1 else None
+        run = lambda: _lib.check("fpt_gate_up_swiglu", lib.fpt_gate_up_swiglu(
+            o.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), rows, dim, hidden, dim, dim, hidden * dim, hidden,
+            ends.data_ptr() if ends is not None else None, groups, 3, 0, 0, status.data_ptr(), stream))
     else:
         raise SystemExit(f"unknown profile case {case}")
     for _ in range(args.steps):

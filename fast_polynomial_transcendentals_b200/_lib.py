@@ -34,6 +34,7 @@ SIGNATURES: dict[str, list] = {
     "fpt_swish_mul_bwd": [_vp, _vp, _vp, _vp, _vp, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed": [_vp, _vp, _i64, _i64, _int, _int, _int, _vp],
     "fpt_swish_mul_packed_bwd": [_vp, _vp, _vp, _i64, _i64, _int, _int, _int, _vp],
+    "fpt_gate_up_swiglu": [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _i64, _vp, _i64, _int, _int, _int, _vp, _vp],
     "fpt_b3_sigmoid_direct": [_vp, _vp, _vp, _i64, _int, _int, _vp],
     "fpt_b3_sigmoid_direct_variant": [_vp, _vp, _vp, _i64, _int, _int, _int, _vp],
     "fpt_fwd_deriv": [_vp, _vp, _vp, _i64, _int, _int, _vp],

@@ -1,0 +1,405 @@
+// Gate / up projection with the SwiGLU applied in the epilogue, for sm_100a: out = swish(x Wg^T) * (x Wu^T) without the
+// [rows, 2 hidden] intermediate ever reaching memory.  Dense (one weight pair) and grouped (expert-sorted rows, one
+// weight pair per group) in one kernel.
+//
+// Persistent CTAs, one per SM, each walking tiles of (128 x HALVES) rows x 128 hidden columns.  128 rows of a tile own
+// ONE accumulator of 128 x 256 fp32 in tensor memory: columns 0..127 are the gate product, 128..255 the up product of
+// the same hidden columns, so that one tcgen05.mma of shape 128 x 256 x 16 feeds both and the epilogue finds a gate
+// value and its up value in the same lane.
+//   warp 0      TMA producer: x tile [128 HALVES x 64] and the two weight tiles [128 x 64] per K block into a ring
+//   warp 1      single-thread tcgen05.mma issuer (both operands K-major from shared memory, 128-byte swizzle)
+//   warp 2      allocates tensor memory (512 columns = two accumulators)
+//   warps 4..   epilogue, four warps per accumulator: thread = one row; fp32 -> bf16 (round to nearest even, what a
+//               separate GEMM would have stored), then the same packed polynomial program as fpt_swish_mul, then
+//               16-byte stores
+// HALVES = 1 (grouped problems: ragged groups waste less of a 128-row tile): the two accumulators alternate, the epilogue
+// of a tile runs under the products of the next one; 4-stage ring.
+// HALVES = 2 (dense problems): both accumulators belong to one tile of 256 rows whose two halves share every weight
+// tile, which takes a third off the bytes that have to arrive per product (64 instead of 96 KiB per 2 x 128 x 256 x 64)
+// -- the kernel is bound by that arrival rate, not by the tensor pipe -- at the price of an epilogue that overlaps
+// only with the loads of the next tile; 3-stage ring of 64 KiB.
+// The result therefore equals fpt_swish_mul_packed applied to this kernel's own raw [gate | up] output bit for bit
+// (epilogue = FPT_GATE_UP_RAW writes that output).
+// Tile order: bands of 4096 rows; inside a band the hidden tile is the slow index, so that the CTAs running together
+// share a few weight panels and the band's rows stay in L2 (measured at 16384 x 4096 -> 14336 under the power cap: bands
+// of 1024 / 2048 / 4096 / 8192 / 16384 rows give 0.93 / 0.95 / 1 / 0.93 / 0.83 of the best rate).  Groups are bands of
+// their own (their rows use other weights).
+// Every mbarrier wait is bounded; on a timeout the CTA records where it stopped and unwinds.
+#include <algorithm>
+#include <type_traits>
+
+#include "fpt_common.h"
+#include "fpt_programs.h"
+#include "fpt_sm100.cuh"
+
+namespace fpt {
+namespace {
+
+using namespace sm100;
+
+constexpr int kRowsPerHalf = 128;
+constexpr int kHiddenPerTile = 128;
+constexpr int kBlockK = 64;
+#ifndef FPT_GATE_UP_BAND_ROWS
+#define FPT_GATE_UP_BAND_ROWS 4096
+#endif
+// Tuning builds only (-DFPT_GATE_UP_DIAG=n): 1 leaves out the epilogue's work, 2 the loads (the products run on whatever
+// shared memory holds), 3 the products; each shows what the other two sustain alone.  Results are then meaningless.
+#ifndef FPT_GATE_UP_DIAG
+#define FPT_GATE_UP_DIAG 0
+#endif
+constexpr int kBandRows = FPT_GATE_UP_BAND_ROWS;   // rows per band
+constexpr int kMaxGroups = 256;
+constexpr uint32_t kXHalfBytes = kRowsPerHalf * 128;   // 128 rows x 64 bf16
+constexpr uint32_t kWBytes = 2 * kHiddenPerTile * 128;
+constexpr int kMaxThreads = 384;
+
+template <int HALVES>
+struct GateUpSmem {
+    static constexpr int kRing = 192 * 1024 / int(HALVES * kXHalfBytes + kWBytes);
+    alignas(1024) uint8_t x[kRing][HALVES * kXHalfBytes];
+    alignas(1024) uint8_t w[kRing][kWBytes];       // rows 0..127 gate weights, 128..255 up weights
+    alignas(8) uint64_t full[kRing];
+    uint64_t empty[kRing];
+    uint64_t acc_full[2], acc_empty[2];
+    int32_t group_begin[kMaxGroups], group_end[kMaxGroups];
+    int32_t tile_prefix[kMaxGroups + 1];           // tiles of the groups before g
+    int32_t warp_total[kMaxThreads / 32];
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+struct GateUpParams {
+    uint16_t* out;
+    const int32_t* group_ends;     // device, cumulative row counts per group, or null (one group of all rows)
+    int64_t out_ld;
+    int rows, hidden, groups;
+    int hidden_tiles, k_blocks;
+    int raw;
+    uint32_t* status;
+};
+
+enum : uint32_t { kGuEmpty = 1, kGuFull, kGuAccEmpty, kGuAccFull };
+
+struct Tile {
+    int row0, row_end, hidden_tile, group;
+};
+
+// tile index -> coordinates; every role decodes the same sequence
+template <int HALVES>
+__device__ __forceinline__ Tile decode_tile(const GateUpSmem<HALVES>& sm, const GateUpParams& p, int tile) {
+    constexpr int kRowsPerTile = kRowsPerHalf * HALVES, kBand = kBandRows / kRowsPerTile;
+    int lo = 0, hi = p.groups - 1;
+    while (lo < hi) {                               // last group whose prefix is <= tile
+        const int mid = (lo + hi + 1) >> 1;
+        if (sm.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+    }
+    const int g = lo;
+    const int begin = sm.group_begin[g], end = sm.group_end[g];
+    const int row_tiles = (end - begin + kRowsPerTile - 1) / kRowsPerTile;
+    const int r = tile - sm.tile_prefix[g];
+    const int per_band = kBand * p.hidden_tiles;
+    const int band = r / per_band, r2 = r - band * per_band;
+    const int in_band = min(kBand, row_tiles - band * kBand);
+    const int hidden_tile = r2 / in_band, row_tile = band * kBand + (r2 - hidden_tile * in_band);
+    return Tile{begin + row_tile * kRowsPerTile, end, hidden_tile, g};
+}
+
+struct RawEpilogue {};
+
+template <class Op, int HALVES>
+__global__ void __launch_bounds__(128 + 128 * HALVES, 1)
+gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                      const __grid_constant__ CUtensorMap map_wu, const GateUpParams p, const Op op) {
+    using Smem = GateUpSmem<HALVES>;
+    constexpr int kRing = Smem::kRing, kRowsPerTile = kRowsPerHalf * HALVES;
+    constexpr uint32_t kXBytes = HALVES * kXHalfBytes;
+    extern __shared__ uint8_t smem_raw[];
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    volatile uint32_t* abort_flag = &sm.abort_flag;
+
+    // ---- the tile table: rows of every group, tiles before every group
+    {
+        const int g = threadIdx.x;                  // at most 256 groups: the launch has at least 256 threads
+        int begin = 0, end = 0;
+        if (g < p.groups) {
+            if (p.group_ends) {
+                begin = g ? p.group_ends[g - 1] : 0;
+                end = p.group_ends[g];
+            } else {
+                end = p.rows;
+            }
+            begin = min(max(begin, 0), p.rows);
+            end = min(max(end, begin), p.rows);
+            sm.group_begin[g] = begin;
+            sm.group_end[g] = end;
+        }
+        const int tiles = (end - begin + kRowsPerTile - 1) / kRowsPerTile * p.hidden_tiles;
+        int scan = tiles;
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+            const int other = __shfl_up_sync(0xffffffffu, scan, off);
+            if (lane >= off) scan += other;
+        }
+        if (lane == 31) sm.warp_total[warp] = scan;
+        __syncthreads();
+        int before = 0;
+        for (int w = 0; w < warp; ++w) before += sm.warp_total[w];
+        if (g < p.groups) sm.tile_prefix[g + 1] = before + scan;
+        if (g == 0) sm.tile_prefix[0] = 0;
+    }
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kRing; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sm.acc_full[a], 1);
+            mbar_init(&sm.acc_empty[a], 4);        // one arrive per epilogue warp
+        }
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        mbar_fence_init();
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(&map_wg);
+        tma_prefetch_descriptor(&map_wu);
+    }
+    if (warp == 2) {
+        tmem_alloc(&sm.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const int total_tiles = sm.tile_prefix[p.groups];
+    const bool skip = sm.abort_flag != 0u;
+
+    // Accumulators: HALVES = 1 alternates them (tile `local` uses accumulator local & 1 for the (local >> 1)-th time);
+    // HALVES = 2 gives accumulator h to rows 128 h .. 128 h + 127 of every tile.
+    if (skip) {
+        // a CTA that starts after another one reported a timeout does nothing
+    } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+                const Tile t = decode_tile(sm, p, tile);
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kRing, use = it / kRing;
+                    if (use > 0) ok = mbar_wait(&sm.empty[s], (use - 1u) & 1u, abort_flag, p.status, kGuEmpty);
+                    if (!ok) break;
+#if FPT_GATE_UP_DIAG == 2
+                    mbar_arrive(&sm.full[s]);
+#else
+                    mbar_arrive_expect_tx(&sm.full[s], kXBytes + kWBytes);
+                    tma_load_4d(sm.x[s], &map_x, &sm.full[s], kb * kBlockK, t.row0, 0, 0);
+                    tma_load_4d(sm.w[s], &map_wg, &sm.full[s], kb * kBlockK, t.hidden_tile * kHiddenPerTile, t.group, 0);
+                    tma_load_4d(sm.w[s] + kWBytes / 2, &map_wu, &sm.full[s], kb * kBlockK, t.hidden_tile * kHiddenPerTile,
+                                t.group, 0);
+#endif
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ tcgen05.mma issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(kRowsPerHalf, 2 * kHiddenPerTile, 0, 0);
+            constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+                for (int kb = 0; kb < p.k_blocks && ok; ++kb, ++it) {
+                    const uint32_t s = it % kRing, use_s = it / kRing;
+                    ok = mbar_wait(&sm.full[s], use_s & 1u, abort_flag, p.status, kGuFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t x_lo = umma_smem_desc_lo(smem_u32(sm.x[s]), 16);
+                    const uint32_t w_lo = umma_smem_desc_lo(smem_u32(sm.w[s]), 16);
+#pragma unroll
+                    for (int h = 0; h < HALVES; ++h) {
+                        const uint32_t a = HALVES == 1 ? (local & 1u) : uint32_t(h);
+                        const uint32_t use = HALVES == 1 ? (local >> 1) : local;
+                        if (kb == 0 && use > 0) {       // the epilogue of this accumulator's previous tile has read it
+                            ok = mbar_wait(&sm.acc_empty[a], (use - 1u) & 1u, abort_flag, p.status, kGuAccEmpty);
+                            if (!ok) break;
+                            tc_fence_after_sync();
+                        }
+                        const uint32_t d = tmem + a * 256u, xh = x_lo + uint32_t(h) * (kXHalfBytes / 16u);
+#pragma unroll
+#if FPT_GATE_UP_DIAG != 3
+                        for (uint32_t k = 0; k < kBlockK / 16; ++k)  // 32 bytes along the swizzled row per K step of 16
+                            umma_ss_words(d, xh + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#endif
+                    }
+                    if (!ok) break;
+                    umma_commit(&sm.empty[s]);
+                }
+                if (ok) {
+                    if constexpr (HALVES == 1) {
+                        umma_commit(&sm.acc_full[local & 1u]);
+                    } else {
+                        umma_commit(&sm.acc_full[0]);
+                        umma_commit(&sm.acc_full[1]);
+                    }
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue
+        const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+        const int half = (warp - 4) >> 2;              // 0 when HALVES = 1
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
+            const Tile t = decode_tile(sm, p, tile);
+            const uint32_t a = HALVES == 1 ? (local & 1u) : uint32_t(half);
+            const uint32_t use = HALVES == 1 ? (local >> 1) : local;
+            ok = mbar_wait(&sm.acc_full[a], use & 1u, abort_flag, p.status, kGuAccFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = t.row0 + half * kRowsPerHalf + 32 * (warp & 3) + lane;
+            const bool valid = row < t.row_end;
+            const uint32_t t_acc = tmem + lane_base + a * 256u;
+            uint16_t* out_row = p.out + int64_t(row) * p.out_ld + t.hidden_tile * kHiddenPerTile;
+#if FPT_GATE_UP_DIAG != 1
+#pragma unroll 1
+            for (int c = 0; c < kHiddenPerTile / 32; ++c) {
+                uint32_t g[32], u[32];
+                tmem_ld_32x32b_x32(t_acc + uint32_t(c) * 32u, g);
+                tmem_ld_32x32b_x32(t_acc + 128u + uint32_t(c) * 32u, u);
+                tmem_ld_wait();
+                uint32_t gw[16], uw[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    gw[i] = Sfu<kBf16>::pack(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+                    uw[i] = Sfu<kBf16>::pack(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+                }
+                if constexpr (std::is_same<Op, RawEpilogue>::value) {
+                    if (valid) {
+                        uint4* dg = reinterpret_cast<uint4*>(out_row + c * 32);
+                        uint4* du = reinterpret_cast<uint4*>(out_row + p.hidden + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) {
+                            dg[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
+                            du[q] = make_uint4(uw[4 * q], uw[4 * q + 1], uw[4 * q + 2], uw[4 * q + 3]);
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) {
+                        const uint32_t in[2] = {gw[i], uw[i]};
+                        uint32_t o[1];
+                        op.apply(in, o);
+                        gw[i] = o[0];
+                    }
+                    if (valid) {
+                        uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
+#pragma unroll
+                        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
+                    }
+                }
+            }
+#endif
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.acc_empty[a]);
+        }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 2) tmem_dealloc(tmem, 512);
+}
+
+// out = swish(gate) * up on packed bf16 lanes (the operator of fpt_swish_mul)
+template <int SHAPE, int DEG>
+struct PolySwishMul {
+    ProgramWords p;
+    __device__ __forceinline__ void apply(const uint32_t (&in)[2], uint32_t (&out)[1]) const {
+        out[0] = Pk<kBf16>::mul(eval_program<kBf16, SHAPE, DEG>(in[0], p), in[1]);
+    }
+};
+struct NativeSwishMul {
+    __device__ __forceinline__ void apply(const uint32_t (&in)[2], uint32_t (&out)[1]) const {
+        out[0] = Pk<kBf16>::mul(eval_native<kBf16, kNatSwish>(in[0]), in[1]);
+    }
+};
+
+}  // namespace
+}  // namespace fpt
+
+using namespace fpt;
+
+extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, const void* w_up, int64_t rows, int64_t dim,
+                                  int64_t hidden, int64_t x_ld, int64_t w_ld, int64_t w_group_stride, int64_t out_ld,
+                                  const int32_t* group_ends, int64_t groups, int degree, int source, int epilogue,
+                                  void* status, fpt_stream_t stream) {
+    if (rows < 0 || dim <= 0 || hidden <= 0 || groups <= 0) return FPT_ERR_BAD_SIZE;
+    if (groups > kMaxGroups || rows > 0x7fffffff - 2 * kRowsPerHalf || (groups > 1 && !group_ends)) return FPT_ERR_BAD_SIZE;
+    if (hidden % kHiddenPerTile != 0 || dim % 8 != 0) return FPT_ERR_UNSUPPORTED_SHAPE;
+    if (epilogue != FPT_GATE_UP_SWIGLU && epilogue != FPT_GATE_UP_RAW) return FPT_ERR_BAD_ENUM;
+    if (source != FPT_SRC_CURRENT && source != FPT_SRC_SOLLYA) return FPT_ERR_BAD_ENUM;
+    if (!status) return FPT_ERR_NULL_POINTER;
+    if (rows == 0) return FPT_OK;
+    if (!out || !x || !w_gate || !w_up) return FPT_ERR_NULL_POINTER;
+    const int64_t out_width = epilogue == FPT_GATE_UP_RAW ? 2 * hidden : hidden;
+    if (x_ld < dim || w_ld < dim || out_ld < out_width || w_group_stride < 0) return FPT_ERR_BAD_SIZE;
+    if ((reinterpret_cast<uintptr_t>(out) & 15u) || ((out_ld * 2) & 15)) return FPT_ERR_MISALIGNED;
+    DeviceInfo dev;
+    if (int rc = current_device_info(&dev)) return rc;
+
+    // 256-row tiles halve the weight bytes per row where the rows are plentiful and regular; ragged groups lose less of
+    // a 128-row tile
+    const int tile_rows_key = fpt::tuning_gate_up_tile_rows();
+    const int halves = tile_rows_key ? tile_rows_key / kRowsPerHalf : (group_ends ? 1 : 2);
+    const int tile_rows = halves * kRowsPerHalf;
+
+    CUtensorMap map_x, map_wg, map_wu;
+    {
+        const uint64_t dims[4] = {uint64_t(dim), uint64_t(rows), 1, 1};
+        const uint64_t strides[3] = {uint64_t(x_ld) * 2, uint64_t(x_ld) * 2 * uint64_t(rows), uint64_t(x_ld) * 2 * uint64_t(rows)};
+        if (int rc = make_tensor_map_bf16_4d(&map_x, x, dims, strides, uint32_t(tile_rows))) return rc;
+    }
+    {
+        const uint64_t group_bytes = groups > 1 ? uint64_t(w_group_stride) * 2 : uint64_t(w_ld) * 2 * uint64_t(hidden);
+        const uint64_t dims[4] = {uint64_t(dim), uint64_t(hidden), uint64_t(groups), 1};
+        const uint64_t strides[3] = {uint64_t(w_ld) * 2, group_bytes, group_bytes * uint64_t(groups)};
+        if (int rc = make_tensor_map_bf16_4d(&map_wg, w_gate, dims, strides, kHiddenPerTile)) return rc;
+        if (int rc = make_tensor_map_bf16_4d(&map_wu, w_up, dims, strides, kHiddenPerTile)) return rc;
+    }
+    GateUpParams p{};
+    p.out = static_cast<uint16_t*>(out);
+    p.group_ends = group_ends;
+    p.out_ld = out_ld;
+    p.rows = int(rows);
+    p.hidden = int(hidden);
+    p.groups = int(groups);
+    p.hidden_tiles = int(hidden / kHiddenPerTile);
+    p.k_blocks = int((dim + kBlockK - 1) / kBlockK);
+    p.raw = epilogue == FPT_GATE_UP_RAW;
+    p.status = static_cast<uint32_t*>(status);
+
+    static_assert(sizeof(GateUpSmem<1>) + 1024 <= 227 * 1024 && sizeof(GateUpSmem<2>) + 1024 <= 227 * 1024, "shared memory budget");
+    // the number of tiles of a grouped problem is only known on the device: one CTA per SM, CTAs without a tile leave
+    const int64_t dense_tiles = (rows + tile_rows - 1) / tile_rows * (hidden / kHiddenPerTile);
+    const unsigned grid = unsigned(group_ends ? dev.sm_count : std::min<int64_t>(dense_tiles, dev.sm_count));
+    auto launch_halves = [&](auto op, auto halves_c) {
+        constexpr int H = decltype(halves_c)::value;
+        const size_t smem = sizeof(GateUpSmem<H>) + 1024;
+        auto kernel = gate_up_swiglu_kernel<decltype(op), H>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
+        kernel<<<grid, 128 + 128 * H, smem, stream>>>(map_x, map_wg, map_wu, p, op);
+        return cuda_status(cudaGetLastError());
+    };
+    auto launch = [&](auto op) { return halves == 2 ? launch_halves(op, IC<2>{}) : launch_halves(op, IC<1>{}); };
+    if (epilogue == FPT_GATE_UP_RAW) return launch(RawEpilogue{});
+    if (degree == 0) return launch(NativeSwishMul{});
+    const ProgramRow* row = find_program(FPT_FN_SWISH, FPT_FWD, degree, FPT_BF16, source);
+    if (!row || row->degree != 3) return FPT_ERR_UNKNOWN_PROGRAM;      // the B1 / B4 program is the cubic
+    const ProgramWords words = program_words(*row);
+    if (row->shape == kSwish) return launch(PolySwishMul<kSwish, 3>{words});
+    if (row->shape == kXmulHalf) return launch(PolySwishMul<kXmulHalf, 3>{words});
+    return FPT_ERR_UNSUPPORTED_SHAPE;
+}

@@ -16,6 +16,7 @@ from typing import Any, Callable
 import torch
 from torch import nn
 
+from ..gate_up import gate_up_swiglu
 from .activations import (resolve_mlp_activation_impl, resolve_mlp_activation_mul_impl,
                           resolve_mlp_activation_packed_impl)
 
@@ -103,12 +104,19 @@ def patch_dense_swiglu(model: nn.Module, *, variant: str = "polynomial", degree:
 class FusedGateUpFeedForward(nn.Module):
     """One [dim -> 2*hidden] projection, packed SwiGLU, one [hidden -> dim] projection (the B1 layout)."""
 
-    def __init__(self, w_in: nn.Linear, w_out: nn.Linear, activation_packed: Callable[[torch.Tensor], torch.Tensor]):
+    def __init__(self, w_in: nn.Linear, w_out: nn.Linear, activation_packed: Callable[[torch.Tensor], torch.Tensor],
+                 fused_projection: dict | None = None):
         super().__init__()
         self.w_in, self.w_out = w_in, w_out
         self.sfu_activation_packed = activation_packed
+        # {"degree": ..., "coeff_source": ...}: run projection and activation as one kernel where no gradient is wanted
+        self.sfu_fused_projection = fused_projection
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        if self.sfu_fused_projection is not None and _fusable(x, self.w_in.weight, self.w_out.weight.shape[-1]):
+            hidden = self.w_out.weight.shape[-1]
+            weight = self.w_in.weight
+            return self.w_out(gate_up_swiglu(x, weight[:hidden], weight[hidden:], **self.sfu_fused_projection))
         return self.w_out(self.sfu_activation_packed(self.w_in(x)))
 
     def init_weights(self, init_std: float) -> None:
@@ -119,12 +127,22 @@ class FusedGateUpFeedForward(nn.Module):
         nn.init.trunc_normal_(self.w_out.weight, mean=0.0, std=init_std)
 
 
+def _fusable(x: torch.Tensor, weight: torch.Tensor, hidden: int) -> bool:
+    """The one-kernel projection + SwiGLU serves bf16 CUDA inputs when no gradient is recorded (a backward pass needs the
+    two products, which that kernel never stores)."""
+    if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+        return False
+    return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden % 128 == 0
+            and weight.shape[-1] % 8 == 0)
+
+
 @torch.no_grad()
 def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
                              coeff_source: str = "current", backward_impl: str = "matched",
-                             skipped: list[tuple[str, str]] | None = None) -> int:
+                             skipped: list[tuple[str, str]] | None = None, fuse_projection: bool = False) -> int:
     """Replace every bias-free SiLU-gated MLP by `FusedGateUpFeedForward` with w_in = cat(gate, up) (rows); gated MLPs
-    with another activation are left alone and reported through `skipped`."""
+    with another activation are left alone and reported through `skipped`.  `fuse_projection=True` also lets forward
+    passes without gradients run the projection and the activation as one kernel (`gate_up.gate_up_swiglu`)."""
     implementation = "native_silu" if variant == "native" else "spline_silu_compile"
     _, activation_packed = resolve_mlp_activation_packed_impl(implementation, degree=degree, coeff_source=coeff_source,
                                                               backward_impl=backward_impl)
@@ -151,7 +169,8 @@ def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", d
                 w_out.weight.copy_(down.weight)
                 if down.bias is not None:
                     w_out.bias.copy_(down.bias)
-            setattr(parent, child_name, FusedGateUpFeedForward(w_in, w_out, activation_packed))
+            fused = {"degree": 0 if variant == "native" else degree, "coeff_source": coeff_source} if fuse_projection else None
+            setattr(parent, child_name, FusedGateUpFeedForward(w_in, w_out, activation_packed, fused))
             replaced += 1
     return replaced
 
@@ -161,20 +180,26 @@ def _is_grouped_experts(module: nn.Module) -> bool:
     return all(isinstance(w, (torch.Tensor, nn.Parameter)) and w.dim() == 3 for w in weights)
 
 
-def run_grouped_experts(w1, w2, w3, x, num_tokens_per_expert, activation_mul) -> torch.Tensor:
-    """Expert-sorted rows through three grouped GEMMs with the fused SwiGLU between them (the B4 site)."""
+def run_grouped_experts(w1, w2, w3, x, num_tokens_per_expert, activation_mul, fused_projection: dict | None = None) -> torch.Tensor:
+    """Expert-sorted rows through three grouped GEMMs with the fused SwiGLU between them (the B4 site); with
+    `fused_projection` and no gradient wanted, the first two and the activation are one kernel."""
     offsets = torch.cumsum(num_tokens_per_expert, dim=0, dtype=torch.int32)
     xb = x.bfloat16()
-    gate = torch._grouped_mm(xb, w1.bfloat16().transpose(-2, -1), offs=offsets)
-    up = torch._grouped_mm(xb, w3.bfloat16().transpose(-2, -1), offs=offsets)
-    hidden = activation_mul(gate, up)
+    if (fused_projection is not None and w1.dtype == torch.bfloat16 and w3.dtype == torch.bfloat16 and w1.shape[0] <= 256
+            and w1.stride() == w3.stride() and _fusable(xb, w1, w1.shape[-2])):
+        hidden = gate_up_swiglu(xb, w1, w3, group_ends=offsets, **fused_projection)
+    else:
+        gate = torch._grouped_mm(xb, w1.bfloat16().transpose(-2, -1), offs=offsets)
+        up = torch._grouped_mm(xb, w3.bfloat16().transpose(-2, -1), offs=offsets)
+        hidden = activation_mul(gate, up)
     return torch._grouped_mm(hidden, w2.bfloat16().transpose(-2, -1), offs=offsets).type_as(x)
 
 
 def patch_grouped_experts(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
-                          coeff_source: str = "current") -> int:
+                          coeff_source: str = "current", fuse_projection: bool = False) -> int:
     """Modules holding 3-D `w1 / w2 / w3` ([experts, hidden, dim], [experts, dim, hidden], [experts, hidden, dim])
-    and called as `forward(x, num_tokens_per_expert)`."""
+    and called as `forward(x, num_tokens_per_expert)`.  `fuse_projection=True`: forward passes without gradients run
+    the two input projections and the activation as one kernel."""
     implementation = "native_silu" if variant == "native" else "spline_silu_compile"
     _, activation_mul = resolve_mlp_activation_mul_impl(implementation, degree=degree, coeff_source=coeff_source)
     patched = 0
@@ -183,9 +208,12 @@ def patch_grouped_experts(model: nn.Module, *, variant: str = "polynomial", degr
             continue
 
         def forward(self, x, num_tokens_per_expert):
-            return run_grouped_experts(self.w1, self.w2, self.w3, x, num_tokens_per_expert, self.sfu_activation_mul)
+            return run_grouped_experts(self.w1, self.w2, self.w3, x, num_tokens_per_expert, self.sfu_activation_mul,
+                                       self.sfu_fused_projection)
 
         module.sfu_activation_mul = activation_mul
+        module.sfu_fused_projection = ({"degree": 0 if variant == "native" else degree, "coeff_source": coeff_source}
+                                       if fuse_projection else None)
         if _ORIGINAL not in module.__dict__:
             module.__dict__[_ORIGINAL] = module.forward
         module.forward = MethodType(forward, module)

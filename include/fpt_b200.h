@@ -128,6 +128,28 @@ int fpt_swish_mul_packed(void* out, const void* packed, int64_t rows, int64_t hi
 int fpt_swish_mul_packed_bwd(void* grad_packed, const void* grad_out, const void* packed, int64_t rows,
                              int64_t hidden, int degree, int dtype, int source, fpt_stream_t stream);
 
+/* ---- gate / up projection with the SwiGLU in its epilogue (the step before the activation, B1 and B4):
+ *      out[r, h] = swish(sum_k x[r, k] w_gate[g, h, k]) * (sum_k x[r, k] w_up[g, h, k]),  g = the group of row r
+ *      on the tensor cores (bf16 operands, fp32 accumulation), each product rounded to bf16 before the same packed
+ *      program as fpt_swish_mul: the [rows, 2*hidden] intermediate of
+ *      `w_in(x)` -> launch_swish_mul_packed_fwd_* (reference: src/sfu_repro/torchtitan/plugin.py:238-239, the fused
+ *      gate / up feed-forward) and of `_grouped_mm(x, w1)`, `_grouped_mm(x, w3)` -> launch_swish_mul_fwd_*
+ *      (reference: plugin.py:294-310, the routed experts) is never written.
+ *      x [rows, dim] with row stride x_ld; w_gate, w_up [groups, hidden, dim] with row stride w_ld and group stride
+ *      w_group_stride (a packed [2*hidden, dim] weight is w_gate = w, w_up = w + hidden*w_ld, groups = 1); out
+ *      [rows, hidden] (or [rows, 2*hidden] = [gate | up] with FPT_GATE_UP_RAW: the products alone, for callers that
+ *      keep them for a backward pass) with row stride out_ld; all strides in elements, all tensors bf16.
+ *      group_ends (device memory, int32, cumulative row counts: the `offs` of a grouped matrix product) may be NULL
+ *      when groups == 1; rows beyond the last end are left untouched.  hidden must be a multiple of 128, dim and the
+ *      strides multiples of 8, groups <= 256.  degree 0 = the special-function twin, 3 = the cubic program.
+ *      `status` as in the attention entry points (a zeroed device word, non-zero afterwards = a bounded wait ran
+ *      out and `out` is invalid). */
+enum { FPT_GATE_UP_SWIGLU = 0, FPT_GATE_UP_RAW = 1 };
+int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, const void* w_up, int64_t rows, int64_t dim,
+                       int64_t hidden, int64_t x_ld, int64_t w_ld, int64_t w_group_stride, int64_t out_ld,
+                       const int32_t* group_ends, int64_t groups, int degree, int source, int epilogue, void* status,
+                       fpt_stream_t stream);
+
 /* ---- B3 sigmoid attention score-mod, isolated: prob = p(score) ~ sigmoid(score - log n), bf16 out
  *      Direct piecewise cubic on the raw score with the deployed n = 4096 constants shifted to
  *      n = 2^log2_n (reference: scripts/audit_b3_deployed_fit.py:341-366 for the arithmetic,
@@ -362,7 +384,10 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large);
  * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
  * key "attention_bwd_fused": 1 lets the attention backward take its one-pass form when the workspace allows, 0 (default)
- * keeps the deterministic two-pass form. */
+ * keeps the deterministic two-pass form;
+ * key "gate_up_tile_rows": rows per tile of fpt_gate_up_swiglu, 128 or 256; 0 (default) = 256 for one group (both halves
+ * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
+ * grouped problems (a ragged group wastes less of a smaller tile). */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 
