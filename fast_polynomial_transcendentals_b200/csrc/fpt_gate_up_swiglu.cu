@@ -54,6 +54,13 @@ constexpr uint32_t kXHalfBytes = kRowsPerHalf * 128;   // 128 rows x 64 bf16
 constexpr uint32_t kWBytes = 2 * kHiddenPerTile * 128;
 constexpr int kMaxThreads = 384;
 
+// rows of every group and the number of tiles before it, built by the whole CTA at kernel start
+struct TileTable {
+    int32_t group_begin[kMaxGroups], group_end[kMaxGroups];
+    int32_t tile_prefix[kMaxGroups + 1];
+    int32_t warp_total[kMaxThreads / 32];
+};
+
 template <int HALVES>
 struct GateUpSmem {
     static constexpr int kRing = 192 * 1024 / int(HALVES * kXHalfBytes + kWBytes);
@@ -62,9 +69,7 @@ struct GateUpSmem {
     alignas(8) uint64_t full[kRing];
     uint64_t empty[kRing];
     uint64_t acc_full[2], acc_empty[2];
-    int32_t group_begin[kMaxGroups], group_end[kMaxGroups];
-    int32_t tile_prefix[kMaxGroups + 1];           // tiles of the groups before g
-    int32_t warp_total[kMaxThreads / 32];
+    TileTable table;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -86,26 +91,108 @@ struct Tile {
 };
 
 // tile index -> coordinates; every role decodes the same sequence
-template <int HALVES>
-__device__ __forceinline__ Tile decode_tile(const GateUpSmem<HALVES>& sm, const GateUpParams& p, int tile) {
-    constexpr int kRowsPerTile = kRowsPerHalf * HALVES, kBand = kBandRows / kRowsPerTile;
+template <int ROWS_PER_TILE>
+__device__ __forceinline__ Tile decode_tile(const TileTable& tb, const GateUpParams& p, int tile) {
+    constexpr int kBand = kBandRows / ROWS_PER_TILE;
     int lo = 0, hi = p.groups - 1;
     while (lo < hi) {                               // last group whose prefix is <= tile
         const int mid = (lo + hi + 1) >> 1;
-        if (sm.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
+        if (tb.tile_prefix[mid] <= tile) lo = mid; else hi = mid - 1;
     }
     const int g = lo;
-    const int begin = sm.group_begin[g], end = sm.group_end[g];
-    const int row_tiles = (end - begin + kRowsPerTile - 1) / kRowsPerTile;
-    const int r = tile - sm.tile_prefix[g];
+    const int begin = tb.group_begin[g], end = tb.group_end[g];
+    const int row_tiles = (end - begin + ROWS_PER_TILE - 1) / ROWS_PER_TILE;
+    const int r = tile - tb.tile_prefix[g];
     const int per_band = kBand * p.hidden_tiles;
     const int band = r / per_band, r2 = r - band * per_band;
     const int in_band = min(kBand, row_tiles - band * kBand);
     const int hidden_tile = r2 / in_band, row_tile = band * kBand + (r2 - hidden_tile * in_band);
-    return Tile{begin + row_tile * kRowsPerTile, end, hidden_tile, g};
+    return Tile{begin + row_tile * ROWS_PER_TILE, end, hidden_tile, g};
 }
 
+// Called by every thread of the CTA (at least 256 of them, one per possible group); contains a __syncthreads, and the
+// caller synchronises once more before the table is read.
+template <int ROWS_PER_TILE>
+__device__ __forceinline__ void build_tile_table(TileTable& tb, const GateUpParams& p) {
+    const int g = threadIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    int begin = 0, end = 0;
+    if (g < p.groups) {
+        if (p.group_ends) {
+            begin = g ? p.group_ends[g - 1] : 0;
+            end = p.group_ends[g];
+        } else {
+            end = p.rows;
+        }
+        begin = min(max(begin, 0), p.rows);
+        end = min(max(end, begin), p.rows);
+        tb.group_begin[g] = begin;
+        tb.group_end[g] = end;
+    }
+    const int tiles = (end - begin + ROWS_PER_TILE - 1) / ROWS_PER_TILE * p.hidden_tiles;
+    int scan = tiles;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+        const int other = __shfl_up_sync(0xffffffffu, scan, off);
+        if (lane >= off) scan += other;
+    }
+    if (lane == 31) tb.warp_total[warp] = scan;
+    __syncthreads();
+    int before = 0;
+    for (int w = 0; w < warp; ++w) before += tb.warp_total[w];
+    if (g < p.groups) tb.tile_prefix[g + 1] = before + scan;
+    if (g == 0) tb.tile_prefix[0] = 0;
+}
+
+// One warp's share of an accumulator (its 32 lanes = 32 rows, 128 hidden columns): fp32 -> bf16, the SwiGLU program (or
+// the two products as they are), 16-byte stores.  `t_acc` is the accumulator's tensor-memory address with the warp's
+// lane offset; gate values sit in columns 0..127, up values in 128..255.
+template <class Op>
+__device__ __forceinline__ void epilogue_rows(const Op& op, const GateUpParams& p, uint32_t t_acc, uint16_t* out_row, bool valid);
+
 struct RawEpilogue {};
+
+template <class Op>
+__device__ __forceinline__ void epilogue_rows(const Op& op, const GateUpParams& p, uint32_t t_acc, uint16_t* out_row, bool valid) {
+#if FPT_GATE_UP_DIAG != 1
+#pragma unroll 1
+    for (int c = 0; c < kHiddenPerTile / 32; ++c) {
+        uint32_t g[32], u[32];
+        tmem_ld_32x32b_x32(t_acc + uint32_t(c) * 32u, g);
+        tmem_ld_32x32b_x32(t_acc + 128u + uint32_t(c) * 32u, u);
+        tmem_ld_wait();
+        uint32_t gw[16], uw[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            gw[i] = Sfu<kBf16>::pack(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
+            uw[i] = Sfu<kBf16>::pack(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
+        }
+        if constexpr (std::is_same<Op, RawEpilogue>::value) {
+            if (valid) {
+                uint4* dg = reinterpret_cast<uint4*>(out_row + c * 32);
+                uint4* du = reinterpret_cast<uint4*>(out_row + p.hidden + c * 32);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    dg[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
+                    du[q] = make_uint4(uw[4 * q], uw[4 * q + 1], uw[4 * q + 2], uw[4 * q + 3]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                const uint32_t in[2] = {gw[i], uw[i]};
+                uint32_t o[1];
+                op.apply(in, o);
+                gw[i] = o[0];
+            }
+            if (valid) {
+                uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
+#pragma unroll
+                for (int q = 0; q < 4; ++q) dst[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
+            }
+        }
+    }
+#endif
+}
 
 template <class Op, int HALVES>
 __global__ void __launch_bounds__(128 + 128 * HALVES, 1)
@@ -119,36 +206,7 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     volatile uint32_t* abort_flag = &sm.abort_flag;
 
-    // ---- the tile table: rows of every group, tiles before every group
-    {
-        const int g = threadIdx.x;                  // at most 256 groups: the launch has at least 256 threads
-        int begin = 0, end = 0;
-        if (g < p.groups) {
-            if (p.group_ends) {
-                begin = g ? p.group_ends[g - 1] : 0;
-                end = p.group_ends[g];
-            } else {
-                end = p.rows;
-            }
-            begin = min(max(begin, 0), p.rows);
-            end = min(max(end, begin), p.rows);
-            sm.group_begin[g] = begin;
-            sm.group_end[g] = end;
-        }
-        const int tiles = (end - begin + kRowsPerTile - 1) / kRowsPerTile * p.hidden_tiles;
-        int scan = tiles;
-#pragma unroll
-        for (int off = 1; off < 32; off <<= 1) {
-            const int other = __shfl_up_sync(0xffffffffu, scan, off);
-            if (lane >= off) scan += other;
-        }
-        if (lane == 31) sm.warp_total[warp] = scan;
-        __syncthreads();
-        int before = 0;
-        for (int w = 0; w < warp; ++w) before += sm.warp_total[w];
-        if (g < p.groups) sm.tile_prefix[g + 1] = before + scan;
-        if (g == 0) sm.tile_prefix[0] = 0;
-    }
+    build_tile_table<kRowsPerTile>(sm.table, p);
     if (threadIdx.x == 0) {
         for (int s = 0; s < kRing; ++s) {
             mbar_init(&sm.full[s], 1);
@@ -172,7 +230,7 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
-    const int total_tiles = sm.tile_prefix[p.groups];
+    const int total_tiles = sm.table.tile_prefix[p.groups];
     const bool skip = sm.abort_flag != 0u;
 
     // Accumulators: HALVES = 1 alternates them (tile `local` uses accumulator local & 1 for the (local >> 1)-th time);
@@ -185,7 +243,7 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             uint32_t it = 0;
             bool ok = true;
             for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
-                const Tile t = decode_tile(sm, p, tile);
+                const Tile t = decode_tile<kRowsPerTile>(sm.table, p, tile);
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kRing, use = it / kRing;
                     if (use > 0) ok = mbar_wait(&sm.empty[s], (use - 1u) & 1u, abort_flag, p.status, kGuEmpty);
@@ -227,8 +285,8 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
                             tc_fence_after_sync();
                         }
                         const uint32_t d = tmem + a * 256u, xh = x_lo + uint32_t(h) * (kXHalfBytes / 16u);
-#pragma unroll
 #if FPT_GATE_UP_DIAG != 3
+#pragma unroll
                         for (uint32_t k = 0; k < kBlockK / 16; ++k)  // 32 bytes along the swizzled row per K step of 16
                             umma_ss_words(d, xh + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
 #endif
@@ -253,7 +311,7 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         uint32_t local = 0;
         bool ok = true;
         for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++local) {
-            const Tile t = decode_tile(sm, p, tile);
+            const Tile t = decode_tile<kRowsPerTile>(sm.table, p, tile);
             const uint32_t a = HALVES == 1 ? (local & 1u) : uint32_t(half);
             const uint32_t use = HALVES == 1 ? (local >> 1) : local;
             ok = mbar_wait(&sm.acc_full[a], use & 1u, abort_flag, p.status, kGuAccFull);
@@ -263,45 +321,7 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
             const bool valid = row < t.row_end;
             const uint32_t t_acc = tmem + lane_base + a * 256u;
             uint16_t* out_row = p.out + int64_t(row) * p.out_ld + t.hidden_tile * kHiddenPerTile;
-#if FPT_GATE_UP_DIAG != 1
-#pragma unroll 1
-            for (int c = 0; c < kHiddenPerTile / 32; ++c) {
-                uint32_t g[32], u[32];
-                tmem_ld_32x32b_x32(t_acc + uint32_t(c) * 32u, g);
-                tmem_ld_32x32b_x32(t_acc + 128u + uint32_t(c) * 32u, u);
-                tmem_ld_wait();
-                uint32_t gw[16], uw[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    gw[i] = Sfu<kBf16>::pack(__uint_as_float(g[2 * i]), __uint_as_float(g[2 * i + 1]));
-                    uw[i] = Sfu<kBf16>::pack(__uint_as_float(u[2 * i]), __uint_as_float(u[2 * i + 1]));
-                }
-                if constexpr (std::is_same<Op, RawEpilogue>::value) {
-                    if (valid) {
-                        uint4* dg = reinterpret_cast<uint4*>(out_row + c * 32);
-                        uint4* du = reinterpret_cast<uint4*>(out_row + p.hidden + c * 32);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) {
-                            dg[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
-                            du[q] = make_uint4(uw[4 * q], uw[4 * q + 1], uw[4 * q + 2], uw[4 * q + 3]);
-                        }
-                    }
-                } else {
-#pragma unroll
-                    for (int i = 0; i < 16; ++i) {
-                        const uint32_t in[2] = {gw[i], uw[i]};
-                        uint32_t o[1];
-                        op.apply(in, o);
-                        gw[i] = o[0];
-                    }
-                    if (valid) {
-                        uint4* dst = reinterpret_cast<uint4*>(out_row + c * 32);
-#pragma unroll
-                        for (int q = 0; q < 4; ++q) dst[q] = make_uint4(gw[4 * q], gw[4 * q + 1], gw[4 * q + 2], gw[4 * q + 3]);
-                    }
-                }
-            }
-#endif
+            epilogue_rows(op, p, t_acc, out_row, valid);
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.acc_empty[a]);
@@ -310,6 +330,167 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
     tc_fence_before_sync();
     __syncthreads();
     if (warp == 2) tmem_dealloc(tmem, 512);
+}
+
+// ---- the same tile of 256 rows on a PAIR of CTAs (cta_group::2) -----------------------------------------------------
+// The two CTAs of a cluster of two take 128 rows each.  The leading CTA (rank 0) loads the gate weight tile, the other
+// the up weight tile, each into the same shared-memory offset, and ONE tcgen05.mma.cta_group::2 of shape 256 x 256 x 16,
+// issued by the leading CTA, reads A from both (their own rows) and the two halves of B's N rows from both, and leaves
+// every CTA its 128 x 256 [gate | up] accumulator in its own tensor memory.  Per CTA and K block 32 KiB arrive (as with
+// 256-row tiles on one CTA) but only 16 + 16 KiB are read per product, the ring is six deep and the two accumulators
+// alternate again, so the epilogue runs under the next tile's products.
+// Hand-overs: the loads of both CTAs complete on the leading CTA's `full` barrier (cp.async.bulk.tensor ... cta_group::2
+// with the barrier's shared::cluster address; the barrier expects the bytes of both); the issuer's commits reach `empty`
+// and `acc_full` in both CTAs at once (tcgen05.commit ... multicast); the epilogue warps of both CTAs arrive on the
+// leading CTA's `acc_empty` (8 arrivals, the other CTA's through a remote arrive).
+// A first form let each CTA's loads complete on its own barrier and had a thread of the other CTA pass that on with
+// mbarrier.arrive.release.cluster: it ran at HALF speed, because a releasing remote arrive waits for every bulk load
+// still in flight into its CTA, which empties the ring (a relaxed arrive restored the speed; the direct form needs none).
+#ifndef FPT_GATE_UP_PAIR_ACCS
+#define FPT_GATE_UP_PAIR_ACCS 2
+#endif
+constexpr int kPairRing = 6;
+constexpr uint32_t kPairAccs = FPT_GATE_UP_PAIR_ACCS;      // accumulators of 256 columns (2 = all of tensor memory)
+constexpr uint32_t kPairColumns = 256u * kPairAccs;
+
+struct GateUpPairSmem {
+    alignas(1024) uint8_t x[kPairRing][kXHalfBytes];
+    alignas(1024) uint8_t w[kPairRing][kXHalfBytes];       // rank 0: 128 gate weight rows; rank 1: 128 up weight rows
+    alignas(8) uint64_t full[kPairRing];
+    uint64_t empty[kPairRing];
+    uint64_t acc_full[2], acc_empty[2];                    // acc_empty used in the leading CTA
+    TileTable table;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+template <class Op>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
+                           const __grid_constant__ CUtensorMap map_wu, const GateUpParams p, const Op op) {
+    constexpr int kRowsPerTile = 2 * kRowsPerHalf;
+    extern __shared__ uint8_t smem_raw[];
+    // the same offsets in both CTAs: the dynamic shared memory of both starts at the same address
+    GateUpPairSmem& sm = *reinterpret_cast<GateUpPairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_cta_rank();
+    volatile uint32_t* abort_flag = &sm.abort_flag;
+
+    build_tile_table<kRowsPerTile>(sm.table, p);
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kPairRing; ++s) {
+            mbar_init(&sm.full[s], 1);
+            mbar_init(&sm.empty[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(&sm.acc_full[a], 1);
+            mbar_init(&sm.acc_empty[a], 8);        // four epilogue warps in each CTA
+        }
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        mbar_fence_init();
+        tma_prefetch_descriptor(&map_x);
+        tma_prefetch_descriptor(rank == 0 ? &map_wg : &map_wu);
+    }
+    if (warp == 2) {
+        tmem_alloc_pair(&sm.tmem_base, kPairColumns);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before_sync();
+    cluster_sync_all();                             // barriers of both CTAs initialised before anyone arrives remotely
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const int total_tiles = sm.table.tile_prefix[p.groups];
+    const bool skip = sm.abort_flag != 0u;
+    const int first_tile = blockIdx.x >> 1, tile_step = gridDim.x >> 1;
+#ifdef FPT_GATE_UP_PAIR_DEBUG
+    if (threadIdx.x == 0 && blockIdx.x < 2) p.status[4 + rank] = tmem + 1u;   // tuning builds: the address each CTA was given
+#endif
+
+    if (skip) {
+        // a CTA that starts after another one reported a timeout does nothing
+    } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (both CTAs)
+        if (lane == 0) {
+            const CUtensorMap* map_w = rank == 0 ? &map_wg : &map_wu;
+            uint32_t it = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step) {
+                const Tile t = decode_tile<kRowsPerTile>(sm.table, p, tile);
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kPairRing, use = it / kPairRing;
+                    if (use > 0) ok = mbar_wait(&sm.empty[s], (use - 1u) & 1u, abort_flag, p.status, kGuEmpty);
+                    if (!ok) break;
+#if FPT_GATE_UP_DIAG == 2
+                    if (rank == 0) mbar_arrive(&sm.full[s]);
+#else
+                    // both CTAs' loads complete on the leading CTA's barrier, which expects the bytes of both
+                    const uint32_t bar = map_to_cta(smem_u32(&sm.full[s]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&sm.full[s], 4 * kXHalfBytes);
+                    tma_load_4d_pair(sm.x[s], &map_x, bar, kb * kBlockK, t.row0 + int(rank) * kRowsPerHalf, 0, 0);
+                    tma_load_4d_pair(sm.w[s], map_w, bar, kb * kBlockK, t.hidden_tile * kHiddenPerTile, t.group, 0);
+#endif
+                }
+            }
+        }
+    } else if (warp == 1 && rank == 0) {
+        // ------------------------------------------------------------------ leading CTA: tcgen05.mma issuer for the pair
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16(2 * kRowsPerHalf, 2 * kHiddenPerTile, 0, 0);
+            constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            uint32_t it = 0, local = 0;
+            bool ok = true;
+            for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
+                const uint32_t a = local % kPairAccs, use = local / kPairAccs;
+                if (use > 0) {                              // both CTAs' epilogues have read this accumulator
+                    ok = mbar_wait_cluster(&sm.acc_empty[a], (use - 1u) & 1u, abort_flag, p.status, kGuAccEmpty);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                }
+                const uint32_t d = tmem + a * 256u;
+                for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
+                    const uint32_t s = it % kPairRing, use_s = it / kPairRing;
+                    ok = mbar_wait(&sm.full[s], use_s & 1u, abort_flag, p.status, kGuFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    const uint32_t x_lo = umma_smem_desc_lo(smem_u32(sm.x[s]), 16);
+                    const uint32_t w_lo = umma_smem_desc_lo(smem_u32(sm.w[s]), 16);
+#if FPT_GATE_UP_DIAG != 3
+#pragma unroll
+                    for (uint32_t k = 0; k < kBlockK / 16; ++k)
+                        umma_ss_words_pair(d, x_lo + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+#endif
+                    umma_commit_pair(&sm.empty[s], 3);
+                }
+                if (ok) umma_commit_pair(&sm.acc_full[a], 3);
+            }
+        }
+    } else if (warp >= 4) {
+        // ------------------------------------------------------------------ epilogue (both CTAs, their own 128 rows)
+        const uint32_t lane_base = uint32_t(32 * (warp & 3)) << 16;
+        uint32_t local = 0;
+        bool ok = true;
+        for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
+            const Tile t = decode_tile<kRowsPerTile>(sm.table, p, tile);
+            const uint32_t a = local % kPairAccs, use = local / kPairAccs;
+            ok = mbar_wait(&sm.acc_full[a], use & 1u, abort_flag, p.status, kGuAccFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            const int row = t.row0 + int(rank) * kRowsPerHalf + 32 * (warp & 3) + lane;
+            uint16_t* out_row = p.out + int64_t(row) * p.out_ld + t.hidden_tile * kHiddenPerTile;
+            epilogue_rows(op, p, tmem + lane_base + a * 256u, out_row, row < t.row_end);
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) mbar_arrive(&sm.acc_empty[a]);
+                else mbar_arrive_cluster(map_to_cta(smem_u32(&sm.acc_empty[a]), 0));
+            }
+        }
+    }
+    // neither CTA may leave (or give back tensor memory) while the other can still reach its barriers or memory
+    tc_fence_before_sync();
+    __syncwarp();
+    cluster_sync_all();
+    if (warp == 2) tmem_dealloc_pair(tmem, kPairColumns);
 }
 
 // out = swish(gate) * up on packed bf16 lanes (the operator of fpt_swish_mul)
@@ -352,14 +533,19 @@ extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, 
     // 256-row tiles halve the weight bytes per row where the rows are plentiful and regular; ragged groups lose less of
     // a 128-row tile
     const int tile_rows_key = fpt::tuning_gate_up_tile_rows();
-    const int halves = tile_rows_key ? tile_rows_key / kRowsPerHalf : (group_ends ? 1 : 2);
+    // Measured (profiles): dense problems run alike on one CTA with 256-row tiles and on a pair of CTAs (the single
+    // CTA 0-4 % ahead once the power cap binds); grouped problems run 4 % faster on pairs in isolated launches and alike
+    // under the cap.  An explicit tile height asks for the single-CTA forms.
+    const int pair_key = fpt::tuning_gate_up_cta_pair();
+    const bool pair = pair_key == 1 || (pair_key < 0 && group_ends != nullptr && tile_rows_key == 0);
+    const int halves = pair ? 2 : tile_rows_key ? tile_rows_key / kRowsPerHalf : (group_ends ? 1 : 2);
     const int tile_rows = halves * kRowsPerHalf;
 
     CUtensorMap map_x, map_wg, map_wu;
     {
         const uint64_t dims[4] = {uint64_t(dim), uint64_t(rows), 1, 1};
         const uint64_t strides[3] = {uint64_t(x_ld) * 2, uint64_t(x_ld) * 2 * uint64_t(rows), uint64_t(x_ld) * 2 * uint64_t(rows)};
-        if (int rc = make_tensor_map_bf16_4d(&map_x, x, dims, strides, uint32_t(tile_rows))) return rc;
+        if (int rc = make_tensor_map_bf16_4d(&map_x, x, dims, strides, uint32_t(pair ? kRowsPerHalf : tile_rows))) return rc;
     }
     {
         const uint64_t group_bytes = groups > 1 ? uint64_t(w_group_stride) * 2 : uint64_t(w_ld) * 2 * uint64_t(hidden);
@@ -393,7 +579,19 @@ extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, 
         kernel<<<grid, 128 + 128 * H, smem, stream>>>(map_x, map_wg, map_wu, p, op);
         return cuda_status(cudaGetLastError());
     };
-    auto launch = [&](auto op) { return halves == 2 ? launch_halves(op, IC<2>{}) : launch_halves(op, IC<1>{}); };
+    auto launch_pair = [&](auto op) {
+        const size_t smem = sizeof(GateUpPairSmem) + 1024;
+        auto kernel = gate_up_swiglu_pair_kernel<decltype(op)>;
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
+        const int64_t pairs = std::min<int64_t>(group_ends ? dev.sm_count / 2 : dense_tiles, dev.sm_count / 2);
+        kernel<<<unsigned(2 * pairs), 256, smem, stream>>>(map_x, map_wg, map_wu, p, op);   // clusters of two (kernel attribute)
+        return cuda_status(cudaGetLastError());
+    };
+    auto launch = [&](auto op) {
+        if (pair) return launch_pair(op);
+        return halves == 2 ? launch_halves(op, IC<2>{}) : launch_halves(op, IC<1>{});
+    };
     if (epilogue == FPT_GATE_UP_RAW) return launch(RawEpilogue{});
     if (degree == 0) return launch(NativeSwishMul{});
     const ProgramRow* row = find_program(FPT_FN_SWISH, FPT_FWD, degree, FPT_BF16, source);

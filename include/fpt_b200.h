@@ -387,7 +387,10 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * keeps the deterministic two-pass form;
  * key "gate_up_tile_rows": rows per tile of fpt_gate_up_swiglu, 128 or 256; 0 (default) = 256 for one group (both halves
  * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
- * grouped problems (a ragged group wastes less of a smaller tile). */
+ * grouped problems (a ragged group wastes less of a smaller tile);
+ * key "gate_up_cta_pair": 1 runs fpt_gate_up_swiglu on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one product of
+ * 256 rows whose weight tile is split over the two SMs), 0 never, -1 (default) for grouped problems unless
+ * "gate_up_tile_rows" names a height. */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 

@@ -64,11 +64,16 @@ def products_fp32(x, wg, wu, ends=None):
     return want
 
 
-@pytest.fixture(params=[0, 128, 256], ids=["tile_auto", "tile_128", "tile_256"])
+@pytest.fixture(params=[(0, -1), (128, -1), (256, -1), (0, 1)], ids=["auto", "tile_128", "tile_256", "cta_pair"])
 def tile_rows(request, fpt):
-    fpt.call("fpt_set_tuning", b"gate_up_tile_rows", request.param)
+    """Every form of the kernel: the defaults (dense: 256-row tiles on one CTA; grouped: pairs of CTAs), the two tile
+    heights on one CTA, and pairs of CTAs (cta_group::2) for everything."""
+    rows, pair = request.param
+    fpt.call("fpt_set_tuning", b"gate_up_tile_rows", rows)
+    fpt.call("fpt_set_tuning", b"gate_up_cta_pair", pair)
     yield request.param
     fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
+    fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
 
 
 @pytest.mark.parametrize("rows,dim,hidden", [(1, 64, 128), (128, 64, 128), (300, 4096, 384), (1000, 200, 128), (777, 1024, 1408)])
@@ -129,7 +134,21 @@ def test_grouped_rows_follow_their_group(fpt, cuda, tile_rows, ends):
     assert bool((raw[last:] == 7.0).all()) and bool((fused[last:] == 7.0).all())
 
 
-def test_many_groups_like_routed_experts(fpt, cuda):
+def test_forms_agree_bit_for_bit(fpt, cuda):
+    """One CTA with either tile height and a pair of CTAs add the same products in the same order."""
+    import torch
+    x, wg, wu = make(cuda, 3000, 1024, 384, seed=21)
+    outs = []
+    for rows, pair in ((128, 0), (256, 0), (0, 1)):
+        fpt.call("fpt_set_tuning", b"gate_up_tile_rows", rows)
+        fpt.call("fpt_set_tuning", b"gate_up_cta_pair", pair)
+        outs.append(gate_up(fpt, x, wg, wu))
+    fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
+    fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+
+
+def test_many_groups_like_routed_experts(fpt, cuda, tile_rows):
     """64 groups with Zipf-like sizes (some empty), the B4 layout at a size the check finishes quickly."""
     import torch
     rows, dim, hidden, groups = 9000, 512, 128, 64
