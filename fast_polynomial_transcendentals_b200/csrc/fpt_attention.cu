@@ -47,7 +47,7 @@ struct AttnSmem {
     alignas(1024) uint8_t k[kStages][kTileBytes];
     alignas(1024) uint8_t v[kStages][kTileBytes];
     alignas(8) uint64_t q_full[kSlots];
-    uint64_t k_full[kStages], k_empty[kStages], v_full[kStages], v_empty[kStages];
+    uint64_t k_full[2 * kStages], k_empty[2 * kStages], v_full[2 * kStages], v_empty[2 * kStages];   // a pair's half tiles: twice the stages
     uint64_t s_full[kSlots], p_half[kSlots], p_full[kSlots], pv_done[kSlots];
     uint64_t ld_done[kSlots];            // column-split variant: the eight warps of a slot have their S values in registers
     float xchg[kSlots][2][kTileM];       // column-split variant: row maximum / row sum of the other column half
@@ -150,13 +150,32 @@ constexpr int kThreadsSplit = 128 + 256 * kSlots;
 constexpr float kFixedReferenceLimit = 98.0f;
 constexpr float kFixedReferenceSpan = 96.0f;
 
-template <int MODE, int EMU, bool SPLIT, int EK = kExp2FullD3>
+// PAIR: the block runs as one of a cluster of two (tcgen05 cta_group::2).  Both CTAs own 256 query rows as before (two
+// heads of one K/V group, or two neighbouring row blocks of one head), and every product is ONE instruction of 256 rows
+// issued by the first CTA: S = Q K^T reads each CTA's own Q and HALF of the key tile from each (keys 0..63 from the
+// first CTA, 64..127 from the second), O += P V reads each CTA's own P and half of V's columns from each.  A CTA therefore
+// loads and holds half of every K and V tile (map_kh: the K map with a 64-row box).  Loads of both CTAs complete on the
+// first CTA's barriers, its commits reach both CTAs' barriers, and the score-mod warps of the second CTA announce their
+// P tiles on the first CTA's barriers.  Same bits as the single-CTA kernel.  Measured 0.85-1.00x its speed at every shape
+// (two or four ring stages, either wait scope): the kernel is not bound by the shared-memory reads this form halves, and
+// a product that needs the P tiles of two CTAs waits for the slower of them.  Opt-in (tuning key "attention_cta_pair").
+template <int MODE, int EMU, bool SPLIT, int EK = kExp2FullD3, bool PAIR = false>
 __global__ void __launch_bounds__(SPLIT ? kThreadsSplit : kThreads, 1)
 attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                     const __grid_constant__ CUtensorMap map_v, const AttnParams p) {
+                     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_kh,
+                     const AttnParams p) {
     extern __shared__ uint8_t smem_raw[];
     AttnSmem& sm = *reinterpret_cast<AttnSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = PAIR ? cluster_cta_rank() : 0u;      // clusters of two along x
+    // K / V ring: a CTA of a pair holds half of every tile, so the same shared memory gives it twice the stages
+#ifndef FPT_ATTN_PAIR_STAGES
+#define FPT_ATTN_PAIR_STAGES 4
+#endif
+    constexpr int kSt = PAIR ? FPT_ATTN_PAIR_STAGES : kStages;
+    constexpr uint32_t kStageBytes = PAIR ? kTileBytes / 2 : kTileBytes;
+    auto k_stage = [&](int st) { return &sm.k[0][0] + uint32_t(st) * kStageBytes; };
+    auto v_stage = [&](int st) { return &sm.v[0][0] + uint32_t(st) * kStageBytes; };
     // Blocks are handed out x fastest.  With heads on x the blocks that run together share their length (causal) but walk
     // the K/V of every head at once; with row blocks on x they share one head's K/V, which then stays in L2.
     const int hq = p.rows_fastest ? blockIdx.y : blockIdx.x;
@@ -184,12 +203,12 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         for (int s = 0; s < kSlots; ++s) {
             mbar_init(&sm.q_full[s], 1);
             mbar_init(&sm.s_full[s], 1);
-            mbar_init(&sm.p_half[s], 4);   // one arrive per softmax warp: keys 0..63 of the tile are in place
-            mbar_init(&sm.p_full[s], 4);   // ... and keys 64..127
+            mbar_init(&sm.p_half[s], PAIR ? 8 : 4);   // one arrive per softmax warp: keys 0..63 of the tile are in place
+            mbar_init(&sm.p_full[s], PAIR ? 8 : 4);   // ... and keys 64..127 (PAIR: the warps of both CTAs)
             mbar_init(&sm.pv_done[s], 1);
             mbar_init(&sm.ld_done[s], 8);
         }
-        for (int st = 0; st < kStages; ++st) {
+        for (int st = 0; st < kSt; ++st) {
             mbar_init(&sm.k_full[st], 1);
             mbar_init(&sm.k_empty[st], 1);
             mbar_init(&sm.v_full[st], 1);
@@ -200,18 +219,30 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
         mbar_fence_init();
         tma_prefetch_descriptor(&map_q);
-        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(PAIR ? &map_kh : &map_k);
         tma_prefetch_descriptor(&map_v);
     }
     if (warp == 1) {
-        tmem_alloc(&sm.tmem_base, 512);
-        tmem_relinquish();
+        if constexpr (PAIR) {
+            tmem_alloc_pair(&sm.tmem_base, 512);
+            tmem_relinquish_pair();
+        } else {
+            tmem_alloc(&sm.tmem_base, 512);
+            tmem_relinquish();
+        }
     }
     tc_fence_before_sync();
-    __syncthreads();
+    if constexpr (PAIR) cluster_sync_all();       // both CTAs' barriers exist before anything arrives from the other CTA
+    else __syncthreads();
     tc_fence_after_sync();
     const uint32_t tmem = sm.tmem_base;
     const bool skip = sm.abort_flag != 0u;
+    // "this warp's part of P is in tensor memory" (the warp has waited for its stores): to the issuing CTA's barrier; from the
+    // second CTA of a pair without release semantics, which would wait for the K / V loads in flight into this CTA
+    auto arrive_p = [&](uint64_t* bar) {
+        if (!PAIR || rank == 0) mbar_arrive(bar);
+        else mbar_arrive_cluster_relaxed(map_to_cta(smem_u32(bar), 0));
+    };
 
     // Register budget.  A CTA can only re-distribute the registers it was launched with (threads x the per-thread count
     // the launch bound allows): what the score-mod warps gain must have been given up by warpgroup 0 first, or
@@ -230,47 +261,80 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         if (lane == 0) {
             for (int s = 0; s < kSlots; ++s) {
                 if (n_tiles[s] == 0) continue;
-                mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
-                tma_load_4d(sm.q[s], &map_q, &sm.q_full[s], 0, m0 + s * kTileM, hq, b);
-                tma_load_4d(sm.q[s] + kPanel, &map_q, &sm.q_full[s], 64, m0 + s * kTileM, hq, b);
+                if constexpr (PAIR) {
+                    const uint32_t bar = map_to_cta(smem_u32(&sm.q_full[s]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&sm.q_full[s], 2 * kTileBytes);
+                    tma_load_4d_pair(sm.q[s], &map_q, bar, 0, m0 + s * kTileM, hq, b);
+                    tma_load_4d_pair(sm.q[s] + kPanel, &map_q, bar, 64, m0 + s * kTileM, hq, b);
+                } else {
+                    mbar_arrive_expect_tx(&sm.q_full[s], kTileBytes);
+                    tma_load_4d(sm.q[s], &map_q, &sm.q_full[s], 0, m0 + s * kTileM, hq, b);
+                    tma_load_4d(sm.q[s] + kPanel, &map_q, &sm.q_full[s], 64, m0 + s * kTileM, hq, b);
+                }
             }
             bool ok = true;
             for (int j = 0; j < n_max && ok; ++j) {
-                const int st = j % kStages;
-                const uint32_t ph = uint32_t(j / kStages) & 1u;
-                if (j >= kStages) ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag, p.status, kWhereKEmpty);
+                const int st = j % kSt;
+                const uint32_t ph = uint32_t(j / kSt) & 1u;
+                if (j >= kSt) ok = mbar_wait(&sm.k_empty[st], ph ^ 1u, abort_flag, p.status, kWhereKEmpty);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
-                tma_load_4d(sm.k[st], &map_k, &sm.k_full[st], 0, j * kTileN, hk, b);
-                tma_load_4d(sm.k[st] + kPanel, &map_k, &sm.k_full[st], 64, j * kTileN, hk, b);
-                if (j >= kStages) ok = mbar_wait(&sm.v_empty[st], ph ^ 1u, abort_flag, p.status, kWhereVEmpty);
+                if constexpr (PAIR) {      // this CTA's 64 keys of the tile: two panels [64 keys x 64 columns]
+                    const uint32_t bar = map_to_cta(smem_u32(&sm.k_full[st]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+                    tma_load_4d_pair(k_stage(st), &map_kh, bar, 0, j * kTileN + 64 * int(rank), hk, b);
+                    tma_load_4d_pair(k_stage(st) + kPanel / 2, &map_kh, bar, 64, j * kTileN + 64 * int(rank), hk, b);
+                } else {
+                    mbar_arrive_expect_tx(&sm.k_full[st], kTileBytes);
+                    tma_load_4d(sm.k[st], &map_k, &sm.k_full[st], 0, j * kTileN, hk, b);
+                    tma_load_4d(sm.k[st] + kPanel, &map_k, &sm.k_full[st], 64, j * kTileN, hk, b);
+                }
+                if (j >= kSt) ok = mbar_wait(&sm.v_empty[st], ph ^ 1u, abort_flag, p.status, kWhereVEmpty);
                 if (!ok) break;
-                mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
-                tma_load_4d(sm.v[st], &map_v, &sm.v_full[st], 0, j * kTileN, hk, b);
-                tma_load_4d(sm.v[st] + kPanel, &map_v, &sm.v_full[st], 64, j * kTileN, hk, b);
+                if constexpr (PAIR) {      // this CTA's 64 columns of V for all 128 keys: one panel
+                    const uint32_t bar = map_to_cta(smem_u32(&sm.v_full[st]), 0);
+                    if (rank == 0) mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+                    tma_load_4d_pair(v_stage(st), &map_v, bar, 64 * int(rank), j * kTileN, hk, b);
+                } else {
+                    mbar_arrive_expect_tx(&sm.v_full[st], kTileBytes);
+                    tma_load_4d(sm.v[st], &map_v, &sm.v_full[st], 0, j * kTileN, hk, b);
+                    tma_load_4d(sm.v[st] + kPanel, &map_v, &sm.v_full[st], 64, j * kTileN, hk, b);
+                }
             }
         }
-      } else {
-        // ------------------------------------------------------------------ UMMA issuer
+      } else if (rank == 0) {
+        // ------------------------------------------------------------------ UMMA issuer (PAIR: for both CTAs)
         if (lane == 0) {
-            constexpr uint32_t idesc_qk = umma_idesc_bf16(kTileM, kTileN, 0, 0);
-            constexpr uint32_t idesc_pv = umma_idesc_bf16(kTileM, kHeadDim, 0, 1);
+            constexpr uint32_t idesc_qk = umma_idesc_bf16(PAIR ? 2 * kTileM : kTileM, kTileN, 0, 0);
+            constexpr uint32_t idesc_pv = umma_idesc_bf16(PAIR ? 2 * kTileM : kTileM, kHeadDim, 0, 1);
+            constexpr uint32_t k_panel = PAIR ? kPanel / 2 : kPanel;    // a CTA of a pair holds 64 keys of a tile
+            auto commit = [&](uint64_t* bar) {
+                if constexpr (PAIR) umma_commit_pair(bar, 3);
+                else umma_commit(bar);
+            };
+            // P tiles are announced by the warps of both CTAs of a pair
+            auto wait_p = [&](uint64_t* bar, uint32_t parity) {
+                if constexpr (PAIR) return mbar_wait_cluster(bar, parity, abort_flag, p.status, kWherePFull);
+                return mbar_wait(bar, parity, abort_flag, p.status, kWherePFull);
+            };
             // Every descriptor is "low word of the tile base + a compile-time constant" with one shared high word, so
             // an issue costs the thread a few integer instructions and the tensor pipe, not the thread, sets the pace.
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
-            static_assert(kSlots == 2 && kStages == 2, "the selects below assume two slots and two stages");
+            static_assert(kSlots == 2, "the selects below assume two slots");
             const uint32_t q_lo0 = umma_smem_desc_lo(smem_u32(sm.q[0]), 16), q_lo1 = umma_smem_desc_lo(smem_u32(sm.q[1]), 16);
-            const uint32_t k_lo0 = umma_smem_desc_lo(smem_u32(sm.k[0]), 16), k_lo1 = umma_smem_desc_lo(smem_u32(sm.k[1]), 16);
-            const uint32_t v_lo0 = umma_smem_desc_lo(smem_u32(sm.v[0]), kPanel), v_lo1 = umma_smem_desc_lo(smem_u32(sm.v[1]), kPanel);
+            // stage st of a ring starts st * kStageBytes behind stage 0 (the stages are contiguous)
+            const uint32_t k_lo0 = umma_smem_desc_lo(smem_u32(sm.k[0]), 16);
+            const uint32_t v_lo0 = umma_smem_desc_lo(smem_u32(sm.v[0]), kPanel);
             auto issue_qk = [&](int s, int st) {
-                const uint32_t qa = s ? q_lo1 : q_lo0, ka = st ? k_lo1 : k_lo0, d = tmem + uint32_t(s) * 128u;
+                const uint32_t qa = s ? q_lo1 : q_lo0, ka = k_lo0 + uint32_t(st) * (kStageBytes / 16u), d = tmem + uint32_t(s) * 128u;
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     constexpr uint32_t unit = 16;   // descriptor addresses count 16-byte units
                     const uint32_t off = (uint32_t(kk >> 2) * kPanel + uint32_t(kk & 3) * 32u) / unit;
-                    umma_ss_words(d, qa + off, ka + off, desc_hi, idesc_qk, kk > 0);
+                    const uint32_t off_k = (uint32_t(kk >> 2) * k_panel + uint32_t(kk & 3) * 32u) / unit;
+                    if constexpr (PAIR) umma_ss_words_pair(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
+                    else umma_ss_words(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
                 }
-                umma_commit(&sm.s_full[s]);
+                commit(&sm.s_full[s]);
             };
             // P V in two halves of four K steps: the first starts as soon as the probabilities of keys 0..63 are in
             // tensor memory, while the score-mod warps still work on keys 64..127.
@@ -278,14 +342,15 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             // column-split layout each half writes onto the first 32 columns of its OWN 64 score columns, so that neither
             // half ever touches a column the other still has to read.
             auto issue_pv_half = [&](int s, int st, int half, bool first) {
-                const uint32_t va = st ? v_lo1 : v_lo0, d = tmem + 256u + uint32_t(s) * 128u;
+                const uint32_t va = v_lo0 + uint32_t(st) * (kStageBytes / 16u), d = tmem + 256u + uint32_t(s) * 128u;
                 const uint32_t a = tmem + uint32_t(s) * 128u + uint32_t(half) * (SPLIT ? 64u : 32u);
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                     const uint32_t kk = uint32_t(half) * 4u + uint32_t(k4);
-                    umma_ts_words(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                    if constexpr (PAIR) umma_ts_words_pair(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                    else umma_ts_words(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
                 }
-                if (half == 1) umma_commit(&sm.pv_done[s]);
+                if (half == 1) commit(&sm.pv_done[s]);
             };
             bool ok = true;
             // prologue: S = Q K_0^T for both slots
@@ -297,22 +362,22 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tc_fence_after_sync();
                 issue_qk(s, 0);
             }
-            if (ok && n_max > 0) umma_commit(&sm.k_empty[0]);
+            if (ok && n_max > 0) commit(&sm.k_empty[0]);
             for (int j = 0; j < n_max && ok; ++j) {
-                const int st = j % kStages;
-                const uint32_t ph = uint32_t(j / kStages) & 1u;
-                const int st_next = (j + 1) % kStages;
-                const uint32_t ph_next = uint32_t((j + 1) / kStages) & 1u;
+                const int st = j % kSt;
+                const uint32_t ph = uint32_t(j / kSt) & 1u;
+                const int st_next = (j + 1) % kSt;
+                const uint32_t ph_next = uint32_t((j + 1) / kSt) & 1u;
                 for (int s = 0; s < kSlots && ok; ++s) {
                     if (j >= n_tiles[s]) continue;
                     ok = mbar_wait(&sm.v_full[st], ph, abort_flag, p.status, kWhereVFull);
                     FPT_TRACE(2, 31);
-                    ok = ok && mbar_wait(&sm.p_half[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    ok = ok && wait_p(&sm.p_half[s], uint32_t(j) & 1u);
                     if (!ok) break;
                     tc_fence_after_sync();
                     FPT_TRACE(2, 10 + s);            // first half of P of slot s seen
                     issue_pv_half(s, st, 0, j == 0);
-                    ok = mbar_wait(&sm.p_full[s], uint32_t(j) & 1u, abort_flag, p.status, kWherePFull);
+                    ok = wait_p(&sm.p_full[s], uint32_t(j) & 1u);
                     if (!ok) break;
                     tc_fence_after_sync();
                     issue_pv_half(s, st, 1, j == 0);
@@ -327,8 +392,8 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     }
                 }
                 if (!ok) break;
-                umma_commit(&sm.v_empty[st]);
-                if (j + 1 < n_max) umma_commit(&sm.k_empty[st_next]);
+                commit(&sm.v_empty[st]);
+                if (j + 1 < n_max) commit(&sm.k_empty[st_next]);
                 FPT_TRACE(2, 30);
             }
         }
@@ -434,7 +499,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
+            if (lane == 0) arrive_p(half ? &sm.p_full[s] : &sm.p_half[s]);
             FPT_TRACE(s, 4);                         // P handed over
         }
         if (ok && n > 0) {
@@ -511,7 +576,7 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                 tmem_st_wait();
                 tc_fence_before_sync();
                 __syncwarp();
-                if (lane == 0) mbar_arrive(half ? &sm.p_full[s] : &sm.p_half[s]);
+                if (lane == 0) arrive_p(half ? &sm.p_full[s] : &sm.p_half[s]);
             };
             if constexpr (is_sigmoid(MODE)) {
 #pragma unroll
@@ -653,8 +718,14 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
       }
     }
     tc_fence_before_sync();
-    __syncthreads();
-    if (warp == 1) tmem_dealloc(tmem, 512);
+    if constexpr (PAIR) {
+        __syncwarp();
+        cluster_sync_all();        // neither CTA leaves while the other can still reach its barriers or memory
+        if (warp == 1) tmem_dealloc_pair(tmem, 512);
+    } else {
+        __syncthreads();
+        if (warp == 1) tmem_dealloc(tmem, 512);
+    }
 }
 
 }  // namespace
@@ -697,10 +768,15 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
         const uint64_t strides[3] = {uint64_t(st[1]) * 2, uint64_t(st[2]) * 2, uint64_t(st[0]) * 2};
         return make_tensor_map_bf16_4d(map, base, dims, strides, kTileM);
     };
-    CUtensorMap map_q, map_k, map_v;
+    CUtensorMap map_q, map_k, map_v, map_kh;
     if (int rc = make_map(&map_q, q, q_strides, q_heads)) return rc;
     if (int rc = make_map(&map_k, k, k_strides, kv_heads)) return rc;
     if (int rc = make_map(&map_v, v, v_strides, kv_heads)) return rc;
+    {   // the K map with a box of 64 keys: what one CTA of a pair loads of a key tile
+        const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(seq), uint64_t(kv_heads), uint64_t(batch)};
+        const uint64_t strides[3] = {uint64_t(k_strides[1]) * 2, uint64_t(k_strides[2]) * 2, uint64_t(k_strides[0]) * 2};
+        if (int rc = make_tensor_map_bf16_4d(&map_kh, k, dims, strides, kTileN / 2)) return rc;
+    }
 
     AttnParams p{};
     p.out = static_cast<uint16_t*>(out);
@@ -726,14 +802,55 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     // causal mask heads fastest wins by 3-20 % (blocks that run together have the same length), so that is the default.
     const int raster = fpt::tuning_attention_raster();
     p.rows_fastest = raster >= 0 ? raster : 0;
+    // Pairs of CTAs (clusters of two along x) need two blocks that walk the same K / V in step: two query heads of one
+    // K / V group (heads on x, even group size: they also share their causal length), or two neighbouring row blocks of one
+    // head where no mask makes their lengths differ (rows on x, whole blocks only).
+    bool pair = false;
+    if (fpt::tuning_attention_cta_pair() == 1 && exp2_emu_freq == 0) {
+        const bool heads_pair = (q_heads / kv_heads) % 2 == 0;
+        const bool rows_pair = !causal && n_qblocks % 2 == 0 && seq % (kSlots * kTileM) == 0;
+        if (heads_pair && (raster != 1 || !rows_pair)) { pair = true; p.rows_fastest = 0; }
+        else if (rows_pair) { pair = true; p.rows_fastest = 1; }
+    }
     const dim3 grid = p.rows_fastest ? dim3{unsigned(n_qblocks), unsigned(q_heads), unsigned(batch)}
                                      : dim3{unsigned(q_heads), unsigned(n_qblocks), unsigned(batch)};
     auto launch = [&](auto kernel, int threads) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
-        kernel<<<grid, threads, smem, stream>>>(map_q, map_k, map_v, p);
+        kernel<<<grid, threads, smem, stream>>>(map_q, map_k, map_v, map_kh, p);
         return cuda_status(cudaGetLastError());
     };
+    auto launch_pair = [&](auto kernel, int threads) {
+        cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
+        cudaLaunchConfig_t config{};
+        config.gridDim = grid;
+        config.blockDim = dim3{unsigned(threads), 1, 1};
+        config.dynamicSmemBytes = smem;
+        config.stream = reinterpret_cast<cudaStream_t>(stream);
+        cudaLaunchAttribute attribute{};
+        attribute.id = cudaLaunchAttributeClusterDimension;
+        attribute.val.clusterDim.x = 2;
+        attribute.val.clusterDim.y = 1;
+        attribute.val.clusterDim.z = 1;
+        config.attrs = &attribute;
+        config.numAttrs = 1;
+        return cuda_status(cudaLaunchKernelEx(&config, kernel, map_q, map_k, map_v, map_kh, p));
+    };
+    if (pair) {
+        const bool split_pair = softcap_family && softcap * kLog2e <= kFixedReferenceLimit && fpt::tuning_attention_split() >= 1;
+        switch (mode) {
+            case FPT_ATTN_SOFTCAP_TANH:
+                return split_pair ? launch_pair(attention_fwd_kernel<0, 0, true, kExp2FullD3, true>, kThreadsSplit)
+                                  : launch_pair(attention_fwd_kernel<0, 0, false, kExp2FullD3, true>, kThreads);
+            case FPT_ATTN_SIGMOID_DIRECT: return launch_pair(attention_fwd_kernel<1, 0, false, kExp2FullD3, true>, kThreads);
+            case FPT_ATTN_SOFTMAX: return launch_pair(attention_fwd_kernel<2, 0, false, kExp2FullD3, true>, kThreads);
+            case FPT_ATTN_SOFTCAP_NATIVE:
+                return split_pair ? launch_pair(attention_fwd_kernel<3, 0, true, kExp2FullD3, true>, kThreadsSplit)
+                                  : launch_pair(attention_fwd_kernel<3, 0, false, kExp2FullD3, true>, kThreads);
+            default: return launch_pair(attention_fwd_kernel<4, 0, false, kExp2FullD3, true>, kThreads);
+        }
+    }
     // The column-split variant pays where the score-mod is instruction-heavy and needs no per-tile row reduction: the
     // soft-capped mode while cap * log2(e) stays within the range its fixed exponent reference covers (measured +15..28 %
     // since its tanh and exponential run back to back per key pair).  The sigmoid mode also qualifies but measures no

@@ -22,6 +22,7 @@ std::atomic<int> g_attention_split{1};
 std::atomic<int> g_attention_raster{-1};
 std::atomic<int> g_attention_bwd_fused{0};
 std::atomic<int> g_gate_up_tile_rows{0};
+std::atomic<int> g_attention_cta_pair{0};
 std::atomic<int> g_gate_up_cta_pair{-1};
 std::atomic<int> g_rope_heads_per_block{8};   // measured: 8 is 1.5-3 % ahead of "all heads in one block" at 32 heads
 
@@ -69,6 +70,7 @@ int tuning_attention_split() { return g_attention_split.load(); }
 int tuning_attention_raster() { return g_attention_raster.load(); }
 int tuning_attention_bwd_fused() { return g_attention_bwd_fused.load(); }
 int tuning_gate_up_tile_rows() { return g_gate_up_tile_rows.load(); }
+int tuning_attention_cta_pair() { return g_attention_cta_pair.load(); }
 int tuning_gate_up_cta_pair() { return g_gate_up_cta_pair.load(); }
 int tuning_rope_heads_per_block() { return g_rope_heads_per_block.load(); }
 
@@ -156,6 +158,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!std::strcmp(key, "attention_bwd_fused")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_bwd_fused = value; return FPT_OK; }
     if (!std::strcmp(key, "rope_heads_per_block")) { if (value < 0 || value > 65535) return FPT_ERR_BAD_SIZE; fpt::g_rope_heads_per_block = value; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_tile_rows")) { if (value != 0 && value != 128 && value != 256) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_tile_rows = value; return FPT_OK; }
+    if (!std::strcmp(key, "attention_cta_pair")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_cta_pair = value; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_cta_pair")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_cta_pair = value; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
@@ -169,6 +172,7 @@ int fpt_get_tuning(const char* key, int* value) {
     if (!std::strcmp(key, "attention_bwd_fused")) { *value = fpt::g_attention_bwd_fused; return FPT_OK; }
     if (!std::strcmp(key, "rope_heads_per_block")) { *value = fpt::g_rope_heads_per_block; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_tile_rows")) { *value = fpt::g_gate_up_tile_rows; return FPT_OK; }
+    if (!std::strcmp(key, "attention_cta_pair")) { *value = fpt::g_attention_cta_pair; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_cta_pair")) { *value = fpt::g_gate_up_cta_pair; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }

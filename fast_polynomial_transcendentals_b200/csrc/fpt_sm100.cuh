@@ -225,6 +225,12 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
     asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
 }
+// The same without release semantics.  Measured: a releasing remote arrive waits for every bulk load still in flight
+// into its CTA (a ring of loads then runs one stage deep), so arrivals that sit on a kernel's critical path and only
+// announce work the thread itself has already waited for (tcgen05.wait::st / ::ld) use this form.
+__device__ __forceinline__ void mbar_arrive_cluster_relaxed(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" :: "r"(cluster_addr) : "memory");
+}
 // try_wait that also orders against arrivals from the other CTA of the cluster
 __device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -281,6 +287,15 @@ __device__ __forceinline__ void umma_ss_words_pair(uint32_t d_tmem, uint32_t a_l
         "mov.b64 da, {%1, %3};\n\tmov.b64 db, {%2, %3};\n\t"
         "tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %4, p;\n\t}"
         :: "r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
+}
+// the same with A read from tensor memory (each CTA its own 128 lanes at `a_tmem`)
+__device__ __forceinline__ void umma_ts_words_pair(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_lo, uint32_t desc_hi,
+                                                   uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tsetp.ne.b32 p, %5, 0;\n\t"
+        "mov.b64 db, {%2, %3};\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+        :: "r"(d_tmem), "r"(a_tmem), "r"(b_lo), "r"(desc_hi), "r"(idesc), "r"(accumulate) : "memory");
 }
 // the same thread: the barrier at this offset in every CTA of `cta_mask` receives one arrival once all the products
 // issued so far have completed

@@ -385,6 +385,10 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
  * key "attention_bwd_fused": 1 lets the attention backward take its one-pass form when the workspace allows, 0 (default)
  * keeps the deterministic two-pass form;
+ * key "attention_cta_pair": 1 runs the attention forward on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one
+ * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
+ * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits, measured
+ * 0.85-1.00x the single-CTA speed;
  * key "gate_up_tile_rows": rows per tile of fpt_gate_up_swiglu, 128 or 256; 0 (default) = 256 for one group (both halves
  * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
  * grouped problems (a ragged group wastes less of a smaller tile);

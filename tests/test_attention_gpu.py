@@ -147,6 +147,45 @@ def test_attention_matches_fp32_oracle(fpt, cuda, oracle, case):
     tol.check(case)
 
 
+PAIR_CASES = [
+    # two query heads of one K / V group per pair of CTAs (causal and not), every mode and both soft-cap layouts
+    (1, 1024, 4, 2, 2, True, 0.0, 12), (2, 640, 4, 1, 2, False, 0.0, 12), (1, 1024, 4, 2, 0, True, 30.0, 12),
+    (1, 1024, 4, 2, 0, True, 100.0, 12), (1, 768, 8, 2, 1, True, 0.0, 12), (1, 1024, 4, 2, 3, True, 30.0, 12),
+    (1, 512, 2, 1, 4, False, 0.0, 9), (1, 1000, 4, 1, 2, True, 0.0, 12), (1, 333, 2, 1, 0, False, 50.0, 12),
+    # two neighbouring row blocks of one head (no K / V sharing between heads, no mask)
+    (2, 1024, 2, 2, 1, False, 0.0, 10), (1, 2048, 3, 3, 2, False, 0.0, 12), (1, 1024, 1, 1, 0, False, 50.0, 12),
+    # blocks that cannot pair (one head per K / V head under a causal mask; an odd number of row blocks): the call falls
+    # back to single CTAs
+    (1, 1024, 2, 2, 2, True, 0.0, 12), (1, 768, 3, 3, 1, False, 0.0, 12),
+]
+
+
+@pytest.mark.parametrize("case", PAIR_CASES)
+def test_pairs_of_ctas_give_the_same_bits(fpt, cuda, case):
+    """`attention_cta_pair` = 1 runs the forward on clusters of two CTAs (one 256-row product for two SMs, K and V tiles
+    split between them): same products, same order, so output and log-sum-exp are the single-CTA kernel's bit for bit."""
+    import torch
+    B, S, Hq, Hk, mode, causal, softcap, log2_n = case
+    D = 128
+    g = torch.Generator(device=cuda)
+    g.manual_seed(99)
+    q = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
+    k = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    v = torch.randn(B, S, Hk, D, device=cuda, generator=g).to(torch.bfloat16)
+    scale = 1.0 / math.sqrt(D)
+    base, lse0, status = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    assert status == 0, hex(status)
+    fpt.call("fpt_set_tuning", b"attention_cta_pair", 1)
+    try:
+        got, lse1, status = run_attention(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    finally:
+        fpt.call("fpt_set_tuning", b"attention_cta_pair", 0)
+    assert status == 0, hex(status)
+    assert torch.equal(base.view(torch.int16), got.view(torch.int16))
+    if mode not in UNNORMALISED:
+        assert torch.equal(lse0.view(torch.int32), lse1.view(torch.int32))
+
+
 def test_attention_accepts_head_major_layout(fpt, cuda):
     """(B,H,S,D) storage (what the fused RoPE writes) addressed through strides gives the same result."""
     import torch
