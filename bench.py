@@ -687,6 +687,60 @@ def bench_sharded(torch, dist, lib, _lib, device, rank, world, hbm_peak, tensor_
         "timing": "median of 7 launches, 256 MiB written between launches (a shard can be smaller than the L2)",
         "checksum_total": sum(per_sum), "last_shard_recomputed_on_rank0_equal": recheck}
 
+    # ---- (2b) the same experts with their input projections: out = SwiGLU(x W_gate^T, x W_up^T) in one kernel per GPU
+    dim = 2048
+    offsets_all = np.concatenate([[0], np.cumsum(counts)])
+
+    def b4_projection_shard(r):
+        sh = sharding.expert_group(counts, r, world)
+        n_local = sh.last_row - sh.first_row
+        e_local = sh.last_expert - sh.first_expert
+        x = torch.empty(max(n_local, 1), dim, dtype=torch.bfloat16, device=device)
+        wg = torch.empty(e_local, hidden, dim, dtype=torch.bfloat16, device=device)
+        wu = torch.empty_like(wg)
+        for e in range(sh.first_expert, sh.last_expert):      # values are functions of the GLOBAL row / expert index
+            r0, r1 = int(offsets_all[e]), int(offsets_all[e + 1])
+            if r1 > r0:
+                idx = torch.arange(r0 * dim, r1 * dim, device=device, dtype=torch.int64)
+                x[r0 - sh.first_row:r1 - sh.first_row] = hashed_normal(torch, idx, 21, 1.0).view(r1 - r0, dim).to(torch.bfloat16)
+            idx = torch.arange(e * hidden * dim, (e + 1) * hidden * dim, device=device, dtype=torch.int64)
+            wg[e - sh.first_expert] = hashed_normal(torch, idx, 22, dim ** -0.5).view(hidden, dim).to(torch.bfloat16)
+            wu[e - sh.first_expert] = hashed_normal(torch, idx, 23, dim ** -0.5).view(hidden, dim).to(torch.bfloat16)
+        ends = torch.tensor(offsets_all[sh.first_expert + 1:sh.last_expert + 1] - sh.first_row, dtype=torch.int32, device=device)
+        o = torch.zeros(max(n_local, 1), hidden, dtype=torch.bfloat16, device=device)
+        gstatus = torch.zeros(1, dtype=torch.int32, device=device)
+
+        def run():
+            if n_local:
+                _lib.check("fpt_gate_up_swiglu", lib.fpt_gate_up_swiglu(
+                    o.data_ptr(), x.data_ptr(), wg.data_ptr(), wu.data_ptr(), n_local, dim, hidden, dim, dim, hidden * dim, hidden,
+                    ends.data_ptr(), e_local, 3, 0, 0, gstatus.data_ptr(), stream))
+        return n_local, o, run, gstatus, (x, wg, wu, ends)
+
+    nloc, o, run, gstatus, keep = b4_projection_shard(rank)
+    gu_ms = time_launch(torch, run, 7, flush)
+    if int(gstatus.item()) != 0:
+        raise RuntimeError(f"fpt_gate_up_swiglu reported status {int(gstatus.item()) & 0xffffffff:#x}")
+    gu_sum = bits_checksum(torch, o[:nloc]) if nloc else 0
+    del o, run, keep
+    torch.cuda.empty_cache()
+    per_ms = [v[0] for v in gather_floats(torch, dist, world, device, [gu_ms])]
+    per_sum = [v[0] for v in gather_ints(torch, dist, world, device, [gu_sum])]
+    recheck = None
+    if world > 1 and rank == 0:
+        n2, o2, run2, _, keep2 = b4_projection_shard(world - 1)
+        run2()
+        recheck = (bits_checksum(torch, o2[:n2]) if n2 else 0) == per_sum[world - 1]
+        del o2, run2, keep2
+        torch.cuda.empty_cache()
+    flops = 2.0 * rows_total * dim * 2 * hidden
+    out["b4_routed_experts_with_projections_131072x2048_to_1408"] = {
+        "rows_per_gpu": per_rows, "ms_per_gpu": per_ms, "makespan_ms": max(per_ms),
+        "tflops_aggregate": flops / (max(per_ms) * 1e-3) / 1e12,
+        "tflops_busiest_gpu": 2.0 * max(per_rows) * dim * 2 * hidden / (max(per_ms) * 1e-3) / 1e12,
+        "kernel": "fpt_gate_up_swiglu, one launch per GPU over its expert group (grouped, pairs of CTAs)",
+        "checksum_total": sum(per_sum), "last_shard_recomputed_on_rank0_equal": recheck}
+
     # ---- (3) attention, (batch, kv-head group) blocks
     D = 128
     arr = lambda t: (ctypes.c_int64 * 3)(t.stride(0), t.stride(1), t.stride(2))
