@@ -7,8 +7,9 @@ by the matrix product and read back by the activation kernel; here each product 
 goes through the same packed polynomial program (`fpt_swish_mul`) before anything is stored, so the result equals the
 two-step path applied to this kernel's own products bit for bit and the intermediate never exists.
 
-Forward only: a backward pass needs the products themselves (`raw=True` returns them as `[rows, 2 hidden]`), so callers
-that train keep the two-step path (see `sfu_repro.adapters`).
+`gate_up_swiglu` is the plain forward; a backward pass needs the products themselves (`raw=True` returns them as
+`[rows, 2 hidden]`).  `gate_up_swiglu_recompute` is the differentiable form: it keeps only x and the weights and recomputes
+the products in the backward pass (see `sfu_repro.adapters` for where each is used).
 """
 from __future__ import annotations
 
@@ -77,4 +78,55 @@ def gate_up_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     return out.reshape(*x.shape[:-1], width)
 
 
-__all__ = ["gate_up_swiglu"]
+# ---- dispatcher operators (usable under torch.compile; differentiable by recomputation) -------------------------------
+#   fpt_gate_up::swiglu(x, w_gate, w_up, degree, coeff_source_id)   the fused forward
+#   fpt_gate_up::products(x, w_gate, w_up)                          [gate | up], the kernel's raw epilogue
+# The backward of `swiglu` recomputes the two products with the same kernel (one more projection per layer and step instead
+# of a saved [rows, 2 hidden] activation), applies the packed SwiGLU backward kernel to them and leaves the two matrix
+# products of the projection's own backward to the library.
+_library = torch.library.Library("fpt_gate_up", "DEF")
+_library.define("swiglu(Tensor x, Tensor w_gate, Tensor w_up, int degree, int coeff_source_id) -> Tensor")
+_library.define("products(Tensor x, Tensor w_gate, Tensor w_up) -> Tensor")
+_SOURCES = ("current", "sollya")
+_library.impl("swiglu", lambda x, wg, wu, degree, source: gate_up_swiglu(x, wg, wu, degree=degree, coeff_source=_SOURCES[source]), "CUDA")
+_library.impl("products", lambda x, wg, wu: gate_up_swiglu(x, wg, wu, raw=True), "CUDA")
+torch.library.register_fake("fpt_gate_up::swiglu", lambda x, wg, wu, degree, source: x.new_empty((*x.shape[:-1], wg.shape[-2])),
+                            lib=_library)
+torch.library.register_fake("fpt_gate_up::products", lambda x, wg, wu: x.new_empty((*x.shape[:-1], 2 * wg.shape[-2])),
+                            lib=_library)
+
+
+def _setup_context(ctx, inputs, output):
+    x, w_gate, w_up, ctx.degree, ctx.source = inputs
+    ctx.save_for_backward(x, w_gate, w_up)
+
+
+def _backward(ctx, grad_out):
+    from . import spline_ops
+    x, w_gate, w_up = ctx.saved_tensors
+    hidden, dim = w_gate.shape
+    packed = torch.ops.fpt_gate_up.products(x, w_gate, w_up).reshape(-1, 2 * hidden)
+    grad_packed = spline_ops.swish_mul_packed_bwd_variant(grad_out.reshape(-1, hidden).contiguous(), packed, ctx.degree, ctx.source)
+    grad_gate, grad_up = grad_packed[:, :hidden], grad_packed[:, hidden:]
+    x2 = x.reshape(-1, dim)
+    grad_x = grad_w_gate = grad_w_up = None
+    if ctx.needs_input_grad[0]:
+        grad_x = (grad_gate @ w_gate + grad_up @ w_up).reshape(x.shape)
+    if ctx.needs_input_grad[1]:
+        grad_w_gate = grad_gate.t() @ x2
+    if ctx.needs_input_grad[2]:
+        grad_w_up = grad_up.t() @ x2
+    return grad_x, grad_w_gate, grad_w_up, None, None
+
+
+torch.library.register_autograd("fpt_gate_up::swiglu", _backward, setup_context=_setup_context, lib=_library)
+
+
+def gate_up_swiglu_recompute(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *, degree: int = 3,
+                             coeff_source: str = "current") -> torch.Tensor:
+    """The dense fused forward as a differentiable dispatcher operator: nothing of size [rows, 2 hidden] is kept for the
+    backward pass, which recomputes the two products instead."""
+    return torch.ops.fpt_gate_up.swiglu(x, w_gate, w_up, int(degree), _SOURCES.index(coeff_source))
+
+
+__all__ = ["gate_up_swiglu", "gate_up_swiglu_recompute"]

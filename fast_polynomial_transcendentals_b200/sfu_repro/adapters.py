@@ -16,7 +16,7 @@ from typing import Any, Callable
 import torch
 from torch import nn
 
-from ..gate_up import gate_up_swiglu
+from ..gate_up import gate_up_swiglu, gate_up_swiglu_recompute
 from .activations import (resolve_mlp_activation_impl, resolve_mlp_activation_mul_impl,
                           resolve_mlp_activation_packed_impl)
 
@@ -113,10 +113,12 @@ class FusedGateUpFeedForward(nn.Module):
         self.sfu_fused_projection = fused_projection
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        if self.sfu_fused_projection is not None and _fusable(x, self.w_in.weight, self.w_out.weight.shape[-1]):
+        fused = self.sfu_fused_projection
+        if fused is not None and _fusable(x, self.w_in.weight, self.w_out.weight.shape[-1], fused.get("recompute", False)):
             hidden = self.w_out.weight.shape[-1]
             weight = self.w_in.weight
-            return self.w_out(gate_up_swiglu(x, weight[:hidden], weight[hidden:], **self.sfu_fused_projection))
+            op = gate_up_swiglu_recompute if fused.get("recompute", False) else gate_up_swiglu
+            return self.w_out(op(x, weight[:hidden], weight[hidden:], degree=fused["degree"], coeff_source=fused["coeff_source"]))
         return self.w_out(self.sfu_activation_packed(self.w_in(x)))
 
     def init_weights(self, init_std: float) -> None:
@@ -127,10 +129,10 @@ class FusedGateUpFeedForward(nn.Module):
         nn.init.trunc_normal_(self.w_out.weight, mean=0.0, std=init_std)
 
 
-def _fusable(x: torch.Tensor, weight: torch.Tensor, hidden: int) -> bool:
+def _fusable(x: torch.Tensor, weight: torch.Tensor, hidden: int, recompute: bool = False) -> bool:
     """The one-kernel projection + SwiGLU serves bf16 CUDA inputs when no gradient is recorded (a backward pass needs the
-    two products, which that kernel never stores)."""
-    if torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
+    two products, which that kernel never stores) or when the caller accepts their recomputation in the backward pass."""
+    if not recompute and torch.is_grad_enabled() and (x.requires_grad or weight.requires_grad):
         return False
     return (x.is_cuda and x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and hidden % 128 == 0
             and weight.shape[-1] % 8 == 0)
@@ -139,10 +141,12 @@ def _fusable(x: torch.Tensor, weight: torch.Tensor, hidden: int) -> bool:
 @torch.no_grad()
 def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", degree: int = 3,
                              coeff_source: str = "current", backward_impl: str = "matched",
-                             skipped: list[tuple[str, str]] | None = None, fuse_projection: bool = False) -> int:
+                             skipped: list[tuple[str, str]] | None = None, fuse_projection: bool | str = False) -> int:
     """Replace every bias-free SiLU-gated MLP by `FusedGateUpFeedForward` with w_in = cat(gate, up) (rows); gated MLPs
     with another activation are left alone and reported through `skipped`.  `fuse_projection=True` also lets forward
-    passes without gradients run the projection and the activation as one kernel (`gate_up.gate_up_swiglu`)."""
+    passes without gradients run the projection and the activation as one kernel (`gate_up.gate_up_swiglu`);
+    `fuse_projection="recompute"` uses that kernel in training too: the `[rows, 2 hidden]` products are not kept but
+    recomputed in the backward pass (one more projection per layer and step for 2 x rows x hidden x 2 bytes less memory)."""
     implementation = "native_silu" if variant == "native" else "spline_silu_compile"
     _, activation_packed = resolve_mlp_activation_packed_impl(implementation, degree=degree, coeff_source=coeff_source,
                                                               backward_impl=backward_impl)
@@ -169,7 +173,8 @@ def fuse_gate_up_projections(model: nn.Module, *, variant: str = "polynomial", d
                 w_out.weight.copy_(down.weight)
                 if down.bias is not None:
                     w_out.bias.copy_(down.bias)
-            fused = {"degree": 0 if variant == "native" else degree, "coeff_source": coeff_source} if fuse_projection else None
+            fused = ({"degree": 0 if variant == "native" else degree, "coeff_source": coeff_source,
+                      "recompute": fuse_projection == "recompute"} if fuse_projection else None)
             setattr(parent, child_name, FusedGateUpFeedForward(w_in, w_out, activation_packed, fused))
             replaced += 1
     return replaced
@@ -187,7 +192,8 @@ def run_grouped_experts(w1, w2, w3, x, num_tokens_per_expert, activation_mul, fu
     xb = x.bfloat16()
     if (fused_projection is not None and w1.dtype == torch.bfloat16 and w3.dtype == torch.bfloat16 and w1.shape[0] <= 256
             and w1.stride() == w3.stride() and _fusable(xb, w1, w1.shape[-2])):
-        hidden = gate_up_swiglu(xb, w1, w3, group_ends=offsets, **fused_projection)
+        hidden = gate_up_swiglu(xb, w1, w3, group_ends=offsets, degree=fused_projection["degree"],
+                                coeff_source=fused_projection["coeff_source"])
     else:
         gate = torch._grouped_mm(xb, w1.bfloat16().transpose(-2, -1), offs=offsets)
         up = torch._grouped_mm(xb, w3.bfloat16().transpose(-2, -1), offs=offsets)

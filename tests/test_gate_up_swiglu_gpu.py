@@ -201,6 +201,23 @@ def test_python_wrapper_and_adapters(cuda):
     mlp.sfu_fused_projection = {"degree": 3, "coeff_source": "current"}
     y = mlp(x.clone().requires_grad_(True))
     y.sum().backward()
+    # "recompute": the fused kernel in training too; its backward recomputes the products.  Gradients against the two-step path.
+    def grads(module):
+        module.zero_grad(set_to_none=True)
+        xin = x.clone().requires_grad_(True)
+        (module(xin).float() * probe).sum().backward()
+        return xin.grad.float(), module.w_in.weight.grad.float().clone()
+    probe = torch.randn(3, 50, dim, device=cuda)
+    mlp.sfu_fused_projection = None
+    want_x, want_w = grads(mlp)
+    mlp.sfu_fused_projection = {"degree": 3, "coeff_source": "current", "recompute": True}
+    got_x, got_w = grads(mlp)
+    assert float((got_x - want_x).abs().max()) < 2e-2 * float(want_x.abs().max())
+    assert float((got_w - want_w).abs().max()) < 2e-2 * float(want_w.abs().max())
+    compiled = torch.compile(lambda t: torch.ops.fpt_gate_up.swiglu(t, mlp.w_in.weight[:hidden], mlp.w_in.weight[hidden:], 3, 0),
+                             fullgraph=True)
+    with torch.no_grad():
+        assert torch.equal(compiled(x), gate_up_swiglu(x, mlp.w_in.weight[:hidden], mlp.w_in.weight[hidden:]))
     # wrapper checks come before any launch
     w = mlp.w_in.weight
     with pytest.raises(RuntimeError):
