@@ -847,6 +847,42 @@ def bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep):
     return out
 
 
+def gate_up_forms(torch, lib, _lib, time_sweep, call, flops):
+    """The three forms of the projection kernel on one problem: one CTA with 128- or 256-row tiles, pairs of CTAs.  Each
+    is timed inside one back-to-back loop over the three (clocks as in a training step) and as isolated launches 50 ms
+    apart (clocks at their maximum): TFLOP/s for both."""
+    forms = (("one_cta_128_rows", 128, 0), ("one_cta_256_rows", 256, 0), ("cta_pair", 0, 1))
+
+    def with_form(rows, pair):
+        def run():
+            _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_tile_rows", rows))
+            _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", pair))
+            call()
+        return run
+    try:
+        _, together = time_sweep([(name, 0, with_form(rows, pair)) for name, rows, pair in forms], 15, 2)
+        alone = {}
+        for name, rows, pair in forms:
+            run = with_form(rows, pair)
+            run()
+            torch.cuda.synchronize()
+            times = []
+            for _ in range(5):
+                time.sleep(0.05)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                run()
+                b.record()
+                torch.cuda.synchronize()
+                times.append(a.elapsed_time(b))
+            alone[name] = sorted(times)[len(times) // 2]
+    finally:
+        _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_tile_rows", 0))
+        _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", -1))
+    return {name: {"back_to_back_ms": together[name], "back_to_back_tflops": flops / (together[name] * 1e-3) / 1e12,
+                   "isolated_ms": alone[name], "isolated_tflops": flops / (alone[name] * 1e-3) / 1e12} for name, _, _ in forms}
+
+
 def bench_gate_up(torch, lib, _lib, device, S, time_sweep):
     """The projection that feeds the SwiGLU with the activation in its epilogue (`fpt_gate_up_swiglu`) next to the two-step
     path it replaces, at the B1 and B4 sizes: library matrix product(s) writing [gate | up], then this library's SwiGLU
@@ -885,6 +921,8 @@ def bench_gate_up(torch, lib, _lib, device, S, time_sweep):
         "library_matmul_ms": t["matmul"], "library_matmul_tflops": flops / (t["matmul"] * 1e-3) / 1e12,
         "packed_swiglu_ms": t["packed_swiglu"], "two_step_ms": two_step, "fused_speedup_vs_two_step": two_step / t["fused"],
         "intermediate_bytes_not_written": rows * 2 * hidden * 2}
+    out["B1_dense_16384x4096_to_14336"]["forms"] = gate_up_forms(
+        torch, lib, _lib, time_sweep, fused_call(o, x, w[:hidden], w[hidden:], rows, dim, hidden, 0, None, 1), flops)
     del x, w, o, packed
     torch.cuda.empty_cache()
 
@@ -920,6 +958,8 @@ def bench_gate_up(torch, lib, _lib, device, S, time_sweep):
         two_step = t["grouped_mm_x2"] + t["flat_swiglu"]
         entry |= {"library_grouped_mm_x2_ms": t["grouped_mm_x2"], "flat_swiglu_ms": t["flat_swiglu"], "two_step_ms": two_step,
                   "fused_speedup_vs_two_step": two_step / t["fused"]}
+    entry["forms"] = gate_up_forms(torch, lib, _lib, time_sweep,
+                                   fused_call(o, x, wg, wu, rows, dim, hidden, hidden * dim, ends, groups), flops)
     out["B4_routed_131072x2048_to_1408_x64_experts"] = entry
     if int(status.item()) != 0:
         raise RuntimeError(f"fpt_gate_up_swiglu reported status {int(status.item()) & 0xffffffff:#x}")
