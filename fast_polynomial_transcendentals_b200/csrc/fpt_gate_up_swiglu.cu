@@ -16,8 +16,9 @@
 // of a tile runs under the products of the next one; 4-stage ring.
 // HALVES = 2 (dense problems): both accumulators belong to one tile of 256 rows whose two halves share every weight
 // tile, which takes a third off the bytes that have to arrive per product (64 instead of 96 KiB per 2 x 128 x 256 x 64)
-// -- the kernel is bound by that arrival rate, not by the tensor pipe -- at the price of an epilogue that overlaps
-// only with the loads of the next tile; 3-stage ring of 64 KiB.
+// -- in a loop long enough to meet the power cap the form that moves fewer bytes per product is the faster one -- at
+// the price of an epilogue that overlaps only with the loads of the next tile; 3-stage ring of 64 KiB.
+// A third form runs the 256-row tile on a PAIR of CTAs (gate_up_swiglu_pair_kernel below).
 // The result therefore equals fpt_swish_mul_packed applied to this kernel's own raw [gate | up] output bit for bit
 // (epilogue = FPT_GATE_UP_RAW writes that output).
 // Tile order: bands of 4096 rows; inside a band the hidden tile is the slow index, so that the CTAs running together
@@ -80,7 +81,6 @@ struct GateUpParams {
     int64_t out_ld;
     int rows, hidden, groups;
     int hidden_tiles, k_blocks;
-    int raw;
     uint32_t* status;
 };
 
@@ -563,7 +563,6 @@ extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, 
     p.groups = int(groups);
     p.hidden_tiles = int(hidden / kHiddenPerTile);
     p.k_blocks = int((dim + kBlockK - 1) / kBlockK);
-    p.raw = epilogue == FPT_GATE_UP_RAW;
     p.status = static_cast<uint32_t*>(status);
 
     static_assert(sizeof(GateUpSmem<1>) + 1024 <= 227 * 1024 && sizeof(GateUpSmem<2>) + 1024 <= 227 * 1024, "shared memory budget");
