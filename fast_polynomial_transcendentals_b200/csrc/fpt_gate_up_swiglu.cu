@@ -19,7 +19,7 @@
 // -- in a loop long enough to meet the power cap the form that moves fewer bytes per product is the faster one -- at
 // the price of an epilogue that overlaps only with the loads of the next tile; 3-stage ring of 64 KiB.
 // A third form runs the 256-row tile on a PAIR of CTAs (gate_up_swiglu_pair_kernel below).
-// The result therefore equals fpt_swish_mul_packed applied to this kernel's own raw [gate | up] output bit for bit
+// In every form the result equals fpt_swish_mul_packed applied to this kernel's own raw [gate | up] output bit for bit
 // (epilogue = FPT_GATE_UP_RAW writes that output).
 // Tile order: bands of 4096 rows; inside a band the hidden tile is the slow index, so that the CTAs running together
 // share a few weight panels and the band's rows stay in L2 (measured at 16384 x 4096 -> 14336 under the power cap: bands
