@@ -112,11 +112,16 @@ class SFUReproConverter:
             initialised = _reset_inserted_norms(model)
             if initialised != patched_attention:
                 raise RuntimeError(f"FA4 patch count and initialization-hook count disagree: {patched_attention} != {initialised}")
+        # not in the reference: `job_config.sfu.fuse_projection` (False / True / "recompute") also puts the SwiGLU into the
+        # epilogue of the input projection(s) where the pass allows it (see adapters.fuse_gate_up_projections)
+        fuse_projection = getattr(self.job_config.sfu, "fuse_projection", False)
         if self.case == "b1":
             patched_activation = adapters.fuse_gate_up_projections(model, variant=self.variant, degree=3,
-                                                                   coeff_source="current", backward_impl="matched")
+                                                                   coeff_source="current", backward_impl="matched",
+                                                                   fuse_projection=fuse_projection)
         elif self.case == "b4":
-            patched_activation = adapters.patch_grouped_experts(model, variant=self.variant, degree=3, coeff_source="current")
+            patched_activation = adapters.patch_grouped_experts(model, variant=self.variant, degree=3, coeff_source="current",
+                                                                fuse_projection=bool(fuse_projection))
         expected = 29 if self.case == "b4" else int(getattr(model, "n_layers", 0))
         observed = patched_activation if self.case in {"b1", "b4"} else patched_attention
         if self.strict and observed != expected:
