@@ -660,43 +660,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                         tmem_st_wait();
                     }
                 }
-#ifdef FPT_ATTN_STAGED_EXP
-                // Exponentials in chunks of eight key pairs: all arguments, then all exponentials, then sums and
-                // conversions, with four independent partial sums, so that no instruction waits for the one before it.
-                float part[4][2] = {};
-                const float neg_max = -row_max;
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    uint32_t pw[32];
-#pragma unroll
-                    for (int c = 0; c < 4; ++c) {
-                        float a[16], e[16];
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const int i = half * 32 + c * 8 + u;
-                            fma_f32x2(__uint_as_float(sr[2 * i]), __uint_as_float(sr[2 * i + 1]), mul, neg_max, a[2 * u], a[2 * u + 1]);
-                        }
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            const int i = half * 32 + c * 8 + u;
-                            if (EMU > 0 && (i % (EMU > 0 ? EMU / 2 : 1)) < 2) {
-                                exp2_full_x2<EK>(a[2 * u], a[2 * u + 1], e[2 * u], e[2 * u + 1]);
-                            } else {
-                                e[2 * u] = ex2(a[2 * u]);
-                                e[2 * u + 1] = ex2(a[2 * u + 1]);
-                            }
-                        }
-#pragma unroll
-                        for (int u = 0; u < 8; ++u) {
-                            add_f32x2(part[u & 3][0], part[u & 3][1], e[2 * u], e[2 * u + 1]);
-                            pw[c * 8 + u] = Sfu<kBf16>::pack(e[2 * u], e[2 * u + 1]);
-                        }
-                    }
-                    if (half == 1) FPT_TRACE(s, 3);  // probabilities computed
-                    hand_over(half, pw);
-                }
-                row_sum += ((part[0][0] + part[0][1]) + (part[1][0] + part[1][1])) + ((part[2][0] + part[2][1]) + (part[3][0] + part[3][1]));
-#else
                 float sum_lo = 0.0f, sum_hi = 0.0f;
                 const float neg_max = -row_max;
 #pragma unroll
@@ -721,7 +684,6 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     hand_over(half, pw);
                 }
                 row_sum += sum_lo + sum_hi;
-#endif
             }
             FPT_TRACE(s, 4);                         // P handed over
         }
