@@ -1344,9 +1344,11 @@ def run_profile_case(args):
             lse.data_ptr(), workspace.data_ptr(), need, B, S, Hq, Hk, D, arr(q), arr(k), arr(v), arr(o), arr(dout), mode, 0,
             1.0 / math.sqrt(D), 50.0, 12, 0, status.data_ptr(), stream))
     elif case in ("gate_up_dense", "gate_up_grouped", "gate_up_dense_pair"):
-        if case.endswith("_pair"):                      # 256-row tiles on pairs of CTAs
+        if case.endswith("_pair"):                      # pairs of CTAs (the default form), asked for by name
             _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", 1))
             case = "gate_up_dense"
+        elif case == "gate_up_dense":                   # one CTA per tile of 256 rows
+            _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", 0))
         # --profile-n is the number of rows; dim 4096 -> hidden 3584 (dense) or 16 groups of dim 2048 -> hidden 1408
         rows = n
         dim, hidden, groups = (4096, 3584, 1) if case == "gate_up_dense" else (2048, 1408, 16)

@@ -533,11 +533,12 @@ extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, 
     // 256-row tiles halve the weight bytes per row where the rows are plentiful and regular; ragged groups lose less of
     // a 128-row tile
     const int tile_rows_key = fpt::tuning_gate_up_tile_rows();
-    // Measured (profiles): dense problems run alike on one CTA with 256-row tiles and on a pair of CTAs (the single
-    // CTA 0-4 % ahead once the power cap binds); grouped problems run 4 % faster on pairs in isolated launches and alike
-    // under the cap.  An explicit tile height asks for the single-CTA forms.
+    // Measured (bench.py, extras.gate_up_swiglu_bf16.*.forms, three runs): in a loop long enough to meet the power cap pairs
+    // of CTAs are 3 % (dense) to 7 % (grouped) ahead of the best single-CTA form; in isolated launches dense problems run
+    // alike (1582 against 1590 TFLOP/s) and grouped ones 4 % faster on pairs.  An explicit tile height asks for the
+    // single-CTA forms.
     const int pair_key = fpt::tuning_gate_up_cta_pair();
-    const bool pair = pair_key == 1 || (pair_key < 0 && group_ends != nullptr && tile_rows_key == 0);
+    const bool pair = pair_key == 1 || (pair_key < 0 && tile_rows_key == 0);
     const int halves = pair ? 2 : tile_rows_key ? tile_rows_key / kRowsPerHalf : (group_ends ? 1 : 2);
     const int tile_rows = halves * kRowsPerHalf;
 

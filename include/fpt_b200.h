@@ -389,12 +389,12 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
  * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits, measured
  * 0.85-1.00x the single-CTA speed;
- * key "gate_up_tile_rows": rows per tile of fpt_gate_up_swiglu, 128 or 256; 0 (default) = 256 for one group (both halves
- * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
- * grouped problems (a ragged group wastes less of a smaller tile);
  * key "gate_up_cta_pair": 1 runs fpt_gate_up_swiglu on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one product of
- * 256 rows whose weight tile is split over the two SMs), 0 never, -1 (default) for grouped problems unless
- * "gate_up_tile_rows" names a height. */
+ * 256 rows whose weight tile is split over the two SMs), 0 on single CTAs, -1 (default) on pairs unless
+ * "gate_up_tile_rows" names a height;
+ * key "gate_up_tile_rows": rows per tile of the single-CTA forms, 128 or 256; 0 (default) = 256 for one group (both halves
+ * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
+ * grouped problems (a ragged group wastes less of a smaller tile). */
 int fpt_set_tuning(const char* key, int value);
 int fpt_get_tuning(const char* key, int* value);
 

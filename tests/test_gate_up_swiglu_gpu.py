@@ -64,10 +64,10 @@ def products_fp32(x, wg, wu, ends=None):
     return want
 
 
-@pytest.fixture(params=[(0, -1), (128, -1), (256, -1), (0, 1)], ids=["auto", "tile_128", "tile_256", "cta_pair"])
+@pytest.fixture(params=[(0, -1), (128, -1), (256, -1), (0, 1), (0, 0)], ids=["auto", "tile_128", "tile_256", "cta_pair", "one_cta"])
 def tile_rows(request, fpt):
-    """Every form of the kernel: the defaults (dense: 256-row tiles on one CTA; grouped: pairs of CTAs), the two tile
-    heights on one CTA, and pairs of CTAs (cta_group::2) for everything."""
+    """Every form of the kernel: the default (pairs of CTAs), the two tile heights on one CTA, pairs asked for by name, and
+    single CTAs with the height left to the library (256 rows dense, 128 grouped)."""
     rows, pair = request.param
     fpt.call("fpt_set_tuning", b"gate_up_tile_rows", rows)
     fpt.call("fpt_set_tuning", b"gate_up_cta_pair", pair)
