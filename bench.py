@@ -958,6 +958,33 @@ def bench_gate_up(torch, lib, _lib, device, S, time_sweep):
         two_step = t["grouped_mm_x2"] + t["flat_swiglu"]
         entry |= {"library_grouped_mm_x2_ms": t["grouped_mm_x2"], "flat_swiglu_ms": t["flat_swiglu"], "two_step_ms": two_step,
                   "fused_speedup_vs_two_step": two_step / t["fused"]}
+    # the whole expert feed-forward: fused input projections + SwiGLU, then the projection back as the same kernel's raw
+    # epilogue (a plain grouped product), against three library grouped products with the activation kernel between
+    w2 = (torch.randn(groups, dim, hidden, device=device, generator=g) * hidden ** -0.5).to(torch.bfloat16)
+    y = torch.empty(rows, dim, dtype=torch.bfloat16, device=device)
+    half = dim // 2
+
+    def ours_mlp():
+        fused_call(o, x, wg, wu, rows, dim, hidden, hidden * dim, ends, groups)()
+        _lib.check("fpt_gate_up_swiglu", lib.fpt_gate_up_swiglu(
+            y.data_ptr(), o.data_ptr(), w2.data_ptr(), w2[:, half:].data_ptr(), rows, hidden, half, hidden, hidden, dim * hidden, dim,
+            vp(ends.data_ptr()), groups, 3, 0, 1, status.data_ptr(), S()))
+    ks = [("ours", 0, ours_mlp)]
+    if hasattr(torch, "_grouped_mm"):
+        def library_mlp():
+            gt = torch._grouped_mm(x, wg.transpose(-2, -1), offs=ends)
+            ut = torch._grouped_mm(x, wu.transpose(-2, -1), offs=ends)
+            _lib.check("fpt_swish_mul", lib.fpt_swish_mul(o.data_ptr(), gt.data_ptr(), ut.data_ptr(), rows * hidden, 3, 1, 0, S()))
+            return torch._grouped_mm(o, w2.transpose(-2, -1), offs=ends)
+        ks.append(("library", 0, library_mlp))
+    _, tm = time_sweep(ks, 15, 3)
+    mlp_flops = 2.0 * rows * dim * 3 * hidden
+    entry["expert_feed_forward"] = {"ours_ms": tm["ours"], "ours_tflops": mlp_flops / (tm["ours"] * 1e-3) / 1e12,
+                                    "what": "two launches of fpt_gate_up_swiglu: projections + SwiGLU, then the projection back (raw epilogue)"}
+    if "library" in tm:
+        entry["expert_feed_forward"] |= {"library_ms": tm["library"], "speedup_vs_library": tm["library"] / tm["ours"],
+                                         "library": "three torch._grouped_mm with this library's SwiGLU kernel between"}
+    del w2, y
     entry["forms"] = gate_up_forms(torch, lib, _lib, time_sweep,
                                    fused_call(o, x, wg, wu, rows, dim, hidden, hidden * dim, ends, groups), flops)
     out["B4_routed_131072x2048_to_1408_x64_experts"] = entry

@@ -78,6 +78,17 @@ def gate_up_swiglu(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.Tensor, *,
     return out.reshape(*x.shape[:-1], width)
 
 
+def grouped_linear(x: torch.Tensor, weight: torch.Tensor, *, group_ends: torch.Tensor | None = None) -> torch.Tensor:
+    """`x @ weight.T` per group with the same kernel: weight `[out, dim]` or `[groups, out, dim]` (out a multiple of 256) is
+    taken as two halves of output columns, which is exactly what the kernel's raw epilogue stores side by side.  The
+    projection after the activation of the routed experts (reference: src/sfu_repro/torchtitan/plugin.py:308-310, the third
+    `_grouped_mm`), where rows are already sorted by group."""
+    half = weight.shape[-2] // 2
+    if weight.shape[-2] % 256:
+        raise RuntimeError("the output width must be a multiple of 256")
+    return gate_up_swiglu(x, weight[..., :half, :], weight[..., half:, :], group_ends=group_ends, raw=True)
+
+
 # ---- dispatcher operators (usable under torch.compile; differentiable by recomputation) -------------------------------
 #   fpt_gate_up::swiglu(x, w_gate, w_up, degree, coeff_source_id)   the fused forward
 #   fpt_gate_up::products(x, w_gate, w_up)                          [gate | up], the kernel's raw epilogue
@@ -129,4 +140,4 @@ def gate_up_swiglu_recompute(x: torch.Tensor, w_gate: torch.Tensor, w_up: torch.
     return torch.ops.fpt_gate_up.swiglu(x, w_gate, w_up, int(degree), _SOURCES.index(coeff_source))
 
 
-__all__ = ["gate_up_swiglu", "gate_up_swiglu_recompute"]
+__all__ = ["gate_up_swiglu", "gate_up_swiglu_recompute", "grouped_linear"]

@@ -16,7 +16,7 @@ from typing import Any, Callable
 import torch
 from torch import nn
 
-from ..gate_up import gate_up_swiglu, gate_up_swiglu_recompute
+from ..gate_up import gate_up_swiglu, gate_up_swiglu_recompute, grouped_linear
 from .activations import (resolve_mlp_activation_impl, resolve_mlp_activation_mul_impl,
                           resolve_mlp_activation_packed_impl)
 
@@ -194,6 +194,10 @@ def run_grouped_experts(w1, w2, w3, x, num_tokens_per_expert, activation_mul, fu
             and w1.stride() == w3.stride() and _fusable(xb, w1, w1.shape[-2])):
         hidden = gate_up_swiglu(xb, w1, w3, group_ends=offsets, degree=fused_projection["degree"],
                                 coeff_source=fused_projection["coeff_source"])
+        if w2.dtype == torch.bfloat16 and w2.shape[-2] % 256 == 0 and w2.shape[-1] % 8 == 0 and w2.stride(-1) == 1:
+            # the projection back runs on the same kernel (its raw epilogue is a plain grouped product); rows that no group
+            # owns are left unwritten
+            return grouped_linear(hidden, w2, group_ends=offsets).type_as(x)
     else:
         gate = torch._grouped_mm(xb, w1.bfloat16().transpose(-2, -1), offs=offsets)
         up = torch._grouped_mm(xb, w3.bfloat16().transpose(-2, -1), offs=offsets)

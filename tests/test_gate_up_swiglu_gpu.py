@@ -251,6 +251,30 @@ def test_grouped_adapter_matches_the_three_product_path(cuda):
     assert float((fused[:1024].float() - two_step[:1024].float()).abs().max()) < 2e-2 * float(two_step.float().abs().max())
 
 
+def test_raw_epilogue_is_a_plain_grouped_product(cuda):
+    """`grouped_linear`: one weight seen as two halves of output columns; against an fp32 product per group, dense and grouped."""
+    import torch
+
+    from fast_polynomial_transcendentals_b200.gate_up import grouped_linear
+    torch.manual_seed(3)
+    rows, dim, out_dim, groups = 1500, 1408, 512, 5
+    x = torch.randn(rows, dim, device=cuda).to(torch.bfloat16)
+    w = (torch.randn(groups, out_dim, dim, device=cuda) * dim ** -0.5).to(torch.bfloat16)
+    ends = torch.tensor([100, 100, 700, 1400, 1500], dtype=torch.int32, device=cuda)
+    got = grouped_linear(x, w, group_ends=ends).float()
+    begin = 0
+    for gi, end in enumerate(ends.tolist()):
+        want = x[begin:end].float() @ w[gi].float().T
+        if end > begin:
+            assert float((got[begin:end] - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
+        begin = end
+    dense = grouped_linear(x, w[0]).float()
+    want = x.float() @ w[0].float().T
+    assert float((dense - want).abs().max()) <= 2.0 ** -7 * float(want.abs().max())
+    with pytest.raises(RuntimeError):
+        grouped_linear(x, w[0, :384])
+
+
 def test_argument_errors_come_back_as_status_codes(fpt, cuda):
     import torch
     x, wg, wu = make(cuda, 128, 64, 128)
