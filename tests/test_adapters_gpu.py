@@ -160,7 +160,7 @@ def test_b1_converter_on_a_torchtitan_llama(cuda):
     from torchtitan.models.llama3.model.model import Transformer
 
     from fast_polynomial_transcendentals_b200.sfu_repro import adapters, torchtitan_plugin as plugin
-    args = TransformerModelArgs(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, vocab_size=512, multiple_of=64, max_seq_len=128)
+    args = TransformerModelArgs(dim=256, n_layers=2, n_heads=2, n_kv_heads=1, vocab_size=512, multiple_of=128, max_seq_len=128)
     torch.manual_seed(0)
     base = Transformer(args)
     with torch.device(cuda):
@@ -178,3 +178,20 @@ def test_b1_converter_on_a_torchtitan_llama(cuda):
         assert all(isinstance(b.feed_forward, adapters.FusedGateUpFeedForward) for b in blocks)
         got = model(tokens).float()
         assert float((got - want).abs().max()) <= bound * float(want.abs().max()), variant
+    # the same conversion with the SwiGLU in the epilogue of the fused projection (hidden size permitting): inference runs
+    # one kernel per feed-forward input, "recompute" does so in training too
+    hidden = blocks[0].feed_forward.w_out.weight.shape[-1]
+    assert hidden % 128 == 0          # what the fused kernel tiles by (multiple_of above)
+    if True:
+        for setting in (True, "recompute"):
+            fused_job = job("polynomial")
+            fused_job.sfu.fuse_projection = setting
+            model = copy.deepcopy(base)
+            plugin.SFUReproConverter(fused_job, NS(tp=1)).convert(model)
+            with torch.no_grad():
+                got = model(tokens).float()
+            assert float((got - want).abs().max()) <= 0.08 * float(want.abs().max()), setting
+        loss = model(tokens).float().square().mean()       # "recompute": gradients flow through the fused operator
+        loss.backward()
+        block = (list(model.layers.values()) if hasattr(model.layers, "values") else list(model.layers))[0]
+        assert block.feed_forward.w_in.weight.grad is not None and bool(torch.isfinite(block.feed_forward.w_in.weight.grad).all())
