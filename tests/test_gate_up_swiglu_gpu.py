@@ -251,6 +251,41 @@ def test_grouped_adapter_matches_the_three_product_path(cuda):
     assert float((fused[:1024].float() - two_step[:1024].float()).abs().max()) < 2e-2 * float(two_step.float().abs().max())
 
 
+def test_random_shapes_every_form(fpt, cuda):
+    """Eighty seeded random problems (1..200 groups with empty and ragged ones, rows the groups do not cover, K blocks that
+    end inside a tile, tiny and odd sizes) through every form of the kernel: products against an fp32 product per group,
+    nothing written outside the groups, no status word."""
+    import random
+
+    import torch
+    rng = random.Random(20240611)
+    for _ in range(80):
+        groups = rng.choice([1, 1, 2, 3, 7, 16, 64, 200])
+        rows = rng.choice([1, 5, 127, 128, 129, 255, 256, 257, 300, 1000, 2049, rng.randint(1, 6000)])
+        dim = rng.choice([8, 64, 72, 128, 200, 512])
+        hidden = 128 * rng.choice([1, 1, 2, 3])
+        form = rng.choice([(0, -1), (128, 0), (256, 0), (0, 1), (0, 0)])
+        x, wg, wu = make(cuda, rows, dim, hidden, groups=max(groups, 2), seed=rows + dim)
+        wg, wu = wg[:groups].contiguous(), wu[:groups].contiguous()
+        last = rng.choice([rows, rows, max(0, rows - rng.randint(0, 300))])
+        cuts = sorted(rng.randint(0, last) for _ in range(groups - 1)) + [last]
+        ends = torch.tensor(cuts, dtype=torch.int32, device=cuda)
+        fpt.call("fpt_set_tuning", b"gate_up_tile_rows", form[0])
+        fpt.call("fpt_set_tuning", b"gate_up_cta_pair", form[1])
+        try:
+            raw = gate_up(fpt, x, wg, wu, ends, raw=True, fill=7.0)
+            fused = gate_up(fpt, x, wg, wu, ends, fill=7.0)
+        finally:
+            fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
+            fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
+        what = (groups, rows, dim, hidden, form, last)
+        assert bool((raw[last:] == 7.0).all()) and bool((fused[last:] == 7.0).all()), what
+        if last:
+            want = products_fp32(x, wg, wu, ends)[:last]
+            assert float((raw[:last].float() - want).abs().max()) <= 2.0 ** -7 * max(float(want.abs().max()), 1e-3) + 1e-6, what
+            assert not bool(torch.isnan(fused[:last].float()).any()), what
+
+
 def test_raw_epilogue_is_a_plain_grouped_product(cuda):
     """`grouped_linear`: one weight seen as two halves of output columns; against an fp32 product per group, dense and grouped."""
     import torch
