@@ -1053,6 +1053,21 @@ def bench_attention(torch, lib, _lib, device, S, time_sweep):
             tf = flops / (t["attn"] * 1e-3) / 1e12
             entry[label] = {"ms": t["attn"], "tflops": tf, "frac_of_measured_bf16_peak": tf / tensor_peak,
                             "frac_of_sustained_bf16_peak": tf / sustained}
+            if label == "poly" and route == 0:
+                # the same forward on pairs of CTAs (cta_group::2, opt-in), in the short loop above and in a loop long enough
+                # to meet the power cap (launches back to back for about a third of a second)
+                long_runs = max(20, int(300.0 / t["attn"]))
+                pair_entry = {}
+                for key, use_pair in (("single_cta", 0), ("cta_pair", 1)):
+                    _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"attention_cta_pair", use_pair))
+                    try:
+                        _, ts_ = time_sweep(fwd, 5, 2)
+                        _, tl_ = time_sweep(fwd, long_runs, 2)
+                    finally:
+                        _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"attention_cta_pair", 0))
+                    pair_entry[key] = {"short_loop_tflops": flops / (ts_["attn"] * 1e-3) / 1e12,
+                                       "long_loop_tflops": flops / (tl_["attn"] * 1e-3) / 1e12, "long_loop_launches": long_runs}
+                entry[label]["forward_on_cta_pairs"] = pair_entry
             if with_backward:
                 bwd = [("bwd", 0, lambda: _lib.check("fpt_attention_bwd_routed", lib.fpt_attention_bwd_routed(
                     dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(),

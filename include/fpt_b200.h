@@ -387,8 +387,8 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * keeps the deterministic two-pass form;
  * key "attention_cta_pair": 1 runs the attention forward on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one
  * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
- * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits, measured
- * 0.85-1.00x the single-CTA speed;
+ * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits; 0.85-1.00x the
+ * single-CTA speed in isolated launches, 1.14x in long back-to-back runs where heads share no K / V (B=2, S=16384, 32 heads);
  * key "gate_up_cta_pair": 1 runs fpt_gate_up_swiglu on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one product of
  * 256 rows whose weight tile is split over the two SMs), 0 on single CTAs, -1 (default) on pairs unless
  * "gate_up_tile_rows" names a height;
