@@ -798,10 +798,14 @@ extern "C" int fpt_attention_fwd_routed(void* out, void* lse, const void* q, con
     const size_t smem = sizeof(AttnSmem) + 1024;
     static_assert(sizeof(AttnSmem) + 1024 <= 227 * 1024, "shared memory budget");
     const int n_qblocks = int((seq + kSlots * kTileM - 1) / (kSlots * kTileM));
-    // Measured: the forward is not bound by K/V traffic in either order (B=2, S=16384, 32 heads: within 1 %), and with a
-    // causal mask heads fastest wins by 3-20 % (blocks that run together have the same length), so that is the default.
+    // Measured: with a causal mask heads fastest wins by 3-20 % (blocks that run together have the same length).  Without
+    // a mask isolated launches run alike in either order (B=2, S=16384, 32 heads: within 1 %), but heads fastest streams the
+    // K / V of every head at once (537 MB there, against 126 MB of L2: 30 GB of re-reads per launch), and in a run long
+    // enough to meet the power cap that traffic costs clock: rows fastest 1020-1100 against 885-990 TFLOP/s.  So: rows
+    // fastest when nothing is masked and K and V together exceed 64 MB, heads fastest otherwise.
     const int raster = fpt::tuning_attention_raster();
-    p.rows_fastest = raster >= 0 ? raster : 0;
+    const int64_t kv_bytes = 2 * batch * kv_heads * seq * head_dim * 2;
+    p.rows_fastest = raster >= 0 ? raster : (!causal && kv_bytes > (int64_t(64) << 20) ? 1 : 0);
     // Pairs of CTAs (clusters of two along x) need two blocks that walk the same K / V in step: two query heads of one
     // K / V group (heads on x, even group size: they also share their causal length), or two neighbouring row blocks of one
     // head where no mask makes their lengths differ (rows on x, whole blocks only).

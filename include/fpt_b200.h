@@ -381,14 +381,15 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * allows (soft-cap with cap*log2(e) <= 98), 0 forces the one-thread-per-row layout, 2 uses the column-split layout for
  * the sigmoid mode as well (measured no faster; kept for comparison runs);
  * key "attention_raster": order in which attention blocks are handed out: 0 heads fastest, 1 row blocks of one head
- * fastest, -1 (default) the measured-best choice per kernel (forward: heads; backward: rows when unmasked and large);
+ * fastest, -1 (default) the measured-best choice per kernel (forward and backward: rows when nothing is masked and the
+ * streamed tensors exceed 64 MB, heads otherwise);
  * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
  * key "attention_bwd_fused": 1 lets the attention backward take its one-pass form when the workspace allows, 0 (default)
  * keeps the deterministic two-pass form;
  * key "attention_cta_pair": 1 runs the attention forward on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one
  * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
  * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits; 0.85-1.00x the
- * single-CTA speed in isolated launches, 1.14x in long back-to-back runs where heads share no K / V (B=2, S=16384, 32 heads);
+ * single-CTA speed;
  * key "gate_up_cta_pair": 1 runs fpt_gate_up_swiglu on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one product of
  * 256 rows whose weight tile is split over the two SMs), 0 on single CTAs, -1 (default) on pairs unless
  * "gate_up_tile_rows" names a height;
