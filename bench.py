@@ -848,22 +848,25 @@ def bench_swiglu(torch, lib, _lib, device, S, hbm_peak, time_sweep):
 
 
 def gate_up_forms(torch, lib, _lib, time_sweep, call, flops):
-    """The three forms of the projection kernel on one problem: one CTA with 128- or 256-row tiles, pairs of CTAs.  Each
+    """The forms of the projection kernel on one problem: one CTA with 128- or 256-row tiles, pairs of CTAs with one or two
+    hidden tiles per row tile (the latter where the number of hidden tiles is even; otherwise it runs as the former).  Each
     is timed inside one back-to-back loop over the three (clocks as in a training step) and as isolated launches 50 ms
     apart (clocks at their maximum): TFLOP/s for both."""
-    forms = (("one_cta_128_rows", 128, 0), ("one_cta_256_rows", 256, 0), ("cta_pair", 0, 1))
+    forms = (("one_cta_128_rows", 128, 0, 0), ("one_cta_256_rows", 256, 0, 0), ("cta_pair_one_hidden_tile", 0, 1, 0),
+             ("cta_pair_two_hidden_tiles", 0, 1, 1))
 
-    def with_form(rows, pair):
+    def with_form(rows, pair, wide):
         def run():
             _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_tile_rows", rows))
             _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", pair))
+            _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_pair_wide", wide))
             call()
         return run
     try:
-        _, together = time_sweep([(name, 0, with_form(rows, pair)) for name, rows, pair in forms], 15, 2)
+        _, together = time_sweep([(name, 0, with_form(rows, pair, wide)) for name, rows, pair, wide in forms], 15, 2)
         alone = {}
-        for name, rows, pair in forms:
-            run = with_form(rows, pair)
+        for name, rows, pair, wide in forms:
+            run = with_form(rows, pair, wide)
             run()
             torch.cuda.synchronize()
             times = []
@@ -879,8 +882,9 @@ def gate_up_forms(torch, lib, _lib, time_sweep, call, flops):
     finally:
         _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_tile_rows", 0))
         _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_cta_pair", -1))
+        _lib.check("fpt_set_tuning", lib.fpt_set_tuning(b"gate_up_pair_wide", 0))
     return {name: {"back_to_back_ms": together[name], "back_to_back_tflops": flops / (together[name] * 1e-3) / 1e12,
-                   "isolated_ms": alone[name], "isolated_tflops": flops / (alone[name] * 1e-3) / 1e12} for name, _, _ in forms}
+                   "isolated_ms": alone[name], "isolated_tflops": flops / (alone[name] * 1e-3) / 1e12} for name, *_ in forms}
 
 
 def bench_gate_up(torch, lib, _lib, device, S, time_sweep):

@@ -28,6 +28,7 @@ Tuning tuning();
 // -1 (default) picks by the size of the K/V working set of the blocks that run together
 int tuning_attention_raster();
 int tuning_attention_bwd_fused();
+int tuning_gate_up_pair_wide();     // pairs of CTAs: 1 two hidden tiles per row tile where their number is even, 0 (default) one
 int tuning_gate_up_cta_pair();      // gate / up projection on pairs of CTAs (cta_group::2): 1 always, 0 never, -1 (default) unless a tile height is named
 int tuning_attention_cta_pair();    // attention forward on pairs of CTAs (cta_group::2) where two blocks share their K / V: 0 never, 1 where possible
 int tuning_gate_up_tile_rows();     // gate / up projection: rows per tile, 128 or 256 (0: 256 for dense, 128 for grouped problems)

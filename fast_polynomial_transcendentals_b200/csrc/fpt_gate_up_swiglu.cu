@@ -346,32 +346,37 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 // A first form let each CTA's loads complete on its own barrier and had a thread of the other CTA pass that on with
 // mbarrier.arrive.release.cluster: it ran at HALF speed, because a releasing remote arrive waits for every bulk load
 // still in flight into its CTA, which empties the ring (a relaxed arrive restored the speed; the direct form needs none).
-#ifndef FPT_GATE_UP_PAIR_ACCS
-#define FPT_GATE_UP_PAIR_ACCS 2
-#endif
-constexpr int kPairRing = 6;
-constexpr uint32_t kPairAccs = FPT_GATE_UP_PAIR_ACCS;      // accumulators of 256 columns (2 = all of tensor memory)
-constexpr uint32_t kPairColumns = 256u * kPairAccs;
+// WIDE = 2 gives the pair TWO hidden tiles per row tile (a 256 x 256 output tile, [gate | up] accumulators for both in the
+// 512 columns of tensor memory): x arrives once for both, which takes another quarter off the bytes per product (48
+// instead of 64 KiB per K block and CTA, for twice the products); the ring is four stages of 48 KiB and the epilogue (eight
+// warps, one accumulator per four) overlaps only with the loads of the next tile.  Needs an even number of hidden tiles.
+// Measured SLOWER than one hidden tile per row tile (16384 x 4096 -> 14336: 1362 against 1477 TFLOP/s back to back, 1521
+// against 1550 isolated): the alternating accumulators and the deeper ring are worth more than the bytes.  Opt-in.
+constexpr uint32_t kPairColumns = 512;
 
+template <int WIDE>
 struct GateUpPairSmem {
-    alignas(1024) uint8_t x[kPairRing][kXHalfBytes];
-    alignas(1024) uint8_t w[kPairRing][kXHalfBytes];       // rank 0: 128 gate weight rows; rank 1: 128 up weight rows
-    alignas(8) uint64_t full[kPairRing];
-    uint64_t empty[kPairRing];
+    static constexpr int kRing = 192 * 1024 / int(kXHalfBytes * (1 + WIDE));
+    alignas(1024) uint8_t x[kRing][kXHalfBytes];
+    alignas(1024) uint8_t w[kRing][WIDE * kXHalfBytes];    // rank 0: 128 gate weight rows per hidden tile; rank 1: up weight rows
+    alignas(8) uint64_t full[kRing];
+    uint64_t empty[kRing];
     uint64_t acc_full[2], acc_empty[2];                    // acc_empty used in the leading CTA
     TileTable table;
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
 
-template <class Op>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(256, 1)
+template <class Op, int WIDE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(128 + 128 * WIDE, 1)
 gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_wg,
                            const __grid_constant__ CUtensorMap map_wu, const GateUpParams p, const Op op) {
     constexpr int kRowsPerTile = 2 * kRowsPerHalf;
     extern __shared__ uint8_t smem_raw[];
     // the same offsets in both CTAs: the dynamic shared memory of both starts at the same address
-    GateUpPairSmem& sm = *reinterpret_cast<GateUpPairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    using Smem = GateUpPairSmem<WIDE>;
+    constexpr int kPairRing = Smem::kRing;
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_cta_rank();
     volatile uint32_t* abort_flag = &sm.abort_flag;
@@ -425,9 +430,12 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
 #else
                     // both CTAs' loads complete on the leading CTA's barrier, which expects the bytes of both
                     const uint32_t bar = map_to_cta(smem_u32(&sm.full[s]), 0);
-                    if (rank == 0) mbar_arrive_expect_tx(&sm.full[s], 4 * kXHalfBytes);
+                    if (rank == 0) mbar_arrive_expect_tx(&sm.full[s], 2 * (1 + WIDE) * kXHalfBytes);
                     tma_load_4d_pair(sm.x[s], &map_x, bar, kb * kBlockK, t.row0 + int(rank) * kRowsPerHalf, 0, 0);
-                    tma_load_4d_pair(sm.w[s], map_w, bar, kb * kBlockK, t.hidden_tile * kHiddenPerTile, t.group, 0);
+#pragma unroll
+                    for (int h = 0; h < WIDE; ++h)
+                        tma_load_4d_pair(sm.w[s] + h * kXHalfBytes, map_w, bar, kb * kBlockK,
+                                         (t.hidden_tile * WIDE + h) * kHiddenPerTile, t.group, 0);
 #endif
                 }
             }
@@ -440,13 +448,15 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
             uint32_t it = 0, local = 0;
             bool ok = true;
             for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
-                const uint32_t a = local % kPairAccs, use = local / kPairAccs;
-                if (use > 0) {                              // both CTAs' epilogues have read this accumulator
-                    ok = mbar_wait_cluster(&sm.acc_empty[a], (use - 1u) & 1u, abort_flag, p.status, kGuAccEmpty);
+                // WIDE = 1: the two accumulators alternate; WIDE = 2: accumulator h belongs to hidden tile h of every tile
+                const uint32_t a0 = WIDE == 1 ? (local & 1u) : 0u, use = WIDE == 1 ? (local >> 1) : local;
+                if (use > 0) {                              // both CTAs' epilogues have read the accumulator(s)
+#pragma unroll
+                    for (uint32_t h = 0; h < uint32_t(WIDE); ++h)
+                        ok = ok && mbar_wait_cluster(&sm.acc_empty[a0 + h], (use - 1u) & 1u, abort_flag, p.status, kGuAccEmpty);
                     if (!ok) break;
                     tc_fence_after_sync();
                 }
-                const uint32_t d = tmem + a * 256u;
                 for (int kb = 0; kb < p.k_blocks; ++kb, ++it) {
                     const uint32_t s = it % kPairRing, use_s = it / kPairRing;
                     ok = mbar_wait(&sm.full[s], use_s & 1u, abort_flag, p.status, kGuFull);
@@ -456,12 +466,19 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
                     const uint32_t w_lo = umma_smem_desc_lo(smem_u32(sm.w[s]), 16);
 #if FPT_GATE_UP_DIAG != 3
 #pragma unroll
-                    for (uint32_t k = 0; k < kBlockK / 16; ++k)
-                        umma_ss_words_pair(d, x_lo + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    for (uint32_t h = 0; h < uint32_t(WIDE); ++h) {
+#pragma unroll
+                        for (uint32_t k = 0; k < kBlockK / 16; ++k)
+                            umma_ss_words_pair(tmem + (a0 + h) * 256u, x_lo + 2u * k, w_lo + h * (kXHalfBytes / 16u) + 2u * k, desc_hi,
+                                               idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    }
 #endif
                     umma_commit_pair(&sm.empty[s], 3);
                 }
-                if (ok) umma_commit_pair(&sm.acc_full[a], 3);
+                if (ok) {
+#pragma unroll
+                    for (uint32_t h = 0; h < uint32_t(WIDE); ++h) umma_commit_pair(&sm.acc_full[a0 + h], 3);
+                }
             }
         }
     } else if (warp >= 4) {
@@ -471,12 +488,13 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
         bool ok = true;
         for (int tile = first_tile; tile < total_tiles && ok; tile += tile_step, ++local) {
             const Tile t = decode_tile<kRowsPerTile>(sm.table, p, tile);
-            const uint32_t a = local % kPairAccs, use = local / kPairAccs;
+            const uint32_t h = WIDE == 1 ? 0u : uint32_t(warp - 4) >> 2;       // which hidden tile of the row tile
+            const uint32_t a = WIDE == 1 ? (local & 1u) : h, use = WIDE == 1 ? (local >> 1) : local;
             ok = mbar_wait(&sm.acc_full[a], use & 1u, abort_flag, p.status, kGuAccFull);
             if (!ok) break;
             tc_fence_after_sync();
             const int row = t.row0 + int(rank) * kRowsPerHalf + 32 * (warp & 3) + lane;
-            uint16_t* out_row = p.out + int64_t(row) * p.out_ld + t.hidden_tile * kHiddenPerTile;
+            uint16_t* out_row = p.out + int64_t(row) * p.out_ld + (t.hidden_tile * WIDE + int(h)) * kHiddenPerTile;
             epilogue_rows(op, p, tmem + lane_base + a * 256u, out_row, row < t.row_end);
             tc_fence_before_sync();
             __syncwarp();
@@ -579,15 +597,23 @@ extern "C" int fpt_gate_up_swiglu(void* out, const void* x, const void* w_gate, 
         kernel<<<grid, 128 + 128 * H, smem, stream>>>(map_x, map_wg, map_wu, p, op);
         return cuda_status(cudaGetLastError());
     };
-    auto launch_pair = [&](auto op) {
-        const size_t smem = sizeof(GateUpPairSmem) + 1024;
-        auto kernel = gate_up_swiglu_pair_kernel<decltype(op)>;
+    // two hidden tiles per row tile of a pair where asked for (tuning key gate_up_pair_wide) and their number is even
+    const bool wide = pair && (hidden / kHiddenPerTile) % 2 == 0 && fpt::tuning_gate_up_pair_wide() != 0;
+    auto launch_pair_wide = [&](auto op, auto wide_c) {
+        constexpr int W = decltype(wide_c)::value;
+        GateUpParams pw = p;
+        pw.hidden_tiles = p.hidden_tiles / W;               // the table counts tiles of W hidden tiles
+        const size_t smem = sizeof(GateUpPairSmem<W>) + 1024;
+        static_assert(sizeof(GateUpPairSmem<W>) + 1024 <= 227 * 1024, "shared memory budget");
+        auto kernel = gate_up_swiglu_pair_kernel<decltype(op), W>;
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
-        const int64_t pairs = std::min<int64_t>(group_ends ? dev.sm_count / 2 : dense_tiles, dev.sm_count / 2);
-        kernel<<<unsigned(2 * pairs), 256, smem, stream>>>(map_x, map_wg, map_wu, p, op);   // clusters of two (kernel attribute)
+        const int64_t tiles = (rows + 2 * kRowsPerHalf - 1) / (2 * kRowsPerHalf) * pw.hidden_tiles;
+        const int64_t pairs = std::min<int64_t>(group_ends ? dev.sm_count / 2 : tiles, dev.sm_count / 2);
+        kernel<<<unsigned(2 * pairs), 128 + 128 * W, smem, stream>>>(map_x, map_wg, map_wu, pw, op);   // clusters of two (kernel attribute)
         return cuda_status(cudaGetLastError());
     };
+    auto launch_pair = [&](auto op) { return wide ? launch_pair_wide(op, IC<2>{}) : launch_pair_wide(op, IC<1>{}); };
     auto launch = [&](auto op) {
         if (pair) return launch_pair(op);
         return halves == 2 ? launch_halves(op, IC<2>{}) : launch_halves(op, IC<1>{});

@@ -24,6 +24,7 @@ std::atomic<int> g_attention_bwd_fused{0};
 std::atomic<int> g_gate_up_tile_rows{0};
 std::atomic<int> g_attention_cta_pair{0};
 std::atomic<int> g_gate_up_cta_pair{-1};
+std::atomic<int> g_gate_up_pair_wide{0};
 std::atomic<int> g_rope_heads_per_block{8};   // measured: 8 is 1.5-3 % ahead of "all heads in one block" at 32 heads
 
 enum { DT_FP16 = kFp16, DT_BF16 = kBf16 };
@@ -72,6 +73,7 @@ int tuning_attention_bwd_fused() { return g_attention_bwd_fused.load(); }
 int tuning_gate_up_tile_rows() { return g_gate_up_tile_rows.load(); }
 int tuning_attention_cta_pair() { return g_attention_cta_pair.load(); }
 int tuning_gate_up_cta_pair() { return g_gate_up_cta_pair.load(); }
+int tuning_gate_up_pair_wide() { return g_gate_up_pair_wide.load(); }
 int tuning_rope_heads_per_block() { return g_rope_heads_per_block.load(); }
 
 const ProgramRow* program_table(int* count) {
@@ -159,6 +161,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!std::strcmp(key, "rope_heads_per_block")) { if (value < 0 || value > 65535) return FPT_ERR_BAD_SIZE; fpt::g_rope_heads_per_block = value; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_tile_rows")) { if (value != 0 && value != 128 && value != 256) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_tile_rows = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_cta_pair")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_cta_pair = value; return FPT_OK; }
+    if (!std::strcmp(key, "gate_up_pair_wide")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_pair_wide = value; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_cta_pair")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_cta_pair = value; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }
@@ -173,6 +176,7 @@ int fpt_get_tuning(const char* key, int* value) {
     if (!std::strcmp(key, "rope_heads_per_block")) { *value = fpt::g_rope_heads_per_block; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_tile_rows")) { *value = fpt::g_gate_up_tile_rows; return FPT_OK; }
     if (!std::strcmp(key, "attention_cta_pair")) { *value = fpt::g_attention_cta_pair; return FPT_OK; }
+    if (!std::strcmp(key, "gate_up_pair_wide")) { *value = fpt::g_gate_up_pair_wide; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_cta_pair")) { *value = fpt::g_gate_up_cta_pair; return FPT_OK; }
     return FPT_ERR_BAD_ENUM;
 }

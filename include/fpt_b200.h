@@ -393,6 +393,8 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * key "gate_up_cta_pair": 1 runs fpt_gate_up_swiglu on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one product of
  * 256 rows whose weight tile is split over the two SMs), 0 on single CTAs, -1 (default) on pairs unless
  * "gate_up_tile_rows" names a height;
+ * key "gate_up_pair_wide": 1 gives a pair two hidden tiles per row tile (a 256 x 256 output tile) where the number of hidden
+ * tiles is even, 0 (default) one: measured slower (no accumulator left to alternate);
  * key "gate_up_tile_rows": rows per tile of the single-CTA forms, 128 or 256; 0 (default) = 256 for one group (both halves
  * of a tile share every weight tile: fewer bytes per product, which under the power cap is the faster form), 128 for
  * grouped problems (a ragged group wastes less of a smaller tile). */

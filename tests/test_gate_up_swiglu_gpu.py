@@ -64,16 +64,20 @@ def products_fp32(x, wg, wu, ends=None):
     return want
 
 
-@pytest.fixture(params=[(0, -1), (128, -1), (256, -1), (0, 1), (0, 0)], ids=["auto", "tile_128", "tile_256", "cta_pair", "one_cta"])
+@pytest.fixture(params=[(0, -1, 0), (128, -1, 0), (256, -1, 0), (0, 1, 1), (0, 0, 0)],
+                ids=["auto", "tile_128", "tile_256", "cta_pair_wide", "one_cta"])
 def tile_rows(request, fpt):
-    """Every form of the kernel: the default (pairs of CTAs), the two tile heights on one CTA, pairs asked for by name, and
-    single CTAs with the height left to the library (256 rows dense, 128 grouped)."""
-    rows, pair = request.param
+    """Every form of the kernel: the default (pairs of CTAs, one hidden tile per row tile), the two tile heights on one CTA,
+    pairs with two hidden tiles per row tile (where their number is even), and single CTAs with the height left to the
+    library (256 rows dense, 128 grouped)."""
+    rows, pair, wide = request.param
     fpt.call("fpt_set_tuning", b"gate_up_tile_rows", rows)
     fpt.call("fpt_set_tuning", b"gate_up_cta_pair", pair)
+    fpt.call("fpt_set_tuning", b"gate_up_pair_wide", wide)
     yield request.param
     fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
     fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
+    fpt.call("fpt_set_tuning", b"gate_up_pair_wide", 0)
 
 
 @pytest.mark.parametrize("rows,dim,hidden", [(1, 64, 128), (128, 64, 128), (300, 4096, 384), (1000, 200, 128), (777, 1024, 1408)])
@@ -137,15 +141,17 @@ def test_grouped_rows_follow_their_group(fpt, cuda, tile_rows, ends):
 def test_forms_agree_bit_for_bit(fpt, cuda):
     """One CTA with either tile height and a pair of CTAs add the same products in the same order."""
     import torch
-    x, wg, wu = make(cuda, 3000, 1024, 384, seed=21)
+    x, wg, wu = make(cuda, 3000, 1024, 512, seed=21)      # four hidden tiles: the wide pair form applies
     outs = []
-    for rows, pair in ((128, 0), (256, 0), (0, 1)):
+    for rows, pair, wide in ((128, 0, 1), (256, 0, 1), (0, 1, 0), (0, 1, 1)):
         fpt.call("fpt_set_tuning", b"gate_up_tile_rows", rows)
         fpt.call("fpt_set_tuning", b"gate_up_cta_pair", pair)
+        fpt.call("fpt_set_tuning", b"gate_up_pair_wide", wide)
         outs.append(gate_up(fpt, x, wg, wu))
     fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
     fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
-    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    fpt.call("fpt_set_tuning", b"gate_up_pair_wide", 0)
+    assert all(torch.equal(outs[0], other) for other in outs[1:])
 
 
 def test_many_groups_like_routed_experts(fpt, cuda, tile_rows):
@@ -263,8 +269,9 @@ def test_random_shapes_every_form(fpt, cuda):
         groups = rng.choice([1, 1, 2, 3, 7, 16, 64, 200])
         rows = rng.choice([1, 5, 127, 128, 129, 255, 256, 257, 300, 1000, 2049, rng.randint(1, 6000)])
         dim = rng.choice([8, 64, 72, 128, 200, 512])
-        hidden = 128 * rng.choice([1, 1, 2, 3])
+        hidden = 128 * rng.choice([1, 1, 2, 3, 4])
         form = rng.choice([(0, -1), (128, 0), (256, 0), (0, 1), (0, 0)])
+        wide = rng.choice([0, 1])
         x, wg, wu = make(cuda, rows, dim, hidden, groups=max(groups, 2), seed=rows + dim)
         wg, wu = wg[:groups].contiguous(), wu[:groups].contiguous()
         last = rng.choice([rows, rows, max(0, rows - rng.randint(0, 300))])
@@ -272,13 +279,15 @@ def test_random_shapes_every_form(fpt, cuda):
         ends = torch.tensor(cuts, dtype=torch.int32, device=cuda)
         fpt.call("fpt_set_tuning", b"gate_up_tile_rows", form[0])
         fpt.call("fpt_set_tuning", b"gate_up_cta_pair", form[1])
+        fpt.call("fpt_set_tuning", b"gate_up_pair_wide", wide)
         try:
             raw = gate_up(fpt, x, wg, wu, ends, raw=True, fill=7.0)
             fused = gate_up(fpt, x, wg, wu, ends, fill=7.0)
         finally:
             fpt.call("fpt_set_tuning", b"gate_up_tile_rows", 0)
             fpt.call("fpt_set_tuning", b"gate_up_cta_pair", -1)
-        what = (groups, rows, dim, hidden, form, last)
+            fpt.call("fpt_set_tuning", b"gate_up_pair_wide", 0)
+        what = (groups, rows, dim, hidden, form, wide, last)
         assert bool((raw[last:] == 7.0).all()) and bool((fused[last:] == 7.0).all()), what
         if last:
             want = products_fp32(x, wg, wu, ends)[:last]
