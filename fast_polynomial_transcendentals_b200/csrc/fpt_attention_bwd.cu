@@ -64,7 +64,7 @@ using BwdSmem = BwdSmemT<false>;
 struct BwdParams {
     uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
     uint16_t* out1;        // dV (WHICH 1, 2)
-    float* dq_accum;       // WHICH 2: fp32 [B, S, Hq, D], zeroed before the launch (reached through its tensor map)
+    float* dq_accum;       // WHICH 2: fp32 [B, Hq, S, D], zeroed before the launch (reached through its tensor map)
     const float* lse2;     // workspace plane 0: [B, Hq, S rounded up to whole tiles]
     const float* delta;    // workspace plane 1
     int batch, seq, q_heads, kv_heads;
@@ -149,17 +149,25 @@ __global__ void __launch_bounds__(256) attention_bwd_prepass_kernel(const Prepas
     }
 }
 
-// ---- last pass of the fused form: dq = bf16(scale * accumulated fp32 dQ), eight elements per thread and step ----------
+// ---- last pass of the fused form: dq [B, S, Hq, 128] = bf16(scale * accumulated fp32 dQ [B, Hq, S, 128]), eight elements
+// per thread and step ----------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(256) attention_bwd_dq_convert_kernel(const float* __restrict__ accum, uint16_t* __restrict__ dq,
-                                                                      int64_t n8, float scale) {
+                                                                      int64_t n8, int seq, int heads, float scale) {
 #pragma unroll 1
     for (int64_t i = int64_t(blockIdx.x) * 256 + threadIdx.x; i < n8; i += int64_t(gridDim.x) * 256) {
-        const float4 a = reinterpret_cast<const float4*>(accum)[2 * i], b = reinterpret_cast<const float4*>(accum)[2 * i + 1];
+        const int d8 = int(i % (kDim / 8));
+        const int64_t row = i / (kDim / 8);                 // (b, s, h) of the output
+        const int h = int(row % heads);
+        const int64_t bs = row / heads;
+        const int sq = int(bs % seq);
+        const int64_t b = bs / seq;
+        const float4* src = reinterpret_cast<const float4*>(accum + ((b * heads + h) * seq + sq) * kDim) + 2 * d8;
+        const float4 a = src[0], c = src[1];
         uint4 o;
         o.x = Sfu<kBf16>::pack(a.x * scale, a.y * scale);
         o.y = Sfu<kBf16>::pack(a.z * scale, a.w * scale);
-        o.z = Sfu<kBf16>::pack(b.x * scale, b.y * scale);
-        o.w = Sfu<kBf16>::pack(b.z * scale, b.w * scale);
+        o.z = Sfu<kBf16>::pack(c.x * scale, c.y * scale);
+        o.w = Sfu<kBf16>::pack(c.z * scale, c.w * scale);
         reinterpret_cast<uint4*>(dq)[i] = o;
     }
 }
@@ -834,9 +842,11 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     float* dq_accum = fused ? reinterpret_cast<float*>(static_cast<char*>(workspace) + bwd_planes_bytes(batch, seq, q_heads)) : nullptr;
     CUtensorMap map_dq = map_q;          // only the single-pass form reads it
     if (fused) {
-        // fp32 [B, S, Hq, 128] as (dim, seq, head, batch); a box is 32 columns (one 128-byte line) x 32 query rows
+        // fp32 [B, Hq, S, 128] as (dim, seq, head, batch); a box is 32 columns (one 128-byte line) x 32 query rows.  Head-major,
+        // so that the 128 x 128 tile a block adds into is one contiguous 64 KiB: with the rows of a tile 16 KiB apart
+        // ([B, S, Hq, 128], 32 heads) the additions of a tile fell on few L2 slices
         const uint64_t dims[4] = {uint64_t(kDim), uint64_t(seq), uint64_t(q_heads), uint64_t(batch)};
-        const uint64_t strides[3] = {uint64_t(q_heads) * kDim * 4, uint64_t(kDim) * 4, uint64_t(seq) * q_heads * kDim * 4};
+        const uint64_t strides[3] = {uint64_t(kDim) * 4, uint64_t(seq) * kDim * 4, uint64_t(seq) * q_heads * kDim * 4};
         const uint32_t box[4] = {32u, 32u, 1u, 1u};
         if (int rc = make_tensor_map_f32_4d(&map_dq, dq_accum, dims, strides, box)) return rc;
     }
@@ -874,7 +884,8 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
             int64_t grid = (n / 8 + 255) / 256;
             const int64_t cap = int64_t(dev.sm_count) * 16;
             if (grid > cap) grid = cap;
-            attention_bwd_dq_convert_kernel<<<unsigned(grid), 256, 0, stream>>>(dq_accum, static_cast<uint16_t*>(dq), n / 8, scale);
+            attention_bwd_dq_convert_kernel<<<unsigned(grid), 256, 0, stream>>>(dq_accum, static_cast<uint16_t*>(dq), n / 8, int(seq),
+                                                                                int(q_heads), scale);
             return cuda_status(cudaGetLastError());
         }
         // dQ: fixed Q, dO; streamed K, V.   dK, dV: fixed K, V; streamed Q, dO
