@@ -6,18 +6,18 @@
 //   WHICH = 1  dK, dV:  one CTA per (batch, kv head, 128 keys), loops over the query heads of its group and their
 //                       query tiles;  S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
 //   WHICH = 2  dK, dV and dQ in one pass (5 matrix products per tile pair instead of 7): the dK / dV block also forms
-//                       dQ_partial = dS K for the streamed query tile (dS^T goes to shared memory as well, read back as
-//                       an MN-major A operand; K is the block's fixed tile, read as an MN-major B operand), the score-mod
-//                       warps read the partial tile out of tensor memory, stage it in shared memory and add it into an
-//                       fp32 dQ buffer with tiled reduce-add copies (one partial per key tile: the order of the
-//                       additions, and so the last bits of dQ, is not fixed from run to run); a last pass scales and
-//                       rounds the buffer to bf16
+//                       dQ_partial^T = K^T dS^T for the streamed query tile (K is the block's fixed tile, read as an
+//                       MN-major A operand; dS^T goes to shared memory as well and is read back as an MN-major B
+//                       operand), a fourth warpgroup reads the partial tile out of tensor memory, stages it in shared
+//                       memory that the step no longer needs and adds it into an fp32 dQ buffer with untiled reduce-add
+//                       copies (one partial per key tile: the order of the additions, and so the last bits of dQ, is not
+//                       fixed from run to run); a last pass scales and rounds the buffer to bf16
 // Written once in terms of "fixed" tiles X, Y (loaded once) and "streamed" tiles U, W (2-stage ring):
 //   S = X U^T and dP = Y W^T (both operands K-major from shared memory),
 //   acc0 += dS U and (WHICH = 1) acc1 += P W, with P / dS read from tensor memory and U / W as MN-major operands.
-// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
-// tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
-// (the backward has no row reduction, so the split needs no exchange).
+// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, (WHICH = 2) warps 12..15 read-out of the partial dQ
+// tiles, warps 4..11 score-mod warps: thread = one tensor-memory lane (row of the fixed tile), warps w and w+4 share a
+// lane quarter and split the 128 columns in halves (the backward has no row reduction, so the split needs no exchange).
 // Tensor memory: S is never overwritten (each score-mod warp writes its bf16 dS and P words over its own 64 columns of
 // the dP tile), so the S product of the next step runs under the score-mod of the current one; dQ also double-buffers
 // dP.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
@@ -41,6 +41,7 @@ constexpr int kRing = 2;
 constexpr uint32_t kPanelB = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
 constexpr uint32_t kTileB = 2 * kPanelB;
 constexpr int kBwdThreads = 384;
+constexpr int kBwdThreadsFused = 512;   // the single-pass form adds a warpgroup that reads the partial dQ tiles out
 constexpr float kLog2eB = 1.4426950408889634f;
 
 template <bool WITH_DS_TILE>
@@ -55,7 +56,9 @@ struct BwdSmemT {
     alignas(8) uint64_t xy_full;
     uint64_t uw_full[kRing], uw_empty[kRing];
     uint64_t s_full, ld_done, p_full, acc_done;
-    uint64_t dq_full, dq_read;                 // WHICH = 2: partial dQ tile complete / read out of tensor memory
+    uint64_t dq_full[2], dq_read;              // WHICH = 2: half of the partial dQ tile complete / all read out of tensor memory
+    uint64_t dq_staged;                        // WHICH = 2: one half of the partial dQ tile is in shared memory (4 warps)
+    uint64_t w_empty[kRing], ds_free;          // WHICH = 2: the copy engine has read the half staged in w[st] / in ds
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
@@ -64,7 +67,7 @@ using BwdSmem = BwdSmemT<false>;
 struct BwdParams {
     uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
     uint16_t* out1;        // dV (WHICH 1, 2)
-    float* dq_accum;       // WHICH 2: fp32 [B, Hq, S, D], zeroed before the launch (reached through its tensor map)
+    float* dq_accum;       // WHICH 2: fp32 [B, Hq, S, D], zeroed before the launch
     const float* lse2;     // workspace plane 0: [B, Hq, S rounded up to whole tiles]
     const float* delta;    // workspace plane 1
     int batch, seq, q_heads, kv_heads;
@@ -99,9 +102,12 @@ struct BwdParams {
 #define FPT_BTRACE(slot, tag) do { } while (0)
 #endif
 
-enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone, kBwdDqFull, kBwdDqRead };
+enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone, kBwdDqFull, kBwdDqRead, kBwdDqStaged, kBwdWEmpty, kBwdDsFree };
 
 // 16 bytes to shared memory (address from smem_u32)
+__device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
+    asm volatile("st.shared.b32 [%0], %1;" :: "r"(addr), "r"(a) : "memory");
+}
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
     asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" :: "r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
@@ -308,10 +314,10 @@ struct Cols {
 // every EMU columns of a score-mod warp's 64 take exp2_full_x2<EK> on the FMA pipe (reference: exp2_emu_freq_bwd,
 // src/sfu_repro/fa4.py:724-752).
 template <int MODE, int WHICH, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(WHICH == 2 ? kBwdThreadsFused : kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                      const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
-                     const __grid_constant__ CUtensorMap map_dq, const BwdParams p) {
+                     const BwdParams p) {
     constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;    // no normalisation: neither lse nor delta
     constexpr bool kKeysFixed = WHICH >= 1;                   // rows of the fixed tiles are keys, streamed tiles are queries
     constexpr bool kFusedDq = WHICH == 2;
@@ -356,8 +362,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         mbar_init(&sm.ld_done, 8);      // one arrive per score-mod warp: its S and dP values are in registers
         mbar_init(&sm.p_full, 8);       // one arrive per score-mod warp: its P and dS words are in tensor memory
         mbar_init(&sm.acc_done, 1);
-        mbar_init(&sm.dq_full, 1);
-        mbar_init(&sm.dq_read, 8);      // one arrive per score-mod warp: its part of the partial dQ tile is in registers
+        mbar_init(&sm.dq_full[0], 1);
+        mbar_init(&sm.dq_full[1], 1);
+        mbar_init(&sm.dq_staged, 4);
+        mbar_init(&sm.w_empty[0], 1);
+        mbar_init(&sm.w_empty[1], 1);
+        mbar_init(&sm.ds_free, 1);
+        mbar_init(&sm.dq_read, 4);      // one arrive per read-out warp: its rows of the partial dQ tile are in registers
         sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
         if (kFusedDq && (smem_u32(&sm) & 1023u) != 0u) {      // the operand layouts need 1024-byte alignment
             sm.abort_flag = 1u;
@@ -379,8 +390,13 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const uint32_t tmem = sm.tmem_base;
     const bool skip = sm.abort_flag != 0u;
 
+    // Register budget (see the forward kernel): 384 threads start at 168 and move 128 x (168 - 80) to the score-mod warps
+    // (208 each); the single-pass form's 512 threads start at 128: 128 x (128 - 56) + 128 x (128 - 104) released,
+    // 256 x (176 - 128) taken.
+    static_assert(128 * (128 - 56) + 128 * (128 - 104) >= 256 * (176 - 128), "register hand-over of the single-pass form");
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+      if constexpr (kFusedDq) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      else asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
       if (skip || warp >= 2) {
         // warps 2 and 3 only hold registers for the others
       } else if (warp == 0) {
@@ -404,13 +420,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 mbar_arrive_expect_tx(&sm.uw_full[st], 2 * kTileB + vec_bytes);
                 tma_load_4d(sm.u[st], &map_u, &sm.uw_full[st], 0, r0, sh, b);
                 tma_load_4d(sm.u[st] + kPanelB, &map_u, &sm.uw_full[st], 64, r0, sh, b);
-                tma_load_4d(sm.w[st], &map_w, &sm.uw_full[st], 0, r0, sh, b);
-                tma_load_4d(sm.w[st] + kPanelB, &map_w, &sm.uw_full[st], 64, r0, sh, b);
                 if (vec_bytes) {   // per-query vectors of the streamed query tile
                     const int64_t off = (int64_t(b) * p.q_heads + sh) * seq_pad + r0;
                     bulk_load_1d(sm.lse2[st], p.lse2 + off, kTile * 4u, &sm.uw_full[st]);
                     bulk_load_1d(sm.delta[st], p.delta + off, kTile * 4u, &sm.uw_full[st]);
                 }
+                if constexpr (kFusedDq) {      // the read-out warps staged half a partial dQ tile in this stage's W tile
+                    if (t >= kRing) ok = mbar_wait(&sm.w_empty[st], ph ^ 1u, abort_flag, p.status, kBwdWEmpty);
+                    if (!ok) break;
+                }
+                tma_load_4d(sm.w[st], &map_w, &sm.uw_full[st], 0, r0, sh, b);
+                tma_load_4d(sm.w[st] + kPanelB, &map_w, &sm.uw_full[st], 64, r0, sh, b);
             }
         }
       } else {
@@ -418,7 +438,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
-            constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kTile, kDim, 1, 1);  // both operands MN-major (partial dQ)
+            constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kDim, kTile / 2, 1, 1);   // both operands MN-major (partial dQ)
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
             constexpr uint32_t kColAcc0 = Cols<WHICH>::acc0;
             auto dp_col = [](int t) { return Cols<WHICH>::dp(t); };
@@ -493,21 +513,27 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                                       w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 }
                 if constexpr (kFusedDq) {
-                    // partial dQ of the streamed query tile: dS (queries x keys: the dS^T tile in shared memory read as an
-                    // MN-major A operand) times K (the fixed tile, read as an MN-major B operand), into the dP tile's
-                    // columns, which the two products above have finished reading by the time this one runs (in order)
+                    // partial dQ of the streamed query tile, transposed: K^T (head dimension x keys: the fixed tile read as an
+                    // MN-major A operand) times dS^T (the dS^T tile in shared memory read as an MN-major B operand), into
+                    // the dP tile's columns, which the two products above have finished reading by the time this one runs
+                    // (in order).  Lanes of the result are the head dimension and columns the queries.  Issued as two
+                    // products of 64 queries (one panel of the dS^T tile each) with a commit of their own, so that the
+                    // read-out of the first half runs under the second product.
                     const uint32_t ds_mn = umma_smem_desc_lo(smem_u32(sm.ds), kPanelB);
                     const uint32_t x_mn = umma_smem_desc_lo(smem_u32(sm.x), kPanelB);
 #pragma unroll
-                    for (int kk = 0; kk < 8; ++kk)
-                        umma_ss_words(tmem + dp_col(t), ds_mn + uint32_t(kk) * (2048u / 16u), x_mn + uint32_t(kk) * (2048u / 16u),
-                                      desc_hi, idesc_mnmn, kk > 0);
-                    umma_commit(&sm.dq_full);
+                    for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                        for (int kk = 0; kk < 8; ++kk)
+                            umma_ss_words(tmem + dp_col(t) + uint32_t(64 * h), x_mn + uint32_t(kk) * (2048u / 16u),
+                                          ds_mn + uint32_t(h) * (kPanelB / 16u) + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mnmn, kk > 0);
+                        umma_commit(&sm.dq_full[h]);
+                    }
                 }
                 umma_commit(&sm.uw_empty[st]);
                 FPT_BTRACE(2, 13);
                 // [C] WHICH 1, 2: the one dP tile is free again once the products above have read it (same thread, in
-                // order) and, WHICH 2, once the score-mod warps have read the partial dQ tile out of it
+                // order) and, WHICH 2, once the read-out warps have taken the partial dQ tile out of it
                 if constexpr (kKeysFixed) {
                     if constexpr (kFusedDq) {
                         ok = mbar_wait(&sm.dq_read, uint32_t(t) & 1u, abort_flag, p.status, kBwdDqRead);
@@ -524,8 +550,75 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             if (ok) umma_commit(&sm.acc_done);
         }
       }
+    } else if (kFusedDq && warp >= 12) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+      if (!skip) {
+        // ------------------------------------------------------------------ read-out warps of the single-pass form
+        // Off the serial chain of a step: once the partial dQ product of step t is complete (and with it every product
+        // that read the streamed tiles of ring stage st and the dS^T tile), this warpgroup copies the tile out of tensor
+        // memory into shared memory, 512 bytes per query as in the fp32 buffer: queries 0..63 over the stage's dO tile,
+        // 64..127 over the dS^T tile (32 KiB each), releases the dP tile's columns, and hands each half to the copy engine
+        // as one untiled reduce-add.  The product is held transposed (lane = head-dimension index, column = query), so a
+        // warp's store of one register covers 128 consecutive bytes of shared memory.  The dO tile goes back to the
+        // producer and the dS^T tile to the score-mod warps (who write it at the end of the next step's pass) once the
+        // copy engine has read them; the Q tile of the stage, which the next S product but one wants first, is not used.
+        const int quarter = warp & 3;
+        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        bool ok = true;
+        for (int t = 0; t < n_inner && ok; ++t) {
+            const int st = t % kRing;
+            const int g = t / per_head;
+            const int q_tile0 = (first_inner + (t - g * per_head)) * kTile;      // first query of the streamed tile
+            float* tile_dst = p.dq_accum + ((int64_t(b) * p.q_heads + stream_head0 + g) * p.seq + q_tile0) * kDim;
+            const int q_left = p.seq - q_tile0;                                  // queries of this tile that exist
+#pragma unroll
+            for (int batch = 0; batch < 2; ++batch) {          // 64 queries at a time
+                ok = mbar_wait(&sm.dq_full[batch], uint32_t(t) & 1u, abort_flag, p.status, kBwdDqFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                uint32_t v0[32], v1[32];
+                tmem_ld_32x32b_x32(tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * batch), v0);
+                tmem_ld_32x32b_x32(tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * batch + 32), v1);
+                tmem_ld_wait();
+                if (batch == 1) {                              // everything is in registers: the columns are free
+                    tc_fence_before_sync();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(&sm.dq_read);
+                }
+                uint8_t* stage = batch == 0 ? sm.w[st] : sm.ds;
+                const uint32_t mine = smem_u32(stage) + uint32_t(32 * quarter + lane) * 4u;
+#pragma unroll
+                for (int j = 0; j < 64; ++j) sts32(mine + uint32_t(j) * (kDim * 4u), j < 32 ? v0[j & 31] : v1[j & 31]);
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.dq_staged);
+                if (warp == 12) {                              // one thread hands the half tiles to the copy engine
+                    if (lane == 0) {
+                        if (batch == 1) {                      // first half: read by now, or soon
+                            bulk_wait_group_read0();
+                            mbar_arrive(&sm.w_empty[st]);
+                        }
+                        ok = mbar_wait(&sm.dq_staged, uint32_t(batch), abort_flag, p.status, kBwdDqStaged);
+                        const int rows = min(64, q_left - 64 * batch);
+#ifndef FPT_DIAG_NO_RED
+                        if (ok && rows > 0) bulk_reduce_add_f32_1d(tile_dst + 64 * batch * kDim, stage, uint32_t(rows) * (kDim * 4u));
+#endif
+                        bulk_commit_group();
+                        if (ok && batch == 1) {
+                            bulk_wait_group_read0();
+                            mbar_arrive(&sm.ds_free);
+                        }
+                    }
+                    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+                    if (!ok) break;
+                }
+            }
+        }
+        if (warp == 12 && lane == 0) bulk_wait_group0();
+      }
     } else {
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+      if constexpr (kFusedDq) asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+      else asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
       if (!skip) {
         // ------------------------------------------------------------------ score-mod warps
         const int quarter = warp & 3, half = (warp - 4) >> 2;
@@ -622,6 +715,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 // dS^T also goes to shared memory for the partial dQ product: this thread's key row, the 64 queries of its
                 // column half = one 128-byte line of panel `half`, chunk c stored at position c ^ (row % 8) (the 128-byte
                 // swizzle of the operand layout); made visible to the tensor core's reads by the proxy fence
+                // (the tile also stages half of the previous step's partial dQ tile on its way out)
+                if (t > 0) ok = mbar_wait(&sm.ds_free, uint32_t(t - 1) & 1u, abort_flag, p.status, kBwdDsFree);
+                if (!ok) break;
                 const uint32_t line = smem_u32(sm.ds) + uint32_t(half) * kPanelB + uint32_t(r) * 128u;
 #pragma unroll
                 for (int c = 0; c < 8; ++c)
@@ -634,48 +730,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full);
             FPT_BTRACE(half, 6);
-            if constexpr (kFusedDq) {
-                // read the partial dQ tile (rows = the streamed tile's queries, this warp's 32 lanes x its 64 columns of
-                // the head dimension) out of the dP tile's columns, release them, and add the values into the fp32 buffer
-                ok = mbar_wait(&sm.dq_full, uint32_t(t) & 1u, abort_flag, p.status, kBwdDqFull);
-                if (!ok) break;
-                tc_fence_after_sync();
-                uint32_t dq[64];
-                tmem_ld_32x32b_x32(t_own, reinterpret_cast<uint32_t(&)[32]>(dq[0]));
-                tmem_ld_32x32b_x32(t_own + 32, reinterpret_cast<uint32_t(&)[32]>(dq[32]));
-                tmem_ld_wait();
-                tc_fence_before_sync();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.dq_read);
-#ifndef FPT_DIAG_NO_RED            // tuning builds only: what the pass costs without the global additions
-                // The warp stages its 32 rows x 64 columns in shared memory, 32 columns per round, in its own 32 lines of the
-                // dS^T tile (4 KiB nobody else touches; the product that read them is complete), swizzled like the operand
-                // layout (chunk c of line l at position c ^ (l % 8)).  Measured: per-lane red.global.add.v4 straight from
-                // registers (every lane a different row) 472 TFLOP/s on the causal soft-cap workload, the same additions
-                // coalesced through this staging 566, the tiled reduction below 567: all three run into the L2's fp32
-                // reduction rate (~2.1 TB/s), which is what bounds the single-pass form.
-                const uint32_t scratch = smem_u32(sm.ds) + uint32_t(half) * kPanelB + uint32_t(32 * quarter) * 128u;
-                const int q_first = c0 - 64 * half + 32 * quarter;       // query of this warp's lane 0
-                // the warp's 32 rows x 32 columns of a round leave as ONE tiled reduction (the copy engine adds the box
-                // into the fp32 tensor, undoing the swizzle; rows beyond the sequence are dropped by the tensor map)
-#pragma unroll
-                for (int round = 0; round < 2; ++round) {
-#pragma unroll
-                    for (int c = 0; c < 8; ++c)
-                        sts128(scratch + uint32_t(lane) * 128u + (uint32_t(c ^ (lane & 7)) << 4), dq[32 * round + 4 * c],
-                               dq[32 * round + 4 * c + 1], dq[32 * round + 4 * c + 2], dq[32 * round + 4 * c + 3]);
-                    fence_async_shared();
-                    __syncwarp();
-                    if (lane == 0 && q_first < p.seq) {
-                        tma_reduce_add_4d(&map_dq, sm.ds + half * kPanelB + (32 * quarter) * 128, 64 * half + 32 * round, q_first,
-                                          stream_head0 + g, b);
-                        bulk_commit_group();
-                        bulk_wait_group_read0();      // the lines are free again (next round, next step's dS^T)
-                    }
-                    __syncwarp();
-                }
-#endif
-            }
         }
         if (ok && n_inner > 0) {
             ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
@@ -840,18 +894,8 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     static_assert(sizeof(BwdSmemT<true>) <= 227 * 1024, "shared memory budget of the single-pass form (no alignment slack)");
     const unsigned tiles = unsigned(seq_pad / kTile);
     float* dq_accum = fused ? reinterpret_cast<float*>(static_cast<char*>(workspace) + bwd_planes_bytes(batch, seq, q_heads)) : nullptr;
-    CUtensorMap map_dq = map_q;          // only the single-pass form reads it
-    if (fused) {
-        // fp32 [B, Hq, S, 128] as (dim, seq, head, batch); a box is 32 columns (one 128-byte line) x 32 query rows.  Head-major,
-        // so that the 128 x 128 tile a block adds into is one contiguous 64 KiB: with the rows of a tile 16 KiB apart
-        // ([B, S, Hq, 128], 32 heads) the additions of a tile fell on few L2 slices
-        const uint64_t dims[4] = {uint64_t(kDim), uint64_t(seq), uint64_t(q_heads), uint64_t(batch)};
-        const uint64_t strides[3] = {uint64_t(kDim) * 4, uint64_t(seq) * kDim * 4, uint64_t(seq) * q_heads * kDim * 4};
-        const uint32_t box[4] = {32u, 32u, 1u, 1u};
-        if (int rc = make_tensor_map_f32_4d(&map_dq, dq_accum, dims, strides, box)) return rc;
-    }
     auto launch = [&](auto kernel, size_t smem, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my,
-                      const CUtensorMap& mu, const CUtensorMap& mw, uint16_t* o0, uint16_t* o1) {
+                      const CUtensorMap& mu, const CUtensorMap& mw, uint16_t* o0, uint16_t* o1, unsigned threads = kBwdThreads) {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
         BwdParams pp = p;
@@ -859,7 +903,7 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
         pp.out1 = o1;
         pp.dq_accum = dq_accum;
         const dim3 grid = pp.rows_fastest ? dim3{tiles, heads, unsigned(batch)} : dim3{heads, tiles, unsigned(batch)};
-        kernel<<<grid, kBwdThreads, smem, stream>>>(mx, my, mu, mw, map_dq, pp);
+        kernel<<<grid, threads, smem, stream>>>(mx, my, mu, mw, pp);
         return cuda_status(cudaGetLastError());
     };
     // Measured: with full (unmasked) attention over many heads, row tiles fastest is 10-12 % faster (B=2, S=16384, 32 heads:
@@ -879,7 +923,7 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
             cudaError_t e = cudaMemsetAsync(dq_accum, 0, size_t(n) * sizeof(float), stream);
             if (e != cudaSuccess) return int(e);
             if (int rc = launch(attention_bwd_kernel<M, 2, G, E, EK>, sizeof(BwdSmemT<true>), unsigned(kv_heads), map_k, map_v,
-                                map_q, map_do, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv)))
+                                map_q, map_do, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), kBwdThreadsFused))
                 return rc;
             int64_t grid = (n / 8 + 255) / 256;
             const int64_t cap = int64_t(dev.sm_count) * 16;

@@ -94,14 +94,11 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gmem_sr
                  : "memory");
 }
 
-// 4-D tiled reduction shared -> global (element-wise add of the box into the tensor, in the tensor map's data type),
-// tracked by the issuing thread's bulk groups.  Elements of the box outside the tensor are dropped.  The innermost
-// coordinate times the element size must be a multiple of 16 bytes and no coordinate may be negative.
-__device__ __forceinline__ void tma_reduce_add_4d(const CUtensorMap* map, const void* smem_src, int c0, int c1, int c2, int c3) {
-    asm volatile(
-        "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-        :: "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(smem_src)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-        : "memory");
+// Untiled reduce-add of fp32 values, shared -> global (both addresses 16-byte aligned, size a multiple of 16 bytes), tracked
+// by the issuing thread's bulk groups.
+__device__ __forceinline__ void bulk_reduce_add_f32_1d(float* gmem_dst, const void* smem_src, uint32_t bytes) {
+    asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;"
+                 :: "l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // until the shared-memory sources of this thread's bulk groups have been read (they may then be overwritten)
@@ -340,8 +337,4 @@ __host__ __device__ constexpr uint32_t umma_idesc_bf16(uint32_t m, uint32_t n, u
 // box = {64, box_rows, 1, 1}, 128-byte swizzle, zero fill outside the tensor.  Returns an fpt status.
 int make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
                             uint32_t box_rows);
-// The same over an fp32 tensor with a caller-chosen box whose innermost extent is 32 elements (one 128-byte line).
-int make_tensor_map_f32_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-                           const uint32_t box[4]);
-
 }  // namespace fpt

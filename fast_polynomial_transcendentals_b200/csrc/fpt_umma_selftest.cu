@@ -47,24 +47,6 @@ int make_tensor_map_bf16_4d(CUtensorMap* map, const void* base, const uint64_t d
     return r == CUDA_SUCCESS ? FPT_OK : FPT_ERR_BAD_SIZE;
 }
 
-int make_tensor_map_f32_4d(CUtensorMap* map, const void* base, const uint64_t dims[4], const uint64_t strides_bytes[3],
-                           const uint32_t box[4]) {
-    EncodeTiledFn encode = encode_tiled_fn();
-    if (!encode) return FPT_ERR_NO_DEVICE;
-    if (reinterpret_cast<uintptr_t>(base) & 15u) return FPT_ERR_MISALIGNED;
-    for (int i = 0; i < 3; ++i)
-        if (strides_bytes[i] & 15u) return FPT_ERR_MISALIGNED;
-    if (box[0] * 4u != 128u) return FPT_ERR_BAD_SIZE;       // one 128-byte line per row: the span of the swizzle
-    cuuint64_t gdim[4] = {dims[0], dims[1], dims[2], dims[3]};
-    cuuint64_t gstride[3] = {strides_bytes[0], strides_bytes[1], strides_bytes[2]};
-    cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
-    cuuint32_t estride[4] = {1u, 1u, 1u, 1u};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), gdim, gstride, b, estride,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? FPT_OK : FPT_ERR_BAD_SIZE;
-}
-
 namespace {
 
 using namespace sm100;

@@ -328,11 +328,11 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
  *          one for dK and dV, each recomputing S and dP: 7 matrix products per tile pair, no atomics, deterministic;
  *        one pass (workspace >= fpt_attention_bwd_fused_workspace_bytes, in every mode, AND tuning key
  *          "attention_bwd_fused" set to 1; the default is 0): the dK / dV blocks also form the partial dQ of every
- *          query tile they stream (5 products per tile pair) and add it into an fp32 [B, S, Hq, 128] buffer inside
- *          the workspace with tiled reduce-add copies; a last pass scales and rounds it to bf16.  The order of the fp32
+ *          query tile they stream (5 products per tile pair) and add it into an fp32 [B, Hq, S, 128] buffer inside
+ *          the workspace with reduce-add copies; a last pass scales and rounds it to bf16.  The order of the fp32
  *          additions is not fixed, so the last bit of a dQ element can differ from run to run (dK and dV stay
- *          deterministic).  Measured on B200: 0.92-1.09x the two-pass form (the L2's fp32 reduction rate bounds it),
- *          which is why it is opt-in. */
+ *          deterministic), which is why it is opt-in.  Measured on B200: 1.13-1.17x the two-pass form with a score-mod
+ *          (soft-cap, sigmoid), 0.95-1.0x in plain soft-max. */
 enum { FPT_SOFTCAP_GRAD_ANALYTICAL = 0, FPT_SOFTCAP_GRAD_ONE_MINUS_T2 = 1 };
 int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
 int64_t fpt_attention_bwd_fused_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
