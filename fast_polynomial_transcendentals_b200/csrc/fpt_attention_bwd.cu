@@ -1,23 +1,18 @@
 // Attention backward for sm_100a, same score-mods as the forward (soft-capped softmax, direct sigmoid, plain softmax).
 //
-// Two launches of one kernel template, each deterministic and free of atomics (S and dP are recomputed in both):
+// Two forms.  The single-pass form (attention_bwd_pipelined_kernel, further down: dK, dV and dQ in one kernel, 5 matrix
+// products per tile pair, dQ accumulated in an fp32 buffer by reduce-add copies) and the two-pass form described here:
+// two launches of one kernel template, each deterministic and free of atomics (S and dP are recomputed in both):
 //   WHICH = 0  dQ:      one CTA per (batch, query head, 128 query rows), loops over key tiles
 //                       S = Q K^T,  dP = dO V^T,  dS = f(S, dP),  dQ += dS K
 //   WHICH = 1  dK, dV:  one CTA per (batch, kv head, 128 keys), loops over the query heads of its group and their
 //                       query tiles;  S^T = K Q^T,  dP^T = V dO^T,  dV += P^T dO,  dK += dS^T Q
-//   WHICH = 2  dK, dV and dQ in one pass (5 matrix products per tile pair instead of 7): the dK / dV block also forms
-//                       dQ_partial^T = K^T dS^T for the streamed query tile (K is the block's fixed tile, read as an
-//                       MN-major A operand; dS^T goes to shared memory as well and is read back as an MN-major B
-//                       operand), a fourth warpgroup reads the partial tile out of tensor memory, stages it in shared
-//                       memory that the step no longer needs and adds it into an fp32 dQ buffer with untiled reduce-add
-//                       copies (one partial per key tile: the order of the additions, and so the last bits of dQ, is not
-//                       fixed from run to run); a last pass scales and rounds the buffer to bf16
 // Written once in terms of "fixed" tiles X, Y (loaded once) and "streamed" tiles U, W (2-stage ring):
 //   S = X U^T and dP = Y W^T (both operands K-major from shared memory),
 //   acc0 += dS U and (WHICH = 1) acc1 += P W, with P / dS read from tensor memory and U / W as MN-major operands.
-// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, (WHICH = 2) warps 12..15 read-out of the partial dQ
-// tiles, warps 4..11 score-mod warps: thread = one tensor-memory lane (row of the fixed tile), warps w and w+4 share a
-// lane quarter and split the 128 columns in halves (the backward has no row reduction, so the split needs no exchange).
+// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
+// tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
+// (the backward has no row reduction, so the split needs no exchange).
 // Tensor memory: S is never overwritten (each score-mod warp writes its bf16 dS and P words over its own 64 columns of
 // the dP tile), so the S product of the next step runs under the score-mod of the current one; dQ also double-buffers
 // dP.  A pre-pass writes lse * log2(e) and delta = rowsum(dO * O) into a caller-provided workspace.
@@ -41,33 +36,27 @@ constexpr int kRing = 2;
 constexpr uint32_t kPanelB = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
 constexpr uint32_t kTileB = 2 * kPanelB;
 constexpr int kBwdThreads = 384;
-constexpr int kBwdThreadsFused = 512;   // the single-pass form adds a warpgroup that reads the partial dQ tiles out
+constexpr int kBwdThreadsFused = 512;   // the single-pass form has a fourth warpgroup, which reads the partial dQ tiles out
 constexpr float kLog2eB = 1.4426950408889634f;
 
-template <bool WITH_DS_TILE>
-struct BwdSmemT {
+struct BwdSmem {
     alignas(1024) uint8_t x[kTileB];
     alignas(1024) uint8_t y[kTileB];
     alignas(1024) uint8_t u[kRing][kTileB];
     alignas(1024) uint8_t w[kRing][kTileB];
-    alignas(1024) uint8_t ds[WITH_DS_TILE ? kTileB : 16];   // WHICH = 2: dS^T [keys x queries] bf16, two swizzled panels
     alignas(16) float lse2[kRing][kTile];      // WHICH >= 1: per streamed query column
     alignas(16) float delta[kRing][kTile];
     alignas(8) uint64_t xy_full;
     uint64_t uw_full[kRing], uw_empty[kRing];
     uint64_t s_full, ld_done, p_full, acc_done;
-    uint64_t dq_full[2], dq_read;              // WHICH = 2: half of the partial dQ tile complete / all read out of tensor memory
-    uint64_t dq_staged;                        // WHICH = 2: one half of the partial dQ tile is in shared memory (4 warps)
-    uint64_t w_empty[kRing], ds_free;          // WHICH = 2: the copy engine has read the half staged in w[st] / in ds
     uint32_t tmem_base;
     uint32_t abort_flag;
 };
-using BwdSmem = BwdSmemT<false>;
 
 struct BwdParams {
     uint16_t* out0;        // dQ (WHICH 0) or dK (WHICH 1): contiguous [B, S, H, D]
     uint16_t* out1;        // dV (WHICH 1, 2)
-    float* dq_accum;       // WHICH 2: fp32 [B, Hq, S, D], zeroed before the launch
+    float* dq_accum;       // single-pass form: fp32 [B, Hq, S, D], zeroed before the launch
     const float* lse2;     // workspace plane 0: [B, Hq, S rounded up to whole tiles]
     const float* delta;    // workspace plane 1
     int batch, seq, q_heads, kv_heads;
@@ -102,7 +91,7 @@ struct BwdParams {
 #define FPT_BTRACE(slot, tag) do { } while (0)
 #endif
 
-enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone, kBwdDqFull, kBwdDqRead, kBwdDqStaged, kBwdWEmpty, kBwdDsFree };
+enum : uint32_t { kBwdXY = 1, kBwdUwEmpty, kBwdUwFull, kBwdSFull, kBwdPFull, kBwdAccDone, kBwdLdDone };
 
 // 16 bytes to shared memory (address from smem_u32)
 __device__ __forceinline__ void sts32(uint32_t addr, uint32_t a) {
@@ -300,8 +289,6 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
 // 32 columns of bf16 dS pairs, then 32 columns of bf16 P pairs; the products read K steps 0..3 from the first half and
 // 4..7 from the second.
 constexpr uint32_t kColS = 0, kColDp = 128, kColAcc1 = 384;
-// WHICH 2 uses the WHICH 1 layout; its partial dQ tile (128 fp32 columns) takes the place of the dP tile once the products
-// that read dS and P from it have been issued, and is read out before dP of the next step is issued.
 template <int WHICH>
 struct Cols {
     static constexpr uint32_t acc0 = WHICH == 0 ? 384u : 256u;
@@ -314,19 +301,15 @@ struct Cols {
 // every EMU columns of a score-mod warp's 64 take exp2_full_x2<EK> on the FMA pipe (reference: exp2_emu_freq_bwd,
 // src/sfu_repro/fa4.py:724-752).
 template <int MODE, int WHICH, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
-__global__ void __launch_bounds__(WHICH == 2 ? kBwdThreadsFused : kBwdThreads, 1)
+__global__ void __launch_bounds__(kBwdThreads, 1)
 attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                      const __grid_constant__ CUtensorMap map_u, const __grid_constant__ CUtensorMap map_w,
                      const BwdParams p) {
     constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;    // no normalisation: neither lse nor delta
-    constexpr bool kKeysFixed = WHICH >= 1;                   // rows of the fixed tiles are keys, streamed tiles are queries
-    constexpr bool kFusedDq = WHICH == 2;
-    using Smem = BwdSmemT<kFusedDq>;
+    constexpr bool kKeysFixed = WHICH == 1;                   // rows of the fixed tiles are keys, streamed tiles are queries
+    using Smem = BwdSmem;
     extern __shared__ uint8_t smem_raw[];
-    // WHICH 2 fills the shared memory of an SM to the last kilobyte and cannot afford alignment slack: the host gives it
-    // exactly sizeof(Smem) and the base is checked below (a misaligned base is reported, not used)
-    Smem& sm = *reinterpret_cast<Smem*>(kFusedDq ? reinterpret_cast<uintptr_t>(smem_raw)
-                                                 : (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    Smem& sm = *reinterpret_cast<Smem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     // Blocks are handed out x fastest: with row tiles on x the blocks that run together stream the same head's tiles,
     // which then come from L2; with heads on x they share their loop length (causal).
@@ -362,18 +345,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         mbar_init(&sm.ld_done, 8);      // one arrive per score-mod warp: its S and dP values are in registers
         mbar_init(&sm.p_full, 8);       // one arrive per score-mod warp: its P and dS words are in tensor memory
         mbar_init(&sm.acc_done, 1);
-        mbar_init(&sm.dq_full[0], 1);
-        mbar_init(&sm.dq_full[1], 1);
-        mbar_init(&sm.dq_staged, 4);
-        mbar_init(&sm.w_empty[0], 1);
-        mbar_init(&sm.w_empty[1], 1);
-        mbar_init(&sm.ds_free, 1);
-        mbar_init(&sm.dq_read, 4);      // one arrive per read-out warp: its rows of the partial dQ tile are in registers
         sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
-        if (kFusedDq && (smem_u32(&sm) & 1023u) != 0u) {      // the operand layouts need 1024-byte alignment
-            sm.abort_flag = 1u;
-            atomicCAS(p.status, 0u, 0x80000000u | kBwdXY | 0x100u);
-        }
         mbar_fence_init();
         tma_prefetch_descriptor(&map_x);
         tma_prefetch_descriptor(&map_y);
@@ -391,12 +363,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
     const bool skip = sm.abort_flag != 0u;
 
     // Register budget (see the forward kernel): 384 threads start at 168 and move 128 x (168 - 80) to the score-mod warps
-    // (208 each); the single-pass form's 512 threads start at 128: 128 x (128 - 56) + 128 x (128 - 104) released,
-    // 256 x (176 - 128) taken.
-    static_assert(128 * (128 - 56) + 128 * (128 - 104) >= 256 * (176 - 128), "register hand-over of the single-pass form");
+    // (208 each).
     if (warp < 4) {
-      if constexpr (kFusedDq) asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
-      else asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 80;");
       if (skip || warp >= 2) {
         // warps 2 and 3 only hold registers for the others
       } else if (warp == 0) {
@@ -425,10 +394,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     bulk_load_1d(sm.lse2[st], p.lse2 + off, kTile * 4u, &sm.uw_full[st]);
                     bulk_load_1d(sm.delta[st], p.delta + off, kTile * 4u, &sm.uw_full[st]);
                 }
-                if constexpr (kFusedDq) {      // the read-out warps staged half a partial dQ tile in this stage's W tile
-                    if (t >= kRing) ok = mbar_wait(&sm.w_empty[st], ph ^ 1u, abort_flag, p.status, kBwdWEmpty);
-                    if (!ok) break;
-                }
                 tma_load_4d(sm.w[st], &map_w, &sm.uw_full[st], 0, r0, sh, b);
                 tma_load_4d(sm.w[st] + kPanelB, &map_w, &sm.uw_full[st], 64, r0, sh, b);
             }
@@ -438,7 +403,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         if (lane == 0) {
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
-            constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kDim, kTile / 2, 1, 1);   // both operands MN-major (partial dQ)
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
             constexpr uint32_t kColAcc0 = Cols<WHICH>::acc0;
             auto dp_col = [](int t) { return Cols<WHICH>::dp(t); };
@@ -512,34 +476,10 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                         umma_ts_words(tmem + kColAcc1, tmem + dp_col(t) + 64u * (kk >> 2) + 32u + 8u * (kk & 3),
                                       w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 }
-                if constexpr (kFusedDq) {
-                    // partial dQ of the streamed query tile, transposed: K^T (head dimension x keys: the fixed tile read as an
-                    // MN-major A operand) times dS^T (the dS^T tile in shared memory read as an MN-major B operand), into
-                    // the dP tile's columns, which the two products above have finished reading by the time this one runs
-                    // (in order).  Lanes of the result are the head dimension and columns the queries.  Issued as two
-                    // products of 64 queries (one panel of the dS^T tile each) with a commit of their own, so that the
-                    // read-out of the first half runs under the second product.
-                    const uint32_t ds_mn = umma_smem_desc_lo(smem_u32(sm.ds), kPanelB);
-                    const uint32_t x_mn = umma_smem_desc_lo(smem_u32(sm.x), kPanelB);
-#pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                        for (int kk = 0; kk < 8; ++kk)
-                            umma_ss_words(tmem + dp_col(t) + uint32_t(64 * h), x_mn + uint32_t(kk) * (2048u / 16u),
-                                          ds_mn + uint32_t(h) * (kPanelB / 16u) + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mnmn, kk > 0);
-                        umma_commit(&sm.dq_full[h]);
-                    }
-                }
                 umma_commit(&sm.uw_empty[st]);
                 FPT_BTRACE(2, 13);
-                // [C] WHICH 1, 2: the one dP tile is free again once the products above have read it (same thread, in
-                // order) and, WHICH 2, once the read-out warps have taken the partial dQ tile out of it
+                // [C] WHICH 1: the one dP tile is free again once the products above have read it (same thread, in order)
                 if constexpr (kKeysFixed) {
-                    if constexpr (kFusedDq) {
-                        ok = mbar_wait(&sm.dq_read, uint32_t(t) & 1u, abort_flag, p.status, kBwdDqRead);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                    }
                     if (more) {
                         issue_dp(nw_k, t + 1);
                         umma_commit(&sm.s_full);
@@ -550,75 +490,8 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
             if (ok) umma_commit(&sm.acc_done);
         }
       }
-    } else if (kFusedDq && warp >= 12) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
-      if (!skip) {
-        // ------------------------------------------------------------------ read-out warps of the single-pass form
-        // Off the serial chain of a step: once the partial dQ product of step t is complete (and with it every product
-        // that read the streamed tiles of ring stage st and the dS^T tile), this warpgroup copies the tile out of tensor
-        // memory into shared memory, 512 bytes per query as in the fp32 buffer: queries 0..63 over the stage's dO tile,
-        // 64..127 over the dS^T tile (32 KiB each), releases the dP tile's columns, and hands each half to the copy engine
-        // as one untiled reduce-add.  The product is held transposed (lane = head-dimension index, column = query), so a
-        // warp's store of one register covers 128 consecutive bytes of shared memory.  The dO tile goes back to the
-        // producer and the dS^T tile to the score-mod warps (who write it at the end of the next step's pass) once the
-        // copy engine has read them; the Q tile of the stage, which the next S product but one wants first, is not used.
-        const int quarter = warp & 3;
-        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
-        bool ok = true;
-        for (int t = 0; t < n_inner && ok; ++t) {
-            const int st = t % kRing;
-            const int g = t / per_head;
-            const int q_tile0 = (first_inner + (t - g * per_head)) * kTile;      // first query of the streamed tile
-            float* tile_dst = p.dq_accum + ((int64_t(b) * p.q_heads + stream_head0 + g) * p.seq + q_tile0) * kDim;
-            const int q_left = p.seq - q_tile0;                                  // queries of this tile that exist
-#pragma unroll
-            for (int batch = 0; batch < 2; ++batch) {          // 64 queries at a time
-                ok = mbar_wait(&sm.dq_full[batch], uint32_t(t) & 1u, abort_flag, p.status, kBwdDqFull);
-                if (!ok) break;
-                tc_fence_after_sync();
-                uint32_t v0[32], v1[32];
-                tmem_ld_32x32b_x32(tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * batch), v0);
-                tmem_ld_32x32b_x32(tmem + lane_base + Cols<WHICH>::dp(t) + uint32_t(64 * batch + 32), v1);
-                tmem_ld_wait();
-                if (batch == 1) {                              // everything is in registers: the columns are free
-                    tc_fence_before_sync();
-                    __syncwarp();
-                    if (lane == 0) mbar_arrive(&sm.dq_read);
-                }
-                uint8_t* stage = batch == 0 ? sm.w[st] : sm.ds;
-                const uint32_t mine = smem_u32(stage) + uint32_t(32 * quarter + lane) * 4u;
-#pragma unroll
-                for (int j = 0; j < 64; ++j) sts32(mine + uint32_t(j) * (kDim * 4u), j < 32 ? v0[j & 31] : v1[j & 31]);
-                fence_async_shared();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.dq_staged);
-                if (warp == 12) {                              // one thread hands the half tiles to the copy engine
-                    if (lane == 0) {
-                        if (batch == 1) {                      // first half: read by now, or soon
-                            bulk_wait_group_read0();
-                            mbar_arrive(&sm.w_empty[st]);
-                        }
-                        ok = mbar_wait(&sm.dq_staged, uint32_t(batch), abort_flag, p.status, kBwdDqStaged);
-                        const int rows = min(64, q_left - 64 * batch);
-#ifndef FPT_DIAG_NO_RED
-                        if (ok && rows > 0) bulk_reduce_add_f32_1d(tile_dst + 64 * batch * kDim, stage, uint32_t(rows) * (kDim * 4u));
-#endif
-                        bulk_commit_group();
-                        if (ok && batch == 1) {
-                            bulk_wait_group_read0();
-                            mbar_arrive(&sm.ds_free);
-                        }
-                    }
-                    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-                    if (!ok) break;
-                }
-            }
-        }
-        if (warp == 12 && lane == 0) bulk_wait_group0();
-      }
     } else {
-      if constexpr (kFusedDq) asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
-      else asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
       if (!skip) {
         // ------------------------------------------------------------------ score-mod warps
         const int quarter = warp & 3, half = (warp - 4) >> 2;
@@ -711,19 +584,6 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 tmem_st_32x32b_x32(t_own, dsw);
                 if constexpr (kKeysFixed) tmem_st_32x32b_x32(t_own + 32, pw);
             }
-            if constexpr (kFusedDq) {
-                // dS^T also goes to shared memory for the partial dQ product: this thread's key row, the 64 queries of its
-                // column half = one 128-byte line of panel `half`, chunk c stored at position c ^ (row % 8) (the 128-byte
-                // swizzle of the operand layout); made visible to the tensor core's reads by the proxy fence
-                // (the tile also stages half of the previous step's partial dQ tile on its way out)
-                if (t > 0) ok = mbar_wait(&sm.ds_free, uint32_t(t - 1) & 1u, abort_flag, p.status, kBwdDsFree);
-                if (!ok) break;
-                const uint32_t line = smem_u32(sm.ds) + uint32_t(half) * kPanelB + uint32_t(r) * 128u;
-#pragma unroll
-                for (int c = 0; c < 8; ++c)
-                    sts128(line + (uint32_t(c ^ (r & 7)) << 4), dsw[4 * c], dsw[4 * c + 1], dsw[4 * c + 2], dsw[4 * c + 3]);
-                fence_async_shared();
-            }
             FPT_BTRACE(half, 5);
             tmem_st_wait();
             tc_fence_before_sync();
@@ -746,6 +606,430 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
                         tmem_ld_32x32b_x32(tmem + lane_base + (acc == 0 ? Cols<WHICH>::acc0 : kColAcc1) + uint32_t(64 * half + 32 * c), v);
+                        tmem_ld_wait();
+#pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 o;
+                            o.x = pack_bf16(__uint_as_float(v[q4 * 8 + 0]) * f, __uint_as_float(v[q4 * 8 + 1]) * f);
+                            o.y = pack_bf16(__uint_as_float(v[q4 * 8 + 2]) * f, __uint_as_float(v[q4 * 8 + 3]) * f);
+                            o.z = pack_bf16(__uint_as_float(v[q4 * 8 + 4]) * f, __uint_as_float(v[q4 * 8 + 5]) * f);
+                            o.w = pack_bf16(__uint_as_float(v[q4 * 8 + 6]) * f, __uint_as_float(v[q4 * 8 + 7]) * f);
+                            if (real_row) reinterpret_cast<uint4*>(dst + 32 * c)[q4] = o;
+                        }
+                    }
+                }
+            }
+        }
+      }
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+
+// ---- single pass, pipelined by half steps ---------------------------------------------------------------------------------
+// dK, dV and dQ in one kernel (5 matrix products per tile pair), one CTA per (batch, kv head, 128 keys), looping over the
+// query heads of the group and their query tiles like WHICH = 1.  A step (one streamed 128-query tile) is cut into two
+// half steps of 64 queries; S^T and dP^T of a half step take 64 tensor-memory columns each and there are two buffers of
+// each (S 0..127, dP 128..255, dK 256..383, dV 384..511), so the tensor core computes S^T and dP^T of half step n + 1 and
+// the three products of half step n - 1 while the score-mod warps work on half step n: the serial chain of the one-buffer
+// forms (dP product -> score-mod -> products -> dP of the next step) is gone and a step costs what the slower of the two
+// sides costs, not their sum.
+//   S^T_n  = K Q_n^T, dP^T_n = V dO_n^T                      (M = 128 keys, N = 64 queries, both operands K-major)
+//   dK += dS^T_n Q_n, dV += P^T_n dO_n                        (A from tensor memory, B MN-major; 4 K steps of 16 queries)
+//   dQ^T_n = K^T dS^T_n                                       (M = 128 head-dim, N = 64 queries, both operands MN-major; into
+//                                                              the dP buffer of the half step, behind the two products that
+//                                                              read dS and P from it)
+// Roles: warp 0 TMA producer, warp 1 issuer (one thread), warps 4..11 score-mod (thread = key row; warps w and w + 4 split
+// the 64 queries of a half step), warps 12..15 read-out of dQ^T (lane = head-dim index): registers, then 32 queries at a time
+// through one of three 16 KiB staging buffers (512 bytes per query, the layout of the head-major fp32 buffer) into one
+// untiled reduce-add copy each, two of them in flight while the third buffer fills (a copy of 16 KiB takes ~1700 cycles
+// from issue to "read", whatever its size: waiting for each one before staging the next made the read-out the slowest
+// role).  The streamed Q / dO ring holds half tiles (64 queries), three stages, which is what leaves room for the staging.  The dS^T tile in shared memory is one panel ([keys x 64 queries]) reused by every half step: it is
+// written at the end of a score-mod pass, long after the dQ^T product of the half step before has read it.
+constexpr int kPipeRing = 3;       // half-tile stages of the streamed Q / dO ring
+constexpr int kPipeStaging = 3;    // staging buffers of the read-out: two reduce-add copies in flight while the third fills
+constexpr uint32_t kHalfPanelB = kPanelB / 2;   // one [64 rows x 64 bf16] panel
+
+struct PipeSmem {
+    alignas(1024) uint8_t x[kTileB];            // K tile
+    alignas(1024) uint8_t y[kTileB];            // V tile
+    alignas(1024) uint8_t u[kPipeRing][kPanelB];    // Q half tiles (64 queries): two panels of [64 rows x 64 bf16]
+    alignas(1024) uint8_t w[kPipeRing][kPanelB];    // dO half tiles
+    alignas(1024) uint8_t ds[kPanelB];              // dS^T of one half step, bf16, swizzled
+    alignas(1024) uint8_t stage[kPipeStaging][kPanelB];   // 32 queries x 128 fp32 of a partial dQ tile on their way out
+    alignas(16) float lse2[kPipeRing][kTile / 2];
+    alignas(16) float delta[kPipeRing][kTile / 2];
+    alignas(8) uint64_t xy_full;
+    uint64_t uw_full[kPipeRing], uw_empty[kPipeRing];
+    uint64_t sd_full[2];      // S^T and dP^T of a half step are complete (per buffer)
+    uint64_t ld_done[2];      // 8 warps: they are in registers (the S buffer is free)
+    uint64_t p_full[2];       // 8 warps: dS and P words in tensor memory, dS^T in shared memory
+    uint64_t dq_full[2];      // dQ^T of a half step complete (and with it everything that read the dS^T tile)
+    uint64_t dq_read[2];      // 4 warps: dQ^T in registers (the dP buffer is free)
+    uint64_t staged[kPipeStaging];       // 4 warps: 32 queries are in the staging buffer
+    uint64_t stage_free[kPipeStaging];   // the copy engine has read them
+    uint64_t acc_done;
+    uint32_t tmem_base;
+    uint32_t abort_flag;
+};
+
+enum : uint32_t { kPipeSdFull = 16, kPipeLdDone, kPipePFull, kPipeDqFull, kPipeDqRead, kPipeStaged, kPipeStageFree };
+
+template <int MODE, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
+__global__ void __launch_bounds__(kBwdThreadsFused, 1)
+attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                               const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
+                               const BwdParams p) {
+    constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;
+    constexpr int kHalf = kTile / 2;                      // queries of a half step
+    extern __shared__ uint8_t smem_raw[];
+    // the shared memory of an SM is filled to the last kilobyte: no alignment slack, the base is checked below
+    PipeSmem& sm = *reinterpret_cast<PipeSmem*>(smem_raw);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int head = p.rows_fastest ? blockIdx.y : blockIdx.x;                  // kv head
+    const int tile = p.rows_fastest ? blockIdx.x : blockIdx.y;                  // key tile
+    const int b = blockIdx.z;
+    const int total = (p.seq + kTile - 1) / kTile;
+    const int seq_pad = total * kTile;
+    const bool ragged = (p.seq % kTile) != 0;
+    const int group = p.q_heads / p.kv_heads;
+    const int row0 = tile * kTile;                        // first key
+    const int first_inner = p.causal ? tile : 0;          // first query tile
+    const int per_head = total - first_inner;
+    const int n_inner = per_head * group;
+    const int n_half = 2 * n_inner;
+    const int stream_head0 = head * group;
+    volatile uint32_t* abort_flag = &sm.abort_flag;
+#ifdef FPT_ATTN_TRACE
+    constexpr int WHICH = 2;
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8 || warp == 12);
+    int trace_n = 0;
+#endif
+
+    if (threadIdx.x == 0) {
+        mbar_init(&sm.xy_full, 1);
+        for (int st = 0; st < kPipeRing; ++st) {
+            mbar_init(&sm.uw_full[st], 1);
+            mbar_init(&sm.uw_empty[st], 1);
+        }
+        for (int i = 0; i < kPipeStaging; ++i) {
+            mbar_init(&sm.staged[i], 4);
+            mbar_init(&sm.stage_free[i], 1);
+        }
+        for (int h = 0; h < 2; ++h) {
+            mbar_init(&sm.sd_full[h], 1);
+            mbar_init(&sm.ld_done[h], 8);
+            mbar_init(&sm.p_full[h], 8);
+            mbar_init(&sm.dq_full[h], 1);
+            mbar_init(&sm.dq_read[h], 4);
+        }
+        mbar_init(&sm.acc_done, 1);
+        sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
+        if ((smem_u32(&sm) & 1023u) != 0u) {              // the operand layouts need 1024-byte alignment
+            sm.abort_flag = 1u;
+            atomicCAS(p.status, 0u, 0x80000000u | kBwdXY | 0x100u);
+        }
+        mbar_fence_init();
+        tma_prefetch_descriptor(&map_k);
+        tma_prefetch_descriptor(&map_v);
+        tma_prefetch_descriptor(&map_q);
+        tma_prefetch_descriptor(&map_do);
+    }
+    if (warp == 1) {
+        tmem_alloc(&sm.tmem_base, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const uint32_t tmem = sm.tmem_base;
+    const bool skip = sm.abort_flag != 0u;
+    constexpr uint32_t kS = 0, kDp = 128, kAcc0 = 256, kAcc1 = 384;   // tensor-memory columns
+
+    // 512 threads start at 128 registers: 128 x (128 - 56) + 128 x (128 - 104) released, 256 x (176 - 128) taken
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (skip || warp >= 2) {
+        // warps 2 and 3 only hold registers for the others
+      } else if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            mbar_arrive_expect_tx(&sm.xy_full, 2 * kTileB);
+            tma_load_4d(sm.x, &map_k, &sm.xy_full, 0, row0, head, b);
+            tma_load_4d(sm.x + kPanelB, &map_k, &sm.xy_full, 64, row0, head, b);
+            tma_load_4d(sm.y, &map_v, &sm.xy_full, 0, row0, head, b);
+            tma_load_4d(sm.y + kPanelB, &map_v, &sm.xy_full, 64, row0, head, b);
+            bool ok = true;
+            for (int n = 0; n < n_half && ok; ++n) {      // one ring stage per half step: 64 queries of Q and of dO
+                const int t = n >> 1, h = n & 1, st = n % kPipeRing;
+                const uint32_t ph = uint32_t(n / kPipeRing) & 1u;
+                if (n >= kPipeRing) ok = mbar_wait(&sm.uw_empty[st], ph ^ 1u, abort_flag, p.status, kBwdUwEmpty);
+                if (!ok) break;
+                const int g = t / per_head;
+                const int r0 = (first_inner + (t - g * per_head)) * kTile + kHalf * h;   // may lie past the end: zero fill
+                const int sh = stream_head0 + g;
+                const uint32_t vec_bytes = !kSigmoidMode ? 2u * kHalf * 4u : 0u;
+                mbar_arrive_expect_tx(&sm.uw_full[st], kTileB + vec_bytes);
+                tma_load_4d(sm.u[st], &map_q, &sm.uw_full[st], 0, r0, sh, b);
+                tma_load_4d(sm.u[st] + kHalfPanelB, &map_q, &sm.uw_full[st], 64, r0, sh, b);
+                tma_load_4d(sm.w[st], &map_do, &sm.uw_full[st], 0, r0, sh, b);
+                tma_load_4d(sm.w[st] + kHalfPanelB, &map_do, &sm.uw_full[st], 64, r0, sh, b);
+                if (vec_bytes) {   // per-query vectors of the 64 queries (the planes are padded to whole tiles)
+                    const int64_t off = (int64_t(b) * p.q_heads + sh) * seq_pad + r0;
+                    bulk_load_1d(sm.lse2[st], p.lse2 + off, kHalf * 4u, &sm.uw_full[st]);
+                    bulk_load_1d(sm.delta[st], p.delta + off, kHalf * 4u, &sm.uw_full[st]);
+                }
+            }
+        }
+      } else {
+        // ------------------------------------------------------------------ UMMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kHalf, 0, 0);     // S^T, dP^T: both operands K-major
+            constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);      // dK, dV: B operand MN-major
+            constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kDim, kHalf, 1, 1);    // dQ^T: both operands MN-major
+            constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
+            const uint32_t x_k = umma_smem_desc_lo(smem_u32(sm.x), 16), y_k = umma_smem_desc_lo(smem_u32(sm.y), 16);
+            const uint32_t x_mn = umma_smem_desc_lo(smem_u32(sm.x), kPanelB);
+            const uint32_t ds_mn = umma_smem_desc_lo(smem_u32(sm.ds), kPanelB);
+            // K-major operand, K step kk of 16 head-dim elements: panel kk / 4 (16 KiB apart in the fixed tiles, 8 KiB in the
+            // half tiles of the ring), 32 bytes per step inside the 128-byte line
+            auto issue_s = [&](int st, int h) {
+                const uint32_t u_k = umma_smem_desc_lo(smem_u32(sm.u[st]), 16);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t in = uint32_t(kk & 3) * 32u;
+                    umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
+                                  u_k + (uint32_t(kk >> 2) * kHalfPanelB + in) / 16u, desc_hi, idesc_kk, kk > 0);
+                }
+            };
+            auto issue_dp = [&](int st, int h) {
+                const uint32_t w_k = umma_smem_desc_lo(smem_u32(sm.w[st]), 16);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk) {
+                    const uint32_t in = uint32_t(kk & 3) * 32u;
+                    umma_ss_words(tmem + kDp + uint32_t(kHalf * h), y_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
+                                  w_k + (uint32_t(kk >> 2) * kHalfPanelB + in) / 16u, desc_hi, idesc_kk, kk > 0);
+                }
+            };
+            bool ok = mbar_wait(&sm.xy_full, 0, abort_flag, p.status, kBwdXY);
+            if (ok && n_half > 0) ok = mbar_wait(&sm.uw_full[0], 0, abort_flag, p.status, kBwdUwFull);
+            if (ok && n_half > 0) {
+                tc_fence_after_sync();
+                issue_s(0, 0);
+                issue_dp(0, 0);
+                umma_commit(&sm.sd_full[0]);
+            }
+            for (int n = 0; n < n_half && ok; ++n) {
+                const int t = n >> 1, h = n & 1, st = n % kPipeRing;
+                FPT_BTRACE(2, 10);
+                if (n + 1 < n_half) {
+                    // S^T and dP^T of the next half step: its S buffer is free once the score-mod warps have loaded the half
+                    // step before this one, its dP buffer once the read-out warps have taken that half step's dQ^T out
+                    const int n1 = n + 1, h1 = n1 & 1, st1 = n1 % kPipeRing;
+                    ok = mbar_wait(&sm.uw_full[st1], uint32_t(n1 / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
+                    if (!ok) break;
+                    if (n >= 1) {
+                        ok = mbar_wait(&sm.ld_done[h1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeLdDone);
+                        if (!ok) break;
+                    }
+                    tc_fence_after_sync();
+                    FPT_BTRACE(2, 11);
+                    issue_s(st1, h1);
+                    FPT_BTRACE(2, 12);
+                    if (n >= 1) {
+                        ok = mbar_wait(&sm.dq_read[h1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeDqRead);
+                        if (!ok) break;
+                        tc_fence_after_sync();
+                    }
+                    FPT_BTRACE(2, 13);
+                    issue_dp(st1, h1);
+                    umma_commit(&sm.sd_full[h1]);
+                    FPT_BTRACE(2, 14);
+                }
+                // dS, P (tensor memory) and dS^T (shared memory) of this half step are written
+                ok = mbar_wait(&sm.p_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipePFull);
+                if (!ok) break;
+                tc_fence_after_sync();
+                FPT_BTRACE(2, 15);
+                const uint32_t u_mn = umma_smem_desc_lo(smem_u32(sm.u[st]), kHalfPanelB);
+                const uint32_t w_mn = umma_smem_desc_lo(smem_u32(sm.w[st]), kHalfPanelB);
+                const uint32_t a_base = tmem + kDp + uint32_t(kHalf * h);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)          // dK += dS^T Q: 16 queries per K step; warp group c = k / 2 owns 32 columns
+                    umma_ts_words(tmem + kAcc0, a_base + 32u * (k >> 1) + 8u * (k & 1), u_mn + uint32_t(k) * (2048u / 16u),
+                                  desc_hi, idesc_mn, n > 0 || k > 0);
+#pragma unroll
+                for (int k = 0; k < 4; ++k)          // dV += P^T dO
+                    umma_ts_words(tmem + kAcc1, a_base + 32u * (k >> 1) + 16u + 8u * (k & 1), w_mn + uint32_t(k) * (2048u / 16u),
+                                  desc_hi, idesc_mn, n > 0 || k > 0);
+#pragma unroll
+                for (int kk = 0; kk < 8; ++kk)       // dQ^T = K^T dS^T over the dP buffer (behind the two products above)
+                    umma_ss_words(a_base, x_mn + uint32_t(kk) * (2048u / 16u), ds_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
+                                  idesc_mnmn, kk > 0);
+                umma_commit(&sm.dq_full[h]);
+                FPT_BTRACE(2, 16);
+                umma_commit(&sm.uw_empty[st]);       // every product that reads the stage is behind this commit
+            }
+            if (ok) umma_commit(&sm.acc_done);
+        }
+      }
+    } else if (warp >= 12) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+      if (!skip) {
+        // ------------------------------------------------------------------ read-out warps
+        const int quarter = warp & 3;
+        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        bool ok = true;
+        int m = 0;                                          // chunks of 32 queries staged so far
+        for (int n = 0; n < n_half && ok; ++n) {
+            const int t = n >> 1, h = n & 1;
+            const int g = t / per_head;
+            const int q0 = (first_inner + (t - g * per_head)) * kTile + kHalf * h;     // first query of the half step
+            ok = mbar_wait(&sm.dq_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipeDqFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            FPT_BTRACE(3, 20);
+            uint32_t v0[32], v1[32];
+            tmem_ld_32x32b_x32(tmem + lane_base + kDp + uint32_t(kHalf * h), v0);
+            tmem_ld_32x32b_x32(tmem + lane_base + kDp + uint32_t(kHalf * h + 32), v1);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.dq_read[h]);
+            FPT_BTRACE(3, 21);
+            float* dst = p.dq_accum + ((int64_t(b) * p.q_heads + stream_head0 + g) * p.seq + q0) * kDim;
+#pragma unroll
+            for (int a = 0; a < 2; ++a, ++m) {
+                // Buffer m % 3; the copy that last read it is chunk m - 3.  The issuing thread keeps two copies in flight:
+                // after committing chunk m it waits until at most two groups are unread (chunk m - 2 has been read) and
+                // frees that chunk's buffer, which is the one chunk m + 1 fills.
+                const int buf = m % kPipeStaging;
+                const uint32_t use = uint32_t(m / kPipeStaging);
+                if (m >= kPipeStaging) ok = mbar_wait(&sm.stage_free[buf], (use & 1u) ^ 1u, abort_flag, p.status, kPipeStageFree);
+                if (!ok) break;
+                const uint32_t mine = smem_u32(sm.stage[buf]) + uint32_t(32 * quarter + lane) * 4u;
+#pragma unroll
+                for (int j = 0; j < 32; ++j) sts32(mine + uint32_t(j) * (kDim * 4u), a == 0 ? v0[j] : v1[j]);
+                fence_async_shared();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(&sm.staged[buf]);
+                if (warp == 12) {
+                    if (lane == 0) {
+                        ok = mbar_wait(&sm.staged[buf], use & 1u, abort_flag, p.status, kPipeStaged);
+                        const int rows = min(32, p.seq - q0 - 32 * a);
+#ifndef FPT_DIAG_NO_RED
+                        if (ok && rows > 0) bulk_reduce_add_f32_1d(dst + 32 * a * kDim, sm.stage[buf], uint32_t(rows) * (kDim * 4u));
+#endif
+                        bulk_commit_group();
+                        bulk_wait_group_read<kPipeStaging - 1>();
+                        if (ok && m >= kPipeStaging - 1) mbar_arrive(&sm.stage_free[(m + 1) % kPipeStaging]);
+                    }
+                    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+                    if (!ok) break;
+                    FPT_BTRACE(3, 22 + a);
+                }
+            }
+        }
+        if (warp == 12 && lane == 0) bulk_wait_group0();
+      }
+    } else {
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+      if (!skip) {
+        // ------------------------------------------------------------------ score-mod warps
+        const int quarter = warp & 3, c32 = (warp - 4) >> 2;        // lane quarter; which 32 of a half step's 64 queries
+        const int r = 32 * quarter + lane;                           // key row of the tile = tensor-memory lane
+        const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        bool ok = true;
+        for (int n = 0; n < n_half && ok; ++n) {
+            const int t = n >> 1, h = n & 1, st = n % kPipeRing;
+            ok = mbar_wait(&sm.sd_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipeSdFull);
+            if (!ok) break;
+            tc_fence_after_sync();
+            FPT_BTRACE(c32, 2);
+            // This warp owns columns [32 c32, 32 c32 + 32) of the half step's S and dP buffers; it writes its 16 dS words over
+            // the first 16 and its 16 P words over the last 16 of its own dP columns, so nobody's loads are in the way.
+            uint32_t dv[32], sv[32];
+            const uint32_t t_own = tmem + lane_base + kDp + uint32_t(kHalf * h + 32 * c32);
+            tmem_ld_32x32b_x32(t_own, dv);
+            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32 * c32), sv);
+            tmem_ld_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.ld_done[h]);
+            FPT_BTRACE(c32, 3);
+            if (!kSigmoidMode)                 // the per-query vectors arrived on this barrier (complete by now)
+                ok = mbar_wait(&sm.uw_full[st], uint32_t(n / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
+            if (!ok) break;
+            const int g = t / per_head;
+            const int tile_c0 = (first_inner + (t - g * per_head)) * kTile;        // first query of the streamed tile
+            const int in_tile = kHalf * h + 32 * c32;                              // this warp's first query inside it
+            const int c0 = tile_c0 + in_tile;
+            const bool diagonal = (p.causal && tile_c0 == row0) || (ragged && (tile_c0 + kTile > p.seq || row0 + kTile > p.seq));
+            const uint32_t lse_addr = smem_u32(&sm.lse2[st][32 * c32]), delta_addr = smem_u32(&sm.delta[st][32 * c32]);
+            uint32_t pw[16], dsw[16];
+            auto columns = [&](auto masked) {
+#pragma unroll
+                for (int quad = 0; quad < 8; ++quad) {       // four queries = two pairs per 128-bit shared load
+                    const int cq = 4 * quad;
+                    float lv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+                    if (!kSigmoidMode) {
+                        lds128(lse_addr + 4u * cq, lv);
+                        lds128(delta_addr + 4u * cq, dl);
+                    }
+#pragma unroll
+                    for (int h2 = 0; h2 < 2; ++h2) {
+                        const int c = cq + 2 * h2;
+                        bool m0 = false, m1 = false;
+                        if constexpr (decltype(masked)::value) {
+                            const int key = row0 + r, query0 = c0 + c, query1 = c0 + c + 1;
+                            m0 = (p.causal && key > query0) || key >= p.seq || query0 >= p.seq;
+                            m1 = (p.causal && key > query1) || key >= p.seq || query1 >= p.seq;
+                        }
+                        const bool routed = EMU > 0 && ((c / 2) % (EMU > 0 ? EMU / 2 : 1)) < 2;
+                        score_pair<MODE, GRAD, EK>(p, __uint_as_float(sv[c]), __uint_as_float(sv[c + 1]), __uint_as_float(dv[c]),
+                                                   __uint_as_float(dv[c + 1]), lv[2 * h2], lv[2 * h2 + 1], dl[2 * h2], dl[2 * h2 + 1],
+                                                   m0, m1, routed, pw[2 * quad + h2], dsw[2 * quad + h2]);
+                    }
+                }
+            };
+            if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
+            else columns(std::false_type{});
+            FPT_BTRACE(c32, 4);
+            tmem_st_32x32b_x16(t_own, dsw);
+            tmem_st_32x32b_x16(t_own + 16, pw);
+            // dS^T also goes to shared memory for the dQ^T product: this thread's key row, its 32 queries = chunks 4 c32 ..
+            // 4 c32 + 3 of the row's 128-byte line, chunk j stored at position j ^ (row % 8) (the 128-byte swizzle of the
+            // operand layout).  The tile is free once the dQ^T product of the half step before is complete.
+            if (n > 0) ok = mbar_wait(&sm.dq_full[h ^ 1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeDqFull);
+            if (!ok) break;
+            FPT_BTRACE(c32, 5);
+            const uint32_t line = smem_u32(sm.ds) + uint32_t(r) * 128u;
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                sts128(line + (uint32_t((4 * c32 + j) ^ (r & 7)) << 4), dsw[4 * j], dsw[4 * j + 1], dsw[4 * j + 2], dsw[4 * j + 3]);
+            fence_async_shared();
+            tmem_st_wait();
+            tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.p_full[h]);
+            FPT_BTRACE(c32, 6);
+        }
+        if (ok && n_half > 0) {
+            ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
+            if (ok) {
+                tc_fence_after_sync();
+                const int64_t off = ((int64_t(b) * p.seq + row0 + r) * p.kv_heads + head) * kDim + 64 * c32;
+                const bool real_row = row0 + r < p.seq;
+#pragma unroll
+                for (int acc = 0; acc < 2; ++acc) {
+                    const float f = acc == 0 ? p.scale : 1.0f;
+                    uint16_t* dst = (acc == 0 ? p.out0 : p.out1) + off;
+#pragma unroll
+                    for (int c = 0; c < 2; ++c) {
+                        uint32_t v[32];
+                        tmem_ld_32x32b_x32(tmem + lane_base + (acc == 0 ? kAcc0 : kAcc1) + uint32_t(64 * c32 + 32 * c), v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
@@ -829,16 +1113,21 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     DeviceInfo dev;
     if (int rc = current_device_info(&dev)) return rc;
 
-    auto make_map = [&](CUtensorMap* map, const void* base, const int64_t* st, int64_t heads) {
+    auto make_map = [&](CUtensorMap* map, const void* base, const int64_t* st, int64_t heads, uint32_t box_rows = kTile) {
         const uint64_t dims[4] = {uint64_t(head_dim), uint64_t(seq), uint64_t(heads), uint64_t(batch)};
         const uint64_t strides[3] = {uint64_t(st[1]) * 2, uint64_t(st[2]) * 2, uint64_t(st[0]) * 2};
-        return make_tensor_map_bf16_4d(map, base, dims, strides, kTile);
+        return make_tensor_map_bf16_4d(map, base, dims, strides, box_rows);
     };
     CUtensorMap map_q, map_k, map_v, map_do;
     if (int rc = make_map(&map_q, q, q_strides, q_heads)) return rc;
     if (int rc = make_map(&map_k, k, k_strides, kv_heads)) return rc;
     if (int rc = make_map(&map_v, v, v_strides, kv_heads)) return rc;
     if (int rc = make_map(&map_do, dout, dout_strides, q_heads)) return rc;
+    CUtensorMap map_q_half = map_q, map_do_half = map_do;      // 64-row boxes: the pipelined single-pass form streams half tiles
+    if (fused) {
+        if (int rc = make_map(&map_q_half, q, q_strides, q_heads, kTile / 2)) return rc;
+        if (int rc = make_map(&map_do_half, dout, dout_strides, q_heads, kTile / 2)) return rc;
+    }
 
     float* lse2 = static_cast<float*>(workspace);
     const int64_t seq_pad = (seq + kTile - 1) / kTile * kTile;
@@ -891,7 +1180,7 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
     p.sigmoid_add = float(log2_n);
 
     static_assert(sizeof(BwdSmem) + 1024 <= 227 * 1024, "shared memory budget");
-    static_assert(sizeof(BwdSmemT<true>) <= 227 * 1024, "shared memory budget of the single-pass form (no alignment slack)");
+    static_assert(sizeof(PipeSmem) <= 227 * 1024, "shared memory budget of the single-pass form (no alignment slack)");
     const unsigned tiles = unsigned(seq_pad / kTile);
     float* dq_accum = fused ? reinterpret_cast<float*>(static_cast<char*>(workspace) + bwd_planes_bytes(batch, seq, q_heads)) : nullptr;
     auto launch = [&](auto kernel, size_t smem, unsigned heads, const CUtensorMap& mx, const CUtensorMap& my,
@@ -922,8 +1211,8 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
             const int64_t n = batch * seq * q_heads * kDim;
             cudaError_t e = cudaMemsetAsync(dq_accum, 0, size_t(n) * sizeof(float), stream);
             if (e != cudaSuccess) return int(e);
-            if (int rc = launch(attention_bwd_kernel<M, 2, G, E, EK>, sizeof(BwdSmemT<true>), unsigned(kv_heads), map_k, map_v,
-                                map_q, map_do, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), kBwdThreadsFused))
+            if (int rc = launch(attention_bwd_pipelined_kernel<M, G, E, EK>, sizeof(PipeSmem), unsigned(kv_heads), map_k, map_v,
+                                map_q_half, map_do_half, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), kBwdThreadsFused))
                 return rc;
             int64_t grid = (n / 8 + 255) / 256;
             const int64_t cap = int64_t(dev.sm_count) * 16;

@@ -20,7 +20,7 @@ std::atomic<int> g_blocks_per_sm{0};
 std::atomic<int> g_streaming{-1};
 std::atomic<int> g_attention_split{1};
 std::atomic<int> g_attention_raster{-1};
-std::atomic<int> g_attention_bwd_fused{0};
+std::atomic<int> g_attention_bwd_fused{1};
 std::atomic<int> g_gate_up_tile_rows{0};
 std::atomic<int> g_attention_cta_pair{0};
 std::atomic<int> g_gate_up_cta_pair{-1};

@@ -101,6 +101,9 @@ __device__ __forceinline__ void bulk_reduce_add_f32_1d(float* gmem_dst, const vo
                  :: "l"(gmem_dst), "r"(smem_u32(smem_src)), "r"(bytes) : "memory");
 }
 __device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// until at most N of this thread's bulk groups still have shared-memory sources to read
+template <int N>
+__device__ __forceinline__ void bulk_wait_group_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
 // until the shared-memory sources of this thread's bulk groups have been read (they may then be overwritten)
 __device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 // until this thread's bulk groups have completed altogether

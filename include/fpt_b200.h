@@ -324,15 +324,16 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
  *      the derivative of the polynomial itself (zero where the input is clamped or the output saturated), or
  *      1 - t^2 of its value.  status as in the forward.
  *      Two forms, chosen by the size of the workspace the caller passes:
+ *        one pass (workspace >= fpt_attention_bwd_fused_workspace_bytes, in every mode, unless tuning key
+ *          "attention_bwd_fused" is set to 0): one kernel for dK, dV and dQ, 5 matrix products per tile pair.  The block
+ *          of a key tile also forms the partial dQ of every query tile it streams and adds it into an fp32
+ *          [B, Hq, S, 128] buffer inside the workspace with reduce-add copies; a last pass scales and rounds it to bf16.
+ *          The order of those fp32 additions is not fixed, so the last bit of a dQ element can differ from run to run
+ *          (dK and dV are deterministic, and the same bits as in the two-pass form).  Measured on B200: 1.12-1.32x the
+ *          two-pass form;
  *        two passes (workspace >= fpt_attention_bwd_workspace_bytes; none needed in the sigmoid modes): one launch for dQ,
- *          one for dK and dV, each recomputing S and dP: 7 matrix products per tile pair, no atomics, deterministic;
- *        one pass (workspace >= fpt_attention_bwd_fused_workspace_bytes, in every mode, AND tuning key
- *          "attention_bwd_fused" set to 1; the default is 0): the dK / dV blocks also form the partial dQ of every
- *          query tile they stream (5 products per tile pair) and add it into an fp32 [B, Hq, S, 128] buffer inside
- *          the workspace with reduce-add copies; a last pass scales and rounds it to bf16.  The order of the fp32
- *          additions is not fixed, so the last bit of a dQ element can differ from run to run (dK and dV stay
- *          deterministic), which is why it is opt-in.  Measured on B200: 1.13-1.17x the two-pass form with a score-mod
- *          (soft-cap, sigmoid), 0.95-1.0x in plain soft-max. */
+ *          one for dK and dV, each recomputing S and dP: 7 matrix products per tile pair, no atomics, deterministic.
+ *          A caller who needs run-to-run identical dQ passes the smaller workspace or sets the tuning key to 0. */
 enum { FPT_SOFTCAP_GRAD_ANALYTICAL = 0, FPT_SOFTCAP_GRAD_ONE_MINUS_T2 = 1 };
 int64_t fpt_attention_bwd_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
 int64_t fpt_attention_bwd_fused_workspace_bytes(int64_t batch, int64_t seq, int64_t q_heads);
@@ -384,8 +385,8 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * fastest, -1 (default) the measured-best choice per kernel (forward and backward: rows when nothing is masked and the
  * streamed tensors exceed 64 MB, heads otherwise);
  * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
- * key "attention_bwd_fused": 1 lets the attention backward take its one-pass form when the workspace allows, 0 (default)
- * keeps the deterministic two-pass form;
+ * key "attention_bwd_fused": 1 (default) lets the attention backward take its one-pass form when the workspace allows, 0
+ * keeps the deterministic two-pass form whatever the workspace;
  * key "attention_cta_pair": 1 runs the attention forward on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one
  * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
  * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits; 0.85-1.00x the

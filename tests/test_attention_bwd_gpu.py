@@ -159,7 +159,7 @@ def test_backward_with_routed_software_exponential(fpt, cuda, backend, freq, bou
 @pytest.mark.parametrize("case", CASES)
 def test_single_pass_backward_matches_the_cpu_restatement_and_the_two_pass_form(fpt, cuda, oracle, case):
     """The one-pass form (dK / dV blocks also produce the partial dQ tiles, added in fp32; 5 matrix products instead of
-    7): same tolerance against the float64 restatement; dK and dV are the same bits as the two-pass form (same
+    7; the default when the workspace holds the fp32 dQ buffer): same tolerance against the float64 restatement; dK and dV are the same bits as the two-pass form (same
     arithmetic, same order); dQ differs from it by the rounding of one fp32 sum at most (one bf16 unit in the last place
     of the largest gradients)."""
     import torch
@@ -174,13 +174,12 @@ def test_single_pass_backward_matches_the_cpu_restatement_and_the_two_pass_form(
     dout = torch.randn(B, S, Hq, D, device=cuda, generator=g).to(torch.bfloat16)
     scale = 1.0 / math.sqrt(D)
     out, lse = forward(fpt, cuda, q, k, v, mode, causal, scale, softcap, log2_n)
+    # the smaller workspace selects the two-pass form, the larger one the single-pass form (tuning key at its default, 1)
     two = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad)
     lib = fpt.load()
-    assert lib.fpt_set_tuning(b"attention_bwd_fused", 1) == 0          # the one-pass form is opt-in
-    try:
-        one = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
-    finally:
-        assert lib.fpt_set_tuning(b"attention_bwd_fused", 0) == 0
+    value = ctypes.c_int(-1)
+    assert lib.fpt_get_tuning(b"attention_bwd_fused", ctypes.byref(value)) == 0 and value.value == 1
+    one = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
     _, _, want_dq, want_dk, want_dv = attention_bwd.attention_fwd_bwd(bits(q), bits(k), bits(v), bits(dout), mode, causal, scale,
                                                                       softcap, log2_n, softcap_grad)
     close(one[0], want_dq, "dq")
@@ -189,8 +188,12 @@ def test_single_pass_backward_matches_the_cpu_restatement_and_the_two_pass_form(
     assert torch.equal(one[1], two[1]) and torch.equal(one[2], two[2]), "dK / dV of the two forms must be the same bits"
     gap = (one[0].float() - two[0].float()).abs().max()
     assert float(gap) <= 2.0 ** -7 * float(two[0].float().abs().max()), float(gap)
-    # with the tuning key off (the default) the same call, large workspace and all, takes the two-pass form: bits equal
-    forced = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
+    # with the tuning key off the same call, large workspace and all, takes the two-pass form: bits equal
+    assert lib.fpt_set_tuning(b"attention_bwd_fused", 0) == 0
+    try:
+        forced = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
+    finally:
+        assert lib.fpt_set_tuning(b"attention_bwd_fused", 1) == 0
     assert all(torch.equal(a, b) for a, b in zip(forced, two))
 
 
