@@ -488,8 +488,8 @@ def _b200_flash_attn_bwd(q, k, v, out, dout, lse, softmax_scale=None, causal=Tru
     needs_forward = mode not in (1, 4)
     if needs_forward and (out is None or lse is None):
         raise RuntimeError("soft-max attention backward needs the forward's out and lse")
-    # The single-pass form by default (5 matrix products, fp32 dQ buffer in the workspace; like the reference's FA4 backward
-    # it accumulates dQ with additions whose order is not fixed, so the last bit of dQ is not reproducible from run to run).
+    # The single-pass form by default (5 matrix products, fp32 dQ buffer in the workspace; it accumulates dQ with additions
+    # whose order is not fixed, so the last bit of dQ is not reproducible from run to run).
     # FPT_ATTENTION_BWD_SINGLE_PASS=0 asks for the deterministic two-pass form: the smaller workspace selects it.
     if os.environ.get("FPT_ATTENTION_BWD_SINGLE_PASS", "1").strip().lower() not in ("0", "false", "no", "off"):
         need = int(_lib.load().fpt_attention_bwd_fused_workspace_bytes(batch, seq, q_heads))
