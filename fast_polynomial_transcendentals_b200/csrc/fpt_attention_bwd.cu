@@ -632,15 +632,16 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 // dK, dV and dQ in one kernel (5 matrix products per tile pair), one CTA per (batch, kv head, 128 keys), looping over the
 // query heads of the group and their query tiles like WHICH = 1.  A step (one streamed 128-query tile) is cut into two
 // half steps of 64 queries; S^T and dP^T of a half step take 64 tensor-memory columns each and there are two buffers of
-// each (S 0..127, dP 128..255, dK 256..383, dV 384..511), so the tensor core computes S^T and dP^T of half step n + 1 and
-// the three products of half step n - 1 while the score-mod warps work on half step n: the serial chain of the one-buffer
+// each (S 0..127, dP 128..255, dK 256..383, dV 384..511), so the tensor core computes the three products of half step n and
+// then S^T and dP^T of half step n + 2 while the score-mod warps work on half step n + 1: the serial chain of the one-buffer
 // forms (dP product -> score-mod -> products -> dP of the next step) is gone and a step costs what the slower of the two
-// sides costs, not their sum.
+// sides costs, not their sum.  dQ^T of a half step is written over its S buffer (in registers since the start of its
+// score-mod pass), so the dP buffer is free for half step n + 2 as soon as the products that read dS and P from it have been
+// issued, and the wait for the read-out of dQ^T falls under the dP^T product.
 //   S^T_n  = K Q_n^T, dP^T_n = V dO_n^T                      (M = 128 keys, N = 64 queries, both operands K-major)
 //   dK += dS^T_n Q_n, dV += P^T_n dO_n                        (A from tensor memory, B MN-major; 4 K steps of 16 queries)
 //   dQ^T_n = K^T dS^T_n                                       (M = 128 head-dim, N = 64 queries, both operands MN-major; into
-//                                                              the dP buffer of the half step, behind the two products that
-//                                                              read dS and P from it)
+//                                                              the S buffer of the half step)
 // Roles: warp 0 TMA producer, warp 1 issuer (one thread), warps 4..11 score-mod (thread = key row; warps w and w + 4 split
 // the 64 queries of a half step), warps 12..15 read-out of dQ^T (lane = head-dim index): registers, then 32 queries at a time
 // through one of three 16 KiB staging buffers (512 bytes per query, the layout of the head-major fp32 buffer) into one
@@ -664,10 +665,9 @@ struct PipeSmem {
     alignas(8) uint64_t xy_full;
     uint64_t uw_full[kPipeRing], uw_empty[kPipeRing];
     uint64_t sd_full[2];      // S^T and dP^T of a half step are complete (per buffer)
-    uint64_t ld_done[2];      // 8 warps: they are in registers (the S buffer is free)
     uint64_t p_full[2];       // 8 warps: dS and P words in tensor memory, dS^T in shared memory
     uint64_t dq_full[2];      // dQ^T of a half step complete (and with it everything that read the dS^T tile)
-    uint64_t dq_read[2];      // 4 warps: dQ^T in registers (the dP buffer is free)
+    uint64_t dq_read[2];      // 4 warps: dQ^T in registers (the S buffer it was written over is free)
     uint64_t staged[kPipeStaging];       // 4 warps: 32 queries are in the staging buffer
     uint64_t stage_free[kPipeStaging];   // the copy engine has read them
     uint64_t acc_done;
@@ -675,7 +675,7 @@ struct PipeSmem {
     uint32_t abort_flag;
 };
 
-enum : uint32_t { kPipeSdFull = 16, kPipeLdDone, kPipePFull, kPipeDqFull, kPipeDqRead, kPipeStaged, kPipeStageFree };
+enum : uint32_t { kPipeSdFull = 16, kPipePFull, kPipeDqFull, kPipeDqRead, kPipeStaged, kPipeStageFree };
 
 template <int MODE, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
 __global__ void __launch_bounds__(kBwdThreadsFused, 1)
@@ -720,7 +720,6 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(&sm.sd_full[h], 1);
-            mbar_init(&sm.ld_done[h], 8);
             mbar_init(&sm.p_full[h], 8);
             mbar_init(&sm.dq_full[h], 1);
             mbar_init(&sm.dq_read[h], 4);
@@ -814,40 +813,18 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 }
             };
             bool ok = mbar_wait(&sm.xy_full, 0, abort_flag, p.status, kBwdXY);
-            if (ok && n_half > 0) ok = mbar_wait(&sm.uw_full[0], 0, abort_flag, p.status, kBwdUwFull);
-            if (ok && n_half > 0) {
+            // S^T and dP^T of the first two half steps (both buffers are free)
+            for (int n = 0; n < 2 && n < n_half && ok; ++n) {
+                ok = mbar_wait(&sm.uw_full[n], 0, abort_flag, p.status, kBwdUwFull);
+                if (!ok) break;
                 tc_fence_after_sync();
-                issue_s(0, 0);
-                issue_dp(0, 0);
-                umma_commit(&sm.sd_full[0]);
+                issue_s(n, n);
+                issue_dp(n, n);
+                umma_commit(&sm.sd_full[n]);
             }
             for (int n = 0; n < n_half && ok; ++n) {
                 const int t = n >> 1, h = n & 1, st = n % kPipeRing;
                 FPT_BTRACE(2, 10);
-                if (n + 1 < n_half) {
-                    // S^T and dP^T of the next half step: its S buffer is free once the score-mod warps have loaded the half
-                    // step before this one, its dP buffer once the read-out warps have taken that half step's dQ^T out
-                    const int n1 = n + 1, h1 = n1 & 1, st1 = n1 % kPipeRing;
-                    ok = mbar_wait(&sm.uw_full[st1], uint32_t(n1 / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
-                    if (!ok) break;
-                    if (n >= 1) {
-                        ok = mbar_wait(&sm.ld_done[h1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeLdDone);
-                        if (!ok) break;
-                    }
-                    tc_fence_after_sync();
-                    FPT_BTRACE(2, 11);
-                    issue_s(st1, h1);
-                    FPT_BTRACE(2, 12);
-                    if (n >= 1) {
-                        ok = mbar_wait(&sm.dq_read[h1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeDqRead);
-                        if (!ok) break;
-                        tc_fence_after_sync();
-                    }
-                    FPT_BTRACE(2, 13);
-                    issue_dp(st1, h1);
-                    umma_commit(&sm.sd_full[h1]);
-                    FPT_BTRACE(2, 14);
-                }
                 // dS, P (tensor memory) and dS^T (shared memory) of this half step are written
                 ok = mbar_wait(&sm.p_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipePFull);
                 if (!ok) break;
@@ -865,12 +842,31 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                     umma_ts_words(tmem + kAcc1, a_base + 32u * (k >> 1) + 16u + 8u * (k & 1), w_mn + uint32_t(k) * (2048u / 16u),
                                   desc_hi, idesc_mn, n > 0 || k > 0);
 #pragma unroll
-                for (int kk = 0; kk < 8; ++kk)       // dQ^T = K^T dS^T over the dP buffer (behind the two products above)
-                    umma_ss_words(a_base, x_mn + uint32_t(kk) * (2048u / 16u), ds_mn + uint32_t(kk) * (2048u / 16u), desc_hi,
-                                  idesc_mnmn, kk > 0);
+                for (int kk = 0; kk < 8; ++kk)       // dQ^T = K^T dS^T over the S buffer of the half step (in registers long ago)
+                    umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_mn + uint32_t(kk) * (2048u / 16u),
+                                  ds_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mnmn, kk > 0);
                 umma_commit(&sm.dq_full[h]);
                 FPT_BTRACE(2, 16);
                 umma_commit(&sm.uw_empty[st]);       // every product that reads the stage is behind this commit
+                if (n + 2 < n_half) {
+                    // S^T and dP^T of the half step after the next one, into this half step's buffers.  The dP buffer is free
+                    // as soon as the two products above have read dS and P from it (issued before, executed in order); the S
+                    // buffer once the read-out warps have taken dQ^T out of it, which happens under the dP^T product.
+                    const int n2 = n + 2, st2 = n2 % kPipeRing;
+                    ok = mbar_wait(&sm.uw_full[st2], uint32_t(n2 / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    FPT_BTRACE(2, 11);
+                    issue_dp(st2, h);
+                    FPT_BTRACE(2, 12);
+                    ok = mbar_wait(&sm.dq_read[h], uint32_t(t) & 1u, abort_flag, p.status, kPipeDqRead);
+                    if (!ok) break;
+                    tc_fence_after_sync();
+                    FPT_BTRACE(2, 13);
+                    issue_s(st2, h);
+                    umma_commit(&sm.sd_full[h]);
+                    FPT_BTRACE(2, 14);
+                }
             }
             if (ok) umma_commit(&sm.acc_done);
         }
@@ -892,8 +888,8 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             tc_fence_after_sync();
             FPT_BTRACE(3, 20);
             uint32_t v0[32], v1[32];
-            tmem_ld_32x32b_x32(tmem + lane_base + kDp + uint32_t(kHalf * h), v0);
-            tmem_ld_32x32b_x32(tmem + lane_base + kDp + uint32_t(kHalf * h + 32), v1);
+            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h), v0);
+            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32), v1);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
@@ -955,9 +951,6 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             tmem_ld_32x32b_x32(t_own, dv);
             tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32 * c32), sv);
             tmem_ld_wait();
-            tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&sm.ld_done[h]);
             FPT_BTRACE(c32, 3);
             if (!kSigmoidMode)                 // the per-query vectors arrived on this barrier (complete by now)
                 ok = mbar_wait(&sm.uw_full[st], uint32_t(n / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
