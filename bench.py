@@ -1370,10 +1370,12 @@ def run_profile_case(args):
         run = lambda: _lib.check("fpt_attention_fwd", lib.fpt_attention_fwd(
             o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
             arr(o), mode, causal, 1.0 / math.sqrt(D), 50.0, 12, status.data_ptr(), stream))
-    elif case in ("attn_bwd_softmax", "attn_bwd_softcap", "attn_bwd_sigmoid"):
+    elif case in ("attn_bwd_softmax", "attn_bwd_softcap", "attn_bwd_sigmoid",
+                  "attn_bwd_single_pass_softmax", "attn_bwd_single_pass_softcap", "attn_bwd_single_pass_sigmoid"):
         import ctypes
         B, S, Hq, Hk, D = 1, n, 32, 8, 128      # --profile-n is the sequence length; no mask
-        mode = {"attn_bwd_softcap": 0, "attn_bwd_sigmoid": 1, "attn_bwd_softmax": 2}[case]
+        single_pass = "_single_pass_" in case   # the workspace decides: with the fp32 dQ buffer the single-pass kernel runs
+        mode = {"softcap": 0, "sigmoid": 1, "softmax": 2}[case.rsplit("_", 1)[1]]
         mk = lambda h: torch.randn(B, S, h, D, device=device, generator=g).to(torch.bfloat16)
         q, k, v, dout = mk(Hq), mk(Hk), mk(Hk), mk(Hq)
         o = torch.empty_like(q)
@@ -1384,7 +1386,7 @@ def run_profile_case(args):
             o.data_ptr(), lse.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), B, S, Hq, Hk, D, arr(q), arr(k), arr(v),
             arr(o), mode, 0, 1.0 / math.sqrt(D), 50.0, 12, status.data_ptr(), stream))
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        need = int(lib.fpt_attention_bwd_workspace_bytes(B, S, Hq))
+        need = int((lib.fpt_attention_bwd_fused_workspace_bytes if single_pass else lib.fpt_attention_bwd_workspace_bytes)(B, S, Hq))
         workspace = torch.empty(need, dtype=torch.uint8, device=device)
         run = lambda: _lib.check("fpt_attention_bwd", lib.fpt_attention_bwd(
             dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), dout.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), o.data_ptr(),
