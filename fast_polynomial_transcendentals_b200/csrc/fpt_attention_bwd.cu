@@ -262,24 +262,26 @@ __device__ __forceinline__ void score_pair(const BwdParams& p, float s0, float s
         float p0 = ex2f(a0), p1 = ex2f(a1);
         if (m0) p0 = 0.0f;
         if (m1) p1 = 0.0f;
-        float g0, g1;
-        if constexpr (GRAD == 1) {
-            fma2(-th0, -th1, th0, th1, 1.0f, 1.0f, g0, g1);
-        } else {
-            // derivative of the polynomial on packed bf16 lanes, like the polynomial itself: three fused
-            // multiply-adds per pair; zero where the input is clamped or the output saturated (flat regions)
-            uint32_t gw = P::fma(c, p.tanh_dw[3], p.tanh_dw[2]);
-            gw = P::fma(c, gw, p.tanh_dw[1]);
-            gw = P::fma(c, gw, p.tanh_dw[0]);
-            gw &= ~(P::ge_mask(c, p.tanh.clamp) | P::ge_mask(sat, Consts<kBf16>::one));
-            unpack_bf16x2(gw, g0, g1);
-        }
         p_word = pack_bf16(p0, p1);
         float e0, e1;
         sub2(d0, d1, t0, t1, e0, e1);
         mul2(p0, p1, e0, e1, e0, e1);
-        mul2(e0, e1, g0, g1, e0, e1);
-        ds_word = pack_bf16(e0, e1);
+        if constexpr (GRAD == 1) {
+            float g0, g1;
+            fma2(-th0, -th1, th0, th1, 1.0f, 1.0f, g0, g1);
+            mul2(e0, e1, g0, g1, e0, e1);
+            ds_word = pack_bf16(e0, e1);
+        } else {
+            // derivative of the polynomial on packed bf16 lanes, like the polynomial itself: three fused
+            // multiply-adds per pair; zero where the input is clamped or the output saturated (flat regions).  It
+            // multiplies the packed P (dP - delta) directly (one packed multiply instead of unpacking the derivative and
+            // multiplying in fp32: the product is rounded to bf16 either way, its first factor once more)
+            uint32_t gw = P::fma(c, p.tanh_dw[3], p.tanh_dw[2]);
+            gw = P::fma(c, gw, p.tanh_dw[1]);
+            gw = P::fma(c, gw, p.tanh_dw[0]);
+            gw &= ~(P::ge_mask(c, p.tanh.clamp) | P::ge_mask(sat, Consts<kBf16>::one));
+            ds_word = P::mul(pack_bf16(e0, e1), gw);
+        }
     }
 }
 
