@@ -635,11 +635,12 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 // query heads of the group and their query tiles like WHICH = 1.  A step (one streamed 128-query tile) is cut into two
 // half steps of 64 queries; S^T and dP^T of a half step take 64 tensor-memory columns each and there are two buffers of
 // each (S 0..127, dP 128..255, dK 256..383, dV 384..511), so the tensor core computes the three products of half step n and
-// then S^T and dP^T of half step n + 2 while the score-mod warps work on half step n + 1: the serial chain of the one-buffer
-// forms (dP product -> score-mod -> products -> dP of the next step) is gone and a step costs what the slower of the two
-// sides costs, not their sum.  dQ^T of a half step is written over its S buffer (in registers since the start of its
-// score-mod pass), so the dP buffer is free for half step n + 2 as soon as the products that read dS and P from it have been
-// issued, and the wait for the read-out of dQ^T falls under the dP^T product.
+// then S^T and dP^T of half step n + 2 while the score-mod warps work on half step n + 1: the serial chain of a form with
+// one S and one dP tile (dP product -> score-mod -> products -> dP of the next step) is gone and a step costs what the
+// slower of the two sides costs, not their sum.  dQ^T of a half step is written over its S buffer (in registers since the
+// start of its score-mod pass), so the dP buffer is free for half step n + 2 as soon as the products that read dS and P
+// from it have been issued, and the wait for the read-out of dQ^T falls under the dP^T product.  (An M = 128, N = 64 product
+// takes 49-54 cycles where an N = 128 one takes 64: the price of the two buffers.)
 //   S^T_n  = K Q_n^T, dP^T_n = V dO_n^T                      (M = 128 keys, N = 64 queries, both operands K-major)
 //   dK += dS^T_n Q_n, dV += P^T_n dO_n                        (A from tensor memory, B MN-major; 4 K steps of 16 queries)
 //   dQ^T_n = K^T dS^T_n                                       (M = 128 head-dim, N = 64 queries, both operands MN-major; into
@@ -705,7 +706,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
     const int stream_head0 = head * group;
     volatile uint32_t* abort_flag = &sm.abort_flag;
 #ifdef FPT_ATTN_TRACE
-    constexpr int WHICH = 2;
+    constexpr int WHICH = 2;      // trace slots 6..9
     const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8 || warp == 12);
     int trace_n = 0;
 #endif
