@@ -303,13 +303,17 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
         }
       } else if (rank == 0) {
         // ------------------------------------------------------------------ UMMA issuer (PAIR: for both CTAs)
-        if (lane == 0) {
+        // The whole warp runs the loop (waits included) and one elected lane issues: see elect_one().
+        {
+            const bool elected = elect_one();
             constexpr uint32_t idesc_qk = umma_idesc_bf16(PAIR ? 2 * kTileM : kTileM, kTileN, 0, 0);
             constexpr uint32_t idesc_pv = umma_idesc_bf16(PAIR ? 2 * kTileM : kTileM, kHeadDim, 0, 1);
             constexpr uint32_t k_panel = PAIR ? kPanel / 2 : kPanel;    // a CTA of a pair holds 64 keys of a tile
             auto commit = [&](uint64_t* bar) {
-                if constexpr (PAIR) umma_commit_pair(bar, 3);
-                else umma_commit(bar);
+                if (elected) {
+                    if constexpr (PAIR) umma_commit_pair(bar, 3);
+                    else umma_commit(bar);
+                }
             };
             // P tiles are announced by the warps of both CTAs of a pair
             auto wait_p = [&](uint64_t* bar, uint32_t parity) {
@@ -331,8 +335,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
                     constexpr uint32_t unit = 16;   // descriptor addresses count 16-byte units
                     const uint32_t off = (uint32_t(kk >> 2) * kPanel + uint32_t(kk & 3) * 32u) / unit;
                     const uint32_t off_k = (uint32_t(kk >> 2) * k_panel + uint32_t(kk & 3) * 32u) / unit;
-                    if constexpr (PAIR) umma_ss_words_pair(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
-                    else umma_ss_words(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
+                    if (elected) {
+                        if constexpr (PAIR) umma_ss_words_pair(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
+                        else umma_ss_words(d, qa + off, ka + off_k, desc_hi, idesc_qk, kk > 0);
+                    }
                 }
                 commit(&sm.s_full[s]);
             };
@@ -347,8 +353,10 @@ attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_con
 #pragma unroll
                 for (int k4 = 0; k4 < 4; ++k4) {
                     const uint32_t kk = uint32_t(half) * 4u + uint32_t(k4);
-                    if constexpr (PAIR) umma_ts_words_pair(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
-                    else umma_ts_words(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                    if (elected) {
+                        if constexpr (PAIR) umma_ts_words_pair(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                        else umma_ts_words(d, a + 8u * uint32_t(k4), va + kk * (2048u / 16u), desc_hi, idesc_pv, (!first) || kk > 0);
+                    }
                 }
                 if (half == 1) commit(&sm.pv_done[s]);
             };

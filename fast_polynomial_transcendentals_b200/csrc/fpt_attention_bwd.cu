@@ -402,7 +402,9 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
         }
       } else {
         // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        // The whole warp runs the loop (waits included) and one elected lane issues: see elect_one().
+        {
+            const bool elected = elect_one();
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kTile, 0, 0);   // both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);    // B operand MN-major
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
@@ -423,14 +425,14 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
-                    umma_ss_words(tmem + kColS, x_lo + off, u_k + off, desc_hi, idesc_kk, kk > 0);
+                    if (elected) umma_ss_words(tmem + kColS, x_lo + off, u_k + off, desc_hi, idesc_kk, kk > 0);
                 }
             };
             auto issue_dp = [&](uint32_t w_k, int t) {   // dP = Y W^T into the tile of step t
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t off = (uint32_t(kk >> 2) * kPanelB + uint32_t(kk & 3) * 32u) / 16u;
-                    umma_ss_words(tmem + dp_col(t), y_lo + off, w_k + off, desc_hi, idesc_kk, kk > 0);
+                    if (elected) umma_ss_words(tmem + dp_col(t), y_lo + off, w_k + off, desc_hi, idesc_kk, kk > 0);
                 }
             };
             bool ok = mbar_wait(&sm.xy_full, 0, abort_flag, p.status, kBwdXY);
@@ -441,7 +443,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 stage_words(0, u_k, w_k, u_mn, w_mn);
                 issue_s(u_k);
                 issue_dp(w_k, 0);
-                umma_commit(&sm.s_full);
+                if (elected) umma_commit(&sm.s_full);
             }
             for (int t = 0; t < n_inner && ok; ++t) {
                 const int st = t % kRing, st_next = (t + 1) % kRing;
@@ -459,7 +461,7 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                     issue_s(nu_k);
                     if constexpr (WHICH == 0) {
                         issue_dp(nw_k, t + 1);
-                        umma_commit(&sm.s_full);
+                        if (elected) umma_commit(&sm.s_full);
                     }
                 }
                 FPT_BTRACE(2, 11);
@@ -470,26 +472,26 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
                 FPT_BTRACE(2, 12);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)       // acc0 += dS U
-                    umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 64u * (kk >> 2) + 8u * (kk & 3),
+                    if (elected) umma_ts_words(tmem + kColAcc0, tmem + dp_col(t) + 64u * (kk >> 2) + 8u * (kk & 3),
                                   u_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 if constexpr (kKeysFixed) {
 #pragma unroll
                     for (int kk = 0; kk < 8; ++kk)   // acc1 += P W
-                        umma_ts_words(tmem + kColAcc1, tmem + dp_col(t) + 64u * (kk >> 2) + 32u + 8u * (kk & 3),
+                        if (elected) umma_ts_words(tmem + kColAcc1, tmem + dp_col(t) + 64u * (kk >> 2) + 32u + 8u * (kk & 3),
                                       w_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mn, t > 0 || kk > 0);
                 }
-                umma_commit(&sm.uw_empty[st]);
+                if (elected) umma_commit(&sm.uw_empty[st]);
                 FPT_BTRACE(2, 13);
                 // [C] WHICH 1: the one dP tile is free again once the products above have read it (same thread, in order)
                 if constexpr (kKeysFixed) {
                     if (more) {
                         issue_dp(nw_k, t + 1);
-                        umma_commit(&sm.s_full);
+                        if (elected) umma_commit(&sm.s_full);
                     }
                 }
                 u_k = nu_k; w_k = nw_k; u_mn = nu_mn; w_mn = nw_mn;
             }
-            if (ok) umma_commit(&sm.acc_done);
+            if (ok && elected) umma_commit(&sm.acc_done);
         }
       }
     } else {
@@ -787,7 +789,9 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
       } else {
         // ------------------------------------------------------------------ UMMA issuer
-        if (lane == 0) {
+        // The whole warp runs the loop (waits included) and one elected lane issues: see elect_one().
+        {
+            const bool elected = elect_one();
             constexpr uint32_t idesc_kk = umma_idesc_bf16(kTile, kHalf, 0, 0);     // S^T, dP^T: both operands K-major
             constexpr uint32_t idesc_mn = umma_idesc_bf16(kTile, kDim, 0, 1);      // dK, dV: B operand MN-major
             constexpr uint32_t idesc_mnmn = umma_idesc_bf16(kDim, kHalf, 1, 1);    // dQ^T: both operands MN-major
@@ -802,7 +806,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t in = uint32_t(kk & 3) * 32u;
-                    umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
+                    if (elected) umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
                                   u_k + (uint32_t(kk >> 2) * kHalfPanelB + in) / 16u, desc_hi, idesc_kk, kk > 0);
                 }
             };
@@ -811,7 +815,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk) {
                     const uint32_t in = uint32_t(kk & 3) * 32u;
-                    umma_ss_words(tmem + kDp + uint32_t(kHalf * h), y_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
+                    if (elected) umma_ss_words(tmem + kDp + uint32_t(kHalf * h), y_k + (uint32_t(kk >> 2) * kPanelB + in) / 16u,
                                   w_k + (uint32_t(kk >> 2) * kHalfPanelB + in) / 16u, desc_hi, idesc_kk, kk > 0);
                 }
             };
@@ -823,7 +827,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 tc_fence_after_sync();
                 issue_s(n, n);
                 issue_dp(n, n);
-                umma_commit(&sm.sd_full[n]);
+                if (elected) umma_commit(&sm.sd_full[n]);
             }
             for (int n = 0; n < n_half && ok; ++n) {
                 const int t = n >> 1, h = n & 1, st = n % kPipeRing;
@@ -838,19 +842,19 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 const uint32_t a_base = tmem + kDp + uint32_t(kHalf * h);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)          // dK += dS^T Q: 16 queries per K step; warp group c = k / 2 owns 32 columns
-                    umma_ts_words(tmem + kAcc0, a_base + 32u * (k >> 1) + 8u * (k & 1), u_mn + uint32_t(k) * (2048u / 16u),
+                    if (elected) umma_ts_words(tmem + kAcc0, a_base + 32u * (k >> 1) + 8u * (k & 1), u_mn + uint32_t(k) * (2048u / 16u),
                                   desc_hi, idesc_mn, n > 0 || k > 0);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)          // dV += P^T dO
-                    umma_ts_words(tmem + kAcc1, a_base + 32u * (k >> 1) + 16u + 8u * (k & 1), w_mn + uint32_t(k) * (2048u / 16u),
+                    if (elected) umma_ts_words(tmem + kAcc1, a_base + 32u * (k >> 1) + 16u + 8u * (k & 1), w_mn + uint32_t(k) * (2048u / 16u),
                                   desc_hi, idesc_mn, n > 0 || k > 0);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)       // dQ^T = K^T dS^T over the S buffer of the half step (in registers long ago)
-                    umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_mn + uint32_t(kk) * (2048u / 16u),
+                    if (elected) umma_ss_words(tmem + kS + uint32_t(kHalf * h), x_mn + uint32_t(kk) * (2048u / 16u),
                                   ds_mn + uint32_t(kk) * (2048u / 16u), desc_hi, idesc_mnmn, kk > 0);
-                umma_commit(&sm.dq_full[h]);
+                if (elected) umma_commit(&sm.dq_full[h]);
                 FPT_BTRACE(2, 16);
-                umma_commit(&sm.uw_empty[st]);       // every product that reads the stage is behind this commit
+                if (elected) umma_commit(&sm.uw_empty[st]);       // every product that reads the stage is behind this commit
                 if (n + 2 < n_half) {
                     // S^T and dP^T of the half step after the next one, into this half step's buffers.  The dP buffer is free
                     // as soon as the two products above have read dS and P from it (issued before, executed in order); the S
@@ -867,11 +871,11 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                     tc_fence_after_sync();
                     FPT_BTRACE(2, 13);
                     issue_s(st2, h);
-                    umma_commit(&sm.sd_full[h]);
+                    if (elected) umma_commit(&sm.sd_full[h]);
                     FPT_BTRACE(2, 14);
                 }
             }
-            if (ok) umma_commit(&sm.acc_done);
+            if (ok && elected) umma_commit(&sm.acc_done);
         }
       }
     } else if (warp >= 12) {

@@ -126,6 +126,18 @@ __device__ __forceinline__ void tc_fence_before_sync() { asm volatile("tcgen05.f
 __device__ __forceinline__ void tc_fence_after_sync() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void fence_async_shared() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// One lane of a converged warp.  The warp that issues tcgen05.mma runs its whole loop converged and lets the elected lane
+// issue: operand descriptors computed by all 32 lanes alike stay on the uniform datapath.  With the loop under
+// `if (lane == 0)` instead, every descriptor word is computed in a vector register and moved over for each instruction,
+// and an arithmetic-heavy warp on the same scheduler then holds the issue down to one product per ~105 cycles (measured
+// with a one-block-per-SM stream of 128 x 128 x 16 products: 64 cycles alone or with the converged form, 105 with the
+// single-lane branch next to one warp of dependent FMAs).
+__device__ __forceinline__ bool elect_one() {
+    uint32_t pred;
+    asm volatile("{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(pred));
+    return pred != 0;
+}
+
 // mbarrier arrives once all tcgen05.mma issued so far by this thread have completed
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];"
