@@ -262,7 +262,9 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ tcgen05.mma issuer
-        if (lane == 0) {
+        // The whole warp runs the loop (waits included) and one elected lane issues: see elect_one().
+        {
+            const bool elected = elect_one();
             constexpr uint32_t idesc = umma_idesc_bf16(kRowsPerHalf, 2 * kHiddenPerTile, 0, 0);
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
             uint32_t it = 0, local = 0;
@@ -288,18 +290,18 @@ gate_up_swiglu_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_co
 #if FPT_GATE_UP_DIAG != 3
 #pragma unroll
                         for (uint32_t k = 0; k < kBlockK / 16; ++k)  // 32 bytes along the swizzled row per K step of 16
-                            umma_ss_words(d, xh + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                            if (elected) umma_ss_words(d, xh + 2u * k, w_lo + 2u * k, desc_hi, idesc, (kb > 0 || k > 0) ? 1u : 0u);
 #endif
                     }
                     if (!ok) break;
-                    umma_commit(&sm.empty[s]);
+                    if (elected) umma_commit(&sm.empty[s]);
                 }
                 if (ok) {
                     if constexpr (HALVES == 1) {
-                        umma_commit(&sm.acc_full[local & 1u]);
+                        if (elected) umma_commit(&sm.acc_full[local & 1u]);
                     } else {
-                        umma_commit(&sm.acc_full[0]);
-                        umma_commit(&sm.acc_full[1]);
+                        if (elected) umma_commit(&sm.acc_full[0]);
+                        if (elected) umma_commit(&sm.acc_full[1]);
                     }
                 }
             }
@@ -442,7 +444,9 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
         }
     } else if (warp == 1 && rank == 0) {
         // ------------------------------------------------------------------ leading CTA: tcgen05.mma issuer for the pair
-        if (lane == 0) {
+        // The whole warp runs the loop (waits included) and one elected lane issues: see elect_one().
+        {
+            const bool elected = elect_one();
             constexpr uint32_t idesc = umma_idesc_bf16(2 * kRowsPerHalf, 2 * kHiddenPerTile, 0, 0);
             constexpr uint32_t desc_hi = umma_smem_desc_hi(1024);
             uint32_t it = 0, local = 0;
@@ -469,15 +473,16 @@ gate_up_swiglu_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __gr
                     for (uint32_t h = 0; h < uint32_t(WIDE); ++h) {
 #pragma unroll
                         for (uint32_t k = 0; k < kBlockK / 16; ++k)
-                            umma_ss_words_pair(tmem + (a0 + h) * 256u, x_lo + 2u * k, w_lo + h * (kXHalfBytes / 16u) + 2u * k, desc_hi,
+                            if (elected) umma_ss_words_pair(tmem + (a0 + h) * 256u, x_lo + 2u * k, w_lo + h * (kXHalfBytes / 16u) + 2u * k, desc_hi,
                                                idesc, (kb > 0 || k > 0) ? 1u : 0u);
                     }
 #endif
-                    umma_commit_pair(&sm.empty[s], 3);
+                    if (elected) umma_commit_pair(&sm.empty[s], 3);
                 }
                 if (ok) {
 #pragma unroll
-                    for (uint32_t h = 0; h < uint32_t(WIDE); ++h) umma_commit_pair(&sm.acc_full[a0 + h], 3);
+                    for (uint32_t h = 0; h < uint32_t(WIDE); ++h)
+                        if (elected) umma_commit_pair(&sm.acc_full[a0 + h], 3);
                 }
             }
         }
