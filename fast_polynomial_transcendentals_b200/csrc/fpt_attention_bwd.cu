@@ -36,7 +36,7 @@ constexpr int kRing = 2;
 constexpr uint32_t kPanelB = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
 constexpr uint32_t kTileB = 2 * kPanelB;
 constexpr int kBwdThreads = 384;
-constexpr int kBwdThreadsFused = 512;   // the single-pass form has a fourth warpgroup, which reads the partial dQ tiles out
+constexpr int kBwdThreadsFused = 640;   // the single-pass form has two more warpgroups, which read the partial dQ tiles out
 constexpr float kLog2eB = 1.4426950408889634f;
 
 struct BwdSmem {
@@ -647,15 +647,17 @@ attention_bwd_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_con
 //   dK += dS^T_n Q_n, dV += P^T_n dO_n                        (A from tensor memory, B MN-major; 4 K steps of 16 queries)
 //   dQ^T_n = K^T dS^T_n                                       (M = 128 head-dim, N = 64 queries, both operands MN-major; into
 //                                                              the S buffer of the half step)
-// Roles: warp 0 TMA producer, warp 1 issuer (one thread), warps 4..11 score-mod (thread = key row; warps w and w + 4 split
-// the 64 queries of a half step), warps 12..15 read-out of dQ^T (lane = head-dim index): registers, then 32 queries at a time
-// through one of three 16 KiB staging buffers (512 bytes per query, the layout of the head-major fp32 buffer) into one
-// untiled reduce-add copy each, two of them in flight while the third buffer fills (a copy of 16 KiB takes ~1700 cycles
-// from issue to "read", whatever its size: waiting for each one before staging the next made the read-out the slowest
-// role).  The streamed Q / dO ring holds half tiles (64 queries), three stages, which is what leaves room for the staging.  The dS^T tile in shared memory is one panel ([keys x 64 queries]) reused by every half step: it is
-// written at the end of a score-mod pass, long after the dQ^T product of the half step before has read it.
+// Roles: warp 0 TMA producer, warp 1 issuer (converged, an elected lane issues), warps 4..11 score-mod (thread = key row;
+// warps w and w + 4 split the 64 queries of a half step), warps 12..19 read-out of dQ^T (lane = head-dim index) in two
+// warpgroups, one per 32 queries of a half step: registers (the columns are released at once), then the team's 16 KiB
+// staging buffer (512 bytes per query, the layout of the head-major fp32 buffer) and one untiled reduce-add copy, which
+// the team waits for only when it needs the buffer again.  (One warpgroup doing both chunks of a half step took ~3000
+// cycles per half step on schedulers it shares with the score-mod warps and held the whole pipeline to that.)  The streamed
+// Q / dO ring holds half tiles (64 queries), three stages.  The dS^T tile in shared memory is one panel ([keys x 64
+// queries]) reused by every half step: it is written at the end of a score-mod pass, long after the dQ^T product of the
+// half step before has read it.
 constexpr int kPipeRing = 3;       // half-tile stages of the streamed Q / dO ring
-constexpr int kPipeStaging = 3;    // staging buffers of the read-out: two reduce-add copies in flight while the third fills
+constexpr int kPipeStaging = 2;    // staging buffers of the read-out: one per read-out warpgroup
 constexpr uint32_t kHalfPanelB = kPanelB / 2;   // one [64 rows x 64 bf16] panel
 
 struct PipeSmem {
@@ -727,7 +729,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             mbar_init(&sm.sd_full[h], 1);
             mbar_init(&sm.p_full[h], 8);
             mbar_init(&sm.dq_full[h], 1);
-            mbar_init(&sm.dq_read[h], 4);
+            mbar_init(&sm.dq_read[h], 8);
         }
         mbar_init(&sm.acc_done, 1);
         sm.abort_flag = *reinterpret_cast<volatile uint32_t*>(p.status) != 0u ? 1u : 0u;
@@ -752,9 +754,14 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
     const bool skip = sm.abort_flag != 0u;
     constexpr uint32_t kS = 0, kDp = 128, kAcc0 = 256, kAcc1 = 384;   // tensor-memory columns
 
-    // 512 threads start at 128 registers: 128 x (128 - 56) + 128 x (128 - 104) released, 256 x (176 - 128) taken
+    // 640 threads start at 96 registers each.  The producer / issuer warpgroup and the two read-out warpgroups give registers
+    // back, the two score-mod warpgroups take them; an increase waits until the registers are there, so the sums must work out.
+    constexpr int kRegsStart = 96, kRegsWg0 = 56, kRegsReadOut = 80, kRegsScoreMod = 128;
+    static_assert(65536 / kBwdThreadsFused / 8 * 8 == kRegsStart, "registers per thread at launch");
+    static_assert(128 * (kRegsStart - kRegsWg0) + 256 * (kRegsStart - kRegsReadOut) >= 256 * (kRegsScoreMod - kRegsStart),
+                  "register hand-over: more taken than released would block the score-mod warps for ever");
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegsWg0));
       if (skip || warp >= 2) {
         // warps 2 and 3 only hold registers for the others
       } else if (warp == 0) {
@@ -879,66 +886,64 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
       }
     } else if (warp >= 12) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 104;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegsReadOut));
       if (!skip) {
         // ------------------------------------------------------------------ read-out warps
-        const int quarter = warp & 3;
+        // Two warpgroups: team 0 (warps 12..15) takes queries 0..31 of every half step, team 1 (warps 16..19) queries 32..63,
+        // each through its own 16 KiB staging buffer and its own reduce-add copy per half step.  The tensor-memory columns
+        // are released as soon as both teams have their values in registers; the copy of a half step is waited for (by the
+        // team's issuing lane) only when the buffer is needed again, after the next release.
+        const int team = (warp - 12) >> 2, quarter = warp & 3;
+        const bool issuing = quarter == 0;                  // the team's first warp hands the staged chunk to the copy engine
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
+        const uint32_t mine = smem_u32(sm.stage[team]) + uint32_t(32 * quarter + lane) * 4u;
         bool ok = true;
-        int m = 0;                                          // chunks of 32 queries staged so far
         for (int n = 0; n < n_half && ok; ++n) {
             const int t = n >> 1, h = n & 1;
             const int g = t / per_head;
-            const int q0 = (first_inner + (t - g * per_head)) * kTile + kHalf * h;     // first query of the half step
+            const int q0 = (first_inner + (t - g * per_head)) * kTile + kHalf * h + 32 * team;     // first query of the chunk
             ok = mbar_wait(&sm.dq_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipeDqFull);
             if (!ok) break;
             tc_fence_after_sync();
             FPT_BTRACE(3, 20);
-            uint32_t v0[32], v1[32];
-            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h), v0);
-            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32), v1);
+            uint32_t v[32];
+            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32 * team), v);
             tmem_ld_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.dq_read[h]);
             FPT_BTRACE(3, 21);
-            float* dst = p.dq_accum + ((int64_t(b) * p.q_heads + stream_head0 + g) * p.seq + q0) * kDim;
-#pragma unroll
-            for (int a = 0; a < 2; ++a, ++m) {
-                // Buffer m % 3; the copy that last read it is chunk m - 3.  The issuing thread keeps two copies in flight:
-                // after committing chunk m it waits until at most two groups are unread (chunk m - 2 has been read) and
-                // frees that chunk's buffer, which is the one chunk m + 1 fills.
-                const int buf = m % kPipeStaging;
-                const uint32_t use = uint32_t(m / kPipeStaging);
-                if (m >= kPipeStaging) ok = mbar_wait(&sm.stage_free[buf], (use & 1u) ^ 1u, abort_flag, p.status, kPipeStageFree);
-                if (!ok) break;
-                const uint32_t mine = smem_u32(sm.stage[buf]) + uint32_t(32 * quarter + lane) * 4u;
-#pragma unroll
-                for (int j = 0; j < 32; ++j) sts32(mine + uint32_t(j) * (kDim * 4u), a == 0 ? v0[j] : v1[j]);
-                fence_async_shared();
-                __syncwarp();
-                if (lane == 0) mbar_arrive(&sm.staged[buf]);
-                if (warp == 12) {
-                    if (lane == 0) {
-                        ok = mbar_wait(&sm.staged[buf], use & 1u, abort_flag, p.status, kPipeStaged);
-                        const int rows = min(32, p.seq - q0 - 32 * a);
-#ifndef FPT_DIAG_NO_RED
-                        if (ok && rows > 0) bulk_reduce_add_f32_1d(dst + 32 * a * kDim, sm.stage[buf], uint32_t(rows) * (kDim * 4u));
-#endif
-                        bulk_commit_group();
-                        bulk_wait_group_read<kPipeStaging - 1>();
-                        if (ok && m >= kPipeStaging - 1) mbar_arrive(&sm.stage_free[(m + 1) % kPipeStaging]);
-                    }
-                    ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
-                    if (!ok) break;
-                    FPT_BTRACE(3, 22 + a);
+            if (n > 0) {                                    // the copy of the half step before has read the buffer
+                if (issuing && lane == 0) {
+                    bulk_wait_group_read0();
+                    mbar_arrive(&sm.stage_free[team]);
                 }
+                ok = mbar_wait(&sm.stage_free[team], uint32_t(n - 1) & 1u, abort_flag, p.status, kPipeStageFree);
+                if (!ok) break;
+            }
+#pragma unroll
+            for (int j = 0; j < 32; ++j) sts32(mine + uint32_t(j) * (kDim * 4u), v[j]);
+            fence_async_shared();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&sm.staged[team]);
+            if (issuing) {
+                if (lane == 0) {
+                    ok = mbar_wait(&sm.staged[team], uint32_t(n) & 1u, abort_flag, p.status, kPipeStaged);
+                    const int rows = min(32, p.seq - q0);
+                    float* dst = p.dq_accum + ((int64_t(b) * p.q_heads + stream_head0 + g) * p.seq + q0) * kDim;
+#ifndef FPT_DIAG_NO_RED
+                    if (ok && rows > 0) bulk_reduce_add_f32_1d(dst, sm.stage[team], uint32_t(rows) * (kDim * 4u));
+#endif
+                    bulk_commit_group();
+                }
+                ok = __shfl_sync(0xffffffffu, int(ok), 0) != 0;
+                FPT_BTRACE(3, 22);
             }
         }
-        if (warp == 12 && lane == 0) bulk_wait_group0();
+        if (issuing && lane == 0) bulk_wait_group0();
       }
     } else {
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 176;");
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(kRegsScoreMod));
       if (!skip) {
         // ------------------------------------------------------------------ score-mod warps
         const int quarter = warp & 3, c32 = (warp - 4) >> 2;        // lane quarter; which 32 of a half step's 64 queries
