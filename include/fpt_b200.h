@@ -329,7 +329,7 @@ int fpt_attention_fwd_routed(void* out, void* lse, const void* q, const void* k,
  *          of a key tile also forms the partial dQ of every query tile it streams and adds it into an fp32
  *          [B, Hq, S, 128] buffer inside the workspace with reduce-add copies; a last pass scales and rounds it to bf16.
  *          The order of those fp32 additions is not fixed, so the last bit of a dQ element can differ from run to run
- *          (dK and dV are deterministic, and the same bits as in the two-pass form).  Measured on B200: 1.12-1.32x the
+ *          (dK and dV are deterministic, and the same bits as in the two-pass form).  Measured on B200: 1.4-1.65x the
  *          two-pass form;
  *        two passes (workspace >= fpt_attention_bwd_workspace_bytes; none needed in the sigmoid modes): one launch for dQ,
  *          one for dK and dV, each recomputing S and dP: 7 matrix products per tile pair, no atomics, deterministic.
