@@ -36,7 +36,6 @@ constexpr int kRing = 2;
 constexpr uint32_t kPanelB = 128 * 128;        // bytes of one [128 rows x 64 bf16] panel
 constexpr uint32_t kTileB = 2 * kPanelB;
 constexpr int kBwdThreads = 384;
-constexpr int kBwdThreadsFused = 640;   // the single-pass form has two more warpgroups, which read the partial dQ tiles out
 constexpr float kLog2eB = 1.4426950408889634f;
 
 struct BwdSmem {
@@ -684,13 +683,19 @@ struct PipeSmem {
 
 enum : uint32_t { kPipeSdFull = 16, kPipePFull, kPipeDqFull, kPipeDqRead, kPipeStaged, kPipeStageFree };
 
-template <int MODE, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3>
-__global__ void __launch_bounds__(kBwdThreadsFused, 1)
+// SMW: score-mod warps, 8 (two per lane quarter, 32 queries of a half step each) or 16 (four per lane quarter, 16 queries each)
+constexpr int pipe_threads(int smw) { return 128 + 32 * smw + 256; }
+
+template <int MODE, int GRAD = 0, int EMU = 0, int EK = kExp2FullD3, int SMW = 8>
+__global__ void __launch_bounds__(pipe_threads(SMW), 1)
 attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                                const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_do,
                                const BwdParams p) {
     constexpr bool kSigmoidMode = MODE == 1 || MODE == 4;
     constexpr int kHalf = kTile / 2;                      // queries of a half step
+    static_assert(SMW == 8 || SMW == 16, "two or four score-mod warps per lane quarter");
+    constexpr int kCols = kHalf / (SMW / 4);              // queries of a half step per score-mod warp: 32 or 16
+    constexpr int kFirstReadOut = 4 + SMW;                // first read-out warp
     extern __shared__ uint8_t smem_raw[];
     // the shared memory of an SM is filled to the last kilobyte: no alignment slack, the base is checked below
     PipeSmem& sm = *reinterpret_cast<PipeSmem*>(smem_raw);
@@ -711,7 +716,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
     volatile uint32_t* abort_flag = &sm.abort_flag;
 #ifdef FPT_ATTN_TRACE
     constexpr int WHICH = 2;      // trace slots 6..9
-    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8 || warp == 12);
+    const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (warp == 1 || warp == 4 || warp == 8 || warp == kFirstReadOut);
     int trace_n = 0;
 #endif
 
@@ -727,7 +732,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
         }
         for (int h = 0; h < 2; ++h) {
             mbar_init(&sm.sd_full[h], 1);
-            mbar_init(&sm.p_full[h], 8);
+            mbar_init(&sm.p_full[h], SMW);
             mbar_init(&sm.dq_full[h], 1);
             mbar_init(&sm.dq_read[h], 8);
         }
@@ -754,11 +759,14 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
     const bool skip = sm.abort_flag != 0u;
     constexpr uint32_t kS = 0, kDp = 128, kAcc0 = 256, kAcc1 = 384;   // tensor-memory columns
 
-    // 640 threads start at 96 registers each.  The producer / issuer warpgroup and the two read-out warpgroups give registers
-    // back, the two score-mod warpgroups take them; an increase waits until the registers are there, so the sums must work out.
-    constexpr int kRegsStart = 96, kRegsWg0 = 56, kRegsReadOut = 80, kRegsScoreMod = 128;
-    static_assert(65536 / kBwdThreadsFused / 8 * 8 == kRegsStart, "registers per thread at launch");
-    static_assert(128 * (kRegsStart - kRegsWg0) + 256 * (kRegsStart - kRegsReadOut) >= 256 * (kRegsScoreMod - kRegsStart),
+    // 640 (896) threads start at 96 (72) registers each.  The producer / issuer warpgroup and the two read-out warpgroups give
+    // registers back, the score-mod warpgroups take them; an increase waits until the registers are there, so the sums must
+    // work out.
+    constexpr int kThreadsAll = pipe_threads(SMW);
+    constexpr int kRegsStart = SMW == 8 ? 96 : 72, kRegsWg0 = SMW == 8 ? 56 : 48, kRegsReadOut = SMW == 8 ? 80 : 64;
+    constexpr int kRegsScoreMod = SMW == 8 ? 128 : 80;
+    static_assert(65536 / kThreadsAll / 8 * 8 == kRegsStart, "registers per thread at launch");
+    static_assert(128 * (kRegsStart - kRegsWg0) + 256 * (kRegsStart - kRegsReadOut) >= 32 * SMW * (kRegsScoreMod - kRegsStart),
                   "register hand-over: more taken than released would block the score-mod warps for ever");
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegsWg0));
@@ -806,6 +814,9 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             const uint32_t x_k = umma_smem_desc_lo(smem_u32(sm.x), 16), y_k = umma_smem_desc_lo(smem_u32(sm.y), 16);
             const uint32_t x_mn = umma_smem_desc_lo(smem_u32(sm.x), kPanelB);
             const uint32_t ds_mn = umma_smem_desc_lo(smem_u32(sm.ds), kPanelB);
+            // K step k of a half step (16 queries) belongs to score-mod warp k / (kCols / 16) of each lane quarter, which keeps
+            // its dS words in the first half of its own kCols dP columns and its P words in the second half
+            auto a_col = [](int k) { return uint32_t(kCols * (k / (kCols / 16)) + 8 * (k % (kCols / 16))); };
             // K-major operand, K step kk of 16 head-dim elements: panel kk / 4 (16 KiB apart in the fixed tiles, 8 KiB in the
             // half tiles of the ring), 32 bytes per step inside the 128-byte line
             auto issue_s = [&](int st, int h) {
@@ -848,12 +859,12 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
                 const uint32_t w_mn = umma_smem_desc_lo(smem_u32(sm.w[st]), kHalfPanelB);
                 const uint32_t a_base = tmem + kDp + uint32_t(kHalf * h);
 #pragma unroll
-                for (int k = 0; k < 4; ++k)          // dK += dS^T Q: 16 queries per K step; warp group c = k / 2 owns 32 columns
-                    if (elected) umma_ts_words(tmem + kAcc0, a_base + 32u * (k >> 1) + 8u * (k & 1), u_mn + uint32_t(k) * (2048u / 16u),
+                for (int k = 0; k < 4; ++k)          // dK += dS^T Q: 16 queries per K step, out of the columns of the warp that wrote them
+                    if (elected) umma_ts_words(tmem + kAcc0, a_base + a_col(k), u_mn + uint32_t(k) * (2048u / 16u),
                                   desc_hi, idesc_mn, n > 0 || k > 0);
 #pragma unroll
                 for (int k = 0; k < 4; ++k)          // dV += P^T dO
-                    if (elected) umma_ts_words(tmem + kAcc1, a_base + 32u * (k >> 1) + 16u + 8u * (k & 1), w_mn + uint32_t(k) * (2048u / 16u),
+                    if (elected) umma_ts_words(tmem + kAcc1, a_base + a_col(k) + uint32_t(kCols / 2), w_mn + uint32_t(k) * (2048u / 16u),
                                   desc_hi, idesc_mn, n > 0 || k > 0);
 #pragma unroll
                 for (int kk = 0; kk < 8; ++kk)       // dQ^T = K^T dS^T over the S buffer of the half step (in registers long ago)
@@ -885,15 +896,15 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             if (ok && elected) umma_commit(&sm.acc_done);
         }
       }
-    } else if (warp >= 12) {
+    } else if (warp >= kFirstReadOut) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" :: "n"(kRegsReadOut));
       if (!skip) {
         // ------------------------------------------------------------------ read-out warps
-        // Two warpgroups: team 0 (warps 12..15) takes queries 0..31 of every half step, team 1 (warps 16..19) queries 32..63,
+        // Two warpgroups: team 0 (the first four warps) takes queries 0..31 of every half step, team 1 queries 32..63,
         // each through its own 16 KiB staging buffer and its own reduce-add copy per half step.  The tensor-memory columns
         // are released as soon as both teams have their values in registers; the copy of a half step is waited for (by the
         // team's issuing lane) only when the buffer is needed again, after the next release.
-        const int team = (warp - 12) >> 2, quarter = warp & 3;
+        const int team = (warp - kFirstReadOut) >> 2, quarter = warp & 3;
         const bool issuing = quarter == 0;                  // the team's first warp hands the staged chunk to the copy engine
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
         const uint32_t mine = smem_u32(sm.stage[team]) + uint32_t(32 * quarter + lane) * 4u;
@@ -946,7 +957,7 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
       asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" :: "n"(kRegsScoreMod));
       if (!skip) {
         // ------------------------------------------------------------------ score-mod warps
-        const int quarter = warp & 3, c32 = (warp - 4) >> 2;        // lane quarter; which 32 of a half step's 64 queries
+        const int quarter = warp & 3, cw = (warp - 4) >> 2;          // lane quarter; which kCols of a half step's 64 queries
         const int r = 32 * quarter + lane;                           // key row of the tile = tensor-memory lane
         const uint32_t lane_base = uint32_t(32 * quarter) << 16;
         bool ok = true;
@@ -955,28 +966,34 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             ok = mbar_wait(&sm.sd_full[h], uint32_t(t) & 1u, abort_flag, p.status, kPipeSdFull);
             if (!ok) break;
             tc_fence_after_sync();
-            FPT_BTRACE(c32, 2);
-            // This warp owns columns [32 c32, 32 c32 + 32) of the half step's S and dP buffers; it writes its 16 dS words over
-            // the first 16 and its 16 P words over the last 16 of its own dP columns, so nobody's loads are in the way.
-            uint32_t dv[32], sv[32];
-            const uint32_t t_own = tmem + lane_base + kDp + uint32_t(kHalf * h + 32 * c32);
-            tmem_ld_32x32b_x32(t_own, dv);
-            tmem_ld_32x32b_x32(tmem + lane_base + kS + uint32_t(kHalf * h + 32 * c32), sv);
+            FPT_BTRACE(cw & 1, 2);
+            // This warp owns columns [kCols cw, kCols cw + kCols) of the half step's S and dP buffers; it writes its dS words
+            // over the first half and its P words over the second half of its own dP columns, so nobody's loads are in the way.
+            uint32_t dv[kCols], sv[kCols];
+            const uint32_t t_own = tmem + lane_base + kDp + uint32_t(kHalf * h + kCols * cw);
+            const uint32_t t_s = tmem + lane_base + kS + uint32_t(kHalf * h + kCols * cw);
+            if constexpr (kCols == 32) {
+                tmem_ld_32x32b_x32(t_own, dv);
+                tmem_ld_32x32b_x32(t_s, sv);
+            } else {
+                tmem_ld_32x32b_x16(t_own, dv);
+                tmem_ld_32x32b_x16(t_s, sv);
+            }
             tmem_ld_wait();
-            FPT_BTRACE(c32, 3);
+            FPT_BTRACE(cw & 1, 3);
             if (!kSigmoidMode)                 // the per-query vectors arrived on this barrier (complete by now)
                 ok = mbar_wait(&sm.uw_full[st], uint32_t(n / kPipeRing) & 1u, abort_flag, p.status, kBwdUwFull);
             if (!ok) break;
             const int g = t / per_head;
             const int tile_c0 = (first_inner + (t - g * per_head)) * kTile;        // first query of the streamed tile
-            const int in_tile = kHalf * h + 32 * c32;                              // this warp's first query inside it
+            const int in_tile = kHalf * h + kCols * cw;                            // this warp's first query inside it
             const int c0 = tile_c0 + in_tile;
             const bool diagonal = (p.causal && tile_c0 == row0) || (ragged && (tile_c0 + kTile > p.seq || row0 + kTile > p.seq));
-            const uint32_t lse_addr = smem_u32(&sm.lse2[st][32 * c32]), delta_addr = smem_u32(&sm.delta[st][32 * c32]);
-            uint32_t pw[16], dsw[16];
+            const uint32_t lse_addr = smem_u32(&sm.lse2[st][kCols * cw]), delta_addr = smem_u32(&sm.delta[st][kCols * cw]);
+            uint32_t pw[kCols / 2], dsw[kCols / 2];
             auto columns = [&](auto masked) {
 #pragma unroll
-                for (int quad = 0; quad < 8; ++quad) {       // four queries = two pairs per 128-bit shared load
+                for (int quad = 0; quad < kCols / 4; ++quad) {       // four queries = two pairs per 128-bit shared load
                     const int cq = 4 * quad;
                     float lv[4] = {0.0f, 0.0f, 0.0f, 0.0f}, dl[4] = {0.0f, 0.0f, 0.0f, 0.0f};
                     if (!kSigmoidMode) {
@@ -1001,40 +1018,47 @@ attention_bwd_pipelined_kernel(const __grid_constant__ CUtensorMap map_k, const 
             };
             if (diagonal) columns(std::true_type{});    // a branch the whole CTA takes together
             else columns(std::false_type{});
-            FPT_BTRACE(c32, 4);
-            tmem_st_32x32b_x16(t_own, dsw);
-            tmem_st_32x32b_x16(t_own + 16, pw);
-            // dS^T also goes to shared memory for the dQ^T product: this thread's key row, its 32 queries = chunks 4 c32 ..
-            // 4 c32 + 3 of the row's 128-byte line, chunk j stored at position j ^ (row % 8) (the 128-byte swizzle of the
+            FPT_BTRACE(cw & 1, 4);
+            if constexpr (kCols == 32) {
+                tmem_st_32x32b_x16(t_own, dsw);
+                tmem_st_32x32b_x16(t_own + 16, pw);
+            } else {
+                tmem_st_32x32b_x8(t_own, dsw);
+                tmem_st_32x32b_x8(t_own + 8, pw);
+            }
+            // dS^T also goes to shared memory for the dQ^T product: this thread's key row, its kCols queries = kCols / 8
+            // chunks of the row's 128-byte line, chunk j stored at position j ^ (row % 8) (the 128-byte swizzle of the
             // operand layout).  The tile is free once the dQ^T product of the half step before is complete.
             if (n > 0) ok = mbar_wait(&sm.dq_full[h ^ 1], uint32_t((n - 1) >> 1) & 1u, abort_flag, p.status, kPipeDqFull);
             if (!ok) break;
-            FPT_BTRACE(c32, 5);
+            FPT_BTRACE(cw & 1, 5);
             const uint32_t line = smem_u32(sm.ds) + uint32_t(r) * 128u;
 #pragma unroll
-            for (int j = 0; j < 4; ++j)
-                sts128(line + (uint32_t((4 * c32 + j) ^ (r & 7)) << 4), dsw[4 * j], dsw[4 * j + 1], dsw[4 * j + 2], dsw[4 * j + 3]);
+            for (int j = 0; j < kCols / 8; ++j)
+                sts128(line + (uint32_t(((kCols / 8) * cw + j) ^ (r & 7)) << 4), dsw[4 * j], dsw[4 * j + 1], dsw[4 * j + 2],
+                       dsw[4 * j + 3]);
             fence_async_shared();
             tmem_st_wait();
             tc_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&sm.p_full[h]);
-            FPT_BTRACE(c32, 6);
+            FPT_BTRACE(cw & 1, 6);
         }
         if (ok && n_half > 0) {
             ok = mbar_wait(&sm.acc_done, 0, abort_flag, p.status, kBwdAccDone);
             if (ok) {
                 tc_fence_after_sync();
-                const int64_t off = ((int64_t(b) * p.seq + row0 + r) * p.kv_heads + head) * kDim + 64 * c32;
+                constexpr int kOutCols = kDim / (SMW / 4);      // head-dimension columns of dK and dV this warp writes out
+                const int64_t off = ((int64_t(b) * p.seq + row0 + r) * p.kv_heads + head) * kDim + kOutCols * cw;
                 const bool real_row = row0 + r < p.seq;
 #pragma unroll
                 for (int acc = 0; acc < 2; ++acc) {
                     const float f = acc == 0 ? p.scale : 1.0f;
                     uint16_t* dst = (acc == 0 ? p.out0 : p.out1) + off;
 #pragma unroll
-                    for (int c = 0; c < 2; ++c) {
+                    for (int c = 0; c < kOutCols / 32; ++c) {
                         uint32_t v[32];
-                        tmem_ld_32x32b_x32(tmem + lane_base + (acc == 0 ? kAcc0 : kAcc1) + uint32_t(64 * c32 + 32 * c), v);
+                        tmem_ld_32x32b_x32(tmem + lane_base + (acc == 0 ? kAcc0 : kAcc1) + uint32_t(kOutCols * cw + 32 * c), v);
                         tmem_ld_wait();
 #pragma unroll
                         for (int q4 = 0; q4 < 4; ++q4) {
@@ -1216,9 +1240,15 @@ extern "C" int fpt_attention_bwd_routed(void* dq, void* dk, void* dv, const void
             const int64_t n = batch * seq * q_heads * kDim;
             cudaError_t e = cudaMemsetAsync(dq_accum, 0, size_t(n) * sizeof(float), stream);
             if (e != cudaSuccess) return int(e);
-            if (int rc = launch(attention_bwd_pipelined_kernel<M, G, E, EK>, sizeof(PipeSmem), unsigned(kv_heads), map_k, map_v,
-                                map_q_half, map_do_half, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), kBwdThreadsFused))
-                return rc;
+            // sixteen score-mod warps pay where the score-mod is heaviest (the polynomial soft-cap with its analytical
+            // derivative: +7 % on the causal GQA workload) and cost 4-5 % elsewhere; tuning key value 2 forces them
+            const bool wide = fpt::tuning_attention_bwd_fused() == 2 || (M == 0 && G == 0);
+            const int rc = wide
+                ? launch(attention_bwd_pipelined_kernel<M, G, E, EK, 16>, sizeof(PipeSmem), unsigned(kv_heads), map_k, map_v,
+                         map_q_half, map_do_half, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), pipe_threads(16))
+                : launch(attention_bwd_pipelined_kernel<M, G, E, EK, 8>, sizeof(PipeSmem), unsigned(kv_heads), map_k, map_v,
+                         map_q_half, map_do_half, static_cast<uint16_t*>(dk), static_cast<uint16_t*>(dv), pipe_threads(8));
+            if (rc) return rc;
             int64_t grid = (n / 8 + 255) / 256;
             const int64_t cap = int64_t(dev.sm_count) * 16;
             if (grid > cap) grid = cap;

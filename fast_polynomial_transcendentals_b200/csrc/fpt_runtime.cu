@@ -157,7 +157,7 @@ int fpt_set_tuning(const char* key, int value) {
     if (!std::strcmp(key, "streaming")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_streaming = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_split")) { if (value < 0 || value > 2) return FPT_ERR_BAD_SIZE; fpt::g_attention_split = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_raster")) { if (value < -1 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_raster = value; return FPT_OK; }
-    if (!std::strcmp(key, "attention_bwd_fused")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_bwd_fused = value; return FPT_OK; }
+    if (!std::strcmp(key, "attention_bwd_fused")) { if (value < 0 || value > 2) return FPT_ERR_BAD_SIZE; fpt::g_attention_bwd_fused = value; return FPT_OK; }
     if (!std::strcmp(key, "rope_heads_per_block")) { if (value < 0 || value > 65535) return FPT_ERR_BAD_SIZE; fpt::g_rope_heads_per_block = value; return FPT_OK; }
     if (!std::strcmp(key, "gate_up_tile_rows")) { if (value != 0 && value != 128 && value != 256) return FPT_ERR_BAD_SIZE; fpt::g_gate_up_tile_rows = value; return FPT_OK; }
     if (!std::strcmp(key, "attention_cta_pair")) { if (value < 0 || value > 1) return FPT_ERR_BAD_SIZE; fpt::g_attention_cta_pair = value; return FPT_OK; }

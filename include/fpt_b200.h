@@ -386,7 +386,8 @@ int fpt_selftest_bounded_wait(void* status, void* report, int64_t limit_ns, int 
  * streamed tensors exceed 64 MB, heads otherwise);
  * key "rope_heads_per_block": heads of Q and of K that one block of the fused RoPE rotates (default 8; 0 = all heads);
  * key "attention_bwd_fused": 1 (default) lets the attention backward take its one-pass form when the workspace allows, 0
- * keeps the deterministic two-pass form whatever the workspace;
+ * keeps the deterministic two-pass form whatever the workspace, 2 is 1 with sixteen score-mod warps per block in every mode
+ * (the default uses sixteen for the polynomial soft-cap with the analytical derivative and eight elsewhere; same results);
  * key "attention_cta_pair": 1 runs the attention forward on pairs of CTAs (clusters of two, tcgen05 cta_group::2: one
  * 256-row product per pair, every K and V tile split between the two SMs) wherever two blocks share their K / V (two
  * query heads of one K / V group; two row blocks of one head without a mask), 0 (default) never: same bits; 0.85-1.00x the

@@ -188,6 +188,14 @@ def test_single_pass_backward_matches_the_cpu_restatement_and_the_two_pass_form(
     assert torch.equal(one[1], two[1]) and torch.equal(one[2], two[2]), "dK / dV of the two forms must be the same bits"
     gap = (one[0].float() - two[0].float()).abs().max()
     assert float(gap) <= 2.0 ** -7 * float(two[0].float().abs().max()), float(gap)
+    # tuning key 2: the same kernel with sixteen score-mod warps per block instead of eight: dK and dV the same bits again
+    assert lib.fpt_set_tuning(b"attention_bwd_fused", 2) == 0
+    try:
+        wide = backward(fpt, cuda, q, k, v, out, lse, dout, mode, causal, scale, softcap, log2_n, softcap_grad, single_pass=True)
+    finally:
+        assert lib.fpt_set_tuning(b"attention_bwd_fused", 1) == 0
+    close(wide[0], want_dq, "dq, sixteen score-mod warps")
+    assert torch.equal(wide[1], two[1]) and torch.equal(wide[2], two[2])
     # with the tuning key off the same call, large workspace and all, takes the two-pass form: bits equal
     assert lib.fpt_set_tuning(b"attention_bwd_fused", 0) == 0
     try:
