@@ -3,7 +3,8 @@
 // One CTA owns 256 query rows (two 128-row tiles, "slots") of one (batch, query head) and walks the key/value
 // sequence in tiles of 128 keys:
 //   warp 0        TMA producer: Q once, then K and V tiles into a 2-stage shared-memory ring (no multicast)
-//   warp 1        single-thread UMMA issuer: S = Q K^T into tensor memory, O += P V with P read from tensor memory
+//   warp 1        UMMA issuer (the warp runs converged, an elected lane issues): S = Q K^T into tensor memory,
+//                 O += P V with P read from tensor memory
 //   warps 2..3    idle (they complete the first warpgroup, which gives most of its registers away)
 //   warps 4..7    softmax / score-mod warpgroup of slot 0 (thread = one query row = one tensor-memory lane)
 //   warps 8..11   the same for slot 1

@@ -10,7 +10,7 @@
 // Written once in terms of "fixed" tiles X, Y (loaded once) and "streamed" tiles U, W (2-stage ring):
 //   S = X U^T and dP = Y W^T (both operands K-major from shared memory),
 //   acc0 += dS U and (WHICH = 1) acc1 += P W, with P / dS read from tensor memory and U / W as MN-major operands.
-// Roles: warp 0 TMA producer, warp 1 single-thread tcgen05.mma issuer, warps 4..11 score-mod warps: thread = one
+// Roles: warp 0 TMA producer, warp 1 tcgen05.mma issuer (converged warp, elected lane), warps 4..11 score-mod warps: thread = one
 // tensor-memory lane (row of the fixed tile), warps w and w+4 share a lane quarter and split the 128 columns in halves
 // (the backward has no row reduction, so the split needs no exchange).
 // Tensor memory: S is never overwritten (each score-mod warp writes its bf16 dS and P words over its own 64 columns of

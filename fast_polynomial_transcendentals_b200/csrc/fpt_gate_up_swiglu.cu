@@ -7,7 +7,7 @@
 // the same hidden columns, so that one tcgen05.mma of shape 128 x 256 x 16 feeds both and the epilogue finds a gate
 // value and its up value in the same lane.
 //   warp 0      TMA producer: x tile [128 HALVES x 64] and the two weight tiles [128 x 64] per K block into a ring
-//   warp 1      single-thread tcgen05.mma issuer (both operands K-major from shared memory, 128-byte swizzle)
+//   warp 1      tcgen05.mma issuer, converged warp with an elected lane (both operands K-major from shared memory, 128-byte swizzle)
 //   warp 2      allocates tensor memory (512 columns = two accumulators)
 //   warps 4..   epilogue, four warps per accumulator: thread = one row; fp32 -> bf16 (round to nearest even, what a
 //               separate GEMM would have stored), then the same packed polynomial program as fpt_swish_mul, then
